@@ -1,0 +1,631 @@
+// TF32 / 3xTF32 GEMM for sm_100a: TMA-fed shared-memory tiles, tcgen05.mma accumulating in
+// tensor memory, fused epilogue.
+//
+// One persistent CTA per SM walks a list of 128 x BN output tiles.  Inside a CTA:
+//   warp 0     producer   one lane issues cp.async.bulk.tensor (TMA) loads of A and B k-blocks
+//                         (32 fp32 = one 128-byte swizzle row per k-block) into a ring of stages
+//   warp 1     MMA        one lane issues tcgen05.mma.kind::tf32 (K = 8 per instruction) into
+//                         one of two tensor-memory accumulators; tcgen05.commit hands stages
+//                         back to the producer and finished accumulators to the epilogue
+//   warps 2-5  epilogue   tcgen05.ld the accumulator (lane = row), apply alpha / bias /
+//                         ReLU / GELU / causal mask / accumulate, store to global
+// so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+// NN / NT / TN are read straight from the row-major buffers: an operand whose contraction
+// index is contiguous in memory is "K-major" (one TMA box of 32 x rows), the other kind is
+// "MN-major" (rows/32 boxes of 32 x 32, 4 KB each, in the 32-byte-chunk swizzle that fp32
+// MN-major operands require); the instruction descriptor's major bits tell the tensor core
+// which is which.  No transpose is materialised.
+//
+// 3xTF32: the operands are split beforehand into hi = x & 0xffffe000 and lo = x - hi (both
+// exact); each k-step issues lo*hi, hi*lo, hi*hi into the same accumulator.
+//
+// Every wait in the kernel is bounded: when a limit runs out the waiting thread raises the
+// CTA's abort flag and the context's status word (GT_ERR_TIMEOUT), all roles leave their
+// loops, copies in flight are waited for (bounded), tensor memory is freed, the CTA returns.
+//
+// Replaces: gradtuity/kernels_triton/matmul_kernels.py:18-400 (five kernels, 32x32x32 tiles,
+// tl.dot) and gradtuity/kernels_cuda/matmul_kernels.py:21-236.
+
+#include "gt_internal.h"
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;                       // fp32 elements per k-block = 128 bytes
+constexpr int UMMA_K = 8;                    // tf32 elements per tcgen05.mma
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_STAGES = 8;
+constexpr int SMEM_BUDGET = 232448 - 1024 - 512;   // 227 KB minus alignment slack and barriers
+constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;   // about 1.5 s at 1.9 GHz
+
+struct UmmaParams {
+  float* C; const float* bias; float* aux;
+  long long ldc, sC0, sC1;
+  int M, N, K;
+  int batch0;
+  int tiles_m, tiles_n, num_tiles;
+  int group_m;
+  int epilogue, accumulate, vec_ok;
+  float alpha;
+  int* status;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      atomicExch(status, GT_ERR_TIMEOUT);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets
+// (all >> 4), descriptor version 1 at bit 46, swizzle mode at bits 61-63.
+//   K-major operand : 128-byte swizzle of 16-byte chunks (mode 2); rows of 128 bytes, groups of
+//                     8 rows SBO = 1024 bytes apart; LBO unused.
+//   MN-major operand: fp32 allows only the 128-byte swizzle of 32-byte chunks (mode 1); k-rows of
+//                     128 bytes (32 MN elements), groups of 4 k-rows SBO = 512 bytes apart, the
+//                     next 32 MN elements LBO bytes further.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle_mode) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)swizzle_mode << 61;
+  return d;
+}
+
+// Instruction descriptor, kind::tf32: D = fp32 (1 at bit 4), A and B = tf32 (2 at bits 7
+// and 10), operand major bits 15 / 16 (1 = MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int BN, bool X3>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 4;                 // 16 KB
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (X3 ? 2 : 1);
+  static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > MAX_STAGES ? MAX_STAGES : STAGES_RAW;
+  static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);   // 128 / 256 / 512: powers of two
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
+};
+
+// Tile list order: groups of `group_m` row-tiles sweep all column-tiles before the next
+// group starts, so CTAs that run together share A and B panels in L2.
+__device__ __forceinline__ void tile_coords(const UmmaParams& p, int tile, int& batch, int& tm, int& tn) {
+  const int per_batch = p.tiles_m * p.tiles_n;
+  batch = tile / per_batch;
+  const int t = tile - batch * per_batch;
+  const int group_size = p.group_m * p.tiles_n;
+  const int g = t / group_size;
+  const int first_m = g * p.group_m;
+  const int rows = min(p.tiles_m - first_m, p.group_m);
+  const int r = t - g * group_size;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+template <int BN>
+__device__ __forceinline__ bool tile_is_masked(const UmmaParams& p, int tm, int tn) {
+  return p.epilogue == GT_EPI_CAUSAL && (tn * BN > tm * BM + BM - 1);
+}
+
+template <int BN, bool A_MN, bool B_MN, bool X3>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
+                    const UmmaParams p) {
+  using C = Cfg<BN, X3>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint8_t* ctrl = smem_aligned + STAGES * C::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);              // full[S], empty[S], tfull[2], tempty[2], drain
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * MAX_STAGES + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * MAX_STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  const uint32_t bar_drain = bar_tempty + 16;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 128);
+    }
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int batch, tm, tn;
+        tile_coords(p, tile, batch, tm, tn);
+        if (tile_is_masked<BN>(p, tm, tn)) continue;
+        const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+        const int m0 = tm * BM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+          const uint32_t full = bar_full + 8 * s;
+          mbar_expect_tx(full, C::STAGE_BYTES);
+          const uint32_t sa = smem_base + s * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_BYTES * (X3 ? 2 : 1);
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 32; ++j) {
+              tma_load_4d(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
+              if (X3) tma_load_4d(sa + C::A_BYTES + j * 4096, &map_a_lo, full, m0 + 32 * j, k0, i0, i1);
+            }
+          } else {
+            tma_load_4d(sa, &map_a, full, k0, m0, i0, i1);
+            if (X3) tma_load_4d(sa + C::A_BYTES, &map_a_lo, full, k0, m0, i0, i1);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j) {
+              tma_load_4d(sb + j * 4096, &map_b, full, n0 + 32 * j, k0, i0, i1);
+              if (X3) tma_load_4d(sb + C::B_BYTES + j * 4096, &map_b_lo, full, n0 + 32 * j, k0, i0, i1);
+            }
+          } else {
+            tma_load_4d(sb, &map_b, full, k0, n0, i0, i1);
+            if (X3) tma_load_4d(sb + C::B_BYTES, &map_b_lo, full, k0, n0, i0, i1);
+          }
+          ++issued;
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Aborting: let the loads already issued land before shared memory is released.
+        long long first = issued > STAGES ? issued - STAGES : 0;
+        for (long long i = first; i < issued; ++i) {
+          const int st = (int)(i % STAGES);
+          const uint32_t par = (uint32_t)((i / STAGES) & 1);
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar_full + 8 * st, par) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN, A_MN, B_MN);
+      int s = 0; uint32_t ph = 0;
+      int acc = 0; uint32_t aph = 0;
+      bool ok = true;
+      bool any_issued = false;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int batch, tm, tn;
+        tile_coords(p, tile, batch, tm, tn);
+        if (tile_is_masked<BN>(p, tm, tn)) continue;
+        if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::A_BYTES * (X3 ? 2 : 1);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // K-major: the 8 k-values of this step are 32 bytes further along each 128-byte row.
+            // MN-major: they are the next 8 rows (1024 bytes) of every 32-wide column of atoms.
+            const uint32_t a_off = A_MN ? kk * 1024 : kk * 32;
+            const uint32_t b_off = B_MN ? kk * 1024 : kk * 32;
+            const uint32_t a_lbo = A_MN ? 4096 : 16, b_lbo = B_MN ? 4096 : 16;
+            const uint32_t a_sbo = A_MN ? 512 : 1024, b_sbo = B_MN ? 512 : 1024;
+            const uint32_t a_sw = A_MN ? 1 : 2, b_sw = B_MN ? 1 : 2;
+            const uint64_t ad = make_smem_desc(sa + a_off, a_lbo, a_sbo, a_sw);
+            const uint64_t bd = make_smem_desc(sb + b_off, b_lbo, b_sbo, b_sw);
+            const uint32_t first = (kb | kk) != 0 ? 1u : 0u;
+            if (X3) {
+              const uint64_t ad_lo = make_smem_desc(sa + C::A_BYTES + a_off, a_lbo, a_sbo, a_sw);
+              const uint64_t bd_lo = make_smem_desc(sb + C::B_BYTES + b_off, b_lbo, b_sbo, b_sw);
+              tc_mma_tf32(d_tmem, ad_lo, bd, idesc, first);
+              tc_mma_tf32(d_tmem, ad, bd_lo, idesc, 1u);
+              tc_mma_tf32(d_tmem, ad, bd, idesc, 1u);
+            } else {
+              tc_mma_tf32(d_tmem, ad, bd, idesc, first);
+            }
+          }
+          any_issued = true;
+          tc_commit(bar_empty + 8 * s);          // stage reusable once these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(bar_tfull + 8 * acc);          // accumulator complete
+        if (++acc == 2) { acc = 0; aph ^= 1u; }
+      }
+      if (!ok && any_issued) {
+        // Aborting: wait (bounded) until the tensor core has retired what was issued.
+        tc_commit(bar_drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
+    int acc = 0; uint32_t aph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int batch, tm, tn;
+      tile_coords(p, tile, batch, tm, tn);
+      const bool masked = tile_is_masked<BN>(p, tm, tn);
+      const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * BN;
+      if (!masked) {
+        if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+      }
+      const long long row_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1 + (long long)row * p.ldc;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int nb = n0 + c * 32;
+        if (nb >= p.N) break;
+        float v[32];
+        if (!masked) {
+          tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+        }
+        if (!row_ok) continue;
+        const bool full_chunk = (nb + 32 <= p.N);
+        float* cptr = p.C + row_off + nb;
+        const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
+        if (full_chunk && p.vec_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 x = make_float4(p.alpha * v[j], p.alpha * v[j + 1], p.alpha * v[j + 2], p.alpha * v[j + 3]);
+            if (has_bias) {
+              const float4 b = *reinterpret_cast<const float4*>(p.bias + nb + j);
+              x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+            }
+            if (p.aux) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
+            if (p.epilogue == GT_EPI_BIAS_RELU) {
+              x.x = fmaxf(x.x, 0.0f); x.y = fmaxf(x.y, 0.0f); x.z = fmaxf(x.z, 0.0f); x.w = fmaxf(x.w, 0.0f);
+            } else if (p.epilogue == GT_EPI_BIAS_GELU) {
+              x.x = gt_gelu_tanh(x.x); x.y = gt_gelu_tanh(x.y); x.z = gt_gelu_tanh(x.z); x.w = gt_gelu_tanh(x.w);
+            } else if (p.epilogue == GT_EPI_CAUSAL) {
+              const int col = nb + j;
+              if (col > row) x.x = GT_CAUSAL_MASK_VALUE;
+              if (col + 1 > row) x.y = GT_CAUSAL_MASK_VALUE;
+              if (col + 2 > row) x.z = GT_CAUSAL_MASK_VALUE;
+              if (col + 3 > row) x.w = GT_CAUSAL_MASK_VALUE;
+            }
+            float4* dst = reinterpret_cast<float4*>(cptr + j);
+            if (p.accumulate) {
+              const float4 o = *dst;
+              x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+            }
+            *dst = x;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = nb + j;
+            if (col < p.N) {
+              float x = p.alpha * v[j];
+              if (has_bias) x += p.bias[col];
+              if (p.aux) p.aux[row_off + col] = x;
+              if (p.epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
+              else if (p.epilogue == GT_EPI_BIAS_GELU) x = gt_gelu_tanh(x);
+              else if (p.epilogue == GT_EPI_CAUSAL && col > row) x = GT_CAUSAL_MASK_VALUE;
+              if (p.accumulate) x += cptr[j];
+              cptr[j] = x;
+            }
+          }
+        }
+      }
+      if (!masked) {
+        tc_fence_before();
+        mbar_arrive(bar_tempty + 8 * acc);        // 128 arrivals hand the accumulator back
+        if (++acc == 2) { acc = 0; aph ^= 1u; }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+// ---- operand splitting for 3xTF32 ---------------------------------------------------------
+// hi keeps the 19 bits a tf32 operand carries (sign, exponent, 10 mantissa bits), lo = x - hi
+// is exact in fp32.  Rows of `cols` elements with pitch `ld` are packed at pitch `cols_pad`.
+__global__ void gt_split_tf32_kernel(const float* __restrict__ x, float* __restrict__ hi, float* __restrict__ lo,
+                                     long long rows, int cols, long long ld, int cols_pad,
+                                     int batch0, long long s0, long long s1, long long slice_out) {
+  const long long per_slice = rows * cols_pad;
+  const int b = blockIdx.y;
+  const float* src = x + (long long)(b % batch0) * s0 + (long long)(b / batch0) * s1;
+  float* h = hi + (long long)b * slice_out;
+  float* l = lo + (long long)b * slice_out;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_slice; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / cols_pad;
+    const int c = (int)(i - r * cols_pad);
+    float v = c < cols ? src[r * ld + c] : 0.0f;
+    const float vh = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    h[i] = vh;
+    l[i] = v - vh;
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+
+struct OperandView {
+  const float* ptr; long long rows, cols, ld, s0, s1;   // stored (rows, cols), cols contiguous
+};
+
+int encode_map(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int box_cols, int box_rows,
+               long long batch0, long long batch1, bool mn_major) {
+  cuuint64_t dims[4] = {(cuuint64_t)v.cols, (cuuint64_t)v.rows, (cuuint64_t)batch0, (cuuint64_t)batch1};
+  const cuuint64_t slice = (cuuint64_t)v.rows * (cuuint64_t)v.ld * 4ull;
+  cuuint64_t strides[3] = {(cuuint64_t)v.ld * 4ull,
+                           batch0 > 1 ? (cuuint64_t)v.s0 * 4ull : slice,
+                           batch1 > 1 ? (cuuint64_t)v.s1 * 4ull : slice * (cuuint64_t)batch0};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = ctx->encode_tiled(map, ctx->tma_round ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                 4, (void*)v.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    GT_FAIL(ctx, GT_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d): ptr=%p dims=(%llu,%llu,%llu,%llu) strides=(%llu,%llu,%llu) box=(%u,%u)",
+            (int)r, (const void*)v.ptr, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+            (unsigned long long)dims[3], (unsigned long long)strides[0], (unsigned long long)strides[1],
+            (unsigned long long)strides[2], box[0], box[1]);
+  }
+  return GT_OK;
+}
+
+template <int BN, bool A_MN, bool B_MN, bool X3>
+int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[4], const UmmaParams& p, int grid, cudaStream_t stream) {
+  using C = Cfg<BN, X3>;
+  auto kern = gt_gemm_umma_kernel<BN, A_MN, B_MN, X3>;
+  static bool attr_set = false;   // per instantiation; one caller thread per context
+  if (!attr_set) {
+    GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    attr_set = true;
+  }
+  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
+
+template <int BN, bool X3>
+int launch_layout(gt_ctx* ctx, int layout, const CUtensorMap maps[4], const UmmaParams& p, int grid, cudaStream_t stream) {
+  switch (layout) {
+    case GT_LAYOUT_NN: return launch_cfg<BN, false, true, X3>(ctx, maps, p, grid, stream);
+    case GT_LAYOUT_NT: return launch_cfg<BN, false, false, X3>(ctx, maps, p, grid, stream);
+    case GT_LAYOUT_TN: return launch_cfg<BN, true, true, X3>(ctx, maps, p, grid, stream);
+  }
+  return GT_ERR_INVALID_ARG;
+}
+
+int pick_bn(const gt_gemm_args& g, int sms, bool x3) {
+  if (g.N <= 64) return 64;
+  if (g.N <= 128) return 128;
+  const long long batches = g.batch0 * g.batch1;
+  const long long tm = (g.M + BM - 1) / BM;
+  // Cost in "column units per SM": waves x tile width x a per-width efficiency penalty.
+  double best = 1e30; int best_bn = 256;
+  const int cands[3] = {256, 128, 64};
+  const double pen[3] = {1.0, 1.12, 1.45};
+  for (int i = 0; i < 3; ++i) {
+    if (x3 && cands[i] == 256) continue;            // 3xTF32 at 256 leaves only two stages
+    const long long tiles = tm * ((g.N + cands[i] - 1) / cands[i]) * batches;
+    const long long waves = (tiles + sms - 1) / sms;
+    const double cost = (double)waves * cands[i] * pen[i];
+    if (cost < best) { best = cost; best_bn = cands[i]; }
+  }
+  return best_bn;
+}
+
+}  // namespace
+
+bool gt_gemm_umma_eligible(const gt_gemm_args& g) {
+  if (g.precision == GT_PREC_FP32) return false;
+  if (g.M > 0x7fffffffLL || g.N > 0x7fffffffLL || g.K > 0x7fffffffLL) return false;
+  if (g.batch0 * g.batch1 > 0x7fffffffLL) return false;
+  if (((uintptr_t)g.A & 15) || ((uintptr_t)g.B & 15)) return false;
+  if ((g.lda & 3) || (g.ldb & 3)) return false;
+  if (g.batch0 > 1 && ((g.sA0 & 3) || (g.sB0 & 3))) return false;
+  if (g.batch1 > 1 && ((g.sA1 & 3) || (g.sB1 & 3))) return false;
+  // TMA strides are limited to 2^40 bytes.
+  const long long lim = 1LL << 38;
+  if (g.lda >= lim || g.ldb >= lim || g.sA0 >= lim || g.sA1 >= lim || g.sB0 >= lim || g.sB1 >= lim) return false;
+  return true;
+}
+
+int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream) {
+  const bool x3 = g.precision == GT_PREC_TF32X3;
+  const bool a_mn = g.layout == GT_LAYOUT_TN;
+  const bool b_mn = g.layout != GT_LAYOUT_NT;
+  const int bn = pick_bn(g, ctx->sm_count, x3);
+  const long long nbatch = g.batch0 * g.batch1;
+
+  OperandView va, vb;
+  if (a_mn) va = {g.A, g.K, g.M, g.lda, g.sA0, g.sA1}; else va = {g.A, g.M, g.K, g.lda, g.sA0, g.sA1};
+  if (b_mn) vb = {g.B, g.K, g.N, g.ldb, g.sB0, g.sB1}; else vb = {g.B, g.N, g.K, g.ldb, g.sB0, g.sB1};
+
+  CUtensorMap maps[4];
+  long long b0 = g.batch0, b1 = g.batch1;
+  OperandView va_lo = va, vb_lo = vb;
+  if (x3) {
+    // Packed hi/lo copies of both operands in the context's scratch block.
+    const int a_pad = (int)((va.cols + 3) & ~3LL), b_pad = (int)((vb.cols + 3) & ~3LL);
+    const long long a_slice = va.rows * a_pad, b_slice = vb.rows * b_pad;
+    const size_t need = (size_t)(2 * (a_slice + b_slice) * nbatch) * sizeof(float);
+    int rc = gt_workspace_reserve(ctx, need);
+    if (rc != GT_OK) return rc;
+    float* a_hi = (float*)ctx->workspace;
+    float* a_lo = a_hi + a_slice * nbatch;
+    float* b_hi = a_lo + a_slice * nbatch;
+    float* b_lo = b_hi + b_slice * nbatch;
+    const int threads = 256;
+    auto blocks_for = [&](long long n) { long long b = (n + threads - 1) / threads; return (unsigned)(b > 4096 ? 4096 : (b < 1 ? 1 : b)); };
+    if (nbatch > 65535) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "3xTF32 batched GEMM supports at most 65535 slices, got %lld", nbatch);
+    gt_split_tf32_kernel<<<dim3(blocks_for(a_slice), (unsigned)nbatch), threads, 0, stream>>>(
+        va.ptr, a_hi, a_lo, va.rows, (int)va.cols, va.ld, a_pad, (int)g.batch0, va.s0, va.s1, a_slice);
+    gt_split_tf32_kernel<<<dim3(blocks_for(b_slice), (unsigned)nbatch), threads, 0, stream>>>(
+        vb.ptr, b_hi, b_lo, vb.rows, (int)vb.cols, vb.ld, b_pad, (int)g.batch0, vb.s0, vb.s1, b_slice);
+    GT_CUDA_OK(ctx, cudaGetLastError());
+    ctx->launches += 2;
+    va = {a_hi, va.rows, va.cols, a_pad, a_slice, a_slice * g.batch0};
+    va_lo = va; va_lo.ptr = a_lo;
+    vb = {b_hi, vb.rows, vb.cols, b_pad, b_slice, b_slice * g.batch0};
+    vb_lo = vb; vb_lo.ptr = b_lo;
+  }
+
+  const int a_box_c = 32, a_box_r = a_mn ? 32 : BM;
+  const int b_box_c = 32, b_box_r = b_mn ? 32 : bn;
+  int rc;
+  if ((rc = encode_map(ctx, &maps[0], va, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &maps[1], vb, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
+  if (x3) {
+    if ((rc = encode_map(ctx, &maps[2], va_lo, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
+    if ((rc = encode_map(ctx, &maps[3], vb_lo, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
+  } else {
+    maps[2] = maps[0];
+    maps[3] = maps[1];
+  }
+
+  UmmaParams p;
+  p.C = g.C; p.bias = g.bias; p.aux = g.aux;
+  p.ldc = g.ldc; p.sC0 = g.sC0; p.sC1 = g.sC1;
+  p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
+  p.batch0 = (int)g.batch0;
+  p.tiles_m = (int)((g.M + BM - 1) / BM);
+  p.tiles_n = (int)((g.N + bn - 1) / bn);
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * nbatch;
+  if (tiles > 0x7fffffffLL) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: %lld tiles out of range", tiles);
+  p.num_tiles = (int)tiles;
+  p.group_m = 16;
+  p.epilogue = g.epilogue; p.accumulate = g.accumulate;
+  p.alpha = g.alpha;
+  p.status = ctx->d_status;
+  bool vec = (((uintptr_t)g.C & 15) == 0) && (g.ldc % 4 == 0) && (g.sC0 % 4 == 0) && (g.sC1 % 4 == 0);
+  if (g.aux) vec = vec && (((uintptr_t)g.aux & 15) == 0);
+  if (g.bias) vec = vec && (((uintptr_t)g.bias & 15) == 0);
+  p.vec_ok = vec ? 1 : 0;
+  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+
+#define GT_DISPATCH(BN_)                                                                         \
+  return x3 ? launch_layout<BN_, true>(ctx, g.layout, maps, p, grid, stream)                    \
+            : launch_layout<BN_, false>(ctx, g.layout, maps, p, grid, stream)
+  if (bn == 256) { GT_DISPATCH(256); }
+  if (bn == 128) { GT_DISPATCH(128); }
+  GT_DISPATCH(64);
+#undef GT_DISPATCH
+}

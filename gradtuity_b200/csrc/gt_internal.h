@@ -1,0 +1,76 @@
+// Internal declarations shared by the translation units of libgt_b200.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "gt_b200.h"
+
+typedef CUresult (*gt_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                       const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                       const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct gt_ctx {
+  int device;
+  int sm_count;
+  cudaStream_t stream;        // compute stream (non-blocking)
+  int* d_status;              // device status word written by bounded waits that ran out
+  gt_encode_tiled_fn encode_tiled;
+  void* workspace;            // scratch for operand splitting (TF32X3) and split-K partials
+  size_t workspace_bytes;
+  int64_t launches;
+  int tma_round;              // 1: tensor maps use the TFLOAT32 data type (TMA rounds), 0: FLOAT32
+  char last_error[256];
+};
+
+#define GT_CUDA_OK(ctx, expr)                                                              \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess) {                                                               \
+      snprintf((ctx)->last_error, sizeof((ctx)->last_error), "%s: %s (%s:%d)", #expr,      \
+               cudaGetErrorString(_e), __FILE__, __LINE__);                                \
+      return GT_ERR_CUDA;                                                                  \
+    }                                                                                      \
+  } while (0)
+
+#define GT_FAIL(ctx, code, ...)                                                            \
+  do {                                                                                     \
+    snprintf((ctx)->last_error, sizeof((ctx)->last_error), __VA_ARGS__);                   \
+    return (code);                                                                         \
+  } while (0)
+
+// One GEMM problem, fully resolved (used by both kernels).
+struct gt_gemm_args {
+  int layout, epilogue, precision, accumulate;
+  int64_t M, N, K;
+  const float* A; int64_t lda, sA0, sA1;
+  const float* B; int64_t ldb, sB0, sB1;
+  float* C; int64_t ldc, sC0, sC1;
+  int64_t batch0, batch1;
+  const float* bias;
+  float* aux;
+  float alpha;
+};
+
+int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes);
+int gt_gemm_fma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
+int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
+bool gt_gemm_umma_eligible(const gt_gemm_args& g);
+
+// GELU, tanh form, with the branch structure of the reference kernel
+// (gradtuity/kernels_cuda/elemwise_kernels.py:104-125).
+__device__ __forceinline__ float gt_gelu_tanh(float x) {
+  float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  float t;
+  if (u >= 0.0f) {
+    t = 2.0f / (1.0f + __expf(-2.0f * u)) - 1.0f;
+  } else {
+    float e = __expf(2.0f * u);
+    t = (e - 1.0f) / (e + 1.0f);
+  }
+  return 0.5f * x * (1.0f + t);
+}

@@ -1,0 +1,221 @@
+// The small element-wise and reduction kernels that sit beside the GEMMs in the autograd
+// closures of Tensor.matmul / linear / linear_relu / bmm (gradtuity/tensor.py:530-657,
+// 1561-1904): gradient seeding and accumulation, ReLU and its mask, the bias-gradient column
+// sum, the scalar sum used as a test loss.  Plain CUDA, fp32, memory-bound; grids are sized
+// in multiples of the SM count and walk the data with grid-stride loops of float4.
+//
+// fp32 specifications followed: gradtuity/kernels_cuda/elemwise_kernels.py:20-101 (add, mul,
+// relu, relu_backward, relu_mask_mul), gradtuity/kernels_cuda/reduce_kernels.py (sum_all,
+// sum_axis0, add_scalar_inplace, add_bias), gradtuity/kernels_cuda/optim_kernels.py (fill).
+
+#include "gt_internal.h"
+
+namespace {
+
+constexpr int EW_THREADS = 256;
+
+inline unsigned ew_blocks(gt_ctx* ctx, long long n_items) {
+  long long b = (n_items + EW_THREADS - 1) / EW_THREADS;
+  long long cap = (long long)ctx->sm_count * 8;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (unsigned)b;
+}
+
+enum { OP_ADD = 0, OP_MUL = 1, OP_RELU = 2, OP_RELU_MASK_MUL = 3, OP_SCALE = 4, OP_GELU = 5, OP_GELU_BWD = 6 };
+
+template <int OP>
+__device__ __forceinline__ float ew_apply(float a, float b, float s) {
+  if (OP == OP_ADD) return a + b;
+  if (OP == OP_MUL) return a * b;
+  if (OP == OP_RELU) return fmaxf(a, 0.0f);
+  if (OP == OP_RELU_MASK_MUL) return b > 0.0f ? a : 0.0f;        // a = dY, b = Y
+  if (OP == OP_SCALE) return a * s;
+  if (OP == OP_GELU) return gt_gelu_tanh(a);
+  if (OP == OP_GELU_BWD) {                                        // a = dY, b = x
+    float u = 0.7978845608028654f * (b + 0.044715f * b * b * b);
+    float t;
+    if (u >= 0.0f) { t = 2.0f / (1.0f + __expf(-2.0f * u)) - 1.0f; }
+    else { float e = __expf(2.0f * u); t = (e - 1.0f) / (e + 1.0f); }
+    float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * b * b);
+    return a * (0.5f * (1.0f + t) + 0.5f * b * (1.0f - t * t) * du);
+  }
+  return 0.0f;
+}
+
+// out = op(a, b) or out += op(a, b); b may be null for unary ops.
+template <int OP, bool ACC>
+__global__ void __launch_bounds__(EW_THREADS) ew_kernel(float* out, const float* a,
+                                                        const float* b, float s, long long n, int vec) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (vec) {
+    const long long n4 = n >> 2;
+    const float4* a4 = reinterpret_cast<const float4*>(a);
+    const float4* b4 = reinterpret_cast<const float4*>(b);
+    float4* o4 = reinterpret_cast<float4*>(out);
+    for (long long i = tid; i < n4; i += stride) {
+      float4 x = a4[i];
+      float4 y = b ? b4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 r = make_float4(ew_apply<OP>(x.x, y.x, s), ew_apply<OP>(x.y, y.y, s), ew_apply<OP>(x.z, y.z, s), ew_apply<OP>(x.w, y.w, s));
+      if (ACC) { float4 o = o4[i]; r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w; }
+      o4[i] = r;
+    }
+    for (long long i = (n4 << 2) + tid; i < n; i += stride) {
+      float r = ew_apply<OP>(a[i], b ? b[i] : 0.f, s);
+      out[i] = ACC ? out[i] + r : r;
+    }
+  } else {
+    for (long long i = tid; i < n; i += stride) {
+      float r = ew_apply<OP>(a[i], b ? b[i] : 0.f, s);
+      out[i] = ACC ? out[i] + r : r;
+    }
+  }
+}
+
+template <int OP>
+int ew_launch(gt_ctx* ctx, float* out, const float* a, const float* b, float s, long long n, int accumulate) {
+  if (!ctx || !out || !a || n < 0) return GT_ERR_INVALID_ARG;
+  if (n == 0) return GT_OK;
+  const int vec = (((uintptr_t)out | (uintptr_t)a | (uintptr_t)b) & 15) == 0;
+  const unsigned blocks = ew_blocks(ctx, vec ? (n + 3) / 4 : n);
+  if (accumulate) ew_kernel<OP, true><<<blocks, EW_THREADS, 0, ctx->stream>>>(out, a, b, s, n, vec);
+  else ew_kernel<OP, false><<<blocks, EW_THREADS, 0, ctx->stream>>>(out, a, b, s, n, vec);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
+
+__global__ void __launch_bounds__(EW_THREADS) fill_kernel(float* __restrict__ out, float v, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) out[i] = v;
+}
+
+// dst[i] += *scalar (gradient of sum(): gradtuity/tensor.py:1380-1386)
+__global__ void __launch_bounds__(EW_THREADS) add_scalar_kernel(float* __restrict__ dst, const float* __restrict__ scalar, long long n) {
+  const float v = *scalar;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) dst[i] += v;
+}
+
+// out[r, c] = x[r, c] + bias[c]
+__global__ void __launch_bounds__(EW_THREADS) add_bias_kernel(float* __restrict__ out, const float* __restrict__ x,
+                                                              const float* __restrict__ bias, long long rows, int cols) {
+  const long long n = rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    out[i] = x[i] + bias[i % cols];
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.0f;
+  if (w == 0) {
+    t = l < (blockDim.x >> 5) ? red[l] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  }
+  __syncthreads();
+  return t;   // valid in warp 0
+}
+
+// Two-pass deterministic sum: partial sums per block, then one block folds them.
+__global__ void __launch_bounds__(EW_THREADS) sum_partial_kernel(const float* __restrict__ x, float* __restrict__ partial, long long n) {
+  __shared__ float red[32];
+  float v = 0.0f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) v += x[i];
+  float t = block_sum(v, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = t;
+}
+__global__ void __launch_bounds__(EW_THREADS) sum_final_kernel(const float* __restrict__ partial, float* __restrict__ out, int n, int accumulate) {
+  __shared__ float red[32];
+  float v = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) v += partial[i];
+  float t = block_sum(v, red);
+  if (threadIdx.x == 0) *out = accumulate ? *out + t : t;
+}
+
+// db[c] += sum over rows of dY[r, c].  Block = 32 columns x 8 row lanes; grid.y splits the rows.
+__global__ void __launch_bounds__(256) colsum_acc_kernel(float* __restrict__ db, const float* __restrict__ dy,
+                                                         long long rows, int cols, long long ld, int rows_per_block) {
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
+  const long long r0 = (long long)blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block; if (r1 > rows) r1 = rows;
+  float v = 0.0f;
+  if (c < cols) for (long long r = r0 + ry; r < r1; r += 8) v += dy[r * ld + c];
+  red[ry][cx] = v;
+  __syncthreads();
+  if (ry == 0 && c < cols) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i][cx];
+    atomicAdd(db + c, t);
+  }
+}
+
+}  // namespace
+
+extern "C" int gt_fill(gt_ctx* ctx, float* out, float value, int64_t n) {
+  if (!ctx || !out || n < 0) return GT_ERR_INVALID_ARG;
+  if (n == 0) return GT_OK;
+  fill_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(out, value, n);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
+extern "C" int gt_add(gt_ctx* ctx, float* out, const float* a, const float* b, int64_t n, int accumulate) { return b ? ew_launch<OP_ADD>(ctx, out, a, b, 0.f, n, accumulate) : GT_ERR_INVALID_ARG; }
+extern "C" int gt_mul(gt_ctx* ctx, float* out, const float* a, const float* b, int64_t n, int accumulate) { return b ? ew_launch<OP_MUL>(ctx, out, a, b, 0.f, n, accumulate) : GT_ERR_INVALID_ARG; }
+extern "C" int gt_scale(gt_ctx* ctx, float* out, const float* a, float s, int64_t n, int accumulate) { return ew_launch<OP_SCALE>(ctx, out, a, nullptr, s, n, accumulate); }
+extern "C" int gt_relu(gt_ctx* ctx, float* out, const float* a, int64_t n) { return ew_launch<OP_RELU>(ctx, out, a, nullptr, 0.f, n, 0); }
+extern "C" int gt_relu_mask_mul(gt_ctx* ctx, float* out, const float* dy, const float* y, int64_t n, int accumulate) { return y ? ew_launch<OP_RELU_MASK_MUL>(ctx, out, dy, y, 0.f, n, accumulate) : GT_ERR_INVALID_ARG; }
+extern "C" int gt_gelu(gt_ctx* ctx, float* out, const float* a, int64_t n) { return ew_launch<OP_GELU>(ctx, out, a, nullptr, 0.f, n, 0); }
+extern "C" int gt_gelu_backward(gt_ctx* ctx, float* dx, const float* dy, const float* x, int64_t n, int accumulate) { return x ? ew_launch<OP_GELU_BWD>(ctx, dx, dy, x, 0.f, n, accumulate) : GT_ERR_INVALID_ARG; }
+
+extern "C" int gt_add_scalar(gt_ctx* ctx, float* dst, const float* scalar, int64_t n) {
+  if (!ctx || !dst || !scalar || n < 0) return GT_ERR_INVALID_ARG;
+  if (n == 0) return GT_OK;
+  add_scalar_kernel<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(dst, scalar, n);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
+
+extern "C" int gt_add_bias(gt_ctx* ctx, float* out, const float* x, const float* bias, int64_t rows, int64_t cols) {
+  if (!ctx || !out || !x || !bias || rows <= 0 || cols <= 0 || cols > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  add_bias_kernel<<<ew_blocks(ctx, rows * cols), EW_THREADS, 0, ctx->stream>>>(out, x, bias, rows, (int)cols);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
+
+extern "C" int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate) {
+  if (!ctx || !out || !x || n <= 0) return GT_ERR_INVALID_ARG;
+  const unsigned blocks = ew_blocks(ctx, n);
+  int rc = gt_workspace_reserve(ctx, 4096 * sizeof(float));
+  if (rc != GT_OK) return rc;
+  float* partial = (float*)ctx->workspace;
+  sum_partial_kernel<<<blocks, EW_THREADS, 0, ctx->stream>>>(x, partial, n);
+  sum_final_kernel<<<1, EW_THREADS, 0, ctx->stream>>>(partial, out, (int)blocks, accumulate);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 2;
+  return GT_OK;
+}
+
+extern "C" int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld) {
+  if (!ctx || !db || !dy || rows <= 0 || cols <= 0 || cols > 0x7fffffff || ld < cols) return GT_ERR_INVALID_ARG;
+  const unsigned gx = (unsigned)((cols + 31) / 32);
+  long long want_y = ((long long)ctx->sm_count * 4 + gx - 1) / gx;
+  long long max_y = (rows + 63) / 64;
+  if (want_y > max_y) want_y = max_y;
+  if (want_y < 1) want_y = 1;
+  if (want_y > 65535) want_y = 65535;
+  const int rpb = (int)((rows + want_y - 1) / want_y);
+  const unsigned gy = (unsigned)((rows + rpb - 1) / rpb);
+  colsum_acc_kernel<<<dim3(gx, gy), 256, 0, ctx->stream>>>(db, dy, rows, (int)cols, ld, rpb);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}

@@ -1,0 +1,225 @@
+// Context, memory, events and error reporting of libgt_b200.so.
+//
+// Plays the part of the reference's ctypes bindings to libcudart
+// (gradtuity/cuda_mem.py:30-153) and of its event timer (gradtuity/cuda_driver.py:472-511)
+// for the GEMM path, with two differences: allocation is stream-ordered from a pooled
+// allocator (the reference calls cudaMalloc/cudaFree once per tensor,
+// gradtuity/tensor.py:122-126), and every call reports a status instead of ignoring it.
+
+#include <stdlib.h>
+
+#include "gt_internal.h"
+
+extern "C" const char* gt_strerror(int status) {
+  switch (status) {
+    case GT_OK: return "success";
+    case GT_ERR_INVALID_ARG: return "invalid argument";
+    case GT_ERR_CUDA: return "CUDA call failed";
+    case GT_ERR_UNSUPPORTED: return "unsupported request";
+    case GT_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case GT_ERR_NOMEM: return "out of memory";
+    case GT_ERR_NCCL: return "NCCL call failed";
+    case GT_ERR_TOO_LARGE: return "size exceeds the fixed maximum of this entry point";
+    case GT_ERR_NOT_INIT: return "context not initialised";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* gt_last_error(gt_ctx* ctx) { return ctx ? ctx->last_error : "null context"; }
+
+extern "C" int gt_init(int device, gt_ctx** out) {
+  if (!out || device < 0) return GT_ERR_INVALID_ARG;
+  *out = nullptr;
+  gt_ctx* ctx = (gt_ctx*)calloc(1, sizeof(gt_ctx));
+  if (!ctx) return GT_ERR_NOMEM;
+  ctx->device = device;
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
+  if (prop.major != 10) {
+    // The kernels are sm_100a only; there is no fallback for other parts.
+    free(ctx);
+    return GT_ERR_UNSUPPORTED;
+  }
+  ctx->sm_count = prop.multiProcessorCount;
+  if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
+  if (cudaMalloc((void**)&ctx->d_status, sizeof(int)) != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
+  cudaMemset(ctx->d_status, 0, sizeof(int));
+
+  // Keep freed blocks in the pool instead of returning them to the driver at every sync.
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+    uint64_t keep = UINT64_MAX;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+  }
+
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+    cudaFree(ctx->d_status);
+    free(ctx);
+    return GT_ERR_CUDA;
+  }
+  ctx->encode_tiled = (gt_encode_tiled_fn)fn;
+  const char* r = getenv("GRADTUITY_GEMM_TMA_ROUND");
+  // Tensor maps of type TFLOAT32 make the TMA unit round fp32 to tf32 (nearest) on the way into
+  // shared memory; with FLOAT32 maps the tensor core just drops the low 13 mantissa bits, which
+  // biases every product towards zero (measured: 7.7e-4 relative error instead of 2.9e-4).
+  ctx->tma_round = (r && r[0] == '0') ? 0 : 1;
+  *out = ctx;
+  return GT_OK;
+}
+
+extern "C" int gt_destroy(gt_ctx* ctx) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (ctx->workspace) cudaFree(ctx->workspace);
+  cudaFree(ctx->d_status);
+  cudaStreamDestroy(ctx->stream);
+  free(ctx);
+  return GT_OK;
+}
+
+extern "C" void* gt_ctx_stream(gt_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+extern "C" int gt_sm_count(gt_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
+
+extern "C" int gt_device_status(gt_ctx* ctx, int* status) {
+  if (!ctx || !status) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  int h = 0;
+  GT_CUDA_OK(ctx, cudaMemcpy(&h, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (h != 0) GT_CUDA_OK(ctx, cudaMemset(ctx->d_status, 0, sizeof(int)));
+  *status = h;
+  return GT_OK;
+}
+
+extern "C" int gt_launch_count(gt_ctx* ctx, int64_t* count) {
+  if (!ctx || !count) return GT_ERR_INVALID_ARG;
+  *count = ctx->launches;
+  return GT_OK;
+}
+
+int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes) {
+  if (nbytes <= ctx->workspace_bytes) return GT_OK;
+  // Growing is rare (first call at a new largest size); it orders itself against earlier
+  // users of the old block by synchronising the compute stream.
+  GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  if (ctx->workspace) GT_CUDA_OK(ctx, cudaFree(ctx->workspace));
+  ctx->workspace = nullptr;
+  ctx->workspace_bytes = 0;
+  size_t rounded = (nbytes + ((size_t)1 << 21) - 1) & ~(((size_t)1 << 21) - 1);
+  GT_CUDA_OK(ctx, cudaMalloc(&ctx->workspace, rounded));
+  ctx->workspace_bytes = rounded;
+  return GT_OK;
+}
+
+// ---- memory ---------------------------------------------------------------------------
+
+extern "C" int gt_malloc(gt_ctx* ctx, size_t nbytes, void** ptr) {
+  if (!ctx || !ptr) return GT_ERR_INVALID_ARG;
+  *ptr = nullptr;
+  if (nbytes == 0) nbytes = 16;
+  cudaError_t e = cudaMallocAsync(ptr, nbytes, ctx->stream);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    GT_FAIL(ctx, GT_ERR_NOMEM, "cudaMallocAsync(%zu bytes): out of memory", nbytes);
+  }
+  GT_CUDA_OK(ctx, e);
+  return GT_OK;
+}
+
+extern "C" int gt_free(gt_ctx* ctx, void* ptr) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  if (!ptr) return GT_OK;
+  GT_CUDA_OK(ctx, cudaFreeAsync(ptr, ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_memset(gt_ctx* ctx, void* ptr, int value, size_t nbytes) {
+  if (!ctx || (!ptr && nbytes)) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaMemsetAsync(ptr, value, nbytes, ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_memcpy_h2d(gt_ctx* ctx, void* dst, const void* src, size_t nbytes) {
+  if (!ctx || ((!dst || !src) && nbytes)) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+  GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_memcpy_d2h(gt_ctx* ctx, void* dst, const void* src, size_t nbytes) {
+  if (!ctx || ((!dst || !src) && nbytes)) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+  GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_memcpy_h2d_async(gt_ctx* ctx, void* dst, const void* src, size_t nbytes) {
+  if (!ctx || ((!dst || !src) && nbytes)) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_memcpy_d2h_async(gt_ctx* ctx, void* dst, const void* src, size_t nbytes) {
+  if (!ctx || ((!dst || !src) && nbytes)) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_memcpy_d2d(gt_ctx* ctx, void* dst, const void* src, size_t nbytes) {
+  if (!ctx || ((!dst || !src) && nbytes)) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_sync(gt_ctx* ctx) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_host_alloc(gt_ctx* ctx, size_t nbytes, void** ptr) {
+  if (!ctx || !ptr) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaMallocHost(ptr, nbytes ? nbytes : 16));
+  return GT_OK;
+}
+
+extern "C" int gt_host_free(gt_ctx* ctx, void* ptr) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  if (ptr) GT_CUDA_OK(ctx, cudaFreeHost(ptr));
+  return GT_OK;
+}
+
+// ---- events ---------------------------------------------------------------------------
+
+extern "C" int gt_event_create(gt_ctx* ctx, void** ev) {
+  if (!ctx || !ev) return GT_ERR_INVALID_ARG;
+  cudaEvent_t e;
+  GT_CUDA_OK(ctx, cudaEventCreate(&e));
+  *ev = (void*)e;
+  return GT_OK;
+}
+
+extern "C" int gt_event_destroy(gt_ctx* ctx, void* ev) {
+  if (!ctx || !ev) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaEventDestroy((cudaEvent_t)ev));
+  return GT_OK;
+}
+
+extern "C" int gt_event_record(gt_ctx* ctx, void* ev) {
+  if (!ctx || !ev) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaEventRecord((cudaEvent_t)ev, ctx->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_event_elapsed_ms(gt_ctx* ctx, void* start, void* stop, float* ms) {
+  if (!ctx || !start || !stop || !ms) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaEventSynchronize((cudaEvent_t)stop));
+  GT_CUDA_OK(ctx, cudaEventElapsedTime(ms, (cudaEvent_t)start, (cudaEvent_t)stop));
+  return GT_OK;
+}

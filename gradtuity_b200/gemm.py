@@ -1,0 +1,55 @@
+"""Raw-pointer GEMM calls: the Python face of gt_gemm / gt_gemm_batched.
+
+These take device addresses as ints, the way the reference's kernel launches do
+(`matmul_kernel[grid](a_ptr, b_ptr, c_ptr, M, N, K, strides...)`, gradtuity/tensor.py:576-593),
+but one call covers what there takes a kernel choice, a grid and six strides.
+"""
+
+from __future__ import annotations
+
+import os
+from ctypes import c_void_p
+
+from . import _lib
+from ._lib import (EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RELU, EPI_CAUSAL, EPI_NONE, LAYOUT_NN, LAYOUT_NT,
+                   LAYOUT_TN, PREC_FP32, PREC_TF32, PREC_TF32X3)
+
+_PRECISIONS = {"tf32": PREC_TF32, "3xtf32": PREC_TF32X3, "fp32": PREC_FP32}
+
+
+def default_precision() -> int:
+    """Precision selected by GRADTUITY_GEMM_PRECISION (tf32 | 3xtf32 | fp32); tf32 by default."""
+    name = os.environ.get("GRADTUITY_GEMM_PRECISION", "tf32").lower()
+    if name not in _PRECISIONS:
+        raise ValueError(f"GRADTUITY_GEMM_PRECISION must be one of {sorted(_PRECISIONS)}, got {name!r}")
+    return _PRECISIONS[name]
+
+
+def _p(x):
+    return c_void_p(x) if x else None
+
+
+def gemm(layout: int, M: int, N: int, K: int, a_ptr: int, lda: int, b_ptr: int, ldb: int,
+         c_ptr: int, ldc: int, *, bias_ptr: int = 0, aux_ptr: int = 0, alpha: float = 1.0,
+         accumulate: bool = False, epilogue: int = EPI_NONE, precision: int | None = None) -> None:
+    lib = _lib.load_library()
+    if precision is None:
+        precision = default_precision()
+    _lib.check(lib.gt_gemm(_lib.context(), layout, M, N, K, _p(a_ptr), lda, _p(b_ptr), ldb, _p(c_ptr), ldc,
+                           _p(bias_ptr), _p(aux_ptr), alpha, 1 if accumulate else 0, epilogue, precision, None),
+               "gt_gemm")
+
+
+def gemm_batched(layout: int, M: int, N: int, K: int,
+                 a_ptr: int, lda: int, sa0: int, sa1: int,
+                 b_ptr: int, ldb: int, sb0: int, sb1: int,
+                 c_ptr: int, ldc: int, sc0: int, sc1: int,
+                 batch0: int, batch1: int = 1, *, bias_ptr: int = 0, aux_ptr: int = 0, alpha: float = 1.0,
+                 accumulate: bool = False, epilogue: int = EPI_NONE, precision: int | None = None) -> None:
+    lib = _lib.load_library()
+    if precision is None:
+        precision = default_precision()
+    _lib.check(lib.gt_gemm_batched(_lib.context(), layout, M, N, K, _p(a_ptr), lda, sa0, sa1, _p(b_ptr), ldb, sb0, sb1,
+                                   _p(c_ptr), ldc, sc0, sc1, batch0, batch1, _p(bias_ptr), _p(aux_ptr), alpha,
+                                   1 if accumulate else 0, epilogue, precision, None),
+               "gt_gemm_batched")

@@ -1,0 +1,714 @@
+"""Tensor with GPU storage and autograd: the host-side mirror of gradtuity/tensor.py for the
+GEMM path.
+
+Public surface and behaviour follow the reference (`Tensor(data, shape=None, requires_grad=False,
+name="")`, `.shape/.ptr/.numel/.nbytes/.ndim`, `.backward()`, `.grad`, `.view`, `.detach`,
+`.to_list`, `.item`, and the op methods `matmul`, `bmm`, `linear`, `linear_tied`, `linear_relu`,
+`add`, `relu`, `gelu`, `sum`, `add_bias`, `mul`, `scale` …; gradtuity/tensor.py:164-2734): CUDA
+only, float32 only, contiguous row-major only, rank 1-4, same `ValueError` texts for shape
+mistakes, gradients accumulated into `.grad` buffers that are created zeroed on first use.
+
+What differs is below the method signatures.  Every GEMM is one call into libgt_b200.so
+(`gt_gemm` / `gt_gemm_batched`, tcgen05 + TMA on sm_100a) instead of a `kernel[grid](...)`
+launch of a 32x32x32 Triton/NVRTC kernel; NT and TN operands are read in place; `bmm` is a
+single strided-batched launch instead of a Python loop over slices; bias, ReLU and GELU are
+fused into the producing GEMM's epilogue; memory comes from a stream-ordered pool.  There is
+no Triton, no backend switch and no CPU path.
+"""
+
+from __future__ import annotations
+
+import math
+import struct
+from contextlib import contextmanager
+from ctypes import c_void_p
+from typing import Callable, Optional
+
+from . import _lib
+from . import gemm as _gemm
+from ._lib import (EPI_BIAS, EPI_BIAS_GELU, EPI_BIAS_RELU, EPI_NONE, LAYOUT_NN, LAYOUT_NT, LAYOUT_TN)
+from .cuda_mem import (cuda_device_synchronize, cuda_free, cuda_malloc, cuda_memcpy_dtod, cuda_memcpy_dtoh,
+                       cuda_memcpy_dtoh_into, cuda_memcpy_htod, cuda_memset)
+
+F32 = 4
+
+
+def _call(name: str, *args) -> None:
+    lib = _lib.load_library()
+    _lib.check(getattr(lib, name)(_lib.context(), *args), name)
+
+
+def _vp(ptr: int):
+    return c_void_p(ptr) if ptr else None
+
+
+class Storage:
+    """GPU memory buffer: ptr, nbytes, and ownership (gradtuity/tensor.py:87-101)."""
+
+    __slots__ = ("ptr", "nbytes", "owns", "base")
+
+    def __init__(self, ptr: int, nbytes: int, owns: bool = True, base: "Storage | None" = None) -> None:
+        self.ptr = ptr
+        self.nbytes = nbytes
+        self.owns = owns
+        # A non-owning view keeps its owner alive; with a pooled, stream-ordered allocator a
+        # freed block can be handed out again at once, so a view must never outlive its owner.
+        self.base = base
+
+    def free(self) -> None:
+        if self.owns and self.ptr:
+            cuda_free(self.ptr)
+            self.ptr = 0
+
+    def __del__(self) -> None:
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def _validate_shape(shape: tuple[int, ...]) -> None:
+    if len(shape) not in (1, 2, 3, 4):
+        raise ValueError(f"Only rank 1, 2, 3, or 4 tensors supported, got rank {len(shape)}")
+    for i, dim in enumerate(shape):
+        if dim <= 0:
+            raise ValueError(f"Dimension {i} must be positive, got {dim}")
+
+
+def prod(shape: tuple[int, ...]) -> int:
+    return math.prod(shape)
+
+
+def alloc_storage(nbytes: int, zero: bool = False) -> Storage:
+    ptr = cuda_malloc(nbytes)
+    if zero:
+        cuda_memset(ptr, 0, nbytes)
+    return Storage(ptr, nbytes, owns=True)
+
+
+@contextmanager
+def temp_storage(nbytes: int, zero: bool = False):
+    st = alloc_storage(nbytes, zero=zero)
+    try:
+        yield st
+    finally:
+        st.free()
+
+
+def empty_tensor(shape: tuple[int, ...], *, requires_grad: bool = False, zero: bool = False, name: str = "") -> "Tensor":
+    """Allocate a tensor (optionally zero-filled)."""
+    _validate_shape(shape)
+    st = alloc_storage(prod(shape) * F32, zero=zero)
+    return Tensor._wrap(st, shape, requires_grad=requires_grad, name=name)
+
+
+def ensure_grad(t: "Tensor") -> None:
+    """Allocate a zero grad tensor if t.grad is None (gradtuity/tensor.py:152-155)."""
+    if t.grad is None:
+        t.grad = empty_tensor(t.shape, zero=True, requires_grad=False)
+
+
+def accum_grad(t: "Tensor", g: "Tensor") -> None:
+    """t.grad += g (gradtuity/tensor.py:158-161)."""
+    ensure_grad(t)
+    _call("gt_scale", _vp(t.grad.ptr), _vp(g.ptr), 1.0, t.numel, 1)
+
+
+class Tensor:
+    """A float32, contiguous, row-major tensor on the GPU with autograd support."""
+
+    def __init__(self, data, shape: tuple[int, ...] | None = None, requires_grad: bool = False, name: str = "") -> None:
+        if shape is None:
+            shape, flat = self._infer_shape_and_flatten(data)
+        else:
+            flat = self._flatten(data)
+            expected = 1
+            for s in shape:
+                expected *= s
+            if len(flat) != expected:
+                raise ValueError(f"Data has {len(flat)} elements but shape {shape} requires {expected} elements")
+        if len(shape) not in (1, 2, 3, 4):
+            raise ValueError(f"Only rank 1, 2, 3, or 4 tensors supported, got rank {len(shape)}")
+        _validate_shape(tuple(shape))
+        self._shape = tuple(shape)
+        n = len(flat)
+        st = alloc_storage(n * F32)
+        cuda_memcpy_htod(st.ptr, struct.pack(f"{n}f", *flat))
+        self._st = st
+        self.requires_grad = requires_grad
+        self.grad = None
+        self.name = name
+        self._parents = ()
+        self._backward = None
+        self._ctx = None
+
+    # ---- construction helpers -----------------------------------------------------------
+
+    @classmethod
+    def _wrap(cls, st: Storage, shape: tuple[int, ...], requires_grad: bool = False, name: str = "") -> "Tensor":
+        _validate_shape(shape)
+        t = object.__new__(cls)
+        t._st = st
+        t._shape = tuple(shape)
+        t.requires_grad = requires_grad
+        t.grad = None
+        t.name = name
+        t._parents = ()
+        t._backward = None
+        t._ctx = None
+        return t
+
+    @classmethod
+    def _from_ptr(cls, ptr: int, shape: tuple[int, ...], owns_memory: bool = True, requires_grad: bool = False,
+                  name: str = "", base: Storage | None = None) -> "Tensor":
+        st = Storage(ptr, prod(shape) * F32, owns=owns_memory, base=base)
+        return cls._wrap(st, shape, requires_grad=requires_grad, name=name)
+
+    @classmethod
+    def from_numpy(cls, array, requires_grad: bool = False, name: str = "") -> "Tensor":
+        """Upload a numpy array (converted to contiguous float32) in one host-to-device copy.
+
+        Not in the reference, whose constructor walks nested Python lists
+        (gradtuity/tensor.py:192-220); needed to load seeded benchmark inputs of 10^8 elements.
+        """
+        import numpy as np
+
+        a = np.ascontiguousarray(array, dtype=np.float32)
+        t = empty_tensor(tuple(a.shape), requires_grad=requires_grad, name=name)
+        cuda_memcpy_htod(t.ptr, a)
+        return t
+
+    def numpy(self):
+        """Download into a new numpy float32 array of this tensor's shape."""
+        import numpy as np
+
+        out = np.empty(self._shape, dtype=np.float32)
+        cuda_memcpy_dtoh_into(self.ptr, out)
+        return out
+
+    @classmethod
+    def _zeros(cls, shape, requires_grad: bool = False) -> "Tensor":
+        return empty_tensor(tuple(shape), zero=True, requires_grad=requires_grad)
+
+    @classmethod
+    def _zeros_like(cls, t: "Tensor", requires_grad: bool = False) -> "Tensor":
+        return empty_tensor(t.shape, zero=True, requires_grad=requires_grad)
+
+    @classmethod
+    def _ones(cls, shape, requires_grad: bool = False) -> "Tensor":
+        t = empty_tensor(tuple(shape), requires_grad=requires_grad)
+        _call("gt_fill", _vp(t.ptr), 1.0, t.numel)
+        return t
+
+    @classmethod
+    def _ones_like(cls, t: "Tensor", requires_grad: bool = False) -> "Tensor":
+        return cls._ones(t.shape, requires_grad=requires_grad)
+
+    # ---- properties ---------------------------------------------------------------------
+
+    def data_ptr(self) -> int:
+        return self.ptr
+
+    @property
+    def ptr(self) -> int:
+        return self._st.ptr
+
+    @property
+    def shape(self) -> tuple[int, ...]:
+        return self._shape
+
+    @property
+    def numel(self) -> int:
+        return prod(self._shape)
+
+    @property
+    def nbytes(self) -> int:
+        return self._st.nbytes
+
+    @property
+    def ndim(self) -> int:
+        return len(self._shape)
+
+    @property
+    def owns_memory(self) -> bool:
+        storage = getattr(self, "_st", None)
+        if storage is None:
+            raise AttributeError("Tensor has no _st (storage)")
+        return storage.owns
+
+    # ---- autograd -----------------------------------------------------------------------
+
+    def backward(self) -> None:
+        """Back-propagate from this scalar (gradtuity/tensor.py:355-413).
+
+        Same contract as the reference: seeds grad with 1.0, walks the graph in reverse
+        topological order, releases interior nodes as it goes.  The order is built with an
+        explicit stack, so graph depth is not limited by Python's recursion limit.
+        """
+        if self.numel != 1:
+            raise ValueError(f"backward() only works on scalar tensors (numel=1), got numel={self.numel}")
+        if not self.requires_grad:
+            raise RuntimeError(
+                "backward() called on a tensor that doesn't require grad. Set requires_grad=True on leaf tensors."
+            )
+        self.grad = Tensor._ones_like(self)
+
+        visited: set[int] = set()
+        topo: list[Tensor] = []
+        stack: list[tuple[Tensor, int]] = [(self, 0)]
+        visited.add(id(self))
+        while stack:
+            node, i = stack.pop()
+            parents = node._parents
+            if i < len(parents):
+                stack.append((node, i + 1))
+                p = parents[i]
+                if id(p) not in visited:
+                    visited.add(id(p))
+                    stack.append((p, 0))
+            else:
+                topo.append(node)
+
+        for i in range(len(topo) - 1, -1, -1):
+            node = topo[i]
+            if node._backward is not None and node.grad is not None:
+                node._backward(node.grad)
+            if node._parents:
+                node._parents = ()
+                node._backward = None
+                node._ctx = None
+            topo[i] = None
+
+    def _set_graph(self, parents: tuple["Tensor", ...], backward_fn: Callable[["Tensor"], None], ctx: Optional[dict] = None) -> None:
+        """Attach graph fields only if some parent requires grad (gradtuity/tensor.py:415-445)."""
+        self.requires_grad = any(p.requires_grad for p in parents)
+        if self.requires_grad:
+            self._parents = parents
+            self._backward = backward_fn
+            self._ctx = ctx
+
+    def detach(self) -> "Tensor":
+        shared = Storage(self._st.ptr, self._st.nbytes, owns=False, base=self._st)
+        return Tensor._wrap(shared, self._shape, requires_grad=False, name=f"{self.name}_detached" if self.name else "")
+
+    def view(self, new_shape) -> "Tensor":
+        """Same storage, different shape; one dimension may be -1/None (gradtuity/tensor.py:465-524)."""
+        dims = list(new_shape)
+        infer = None
+        product = 1
+        for i, d in enumerate(dims):
+            if d is None or d == -1:
+                if infer is not None:
+                    raise ValueError("view() allows only one dimension to be -1")
+                infer = i
+            else:
+                if d <= 0:
+                    raise ValueError(f"view() dimension {i} must be positive, got {d}")
+                product *= d
+        if infer is not None:
+            inferred = self.numel // product
+            if inferred * product != self.numel:
+                raise ValueError(f"view() shape {tuple(new_shape)} is incompatible with numel {self.numel}")
+            dims[infer] = inferred
+        elif product != self.numel:
+            raise ValueError(f"view() shape {tuple(new_shape)} has {product} elements, but tensor has {self.numel} elements")
+        out = Tensor._from_ptr(self.ptr, tuple(dims), owns_memory=False, requires_grad=False, base=self._st)
+        src = self
+
+        def _backward(out_grad: "Tensor") -> None:
+            if src.requires_grad:
+                accum_grad(src, out_grad)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    # ---- the GEMM family ----------------------------------------------------------------
+
+    def matmul(self, other: "Tensor") -> "Tensor":
+        """C[M,N] = A[M,K] @ B[K,N]; backward dA += dC·Bᵀ (NT), dB += Aᵀ·dC (TN), both read in
+        place and accumulated by the GEMM epilogue (gradtuity/tensor.py:530-657)."""
+        if self.ndim != 2:
+            raise ValueError(f"matmul requires 2D tensors, got self.shape={self._shape}")
+        if other.ndim != 2:
+            raise ValueError(f"matmul requires 2D tensors, got other.shape={other._shape}")
+        if self._shape[1] != other._shape[0]:
+            raise ValueError(
+                f"matmul shape mismatch: {self._shape} @ {other._shape} "
+                f"(inner dimensions {self._shape[1]} vs {other._shape[0]})"
+            )
+        M, K = self._shape
+        _, N = other._shape
+        out = empty_tensor((M, N))
+        _gemm.gemm(LAYOUT_NN, M, N, K, self.ptr, K, other.ptr, N, out.ptr, N)
+        a, b = self, other
+
+        def _backward(g: "Tensor") -> None:
+            if a.requires_grad:
+                ensure_grad(a)
+                _gemm.gemm(LAYOUT_NT, M, K, N, g.ptr, N, b.ptr, N, a.grad.ptr, K, accumulate=True)
+            if b.requires_grad:
+                ensure_grad(b)
+                _gemm.gemm(LAYOUT_TN, K, N, M, a.ptr, K, g.ptr, N, b.grad.ptr, N, accumulate=True)
+
+        out._set_graph(parents=(self, other), backward_fn=_backward)
+        return out
+
+    def bmm(self, other: "Tensor") -> "Tensor":
+        """Batched matmul, rank 3 (B,M,K)@(B,K,N) or rank 4 (B,H,M,K)@(B,H,K,N), as ONE
+        strided-batched launch forward and two backward (the reference loops over slices in
+        Python: gradtuity/tensor.py:760-896)."""
+        ndim = self.ndim
+        if ndim not in (3, 4):
+            raise ValueError(f"bmm requires ndim 3 or 4, got self.ndim={ndim}")
+        if other.ndim != ndim:
+            raise ValueError(f"bmm requires same ndim for both tensors, got {ndim} vs {other.ndim}")
+        if ndim == 3:
+            Bf, M, K = self.shape
+            B2, K2, N = other.shape
+            if B2 != Bf:
+                raise ValueError(f"bmm batch dim mismatch: {self.shape} vs {other.shape}")
+            if K2 != K:
+                raise ValueError(f"bmm inner dim mismatch: a.shape[2]={K} vs b.shape[1]={K2}")
+            out = empty_tensor((Bf, M, N))
+        else:
+            B, H, M, K = self.shape
+            B2, H2, K2, N = other.shape
+            if B2 != B or H2 != H:
+                raise ValueError(f"bmm batch/head dim mismatch: {self.shape} vs {other.shape}")
+            if K2 != K:
+                raise ValueError(f"bmm inner dim mismatch: a.shape[3]={K} vs b.shape[2]={K2}")
+            Bf = B * H
+            out = empty_tensor((B, H, M, N))
+        _gemm.gemm_batched(LAYOUT_NN, M, N, K, self.ptr, K, M * K, 0, other.ptr, N, K * N, 0,
+                           out.ptr, N, M * N, 0, Bf)
+        a, b = self, other
+
+        def _backward(g: "Tensor") -> None:
+            if a.requires_grad:
+                ensure_grad(a)
+                _gemm.gemm_batched(LAYOUT_NT, M, K, N, g.ptr, N, M * N, 0, b.ptr, N, K * N, 0,
+                                   a.grad.ptr, K, M * K, 0, Bf, accumulate=True)
+            if b.requires_grad:
+                ensure_grad(b)
+                _gemm.gemm_batched(LAYOUT_TN, K, N, M, a.ptr, K, M * K, 0, g.ptr, N, M * N, 0,
+                                   b.grad.ptr, N, K * N, 0, Bf, accumulate=True)
+
+        out._set_graph(parents=(self, other), backward_fn=_backward)
+        return out
+
+    def _linear_checks(self, weight: "Tensor", bias: "Tensor", opname: str) -> None:
+        if self.ndim != 2:
+            raise ValueError(f"{opname} requires 2D input, got shape {self._shape}")
+        if weight.ndim != 2:
+            raise ValueError(f"weight must be 2D, got shape {weight._shape}")
+        if bias.ndim != 1:
+            raise ValueError(f"bias must be 1D, got shape {bias._shape}")
+        if self._shape[1] != weight._shape[0]:
+            raise ValueError(f"{opname} shape mismatch: input {self._shape} @ weight {weight._shape}")
+        if weight._shape[1] != bias._shape[0]:
+            raise ValueError(f"bias size {bias._shape[0]} doesn't match weight out_features {weight._shape[1]}")
+
+    def _linear_backward(self, x: "Tensor", weight: "Tensor", bias: "Tensor", dz_ptr: int, M: int, K: int, N: int) -> None:
+        """dX += dZ·Wᵀ (NT), dW += Xᵀ·dZ (TN), db += column sums of dZ (gradtuity/tensor.py:1628-1679)."""
+        if x.requires_grad:
+            ensure_grad(x)
+            _gemm.gemm(LAYOUT_NT, M, K, N, dz_ptr, N, weight.ptr, N, x.grad.ptr, K, accumulate=True)
+        if weight.requires_grad:
+            ensure_grad(weight)
+            _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dz_ptr, N, weight.grad.ptr, N, accumulate=True)
+        if bias.requires_grad:
+            ensure_grad(bias)
+            _call("gt_colsum_acc", _vp(bias.grad.ptr), _vp(dz_ptr), M, N, N)
+
+    def linear(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
+        """Y = X @ W + b with W stored (in_features, out_features); bias fused into the GEMM
+        epilogue (gradtuity/tensor.py:1561-1682)."""
+        self._linear_checks(weight, bias, "linear")
+        M, K = self._shape
+        _, N = weight._shape
+        out = empty_tensor((M, N))
+        _gemm.gemm(LAYOUT_NN, M, N, K, self.ptr, K, weight.ptr, N, out.ptr, N, bias_ptr=bias.ptr, epilogue=EPI_BIAS)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            self._linear_backward(x, weight, bias, g.ptr, M, K, N)
+
+        out._set_graph(parents=(self, weight, bias), backward_fn=_backward)
+        return out
+
+    def linear_relu(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
+        """Y = relu(X @ W + b), one kernel; backward masks dY by [Y > 0] into a temporary and
+        proceeds as `linear` (gradtuity/tensor.py:1781-1904)."""
+        self._linear_checks(weight, bias, "linear_relu")
+        M, K = self._shape
+        _, N = weight._shape
+        out = empty_tensor((M, N))
+        _gemm.gemm(LAYOUT_NN, M, N, K, self.ptr, K, weight.ptr, N, out.ptr, N, bias_ptr=bias.ptr, epilogue=EPI_BIAS_RELU)
+        x = self
+        y = out
+
+        def _backward(g: "Tensor") -> None:
+            with temp_storage(M * N * F32) as st:
+                _call("gt_relu_mask_mul", _vp(st.ptr), _vp(g.ptr), _vp(y.ptr), M * N, 0)
+                self._linear_backward(x, weight, bias, st.ptr, M, K, N)
+
+        out._set_graph(parents=(self, weight, bias), backward_fn=_backward)
+        return out
+
+    def linear_gelu(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
+        """Y = gelu_tanh(X @ W + b) in one kernel that also stores the pre-activation Z, which the
+        backward needs.  Equals the reference's `x.linear(w, b).gelu()` (gpt2/model.py:70,
+        gradtuity/tensor.py:954-984) without the separate 100 MB element-wise passes."""
+        self._linear_checks(weight, bias, "linear_gelu")
+        M, K = self._shape
+        _, N = weight._shape
+        out = empty_tensor((M, N))
+        pre = empty_tensor((M, N))
+        _gemm.gemm(LAYOUT_NN, M, N, K, self.ptr, K, weight.ptr, N, out.ptr, N, bias_ptr=bias.ptr,
+                   aux_ptr=pre.ptr, epilogue=EPI_BIAS_GELU)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            with temp_storage(M * N * F32) as st:
+                _call("gt_gelu_backward", _vp(st.ptr), _vp(g.ptr), _vp(pre.ptr), M * N, 0)
+                self._linear_backward(x, weight, bias, st.ptr, M, K, N)
+
+        out._set_graph(parents=(self, weight, bias), backward_fn=_backward)
+        return out
+
+    def linear_tied(self, weight: "Tensor") -> "Tensor":
+        """Y = X @ Wᵀ with W stored (V, E) (the tied LM head); backward dX += dY·W (NN),
+        dW += dYᵀ·X (TN) (gradtuity/tensor.py:1684-1779)."""
+        if self.ndim != 2:
+            raise ValueError(f"linear_tied requires 2D input, got shape {self._shape}")
+        if weight.ndim != 2:
+            raise ValueError(f"weight must be 2D, got shape {weight._shape}")
+        if self._shape[1] != weight._shape[1]:
+            raise ValueError(
+                f"linear_tied shape mismatch: input last dim {self._shape[1]} != weight last dim {weight._shape[1]}"
+            )
+        M, E = self._shape
+        V, _ = weight._shape
+        out = empty_tensor((M, V))
+        _gemm.gemm(LAYOUT_NT, M, V, E, self.ptr, E, weight.ptr, E, out.ptr, V)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _gemm.gemm(LAYOUT_NN, M, E, V, g.ptr, V, weight.ptr, E, x.grad.ptr, E, accumulate=True)
+            if weight.requires_grad:
+                ensure_grad(weight)
+                _gemm.gemm(LAYOUT_TN, V, E, M, g.ptr, V, x.ptr, E, weight.grad.ptr, E, accumulate=True)
+
+        out._set_graph(parents=(self, weight), backward_fn=_backward)
+        return out
+
+    # ---- element-wise ops beside the GEMMs ------------------------------------------------
+
+    def add(self, other: "Tensor") -> "Tensor":
+        if self.shape != other.shape:
+            raise ValueError(f"Shape mismatch for add: {self.shape} vs {other.shape}")
+        out = empty_tensor(self.shape)
+        _call("gt_add", _vp(out.ptr), _vp(self.ptr), _vp(other.ptr), self.numel, 0)
+        a, b = self, other
+
+        def _backward(g: "Tensor") -> None:
+            if a.requires_grad:
+                accum_grad(a, g)
+            if b.requires_grad:
+                accum_grad(b, g)
+
+        out._set_graph(parents=(self, other), backward_fn=_backward)
+        return out
+
+    def relu(self) -> "Tensor":
+        out = empty_tensor(self.shape)
+        _call("gt_relu", _vp(out.ptr), _vp(self.ptr), self.numel)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _call("gt_relu_mask_mul", _vp(x.grad.ptr), _vp(g.ptr), _vp(x.ptr), x.numel, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def gelu(self, approx: str = "tanh") -> "Tensor":
+        if approx != "tanh":
+            raise ValueError(f'gelu approx must be "tanh" in v1, got {approx!r}')
+        out = empty_tensor(self.shape)
+        _call("gt_gelu", _vp(out.ptr), _vp(self.ptr), self.numel)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _call("gt_gelu_backward", _vp(x.grad.ptr), _vp(g.ptr), _vp(x.ptr), x.numel, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def sum(self) -> "Tensor":
+        """Sum of all elements as a (1,) tensor (gradtuity/tensor.py:1368-1388)."""
+        out = empty_tensor((1,))
+        _call("gt_sum_all", _vp(out.ptr), _vp(self.ptr), self.numel, 0)
+        src = self
+
+        def _backward(g: "Tensor") -> None:
+            if src.requires_grad:
+                ensure_grad(src)
+                _call("gt_add_scalar", _vp(src.grad.ptr), _vp(g.ptr), src.numel)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def add_bias(self, bias: "Tensor") -> "Tensor":
+        if self.ndim != 2:
+            raise ValueError(f"add_bias requires 2D input, got shape {self._shape}")
+        if bias.ndim != 1:
+            raise ValueError(f"bias must be 1D, got shape {bias._shape}")
+        if self._shape[1] != bias._shape[0]:
+            raise ValueError(f"Bias size {bias._shape[0]} doesn't match input features {self._shape[1]}")
+        rows, cols = self._shape
+        out = empty_tensor(self.shape)
+        _call("gt_add_bias", _vp(out.ptr), _vp(self.ptr), _vp(bias.ptr), rows, cols)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                accum_grad(x, g)
+            if bias.requires_grad:
+                ensure_grad(bias)
+                _call("gt_colsum_acc", _vp(bias.grad.ptr), _vp(g.ptr), rows, cols, cols)
+
+        out._set_graph(parents=(self, bias), backward_fn=_backward)
+        return out
+
+    def mul(self, other: "Tensor") -> "Tensor":
+        if self.shape != other.shape:
+            raise ValueError(f"Shape mismatch for mul: {self.shape} vs {other.shape}")
+        out = empty_tensor(self.shape)
+        _call("gt_mul", _vp(out.ptr), _vp(self.ptr), _vp(other.ptr), self.numel, 0)
+        a, b = self, other
+
+        def _backward(g: "Tensor") -> None:
+            if a.requires_grad:
+                ensure_grad(a)
+                _call("gt_mul", _vp(a.grad.ptr), _vp(g.ptr), _vp(b.ptr), a.numel, 1)
+            if b.requires_grad:
+                ensure_grad(b)
+                _call("gt_mul", _vp(b.grad.ptr), _vp(g.ptr), _vp(a.ptr), b.numel, 1)
+
+        out._set_graph(parents=(self, other), backward_fn=_backward)
+        return out
+
+    def scale(self, scalar: float) -> "Tensor":
+        out = empty_tensor(self.shape)
+        _call("gt_scale", _vp(out.ptr), _vp(self.ptr), float(scalar), self.numel, 0)
+        x = self
+        s = float(scalar)
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _call("gt_scale", _vp(x.grad.ptr), _vp(g.ptr), s, x.numel, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def mul_scalar_inplace_(self, scalar: float) -> None:
+        _call("gt_scale", _vp(self.ptr), _vp(self.ptr), float(scalar), self.numel, 0)
+
+    def __add__(self, other: "Tensor") -> "Tensor":
+        return self.add(other)
+
+    def __radd__(self, other: "Tensor") -> "Tensor":
+        return other.add(self)
+
+    def __mul__(self, other):
+        if isinstance(other, Tensor):
+            return self.mul(other)
+        return self.scale(float(other))
+
+    def __rmul__(self, other):
+        return self.__mul__(other)
+
+    def __neg__(self) -> "Tensor":
+        return self.scale(-1.0)
+
+    def __sub__(self, other: "Tensor") -> "Tensor":
+        return self.add(other.scale(-1.0))
+
+    def __rsub__(self, other: "Tensor") -> "Tensor":
+        return other.add(self.scale(-1.0))
+
+    # ---- host access --------------------------------------------------------------------
+
+    def to_list(self) -> list:
+        host = cuda_memcpy_dtoh(self.ptr, self.numel * F32)
+        flat = list(struct.unpack(f"{self.numel}f", host))
+        return self._unflatten(flat, self._shape)
+
+    def item(self) -> float:
+        if self.numel != 1:
+            raise ValueError(f"item() only works for single-element tensors, got {self.numel} elements")
+        return struct.unpack("f", cuda_memcpy_dtoh(self.ptr, F32))[0]
+
+    def __repr__(self) -> str:
+        g = ", requires_grad=True" if self.requires_grad else ""
+        n = f", name={self.name!r}" if self.name else ""
+        return f"Tensor(shape={self._shape}{g}{n})"
+
+    # ---- nested-list plumbing -----------------------------------------------------------
+
+    @staticmethod
+    def _infer_shape_and_flatten(data) -> tuple[tuple[int, ...], list[float]]:
+        shape: list[int] = []
+        probe = data
+        while isinstance(probe, (list, tuple)):
+            shape.append(len(probe))
+            if len(probe) == 0:
+                break
+            probe = probe[0]
+        flat: list[float] = []
+
+        def walk(x, depth: int) -> None:
+            if depth == len(shape):
+                if isinstance(x, (list, tuple)):
+                    raise ValueError("Inconsistent nesting depth in tensor data")
+                flat.append(float(x))
+                return
+            if not isinstance(x, (list, tuple)) or len(x) != shape[depth]:
+                raise ValueError(f"Inconsistent shape at depth {depth}: expected length {shape[depth]}")
+            for y in x:
+                walk(y, depth + 1)
+
+        walk(data, 0)
+        return tuple(shape), flat
+
+    @staticmethod
+    def _flatten(data) -> list[float]:
+        if not isinstance(data, (list, tuple)):
+            return [float(data)]
+        out: list[float] = []
+        stack = [iter(data)]
+        while stack:
+            try:
+                x = next(stack[-1])
+            except StopIteration:
+                stack.pop()
+                continue
+            if isinstance(x, (list, tuple)):
+                stack.append(iter(x))
+            else:
+                out.append(float(x))
+        return out
+
+    @staticmethod
+    def _unflatten(flat: list[float], shape: tuple[int, ...]) -> list:
+        if len(shape) == 1:
+            return list(flat)
+        step = prod(shape[1:])
+        return [Tensor._unflatten(flat[i * step:(i + 1) * step], shape[1:]) for i in range(shape[0])]

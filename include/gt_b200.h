@@ -1,0 +1,175 @@
+/*
+ * gt_b200.h — C ABI of libgt_b200.so, the B200 (sm_100a) GEMM subsystem for the
+ * Gradtuity autograd engine.
+ *
+ * The library replaces, for the matmul family only, what the reference engine reaches
+ * through `gradtuity/kernels.py` (the `kernel[grid](...)` dispatch proxy) and
+ * `gradtuity/kernels_cuda/matmul_kernels.py` / `gradtuity/kernels_triton/matmul_kernels.py`
+ * (the five GEMM kernels), plus the thin slices of `gradtuity/cuda_mem.py` and
+ * `gradtuity/dist/nccl.py` the path needs.  It is loaded from Python with `ctypes.CDLL`
+ * exactly as the reference loads libcudart / libcuda / libnccl.
+ *
+ * Conventions
+ *  - every function returns an int status: 0 = GT_OK, negative = GT_ERR_* (never aborts);
+ *  - all matrices are fp32, row-major; leading dimensions and batch strides are in ELEMENTS;
+ *  - device pointers are plain `void*` / `float*`; the library never owns memory handed to it;
+ *  - `stream` arguments are `cudaStream_t` passed as `void*`; NULL selects the context's
+ *    own compute stream (see gt_ctx_stream);
+ *  - one caller thread per context.
+ */
+#ifndef GT_B200_H
+#define GT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gt_ctx gt_ctx;
+
+/* ---- status codes ------------------------------------------------------------------- */
+#define GT_OK                 0
+#define GT_ERR_INVALID_ARG   -1   /* null pointer, negative size, bad enum                  */
+#define GT_ERR_CUDA          -2   /* a CUDA runtime/driver call failed (see gt_last_error)  */
+#define GT_ERR_UNSUPPORTED   -3   /* valid request this build cannot serve                  */
+#define GT_ERR_TIMEOUT       -4   /* a bounded device-side wait ran out (status word)       */
+#define GT_ERR_NOMEM         -5
+#define GT_ERR_NCCL          -6
+#define GT_ERR_TOO_LARGE     -7   /* size beyond a documented fixed maximum                 */
+#define GT_ERR_NOT_INIT      -8
+
+/* ---- enums -------------------------------------------------------------------------- */
+/* Operand layouts.  Logical op is always C[M,N] (+)= op(A)[M,K] * op(B)[K,N].
+ *   NN: A stored (M,K), B stored (K,N)   — reference `matmul_kernel`, strides (K,1,N,1)
+ *       (gradtuity/tensor.py:576-593)
+ *   NT: A stored (M,K), B stored (N,K)   — reference `matmul_nt_acc_kernel`
+ *       (gradtuity/kernels_triton/matmul_kernels.py:250-323) and the swapped-stride
+ *       `matmul_kernel` call of `linear_tied` (gradtuity/tensor.py:1716-1732)
+ *   TN: A stored (K,M), B stored (K,N)   — reference `matmul_tn_acc_kernel`
+ *       (gradtuity/kernels_triton/matmul_kernels.py:327-400)                              */
+#define GT_LAYOUT_NN 0
+#define GT_LAYOUT_NT 1
+#define GT_LAYOUT_TN 2
+
+/* Epilogues.  v = alpha * acc (+ bias[n]);  aux (if non-NULL) receives v before the
+ * activation;  then the activation / mask;  then C = v or C += v.
+ *   NONE        reference matmul_kernel
+ *   BIAS        reference matmul_bias_kernel        (kernels_triton/matmul_kernels.py:94-168)
+ *   BIAS_RELU   reference matmul_bias_relu_kernel   (kernels_triton/matmul_kernels.py:172-246)
+ *   BIAS_GELU   matmul_bias + gelu_kernel, tanh form (kernels_cuda/elemwise_kernels.py:104-125)
+ *   CAUSAL      per batch slice, entries with n > m are written as GT_CAUSAL_MASK_VALUE
+ *               (the NEG_INF of reference causal_mask_inplace, gradtuity/tensor.py:1316);
+ *               tiles wholly above the diagonal skip the contraction.                      */
+#define GT_EPI_NONE       0
+#define GT_EPI_BIAS       1
+#define GT_EPI_BIAS_RELU  2
+#define GT_EPI_BIAS_GELU  3
+#define GT_EPI_CAUSAL     4
+#define GT_CAUSAL_MASK_VALUE (-1.0e9f)
+
+/* Multiply precision (accumulation is always fp32).
+ *   TF32    one tcgen05.mma kind::tf32 per k-step; parity target: reference Triton path
+ *   TF32X3  operands split hi+lo, three MMAs per k-step; parity target: reference CUDA-C
+ *           path (scalar fp32 FMA) and the float64 oracle
+ *   FP32    plain fp32 FMA on CUDA cores (the kernel that also serves operands TMA cannot
+ *           describe: base not 16-byte aligned or leading dimension not a multiple of 4)   */
+#define GT_PREC_TF32    0
+#define GT_PREC_TF32X3  1
+#define GT_PREC_FP32    2
+
+/* ---- context / runtime (replaces the slices of gradtuity/cuda_mem.py:30-153 and
+ *      gradtuity/cuda_driver.py:214-247,472-511 that the GEMM path uses) ---------------- */
+int         gt_init(int device, gt_ctx** out);
+int         gt_destroy(gt_ctx* ctx);
+const char* gt_strerror(int status);
+const char* gt_last_error(gt_ctx* ctx);            /* detail text of the last failing call */
+void*       gt_ctx_stream(gt_ctx* ctx);            /* the context's compute stream         */
+int         gt_sm_count(gt_ctx* ctx);
+/* Synchronises the compute stream, then returns the device status word in *status
+ * (0, or GT_ERR_TIMEOUT if a kernel's bounded wait ran out) and clears it.               */
+int         gt_device_status(gt_ctx* ctx, int* status);
+
+int gt_malloc(gt_ctx* ctx, size_t nbytes, void** ptr);   /* stream-ordered, pooled          */
+int gt_free(gt_ctx* ctx, void* ptr);
+int gt_memset(gt_ctx* ctx, void* ptr, int value, size_t nbytes);
+int gt_memcpy_h2d(gt_ctx* ctx, void* dst, const void* src, size_t nbytes);   /* blocking   */
+int gt_memcpy_d2h(gt_ctx* ctx, void* dst, const void* src, size_t nbytes);   /* blocking   */
+int gt_memcpy_d2d(gt_ctx* ctx, void* dst, const void* src, size_t nbytes);   /* async      */
+int gt_sync(gt_ctx* ctx);
+int gt_host_alloc(gt_ctx* ctx, size_t nbytes, void** ptr);  /* pinned host memory           */
+int gt_host_free(gt_ctx* ctx, void* ptr);
+int gt_memcpy_h2d_async(gt_ctx* ctx, void* dst, const void* src, size_t nbytes);
+int gt_memcpy_d2h_async(gt_ctx* ctx, void* dst, const void* src, size_t nbytes);
+
+/* cuEvent timing, as gradtuity/cuda_driver.py:472-511 (EventTimer). */
+int gt_event_create(gt_ctx* ctx, void** ev);
+int gt_event_destroy(gt_ctx* ctx, void* ev);
+int gt_event_record(gt_ctx* ctx, void* ev);                 /* on the compute stream       */
+int gt_event_elapsed_ms(gt_ctx* ctx, void* start, void* stop, float* ms); /* syncs on stop */
+
+/* ---- the GEMM family ------------------------------------------------------------------
+ * gt_gemm replaces the five reference kernels
+ *   matmul_kernel / matmul_bias_kernel / matmul_bias_relu_kernel /
+ *   matmul_nt_acc_kernel / matmul_tn_acc_kernel
+ * (gradtuity/kernels_triton/matmul_kernels.py:18-400, gradtuity/kernels_cuda/matmul_kernels.py:21-236)
+ * and their launch wrappers (gradtuity/kernels_cuda/matmul_kernels.py:254-341).
+ *   accumulate = 0 : C  = epilogue(alpha * A*B)      (reference forward kernels)
+ *   accumulate = 1 : C += epilogue(alpha * A*B)      (reference *_acc kernels)
+ *   bias : length N, required for the BIAS* epilogues, else NULL
+ *   aux  : optional (M,N) buffer, leading dimension ldc, that receives the pre-activation
+ */
+int gt_gemm(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+            const float* A, int64_t lda, const float* B, int64_t ldb,
+            float* C, int64_t ldc, const float* bias, float* aux,
+            float alpha, int accumulate, int epilogue, int precision, void* stream);
+
+/* Strided-batched form: batch0 x batch1 independent problems; slice (i1, i0) of operand X
+ * starts at X + i0*strideX0 + i1*strideX1.  One launch replaces the per-slice Python loops of
+ * Tensor.bmm (gradtuity/tensor.py:820-841 forward, :848-893 backward), and two batch strides
+ * let the per-head Q/K/V slices of a (B,S,H,D) projection be read in place, which removes
+ * transpose4d_12 / transpose4d_last2 (gradtuity/nn.py:534-539).                            */
+int gt_gemm_batched(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                    const float* A, int64_t lda, int64_t strideA0, int64_t strideA1,
+                    const float* B, int64_t ldb, int64_t strideB0, int64_t strideB1,
+                    float* C, int64_t ldc, int64_t strideC0, int64_t strideC1,
+                    int64_t batch0, int64_t batch1,
+                    const float* bias, float* aux, float alpha, int accumulate,
+                    int epilogue, int precision, void* stream);
+
+/* Which kernel a call with these arguments would run: 0 = tcgen05/TMA kernel, 1 = fp32 FMA
+ * kernel.  No launch.                                                                       */
+int gt_gemm_path(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                 const float* A, int64_t lda, const float* B, int64_t ldb,
+                 const float* C, int64_t ldc, int precision, int* path);
+
+/* Number of kernels this library has launched on behalf of `ctx` since gt_init. */
+int gt_launch_count(gt_ctx* ctx, int64_t* count);
+
+/* ---- small kernels beside the GEMMs in the autograd closures -------------------------
+ * fp32, element-wise or reductions, all on the context's compute stream.  They restate
+ *   add_kernel / add_inplace_kernel / mul_kernel / mul_scalar_kernel / relu_kernel /
+ *   relu_mask_mul_kernel / gelu_kernel / gelu_backward_kernel
+ *     (gradtuity/kernels_cuda/elemwise_kernels.py:20-141),
+ *   fill_kernel (gradtuity/kernels_cuda/optim_kernels.py), sum_all_kernel, sum_axis0_kernel,
+ *   add_scalar_inplace_kernel, add_bias_kernel (gradtuity/kernels_cuda/reduce_kernels.py).
+ * `accumulate` = 1 turns `out = f(...)` into `out += f(...)`, which is how the reference's
+ * backward closures use them (accum_grad, gradtuity/tensor.py:158-161).                    */
+int gt_fill(gt_ctx* ctx, float* out, float value, int64_t n);
+int gt_add(gt_ctx* ctx, float* out, const float* a, const float* b, int64_t n, int accumulate);
+int gt_mul(gt_ctx* ctx, float* out, const float* a, const float* b, int64_t n, int accumulate);
+int gt_scale(gt_ctx* ctx, float* out, const float* a, float s, int64_t n, int accumulate);
+int gt_relu(gt_ctx* ctx, float* out, const float* a, int64_t n);
+int gt_relu_mask_mul(gt_ctx* ctx, float* out, const float* dy, const float* y, int64_t n, int accumulate);
+int gt_gelu(gt_ctx* ctx, float* out, const float* a, int64_t n);
+int gt_gelu_backward(gt_ctx* ctx, float* dx, const float* dy, const float* x, int64_t n, int accumulate);
+int gt_add_scalar(gt_ctx* ctx, float* dst, const float* scalar, int64_t n);        /* dst[i] += *scalar */
+int gt_add_bias(gt_ctx* ctx, float* out, const float* x, const float* bias, int64_t rows, int64_t cols);
+int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate); /* deterministic */
+int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld); /* db[c] += sum_r dy[r,c] */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GT_B200_H */

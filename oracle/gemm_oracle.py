@@ -1,0 +1,157 @@
+"""float64 numpy oracle for the Gradtuity GEMM path. TEST INFRASTRUCTURE, not product code.
+
+Parity status: PINNED for the kernel-level contracts by the reference's own known answers
+(tests/test_oracle_pins.py re-states, as data, the expectations of
+gradtuity/tests/test_tensor.py:1729-1875 (TestMatmul), gradtuity/tests/test_nn.py:1165-1450
+(TestFusedLinear, TestLinearRelu) and the hashed inputs of
+gradtuity/tests/test_kernels_cuda_phase4.py:27-167).  UNPINNED for anything larger than those
+(GPT-2 activations, loss curves): the reference has no CPU path and no GPU exists in the build
+container, so no reference output could be generated for them.
+
+Each function states which reference code it follows.  All arithmetic is float64 unless a
+function says otherwise; inputs are whatever numpy arrays the caller holds (usually float32).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+CAUSAL_MASK_VALUE = -1.0e9  # NEG_INF of causal_mask_inplace, gradtuity/tensor.py:1316
+
+
+def gelu_tanh(x):
+    """GELU, tanh form: gradtuity/kernels_cuda/elemwise_kernels.py:104-125."""
+    x = np.asarray(x, dtype=np.float64)
+    u = 0.7978845608028654 * (x + 0.044715 * x * x * x)
+    return 0.5 * x * (1.0 + np.tanh(u))
+
+
+def gelu_tanh_grad(x):
+    """d gelu / dx: gradtuity/kernels_cuda/elemwise_kernels.py:127-141."""
+    x = np.asarray(x, dtype=np.float64)
+    u = 0.7978845608028654 * (x + 0.044715 * x * x * x)
+    t = np.tanh(u)
+    du = 0.7978845608028654 * (1.0 + 3.0 * 0.044715 * x * x)
+    return 0.5 * (1.0 + t) + 0.5 * x * (1.0 - t * t) * du
+
+
+def op_a(a, layout):
+    """A as the logical (…, M, K) operand: TN stores it (K, M)."""
+    a = np.asarray(a, dtype=np.float64)
+    return np.swapaxes(a, -1, -2) if layout == "TN" else a
+
+
+def op_b(b, layout):
+    """B as the logical (…, K, N) operand: NT stores it (N, K)."""
+    b = np.asarray(b, dtype=np.float64)
+    return np.swapaxes(b, -1, -2) if layout == "NT" else b
+
+
+def gemm(a, b, layout="NN", *, bias=None, alpha=1.0, epilogue="none", c0=None, return_pre=False):
+    """C (+)= epilogue(alpha * op(A) op(B) (+ bias)).
+
+    layout / kernel it restates:
+      NN  matmul_kernel               gradtuity/kernels_cuda/matmul_kernels.py:21-63
+      NT  matmul_nt_acc_kernel        gradtuity/kernels_cuda/matmul_kernels.py:151-191
+      TN  matmul_tn_acc_kernel        gradtuity/kernels_cuda/matmul_kernels.py:195-236
+    epilogue:
+      "bias"       matmul_bias_kernel       :65-103
+      "bias_relu"  matmul_bias_relu_kernel  :105-146
+      "bias_gelu"  matmul_bias then gelu_kernel (gpt2/model.py:70)
+      "causal"     entries with column > row become CAUSAL_MASK_VALUE (per batch slice)
+    c0: previous contents of C for the accumulate kernels (C += …).
+    Leading axes of a / b are batch axes (Tensor.bmm, gradtuity/tensor.py:760-896).
+    """
+    pre = float(alpha) * np.matmul(op_a(a, layout), op_b(b, layout))
+    if epilogue in ("bias", "bias_relu", "bias_gelu"):
+        pre = pre + np.asarray(bias, dtype=np.float64)
+    out = pre
+    if epilogue == "bias_relu":
+        out = np.maximum(pre, 0.0)
+    elif epilogue == "bias_gelu":
+        out = gelu_tanh(pre)
+    elif epilogue == "causal":
+        m, n = pre.shape[-2], pre.shape[-1]
+        mask = np.arange(n)[None, :] > np.arange(m)[:, None]
+        out = np.where(mask, CAUSAL_MASK_VALUE, pre)
+    elif epilogue not in ("none", "bias"):
+        raise ValueError(epilogue)
+    if c0 is not None:
+        out = np.asarray(c0, dtype=np.float64) + out
+    return (out, pre) if return_pre else out
+
+
+def linear_forward_backward(x, w, b, dy, activation="none"):
+    """Tensor.linear / linear_relu and their backward closures.
+
+    Y = act(X W + b) with W stored (in, out)      gradtuity/tensor.py:1604-1621, :1827-1844
+    dZ = dY (* [Y>0] for relu)                     gradtuity/tensor.py:1851-1866
+    dX = dZ W^T, dW = X^T dZ, db = sum_rows dZ     gradtuity/tensor.py:1632-1679
+    """
+    x = np.asarray(x, np.float64); w = np.asarray(w, np.float64)
+    b = np.asarray(b, np.float64); dy = np.asarray(dy, np.float64)
+    z = x @ w + b
+    if activation == "relu":
+        y = np.maximum(z, 0.0)
+        dz = dy * (y > 0)
+    elif activation == "gelu":
+        y = gelu_tanh(z)
+        dz = dy * gelu_tanh_grad(z)
+    else:
+        y, dz = z, dy
+    return {"y": y, "dx": dz @ w.T, "dw": x.T @ dz, "db": dz.sum(axis=0)}
+
+
+def linear_tied_forward_backward(x, w, dy):
+    """Tensor.linear_tied: logits = X W^T with W stored (V, E); dX = dL W; dW = dL^T X.
+    gradtuity/tensor.py:1716-1776."""
+    x = np.asarray(x, np.float64); w = np.asarray(w, np.float64); dy = np.asarray(dy, np.float64)
+    return {"y": x @ w.T, "dx": dy @ w, "dw": dy.T @ x}
+
+
+def causal_softmax(s):
+    """softmax_with_causal_mask: row i of each (S, S) block attends j <= i, masked outputs are
+    exactly 0.  gradtuity/kernels_cuda/softmax_kernels.py:94-129."""
+    s = np.asarray(s, np.float64)
+    n = s.shape[-1]
+    keep = np.arange(n)[None, :] <= np.arange(s.shape[-2])[:, None]
+    z = np.where(keep, s, -np.inf)
+    z = z - z.max(axis=-1, keepdims=True)
+    e = np.where(keep, np.exp(z), 0.0)
+    return e / e.sum(axis=-1, keepdims=True)
+
+
+def softmax_backward(p, dp):
+    """dS = P * (dP - sum_j P dP): gradtuity/kernels_cuda/softmax_kernels.py:60-92."""
+    p = np.asarray(p, np.float64); dp = np.asarray(dp, np.float64)
+    return p * (dp - (p * dp).sum(axis=-1, keepdims=True))
+
+
+def attention_forward_backward(q, k, v, do):
+    """The batched products of CausalSelfAttention (gradtuity/nn.py:539-547) and their
+    backward (Tensor.bmm backward, gradtuity/tensor.py:848-893): q, k, v, do are (B, H, T, d)."""
+    q = np.asarray(q, np.float64); k = np.asarray(k, np.float64)
+    v = np.asarray(v, np.float64); do = np.asarray(do, np.float64)
+    scale = 1.0 / np.sqrt(q.shape[-1])
+    s = scale * np.matmul(q, np.swapaxes(k, -1, -2))
+    p = causal_softmax(s)
+    o = np.matmul(p, v)
+    dp = np.matmul(do, np.swapaxes(v, -1, -2))
+    dv = np.matmul(np.swapaxes(p, -1, -2), do)
+    ds = softmax_backward(p, dp) * scale
+    dq = np.matmul(ds, k)
+    dk = np.matmul(np.swapaxes(ds, -1, -2), q)
+    return {"s": s, "p": p, "o": o, "dp": dp, "dv": dv, "ds": ds, "dq": dq, "dk": dk}
+
+
+def rel_frobenius(x, ref):
+    """||x - ref||_F / ||ref||_F, the parity metric (<= 1e-3 tf32, <= 1e-5 3xTF32)."""
+    x = np.asarray(x, np.float64); ref = np.asarray(ref, np.float64)
+    den = np.linalg.norm(ref.ravel())
+    return float(np.linalg.norm((x - ref).ravel()) / (den if den > 0 else 1.0))
+
+
+def matmul_f32(a, b):
+    """numpy float32 matmul (OpenBLAS): the CPU path the reference's tests compare against
+    (np.matmul, gradtuity/tests/test_tensor.py:1284,1301). Timed as the CPU baseline."""
+    return np.matmul(np.asarray(a, np.float32), np.asarray(b, np.float32))
