@@ -1,0 +1,381 @@
+#!/usr/bin/env python
+"""Headline benchmark: fp32 GEMM M = N = K = 8192 in tf32 mode on B200, through libgt_b200.so.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of
+synthetic input: C = A @ B with A, B ~ N(0, 1/sqrt(K)) from seed 1 (the 8192^3 case of the GEMM
+sweep).  `value` times K steps with the operands resident in HBM (CUDA events on the library's
+compute stream, which is where the kernels are launched).  `e2e` times the same GEMM through the
+Tensor API with HOST operands: every step copies A and B from pinned host memory, runs the GEMM
+and copies C back.  The operands (805 MB per step) are larger than the 126 MB L2, so successive
+steps cannot be served from cache.
+
+N > 1 (launched under torch.distributed.run) runs N independent replicas, one per GPU, with no
+data-path collective ("replicas only": a single GEMM does not shard across data-parallel ranks);
+torch.distributed is used only for the barrier and the max-over-ranks of the device time.
+
+`--impl reference` times the CPU path the reference's tests check against (numpy float32
+matmul, gradtuity/tests/test_tensor.py:1284,1301) on the host cores, on a bounded sample of the
+same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+FLOPS = 2.0 * M * N * K
+ALG_BYTES = 4.0 * (M * K + K * N + M * N)
+# Rows of A used by the CPU legs: same K and N, a quarter of M (275 GFLOP per pass).
+CPU_SAMPLE_ROWS = 2048
+# DRAM bytes (read + write) per launch of the GEMM kernel from the ncu capture summarised in
+# profiles/; None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        # The file holds a measured dense bf16 GEMM rate; kind::tf32 runs at half the bf16 rate.
+        return p["bf16_tflops"] / 2.0, "measured: MEASURED_PEAKS.json bf16_tflops (burst) / 2 for tf32"
+    return 1590.0 / 2.0, "fallback: 1.59 PFLOP/s bf16 / 2 for tf32"
+
+
+def _operands():
+    import numpy as np
+
+    rng = np.random.default_rng(1)
+    a = (rng.standard_normal((M, K), dtype=np.float32) * np.float32(1.0 / np.sqrt(K)))
+    b = (rng.standard_normal((K, N), dtype=np.float32) * np.float32(1.0 / np.sqrt(K)))
+    return a, b
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device = device
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def _dist_setup(world: int):
+    if world <= 1:
+        return None
+    import torch
+    import torch.distributed as dist
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+    return dist
+
+
+def _barrier_max(dist, value_ms: float) -> float:
+    if dist is None:
+        return value_ms
+    import torch
+
+    t = torch.tensor([value_ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    from ctypes import byref, c_float, c_void_p
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+    dist = _dist_setup(world)
+
+    from gradtuity_b200 import _lib
+    from gradtuity_b200 import gemm as G
+    from gradtuity_b200.tensor import Tensor
+
+    lib = _lib.load_library()
+    ctx = _lib.context()
+
+    a_host, b_host = _operands()
+    ta, tb = Tensor.from_numpy(a_host), Tensor.from_numpy(b_host)
+    tc = Tensor._zeros((M, N))
+
+    def ev():
+        e = c_void_p()
+        _lib.check(lib.gt_event_create(ctx, byref(e)), "gt_event_create")
+        return e
+
+    def step():
+        G.gemm(G.LAYOUT_NN, M, N, K, ta.ptr, K, tb.ptr, N, tc.ptr, N, precision=G.PREC_TF32)
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        step()
+    _lib.check(lib.gt_sync(ctx), "gt_sync")
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    e0, e1 = ev(), ev()
+    lib.gt_event_record(ctx, e0)
+    for _ in range(args.steps):
+        step()
+    lib.gt_event_record(ctx, e1)
+    ms = c_float()
+    _lib.check(lib.gt_event_elapsed_ms(ctx, e0, e1, byref(ms)), "gt_event_elapsed_ms")
+    _lib.check(lib.gt_sync(ctx), "gt_sync")
+    launches = _lib.launch_count() - launches0
+    total_ms = _barrier_max(dist, ms.value)
+    _lib.device_status()
+
+    # ---- end to end through the Tensor API with host buffers ----
+    def pinned(shape):
+        p = c_void_p()
+        nbytes = int(np.prod(shape)) * 4
+        _lib.check(lib.gt_host_alloc(ctx, nbytes, byref(p)), "gt_host_alloc")
+        import ctypes
+        arr = np.ctypeslib.as_array((ctypes.c_float * (nbytes // 4)).from_address(p.value)).reshape(shape)
+        return arr, p
+
+    a_pin, pa = pinned((M, K)); b_pin, pb = pinned((K, N)); c_pin, pc = pinned((M, N))
+    a_pin[...] = a_host; b_pin[...] = b_host
+
+    def e2e_step():
+        x = Tensor.from_numpy(a_pin)
+        w = Tensor.from_numpy(b_pin)
+        x.matmul(w).numpy(out=c_pin)
+
+    e2e_steps = max(1, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    if dist is not None:
+        dist.barrier()
+    f0, f1 = ev(), ev()
+    lib.gt_event_record(ctx, f0)
+    for _ in range(e2e_steps):
+        e2e_step()
+    lib.gt_event_record(ctx, f1)
+    ems = c_float()
+    _lib.check(lib.gt_event_elapsed_ms(ctx, f0, f1, byref(ems)), "gt_event_elapsed_ms")
+    e2e_total_ms = _barrier_max(dist, ems.value)
+    clocks = sampler.stop() if rank == 0 else None
+    # parity spot check of what was just timed: 8 rows against float64
+    rows = np.arange(0, M, M // 8)
+    ref = a_host[rows].astype(np.float64) @ b_host.astype(np.float64)
+    err = float(np.linalg.norm(c_pin[rows] - ref) / np.linalg.norm(ref))
+    if err > 1e-3:
+        raise SystemExit(f"parity failure in bench: relative error {err}")
+
+    ms_per_step = total_ms / args.steps
+    value = world * FLOPS / (ms_per_step * 1e-3) / 1e12
+    peak, peak_src = _peaks()
+    achieved = FLOPS / (ms.value / args.steps * 1e-3) / 1e12
+    out = {
+        "metric": "gemm_tf32_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
+        "config": {"workload": "fp32 GEMM sweep, M=N=K=8192, NN, tf32 multiply / fp32 accumulate, one GEMM per step",
+                   "parallelism": "replicas only" if world > 1 else "single GPU",
+                   "l2": "operands 805 MB per step > 126 MB L2, no flush needed",
+                   "inputs": "A, B ~ N(0, 1/sqrt(K)), numpy default_rng(1)"},
+        "clocks": clocks,
+        "e2e": {"value": round(world * FLOPS / (e2e_total_ms / e2e_steps * 1e-3) / 1e12, 3), "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(4 * (M * K + K * N)), "d2h_bytes_per_step": int(4 * M * N),
+                "steps": e2e_steps, "ms_per_step": round(e2e_total_ms / e2e_steps, 3),
+                "api": "Tensor.from_numpy(A).matmul(Tensor.from_numpy(B)).numpy(out=C), pinned host buffers"},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(peak, 2), "unit": "TFLOP/s",
+                     "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "peak_source": peak_src, "algorithmic_flops_per_launch": FLOPS,
+                     "algorithmic_bytes_per_launch": ALG_BYTES,
+                     "frac_of_nominal_1125": round(achieved / 1125.0, 4)},
+        "parity_check": {"rel_frobenius_8_rows_vs_float64": err},
+    }
+    if rank == 0 and world == 1:
+        out["cpu_baseline"] = cpu_baseline(a_host, b_host, reps=3)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out if rank == 0 else None
+
+
+def run_micro(args) -> dict:
+    """Kernel-only timing of one GEMM shape (used for sweeps and as the small case for ncu):
+    `--shape M N K [--layout NN|NT|TN] [--precision tf32|3xtf32|fp32] [--epilogue ...]`."""
+    import numpy as np
+    from ctypes import byref, c_float, c_void_p
+
+    from gradtuity_b200 import _lib
+    from gradtuity_b200 import gemm as G
+    from gradtuity_b200.tensor import Tensor
+
+    lib = _lib.load_library()
+    ctx = _lib.context()
+    m, n, k = args.shape
+    lay = {"NN": 0, "NT": 1, "TN": 2}[args.layout]
+    prec = {"tf32": 0, "3xtf32": 1, "fp32": 2}[args.precision]
+    epi = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu": 3, "causal": 4}[args.epilogue]
+    rng = np.random.default_rng(1)
+    ashape = (k, m) if lay == 2 else (m, k)
+    bshape = (n, k) if lay == 1 else (k, n)
+    ta = Tensor.from_numpy(rng.standard_normal(ashape, dtype=np.float32) / np.float32(np.sqrt(k)))
+    tb = Tensor.from_numpy(rng.standard_normal(bshape, dtype=np.float32) / np.float32(np.sqrt(k)))
+    tbias = Tensor.from_numpy(rng.standard_normal((n,), dtype=np.float32))
+    tc = Tensor._zeros((m, n))
+
+    def step():
+        G.gemm(lay, m, n, k, ta.ptr, ashape[1], tb.ptr, bshape[1], tc.ptr, n, bias_ptr=tbias.ptr if 1 <= epi <= 3 else 0,
+               accumulate=args.accumulate, epilogue=epi, precision=prec)
+
+    for _ in range(args.warmup):
+        step()
+    e0, e1 = c_void_p(), c_void_p()
+    lib.gt_event_create(ctx, byref(e0)); lib.gt_event_create(ctx, byref(e1))
+    lib.gt_event_record(ctx, e0)
+    for _ in range(args.steps):
+        step()
+    lib.gt_event_record(ctx, e1)
+    ms = c_float()
+    _lib.check(lib.gt_event_elapsed_ms(ctx, e0, e1, byref(ms)), "gt_event_elapsed_ms")
+    _lib.device_status()
+    t = ms.value / args.steps
+    flops = 2.0 * m * n * k
+    nbytes = 4.0 * (m * k + k * n + m * n * (2 if args.accumulate else 1))
+    return {"micro": True, "shape": [m, n, k], "layout": args.layout, "precision": args.precision, "epilogue": args.epilogue,
+            "accumulate": bool(args.accumulate), "ms": round(t, 5), "tflops": round(flops / t / 1e9, 2),
+            "gbs": round(nbytes / t / 1e6, 1), "steps": args.steps, "warmup": args.warmup}
+
+
+def _blas_threads() -> int:
+    try:
+        from threadpoolctl import threadpool_info
+
+        n = [i.get("num_threads", 0) for i in threadpool_info() if i.get("user_api") == "blas"]
+        if n:
+            return max(n)
+    except Exception:
+        pass
+    return os.cpu_count() or 1
+
+
+def cpu_baseline(a, b, reps: int) -> dict:
+    """numpy float32 matmul (the oracle's `matmul_f32`) on a row slice of the same operands."""
+    from oracle import gemm_oracle as O
+
+    a_s = a[:CPU_SAMPLE_ROWS]
+    flops = 2.0 * CPU_SAMPLE_ROWS * N * K
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        O.matmul_f32(a_s, b)
+        best = min(best, time.perf_counter() - t0)
+    return {"value": round(flops / best / 1e12, 4), "unit": "TFLOP/s", "cores": _blas_threads(), "kind": "port",
+            "sample": f"numpy float32 A[:{CPU_SAMPLE_ROWS}] @ B of the same 8192^3 operands ({flops / 1e9:.0f} GFLOP), best of {reps}",
+            "seconds_per_pass": round(best, 4)}
+
+
+def run_reference(args) -> dict | None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from oracle import gemm_oracle as O
+
+    a, b = _operands()
+    a_s = a[:CPU_SAMPLE_ROWS]
+    flops = 2.0 * CPU_SAMPLE_ROWS * N * K
+    for _ in range(args.warmup):
+        O.matmul_f32(a_s, b)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.matmul_f32(a_s, b)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = round(flops / dt / 1e12, 4)
+    sample = f"numpy float32 A[:{CPU_SAMPLE_ROWS}] @ B of the 8192^3 operands per step ({flops / 1e9:.0f} GFLOP)"
+    return {
+        "impl": "reference", "metric": "gemm_tf32_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "fp32 GEMM sweep, M=N=K=8192, NN (CPU: bounded row slice of the same operands)"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": _blas_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="kernel-only timing of one GEMM shape")
+    ap.add_argument("--layout", default="NN", choices=["NN", "NT", "TN"])
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
+    ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_relu", "bias_gelu", "causal"])
+    ap.add_argument("--accumulate", action="store_true")
+    args = ap.parse_args()
+    if args.shape:
+        print(json.dumps(run_micro(args)), flush=True)
+        return
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -36,6 +36,7 @@ constexpr int BK = 32;                       // fp32 elements per k-block = 128 
 constexpr int UMMA_K = 8;                    // tf32 elements per tcgen05.mma
 constexpr int NUM_THREADS = 192;
 constexpr int MAX_STAGES = 8;
+constexpr int X3_CHUNK_KB = 8;                // 3xTF32: k-blocks accumulated in tensor memory before an fp32 register add
 constexpr int SMEM_BUDGET = 232448 - 1024 - 512;   // 227 KB minus alignment slack and barriers
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;   // about 1.5 s at 1.9 GHz
 
@@ -184,6 +185,56 @@ __device__ __forceinline__ bool tile_is_masked(const UmmaParams& p, int tm, int 
   return p.epilogue == GT_EPI_CAUSAL && (tn * BN > tm * BM + BM - 1);
 }
 
+// Fused epilogue for 32 consecutive columns of one output row: v holds the accumulator.
+__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float* v, int row, int nb, long long row_off) {
+  const bool full_chunk = (nb + 32 <= p.N);
+  float* cptr = p.C + row_off + nb;
+  const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
+  if (full_chunk && p.vec_ok) {
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      float4 x = make_float4(p.alpha * v[j], p.alpha * v[j + 1], p.alpha * v[j + 2], p.alpha * v[j + 3]);
+      if (has_bias) {
+        const float4 b = *reinterpret_cast<const float4*>(p.bias + nb + j);
+        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+      }
+      if (p.aux) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
+      if (p.epilogue == GT_EPI_BIAS_RELU) {
+        x.x = fmaxf(x.x, 0.0f); x.y = fmaxf(x.y, 0.0f); x.z = fmaxf(x.z, 0.0f); x.w = fmaxf(x.w, 0.0f);
+      } else if (p.epilogue == GT_EPI_BIAS_GELU) {
+        x.x = gt_gelu_tanh(x.x); x.y = gt_gelu_tanh(x.y); x.z = gt_gelu_tanh(x.z); x.w = gt_gelu_tanh(x.w);
+      } else if (p.epilogue == GT_EPI_CAUSAL) {
+        const int col = nb + j;
+        if (col > row) x.x = GT_CAUSAL_MASK_VALUE;
+        if (col + 1 > row) x.y = GT_CAUSAL_MASK_VALUE;
+        if (col + 2 > row) x.z = GT_CAUSAL_MASK_VALUE;
+        if (col + 3 > row) x.w = GT_CAUSAL_MASK_VALUE;
+      }
+      float4* dst = reinterpret_cast<float4*>(cptr + j);
+      if (p.accumulate) {
+        const float4 o = *dst;
+        x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+      }
+      *dst = x;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int col = nb + j;
+      if (col < p.N) {
+        float x = p.alpha * v[j];
+        if (has_bias) x += p.bias[col];
+        if (p.aux) p.aux[row_off + col] = x;
+        if (p.epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
+        else if (p.epilogue == GT_EPI_BIAS_GELU) x = gt_gelu_tanh(x);
+        else if (p.epilogue == GT_EPI_CAUSAL && col > row) x = GT_CAUSAL_MASK_VALUE;
+        if (p.accumulate) x += cptr[j];
+        cptr[j] = x;
+      }
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, bool X3>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -299,43 +350,50 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         int batch, tm, tn;
         tile_coords(p, tile, batch, tm, tn);
         if (tile_is_masked<BN>(p, tm, tn)) continue;
-        if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1u, abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) { ok = false; break; }
+        // tf32: one accumulator per tile.  3xTF32: a fresh accumulator every X3_CHUNK_KB k-blocks,
+        // because the tensor core truncates on every accumulate and the bias grows with the
+        // length of the chain (measured 2.4e-6 relative per 1024 of K).
+        const int chunk_kb = X3 ? X3_CHUNK_KB : num_kb;
+        for (int kb0 = 0; ok && kb0 < num_kb; kb0 += chunk_kb) {
+          if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1u, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_base + s * C::STAGE_BYTES;
-          const uint32_t sb = sa + C::A_BYTES * (X3 ? 2 : 1);
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+          const int kb1 = min(kb0 + chunk_kb, num_kb);
+          for (int kb = kb0; kb < kb1; ++kb) {
+            if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_base + s * C::STAGE_BYTES;
+            const uint32_t sb = sa + C::A_BYTES * (X3 ? 2 : 1);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-            // K-major: the 8 k-values of this step are 32 bytes further along each 128-byte row.
-            // MN-major: they are the next 8 rows (1024 bytes) of every 32-wide column of atoms.
-            const uint32_t a_off = A_MN ? kk * 1024 : kk * 32;
-            const uint32_t b_off = B_MN ? kk * 1024 : kk * 32;
-            const uint32_t a_lbo = A_MN ? 4096 : 16, b_lbo = B_MN ? 4096 : 16;
-            const uint32_t a_sbo = A_MN ? 512 : 1024, b_sbo = B_MN ? 512 : 1024;
-            const uint32_t a_sw = A_MN ? 1 : 2, b_sw = B_MN ? 1 : 2;
-            const uint64_t ad = make_smem_desc(sa + a_off, a_lbo, a_sbo, a_sw);
-            const uint64_t bd = make_smem_desc(sb + b_off, b_lbo, b_sbo, b_sw);
-            const uint32_t first = (kb | kk) != 0 ? 1u : 0u;
-            if (X3) {
-              const uint64_t ad_lo = make_smem_desc(sa + C::A_BYTES + a_off, a_lbo, a_sbo, a_sw);
-              const uint64_t bd_lo = make_smem_desc(sb + C::B_BYTES + b_off, b_lbo, b_sbo, b_sw);
-              tc_mma_tf32(d_tmem, ad_lo, bd, idesc, first);
-              tc_mma_tf32(d_tmem, ad, bd_lo, idesc, 1u);
-              tc_mma_tf32(d_tmem, ad, bd, idesc, 1u);
-            } else {
-              tc_mma_tf32(d_tmem, ad, bd, idesc, first);
+            for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+              // K-major: the 8 k-values of this step are 32 bytes further along each 128-byte row.
+              // MN-major: they are the next 8 rows (1024 bytes) of every 32-wide column of atoms.
+              const uint32_t a_off = A_MN ? kk * 1024 : kk * 32;
+              const uint32_t b_off = B_MN ? kk * 1024 : kk * 32;
+              const uint32_t a_lbo = A_MN ? 4096 : 16, b_lbo = B_MN ? 4096 : 16;
+              const uint32_t a_sbo = A_MN ? 512 : 1024, b_sbo = B_MN ? 512 : 1024;
+              const uint32_t a_sw = A_MN ? 1 : 2, b_sw = B_MN ? 1 : 2;
+              const uint64_t ad = make_smem_desc(sa + a_off, a_lbo, a_sbo, a_sw);
+              const uint64_t bd = make_smem_desc(sb + b_off, b_lbo, b_sbo, b_sw);
+              const uint32_t keep = (kb != kb0 || kk != 0) ? 1u : 0u;   // 0: overwrite the accumulator
+              if (X3) {
+                const uint64_t ad_lo = make_smem_desc(sa + C::A_BYTES + a_off, a_lbo, a_sbo, a_sw);
+                const uint64_t bd_lo = make_smem_desc(sb + C::B_BYTES + b_off, b_lbo, b_sbo, b_sw);
+                tc_mma_tf32(d_tmem, ad_lo, bd, idesc, keep);
+                tc_mma_tf32(d_tmem, ad, bd_lo, idesc, 1u);
+                tc_mma_tf32(d_tmem, ad, bd, idesc, 1u);
+              } else {
+                tc_mma_tf32(d_tmem, ad, bd, idesc, keep);
+              }
             }
+            any_issued = true;
+            tc_commit(bar_empty + 8 * s);          // stage reusable once these MMAs have read it
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
           }
-          any_issued = true;
-          tc_commit(bar_empty + 8 * s);          // stage reusable once these MMAs have read it
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
+          if (!ok) break;
+          tc_commit(bar_tfull + 8 * acc);          // accumulator (chunk) complete
+          if (++acc == 2) { acc = 0; aph ^= 1u; }
         }
-        if (!ok) break;
-        tc_commit(bar_tfull + 8 * acc);          // accumulator complete
-        if (++acc == 2) { acc = 0; aph ^= 1u; }
       }
       if (!ok && any_issued) {
         // Aborting: wait (bounded) until the tensor core has retired what was issued.
@@ -347,6 +405,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     int acc = 0; uint32_t aph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -356,76 +415,66 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int i0 = batch % p.batch0, i1 = batch / p.batch0;
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * BN;
-      if (!masked) {
-        if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
-      }
       const long long row_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1 + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int nb = n0 + c * 32;
-        if (nb >= p.N) break;
-        float v[32];
+      if constexpr (X3) {
+        // The accumulator arrives in K-chunks; they are summed here in fp32 registers
+        // (round-to-nearest adds) before the fused epilogue runs once.
+        float sum[BN];
+#pragma unroll
+        for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
         if (!masked) {
-          tc_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
-          tc_wait_ld();
-        } else {
+          const int nchunks = (num_kb + X3_CHUNK_KB - 1) / X3_CHUNK_KB;
+          for (int ch = 0; ch < nchunks; ++ch) {
+            if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
+            tc_fence_after();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-        }
-        if (!row_ok) continue;
-        const bool full_chunk = (nb + 32 <= p.N);
-        float* cptr = p.C + row_off + nb;
-        const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
-        if (full_chunk && p.vec_ok) {
+            for (int c = 0; c < BN / 32; ++c) {
+              if (n0 + c * 32 < p.N) {
+                float v[32];
+                tc_ld32(lane_base + (uint32_t)(acc * BN + c * 32), v);
+                tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            float4 x = make_float4(p.alpha * v[j], p.alpha * v[j + 1], p.alpha * v[j + 2], p.alpha * v[j + 3]);
-            if (has_bias) {
-              const float4 b = *reinterpret_cast<const float4*>(p.bias + nb + j);
-              x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                for (int j = 0; j < 32; ++j) sum[c * 32 + j] += v[j];
+              }
             }
-            if (p.aux) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
-            if (p.epilogue == GT_EPI_BIAS_RELU) {
-              x.x = fmaxf(x.x, 0.0f); x.y = fmaxf(x.y, 0.0f); x.z = fmaxf(x.z, 0.0f); x.w = fmaxf(x.w, 0.0f);
-            } else if (p.epilogue == GT_EPI_BIAS_GELU) {
-              x.x = gt_gelu_tanh(x.x); x.y = gt_gelu_tanh(x.y); x.z = gt_gelu_tanh(x.z); x.w = gt_gelu_tanh(x.w);
-            } else if (p.epilogue == GT_EPI_CAUSAL) {
-              const int col = nb + j;
-              if (col > row) x.x = GT_CAUSAL_MASK_VALUE;
-              if (col + 1 > row) x.y = GT_CAUSAL_MASK_VALUE;
-              if (col + 2 > row) x.z = GT_CAUSAL_MASK_VALUE;
-              if (col + 3 > row) x.w = GT_CAUSAL_MASK_VALUE;
-            }
-            float4* dst = reinterpret_cast<float4*>(cptr + j);
-            if (p.accumulate) {
-              const float4 o = *dst;
-              x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
-            }
-            *dst = x;
+            tc_fence_before();
+            mbar_arrive(bar_tempty + 8 * acc);
+            if (++acc == 2) { acc = 0; aph ^= 1u; }
           }
-        } else {
+          if (!ok) break;
+        }
+        if (row_ok) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int col = nb + j;
-            if (col < p.N) {
-              float x = p.alpha * v[j];
-              if (has_bias) x += p.bias[col];
-              if (p.aux) p.aux[row_off + col] = x;
-              if (p.epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
-              else if (p.epilogue == GT_EPI_BIAS_GELU) x = gt_gelu_tanh(x);
-              else if (p.epilogue == GT_EPI_CAUSAL && col > row) x = GT_CAUSAL_MASK_VALUE;
-              if (p.accumulate) x += cptr[j];
-              cptr[j] = x;
-            }
+          for (int c = 0; c < BN / 32; ++c) {
+            const int nb = n0 + c * 32;
+            if (nb < p.N) epilogue_chunk(p, &sum[c * 32], row, nb, row_off);
           }
         }
-      }
-      if (!masked) {
-        tc_fence_before();
-        mbar_arrive(bar_tempty + 8 * acc);        // 128 arrivals hand the accumulator back
-        if (++acc == 2) { acc = 0; aph ^= 1u; }
+      } else {
+        if (!masked) {
+          if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int nb = n0 + c * 32;
+          if (nb >= p.N) break;
+          float v[32];
+          if (!masked) {
+            tc_ld32(lane_base + (uint32_t)(acc * BN + c * 32), v);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+          }
+          if (row_ok) epilogue_chunk(p, v, row, nb, row_off);
+        }
+        if (!masked) {
+          tc_fence_before();
+          mbar_arrive(bar_tempty + 8 * acc);        // 128 arrivals hand the accumulator back
+          if (++acc == 2) { acc = 0; aph ^= 1u; }
+        }
       }
     }
   }
@@ -624,7 +673,7 @@ int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream)
 #define GT_DISPATCH(BN_)                                                                         \
   return x3 ? launch_layout<BN_, true>(ctx, g.layout, maps, p, grid, stream)                    \
             : launch_layout<BN_, false>(ctx, g.layout, maps, p, grid, stream)
-  if (bn == 256) { GT_DISPATCH(256); }
+  if (bn == 256 && !x3) return launch_layout<256, false>(ctx, g.layout, maps, p, grid, stream);
   if (bn == 128) { GT_DISPATCH(128); }
   GT_DISPATCH(64);
 #undef GT_DISPATCH

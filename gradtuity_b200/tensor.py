@@ -178,11 +178,15 @@ class Tensor:
         cuda_memcpy_htod(t.ptr, a)
         return t
 
-    def numpy(self):
-        """Download into a new numpy float32 array of this tensor's shape."""
+    def numpy(self, out=None):
+        """Download into a numpy float32 array of this tensor's shape (a new one, or `out`,
+        which may live in pinned host memory)."""
         import numpy as np
 
-        out = np.empty(self._shape, dtype=np.float32)
+        if out is None:
+            out = np.empty(self._shape, dtype=np.float32)
+        elif out.dtype != np.float32 or out.size != self.numel or not out.flags.c_contiguous:
+            raise ValueError("out must be a C-contiguous float32 array with this tensor's number of elements")
         cuda_memcpy_dtoh_into(self.ptr, out)
         return out
 

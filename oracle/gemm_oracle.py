@@ -81,19 +81,24 @@ def gemm(a, b, layout="NN", *, bias=None, alpha=1.0, epilogue="none", c0=None, r
     return (out, pre) if return_pre else out
 
 
-def linear_forward_backward(x, w, b, dy, activation="none"):
+def linear_forward_backward(x, w, b, dy, activation="none", relu_mask=None):
     """Tensor.linear / linear_relu and their backward closures.
 
     Y = act(X W + b) with W stored (in, out)      gradtuity/tensor.py:1604-1621, :1827-1844
     dZ = dY (* [Y>0] for relu)                     gradtuity/tensor.py:1851-1866
     dX = dZ W^T, dW = X^T dZ, db = sum_rows dZ     gradtuity/tensor.py:1632-1679
+
+    relu_mask: optional boolean (M, N) array to use as [Y > 0] instead of the oracle's own.  ReLU
+    is discontinuous: an output within rounding error of zero may have either sign, and the
+    backward of the implementation under test follows ITS forward (as the reference's does,
+    gradtuity/tensor.py:1853-1860), so a backward comparison has to use the same mask.
     """
     x = np.asarray(x, np.float64); w = np.asarray(w, np.float64)
     b = np.asarray(b, np.float64); dy = np.asarray(dy, np.float64)
     z = x @ w + b
     if activation == "relu":
         y = np.maximum(z, 0.0)
-        dz = dy * (y > 0)
+        dz = dy * ((y > 0) if relu_mask is None else np.asarray(relu_mask, bool))
     elif activation == "gelu":
         y = gelu_tanh(z)
         dz = dy * gelu_tanh_grad(z)

@@ -1,0 +1,202 @@
+"""GPU parity: gt_gemm / gt_gemm_batched through the C ABI against the float64 oracle."""
+import numpy as np
+import pytest
+
+from oracle import gemm_oracle as O
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+# ---- the reference's cross-backend kernel cases, now against absolute goldens ---------------
+
+@pytest.mark.parametrize("precision", ["tf32", "3xtf32", "fp32"])
+@pytest.mark.parametrize("kind,M,N,K", U.PHASE4_CASES)
+def test_phase4_cases(gt, kind, M, N, K, precision):
+    layout, a, b, bias, c0 = U.phase4_inputs(kind, M, N, K)
+    epi = {"matmul": "none", "matmul_bias": "bias", "matmul_bias_relu": "bias_relu"}.get(kind, "none")
+    out = U.run_gemm(layout, a, b, bias=bias, c0=c0, epilogue=epi, precision=precision)
+    gold = U.phase4_vectors()[U.phase4_key(kind, M, N, K)]
+    if precision == "tf32":
+        # the tolerance the reference itself uses between its TF32 and fp32 backends
+        # (gradtuity/tests/test_kernels_cuda_phase4.py:48-52)
+        np.testing.assert_allclose(out, gold, rtol=1e-2, atol=1e-3)
+    else:
+        np.testing.assert_allclose(out, gold, rtol=2e-5, atol=2e-6)
+
+
+# ---- shape / layout / epilogue sweep ----------------------------------------------------------
+
+SHAPES = [
+    (128, 128, 32), (128, 64, 64), (256, 256, 256), (128, 256, 96),
+    (1, 1, 1), (1, 64, 8), (3, 5, 7), (17, 33, 19), (40, 24, 36), (63, 65, 127), (129, 257, 255),
+    (300, 500, 200), (64, 1000, 72), (520, 136, 1028), (1024, 768, 64), (1024, 64, 1024),
+]
+
+
+@pytest.mark.parametrize("precision", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_sweep_plain(gt, M, N, K, layout, precision):
+    a, b, _ = U.make_operands(layout, M, N, K, seed=M * 7 + N * 3 + K)
+    out = U.run_gemm(layout, a, b, precision=precision)
+    assert not np.isnan(out).any()
+    assert O.rel_frobenius(out, O.gemm(a, b, layout)) <= U.TOL[precision]
+
+
+@pytest.mark.parametrize("epilogue", ["bias", "bias_relu", "bias_gelu", "causal"])
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (200, 328, 72), (17, 33, 19), (512, 512, 64)])
+def test_sweep_epilogues(gt, M, N, K, layout, epilogue):
+    a, b, rng = U.make_operands(layout, M, N, K, seed=11, scale=1.0 / np.sqrt(K))
+    bias = rng.standard_normal(N).astype(np.float32) if epilogue != "causal" else None
+    out = U.run_gemm(layout, a, b, bias=bias, epilogue=epilogue)
+    ref = O.gemm(a, b, layout, bias=bias, epilogue=epilogue)
+    if epilogue == "causal":
+        iu = np.triu_indices(M, 1, N)
+        assert np.all(out[iu] == np.float32(O.CAUSAL_MASK_VALUE))
+        keep = np.tril(np.ones((M, N), bool))
+        assert O.rel_frobenius(out[keep], ref[keep]) <= U.TOL["tf32"]
+    else:
+        assert O.rel_frobenius(out, ref) <= U.TOL["tf32"]
+        if epilogue == "bias_relu":
+            assert (out >= 0).all()
+
+
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+def test_gelu_epilogue_stores_preactivation(gt, layout):
+    M, N, K = 256, 384, 160
+    a, b, rng = U.make_operands(layout, M, N, K, seed=5)
+    bias = rng.standard_normal(N).astype(np.float32)
+    out, aux = U.run_gemm(layout, a, b, bias=bias, epilogue="bias_gelu", want_aux=True)
+    y, pre = O.gemm(a, b, layout, bias=bias, epilogue="bias_gelu", return_pre=True)
+    assert O.rel_frobenius(aux, pre) <= U.TOL["tf32"]
+    assert O.rel_frobenius(out, y) <= U.TOL["tf32"]
+    # the stored activation is the GELU of the stored pre-activation (fast-math exp tolerance)
+    np.testing.assert_allclose(out, O.gelu_tanh(aux), rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("precision", ["tf32", "3xtf32", "fp32"])
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+def test_accumulate_and_alpha(gt, layout, precision):
+    M, N, K = 192, 320, 256
+    a, b, rng = U.make_operands(layout, M, N, K, seed=9)
+    c0 = rng.standard_normal((M, N)).astype(np.float32)
+    out = U.run_gemm(layout, a, b, c0=c0, alpha=0.125, precision=precision)
+    ref = O.gemm(a, b, layout, c0=c0, alpha=0.125)
+    # error is measured on the product part, the c0 part is exact
+    assert O.rel_frobenius(out - c0, ref - c0) <= U.TOL[precision]
+
+
+# ---- which kernel runs, alignment, padding ----------------------------------------------------
+
+def test_aligned_operands_take_the_tensor_core_kernel(gt):
+    a, b, _ = U.make_operands("NN", 128, 128, 64)
+    _, path = U.run_gemm("NN", a, b, return_path=True)
+    assert path == 0
+
+
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+def test_unaligned_operands_take_the_fma_kernel_and_match(gt, layout):
+    M, N, K = 70, 50, 45          # leading dimensions 45/50/70: not multiples of 4
+    a, b, _ = U.make_operands(layout, M, N, K)
+    out, path = U.run_gemm(layout, a, b, return_path=True)
+    assert path == 1
+    assert O.rel_frobenius(out, O.gemm(a, b, layout)) <= 1e-5   # this kernel is true fp32
+    out2, path2 = U.run_gemm(layout, *U.make_operands(layout, 64, 64, 64)[:2], misalign=1, return_path=True)
+    assert path2 == 1
+
+
+@pytest.mark.parametrize("precision", ["tf32", "3xtf32", "fp32"])
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+def test_padded_leading_dimensions(gt, layout, precision):
+    M, N, K = 150, 200, 100
+    a, b, _ = U.make_operands(layout, M, N, K, seed=21)
+    out = U.run_gemm(layout, a, b, pad=8, precision=precision)     # NaN padding must never be read
+    assert O.rel_frobenius(out, O.gemm(a, b, layout)) <= U.TOL[precision]
+
+
+def test_bitwise_deterministic(gt):
+    a, b, _ = U.make_operands("TN", 384, 512, 1024, seed=3)
+    assert np.array_equal(U.run_gemm("TN", a, b), U.run_gemm("TN", a, b))
+
+
+def test_tf32_rounding_beats_truncation_margin(gt):
+    # operands are rounded to tf32 (nearest) on the way into shared memory, so the error sits
+    # near 3e-4, a factor three inside the 1e-3 bar, independent of K
+    for K in (256, 4096):
+        a, b, _ = U.make_operands("NT", 256, 256, K, seed=K)
+        assert O.rel_frobenius(U.run_gemm("NT", a, b), O.gemm(a, b, "NT")) <= 4.5e-4
+
+
+# ---- batched ----------------------------------------------------------------------------------
+
+def _run_batched(layout, a, b, *, c0=None, epilogue="none", alpha=1.0, precision="tf32"):
+    """a, b: (B0, rows, cols) stored per slice contiguously."""
+    from gradtuity_b200 import _lib, gemm as G
+
+    Bn = a.shape[0]
+    M = a.shape[2] if layout == "TN" else a.shape[1]
+    K = a.shape[1] if layout == "TN" else a.shape[2]
+    N = b.shape[1] if layout == "NT" else b.shape[2]
+    da, db = U.DeviceBuffer(a), U.DeviceBuffer(b)
+    dc = U.DeviceBuffer(c0 if c0 is not None else np.full((Bn, M, N), np.nan, np.float32))
+    G.gemm_batched(U.LAYOUTS[layout], M, N, K, da.ptr, a.shape[2], a.shape[1] * a.shape[2], 0,
+                   db.ptr, b.shape[2], b.shape[1] * b.shape[2], 0, dc.ptr, N, M * N, 0, Bn, 1,
+                   alpha=alpha, accumulate=c0 is not None, epilogue=U.EPILOGUES[epilogue],
+                   precision=U.PRECISIONS[precision])
+    _lib.device_status()
+    return dc.read((Bn, M, N))
+
+
+@pytest.mark.parametrize("precision", ["tf32", "3xtf32"])
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+def test_batched_matches_per_slice_oracle(gt, layout, precision):
+    rng = np.random.default_rng(42)
+    Bn, M, N, K = 6, 96, 80, 64
+    ashape = (Bn, K, M) if layout == "TN" else (Bn, M, K)
+    bshape = (Bn, N, K) if layout == "NT" else (Bn, K, N)
+    a = rng.standard_normal(ashape).astype(np.float32) / 8
+    b = rng.standard_normal(bshape).astype(np.float32) / 8
+    out = _run_batched(layout, a, b, precision=precision)
+    assert O.rel_frobenius(out, O.gemm(a, b, layout)) <= U.TOL[precision]
+
+
+def test_batched_causal_scores_in_place_heads(gt):
+    """S = Q K^T / sqrt(d) with the causal mask, Q and K read in place from a (B, T, H, d)
+    projection output through two batch strides (no (B, H, T, d) copy)."""
+    from gradtuity_b200 import _lib, gemm as G
+
+    rng = np.random.default_rng(2)
+    B, T, H, d = 2, 256, 3, 64
+    q = rng.standard_normal((B, T, H, d)).astype(np.float32)
+    k = rng.standard_normal((B, T, H, d)).astype(np.float32)
+    dq, dk = U.DeviceBuffer(q), U.DeviceBuffer(k)
+    ds = U.DeviceBuffer(np.full((B, H, T, T), np.nan, np.float32))
+    G.gemm_batched(U.LAYOUTS["NT"], T, T, d, dq.ptr, H * d, d, T * H * d, dk.ptr, H * d, d, T * H * d,
+                   ds.ptr, T, T * T, H * T * T, H, B, alpha=1.0 / 8.0, epilogue=U.EPILOGUES["causal"])
+    _lib.device_status()
+    s = ds.read((B, H, T, T))
+    ref = O.gemm(q.transpose(0, 2, 1, 3), k.transpose(0, 2, 1, 3), "NT", alpha=1.0 / 8.0, epilogue="causal")
+    keep = np.tril(np.ones((T, T), bool))
+    assert np.all(s[..., ~keep] == np.float32(O.CAUSAL_MASK_VALUE))
+    assert O.rel_frobenius(s[..., keep], ref[..., keep]) <= U.TOL["tf32"]
+
+
+# ---- error behaviour --------------------------------------------------------------------------
+
+def test_invalid_arguments_return_status_not_crash(gt):
+    from gradtuity_b200 import gemm as G
+
+    buf = U.DeviceBuffer(np.zeros((64, 64), np.float32))
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        G.gemm(0, 64, 64, 64, 0, 64, buf.ptr, 64, buf.ptr, 64)            # null A
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        G.gemm(7, 64, 64, 64, buf.ptr, 64, buf.ptr, 64, buf.ptr, 64)      # bad layout
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        G.gemm(0, 64, 64, 64, buf.ptr, 32, buf.ptr, 64, buf.ptr, 64)      # lda < K
+    with pytest.raises(RuntimeError, match="bias"):
+        G.gemm(0, 64, 64, 64, buf.ptr, 64, buf.ptr, 64, buf.ptr, 64, epilogue=1)   # bias epilogue, no bias
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        G.gemm(0, 0, 64, 64, buf.ptr, 64, buf.ptr, 64, buf.ptr, 64)       # M = 0
+    gt.device_status()

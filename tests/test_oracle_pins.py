@@ -1,0 +1,87 @@
+"""CPU: the float64 oracle against the reference's own known answers and the pinned vectors."""
+import numpy as np
+import pytest
+
+from oracle import gemm_oracle as O
+from tests import _util as U
+
+
+@pytest.mark.parametrize("case", U.known_answers(), ids=lambda c: c["name"])
+def test_oracle_matches_reference_known_answers(case):
+    op = case["op"]
+    if op == "matmul":
+        y = O.gemm(np.array(case["a"], float), np.array(case["b"], float), "NN")
+        np.testing.assert_allclose(y, np.array(case["y"], float), rtol=1e-6)
+    elif op == "matmul_sum_backward":
+        a, b = np.array(case["a"], float), np.array(case["b"], float)
+        dc = np.ones((a.shape[0], b.shape[1]))
+        if case["a_grad"]:
+            np.testing.assert_allclose(O.gemm(dc, b, "NT"), np.array(case["da"], float), rtol=1e-6)
+        if case["b_grad"]:
+            np.testing.assert_allclose(O.gemm(a, dc, "TN"), np.array(case["db"], float), rtol=1e-6)
+    elif op in ("linear", "linear_relu"):
+        r = O.linear_forward_backward(case["x"], case["w"], case["bias"], np.ones((len(case["x"]), len(case["bias"]))),
+                                      activation="relu" if op == "linear_relu" else "none")
+        np.testing.assert_allclose(r["y"], np.array(case["y"], float), rtol=1e-6, atol=1e-12)
+    elif op in ("linear_sum_backward", "linear_relu_sum_backward"):
+        r = O.linear_forward_backward(case["x"], case["w"], case["bias"], np.ones((len(case["x"]), len(case["bias"]))),
+                                      activation="relu" if "relu" in op else "none")
+        for key, name in (("dx", "dx"), ("dw", "dw"), ("dbias", "db")):
+            if key in case:
+                np.testing.assert_allclose(r[name], np.array(case[key], float), rtol=1e-6, atol=1e-12)
+    else:
+        raise AssertionError(op)
+
+
+@pytest.mark.parametrize("kind,M,N,K", U.PHASE4_CASES)
+def test_oracle_matches_phase4_vectors(kind, M, N, K):
+    layout, a, b, bias, c0 = U.phase4_inputs(kind, M, N, K)
+    epi = {"matmul": "none", "matmul_bias": "bias", "matmul_bias_relu": "bias_relu"}.get(kind, "none")
+    y = O.gemm(a, b, layout, bias=bias, epilogue=epi, c0=c0)
+    gold = U.phase4_vectors()[U.phase4_key(kind, M, N, K)]
+    # fp32 scalar accumulation against float64: a few ulp of the largest partial sum
+    np.testing.assert_allclose(y, gold, rtol=2e-5, atol=2e-6)
+
+
+def test_gelu_matches_reference_formula_points():
+    # 0.5 x (1 + tanh(0.79788456 (x + 0.044715 x^3))): gradtuity/kernels_cuda/elemwise_kernels.py:118-124
+    x = np.array([-3.0, -1.0, 0.0, 0.5, 2.0])
+    want = 0.5 * x * (1 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+    np.testing.assert_allclose(O.gelu_tanh(x), want, rtol=1e-15)
+    h = 1e-6
+    np.testing.assert_allclose(O.gelu_tanh_grad(x), (O.gelu_tanh(x + h) - O.gelu_tanh(x - h)) / (2 * h), rtol=1e-6, atol=1e-8)
+
+
+def test_causal_softmax_masks_to_exact_zero():
+    # masked probabilities are exactly 0.0: gradtuity/tests/test_fused_softmax.py:70-79
+    rng = np.random.default_rng(0)
+    s = rng.standard_normal((2, 3, 8, 8))
+    p = O.causal_softmax(s)
+    iu = np.triu_indices(8, 1)
+    assert np.all(p[..., iu[0], iu[1]] == 0.0)
+    np.testing.assert_allclose(p.sum(-1), 1.0, rtol=1e-12)
+
+
+def test_causal_epilogue_and_accumulate():
+    rng = np.random.default_rng(1)
+    a, b = rng.standard_normal((5, 4)), rng.standard_normal((6, 4))
+    y = O.gemm(a, b, "NT", epilogue="causal", alpha=0.5)
+    full = 0.5 * a @ b.T
+    for i in range(5):
+        for j in range(6):
+            assert y[i, j] == (O.CAUSAL_MASK_VALUE if j > i else full[i, j])
+    c0 = rng.standard_normal((5, 6))
+    np.testing.assert_allclose(O.gemm(a, b, "NT", c0=c0), c0 + a @ b.T)
+
+
+def test_attention_oracle_consistency():
+    # backward of the oracle agrees with finite differences of its own forward
+    rng = np.random.default_rng(2)
+    q, k, v, do = (rng.standard_normal((1, 2, 6, 4)) for _ in range(4))
+    r = O.attention_forward_backward(q, k, v, do)
+    def loss(qq):
+        return (O.attention_forward_backward(qq, k, v, do)["o"] * do).sum()
+    h = 1e-6
+    e = np.zeros_like(q); e[0, 1, 3, 2] = h
+    fd = (loss(q + e) - loss(q - e)) / (2 * h)
+    assert abs(fd - r["dq"][0, 1, 3, 2]) < 1e-6

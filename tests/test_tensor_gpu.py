@@ -1,0 +1,193 @@
+"""GPU: the Tensor API on the reference's own known answers and numpy comparisons
+(gradtuity/tests/test_tensor.py:1276-1375, 1729-1875; gradtuity/tests/test_nn.py:1165-1450)."""
+import numpy as np
+import pytest
+
+from oracle import gemm_oracle as O
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def T(gt):
+    from gradtuity_b200.tensor import Tensor
+    return Tensor
+
+
+def _f(x):
+    return [[float(v) for v in row] for row in x] if isinstance(x[0], list) else [float(v) for v in x]
+
+
+@pytest.mark.parametrize("case", U.known_answers(), ids=lambda c: c["name"])
+def test_reference_known_answers(T, case):
+    op = case["op"]
+    if op == "matmul":
+        y = T(_f(case["a"])).matmul(T(_f(case["b"])))
+        assert y.shape == (len(case["a"]), len(case["b"][0]))
+        np.testing.assert_allclose(np.array(y.to_list()), np.array(case["y"], float), rtol=1e-6)
+    elif op == "matmul_sum_backward":
+        a = T(_f(case["a"]), requires_grad=case["a_grad"])
+        b = T(_f(case["b"]), requires_grad=case["b_grad"])
+        a.matmul(b).sum().backward()
+        for t, key in ((a, "da"), (b, "db")):
+            if case[key] is None:
+                assert t.grad is None
+            else:
+                np.testing.assert_allclose(np.array(t.grad.to_list()), np.array(case[key], float), rtol=1e-6)
+    elif op in ("linear", "linear_relu"):
+        x, w, b = T(_f(case["x"])), T(_f(case["w"])), T(_f(case["bias"]))
+        y = getattr(x, op)(w, b)
+        np.testing.assert_allclose(np.array(y.to_list()), np.array(case["y"], float), rtol=1e-6, atol=1e-7)
+    else:
+        full = "dw" in case or "dbias" in case
+        x = T(_f(case["x"]), requires_grad=True)
+        w = T(_f(case["w"]), requires_grad=full)
+        b = T(_f(case["bias"]), requires_grad=full)
+        y = x.linear_relu(w, b) if "relu" in op else x.linear(w, b)
+        y.sum().backward()
+        if "dx" in case:
+            np.testing.assert_allclose(np.array(x.grad.to_list()), np.array(case["dx"], float), rtol=1e-6, atol=1e-7)
+        if "dw" in case:
+            np.testing.assert_allclose(np.array(w.grad.to_list()), np.array(case["dw"], float), rtol=1e-6, atol=1e-7)
+        if "dbias" in case:
+            np.testing.assert_allclose(np.array(b.grad.to_list()), np.array(case["dbias"], float), rtol=1e-6, atol=1e-7)
+        if not full:
+            assert w.grad is None and b.grad is None
+
+
+def test_matmul_error_messages(T):
+    with pytest.raises(ValueError, match="2D"):
+        T([1.0, 2.0, 3.0]).matmul(T([[1.0], [2.0], [3.0]]))
+    with pytest.raises(ValueError, match="mismatch"):
+        T([[1.0, 2.0]]).matmul(T([[1.0, 2.0, 3.0]]))
+    c = T([[1.0, 2.0], [3.0, 4.0]]).matmul(T([[1.0, 0.0], [0.0, 1.0]]))
+    assert c.requires_grad is False and c._backward is None
+
+
+def test_linear_error_messages(T):
+    with pytest.raises(ValueError, match="shape mismatch"):
+        T([[1.0, 2.0]]).linear(T([[1.0], [2.0], [3.0]]), T([1.0]))
+    with pytest.raises(ValueError, match="bias size"):
+        T([[1.0, 2.0]]).linear(T([[1.0, 2.0], [3.0, 4.0]]), T([1.0, 2.0, 3.0]))
+    with pytest.raises(ValueError, match="shape mismatch"):
+        T([[1.0, 2.0]]).linear_relu(T([[1.0], [2.0], [3.0]]), T([1.0]))
+
+
+def test_linear_matches_matmul_plus_bias(T):
+    x = T([[1.0, 2.0], [3.0, 4.0], [5.0, 6.0]])
+    w = T([[0.1, 0.2, 0.3], [0.4, 0.5, 0.6]])
+    b = T([1.0, 2.0, 3.0])
+    np.testing.assert_allclose(np.array(x.linear(w, b).to_list()), np.array(x.matmul(w).add_bias(b).to_list()), rtol=1e-5)
+
+
+def test_linear_backward_accumulates_into_preset_grads(T):
+    x = T([[1.0, 1.0]], requires_grad=True)
+    w = T([[1.0, 1.0], [1.0, 1.0]], requires_grad=True)
+    b = T([0.0, 0.0], requires_grad=True)
+    x.grad, w.grad, b.grad = T._ones((1, 2)), T._ones((2, 2)), T._ones((2,))
+    x.linear(w, b).sum().backward()
+    np.testing.assert_allclose(np.array(x.grad.to_list()), [[3.0, 3.0]])
+    np.testing.assert_allclose(np.array(w.grad.to_list()), [[2.0, 2.0], [2.0, 2.0]])
+    np.testing.assert_allclose(np.array(b.grad.to_list()), [2.0, 2.0])
+
+
+def test_linear_relu_backward_matches_separate_ops(T):
+    def build():
+        return (T([[1.0, 2.0], [3.0, 4.0]], requires_grad=True), T([[0.5, 0.2], [0.3, 0.4]], requires_grad=True),
+                T([0.1, -0.1], requires_grad=True))
+    x1, w1, b1 = build()
+    x2, w2, b2 = build()
+    x1.linear_relu(w1, b1).sum().backward()
+    x2.linear(w2, b2).relu().sum().backward()
+    for p, q in ((x1, x2), (w1, w2), (b1, b2)):
+        np.testing.assert_allclose(np.array(p.grad.to_list()), np.array(q.grad.to_list()), rtol=1e-5)
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [((3, 5, 7), (3, 7, 4)), ((2, 3, 6, 8), (2, 3, 8, 5))])
+def test_bmm_matches_numpy(T, shape_a, shape_b):
+    rng = np.random.default_rng(42)
+    a = rng.standard_normal(shape_a).astype(np.float32)
+    b = rng.standard_normal(shape_b).astype(np.float32)
+    out = T.from_numpy(a).bmm(T.from_numpy(b))
+    assert out.shape == shape_a[:-1] + (shape_b[-1],)
+    np.testing.assert_allclose(out.numpy(), np.matmul(a, b), rtol=0.01, atol=0.01)
+
+
+def test_bmm_backward_and_double_use(T):
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((4, 16, 24)).astype(np.float32)
+    b = rng.standard_normal((4, 24, 8)).astype(np.float32)
+    ta, tb = T.from_numpy(a, requires_grad=True), T.from_numpy(b, requires_grad=True)
+    ta.bmm(tb).sum().backward()
+    ones = np.ones((4, 16, 8))
+    assert O.rel_frobenius(ta.grad.numpy(), O.gemm(ones, b, "NT")) <= 1e-3
+    assert O.rel_frobenius(tb.grad.numpy(), O.gemm(a, ones, "TN")) <= 1e-3
+    # the same tensor used twice accumulates twice the gradient (gradtuity/tests/test_tensor.py:1354-1375)
+    ta2, tb2 = T.from_numpy(a, requires_grad=True), T.from_numpy(b, requires_grad=True)
+    (ta2.bmm(tb2).sum() + ta2.bmm(tb2).sum()).backward()
+    np.testing.assert_allclose(ta2.grad.numpy(), 2 * ta.grad.numpy(), rtol=1e-5)
+
+
+def test_bmm_error_messages(T):
+    t3 = T.from_numpy(np.zeros((2, 3, 4), np.float32))
+    with pytest.raises(ValueError, match="ndim 3 or 4"):
+        T([[1.0]]).bmm(T([[1.0]]))
+    with pytest.raises(ValueError, match="same ndim"):
+        t3.bmm(T.from_numpy(np.zeros((1, 2, 4, 4), np.float32)))
+    with pytest.raises(ValueError, match="batch"):
+        t3.bmm(T.from_numpy(np.zeros((3, 4, 4), np.float32)))
+    with pytest.raises(ValueError, match="inner"):
+        t3.bmm(T.from_numpy(np.zeros((2, 5, 4), np.float32)))
+
+
+def test_linear_tied_values_and_grads(T):
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((48, 32)).astype(np.float32)
+    w = rng.standard_normal((100, 32)).astype(np.float32)     # (V, E); V = 100: dL has pitch 100
+    dy = rng.standard_normal((48, 100)).astype(np.float32)
+    tx, tw = T.from_numpy(x, requires_grad=True), T.from_numpy(w, requires_grad=True)
+    y = tx.linear_tied(tw)
+    ref = O.linear_tied_forward_backward(x, w, dy)
+    assert O.rel_frobenius(y.numpy(), ref["y"]) <= 1e-3
+    y.mul(T.from_numpy(dy)).sum().backward()
+    assert O.rel_frobenius(tx.grad.numpy(), ref["dx"]) <= 1e-3
+    assert O.rel_frobenius(tw.grad.numpy(), ref["dw"]) <= 1e-3
+
+
+def test_config0_linear_784_128(T):
+    """Config 0: Linear(784 -> 128), batch 128, X ~ U[0,1), W and b ~ U(-1/28, 1/28), dY ~ N(0,1),
+    seed 0; y, dX, dW, db against the float64 oracle."""
+    rng = np.random.default_rng(0)
+    x = rng.random((128, 784), dtype=np.float32)
+    w = rng.uniform(-1 / 28, 1 / 28, (784, 128)).astype(np.float32)
+    b = rng.uniform(-1 / 28, 1 / 28, (128,)).astype(np.float32)
+    dy = rng.standard_normal((128, 128)).astype(np.float32)
+    for act, method in (("none", "linear"), ("relu", "linear_relu"), ("gelu", "linear_gelu")):
+        tx, tw, tb = (T.from_numpy(v, requires_grad=True) for v in (x, w, b))
+        y = getattr(tx, method)(tw, tb)
+        y.mul(T.from_numpy(dy)).sum().backward()
+        y_gpu = y.numpy()
+        ref = O.linear_forward_backward(x, w, b, dy, activation=act, relu_mask=(y_gpu > 0) if act == "relu" else None)
+        assert O.rel_frobenius(y_gpu, ref["y"]) <= 1e-3, (act, "y")
+        if act == "relu":   # the few outputs within rounding error of zero may differ in sign
+            assert np.mean((y_gpu > 0) != (ref["y"] > 0)) < 2e-3
+        assert O.rel_frobenius(tx.grad.numpy(), ref["dx"]) <= 1e-3, (act, "dx")
+        assert O.rel_frobenius(tw.grad.numpy(), ref["dw"]) <= 1e-3, (act, "dw")
+        assert O.rel_frobenius(tb.grad.numpy(), ref["db"]) <= 1e-3, (act, "db")
+
+
+def test_view_detach_item_roundtrip(T):
+    t = T([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], requires_grad=True)
+    v = t.view((3, -1))
+    assert v.shape == (3, 2) and v.ptr == t.ptr and not v.owns_memory
+    d = t.detach()
+    assert d.requires_grad is False and d.ptr == t.ptr
+    s = v.sum()
+    assert s.item() == pytest.approx(21.0)
+    s.backward()
+    np.testing.assert_allclose(np.array(t.grad.to_list()), np.ones((2, 3)))
+    with pytest.raises(ValueError, match="scalar"):
+        t.backward()
+    with pytest.raises(ValueError):
+        t.view((4, -1))
