@@ -200,3 +200,40 @@ def test_invalid_arguments_return_status_not_crash(gt):
     with pytest.raises(RuntimeError, match="invalid argument"):
         G.gemm(0, 0, 64, 64, buf.ptr, 64, buf.ptr, 64, buf.ptr, 64)       # M = 0
     gt.device_status()
+
+
+# ---- full-size cases: size-independent properties and sampled rows ------------------------------
+
+@pytest.mark.parametrize("precision,M,N,K", [("tf32", 8192, 8192, 8192), ("tf32", 8192, 768, 3072),
+                                            ("tf32", 8192, 3072, 768), ("3xtf32", 2048, 2048, 8192)])
+def test_full_size_sampled_rows_and_linearity(gt, precision, M, N, K):
+    """At the benchmark sizes the float64 oracle is run on 16 sampled rows of C, and the whole
+    result is checked through linearity: gemm(A, B1 + B2) == gemm(A, B1) + gemm(A, B2)."""
+    from gradtuity_b200 import _lib, gemm as G
+
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((M, K), dtype=np.float32) / np.float32(np.sqrt(K))
+    b1 = rng.standard_normal((K, N), dtype=np.float32) / np.float32(np.sqrt(K))
+    b2 = rng.standard_normal((K, N), dtype=np.float32) / np.float32(np.sqrt(K))
+    da, db1, db2, db12 = U.DeviceBuffer(a), U.DeviceBuffer(b1), U.DeviceBuffer(b2), U.DeviceBuffer(b1 + b2)
+    dc1, dc12 = U.DeviceBuffer(nbytes=M * N * 4), U.DeviceBuffer(nbytes=M * N * 4)
+    prec = U.PRECISIONS[precision]
+    G.gemm(0, M, N, K, da.ptr, K, db1.ptr, N, dc1.ptr, N, precision=prec)
+    c1 = dc1.read((M, N))
+    G.gemm(0, M, N, K, da.ptr, K, db2.ptr, N, dc1.ptr, N, accumulate=True, precision=prec)   # C1 += A B2
+    G.gemm(0, M, N, K, da.ptr, K, db12.ptr, N, dc12.ptr, N, precision=prec)
+    _lib.device_status()
+    c_sum, c12 = dc1.read((M, N)), dc12.read((M, N))
+    rows = np.arange(0, M, M // 16)
+    ref = a[rows].astype(np.float64) @ b1.astype(np.float64)
+    assert O.rel_frobenius(c1[rows], ref) <= U.TOL[precision]
+    # two roundings of B versus one: the bound is twice the single-GEMM bar
+    assert O.rel_frobenius(c_sum, c12) <= 2 * U.TOL[precision]
+
+
+def test_3xtf32_error_does_not_grow_with_k(gt):
+    """The tensor core truncates on every accumulate; 3xTF32 mode therefore sums K-chunks in
+    fp32 registers.  Without that the error at K = 8192 is about 6e-5."""
+    for K in (1024, 8192):
+        a, b, _ = U.make_operands("NT", 256, 256, K, seed=K)
+        assert O.rel_frobenius(U.run_gemm("NT", a, b, precision="3xtf32"), O.gemm(a, b, "NT")) <= 5e-6
