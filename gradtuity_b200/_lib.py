@@ -70,6 +70,9 @@ SIGNATURES = {
                                 c_void_p, c_int64, c_int64, c_int64,
                                 c_int64, c_int64,
                                 c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p]),
+    "gt_gemm_3xtf32_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
+                                       c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                       c_void_p, c_float, c_int, c_int, c_void_p]),
     "gt_gemm_path": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
                              c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                              c_int, POINTER(c_int)]),

@@ -9,9 +9,7 @@
 
 #include "gt_internal.h"
 
-namespace {
-
-int validate(gt_ctx* ctx, const gt_gemm_args& g) {
+int gt_gemm_validate(gt_ctx* ctx, const gt_gemm_args& g) {
   if (g.layout < GT_LAYOUT_NN || g.layout > GT_LAYOUT_TN) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: layout %d is not NN/NT/TN", g.layout);
   if (g.epilogue < GT_EPI_NONE || g.epilogue > GT_EPI_CAUSAL) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: unknown epilogue %d", g.epilogue);
   if (g.precision < GT_PREC_TF32 || g.precision > GT_PREC_FP32) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: unknown precision %d", g.precision);
@@ -31,9 +29,11 @@ int validate(gt_ctx* ctx, const gt_gemm_args& g) {
   return GT_OK;
 }
 
+namespace {
+
 int run(gt_ctx* ctx, const gt_gemm_args& g, void* stream) {
   if (!ctx) return GT_ERR_INVALID_ARG;
-  int rc = validate(ctx, g);
+  int rc = gt_gemm_validate(ctx, g);
   if (rc != GT_OK) return rc;
   cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
   if (gt_gemm_umma_eligible(g)) return gt_gemm_umma_launch(ctx, g, s);

@@ -597,7 +597,10 @@ bool gt_gemm_umma_eligible(const gt_gemm_args& g) {
   return true;
 }
 
-int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream) {
+// fixed_scratch: when non-null, the 3xTF32 operand split goes there (capacity
+// fixed_scratch_floats) instead of into the context's growable workspace.
+static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream,
+                            float* fixed_scratch, size_t fixed_scratch_floats) {
   const bool x3 = g.precision == GT_PREC_TF32X3;
   const bool a_mn = g.layout == GT_LAYOUT_TN;
   const bool b_mn = g.layout != GT_LAYOUT_NT;
@@ -616,9 +619,17 @@ int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream)
     const int a_pad = (int)((va.cols + 3) & ~3LL), b_pad = (int)((vb.cols + 3) & ~3LL);
     const long long a_slice = va.rows * a_pad, b_slice = vb.rows * b_pad;
     const size_t need = (size_t)(2 * (a_slice + b_slice) * nbatch) * sizeof(float);
-    int rc = gt_workspace_reserve(ctx, need);
-    if (rc != GT_OK) return rc;
-    float* a_hi = (float*)ctx->workspace;
+    float* a_hi;
+    if (fixed_scratch) {
+      if (need > fixed_scratch_floats * sizeof(float))
+        GT_FAIL(ctx, GT_ERR_TOO_LARGE, "operand split needs %zu bytes of scratch, the fixed scratch holds %zu", need,
+                fixed_scratch_floats * sizeof(float));
+      a_hi = fixed_scratch;
+    } else {
+      int rc = gt_workspace_reserve(ctx, need);
+      if (rc != GT_OK) return rc;
+      a_hi = (float*)ctx->workspace;
+    }
     float* a_lo = a_hi + a_slice * nbatch;
     float* b_hi = a_lo + a_slice * nbatch;
     float* b_lo = b_hi + b_slice * nbatch;
@@ -677,4 +688,68 @@ int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream)
   if (bn == 128) { GT_DISPATCH(128); }
   GT_DISPATCH(64);
 #undef GT_DISPATCH
+}
+
+int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream) {
+  return umma_launch_impl(ctx, g, stream, nullptr, 0);
+}
+
+// ---- 3xTF32 GEMM that allocates nothing ---------------------------------------------------------
+//
+// Some callers must not trigger a device allocation while they run: a serving loop that has
+// handed all free device memory to its own pool, so that a cudaMalloc from inside a library
+// fails or evicts; a step that is timed to the microsecond and cannot absorb the device-wide
+// synchronisation cudaMalloc / cudaFree may imply; code that runs while another component
+// holds the allocator lock.  gt_gemm in 3xTF32 mode does allocate, the first time it meets
+// a new largest problem: the hi/lo copies of A and B live in a workspace that grows on demand.
+// This entry point runs the same kernels with those copies in a fixed array inside the
+// library's own image instead, so no cudaMalloc, cudaFree, cudaMallocAsync or allocating library
+// routine is reached, and problems that do not fit are refused rather than served slowly.
+//
+// The array is a file-scope __device__ object: every GPU that loads the library keeps
+// GT_NOALLOC_SCRATCH_BYTES of it until the process exits.  In host code its name is only a
+// handle; the device address is looked up with cudaGetSymbolAddress once per device, with
+// that device current, on the first call made for that device.  That first call should
+// therefore come before any stream capture begins.  All calls share the array and it keeps
+// the previous call's contents: the split kernels overwrite every element the GEMM reads
+// (padding columns included), so nothing needs clearing, but two calls whose kernels overlap
+// on the GPU (different streams without an ordering between them) race on it.
+constexpr size_t GT_NOALLOC_SCRATCH_FLOATS = (size_t)8 << 20;            // 32 MiB
+static __device__ __align__(256) float gt_noalloc_scratch[GT_NOALLOC_SCRATCH_FLOATS];
+static float* g_noalloc_scratch_ptr[64] = {nullptr};
+
+extern "C" int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                                      const float* A, int64_t lda, const float* B, int64_t ldb,
+                                      float* C, int64_t ldc, const float* bias, float alpha,
+                                      int accumulate, int epilogue, void* stream) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  gt_gemm_args g;
+  g.layout = layout; g.epilogue = epilogue; g.precision = GT_PREC_TF32X3; g.accumulate = accumulate;
+  g.M = M; g.N = N; g.K = K;
+  g.A = A; g.lda = lda; g.sA0 = 0; g.sA1 = 0;
+  g.B = B; g.ldb = ldb; g.sB0 = 0; g.sB1 = 0;
+  g.C = C; g.ldc = ldc; g.sC0 = 0; g.sC1 = 0;
+  g.batch0 = 1; g.batch1 = 1;
+  g.bias = bias; g.aux = nullptr; g.alpha = alpha;
+  int rc = gt_gemm_validate(ctx, g);
+  if (rc != GT_OK) return rc;
+  if (!gt_gemm_umma_eligible(g))
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gt_gemm_3xtf32_noalloc needs 16-byte aligned A and B with leading dimensions that are multiples of 4");
+  if (ctx->device < 0 || ctx->device >= 64) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "device index %d out of range", ctx->device);
+  // Refuse oversize problems before touching the device.
+  const int64_t a_rows = layout == GT_LAYOUT_TN ? K : M, a_cols = layout == GT_LAYOUT_TN ? M : K;
+  const int64_t b_rows = layout == GT_LAYOUT_NT ? N : K, b_cols = layout == GT_LAYOUT_NT ? K : N;
+  const double need = 2.0 * ((double)a_rows * (double)((a_cols + 3) & ~3LL) + (double)b_rows * (double)((b_cols + 3) & ~3LL));
+  if (need > (double)GT_NOALLOC_SCRATCH_FLOATS)
+    GT_FAIL(ctx, GT_ERR_TOO_LARGE,
+            "gt_gemm_3xtf32_noalloc: A and B need %.0f floats of split scratch, the built-in array holds %zu (32 MiB); use gt_gemm",
+            need, GT_NOALLOC_SCRATCH_FLOATS);
+  if (!g_noalloc_scratch_ptr[ctx->device]) {
+    GT_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    float* p = nullptr;
+    GT_CUDA_OK(ctx, cudaGetSymbolAddress((void**)&p, gt_noalloc_scratch));
+    g_noalloc_scratch_ptr[ctx->device] = p;
+  }
+  cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
+  return umma_launch_impl(ctx, g, s, g_noalloc_scratch_ptr[ctx->device], GT_NOALLOC_SCRATCH_FLOATS);
 }

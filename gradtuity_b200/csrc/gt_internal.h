@@ -57,6 +57,7 @@ struct gt_gemm_args {
 };
 
 int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes);
+int gt_gemm_validate(gt_ctx* ctx, const gt_gemm_args& g);
 int gt_gemm_fma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 bool gt_gemm_umma_eligible(const gt_gemm_args& g);

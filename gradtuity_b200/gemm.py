@@ -53,3 +53,17 @@ def gemm_batched(layout: int, M: int, N: int, K: int,
                                    _p(c_ptr), ldc, sc0, sc1, batch0, batch1, _p(bias_ptr), _p(aux_ptr), alpha,
                                    1 if accumulate else 0, epilogue, precision, None),
                "gt_gemm_batched")
+
+
+def gemm_3xtf32_noalloc(layout: int, M: int, N: int, K: int, a_ptr: int, lda: int, b_ptr: int, ldb: int,
+                        c_ptr: int, ldc: int, *, bias_ptr: int = 0, alpha: float = 1.0,
+                        accumulate: bool = False, epilogue: int = EPI_NONE) -> None:
+    """3xTF32 GEMM that never allocates device memory: for callers that have handed the whole
+    GPU to their own memory pool or cannot afford an allocation's synchronisation mid-step.
+    The operand split uses a fixed 32 MiB array inside the library, so A and B together are
+    limited (about 4 Mi elements); beyond that the call raises with "exceeds the fixed maximum".
+    Calls share that array: do not let two of them overlap on the GPU."""
+    lib = _lib.load_library()
+    _lib.check(lib.gt_gemm_3xtf32_noalloc(_lib.context(), layout, M, N, K, _p(a_ptr), lda, _p(b_ptr), ldb, _p(c_ptr), ldc,
+                                          _p(bias_ptr), alpha, 1 if accumulate else 0, epilogue, None),
+               "gt_gemm_3xtf32_noalloc")

@@ -138,6 +138,26 @@ int gt_gemm_batched(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
                     const float* bias, float* aux, float alpha, int accumulate,
                     int epilogue, int precision, void* stream);
 
+/* 3xTF32 GEMM for callers that must not cause a device allocation (no counterpart in the
+ * reference, which allocates per tensor).  Same result as gt_gemm(..., GT_PREC_TF32X3) for a
+ * single, non-batched problem without an aux output, but the hi/lo operand copies live in a
+ * fixed 32 MiB array inside the library image rather than in a workspace that grows with
+ * cudaMalloc.  Meant for callers that have given all device memory to their own pool, or that
+ * cannot take the synchronisation an allocation may bring in the middle of a timed step.
+ *   - limit: 2 * (rows(A) * cols4(A) + rows(B) * cols4(B)) <= 8 Mi floats, cols4 = columns
+ *     rounded up to a multiple of 4 (for example M = N = K = 1024, or 2048 x 1024 x 512);
+ *     larger problems return GT_ERR_TOO_LARGE and launch nothing;
+ *   - A and B must be 16-byte aligned with leading dimensions that are multiples of 4
+ *     (else GT_ERR_UNSUPPORTED);
+ *   - the first call on each device looks up the array's device address; make that call
+ *     before starting any stream capture;
+ *   - all calls share the array: calls whose kernels may overlap on the GPU race on it.    */
+#define GT_NOALLOC_SCRATCH_BYTES (32u << 20)
+int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                           const float* A, int64_t lda, const float* B, int64_t ldb,
+                           float* C, int64_t ldc, const float* bias, float alpha,
+                           int accumulate, int epilogue, void* stream);
+
 /* Which kernel a call with these arguments would run: 0 = tcgen05/TMA kernel, 1 = fp32 FMA
  * kernel.  No launch.                                                                       */
 int gt_gemm_path(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,

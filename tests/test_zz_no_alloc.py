@@ -1,0 +1,74 @@
+"""GPU: the allocation-free 3xTF32 entry point against the ordinary one.
+
+gt_gemm_3xtf32_noalloc exists for callers that cannot let a library allocate device memory
+(their own pool owns the GPU, or an allocation's synchronisation would land inside a timed
+step).  It must give what gt_gemm gives in 3xTF32 mode, call after call, although every call
+reuses the same built-in scratch array, and it must refuse problems that do not fit.
+This file is collected last on purpose: a run that stops at the first failure has then
+already run every other test.
+"""
+import numpy as np
+import pytest
+
+from oracle import gemm_oracle as O
+from tests import _util as U
+
+pytestmark = pytest.mark.gpu
+
+
+def _both(layout, a, b, *, bias=None, c0=None, epilogue="none", alpha=1.0):
+    from gradtuity_b200 import _lib, gemm as G
+
+    M = a.shape[1] if layout == "TN" else a.shape[0]
+    K = a.shape[0] if layout == "TN" else a.shape[1]
+    N = b.shape[0] if layout == "NT" else b.shape[1]
+    da, db = U.DeviceBuffer(a), U.DeviceBuffer(b)
+    dbias = U.DeviceBuffer(bias) if bias is not None else None
+    init = c0 if c0 is not None else np.full((M, N), np.nan, np.float32)
+    d_ref, d_new = U.DeviceBuffer(init), U.DeviceBuffer(init)
+    kw = dict(bias_ptr=dbias.ptr if dbias else 0, alpha=alpha, accumulate=c0 is not None, epilogue=U.EPILOGUES[epilogue])
+    G.gemm(U.LAYOUTS[layout], M, N, K, da.ptr, a.shape[1], db.ptr, b.shape[1], d_ref.ptr, N,
+           precision=U.PRECISIONS["3xtf32"], **kw)
+    G.gemm_3xtf32_noalloc(U.LAYOUTS[layout], M, N, K, da.ptr, a.shape[1], db.ptr, b.shape[1], d_new.ptr, N, **kw)
+    _lib.device_status()
+    return d_ref.read((M, N)), d_new.read((M, N))
+
+
+def test_two_calls_in_a_row_match_the_allocating_entry_point(gt):
+    # second call: other layout, other shape, smaller operands, so stale scratch contents from
+    # the first call would show up if anything depended on them
+    calls = [("NN", 384, 640, 520, "bias_gelu", False), ("TN", 200, 136, 96, "none", True)]
+    for layout, M, N, K, epilogue, acc in calls:
+        a, b, rng = U.make_operands(layout, M, N, K, seed=M + N + K)
+        bias = rng.standard_normal(N).astype(np.float32) if epilogue != "none" else None
+        c0 = rng.standard_normal((M, N)).astype(np.float32) if acc else None
+        ref, new = _both(layout, a, b, bias=bias, c0=c0, epilogue=epilogue, alpha=0.5)
+        assert not np.isnan(new).any()
+        # same kernels, same inputs: the tolerance is the 3xTF32 bar, the expectation is equality
+        assert O.rel_frobenius(new, ref) <= U.TOL["3xtf32"]
+        assert np.array_equal(new, ref)
+        want = O.gemm(a, b, layout, bias=bias, epilogue=epilogue, c0=c0, alpha=0.5)
+        base = c0 if c0 is not None else 0.0
+        assert O.rel_frobenius(new - base, want - base) <= U.TOL["3xtf32"]
+
+
+def test_oversize_problem_is_refused_and_nothing_is_written(gt):
+    from gradtuity_b200 import gemm as G
+
+    M = N = K = 2048              # 2 * (4 Mi + 4 Mi) floats of split scratch: twice the built-in array
+    da = U.DeviceBuffer(nbytes=M * K * 4)
+    db = U.DeviceBuffer(nbytes=K * N * 4)
+    sentinel = np.full((4, 4), 7.0, np.float32)
+    dc = U.DeviceBuffer(np.tile(sentinel, (M // 4, N // 4)))
+    with pytest.raises(RuntimeError, match="fixed maximum"):
+        G.gemm_3xtf32_noalloc(0, M, N, K, da.ptr, K, db.ptr, N, dc.ptr, N)
+    gt.device_status()
+    assert np.all(dc.read((M, N)) == 7.0)
+
+
+def test_unaligned_operands_are_refused(gt):
+    from gradtuity_b200 import gemm as G
+
+    buf = U.DeviceBuffer(np.zeros((64, 70), np.float32))
+    with pytest.raises(RuntimeError, match="unsupported"):
+        G.gemm_3xtf32_noalloc(0, 64, 64, 70, buf.ptr, 70, buf.ptr, 70, buf.ptr, 70)
