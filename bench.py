@@ -38,9 +38,9 @@ FLOPS = 2.0 * M * N * K
 ALG_BYTES = 4.0 * (M * K + K * N + M * N)
 # Rows of A used by the CPU legs: same K and N, a quarter of M (275 GFLOP per pass).
 CPU_SAMPLE_ROWS = 2048
-# DRAM bytes (read + write) per launch of the GEMM kernel from the ncu capture summarised in
-# profiles/; None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) per launch of the 8192^3 GEMM kernel, from the ncu capture summarised in
+# profiles/gemm_umma_nn_tf32_8192_dram_traffic.md (2.278 GB read + 0.254 GB written).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2531000000
 
 
 def _peaks():

@@ -89,6 +89,21 @@ SIGNATURES = {
     "gt_add_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64]),
     "gt_sum_all": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int]),
     "gt_colsum_acc": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "gt_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int]),
+    "gt_softmax_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_float]),
+    "gt_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float]),
+    "gt_layernorm_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int64, c_int64, c_int]),
+    "gt_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "gt_embedding_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "gt_cross_entropy": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int]),
+    "gt_cross_entropy_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int64, c_int]),
+    "gt_adamw": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float, c_float, c_float,
+                         c_float, c_float, c_float, c_void_p]),
+    "gt_sumsq": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int]),
+    "gt_clip_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float]),
+    "gt_scale_by_device_scalar": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
+    "gt_transpose12": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int]),
 }
 
 _lib = None

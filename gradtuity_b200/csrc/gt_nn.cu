@@ -1,0 +1,414 @@
+// The non-GEMM kernels a GPT-2 training step needs around the GEMMs: causal softmax and its
+// backward, LayerNorm, embedding gather / scatter-add, cross-entropy, AdamW, gradient norm,
+// the (B,S,H,D) <-> (B,H,S,D) transposes.  Plain CUDA, fp32, memory-bound: one row per block
+// (or per warp), coalesced float4 access where the pitch allows, two-stage reductions instead
+// of one atomic per element.
+//
+// fp32 specifications followed (the reference's CUDA-C twins):
+//   gradtuity/kernels_cuda/softmax_kernels.py   softmax fwd/bwd, softmax_with_causal_mask
+//   gradtuity/kernels_cuda/layernorm_kernels.py layernorm fwd/bwd
+//   gradtuity/kernels_cuda/gather_kernels.py    embedding gather / scatter-add
+//   gradtuity/kernels_cuda/loss_kernels.py      cross-entropy fwd/bwd
+//   gradtuity/kernels_cuda/optim_kernels.py     adamw_step
+//   gradtuity/kernels_cuda/mask_kernels.py      transpose4d_12
+
+#include "gt_internal.h"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide reductions; every thread gets the result.  red: 33 floats of shared memory.
+__device__ __forceinline__ float block_sum_all(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < nw ? red[l] : 0.0f;
+    t = warp_sum(t);
+    if (l == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max_all(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = l < nw ? red[l] : -INFINITY;
+    t = warp_max(t);
+    if (l == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// ---- softmax ------------------------------------------------------------------------------------
+// y = softmax(x) over the last dimension.  causal: row r of each (cols x cols) block keeps columns
+// j <= r % cols; the rest are written as exactly 0 and never read (they may hold anything, e.g.
+// the mask value of the GEMM's causal epilogue).  In-place (y == x) is allowed.
+__global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* x, float* y, long long rows, int cols, int causal) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const float* xr = x + row * cols;
+  float* yr = y + row * cols;
+  const int limit = causal ? (int)(row % cols) + 1 : cols;
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < limit; j += blockDim.x) m = fmaxf(m, xr[j]);
+  m = block_max_all(m, red);
+  float s = 0.0f;
+  for (int j = threadIdx.x; j < limit; j += blockDim.x) s += __expf(xr[j] - m);
+  s = block_sum_all(s, red);
+  const float inv = 1.0f / s;
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) yr[j] = j < limit ? __expf(xr[j] - m) * inv : 0.0f;
+}
+
+// dx = scale * y * (dy - sum_j y_j dy_j), written (not accumulated), as the reference's
+// softmax_backward_kernel does.  causal: only columns j <= r % cols are read; the rest of dx is 0.
+__global__ void __launch_bounds__(256) softmax_bwd_kernel(float* dx, const float* y, const float* dy, long long rows, int cols,
+                                                          int causal, float scale) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const float* yr = y + row * cols;
+  const float* dyr = dy + row * cols;
+  float* dxr = dx + row * cols;
+  const int limit = causal ? (int)(row % cols) + 1 : cols;
+  float dot = 0.0f;
+  for (int j = threadIdx.x; j < limit; j += blockDim.x) dot += yr[j] * dyr[j];
+  dot = block_sum_all(dot, red);
+  for (int j = threadIdx.x; j < cols; j += blockDim.x) dxr[j] = j < limit ? scale * yr[j] * (dyr[j] - dot) : 0.0f;
+}
+
+// ---- LayerNorm ----------------------------------------------------------------------------------
+// y = (x - mean) * rstd * gamma + beta per row; mean and rstd are saved (two floats per row)
+// and x-hat is recomputed in the backward instead of being stored.
+__global__ void __launch_bounds__(256) layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                            const float* __restrict__ beta, float* __restrict__ y,
+                                                            float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                            int H, float eps) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const float* xr = x + row * H;
+  float s = 0.0f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) s += xr[j];
+  const float mean = block_sum_all(s, red) / (float)H;
+  float q = 0.0f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) { const float d = xr[j] - mean; q += d * d; }
+  const float var = block_sum_all(q, red) / (float)H;
+  const float rstd = rsqrtf(var + eps);
+  if (threadIdx.x == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+  float* yr = y + row * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) yr[j] = (xr[j] - mean) * rstd * gamma[j] + beta[j];
+}
+
+// dx += rstd/H * (H*dxhat - sum(dxhat) - xhat*sum(dxhat*xhat)), dxhat = dy*gamma;
+// dgamma += sum_rows dy*xhat, dbeta += sum_rows dy.  Each block walks `rows_per_block` rows and
+// keeps its column partials in registers, so there is one atomic per column per block instead
+// of one per element (the reference: gradtuity/kernels_cuda/layernorm_kernels.py:76-81).
+constexpr int LN_MAX_COLS_PER_THREAD = 16;    // H <= 4096 with 256 threads
+__global__ void __launch_bounds__(256) layernorm_bwd_kernel(float* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                            const float* __restrict__ dy, const float* __restrict__ x,
+                                                            const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                            const float* __restrict__ gamma, long long N, int H, int rows_per_block,
+                                                            int dx_accumulate) {
+  __shared__ float red[33];
+  float pg[LN_MAX_COLS_PER_THREAD], pb[LN_MAX_COLS_PER_THREAD];
+#pragma unroll
+  for (int c = 0; c < LN_MAX_COLS_PER_THREAD; ++c) { pg[c] = 0.0f; pb[c] = 0.0f; }
+  const long long r0 = (long long)blockIdx.x * rows_per_block;
+  long long r1 = r0 + rows_per_block; if (r1 > N) r1 = N;
+  for (long long row = r0; row < r1; ++row) {
+    const float mu = mean[row], rs = rstd[row];
+    const float* xr = x + row * H;
+    const float* dyr = dy + row * H;
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int c = 0; c < LN_MAX_COLS_PER_THREAD; ++c) {
+      const int j = threadIdx.x + c * 256;
+      if (j < H) {
+        const float g = dyr[j];
+        const float xh = (xr[j] - mu) * rs;
+        const float dxh = g * gamma[j];
+        s1 += dxh; s2 += dxh * xh;
+        pg[c] += g * xh; pb[c] += g;
+      }
+    }
+    s1 = block_sum_all(s1, red);
+    s2 = block_sum_all(s2, red);
+    const float invH = 1.0f / (float)H;
+    if (dx) {
+      float* dxr = dx + row * H;
+#pragma unroll
+      for (int c = 0; c < LN_MAX_COLS_PER_THREAD; ++c) {
+        const int j = threadIdx.x + c * 256;
+        if (j < H) {
+          const float xh = (xr[j] - mu) * rs;
+          const float dxh = dyr[j] * gamma[j];
+          const float v = rs * invH * ((float)H * dxh - s1 - xh * s2);
+          dxr[j] = dx_accumulate ? dxr[j] + v : v;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < LN_MAX_COLS_PER_THREAD; ++c) {
+    const int j = threadIdx.x + c * 256;
+    if (j < H) {
+      if (dgamma) atomicAdd(dgamma + j, pg[c]);
+      if (dbeta) atomicAdd(dbeta + j, pb[c]);
+    }
+  }
+}
+
+// ---- embedding ----------------------------------------------------------------------------------
+// out[n, :] = W[idx[n], :]; indices are stored as floats (the engine has one dtype).  An index
+// outside [0, V) raises the status word and is clamped, instead of the reference's host-side loop
+// over a device-to-host copy (gradtuity/tensor.py:694-703).
+__global__ void __launch_bounds__(256) embedding_gather_kernel(float* __restrict__ out, const float* __restrict__ W,
+                                                               const float* __restrict__ idx, long long n, int D, int V, int* status) {
+  const long long row = blockIdx.x;
+  int t = (int)idx[row];
+  if (t < 0 || t >= V) { if (threadIdx.x == 0) atomicExch(status, GT_ERR_INVALID_ARG); t = t < 0 ? 0 : V - 1; }
+  const float* w = W + (long long)t * D;
+  float* o = out + row * D;
+  for (int j = threadIdx.x; j < D; j += blockDim.x) o[j] = w[j];
+}
+__global__ void __launch_bounds__(256) embedding_scatter_add_kernel(float* __restrict__ dW, const float* __restrict__ dout,
+                                                                    const float* __restrict__ idx, long long n, int D, int V) {
+  const long long row = blockIdx.x;
+  int t = (int)idx[row];
+  if (t < 0 || t >= V) return;
+  float* w = dW + (long long)t * D;
+  const float* g = dout + row * D;
+  for (int j = threadIdx.x; j < D; j += blockDim.x) atomicAdd(w + j, g[j]);
+}
+
+// ---- cross-entropy ------------------------------------------------------------------------------
+// Per row: lse = log sum exp(logits), loss_row = lse - logits[target].  One pass over the row
+// (online max / sum).  The per-row losses and lse values are kept; the mean is taken by a
+// deterministic reduction, and the backward reuses lse.
+__global__ void __launch_bounds__(512) cross_entropy_fwd_kernel(const float* __restrict__ logits, const float* __restrict__ targets,
+                                                                float* __restrict__ row_loss, float* __restrict__ row_lse,
+                                                                int C, int* status) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const float* xr = logits + row * C;
+  float m = -INFINITY, s = 0.0f;
+  for (int j = threadIdx.x; j < C; j += blockDim.x) {
+    const float v = xr[j];
+    if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+  }
+  const float gm = block_max_all(m, red);
+  s = (m == -INFINITY) ? 0.0f : s * __expf(m - gm);
+  s = block_sum_all(s, red);
+  if (threadIdx.x == 0) {
+    int t = (int)targets[row];
+    if (t < 0 || t >= C) { atomicExch(status, GT_ERR_INVALID_ARG); t = t < 0 ? 0 : C - 1; }
+    const float lse = gm + logf(s);
+    row_lse[row] = lse;
+    row_loss[row] = lse - xr[t];
+  }
+}
+// dlogits (+)= scale * (softmax - onehot)
+__global__ void __launch_bounds__(512) cross_entropy_bwd_kernel(float* __restrict__ dlogits, const float* __restrict__ logits,
+                                                                const float* __restrict__ targets, const float* __restrict__ row_lse,
+                                                                const float* __restrict__ upstream, float scale, int C, int accumulate) {
+  const long long row = blockIdx.x;
+  const float* xr = logits + row * C;
+  float* dr = dlogits + row * C;
+  const float lse = row_lse[row];
+  const int t = (int)targets[row];
+  const float sc = scale * (upstream ? *upstream : 1.0f);
+  for (int j = threadIdx.x; j < C; j += blockDim.x) {
+    const float v = sc * (__expf(xr[j] - lse) - (j == t ? 1.0f : 0.0f));
+    dr[j] = accumulate ? dr[j] + v : v;
+  }
+}
+
+// ---- optimizer ----------------------------------------------------------------------------------
+// AdamW exactly as gradtuity/kernels_cuda/optim_kernels.py:23-46; grad_scale (read from device
+// memory when given) folds the gradient-clipping factor into the update.
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                                    float* __restrict__ v, long long n, float lr, float beta1, float beta2, float eps,
+                                                    float wd, float bc1, float bc2, const float* __restrict__ grad_scale) {
+  const float gs = grad_scale ? *grad_scale : 1.0f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float pi = p[i];
+    const float gi = g[i] * gs;
+    const float mi = beta1 * m[i] + (1.0f - beta1) * gi;
+    const float vi = beta2 * v[i] + (1.0f - beta2) * gi * gi;
+    const float upd = (mi * bc1) / (sqrtf(vi * bc2) + eps);
+    pi = pi - lr * upd - lr * wd * pi;
+    m[i] = mi; v[i] = vi; p[i] = pi;
+  }
+}
+
+// out[0] (+)= sum x^2, deterministic two-stage.
+__global__ void __launch_bounds__(256) sumsq_partial_kernel(const float* __restrict__ x, float* __restrict__ partial, long long n) {
+  __shared__ float red[33];
+  float s = 0.0f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) { const float v = x[i]; s += v * v; }
+  s = block_sum_all(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+__global__ void __launch_bounds__(256) sum_partials_kernel(const float* __restrict__ partial, float* __restrict__ out, int n, int accumulate) {
+  __shared__ float red[33];
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += partial[i];
+  s = block_sum_all(s, red);
+  if (threadIdx.x == 0) *out = accumulate ? *out + s : s;
+}
+// scale_out[0] = total_norm > max_norm ? max_norm / (total_norm + eps) : 1; norm_out[0] = total_norm
+// (gradtuity/optim/utils.py:38-51, kept on the device so the step needs no host round trip).
+__global__ void clip_scale_kernel(const float* __restrict__ sumsq, float max_norm, float eps, float* __restrict__ scale_out, float* __restrict__ norm_out) {
+  const float nrm = sqrtf(*sumsq);
+  *norm_out = nrm;
+  *scale_out = nrm > max_norm ? max_norm / (nrm + eps) : 1.0f;
+}
+__global__ void __launch_bounds__(256) scale_by_device_scalar_kernel(float* __restrict__ x, const float* __restrict__ s, long long n) {
+  const float v = *s;
+  if (v == 1.0f) return;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= v;
+}
+
+// ---- (B, d1, d2, D) -> (B, d2, d1, D) ------------------------------------------------------------
+__global__ void __launch_bounds__(256) transpose12_kernel(float* __restrict__ out, const float* __restrict__ in, int d1, int d2, int D, int accumulate) {
+  // one block per (b, i1, i2) row of D elements
+  const long long r = blockIdx.x;
+  const int i2 = (int)(r % d2);
+  const long long t = r / d2;
+  const int i1 = (int)(t % d1);
+  const long long b = t / d1;
+  const float* src = in + r * D;
+  float* dst = out + ((b * d2 + i2) * d1 + i1) * (long long)D;
+  for (int j = threadIdx.x; j < D; j += blockDim.x) dst[j] = accumulate ? dst[j] + src[j] : src[j];
+}
+
+inline unsigned blocks_for(gt_ctx* ctx, long long n) {
+  long long b = (n + 255) / 256, cap = (long long)ctx->sm_count * 8;
+  if (b > cap) b = cap;
+  return (unsigned)(b < 1 ? 1 : b);
+}
+
+}  // namespace
+
+#define GT_LAUNCH_CHECK(ctx, n_launches)          \
+  GT_CUDA_OK(ctx, cudaGetLastError());            \
+  (ctx)->launches += (n_launches);                \
+  return GT_OK
+
+extern "C" int gt_softmax(gt_ctx* ctx, float* y, const float* x, int64_t rows, int64_t cols, int causal) {
+  if (!ctx || !y || !x || rows <= 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  softmax_fwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, y, rows, (int)cols, causal);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_softmax_backward(gt_ctx* ctx, float* dx, const float* y, const float* dy, int64_t rows, int64_t cols,
+                                   int causal, float scale) {
+  if (!ctx || !dx || !y || !dy || rows <= 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  softmax_bwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(dx, y, dy, rows, (int)cols, causal, scale);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_layernorm(gt_ctx* ctx, float* y, float* mean, float* rstd, const float* x, const float* gamma,
+                            const float* beta, int64_t N, int64_t H, float eps) {
+  if (!ctx || !y || !mean || !rstd || !x || !gamma || !beta || N <= 0 || H <= 0 || N > 0x7fffffff || H > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  layernorm_fwd_kernel<<<(unsigned)N, 256, 0, ctx->stream>>>(x, gamma, beta, y, mean, rstd, (int)H, eps);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+                                     const float* mean, const float* rstd, const float* gamma, int64_t N, int64_t H,
+                                     int dx_accumulate) {
+  if (!ctx || !dy || !x || !mean || !rstd || !gamma || N <= 0 || H <= 0 || N > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  if (H > 256 * LN_MAX_COLS_PER_THREAD) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "layernorm backward supports H <= %d, got %lld", 256 * LN_MAX_COLS_PER_THREAD, (long long)H);
+  long long blocks = (long long)ctx->sm_count * 4;
+  if (blocks > N) blocks = N;
+  const int rpb = (int)((N + blocks - 1) / blocks);
+  blocks = (N + rpb - 1) / rpb;
+  layernorm_bwd_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, (int)H, rpb, dx_accumulate);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_embedding(gt_ctx* ctx, float* out, const float* W, const float* idx, int64_t n, int64_t D, int64_t V) {
+  if (!ctx || !out || !W || !idx || n <= 0 || D <= 0 || V <= 0 || n > 0x7fffffff || D > 0x7fffffff || V > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  embedding_gather_kernel<<<(unsigned)n, 256, 0, ctx->stream>>>(out, W, idx, n, (int)D, (int)V, ctx->d_status);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V) {
+  if (!ctx || !dW || !dout || !idx || n <= 0 || D <= 0 || V <= 0 || n > 0x7fffffff || D > 0x7fffffff || V > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  embedding_scatter_add_kernel<<<(unsigned)n, 256, 0, ctx->stream>>>(dW, dout, idx, n, (int)D, (int)V);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_cross_entropy(gt_ctx* ctx, float* loss, float* row_loss, float* row_lse, const float* logits,
+                                const float* targets, int64_t B, int64_t C, int mean) {
+  if (!ctx || !loss || !row_loss || !row_lse || !logits || !targets || B <= 0 || C <= 0 || B > 0x7fffffff || C > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  cross_entropy_fwd_kernel<<<(unsigned)B, 512, 0, ctx->stream>>>(logits, targets, row_loss, row_lse, (int)C, ctx->d_status);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  int rc = gt_sum_all(ctx, loss, row_loss, B, 0);
+  if (rc != GT_OK) return rc;
+  if (mean) return gt_scale(ctx, loss, loss, 1.0f / (float)B, 1, 0);
+  return GT_OK;
+}
+
+extern "C" int gt_cross_entropy_backward(gt_ctx* ctx, float* dlogits, const float* logits, const float* targets,
+                                         const float* row_lse, const float* upstream, float scale, int64_t B, int64_t C,
+                                         int accumulate) {
+  if (!ctx || !dlogits || !logits || !targets || !row_lse || B <= 0 || C <= 0 || B > 0x7fffffff || C > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  cross_entropy_bwd_kernel<<<(unsigned)B, 512, 0, ctx->stream>>>(dlogits, logits, targets, row_lse, upstream, scale, (int)C, accumulate);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_adamw(gt_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1,
+                        float beta2, float eps, float weight_decay, float bc1, float bc2, const float* grad_scale) {
+  if (!ctx || !p || !g || !m || !v || n <= 0) return GT_ERR_INVALID_ARG;
+  adamw_kernel<<<blocks_for(ctx, n), 256, 0, ctx->stream>>>(p, g, m, v, n, lr, beta1, beta2, eps, weight_decay, bc1, bc2, grad_scale);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_sumsq(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate) {
+  if (!ctx || !out || !x || n <= 0) return GT_ERR_INVALID_ARG;
+  int rc = gt_workspace_reserve(ctx, 8192 * sizeof(float));
+  if (rc != GT_OK) return rc;
+  float* partial = (float*)ctx->workspace + 4096;
+  const unsigned blocks = blocks_for(ctx, n);
+  sumsq_partial_kernel<<<blocks, 256, 0, ctx->stream>>>(x, partial, n);
+  sum_partials_kernel<<<1, 256, 0, ctx->stream>>>(partial, out, (int)blocks, accumulate);
+  GT_LAUNCH_CHECK(ctx, 2);
+}
+
+extern "C" int gt_clip_scale(gt_ctx* ctx, float* scale_out, float* norm_out, const float* sumsq, float max_norm, float eps) {
+  if (!ctx || !scale_out || !norm_out || !sumsq) return GT_ERR_INVALID_ARG;
+  clip_scale_kernel<<<1, 1, 0, ctx->stream>>>(sumsq, max_norm, eps, scale_out, norm_out);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_scale_by_device_scalar(gt_ctx* ctx, float* x, const float* s, int64_t n) {
+  if (!ctx || !x || !s || n <= 0) return GT_ERR_INVALID_ARG;
+  scale_by_device_scalar_kernel<<<blocks_for(ctx, n), 256, 0, ctx->stream>>>(x, s, n);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_transpose12(gt_ctx* ctx, float* out, const float* in, int64_t B, int64_t d1, int64_t d2, int64_t D, int accumulate) {
+  if (!ctx || !out || !in || B <= 0 || d1 <= 0 || d2 <= 0 || D <= 0) return GT_ERR_INVALID_ARG;
+  const long long rows = B * d1 * d2;
+  if (rows > 0x7fffffffLL || D > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  transpose12_kernel<<<(unsigned)rows, D >= 256 ? 256 : (D >= 128 ? 128 : 64), 0, ctx->stream>>>(out, in, (int)d1, (int)d2, (int)D, accumulate);
+  GT_LAUNCH_CHECK(ctx, 1);
+}

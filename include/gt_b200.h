@@ -189,6 +189,46 @@ int gt_add_bias(gt_ctx* ctx, float* out, const float* x, const float* bias, int6
 int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate); /* deterministic */
 int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld); /* db[c] += sum_r dy[r,c] */
 
+/* ---- the non-GEMM kernels of the GPT-2 training step -----------------------------------
+ * fp32, memory-bound, on the context's compute stream.  Each restates the reference kernel named
+ * beside it; differences are noted.
+ *   gt_softmax(causal=0)          softmax_forward_kernel             kernels_cuda/softmax_kernels.py:22-58
+ *   gt_softmax(causal=1)          softmax_with_causal_mask_forward   kernels_cuda/softmax_kernels.py:94-129
+ *                                 (masked outputs exactly 0; masked inputs are never read)
+ *   gt_softmax_backward           softmax_backward_kernel            kernels_cuda/softmax_kernels.py:60-92
+ *                                 (writes dx; `scale` folds the 1/sqrt(d) of attention; causal=1 reads
+ *                                  only the kept columns and writes 0 elsewhere)
+ *   gt_layernorm(_backward)       layernorm_fwd/bwd_kernel           kernels_cuda/layernorm_kernels.py
+ *                                 (saves mean and rstd, recomputes x-hat; dgamma/dbeta by block partials)
+ *   gt_embedding(_backward)       embedding_gather / scatter_add     kernels_cuda/gather_kernels.py
+ *                                 (indices are floats; out-of-range indices set the status word)
+ *   gt_cross_entropy(_backward)   cross_entropy_forward/backward     kernels_cuda/loss_kernels.py
+ *                                 (keeps per-row log-sum-exp for the backward; deterministic mean)
+ *   gt_adamw                      adamw_step_kernel                  kernels_cuda/optim_kernels.py:23-46
+ *   gt_sumsq / gt_clip_scale / gt_scale_by_device_scalar            optim/utils.py:15-52 without host reads
+ *   gt_transpose12                transpose4d_12_kernel              kernels_cuda/mask_kernels.py        */
+int gt_softmax(gt_ctx* ctx, float* y, const float* x, int64_t rows, int64_t cols, int causal);
+int gt_softmax_backward(gt_ctx* ctx, float* dx, const float* y, const float* dy, int64_t rows, int64_t cols,
+                        int causal, float scale);
+int gt_layernorm(gt_ctx* ctx, float* y, float* mean, float* rstd, const float* x, const float* gamma,
+                 const float* beta, int64_t N, int64_t H, float eps);
+int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
+                          const float* mean, const float* rstd, const float* gamma, int64_t N, int64_t H,
+                          int dx_accumulate);
+int gt_embedding(gt_ctx* ctx, float* out, const float* W, const float* idx, int64_t n, int64_t D, int64_t V);
+int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V);
+int gt_cross_entropy(gt_ctx* ctx, float* loss, float* row_loss, float* row_lse, const float* logits,
+                     const float* targets, int64_t B, int64_t C, int mean);
+int gt_cross_entropy_backward(gt_ctx* ctx, float* dlogits, const float* logits, const float* targets,
+                              const float* row_lse, const float* upstream, float scale, int64_t B, int64_t C,
+                              int accumulate);
+int gt_adamw(gt_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1,
+             float beta2, float eps, float weight_decay, float bc1, float bc2, const float* grad_scale);
+int gt_sumsq(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate);
+int gt_clip_scale(gt_ctx* ctx, float* scale_out, float* norm_out, const float* sumsq, float max_norm, float eps);
+int gt_scale_by_device_scalar(gt_ctx* ctx, float* x, const float* s, int64_t n);
+int gt_transpose12(gt_ctx* ctx, float* out, const float* in, int64_t B, int64_t d1, int64_t d2, int64_t D, int accumulate);
+
 #ifdef __cplusplus
 }
 #endif
