@@ -103,6 +103,13 @@ SIGNATURES = {
     "gt_sumsq": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int]),
     "gt_clip_scale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float]),
     "gt_scale_by_device_scalar": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
+    "gt_dist_get_unique_id": (c_int, [c_void_p, c_char_p]),
+    "gt_dist_init": (c_int, [c_void_p, c_int, c_int, c_char_p]),
+    "gt_dist_destroy": (c_int, [c_void_p]),
+    "gt_dist_allreduce": (c_int, [c_void_p, c_void_p, c_int64, c_int]),
+    "gt_dist_broadcast": (c_int, [c_void_p, c_void_p, c_int64, c_int]),
+    "gt_dist_wait": (c_int, [c_void_p, c_int]),
+    "gt_dist_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int)]),
     "gt_transpose12": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int]),
 }
 

@@ -1,0 +1,183 @@
+// Single-node data-parallel gradient exchange over NCCL (NVLink 5 / NVSwitch).
+//
+// Stands where the reference's ctypes binding of libnccl stands (gradtuity/dist/nccl.py:71-189)
+// and the calls built on it (gradtuity/dist/comm.py:37-170): unique-id creation, communicator
+// init / destroy, in-place fp32 all-reduce, broadcast, barrier.  Differences:
+//   * collectives run on a dedicated non-blocking stream, ordered against the compute stream by
+//     events, so an all-reduce of finished gradient buckets overlaps the rest of backward; the
+//     reference brackets every call with cudaDeviceSynchronize on the NULL stream
+//     (gradtuity/dist/comm.py:129-131);
+//   * the 1/world_size scale is folded into the collective (ncclAvg) instead of a separate kernel
+//     (gradtuity/dist/ddp.py:94-97);
+//   * NCCL is opened with dlopen (GRADTUITY_NCCL_LIBRARY, default libnccl.so.2) with local symbol
+//     scope, so it never clashes with another NCCL copy in the process.
+// No kernel of this library reads a peer GPU's memory; inter-GPU traffic is NCCL's.
+
+#include <dlfcn.h>
+#include <stdlib.h>
+
+#include "gt_internal.h"
+
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+typedef struct { char internal[128]; } ncclUniqueId;
+enum { ncclSuccess = 0 };
+enum { ncclFloat32 = 7 };
+enum { ncclSum = 0, ncclAvg = 4 };
+
+struct NcclApi {
+  void* handle = nullptr;
+  int (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  int (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  int (*CommDestroy)(ncclComm_t) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+};
+
+NcclApi g_nccl;
+
+int load_nccl(char* err, size_t errlen) {
+  if (g_nccl.handle) return GT_OK;
+  const char* name = getenv("GRADTUITY_NCCL_LIBRARY");
+  if (!name || !name[0]) name = "libnccl.so.2";
+  void* h = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+  if (!h) {
+    snprintf(err, errlen, "dlopen(%s) failed: %s", name, dlerror());
+    return GT_ERR_NCCL;
+  }
+#define GT_SYM(field, sym)                                                       \
+  *(void**)(&g_nccl.field) = dlsym(h, sym);                                      \
+  if (!g_nccl.field) { snprintf(err, errlen, "%s lacks %s", name, sym); dlclose(h); return GT_ERR_NCCL; }
+  GT_SYM(GetUniqueId, "ncclGetUniqueId");
+  GT_SYM(CommInitRank, "ncclCommInitRank");
+  GT_SYM(CommDestroy, "ncclCommDestroy");
+  GT_SYM(AllReduce, "ncclAllReduce");
+  GT_SYM(Broadcast, "ncclBroadcast");
+  GT_SYM(GetErrorString, "ncclGetErrorString");
+#undef GT_SYM
+  g_nccl.handle = h;
+  return GT_OK;
+}
+
+struct DistState {
+  ncclComm_t comm = nullptr;
+  cudaStream_t stream = nullptr;     // collectives
+  cudaEvent_t ready = nullptr;       // compute -> comm: "the data is final"
+  cudaEvent_t done = nullptr;        // comm -> compute: "the collective has finished"
+  int rank = 0, world = 1;
+  int pending = 0;                   // collectives enqueued since the last wait
+};
+
+DistState* g_dist[64] = {nullptr};
+
+DistState* state_of(gt_ctx* ctx) { return (ctx && ctx->device >= 0 && ctx->device < 64) ? g_dist[ctx->device] : nullptr; }
+
+#define GT_NCCL_OK(ctx, expr)                                                                  \
+  do {                                                                                         \
+    int _r = (expr);                                                                           \
+    if (_r != ncclSuccess) {                                                                   \
+      snprintf((ctx)->last_error, sizeof((ctx)->last_error), "%s: %s", #expr,                  \
+               g_nccl.GetErrorString ? g_nccl.GetErrorString(_r) : "nccl error");              \
+      return GT_ERR_NCCL;                                                                      \
+    }                                                                                          \
+  } while (0)
+
+}  // namespace
+
+extern "C" int gt_dist_get_unique_id(gt_ctx* ctx, char* out128) {
+  if (!ctx || !out128) return GT_ERR_INVALID_ARG;
+  int rc = load_nccl(ctx->last_error, sizeof(ctx->last_error));
+  if (rc != GT_OK) return rc;
+  ncclUniqueId id;
+  GT_NCCL_OK(ctx, g_nccl.GetUniqueId(&id));
+  memcpy(out128, id.internal, 128);
+  return GT_OK;
+}
+
+extern "C" int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128) {
+  if (!ctx || !uid128 || world < 1 || rank < 0 || rank >= world) return GT_ERR_INVALID_ARG;
+  if (ctx->device < 0 || ctx->device >= 64) return GT_ERR_UNSUPPORTED;
+  if (g_dist[ctx->device]) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gt_dist_init: already initialised on device %d", ctx->device);
+  int rc = load_nccl(ctx->last_error, sizeof(ctx->last_error));
+  if (rc != GT_OK) return rc;
+  GT_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+  DistState* st = new DistState();
+  st->rank = rank; st->world = world;
+  ncclUniqueId id;
+  memcpy(id.internal, uid128, 128);
+  int r = g_nccl.CommInitRank(&st->comm, world, id, rank);
+  if (r != ncclSuccess) {
+    snprintf(ctx->last_error, sizeof(ctx->last_error), "ncclCommInitRank(rank %d of %d): %s", rank, world, g_nccl.GetErrorString(r));
+    delete st;
+    return GT_ERR_NCCL;
+  }
+  GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking));
+  GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&st->ready, cudaEventDisableTiming));
+  GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&st->done, cudaEventDisableTiming));
+  g_dist[ctx->device] = st;
+  return GT_OK;
+}
+
+extern "C" int gt_dist_destroy(gt_ctx* ctx) {
+  DistState* st = state_of(ctx);
+  if (!st) return GT_OK;
+  cudaStreamSynchronize(st->stream);
+  if (st->comm) g_nccl.CommDestroy(st->comm);
+  cudaEventDestroy(st->ready);
+  cudaEventDestroy(st->done);
+  cudaStreamDestroy(st->stream);
+  delete st;
+  g_dist[ctx->device] = nullptr;
+  return GT_OK;
+}
+
+// In-place all-reduce of `count` floats.  The collective is enqueued on the communication stream
+// behind everything the compute stream has been given so far, and returns at once; the compute
+// stream does not wait for it until gt_dist_wait.
+extern "C" int gt_dist_allreduce(gt_ctx* ctx, float* ptr, int64_t count, int average) {
+  DistState* st = state_of(ctx);
+  if (!ctx || !ptr || count <= 0) return GT_ERR_INVALID_ARG;
+  if (!st) GT_FAIL(ctx, GT_ERR_NOT_INIT, "gt_dist_allreduce: process group not initialised");
+  GT_CUDA_OK(ctx, cudaEventRecord(st->ready, ctx->stream));
+  GT_CUDA_OK(ctx, cudaStreamWaitEvent(st->stream, st->ready, 0));
+  GT_NCCL_OK(ctx, g_nccl.AllReduce(ptr, ptr, (size_t)count, ncclFloat32, average ? ncclAvg : ncclSum, st->comm, st->stream));
+  st->pending += 1;
+  return GT_OK;
+}
+
+extern "C" int gt_dist_broadcast(gt_ctx* ctx, float* ptr, int64_t count, int root) {
+  DistState* st = state_of(ctx);
+  if (!ctx || !ptr || count <= 0) return GT_ERR_INVALID_ARG;
+  if (!st) GT_FAIL(ctx, GT_ERR_NOT_INIT, "gt_dist_broadcast: process group not initialised");
+  if (root < 0 || root >= st->world) return GT_ERR_INVALID_ARG;
+  GT_CUDA_OK(ctx, cudaEventRecord(st->ready, ctx->stream));
+  GT_CUDA_OK(ctx, cudaStreamWaitEvent(st->stream, st->ready, 0));
+  GT_NCCL_OK(ctx, g_nccl.Broadcast(ptr, ptr, (size_t)count, ncclFloat32, root, st->comm, st->stream));
+  st->pending += 1;
+  return GT_OK;
+}
+
+// Makes the compute stream wait (on the device) for every collective enqueued so far.  With
+// host_sync != 0 the calling thread also blocks until they have finished.
+extern "C" int gt_dist_wait(gt_ctx* ctx, int host_sync) {
+  DistState* st = state_of(ctx);
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  if (!st) return GT_OK;
+  if (st->pending) {
+    GT_CUDA_OK(ctx, cudaEventRecord(st->done, st->stream));
+    GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, st->done, 0));
+    st->pending = 0;
+  }
+  if (host_sync) GT_CUDA_OK(ctx, cudaStreamSynchronize(st->stream));
+  return GT_OK;
+}
+
+extern "C" int gt_dist_info(gt_ctx* ctx, int* rank, int* world) {
+  DistState* st = state_of(ctx);
+  if (!ctx || !rank || !world) return GT_ERR_INVALID_ARG;
+  *rank = st ? st->rank : 0;
+  *world = st ? st->world : 1;
+  return GT_OK;
+}

@@ -1,0 +1,208 @@
+"""Gradient synchronisation for data parallelism: `sync_grads(params, bucket_mb=25)`.
+
+Same call, same meaning and the same bucket rule as gradtuity/dist/ddp.py:24-106 (consecutive
+parameters are grouped until adding the next one would exceed `bucket_mb`; GRADTUITY_BUCKET_MB
+overrides it; the result is the mean over ranks).  What differs is how the buckets travel:
+
+* the gradients of all parameters live in ONE flat arena (each `p.grad` becomes a view into it the
+  first time `sync_grads` sees the list), so a bucket is a contiguous range that is all-reduced in
+  place: no per-bucket cudaMalloc, no device-to-device pack and unpack, no separate scale kernel
+  (the division by the world size is the collective's ncclAvg);
+* from the second step on, `Tensor.backward()` reports every graph node it has finished; when the
+  last consumer of the last parameter of a bucket has run, that bucket's all-reduce is enqueued on
+  the communication stream at once, so it overlaps the rest of backward.  `sync_grads` then only
+  enqueues what is left (parameters that were not in the graph) and makes the compute stream wait.
+
+The API does not change: `sync_grads` is still called after `backward()` (gpt2/train.py:127-128).
+"""
+from __future__ import annotations
+
+import os
+
+from . import comm
+from . import env as dist_env
+
+F32 = 4
+ARENA_ALIGN_ELEMS = 64          # 256-byte alignment of every gradient inside the arena
+
+
+def bucketize(nbytes_list: list[int], bucket_max_bytes: int) -> list[list[int]]:
+    """Indices of consecutive entries per bucket: a bucket is closed when the next entry would
+    push it past bucket_max_bytes and it is not empty (gradtuity/dist/ddp.py:59-71)."""
+    buckets: list[list[int]] = []
+    cur: list[int] = []
+    cur_bytes = 0
+    for i, n in enumerate(nbytes_list):
+        if cur_bytes + n > bucket_max_bytes and cur:
+            buckets.append(cur)
+            cur, cur_bytes = [], 0
+        cur.append(i)
+        cur_bytes += n
+    if cur:
+        buckets.append(cur)
+    return buckets
+
+
+def arena_offsets(numels: list[int], align: int = ARENA_ALIGN_ELEMS) -> tuple[list[int], int]:
+    """Element offset of every gradient in the flat arena, each aligned; and the arena size."""
+    offs, pos = [], 0
+    for n in numels:
+        offs.append(pos)
+        pos += (n + align - 1) // align * align
+    return offs, pos
+
+
+class DeviceMemoryOps:
+    """How the plan touches memory; the product version works on GPU tensors."""
+
+    def alloc_zeroed(self, numel: int):
+        from ..tensor import Tensor
+
+        return Tensor._zeros((numel,))
+
+    def ensure_grad(self, p) -> None:
+        from ..tensor import ensure_grad
+
+        ensure_grad(p)
+
+    def copy(self, dst_ptr: int, src_ptr: int, nbytes: int) -> None:
+        from ..cuda_mem import cuda_memcpy_dtod
+
+        cuda_memcpy_dtod(dst_ptr, src_ptr, nbytes)
+
+    def view(self, arena, offset_elems: int, shape):
+        from ..tensor import Tensor
+
+        return Tensor._from_ptr(arena.ptr + offset_elems * F32, tuple(shape), owns_memory=False, base=arena._st)
+
+
+class GradPlan:
+    """Arena, views and buckets for one parameter list, plus the per-step readiness counters."""
+
+    def __init__(self, params: list, bucket_max_bytes: int, mem=None) -> None:
+        self.mem = mem or DeviceMemoryOps()
+        self.params = list(params)
+        self.index = {id(p): i for i, p in enumerate(self.params)}
+        numels = [p.numel for p in self.params]
+        self.offsets, total = arena_offsets(numels)
+        self.arena = self.mem.alloc_zeroed(max(total, 1))
+        for p, off in zip(self.params, self.offsets):
+            self.mem.ensure_grad(p)
+            self.mem.copy(self.arena.ptr + off * F32, p.grad.ptr, p.numel * F32)
+            p.grad = self.mem.view(self.arena, off, p.shape)
+        self.views = [p.grad for p in self.params]
+        self.buckets = bucketize([n * F32 for n in numels], bucket_max_bytes)
+        self.bucket_of = {}
+        self.ranges = []                                   # (ptr, numel) per bucket, padding included
+        for b, idxs in enumerate(self.buckets):
+            for i in idxs:
+                self.bucket_of[i] = b
+            start = self.offsets[idxs[0]]
+            end = self.offsets[idxs[-1]] + numels[idxs[-1]]
+            self.ranges.append((self.arena.ptr + start * F32, end - start))
+        # per-step state
+        self.active = False
+        self.launched: set[int] = set()
+        self.launch_order: list[int] = []
+        self._consumers: dict[int, int] = {}
+        self._bucket_left: list[int] = []
+
+    def intact(self) -> bool:
+        """True while every parameter's grad is still the arena view this plan installed."""
+        return all(p.grad is v for p, v in zip(self.params, self.views))
+
+    # ---- called by Tensor.backward() ------------------------------------------------------------
+    def begin(self, topo: list) -> None:
+        self.launched.clear()
+        self.launch_order.clear()
+        self.active = self.intact()
+        if not self.active:
+            return
+        cons = {}
+        for node in topo:
+            for par in node._parents:
+                i = self.index.get(id(par))
+                if i is not None:
+                    cons[i] = cons.get(i, 0) + 1
+        self._consumers = cons
+        self._bucket_left = [sum(1 for i in idxs if i in cons) for idxs in self.buckets]
+        self._in_graph = [any(i in cons for i in idxs) for idxs in self.buckets]
+        self._all_in_graph = [all(i in cons for i in idxs) for idxs in self.buckets]
+
+    def node_done(self, parents: tuple) -> None:
+        if not self.active:
+            return
+        for par in parents:
+            i = self.index.get(id(par))
+            if i is None:
+                continue
+            left = self._consumers.get(i)
+            if left is None:
+                continue
+            left -= 1
+            self._consumers[i] = left
+            if left == 0:
+                b = self.bucket_of[i]
+                self._bucket_left[b] -= 1
+                # a bucket goes out early only if ALL its parameters took part in this graph
+                if self._bucket_left[b] == 0 and self._all_in_graph[b]:
+                    self._launch(b)
+
+    def end(self) -> None:
+        pass
+
+    # ---- collectives ---------------------------------------------------------------------------
+    def _launch(self, b: int) -> None:
+        if b in self.launched:
+            return
+        ptr, numel = self.ranges[b]
+        comm._require().allreduce_async(ptr, numel, average=True)
+        self.launched.add(b)
+        self.launch_order.append(b)
+
+    def finish(self) -> None:
+        """Enqueue every bucket not sent during backward, then order the compute stream behind all."""
+        for b in range(len(self.buckets)):
+            self._launch(b)
+        comm._require().wait()
+        self.active = False
+        self.launched = set()
+
+
+_plans: dict[tuple, GradPlan] = {}
+_mem_ops = None            # tests may install host memory ops
+
+
+def _observer_install(plan: GradPlan | None) -> None:
+    from .. import tensor as _tensor
+
+    _tensor.set_backward_observer(plan)
+
+
+def sync_grads(params: list, bucket_mb: float = 25) -> None:
+    """Average gradients over ranks. Every parameter gets a grad (zeros if missing); parameter
+    order must be the same on all ranks."""
+    world = dist_env.get_world_size()
+    if world == 1:
+        return
+    comm._require()
+    env_mb = os.environ.get("GRADTUITY_BUCKET_MB")
+    if env_mb is not None:
+        bucket_mb = float(env_mb)
+    key = (tuple(id(p) for p in params), float(bucket_mb))
+    plan = _plans.get(key)
+    if plan is None or not plan.intact():
+        plan = GradPlan(params, int(bucket_mb * 1024 * 1024), mem=_mem_ops)
+        _plans.clear()                       # one live parameter list at a time; drops stale arenas
+        _plans[key] = plan
+        _observer_install(plan)
+    plan.finish()
+
+
+def reset() -> None:
+    """Forget plans and stop observing backward (tests, process-group teardown)."""
+    _plans.clear()
+    try:
+        _observer_install(None)
+    except Exception:
+        pass

@@ -1,0 +1,320 @@
+"""Neural-network modules on the GEMM path, with the reference's classes, constructor arguments,
+parameter names and storage layouts (gradtuity/nn.py:24-816): `Module`, `Linear` (weight stored
+`(in_features, out_features)`), `Embedding`, `PositionalEmbedding`, `TiedLMHead`,
+`CausalSelfAttention` (`Wq..Wo`, `bq..bo`), `LayerNorm` (`gamma`, `beta`), `MLP`, `Dropout`.
+
+`state_dict()` keys and `parameters()` order are the reference's, so checkpoints and the
+data-parallel gradient exchange see the same lists.  What changes is inside `__call__`: the
+attention core is one fused op over in-place head slices, and hidden MLP layers use the fused
+bias+ReLU GEMM.  Dropout is the identity at p = 0 (as in the reference, gradtuity/tensor.py:2449-2450);
+p > 0 is not on this path and raises.
+"""
+from __future__ import annotations
+
+from .functional import ones, randn, zero_grad, zeros
+from .tensor import Tensor
+
+
+class Module:
+    """Base class: reflection-based parameter discovery (gradtuity/nn.py:24-170)."""
+
+    def __init__(self) -> None:
+        self.training = True
+
+    def _children(self):
+        for name in dir(self):
+            if name.startswith("_"):
+                continue
+            try:
+                attr = getattr(self, name)
+            except AttributeError:
+                continue
+            yield name, attr
+
+    def train(self, mode: bool = True) -> "Module":
+        self.training = mode
+        for _, attr in self._children():
+            if isinstance(attr, Module):
+                attr.train(mode)
+            elif isinstance(attr, list):
+                for item in attr:
+                    if isinstance(item, Module):
+                        item.train(mode)
+        return self
+
+    def eval(self) -> "Module":
+        return self.train(False)
+
+    def parameters(self) -> list[Tensor]:
+        """All trainable tensors in sorted state_dict key order (identical on every rank)."""
+        state = self.state_dict()
+        return [state[k] for k in sorted(state)]
+
+    def zero_grad(self) -> None:
+        zero_grad(self.parameters())
+
+    def state_dict(self) -> dict[str, Tensor]:
+        """Dot-separated parameter paths, list indices as numeric segments (gradtuity/nn.py:87-114)."""
+        result: dict[str, Tensor] = {}
+
+        def visit(obj, prefix: str) -> None:
+            for name in dir(obj):
+                if name.startswith("_"):
+                    continue
+                try:
+                    attr = getattr(obj, name)
+                except AttributeError:
+                    continue
+                if isinstance(attr, Tensor) and attr.requires_grad:
+                    result[prefix + name] = attr
+                elif isinstance(attr, Module):
+                    visit(attr, prefix + name + ".")
+                elif isinstance(attr, list):
+                    for i, item in enumerate(attr):
+                        if isinstance(item, Module):
+                            visit(item, prefix + name + "." + str(i) + ".")
+
+        visit(self, "")
+        return result
+
+    def load_state_dict(self, state: dict[str, Tensor], strict: bool = True) -> None:
+        own = set(self.state_dict().keys())
+        given = set(state.keys())
+        if strict:
+            if given - own:
+                raise ValueError(f"load_state_dict: unexpected key(s) in state: {given - own}")
+            if own - given:
+                raise ValueError(f"load_state_dict: missing key(s) in state: {own - given}")
+        for key, tensor in state.items():
+            if key not in own:
+                continue
+            parts = key.split(".")
+            cur = self
+            for seg in parts[:-1]:
+                try:
+                    cur = cur[int(seg)] if seg.isdigit() else getattr(cur, seg)
+                except (AttributeError, IndexError, KeyError) as e:
+                    raise ValueError(f"load_state_dict: cannot resolve key {key!r}") from e
+            try:
+                setattr(cur, parts[-1], tensor)
+            except AttributeError as e:
+                raise ValueError(f"load_state_dict: cannot set key {key!r}") from e
+
+    def __call__(self, x: Tensor) -> Tensor:
+        raise NotImplementedError("Subclasses must implement __call__")
+
+
+class Linear(Module):
+    """Y = X @ W + b; weight (in_features, out_features), Xavier-normal init, zero bias
+    (gradtuity/nn.py:173-226)."""
+
+    def __init__(self, in_features: int, out_features: int) -> None:
+        self.in_features = in_features
+        self.out_features = out_features
+        std = (2.0 / (in_features + out_features)) ** 0.5
+        self.weight = randn((in_features, out_features), requires_grad=True, std=std)
+        self.bias = zeros((out_features,), requires_grad=True)
+
+    def __call__(self, x: Tensor) -> Tensor:
+        return x.linear(self.weight, self.bias)
+
+    def parameters(self) -> list[Tensor]:
+        return [self.weight, self.bias]
+
+    def __repr__(self) -> str:
+        return f"Linear(in_features={self.in_features}, out_features={self.out_features})"
+
+
+class Dropout(Module):
+    """Identity at p = 0 or in eval mode; p > 0 in training is outside this build's path."""
+
+    def __init__(self, p: float = 0.1, rng=None) -> None:
+        self.p = p
+        self.training = True
+
+    def __call__(self, x: Tensor) -> Tensor:
+        if self.p == 0.0 or not self.training:
+            return x
+        raise NotImplementedError("dropout with p > 0 is not part of the GEMM path; construct models with p = 0")
+
+    def parameters(self) -> list[Tensor]:
+        return []
+
+    def __repr__(self) -> str:
+        return f"Dropout(p={self.p})"
+
+
+class Embedding(Module):
+    """out = weight[indices]; weight (num_embeddings, embedding_dim), std 1/sqrt(dim)
+    (gradtuity/nn.py:305-354)."""
+
+    def __init__(self, num_embeddings: int, embedding_dim: int) -> None:
+        self.num_embeddings = num_embeddings
+        self.embedding_dim = embedding_dim
+        self.weight = randn((num_embeddings, embedding_dim), requires_grad=True, std=1.0 / (embedding_dim ** 0.5))
+
+    def __call__(self, indices) -> Tensor:
+        return self.weight.embedding(indices)
+
+    def parameters(self) -> list[Tensor]:
+        return [self.weight]
+
+    def __repr__(self) -> str:
+        return f"Embedding(num_embeddings={self.num_embeddings}, embedding_dim={self.embedding_dim})"
+
+
+class PositionalEmbedding(Module):
+    """Learned position vectors, repeated across the batch (gradtuity/nn.py:357-412).  The index
+    tensor for a given (seq_len, batch, start) is built once and kept on the device."""
+
+    def __init__(self, max_positions: int, embed_dim: int) -> None:
+        self.max_positions = max_positions
+        self.embed_dim = embed_dim
+        self.embed = Embedding(max_positions, embed_dim)
+        self._index_cache: dict[tuple[int, int, int], Tensor] = {}
+
+    def __call__(self, seq_len: int, batch_size: int, start_pos: int = 0) -> Tensor:
+        if start_pos + seq_len > self.max_positions:
+            raise ValueError(f"start_pos ({start_pos}) + seq_len ({seq_len}) > max_positions ({self.max_positions})")
+        key = (seq_len, batch_size, start_pos)
+        idx = self._index_cache.get(key)
+        if idx is None:
+            import numpy as np
+
+            pos = np.arange(start_pos, start_pos + seq_len, dtype=np.float32)
+            idx = Tensor.from_numpy(np.tile(pos, batch_size))
+            self._index_cache[key] = idx
+        return self.embed(idx).view((batch_size, seq_len, self.embed_dim))
+
+    def parameters(self) -> list[Tensor]:
+        return self.embed.parameters()
+
+    def __repr__(self) -> str:
+        return f"PositionalEmbedding(max_positions={self.max_positions}, embed_dim={self.embed_dim})"
+
+
+class TiedLMHead(Module):
+    """logits = h @ wte.weight.T, no weight of its own (gradtuity/nn.py:415-459)."""
+
+    def __init__(self, embedding_module: Embedding) -> None:
+        self.embedding_module = embedding_module
+
+    def __call__(self, h: Tensor) -> Tensor:
+        B, S, E = h.shape
+        wte = self.embedding_module
+        if E != wte.embedding_dim:
+            raise ValueError(f"input last dim {E} must equal embedding_dim {wte.embedding_dim}")
+        logits = h.view((B * S, E)).linear_tied(wte.weight)
+        return logits.view((B, S, wte.num_embeddings))
+
+    def parameters(self) -> list[Tensor]:
+        return []
+
+    @property
+    def weight_ref(self) -> Tensor:
+        return self.embedding_module.weight
+
+    def __repr__(self) -> str:
+        return "TiedLMHead(tied to Embedding)"
+
+
+class CausalSelfAttention(Module):
+    """Multi-head causal self-attention, (B, S, E) -> (B, S, E) (gradtuity/nn.py:462-569).
+
+    Same parameters (Wq, Wk, Wv, Wo as (E, E); bq, bk, bv, bo) and the same mathematics.  The
+    part between the projections runs as `Tensor.causal_attention`: three strided-batched GEMM
+    launches and one softmax launch forward, instead of three materialised transposes, 96
+    per-slice transposes, two Python loops of 96 GEMM launches, a scale kernel and a softmax."""
+
+    def __init__(self, embed_dim: int, num_heads: int, attn_pdrop: float = 0.0, resid_pdrop: float = 0.0) -> None:
+        if embed_dim <= 0 or num_heads <= 0:
+            raise ValueError("embed_dim and num_heads must be positive")
+        if embed_dim % num_heads != 0:
+            raise ValueError(f"embed_dim ({embed_dim}) must be divisible by num_heads ({num_heads})")
+        self.embed_dim = embed_dim
+        self.num_heads = num_heads
+        self.head_dim = embed_dim // num_heads
+        self.scale = 1.0 / (self.head_dim ** 0.5)
+        self.attn_pdrop = attn_pdrop
+        self.resid_pdrop = resid_pdrop
+        std = (2.0 / (embed_dim + embed_dim)) ** 0.5
+        self.Wq = randn((embed_dim, embed_dim), requires_grad=True, std=std)
+        self.Wk = randn((embed_dim, embed_dim), requires_grad=True, std=std)
+        self.Wv = randn((embed_dim, embed_dim), requires_grad=True, std=std)
+        self.Wo = randn((embed_dim, embed_dim), requires_grad=True, std=std)
+        self.bq = zeros((embed_dim,), requires_grad=True)
+        self.bk = zeros((embed_dim,), requires_grad=True)
+        self.bv = zeros((embed_dim,), requires_grad=True)
+        self.bo = zeros((embed_dim,), requires_grad=True)
+        self.attn_dropout = Dropout(p=attn_pdrop) if attn_pdrop > 0 else None
+        self.resid_dropout = Dropout(p=resid_pdrop) if resid_pdrop > 0 else None
+
+    def __call__(self, x: Tensor) -> Tensor:
+        B, S, E = x.shape
+        if E != self.embed_dim:
+            raise ValueError(f"input last dim {E} must equal embed_dim {self.embed_dim}")
+        if self.attn_dropout is not None and self.attn_dropout.p > 0 and self.training:
+            raise NotImplementedError("attention dropout with p > 0 is not part of the GEMM path")
+        x_flat = x.view((B * S, E))
+        q = x_flat.linear(self.Wq, self.bq).view((B, S, E))
+        k = x_flat.linear(self.Wk, self.bk).view((B, S, E))
+        v = x_flat.linear(self.Wv, self.bv).view((B, S, E))
+        ctx = q.causal_attention(k, v, self.num_heads)
+        out = ctx.view((B * S, E)).linear(self.Wo, self.bo)
+        if self.resid_dropout is not None:
+            out = self.resid_dropout(out)
+        return out.view((B, S, E))
+
+    def parameters(self) -> list[Tensor]:
+        return [self.Wq, self.Wk, self.Wv, self.Wo, self.bq, self.bk, self.bv, self.bo]
+
+    def __repr__(self) -> str:
+        return f"CausalSelfAttention(embed_dim={self.embed_dim}, num_heads={self.num_heads})"
+
+
+class LayerNorm(Module):
+    """LayerNorm over the last dimension; gamma ones, beta zeros (gradtuity/nn.py:662-710)."""
+
+    def __init__(self, normalized_shape: int, eps: float = 1e-5) -> None:
+        self.normalized_shape = normalized_shape
+        self.eps = eps
+        self.gamma = ones((normalized_shape,), requires_grad=True)
+        self.beta = zeros((normalized_shape,), requires_grad=True)
+
+    def __call__(self, x: Tensor) -> Tensor:
+        return x.layer_norm(self.gamma, self.beta, eps=self.eps)
+
+    def parameters(self) -> list[Tensor]:
+        return [self.gamma, self.beta]
+
+    def __repr__(self) -> str:
+        return f"LayerNorm(normalized_shape={self.normalized_shape}, eps={self.eps})"
+
+
+class MLP(Module):
+    """Linear layers with ReLU between them; hidden layers use the fused bias+ReLU GEMM
+    (gradtuity/nn.py:753-816)."""
+
+    def __init__(self, nin: int, nouts: list[int]) -> None:
+        self.nin = nin
+        self.nouts = nouts
+        sizes = [nin] + nouts
+        self.layers = [Linear(sizes[i], sizes[i + 1]) for i in range(len(nouts))]
+
+    def __call__(self, x: Tensor) -> Tensor:
+        for i, layer in enumerate(self.layers):
+            if i < len(self.layers) - 1:
+                x = x.linear_relu(layer.weight, layer.bias)
+            else:
+                x = x.linear(layer.weight, layer.bias)
+        return x
+
+    def parameters(self) -> list[Tensor]:
+        params = []
+        for layer in self.layers:
+            params.extend(layer.parameters())
+        return params
+
+    def __repr__(self) -> str:
+        inner = ", ".join(f"Linear({l.in_features}, {l.out_features})" for l in self.layers)
+        return f"MLP of [{inner}]"

@@ -1,0 +1,119 @@
+"""Optimizers for the training step: `AdamW`, `SGD`, `clip_grad_norm_` with the reference's
+signatures and update rules (gradtuity/optim/__init__.py:99-159, gradtuity/optim/utils.py:15-52).
+
+The update arithmetic is the reference's `adamw_step_kernel` (gradtuity/kernels_cuda/optim_kernels.py:23-46).
+`clip_grad_norm_` keeps the norm and the clip factor on the device: one reduction chain instead of a
+multiply, a sum and a device-to-host `.item()` per parameter; the returned norm costs one read.
+"""
+from __future__ import annotations
+
+import math
+from ctypes import c_void_p
+
+from .. import _lib
+from ..tensor import Tensor, empty_tensor
+
+
+def _call(name, *args):
+    _lib.check(getattr(_lib.load_library(), name)(_lib.context(), *args), name)
+
+
+class Optimizer:
+    def __init__(self, params: list[Tensor]) -> None:
+        self.params = list(params)
+
+    def zero_grad(self) -> None:
+        from ..functional import zero_grad
+
+        zero_grad(self.params)
+
+    def step(self) -> None:
+        raise NotImplementedError
+
+
+class SGD(Optimizer):
+    def __init__(self, params: list[Tensor], lr: float = 1e-2) -> None:
+        super().__init__(params)
+        self.lr = lr
+
+    def step(self) -> None:
+        for p in self.params:
+            if p.grad is None:
+                continue
+            _call("gt_scale", c_void_p(p.ptr), c_void_p(p.grad.ptr), -float(self.lr), p.numel, 1)
+
+
+class AdamW(Optimizer):
+    """Decoupled weight decay Adam; state m, v on the GPU, step count on the host."""
+
+    def __init__(self, params: list[Tensor], lr: float = 1e-3, betas: tuple[float, float] = (0.9, 0.999),
+                 eps: float = 1e-8, weight_decay: float = 0.01) -> None:
+        super().__init__(params)
+        self.lr = lr
+        self.beta1, self.beta2 = betas[0], betas[1]
+        self.eps = eps
+        self.weight_decay = weight_decay
+        n = len(self.params)
+        self.m: list[Tensor | None] = [None] * n
+        self.v: list[Tensor | None] = [None] * n
+        self.step_count = 0
+
+    def _validate_hyperparams(self) -> None:
+        if self.lr <= 0:
+            raise ValueError(f"lr must be > 0, got {self.lr}")
+        if not (0 <= self.beta1 < 1):
+            raise ValueError(f"beta1 must be in [0, 1), got {self.beta1}")
+        if not (0 <= self.beta2 < 1):
+            raise ValueError(f"beta2 must be in [0, 1), got {self.beta2}")
+        if self.eps <= 0:
+            raise ValueError(f"eps must be > 0, got {self.eps}")
+        if self.weight_decay < 0:
+            raise ValueError(f"weight_decay must be >= 0, got {self.weight_decay}")
+
+    def step(self, grad_scale: Tensor | None = None) -> None:
+        """One update.  grad_scale: optional (1,) device tensor multiplied into every gradient
+        inside the update kernel (the clip factor of `clip_grad_norm_(..., defer=True)`)."""
+        self._validate_hyperparams()
+        self.step_count += 1
+        t = self.step_count
+        bc1 = 1.0 / (1.0 - self.beta1 ** t)
+        bc2 = 1.0 / (1.0 - self.beta2 ** t)
+        gs = c_void_p(grad_scale.ptr) if grad_scale is not None else None
+        for i, p in enumerate(self.params):
+            if p.grad is None:
+                continue
+            if p.grad.shape != p.shape:
+                raise ValueError(f"param[{i}] grad shape {p.grad.shape} does not match param shape {p.shape}")
+            if self.m[i] is None:
+                self.m[i] = Tensor._zeros_like(p)
+                self.v[i] = Tensor._zeros_like(p)
+            _call("gt_adamw", c_void_p(p.ptr), c_void_p(p.grad.ptr), c_void_p(self.m[i].ptr), c_void_p(self.v[i].ptr),
+                  p.numel, float(self.lr), float(self.beta1), float(self.beta2), float(self.eps),
+                  float(self.weight_decay), float(bc1), float(bc2), gs)
+
+
+def clip_grad_norm_(params, max_norm: float, eps: float = 1e-6, defer: bool = False):
+    """Scale all gradients so that their global L2 norm is at most max_norm
+    (gradtuity/optim/utils.py:15-52).  Returns the pre-clip norm as a float.
+
+    defer=True skips the in-place scaling and the host read and returns `(norm_tensor,
+    scale_tensor)` device tensors instead, for `AdamW.step(grad_scale=scale_tensor)`."""
+    params = [p for p in params if p.grad is not None]
+    sumsq = empty_tensor((1,))
+    first = True
+    for p in params:
+        _call("gt_sumsq", c_void_p(sumsq.ptr), c_void_p(p.grad.ptr), p.grad.numel, 0 if first else 1)
+        first = False
+    if first:
+        return 0.0 if not defer else (None, None)
+    scale = empty_tensor((1,))
+    norm = empty_tensor((1,))
+    _call("gt_clip_scale", c_void_p(scale.ptr), c_void_p(norm.ptr), c_void_p(sumsq.ptr), float(max_norm), float(eps))
+    if defer:
+        return norm, scale
+    for p in params:
+        _call("gt_scale_by_device_scalar", c_void_p(p.grad.ptr), c_void_p(scale.ptr), p.grad.numel)
+    return norm.item()
+
+
+__all__ = ["Optimizer", "SGD", "AdamW", "clip_grad_norm_"]

@@ -32,6 +32,16 @@ from .cuda_mem import (cuda_device_synchronize, cuda_free, cuda_malloc, cuda_mem
 
 F32 = 4
 
+# Object told about the progress of backward(): begin(topo), node_done(parents), end().
+# The data-parallel gradient exchange installs one to send finished gradient buckets while the
+# rest of backward still runs (gradtuity_b200/dist/ddp.py).
+_backward_observer = None
+
+
+def set_backward_observer(observer) -> None:
+    global _backward_observer
+    _backward_observer = observer
+
 
 def _call(name: str, *args) -> None:
     lib = _lib.load_library()
@@ -273,15 +283,23 @@ class Tensor:
             else:
                 topo.append(node)
 
+        obs = _backward_observer
+        if obs is not None:
+            obs.begin(topo)
         for i in range(len(topo) - 1, -1, -1):
             node = topo[i]
+            parents = node._parents
             if node._backward is not None and node.grad is not None:
                 node._backward(node.grad)
-            if node._parents:
+            if parents:
                 node._parents = ()
                 node._backward = None
                 node._ctx = None
+                if obs is not None:
+                    obs.node_done(parents)
             topo[i] = None
+        if obs is not None:
+            obs.end()
 
     def _set_graph(self, parents: tuple["Tensor", ...], backward_fn: Callable[["Tensor"], None], ctx: Optional[dict] = None) -> None:
         """Attach graph fields only if some parent requires grad (gradtuity/tensor.py:415-445)."""
@@ -507,6 +525,257 @@ class Tensor:
 
         out._set_graph(parents=(self, weight), backward_fn=_backward)
         return out
+
+    # ---- attention: the batched per-head products ---------------------------------------------
+
+    def causal_attention(self, k: "Tensor", v: "Tensor", num_heads: int) -> "Tensor":
+        """Causal multi-head attention on projection outputs: self = Q, k, v, all (B, S, E).
+
+        Computes exactly what the reference's CausalSelfAttention computes between its
+        projections (gradtuity/nn.py:534-549): S = Q Kᵀ / sqrt(d) per head, P = causal softmax,
+        O = P V, heads merged back to (B, S, E).  Here the three batched products and their four
+        backward products are single strided-batched GEMM launches that address the per-head
+        slices of the (B, S, H, d) buffers in place, so none of transpose4d_12 /
+        transpose4d_last2 / scale_inplace runs and no (B, H, S, d) copy exists; the 1/sqrt(d)
+        scale and the causal mask sit in the score GEMM's epilogue (tiles wholly above the diagonal
+        are not computed).  P (B, H, S, S) is kept for the backward, as in the reference.
+        """
+        q = self
+        if q.ndim != 3 or k.shape != q.shape or v.shape != q.shape:
+            raise ValueError(f"causal_attention requires q, k, v of the same (B, S, E) shape, got {q.shape}, {k.shape}, {v.shape}")
+        B, S, E = q.shape
+        H = num_heads
+        if H <= 0 or E % H != 0:
+            raise ValueError(f"embed_dim ({E}) must be divisible by num_heads ({H})")
+        D = E // H
+        scale = 1.0 / (D ** 0.5)
+        from ._lib import EPI_CAUSAL
+        p = empty_tensor((B, H, S, S))
+        # scores[b, h] = scale * Q[b, :, h, :] K[b, :, h, :]^T, masked: NT, in-place heads
+        _gemm.gemm_batched(LAYOUT_NT, S, S, D, q.ptr, E, D, S * E, k.ptr, E, D, S * E,
+                           p.ptr, S, S * S, H * S * S, H, B, alpha=scale, epilogue=EPI_CAUSAL)
+        _call("gt_softmax", _vp(p.ptr), _vp(p.ptr), B * H * S, S, 1)
+        out = empty_tensor((B, S, E))
+        # O[b, :, h, :] = P[b, h] V[b, :, h, :]: NN, output written straight into (B, S, H, d)
+        _gemm.gemm_batched(LAYOUT_NN, S, D, S, p.ptr, S, S * S, H * S * S, v.ptr, E, D, S * E,
+                           out.ptr, E, D, S * E, H, B)
+
+        def _backward(g: "Tensor") -> None:
+            need_qk = q.requires_grad or k.requires_grad
+            if v.requires_grad:
+                ensure_grad(v)
+                # dV[b, :, h, :] += P[b, h]^T dO[b, :, h, :]   (TN)
+                _gemm.gemm_batched(LAYOUT_TN, S, D, S, p.ptr, S, S * S, H * S * S, g.ptr, E, D, S * E,
+                                   v.grad.ptr, E, D, S * E, H, B, accumulate=True)
+            if need_qk:
+                with temp_storage(B * H * S * S * F32) as st:
+                    # dP[b, h] = dO[b, :, h, :] V[b, :, h, :]^T   (NT); only the lower triangle is needed
+                    _gemm.gemm_batched(LAYOUT_NT, S, S, D, g.ptr, E, D, S * E, v.ptr, E, D, S * E,
+                                       st.ptr, S, S * S, H * S * S, H, B, epilogue=EPI_CAUSAL)
+                    # dS = scale * P * (dP - sum P dP), zero above the diagonal, in place
+                    _call("gt_softmax_backward", _vp(st.ptr), _vp(p.ptr), _vp(st.ptr), B * H * S, S, 1, scale)
+                    if q.requires_grad:
+                        ensure_grad(q)
+                        # dQ[b, :, h, :] += dS[b, h] K[b, :, h, :]   (NN)
+                        _gemm.gemm_batched(LAYOUT_NN, S, D, S, st.ptr, S, S * S, H * S * S, k.ptr, E, D, S * E,
+                                           q.grad.ptr, E, D, S * E, H, B, accumulate=True)
+                    if k.requires_grad:
+                        ensure_grad(k)
+                        # dK[b, :, h, :] += dS[b, h]^T Q[b, :, h, :]   (TN)
+                        _gemm.gemm_batched(LAYOUT_TN, S, D, S, st.ptr, S, S * S, H * S * S, q.ptr, E, D, S * E,
+                                           k.grad.ptr, E, D, S * E, H, B, accumulate=True)
+
+        out._set_graph(parents=(q, k, v), backward_fn=_backward)
+        return out
+
+    # ---- the other ops of the GPT-2 step --------------------------------------------------------
+
+    def softmax(self, dim: int = -1) -> "Tensor":
+        if dim != -1 and dim != self.ndim - 1:
+            raise ValueError(f"softmax v1 only supports dim=-1, got dim={dim}")
+        cols = self._shape[-1]
+        rows = self.numel // cols
+        out = empty_tensor(self.shape)
+        _call("gt_softmax", _vp(out.ptr), _vp(self.ptr), rows, cols, 0)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                with temp_storage(x.numel * F32) as st:
+                    _call("gt_softmax_backward", _vp(st.ptr), _vp(out.ptr), _vp(g.ptr), rows, cols, 0, 1.0)
+                    ensure_grad(x)
+                    _call("gt_scale", _vp(x.grad.ptr), _vp(st.ptr), 1.0, x.numel, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def softmax_with_causal_mask(self) -> "Tensor":
+        """Row softmax of a (B, H, S, S) score tensor under the causal mask; masked probabilities
+        are exactly 0 (gradtuity/tensor.py:1035-1084)."""
+        if self.ndim != 4:
+            raise ValueError(f"softmax_with_causal_mask requires ndim=4, got ndim={self.ndim}")
+        if self._shape[2] != self._shape[3]:
+            raise ValueError(f"softmax_with_causal_mask requires square last two dims, got {self._shape}")
+        cols = self._shape[-1]
+        rows = self.numel // cols
+        out = empty_tensor(self.shape)
+        _call("gt_softmax", _vp(out.ptr), _vp(self.ptr), rows, cols, 1)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                with temp_storage(x.numel * F32) as st:
+                    _call("gt_softmax_backward", _vp(st.ptr), _vp(out.ptr), _vp(g.ptr), rows, cols, 1, 1.0)
+                    ensure_grad(x)
+                    _call("gt_scale", _vp(x.grad.ptr), _vp(st.ptr), 1.0, x.numel, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def layer_norm(self, gamma: "Tensor", beta: "Tensor", eps: float = 1e-5) -> "Tensor":
+        """LayerNorm over the last dimension (gradtuity/tensor.py:1086-1188)."""
+        if self.ndim not in (2, 3, 4):
+            raise ValueError(f"layer_norm v1 requires ndim in (2, 3, 4), got ndim={self.ndim}")
+        if gamma.ndim != 1 or beta.ndim != 1:
+            raise ValueError(f"layer_norm requires 1D gamma and beta, got gamma.ndim={gamma.ndim}, beta.ndim={beta.ndim}")
+        Hd = self.shape[-1]
+        if gamma.shape[0] != Hd or beta.shape[0] != Hd:
+            raise ValueError(f"layer_norm gamma/beta must have shape (H,) with H={Hd}, got gamma={gamma.shape}, beta={beta.shape}")
+        Nr = self.numel // Hd
+        out = empty_tensor(self.shape)
+        mean = empty_tensor((Nr,))
+        rstd = empty_tensor((Nr,))
+        _call("gt_layernorm", _vp(out.ptr), _vp(mean.ptr), _vp(rstd.ptr), _vp(self.ptr), _vp(gamma.ptr), _vp(beta.ptr), Nr, Hd, float(eps))
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            dx_ptr = 0
+            if x.requires_grad:
+                ensure_grad(x)
+                dx_ptr = x.grad.ptr
+            dg_ptr = db_ptr = 0
+            if gamma.requires_grad:
+                ensure_grad(gamma)
+                dg_ptr = gamma.grad.ptr
+            if beta.requires_grad:
+                ensure_grad(beta)
+                db_ptr = beta.grad.ptr
+            _call("gt_layernorm_backward", _vp(dx_ptr), _vp(dg_ptr), _vp(db_ptr), _vp(g.ptr), _vp(x.ptr), _vp(mean.ptr),
+                  _vp(rstd.ptr), _vp(gamma.ptr), Nr, Hd, 1)
+
+        out._set_graph(parents=(self, gamma, beta), backward_fn=_backward)
+        return out
+
+    def embedding(self, indices) -> "Tensor":
+        """Row gather out = self[indices], self = (V, D) weight; indices 1-D or 2-D list / tuple /
+        Tensor of float-encoded ids (gradtuity/tensor.py:659-758).  Index range is checked on the
+        device (status word) rather than by a host loop over a device-to-host copy."""
+        if self.ndim != 2:
+            raise ValueError(f"embedding requires 2D weight, got shape {self._shape}")
+        idx = indices if isinstance(indices, Tensor) else Tensor(indices)
+        if idx.ndim not in (1, 2):
+            raise ValueError(f"embedding indices must be 1D or 2D, got shape {idx.shape}")
+        V, D = self._shape
+        n = idx.numel
+        out = empty_tensor(idx.shape + (D,))
+        _call("gt_embedding", _vp(out.ptr), _vp(self.ptr), _vp(idx.ptr), n, D, V)
+        w = self
+
+        def _backward(g: "Tensor") -> None:
+            if w.requires_grad:
+                ensure_grad(w)
+                _call("gt_embedding_backward", _vp(w.grad.ptr), _vp(g.ptr), _vp(idx.ptr), n, D, V)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def cross_entropy(self, targets: "Tensor", reduction: str = "mean") -> "Tensor":
+        """Softmax cross-entropy of (B, C) logits against float-encoded class ids
+        (gradtuity/tensor.py:1452-1525).  The upstream gradient is read on the device, so the
+        backward needs no device-to-host copy."""
+        if self.ndim != 2:
+            raise ValueError(f"cross_entropy expects 2D logits, got ndim={self.ndim}")
+        if targets.ndim != 1:
+            raise ValueError(f"cross_entropy expects 1D targets, got ndim={targets.ndim}")
+        Bn, C = self.shape
+        if targets.shape[0] != Bn:
+            raise ValueError(f"cross_entropy batch size mismatch: logits {Bn} vs targets {targets.shape[0]}")
+        if reduction not in ("mean", "sum"):
+            raise ValueError(f"cross_entropy reduction must be 'mean' or 'sum', got {reduction!r}")
+        out = empty_tensor((1,))
+        row_loss = empty_tensor((Bn,))
+        row_lse = empty_tensor((Bn,))
+        _call("gt_cross_entropy", _vp(out.ptr), _vp(row_loss.ptr), _vp(row_lse.ptr), _vp(self.ptr), _vp(targets.ptr), Bn, C,
+              1 if reduction == "mean" else 0)
+        logits = self
+
+        def _backward(g: "Tensor") -> None:
+            if logits.requires_grad:
+                fresh = logits.grad is None
+                if fresh:
+                    logits.grad = empty_tensor(logits.shape)      # written, not accumulated: no memset
+                _call("gt_cross_entropy_backward", _vp(logits.grad.ptr), _vp(logits.ptr), _vp(targets.ptr), _vp(row_lse.ptr),
+                      _vp(g.ptr), (1.0 / Bn) if reduction == "mean" else 1.0, Bn, C, 0 if fresh else 1)
+
+        out._set_graph(parents=(self, targets), backward_fn=_backward)
+        return out
+
+    def transpose4d_12(self) -> "Tensor":
+        """(B, d1, d2, D) -> (B, d2, d1, D), materialised (gradtuity/tensor.py:1227-1260)."""
+        if self.ndim != 4:
+            raise ValueError(f"transpose4d_12 requires ndim=4, got ndim={self.ndim}")
+        Bn, d1, d2, D = self._shape
+        out = empty_tensor((Bn, d2, d1, D))
+        _call("gt_transpose12", _vp(out.ptr), _vp(self.ptr), Bn, d1, d2, D, 0)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _call("gt_transpose12", _vp(x.grad.ptr), _vp(g.ptr), Bn, d2, d1, D, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def transpose4d_last2(self) -> "Tensor":
+        """(B, H, M, N) -> (B, H, N, M), materialised (gradtuity/tensor.py:1190-1225)."""
+        if self.ndim != 4:
+            raise ValueError(f"transpose4d_last2 requires ndim=4, got ndim={self.ndim}")
+        Bn, Hn, Mr, Nc = self._shape
+        out = empty_tensor((Bn, Hn, Nc, Mr))
+        # rows of one element: (B*H, M, N, 1) -> (B*H, N, M, 1)
+        _call("gt_transpose12", _vp(out.ptr), _vp(self.ptr), Bn * Hn, Mr, Nc, 1, 0)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _call("gt_transpose12", _vp(x.grad.ptr), _vp(g.ptr), Bn * Hn, Nc, Mr, 1, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def scale_inplace(self, scalar: float) -> "Tensor":
+        """x *= scalar in the same buffer, as a graph node (gradtuity/tensor.py:2395-2427)."""
+        _call("gt_scale", _vp(self.ptr), _vp(self.ptr), float(scalar), self.numel, 0)
+        out = Tensor._from_ptr(self.ptr, self._shape, owns_memory=False, base=self._st)
+        x = self
+        s = float(scalar)
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _call("gt_scale", _vp(x.grad.ptr), _vp(g.ptr), s, x.numel, 1)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
+    def mse_loss(self, target: "Tensor") -> "Tensor":
+        """mean((self - target)^2) as a (1,) tensor (gradtuity/tensor.py:1390-1450)."""
+        if self.shape != target.shape:
+            raise ValueError(f"mse_loss shape mismatch: {self.shape} vs {target.shape}")
+        diff = self.add(target.scale(-1.0))
+        return diff.mul(diff).sum().scale(1.0 / self.numel)
 
     # ---- element-wise ops beside the GEMMs ------------------------------------------------
 

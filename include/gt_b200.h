@@ -229,6 +229,24 @@ int gt_clip_scale(gt_ctx* ctx, float* scale_out, float* norm_out, const float* s
 int gt_scale_by_device_scalar(gt_ctx* ctx, float* x, const float* s, int64_t n);
 int gt_transpose12(gt_ctx* ctx, float* out, const float* in, int64_t B, int64_t d1, int64_t d2, int64_t D, int accumulate);
 
+/* ---- data-parallel gradient exchange (single node, NCCL over NVLink / NVSwitch) ----------
+ * Replaces the reference's libnccl binding and the calls built on it:
+ *   gt_dist_get_unique_id  nccl_get_unique_id        gradtuity/dist/nccl.py:71-79
+ *   gt_dist_init           nccl_comm_init_rank       gradtuity/dist/nccl.py:92-112, dist/comm.py:97
+ *   gt_dist_destroy        nccl_comm_destroy         gradtuity/dist/nccl.py:186-189
+ *   gt_dist_allreduce      _nccl_all_reduce_inplace  gradtuity/dist/nccl.py:130-145, dist/comm.py:117-131
+ *   gt_dist_broadcast      _nccl_broadcast_inplace   gradtuity/dist/nccl.py:163-178, dist/comm.py:134-147
+ * Collectives are enqueued on a separate communication stream behind the work already given to
+ * the compute stream and return at once; gt_dist_wait orders the compute stream behind them.
+ * `average` != 0 divides by the world size inside the collective (ncclAvg).                   */
+int gt_dist_get_unique_id(gt_ctx* ctx, char* out128);
+int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128);
+int gt_dist_destroy(gt_ctx* ctx);
+int gt_dist_allreduce(gt_ctx* ctx, float* ptr, int64_t count, int average);
+int gt_dist_broadcast(gt_ctx* ctx, float* ptr, int64_t count, int root);
+int gt_dist_wait(gt_ctx* ctx, int host_sync);
+int gt_dist_info(gt_ctx* ctx, int* rank, int* world);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,99 @@
+"""Host stand-ins for the pieces of the gradient exchange that touch the GPU, so that the
+bucketing, arena and overlap logic of gradtuity_b200.dist.ddp can run in CPU processes:
+numpy-backed tensors, numpy memory ops, and a communicator over torch.distributed's gloo."""
+import ctypes
+
+import numpy as np
+
+
+class FakeTensor:
+    def __init__(self, array, requires_grad=False):
+        self.array = np.ascontiguousarray(array, dtype=np.float32)
+        self.requires_grad = requires_grad
+        self.grad = None
+        self._parents = ()
+        self._st = self
+
+    @property
+    def ptr(self):
+        return self.array.ctypes.data
+
+    @property
+    def numel(self):
+        return self.array.size
+
+    @property
+    def shape(self):
+        return self.array.shape
+
+
+def as_array(ptr, numel):
+    return np.ctypeslib.as_array((ctypes.c_float * numel).from_address(ptr))
+
+
+class HostMemoryOps:
+    def alloc_zeroed(self, numel):
+        return FakeTensor(np.zeros(numel, np.float32))
+
+    def ensure_grad(self, p):
+        if p.grad is None:
+            p.grad = FakeTensor(np.zeros(p.shape, np.float32))
+
+    def copy(self, dst_ptr, src_ptr, nbytes):
+        ctypes.memmove(dst_ptr, src_ptr, nbytes)
+
+    def view(self, arena, offset_elems, shape):
+        n = int(np.prod(shape))
+        v = FakeTensor.__new__(FakeTensor)
+        v.array = arena.array[offset_elems:offset_elems + n].reshape(shape)     # shares the arena's memory
+        v.requires_grad = False
+        v.grad = None
+        v._parents = ()
+        v._st = arena
+        return v
+
+
+class RecordingBackend:
+    """Single-process communicator that records calls; 'all-reduce' multiplies by a constant so
+    that a test can see which ranges were touched and how often."""
+
+    def __init__(self, world_size=2):
+        self.world_size = world_size
+        self.calls = []
+        self.waits = 0
+
+    def allreduce_async(self, ptr, numel, average):
+        self.calls.append((ptr, numel, average))
+        as_array(ptr, numel)[:] *= 10.0
+
+    def broadcast(self, ptr, numel, src):
+        self.calls.append(("bcast", ptr, numel, src))
+
+    def wait(self, host_sync=False):
+        self.waits += 1
+
+
+class GlooBackend:
+    """All-reduce over torch.distributed (gloo) on host memory addressed by raw pointers."""
+
+    def __init__(self):
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.world_size = dist.get_world_size()
+
+    def allreduce_async(self, ptr, numel, average):
+        import torch
+
+        t = torch.from_numpy(as_array(ptr, numel))
+        self.dist.all_reduce(t)
+        if average:
+            t /= self.world_size
+
+    def broadcast(self, ptr, numel, src):
+        import torch
+
+        self.dist.broadcast(torch.from_numpy(as_array(ptr, numel)), src)
+
+    def wait(self, host_sync=False):
+        pass

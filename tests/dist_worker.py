@@ -1,0 +1,61 @@
+"""Worker for the world_size-2 CPU tests (spawned by tests/test_dist.py through
+gradtuity_b200.launch).  Modes: allreduce | rendezvous | fail."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+
+def main():
+    mode = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if mode == "fail":
+        if rank == 1:
+            sys.exit(3)
+        import time
+        time.sleep(30)          # must be terminated by the launcher long before this ends
+        sys.exit(0)
+    if mode == "rendezvous":
+        from gradtuity_b200.dist import comm
+        uid = comm.exchange_unique_id(rank, lambda: bytes(range(128)), os.environ["GRADTUITY_NCCL_UID_FILE"], timeout=20)
+        assert uid == bytes(range(128))
+        return
+    if mode == "allreduce":
+        import torch.distributed as dist
+        from gradtuity_b200.dist import comm, ddp
+        from tests._dist_host import FakeTensor, GlooBackend, HostMemoryOps
+
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['MASTER_PORT']}", rank=rank, world_size=world)
+        comm.set_backend(GlooBackend())
+        ddp._mem_ops = HostMemoryOps()
+        rng = np.random.default_rng(100 + rank)
+        shapes = [(5, 3), (70,), (2, 2, 2), (129,)]
+        params = [FakeTensor(np.zeros(s), requires_grad=True) for s in shapes]
+        mine = [rng.standard_normal(s).astype(np.float32) for s in shapes]
+        for p, g in zip(params[:-1], mine[:-1]):      # the last parameter has no grad yet: zeros are created
+            p.grad = FakeTensor(g)
+        os.environ["GRADTUITY_BUCKET_MB"] = str(300 / (1024 * 1024))      # 300-byte buckets
+        ddp.sync_grads(params)
+        orng = np.random.default_rng(100 + (1 - rank))
+        other = [orng.standard_normal(s).astype(np.float32) for s in shapes]
+        for i, p in enumerate(params):
+            want = (mine[i] + other[i]) / 2 if i < len(shapes) - 1 else np.zeros(shapes[i], np.float32)
+            np.testing.assert_allclose(p.grad.array, want, rtol=1e-6, atol=1e-7)
+        # second step: the plan is reused, gradients are views of the same arena
+        plan = next(iter(ddp._plans.values()))
+        assert plan.intact()
+        for p, g in zip(params, mine):
+            p.grad.array[...] = g
+        ddp.sync_grads(params)
+        for i, p in enumerate(params):
+            np.testing.assert_allclose(p.grad.array, (mine[i] + other[i]) / 2, rtol=1e-6, atol=1e-7)
+        dist.destroy_process_group()
+        return
+    raise SystemExit(f"unknown mode {mode}")
+
+
+if __name__ == "__main__":
+    main()

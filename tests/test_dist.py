@@ -1,0 +1,162 @@
+"""CPU: host logic of the data-parallel path: environment parsing, the bucket rule, the gradient
+arena, the backward-overlap bookkeeping, the unique-id rendezvous, the launcher, and a
+world_size-2 run over gloo."""
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+import pytest
+
+from gradtuity_b200.dist import comm, ddp
+from gradtuity_b200.dist import env as dist_env
+from tests._dist_host import FakeTensor, HostMemoryOps, RecordingBackend
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+WORKER = os.path.join(ROOT, "tests", "dist_worker.py")
+
+
+@pytest.fixture(autouse=True)
+def _clean():
+    yield
+    ddp.reset()
+    ddp._mem_ops = None
+    comm.set_backend(None)
+
+
+def test_env_parsing(monkeypatch):
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "SLURM_PROCID", "SLURM_NTASKS", "SLURM_LOCALID", "MASTER_ADDR", "MASTER_PORT"):
+        monkeypatch.delenv(k, raising=False)
+    with pytest.raises(RuntimeError, match="RANK"):
+        dist_env.get_rank()
+    with pytest.raises(RuntimeError, match="WORLD_SIZE"):
+        dist_env.get_world_size()
+    monkeypatch.setenv("SLURM_PROCID", "3"); monkeypatch.setenv("SLURM_NTASKS", "8"); monkeypatch.setenv("SLURM_LOCALID", "1")
+    assert (dist_env.get_rank(), dist_env.get_world_size(), dist_env.get_local_rank()) == (3, 8, 1)
+    monkeypatch.setenv("RANK", "5"); monkeypatch.setenv("WORLD_SIZE", "6"); monkeypatch.setenv("LOCAL_RANK", "2")
+    monkeypatch.setenv("MASTER_ADDR", "127.0.0.1"); monkeypatch.setenv("MASTER_PORT", "1234")
+    assert dist_env.get_env_ranks() == (5, 6, 2, "127.0.0.1", "1234")
+
+
+def test_world_size_one_is_a_no_op(monkeypatch):
+    monkeypatch.setenv("RANK", "0"); monkeypatch.setenv("WORLD_SIZE", "1"); monkeypatch.setenv("LOCAL_RANK", "0")
+    p = FakeTensor(np.ones(4), requires_grad=True)
+    ddp.sync_grads([p])                    # no backend installed: must not be needed
+    assert p.grad is None
+    comm.allreduce_inplace(0, 4)
+    comm.broadcast(0, 4)
+    comm.barrier()
+
+
+def test_bucket_rule_matches_the_reference():
+    # a bucket closes when the next entry would exceed the limit and the bucket is not empty
+    assert ddp.bucketize([10, 10, 30, 5, 5], 20) == [[0, 1], [2], [3, 4]]
+    assert ddp.bucketize([100], 20) == [[0]]
+    assert ddp.bucketize([], 20) == []
+    assert ddp.bucketize([20, 1], 20) == [[0], [1]]
+    # GPT-2-small: the 154 MB embedding gradient ends up alone, about 21 buckets in all
+    sizes = [50257 * 768, 1024 * 768]
+    for _ in range(12):
+        sizes += [768, 768] + [768 * 768] * 4 + [768] * 4 + [768, 768, 768 * 3072, 3072, 3072 * 768, 768]
+    sizes += [768, 768]
+    assert sum(sizes) == 124439808
+    b = ddp.bucketize([4 * s for s in sizes], 25 * 1024 * 1024)
+    assert b[0] == [0] and 15 <= len(b) <= 25
+
+
+def test_arena_offsets_are_aligned():
+    offs, total = ddp.arena_offsets([3, 64, 65, 1])
+    assert offs == [0, 64, 128, 256] and total == 320
+
+
+def _plan(monkeypatch, shapes, bucket_bytes):
+    monkeypatch.setenv("RANK", "0"); monkeypatch.setenv("WORLD_SIZE", "2"); monkeypatch.setenv("LOCAL_RANK", "0")
+    monkeypatch.setenv("GRADTUITY_BUCKET_MB", str(bucket_bytes / (1024 * 1024)))
+    be = RecordingBackend()
+    comm.set_backend(be)
+    ddp._mem_ops = HostMemoryOps()
+    params = [FakeTensor(np.zeros(s), requires_grad=True) for s in shapes]
+    for i, p in enumerate(params):
+        p.grad = FakeTensor(np.full(p.shape, float(i + 1)))
+    return params, be
+
+
+def test_first_sync_moves_grads_into_one_arena_and_reduces_every_bucket_once(monkeypatch):
+    params, be = _plan(monkeypatch, [(4,), (100,), (8,), (8,)], 300)
+    ddp.sync_grads(params)
+    plan = next(iter(ddp._plans.values()))
+    assert plan.buckets == [[0], [1], [2, 3]]
+    assert [c[1] for c in be.calls] == [4, 100, 64 + 8]          # ranges include alignment padding
+    assert all(c[2] is True for c in be.calls) and be.waits == 1
+    for i, p in enumerate(params):                                 # values survived the move, touched exactly once
+        assert p.grad is plan.views[i]
+        np.testing.assert_allclose(p.grad.array, 10.0 * (i + 1))
+    base = plan.arena.ptr
+    assert [p.grad.ptr - base for p in params] == [0, 256, 768, 1024]
+
+
+def test_backward_observer_sends_buckets_as_soon_as_their_last_consumer_ran(monkeypatch):
+    from gradtuity_b200 import tensor as tmod
+
+    params, be = _plan(monkeypatch, [(4,), (4,), (4,), (4,)], 40)       # two params per bucket
+    ddp.sync_grads(params)
+    plan = next(iter(ddp._plans.values()))
+    assert tmod._backward_observer is plan and plan.buckets == [[0, 1], [2, 3]]
+    be.calls.clear()
+    # graph: n3 uses p3 and p2; n2 uses p2; n1 uses p1; p0 unused this step.  Reverse walk: n3, n2, n1.
+    def node(*parents):
+        n = FakeTensor(np.zeros(1)); n._parents = parents; return n
+    n1, n2, n3 = node(params[1]), node(params[2]), node(params[3], params[2])
+    topo = [params[1], n1, params[2], n2, params[3], n3]
+    plan.begin(topo)
+    plan.node_done(n3._parents)
+    assert be.calls == []                       # p2 still has a consumer
+    plan.node_done(n2._parents)
+    assert len(be.calls) == 1 and be.calls[0][0] == plan.ranges[1][0]      # bucket 1 went out during backward
+    plan.node_done(n1._parents)
+    assert len(be.calls) == 1                   # bucket 0 holds p0, which was not in the graph: it waits
+    plan.end()
+    ddp.sync_grads(params)
+    assert [c[0] for c in be.calls] == [plan.ranges[1][0], plan.ranges[0][0]]   # every bucket exactly once
+    # a replaced grad tensor invalidates the plan: the next sync rebuilds it
+    params[0].grad = FakeTensor(np.ones(4))
+    ddp.sync_grads(params)
+    assert next(iter(ddp._plans.values())) is not plan
+
+
+def test_rendezvous_times_out_with_a_diagnostic(tmp_path):
+    with pytest.raises(RuntimeError, match="did not reach 128 bytes"):
+        comm.exchange_unique_id(1, None, str(tmp_path / "never.bin"), timeout=0.2)
+    with pytest.raises(RuntimeError, match="unique id has"):
+        comm.exchange_unique_id(0, lambda: b"short", str(tmp_path / "x.bin"))
+
+
+def test_collectives_without_a_group_raise(monkeypatch):
+    monkeypatch.setenv("RANK", "0"); monkeypatch.setenv("WORLD_SIZE", "2"); monkeypatch.setenv("LOCAL_RANK", "0")
+    with pytest.raises(RuntimeError, match="not initialized"):
+        comm.allreduce_inplace(0, 1)
+    with pytest.raises(RuntimeError, match="not initialized"):
+        ddp.sync_grads([FakeTensor(np.zeros(2), requires_grad=True)])
+
+
+def _launch(mode, nproc=2, timeout=120):
+    cmd = [sys.executable, "-m", "gradtuity_b200.launch", "--nproc", str(nproc), "--master-addr", "127.0.0.1", WORKER, mode]
+    return subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=timeout)
+
+
+def test_two_ranks_rendezvous_through_the_uid_file():
+    r = _launch("rendezvous")
+    assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_two_ranks_sync_grads_over_gloo():
+    r = _launch("allreduce")
+    assert r.returncode == 0, r.stderr[-3000:]
+
+
+def test_launcher_stops_siblings_and_propagates_the_exit_code():
+    t0 = time.monotonic()
+    r = _launch("fail")
+    assert r.returncode == 3
+    assert time.monotonic() - t0 < 20          # rank 0 sleeps 30 s unless the launcher terminates it

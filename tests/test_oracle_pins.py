@@ -85,3 +85,39 @@ def test_attention_oracle_consistency():
     e = np.zeros_like(q); e[0, 1, 3, 2] = h
     fd = (loss(q + e) - loss(q - e)) / (2 * h)
     assert abs(fd - r["dq"][0, 1, 3, 2]) < 1e-6
+
+
+def test_gpt2_oracle_backward_matches_finite_differences():
+    from oracle.gpt2_oracle import GPT2Oracle
+
+    rng = np.random.default_rng(3)
+    V, S, E, H, L, B = 11, 5, 8, 2, 2, 2
+    p = {"wte.weight": rng.standard_normal((V, E)) * 0.3, "wpe.embed.weight": rng.standard_normal((S, E)) * 0.3,
+         "ln_f.gamma": 1 + 0.1 * rng.standard_normal(E), "ln_f.beta": 0.1 * rng.standard_normal(E)}
+    for l in range(L):
+        pre = f"blocks.{l}."
+        for ln in ("ln1", "ln2"):
+            p[pre + ln + ".gamma"] = 1 + 0.1 * rng.standard_normal(E)
+            p[pre + ln + ".beta"] = 0.1 * rng.standard_normal(E)
+        for w in ("Wq", "Wk", "Wv", "Wo"):
+            p[pre + "attn." + w] = rng.standard_normal((E, E)) * 0.3
+            p[pre + "attn.b" + w[1]] = rng.standard_normal(E) * 0.1
+        p[pre + "mlp_fc1.weight"] = rng.standard_normal((E, 4 * E)) * 0.3
+        p[pre + "mlp_fc1.bias"] = rng.standard_normal(4 * E) * 0.1
+        p[pre + "mlp_fc2.weight"] = rng.standard_normal((4 * E, E)) * 0.3
+        p[pre + "mlp_fc2.bias"] = rng.standard_normal(E) * 0.1
+    ids = rng.integers(0, V, (B, S))
+    labels = rng.integers(0, V, B * S)
+    orc = GPT2Oracle(L, H)
+    loss, g = orc.loss_and_grads(p, ids, labels)
+    assert set(g) == set(p)
+    h = 1e-6
+    for key in ["wte.weight", "wpe.embed.weight", "blocks.0.attn.Wk", "blocks.1.attn.bq", "blocks.0.ln1.gamma",
+                "blocks.1.mlp_fc1.weight", "blocks.0.mlp_fc2.bias", "ln_f.beta", "blocks.1.attn.Wo"]:
+        idx = tuple(rng.integers(0, s) for s in p[key].shape)
+        q = {k: v.copy() for k, v in p.items()}
+        q[key][idx] += h
+        lp = orc.loss_and_grads(q, ids, labels)[0]
+        q[key][idx] -= 2 * h
+        lm = orc.loss_and_grads(q, ids, labels)[0]
+        assert abs((lp - lm) / (2 * h) - g[key][idx]) < 1e-6, key
