@@ -246,10 +246,77 @@ def run_ours(args) -> dict:
     }
     if rank == 0 and world == 1:
         out["cpu_baseline"] = cpu_baseline(a_host, b_host, reps=3)
+    if not args.no_train:
+        # free the GEMM operands before the model is built
+        del ta, tb, tc
+        for ptr_ in (pa, pb, pc):
+            lib.gt_host_free(ctx, ptr_)
+        train = run_train(args, world, rank, lambda v: _barrier_max(dist, v))
+        out["train"] = train
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
     return out if rank == 0 else None
+
+
+TRAIN_FLOPS_PER_STEP = 6.0 * 123532032 * 8192 + 3 * 12 * 2 * (2.0 * 96 * 1024 * 1024 * 64)   # 7.00 TFLOP per GPU
+
+
+def run_train(args, world: int, rank: int, barrier_max) -> dict:
+    """GPT-2-small data-parallel training (configs 3 and 4): batch 8 x 1024 tokens per GPU, uniform random
+    tokens, weights N(0, 0.02), dropout 0, AdamW lr 3e-4, clip 1.0.  Every step uploads its token ids
+    and labels from host memory and reads the loss back, so the number is end to end."""
+    from ctypes import byref, c_float, c_void_p
+
+    from gradtuity_b200 import _lib
+    from gradtuity_b200.gpt2.train import build_model, synthetic_batch, train_step
+    from gradtuity_b200.optim import AdamW
+    from gradtuity_b200.tensor import Tensor
+
+    lib = _lib.load_library()
+    ctx = _lib.context()
+    if world > 1:
+        from gradtuity_b200 import dist as gdist
+
+        gdist.init()
+    model = build_model()
+    params = model.parameters()
+    if world > 1:
+        gdist.init_sync(model)
+    opt = AdamW(params, lr=3e-4, weight_decay=0.01)
+    steps = max(2, min(args.steps, 10))
+    warm = 3
+    batches = [synthetic_batch(i, rank, 8, 1024, 50257) for i in range(warm + steps)]
+    losses = []
+    for i in range(warm):
+        losses.append(train_step(model, opt, params, Tensor.from_numpy(batches[i][0]), Tensor.from_numpy(batches[i][1]), 1.0, world).item())
+    _lib.check(lib.gt_sync(ctx), "gt_sync")
+    barrier_max(0.0)
+    l0 = _lib.launch_count()
+    e0, e1 = c_void_p(), c_void_p()
+    lib.gt_event_create(ctx, byref(e0)); lib.gt_event_create(ctx, byref(e1))
+    lib.gt_event_record(ctx, e0)
+    for i in range(warm, warm + steps):
+        losses.append(train_step(model, opt, params, Tensor.from_numpy(batches[i][0]), Tensor.from_numpy(batches[i][1]), 1.0, world).item())
+    lib.gt_event_record(ctx, e1)
+    ms = c_float()
+    _lib.check(lib.gt_event_elapsed_ms(ctx, e0, e1, byref(ms)), "gt_event_elapsed_ms")
+    _lib.device_status()
+    launches = _lib.launch_count() - l0
+    total_ms = barrier_max(ms.value)
+    if world > 1:
+        gdist.destroy_process_group()
+    step_ms = total_ms / steps
+    tokens = world * 8 * 1024
+    return {"metric": "gpt2_small_train_tokens_per_s", "value": round(tokens / (step_ms * 1e-3), 1), "unit": "tokens/s",
+            "ms_per_step": round(step_ms, 3), "steps": steps, "warmup": warm, "n_gpus": world,
+            "tflops_per_gpu": round(TRAIN_FLOPS_PER_STEP / (step_ms * 1e-3) / 1e12, 2),
+            "frac_of_tf32_peak_measured": round(TRAIN_FLOPS_PER_STEP / (step_ms * 1e-3) / 1e12 / _peaks()[0], 4),
+            "h2d_bytes_per_step": int(batches[0][0].nbytes + batches[0][1].nbytes), "d2h_bytes_per_step": 4,
+            "gpu_launches_per_step": int(launches // steps), "loss_first": round(losses[0], 4), "loss_last": round(losses[-1], 4),
+            "config": {"workload": "GPT-2-small train step, batch 8x1024 per GPU, fp32 storage, tf32 GEMMs, AdamW, clip 1.0",
+                       "parallelism": f"dp{world}" if world > 1 else "single GPU",
+                       "sync": "sync_grads: NCCL all-reduce (avg) of 25 MiB buckets on a side stream, overlapped with backward" if world > 1 else "none"}}
 
 
 def run_micro(args) -> dict:
@@ -297,6 +364,63 @@ def run_micro(args) -> dict:
     return {"micro": True, "shape": [m, n, k], "layout": args.layout, "precision": args.precision, "epilogue": args.epilogue,
             "accumulate": bool(args.accumulate), "ms": round(t, 5), "tflops": round(flops / t / 1e9, 2),
             "gbs": round(nbytes / t / 1e6, 1), "steps": args.steps, "warmup": args.warmup}
+
+
+def run_attn(args) -> dict:
+    """Kernel-only timing of the batched attention products of config 2 (B=8, H=12, T=1024, d=64),
+    reported as achieved GB/s: these GEMMs are HBM-bound (28 FLOP per byte)."""
+    import numpy as np
+    from ctypes import byref, c_float, c_void_p
+
+    from gradtuity_b200 import _lib
+    from gradtuity_b200 import gemm as G
+    from gradtuity_b200.tensor import Tensor
+
+    lib = _lib.load_library()
+    ctx = _lib.context()
+    B, H, S, D = 8, 12, 1024, 64
+    E = H * D
+    rng = np.random.default_rng(2)
+    q, k, v, do = (Tensor.from_numpy(rng.standard_normal((B, S, E), dtype=np.float32)) for _ in range(4))
+    p = Tensor._zeros((B, H, S, S)); dp = Tensor._zeros((B, H, S, S)); o = Tensor._zeros((B, S, E))
+    hbm = _hbm_peak()
+    cases = {
+        "S=QK^T*scale+mask (NT)": (lambda: G.gemm_batched(1, S, S, D, q.ptr, E, D, S * E, k.ptr, E, D, S * E, p.ptr, S, S * S, H * S * S, H, B,
+                                                            alpha=0.125, epilogue=4), 4.0 * B * H * (2 * S * D + S * S)),
+        "O=PV (NN)": (lambda: G.gemm_batched(0, S, D, S, p.ptr, S, S * S, H * S * S, v.ptr, E, D, S * E, o.ptr, E, D, S * E, H, B),
+                      4.0 * B * H * (S * S + 2 * S * D)),
+        "dP=dO V^T (NT)": (lambda: G.gemm_batched(1, S, S, D, do.ptr, E, D, S * E, v.ptr, E, D, S * E, dp.ptr, S, S * S, H * S * S, H, B, epilogue=4),
+                           4.0 * B * H * (2 * S * D + S * S)),
+        "dV+=P^T dO (TN)": (lambda: G.gemm_batched(2, S, D, S, p.ptr, S, S * S, H * S * S, do.ptr, E, D, S * E, o.ptr, E, D, S * E, H, B, accumulate=True),
+                            4.0 * B * H * (S * S + 3 * S * D)),
+        "dQ+=dS K (NN)": (lambda: G.gemm_batched(0, S, D, S, dp.ptr, S, S * S, H * S * S, k.ptr, E, D, S * E, o.ptr, E, D, S * E, H, B, accumulate=True),
+                          4.0 * B * H * (S * S + 3 * S * D)),
+    }
+    out = {"attn": True, "config": "B=8 H=12 T=1024 d=64, heads read in place from (B,T,H*d)", "hbm_peak_gbs": hbm, "cases": {}}
+    for name, (fn, nbytes) in cases.items():
+        for _ in range(args.warmup):
+            fn()
+        e0, e1 = c_void_p(), c_void_p()
+        lib.gt_event_create(ctx, byref(e0)); lib.gt_event_create(ctx, byref(e1))
+        lib.gt_event_record(ctx, e0)
+        for _ in range(args.steps):
+            fn()
+        lib.gt_event_record(ctx, e1)
+        ms = c_float()
+        _lib.check(lib.gt_event_elapsed_ms(ctx, e0, e1, byref(ms)), "gt_event_elapsed_ms")
+        t = ms.value / args.steps
+        out["cases"][name] = {"ms": round(t, 4), "gbs": round(nbytes / t / 1e6, 1), "frac_hbm": round(nbytes / t / 1e6 / hbm, 3),
+                              "tflops_dense_equiv": round(2.0 * B * H * S * S * D / t / 1e9, 1)}
+    _lib.device_status()
+    return out
+
+
+def _hbm_peak() -> float:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"])
+    return 6650.0
 
 
 def _blas_threads() -> int:
@@ -366,7 +490,12 @@ def main():
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
     ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_relu", "bias_gelu", "causal"])
     ap.add_argument("--accumulate", action="store_true")
+    ap.add_argument("--attn", action="store_true", help="kernel-only timing of the batched attention products (GB/s)")
+    ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the GPT-2 training leg")
     args = ap.parse_args()
+    if args.attn:
+        print(json.dumps(run_attn(args)), flush=True)
+        return
     if args.shape:
         print(json.dumps(run_micro(args)), flush=True)
         return

@@ -27,6 +27,8 @@
 // Replaces: gradtuity/kernels_triton/matmul_kernels.py:18-400 (five kernels, 32x32x32 tiles,
 // tl.dot) and gradtuity/kernels_cuda/matmul_kernels.py:21-236.
 
+#include <stdlib.h>
+
 #include "gt_internal.h"
 
 namespace {
@@ -34,18 +36,23 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 32;                       // fp32 elements per k-block = 128 bytes
 constexpr int UMMA_K = 8;                    // tf32 elements per tcgen05.mma
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 192;            // producer warp, MMA warp, 4 epilogue warps
+constexpr int NUM_THREADS_AGEN = 320;       // + 4 warps that copy an unaligned A operand with cp.async
+constexpr int EPI_SCRATCH_BYTES = 4 * 32 * 33 * 4;   // per-warp 32 x 33 staging tile of the coalesced epilogue
 constexpr int MAX_STAGES = 8;
 constexpr int X3_CHUNK_KB = 8;                // 3xTF32: k-blocks accumulated in tensor memory before an fp32 register add
-constexpr int SMEM_BUDGET = 232448 - 1024 - 512;   // 227 KB minus alignment slack and barriers
+constexpr int SMEM_BUDGET = 232448 - 1024 - 512 - EPI_SCRATCH_BYTES;   // 227 KB minus alignment slack, barriers, epilogue staging
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;   // about 1.5 s at 1.9 GHz
 
 struct UmmaParams {
+  const float* A; long long lda, sA0, sA1;     // used only when A is copied with cp.async
   float* C; const float* bias; float* aux;
   long long ldc, sC0, sC1;
   int M, N, K;
   int batch0;
-  int tiles_m, tiles_n, num_tiles;
+  int tiles_m, tiles_n, num_tiles;       // num_tiles counts work units: output tiles x ksplit
+  int ksplit, kb_per;                    // split-K: units per tile, k-blocks per unit
+  long long ks_stride;                   // split-K: element offset between the partial-sum planes of C
   int group_m;
   int epilogue, accumulate, vec_ok;
   float alpha;
@@ -162,12 +169,14 @@ struct Cfg {
   static constexpr int STAGES_RAW = SMEM_BUDGET / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > MAX_STAGES ? MAX_STAGES : STAGES_RAW;
   static constexpr int TMEM_COLS = (2 * BN) < 32 ? 32 : (2 * BN);   // 128 / 256 / 512: powers of two
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512 + EPI_SCRATCH_BYTES;
 };
 
 // Tile list order: groups of `group_m` row-tiles sweep all column-tiles before the next
 // group starts, so CTAs that run together share A and B panels in L2.
-__device__ __forceinline__ void tile_coords(const UmmaParams& p, int tile, int& batch, int& tm, int& tn) {
+__device__ __forceinline__ void tile_coords(const UmmaParams& p, int unit, int& batch, int& tm, int& tn, int& ks) {
+  ks = unit % p.ksplit;
+  const int tile = unit / p.ksplit;
   const int per_batch = p.tiles_m * p.tiles_n;
   batch = tile / per_batch;
   const int t = tile - batch * per_batch;
@@ -235,8 +244,37 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float*
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool X3>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// Same epilogue for outputs whose rows are not 16-byte aligned (odd leading dimension, e.g. the
+// 50257-wide logits): the warp's 32 x 32 accumulator block goes through a shared-memory tile so
+// that each store instruction writes 32 consecutive floats of ONE row, whatever its alignment.
+__device__ __forceinline__ void epilogue_chunk_coalesced(const UmmaParams& p, const float* v, float* tile, int lane,
+                                                         int row0, int nb, long long batch_off) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = v[j];
+  __syncwarp();
+  const int col = nb + lane;
+  const bool col_ok = col < p.N;
+  const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
+  const float b = (has_bias && col_ok) ? p.bias[col] : 0.0f;
+  const int rows = min(32, p.M - row0);
+  for (int r = 0; r < rows; ++r) {
+    if (col_ok) {
+      const int row = row0 + r;
+      const long long off = batch_off + (long long)row * p.ldc + col;
+      float x = p.alpha * tile[r * 33 + lane] + b;
+      if (p.aux) p.aux[off] = x;
+      if (p.epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
+      else if (p.epilogue == GT_EPI_BIAS_GELU) x = gt_gelu_tanh(x);
+      else if (p.epilogue == GT_EPI_CAUSAL && col > row) x = GT_CAUSAL_MASK_VALUE;
+      if (p.accumulate) x += p.C[off];
+      p.C[off] = x;
+    }
+  }
+  __syncwarp();
+}
+
+template <int BN, bool A_MN, bool B_MN, bool X3, bool A_GEN>
+__global__ void __launch_bounds__(A_GEN ? NUM_THREADS_AGEN : NUM_THREADS, 1)
 gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
                     const UmmaParams p) {
@@ -249,6 +287,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);              // full[S], empty[S], tfull[2], tempty[2], drain
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * MAX_STAGES + 5));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* epi_scratch = reinterpret_cast<float*>(ctrl + 512);
 
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
@@ -261,7 +300,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, A_GEN ? 1 + 128 : 1);   // TMA issuer (+ one arrival per cp.async thread)
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -291,19 +330,22 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       long long issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        int batch, tm, tn;
-        tile_coords(p, tile, batch, tm, tn);
+        int batch, tm, tn, ks;
+        tile_coords(p, tile, batch, tm, tn, ks);
+        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
         if (tile_is_masked<BN>(p, tm, tn)) continue;
         const int i0 = batch % p.batch0, i1 = batch / p.batch0;
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) { ok = false; break; }
           const uint32_t full = bar_full + 8 * s;
-          mbar_expect_tx(full, C::STAGE_BYTES);
+          mbar_expect_tx(full, A_GEN ? C::B_BYTES : C::STAGE_BYTES);
           const uint32_t sa = smem_base + s * C::STAGE_BYTES;
           const uint32_t sb = sa + C::A_BYTES * (X3 ? 2 : 1);
           const int k0 = kb * BK;
-          if (A_MN) {
+          if (A_GEN) {
+            // A arrives through the cp.async warps
+          } else if (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 32; ++j) {
               tma_load_4d(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
@@ -347,20 +389,22 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       bool any_issued = false;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        int batch, tm, tn;
-        tile_coords(p, tile, batch, tm, tn);
+        int batch, tm, tn, ks;
+        tile_coords(p, tile, batch, tm, tn, ks);
+        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
         if (tile_is_masked<BN>(p, tm, tn)) continue;
         // tf32: one accumulator per tile.  3xTF32: a fresh accumulator every X3_CHUNK_KB k-blocks,
         // because the tensor core truncates on every accumulate and the bias grows with the
         // length of the chain (measured 2.4e-6 relative per 1024 of K).
-        const int chunk_kb = X3 ? X3_CHUNK_KB : num_kb;
-        for (int kb0 = 0; ok && kb0 < num_kb; kb0 += chunk_kb) {
+        const int chunk_kb = X3 ? X3_CHUNK_KB : (kb_hi - kb_lo);
+        for (int kb0 = kb_lo; ok && kb0 < kb_hi; kb0 += chunk_kb) {
           if (!mbar_wait(bar_tempty + 8 * acc, aph ^ 1u, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-          const int kb1 = min(kb0 + chunk_kb, num_kb);
+          const int kb1 = min(kb0 + chunk_kb, kb_hi);
           for (int kb = kb0; kb < kb1; ++kb) {
             if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) { ok = false; break; }
+            if (A_GEN) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // cp.async wrote A through the generic proxy
             tc_fence_after();
             const uint32_t sa = smem_base + s * C::STAGE_BYTES;
             const uint32_t sb = sa + C::A_BYTES * (X3 ? 2 : 1);
@@ -402,20 +446,74 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         while (!mbar_try_wait(bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
       }
     }
+  } else if (A_GEN && warp >= 6) {
+    // ------------------------------ cp.async copy of A ------------------------------
+    // A's leading dimension (or base) is not 16-byte aligned, so TMA cannot describe it.  These
+    // 128 threads write the same swizzled tile TMA would have written, 4 bytes at a time, a warp
+    // per 128-byte run; each thread's copies arrive on the stage's full barrier when they land.
+    const int t = threadIdx.x - 192;
+    int s = 0; uint32_t ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int batch, tm, tn, ks;
+      tile_coords(p, tile, batch, tm, tn, ks);
+      const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+      if (tile_is_masked<BN>(p, tm, tn)) continue;
+      const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+      const float* Ab = p.A + (long long)i0 * p.sA0 + (long long)i1 * p.sA1;
+      const int m0 = tm * BM;
+      for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        const uint32_t sa = smem_base + s * C::STAGE_BYTES;
+        const int k0 = kb * BK;
+        if (A_MN) {
+          // stored (K, M): thread t owns column m0 + t of every k-row; a warp covers 32 consecutive m
+          const int m = t;
+          const bool m_ok = (m0 + m) < p.M;
+          const uint32_t base = sa + (uint32_t)(m >> 5) * 4096u + (uint32_t)(m & 7) * 4u;
+          const int c32 = (m & 31) >> 3;
+#pragma unroll 8
+          for (int kr = 0; kr < BK; ++kr) {
+            const bool okk = m_ok && (k0 + kr) < p.K;
+            const float* src = okk ? Ab + (long long)(k0 + kr) * p.lda + (m0 + m) : Ab;
+            const uint32_t dst = base + (uint32_t)kr * 128u + (uint32_t)((c32 ^ (kr & 3)) << 5);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(okk ? 4 : 0) : "memory");
+          }
+        } else {
+          // stored (M, K): a warp covers the 32 k-values of one row; thread t takes rows (t/32) + 4 i
+          const int k = t & 31;
+          const bool k_ok = (k0 + k) < p.K;
+#pragma unroll 8
+          for (int i = 0; i < BM / 4; ++i) {
+            const int r = i * 4 + (t >> 5);
+            const bool okk = k_ok && (m0 + r) < p.M;
+            const float* src = okk ? Ab + (long long)(m0 + r) * p.lda + (k0 + k) : Ab;
+            const uint32_t dst = sa + (uint32_t)r * 128u + (uint32_t)((((k >> 2) ^ (r & 7)) << 4) + (k & 3) * 4);
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(okk ? 4 : 0) : "memory");
+          }
+        }
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar_full + 8 * s) : "memory");
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    float* epi_tile = epi_scratch + (warp - 2) * (32 * 33);
     int acc = 0; uint32_t aph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-      int batch, tm, tn;
-      tile_coords(p, tile, batch, tm, tn);
+      int batch, tm, tn, ks;
+      tile_coords(p, tile, batch, tm, tn, ks);
+      const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
       const bool masked = tile_is_masked<BN>(p, tm, tn);
       const int i0 = batch % p.batch0, i1 = batch / p.batch0;
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * BN;
-      const long long row_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1 + (long long)row * p.ldc;
+      const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1 + (long long)ks * p.ks_stride;
+      const long long row_off = batch_off + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
       if constexpr (X3) {
         // The accumulator arrives in K-chunks; they are summed here in fp32 registers
@@ -424,7 +522,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
         for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
         if (!masked) {
-          const int nchunks = (num_kb + X3_CHUNK_KB - 1) / X3_CHUNK_KB;
+          const int nchunks = (kb_hi - kb_lo + X3_CHUNK_KB - 1) / X3_CHUNK_KB;
           for (int ch = 0; ch < nchunks; ++ch) {
             if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
             tc_fence_after();
@@ -444,11 +542,12 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
           if (!ok) break;
         }
-        if (row_ok) {
 #pragma unroll
-          for (int c = 0; c < BN / 32; ++c) {
-            const int nb = n0 + c * 32;
-            if (nb < p.N) epilogue_chunk(p, &sum[c * 32], row, nb, row_off);
+        for (int c = 0; c < BN / 32; ++c) {
+          const int nb = n0 + c * 32;
+          if (nb < p.N) {
+            if (p.vec_ok) { if (row_ok) epilogue_chunk(p, &sum[c * 32], row, nb, row_off); }
+            else epilogue_chunk_coalesced(p, &sum[c * 32], epi_tile, lane, tm * BM + q * 32, nb, batch_off);
           }
         }
       } else {
@@ -468,7 +567,8 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.0f;
           }
-          if (row_ok) epilogue_chunk(p, v, row, nb, row_off);
+          if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off); }
+          else epilogue_chunk_coalesced(p, v, epi_tile, lane, tm * BM + q * 32, nb, batch_off);
         }
         if (!masked) {
           tc_fence_before();
@@ -484,6 +584,186 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+// ---- 256 x 256 tiles ------------------------------------------------------------------------------
+// For large tf32 problems.  A 128 x 256 tile needs 48 KB of operands per k-block, i.e. 96 bytes per
+// cycle per SM at full tensor rate, and an SM takes in only about 64-69 bytes per cycle from L2
+// (measured).  A 256 x 256 tile held by ONE CTA needs 64 KB per k-block for twice the flops = 64
+// bytes per cycle: two M=128 MMAs per k-step share the B tile and write two accumulators that
+// together fill tensor memory (2 x 256 columns).  Warps: 0 TMA producer, 1 MMA issuer, 2-5
+// epilogue of rows 0-127, 6-9 epilogue of rows 128-255.  Three 64 KB stages.  Tensor memory is
+// not double-buffered here, so a tile's epilogue does not overlap the next main loop (3 % at K = 8192);
+// the host picks this kernel only for long K and at least one full wave of tiles.
+constexpr int T256_STAGE_BYTES = 65536;
+constexpr int T256_STAGES = 3;
+constexpr int T256_THREADS = 320;
+constexpr int T256_SMEM_BYTES = T256_STAGES * T256_STAGE_BYTES + 1024 + 512 + 2 * EPI_SCRATCH_BYTES;
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(T256_THREADS, 1)
+gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaParams p) {
+  constexpr int STAGES = T256_STAGES;
+  constexpr int TM = 256, TN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint8_t* ctrl = smem_aligned + STAGES * T256_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * MAX_STAGES + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* epi_scratch = reinterpret_cast<float*>(ctrl + 512);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * MAX_STAGES;     // [half]
+  const uint32_t bar_tempty = bar_tfull + 16;                // [half]
+  const uint32_t bar_drain = bar_tempty + 16;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int h = 0; h < 2; ++h) { mbar_init(bar_tfull + 8 * h, 1); mbar_init(bar_tempty + 8 * h, 128); }
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (p.K + BK - 1) / BK;
+  constexpr uint32_t A_BYTES = TM * BK * 4;      // 32 KB
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int batch, tm, tn, ks;
+        tile_coords(p, tile, batch, tm, tn, ks);
+        const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+        const int m0 = tm * TM, n0 = tn * TN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+          const uint32_t full = bar_full + 8 * s;
+          mbar_expect_tx(full, T256_STAGE_BYTES);
+          const uint32_t sa = smem_base + s * T256_STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < TM / 32; ++j) tma_load_4d(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
+          } else {
+            tma_load_4d(sa, &map_a, full, k0, m0, i0, i1);                  // one 32 x 256 box
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < TN / 32; ++j) tma_load_4d(sb + j * 4096, &map_b, full, n0 + 32 * j, k0, i0, i1);
+          } else {
+            tma_load_4d(sb, &map_b, full, k0, n0, i0, i1);
+          }
+          ++issued;
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok) {
+        long long first = issued > STAGES ? issued - STAGES : 0;
+        for (long long i = first; i < issued; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar_full + 8 * (int)(i % STAGES), (uint32_t)((i / STAGES) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(TN, A_MN, B_MN);
+      int s = 0; uint32_t ph = 0, tph = 0;
+      bool ok = true, any_issued = false;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        // both accumulators must have been drained by the previous tile's epilogue
+        if (!mbar_wait(bar_tempty, tph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait(bar_tempty + 8, tph ^ 1u, abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * T256_STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint32_t a_off = A_MN ? kk * 1024 : kk * 32;
+            const uint32_t b_off = B_MN ? kk * 1024 : kk * 32;
+            const uint64_t bd = make_smem_desc(sb + b_off, B_MN ? 4096 : 16, B_MN ? 512 : 1024, B_MN ? 1 : 2);
+            const uint32_t keep = (kb | kk) != 0 ? 1u : 0u;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              // rows 128 h .. 128 h + 127 of the A tile: 16 KB further (K-major) or four 4 KB column blocks further (MN-major)
+              const uint64_t ad = make_smem_desc(sa + h * 16384 + a_off, A_MN ? 4096 : 16, A_MN ? 512 : 1024, A_MN ? 1 : 2);
+              tc_mma_tf32(tmem_base + (uint32_t)(h * TN), ad, bd, idesc, keep);
+            }
+          }
+          any_issued = true;
+          tc_commit(bar_empty + 8 * s);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(bar_tfull);
+        tc_commit(bar_tfull + 8);
+        tph ^= 1u;
+      }
+      if (!ok && any_issued) {
+        tc_commit(bar_drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * TN);
+    float* epi_tile = epi_scratch + (warp - 2) * (32 * 33);
+    uint32_t tph = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      int batch, tm, tn, ks;
+      tile_coords(p, tile, batch, tm, tn, ks);
+      const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+      const int row0 = tm * TM + half * 128 + q * 32;
+      const int row = row0 + lane;
+      const int n0 = tn * TN;
+      const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1;
+      const long long row_off = batch_off + (long long)row * p.ldc;
+      const bool row_ok = row < p.M;
+      if (!mbar_wait(bar_tfull + 8 * half, tph, abort_flag, p.status)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < TN / 32; ++c) {
+        const int nb = n0 + c * 32;
+        if (nb >= p.N) break;
+        float v[32];
+        tc_ld32(lane_base + (uint32_t)(c * 32), v);
+        tc_wait_ld();
+        if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off); }
+        else if (row0 < p.M) epilogue_chunk_coalesced(p, v, epi_tile, lane, row0, nb, batch_off);
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty + 8 * half);
+      tph ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
   }
 }
 
@@ -505,6 +785,30 @@ __global__ void gt_split_tf32_kernel(const float* __restrict__ x, float* __restr
     const float vh = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
     h[i] = vh;
     l[i] = v - vh;
+  }
+}
+
+// ---- split-K reduction --------------------------------------------------------------------------
+// C (+)= epilogue(alpha * sum_s partial[s] (+ bias)), partial planes packed (batch, M, N).  The sum
+// runs in plane order, so the result does not depend on which CTA finished first.
+__global__ void __launch_bounds__(256) gt_splitk_reduce_kernel(const float* __restrict__ ws, int ksplit, long long plane,
+                                                               float* C, const float* __restrict__ bias, float* aux,
+                                                               int M, int N, int batch0, long long ldc, long long sC0, long long sC1,
+                                                               float alpha, int epilogue, int accumulate, long long total) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int n = (int)(i % N);
+    const long long t = i / N;
+    const int m = (int)(t % M);
+    const int b = (int)(t / M);
+    float acc = 0.0f;
+    for (int s2 = 0; s2 < ksplit; ++s2) acc += ws[(long long)s2 * plane + i];
+    float x = alpha * acc;
+    if (epilogue >= GT_EPI_BIAS && epilogue <= GT_EPI_BIAS_GELU) x += bias[n];
+    const long long off = (long long)(b % batch0) * sC0 + (long long)(b / batch0) * sC1 + (long long)m * ldc + n;
+    if (aux) aux[off] = x;
+    if (epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
+    else if (epilogue == GT_EPI_BIAS_GELU) x = gt_gelu_tanh(x);
+    C[off] = accumulate ? C[off] + x : x;
   }
 }
 
@@ -537,36 +841,52 @@ int encode_map(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int box_cols
   return GT_OK;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool X3>
+template <int BN, bool A_MN, bool B_MN, bool X3, bool A_GEN>
 int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[4], const UmmaParams& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN, X3>;
-  auto kern = gt_gemm_umma_kernel<BN, A_MN, B_MN, X3>;
+  auto kern = gt_gemm_umma_kernel<BN, A_MN, B_MN, X3, A_GEN>;
   static bool attr_set = false;   // per instantiation; one caller thread per context
   if (!attr_set) {
     GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
-  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  kern<<<grid, A_GEN ? NUM_THREADS_AGEN : NUM_THREADS, C::SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return GT_OK;
 }
 
-template <int BN, bool X3>
+template <int BN, bool X3, bool A_GEN>
 int launch_layout(gt_ctx* ctx, int layout, const CUtensorMap maps[4], const UmmaParams& p, int grid, cudaStream_t stream) {
   switch (layout) {
-    case GT_LAYOUT_NN: return launch_cfg<BN, false, true, X3>(ctx, maps, p, grid, stream);
-    case GT_LAYOUT_NT: return launch_cfg<BN, false, false, X3>(ctx, maps, p, grid, stream);
-    case GT_LAYOUT_TN: return launch_cfg<BN, true, true, X3>(ctx, maps, p, grid, stream);
+    case GT_LAYOUT_NN: return launch_cfg<BN, false, true, X3, A_GEN>(ctx, maps, p, grid, stream);
+    case GT_LAYOUT_NT: return launch_cfg<BN, false, false, X3, A_GEN>(ctx, maps, p, grid, stream);
+    case GT_LAYOUT_TN: return launch_cfg<BN, true, true, X3, A_GEN>(ctx, maps, p, grid, stream);
   }
   return GT_ERR_INVALID_ARG;
 }
 
-int pick_bn(const gt_gemm_args& g, int sms, bool x3) {
+// Can TMA describe this operand?  16-byte aligned base, leading dimension and batch strides
+// multiples of four floats, strides below the 2^40-byte limit.
+bool tma_ok(const float* ptr, long long ld, long long s0, long long s1, long long batch0, long long batch1) {
+  if ((uintptr_t)ptr & 15) return false;
+  if (ld & 3) return false;
+  if (batch0 > 1 && (s0 & 3)) return false;
+  if (batch1 > 1 && (s1 & 3)) return false;
+  const long long lim = 1LL << 38;
+  return ld < lim && s0 < lim && s1 < lim;
+}
+
+int pick_bn(const gt_gemm_args& g, int sms, bool x3, bool a_gen) {
   if (g.N <= 64) return 64;
   if (g.N <= 128) return 128;
+  // An unaligned A is copied 4 bytes at a time; the widest tile gives those copies the most
+  // tensor-core time to hide behind.
+  if (a_gen && g.N >= 256) return 256;
   const long long batches = g.batch0 * g.batch1;
   const long long tm = (g.M + BM - 1) / BM;
+  // Few output tiles and a long K: take the widest tile, split-K fills the remaining SMs.
+  if (!x3 && g.epilogue != GT_EPI_CAUSAL && g.K >= 32 * BK && tm * ((g.N + 255) / 256) * batches * 2 <= sms) return 256;
   // Cost in "column units per SM": waves x tile width x a per-width efficiency penalty.
   double best = 1e30; int best_bn = 256;
   const int cands[3] = {256, 128, 64};
@@ -587,14 +907,10 @@ bool gt_gemm_umma_eligible(const gt_gemm_args& g) {
   if (g.precision == GT_PREC_FP32) return false;
   if (g.M > 0x7fffffffLL || g.N > 0x7fffffffLL || g.K > 0x7fffffffLL) return false;
   if (g.batch0 * g.batch1 > 0x7fffffffLL) return false;
-  if (((uintptr_t)g.A & 15) || ((uintptr_t)g.B & 15)) return false;
-  if ((g.lda & 3) || (g.ldb & 3)) return false;
-  if (g.batch0 > 1 && ((g.sA0 & 3) || (g.sB0 & 3))) return false;
-  if (g.batch1 > 1 && ((g.sA1 & 3) || (g.sB1 & 3))) return false;
-  // TMA strides are limited to 2^40 bytes.
-  const long long lim = 1LL << 38;
-  if (g.lda >= lim || g.ldb >= lim || g.sA0 >= lim || g.sA1 >= lim || g.sB0 >= lim || g.sB1 >= lim) return false;
-  return true;
+  // 3xTF32 reads packed, aligned hi/lo copies of both operands, so any alignment will do.
+  if (g.precision == GT_PREC_TF32X3) return g.batch0 * g.batch1 <= 65535;
+  // tf32: B must be describable by TMA; an unaligned A is copied by the cp.async warps instead.
+  return tma_ok(g.B, g.ldb, g.sB0, g.sB1, g.batch0, g.batch1);
 }
 
 // fixed_scratch: when non-null, the 3xTF32 operand split goes there (capacity
@@ -604,8 +920,14 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   const bool x3 = g.precision == GT_PREC_TF32X3;
   const bool a_mn = g.layout == GT_LAYOUT_TN;
   const bool b_mn = g.layout != GT_LAYOUT_NT;
-  const int bn = pick_bn(g, ctx->sm_count, x3);
+  const bool a_gen = !x3 && !tma_ok(g.A, g.lda, g.sA0, g.sA1, g.batch0, g.batch1);
   const long long nbatch = g.batch0 * g.batch1;
+  // Large tf32 problems (long K, at least one full wave of 256 x 256 tiles) take the big-tile kernel.
+  const long long tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256) * nbatch;
+  static const bool t256_off = getenv("GRADTUITY_GEMM_NO_T256") != nullptr;
+  const bool use256 = !t256_off && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && g.K >= 512 && tiles256 >= ctx->sm_count;
+  const int bn = use256 ? 256 : pick_bn(g, ctx->sm_count, x3, a_gen);
+  const int tile_m = use256 ? 256 : BM;
 
   OperandView va, vb;
   if (a_mn) va = {g.A, g.K, g.M, g.lda, g.sA0, g.sA1}; else va = {g.A, g.M, g.K, g.lda, g.sA0, g.sA1};
@@ -648,11 +970,12 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     vb_lo = vb; vb_lo.ptr = b_lo;
   }
 
-  const int a_box_c = 32, a_box_r = a_mn ? 32 : BM;
+  const int a_box_c = 32, a_box_r = a_mn ? 32 : tile_m;
   const int b_box_c = 32, b_box_r = b_mn ? 32 : bn;
   int rc;
-  if ((rc = encode_map(ctx, &maps[0], va, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
   if ((rc = encode_map(ctx, &maps[1], vb, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
+  if (a_gen) maps[0] = maps[1];               // unused by the kernel in this mode
+  else if ((rc = encode_map(ctx, &maps[0], va, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
   if (x3) {
     if ((rc = encode_map(ctx, &maps[2], va_lo, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
     if ((rc = encode_map(ctx, &maps[3], vb_lo, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
@@ -662,16 +985,32 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   }
 
   UmmaParams p;
+  p.A = g.A; p.lda = g.lda; p.sA0 = g.sA0; p.sA1 = g.sA1;
   p.C = g.C; p.bias = g.bias; p.aux = g.aux;
   p.ldc = g.ldc; p.sC0 = g.sC0; p.sC1 = g.sC1;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
   p.batch0 = (int)g.batch0;
-  p.tiles_m = (int)((g.M + BM - 1) / BM);
+  p.tiles_m = (int)((g.M + tile_m - 1) / tile_m);
   p.tiles_n = (int)((g.N + bn - 1) / bn);
   const long long tiles = (long long)p.tiles_m * p.tiles_n * nbatch;
   if (tiles > 0x7fffffffLL) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: %lld tiles out of range", tiles);
-  p.num_tiles = (int)tiles;
-  p.group_m = 16;
+  p.group_m = use256 ? 8 : 16;
+  // Split-K: when the output has far fewer tiles than the GPU has SMs and K is long (the dW
+  // GEMMs: 768 x 768 output, K = 8192 -> 18 tiles), several CTAs share a tile's K range; their
+  // partial sums go to the workspace and a second kernel adds them in a fixed order.
+  const int num_kb = (int)((g.K + BK - 1) / BK);
+  int ksplit = 1;
+  if (!x3 && g.epilogue != GT_EPI_CAUSAL && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
+    ksplit = (int)(ctx->sm_count / tiles);
+    if (ksplit > num_kb / 8) ksplit = num_kb / 8;
+    if (ksplit > 32) ksplit = 32;
+    if (ksplit < 1) ksplit = 1;
+  }
+  p.kb_per = (num_kb + ksplit - 1) / ksplit;
+  ksplit = (num_kb + p.kb_per - 1) / p.kb_per;
+  p.ksplit = ksplit;
+  p.ks_stride = 0;
+  p.num_tiles = (int)(tiles * ksplit);
   p.epilogue = g.epilogue; p.accumulate = g.accumulate;
   p.alpha = g.alpha;
   p.status = ctx->d_status;
@@ -679,15 +1018,57 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   if (g.aux) vec = vec && (((uintptr_t)g.aux & 15) == 0);
   if (g.bias) vec = vec && (((uintptr_t)g.bias & 15) == 0);
   p.vec_ok = vec ? 1 : 0;
-  const int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  const long long plane = nbatch * g.M * g.N;
+  float* ws = nullptr;
+  if (ksplit > 1) {
+    int rc2 = gt_workspace_reserve(ctx, (size_t)(8192 + plane * ksplit) * sizeof(float));
+    if (rc2 != GT_OK) return rc2;
+    ws = (float*)ctx->workspace + 8192;           // the first 8192 floats belong to the reductions
+    p.C = ws; p.bias = nullptr; p.aux = nullptr;
+    p.ldc = g.N; p.sC0 = g.M * g.N; p.sC1 = g.M * g.N * g.batch0;
+    p.ks_stride = plane;
+    p.epilogue = GT_EPI_NONE; p.accumulate = 0; p.alpha = 1.0f;
+    p.vec_ok = (g.N % 4 == 0) ? 1 : 0;
+  }
+  const int grid = (int)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);
 
+  if (use256) {
+    static bool attr_set[3] = {false, false, false};
+    auto launch256 = [&](auto kern, int idx) -> int {
+      if (!attr_set[idx]) {
+        GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T256_SMEM_BYTES));
+        attr_set[idx] = true;
+      }
+      kern<<<grid, T256_THREADS, T256_SMEM_BYTES, stream>>>(maps[0], maps[1], p);
+      GT_CUDA_OK(ctx, cudaGetLastError());
+      ctx->launches += 1;
+      return GT_OK;
+    };
+    switch (g.layout) {
+      case GT_LAYOUT_NN: return launch256(gt_gemm_umma256_kernel<false, true>, 0);
+      case GT_LAYOUT_NT: return launch256(gt_gemm_umma256_kernel<false, false>, 1);
+      default: return launch256(gt_gemm_umma256_kernel<true, true>, 2);
+    }
+  }
 #define GT_DISPATCH(BN_)                                                                         \
-  return x3 ? launch_layout<BN_, true>(ctx, g.layout, maps, p, grid, stream)                    \
-            : launch_layout<BN_, false>(ctx, g.layout, maps, p, grid, stream)
-  if (bn == 256 && !x3) return launch_layout<256, false>(ctx, g.layout, maps, p, grid, stream);
-  if (bn == 128) { GT_DISPATCH(128); }
-  GT_DISPATCH(64);
+  rc = x3 ? launch_layout<BN_, true, false>(ctx, g.layout, maps, p, grid, stream)               \
+          : (a_gen ? launch_layout<BN_, false, true>(ctx, g.layout, maps, p, grid, stream)      \
+                   : launch_layout<BN_, false, false>(ctx, g.layout, maps, p, grid, stream))
+  if (bn == 256 && !x3)
+    rc = a_gen ? launch_layout<256, false, true>(ctx, g.layout, maps, p, grid, stream)
+               : launch_layout<256, false, false>(ctx, g.layout, maps, p, grid, stream);
+  else if (bn == 128) { GT_DISPATCH(128); }
+  else { GT_DISPATCH(64); }
 #undef GT_DISPATCH
+  if (rc != GT_OK || ksplit == 1) return rc;
+  long long blocks = (plane + 255) / 256;
+  if (blocks > (long long)ctx->sm_count * 8) blocks = (long long)ctx->sm_count * 8;
+  gt_splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ws, ksplit, plane, g.C, g.bias, g.aux, (int)g.M, (int)g.N,
+                                                                (int)g.batch0, g.ldc, g.sC0, g.sC1, g.alpha, g.epilogue,
+                                                                g.accumulate, plane);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
 }
 
 int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream) {
@@ -733,8 +1114,6 @@ extern "C" int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_
   g.bias = bias; g.aux = nullptr; g.alpha = alpha;
   int rc = gt_gemm_validate(ctx, g);
   if (rc != GT_OK) return rc;
-  if (!gt_gemm_umma_eligible(g))
-    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gt_gemm_3xtf32_noalloc needs 16-byte aligned A and B with leading dimensions that are multiples of 4");
   if (ctx->device < 0 || ctx->device >= 64) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "device index %d out of range", ctx->device);
   // Refuse oversize problems before touching the device.
   const int64_t a_rows = layout == GT_LAYOUT_TN ? K : M, a_cols = layout == GT_LAYOUT_TN ? M : K;

@@ -92,6 +92,82 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(float* dx, const float
   for (int j = threadIdx.x; j < cols; j += blockDim.x) dxr[j] = j < limit ? scale * yr[j] * (dyr[j] - dot) : 0.0f;
 }
 
+// Vectorised forms for rows of up to 4096 floats whose length is a multiple of 4: the row is read
+// ONCE into registers (float4), reduced, and written once.  Under the causal mask the columns
+// beyond the diagonal are not read at all.
+constexpr int SM_VEC_ITERS = 4;          // 256 threads x 4 iterations x 4 floats = 4096 columns
+__global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(const float* x, float* y, int cols, int causal) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+  float4* yr = reinterpret_cast<float4*>(y + row * cols);
+  const int limit = causal ? (int)(row % cols) + 1 : cols;
+  float4 v[SM_VEC_ITERS];
+  float m = -INFINITY;
+#pragma unroll
+  for (int it = 0; it < SM_VEC_ITERS; ++it) {
+    const int j = (it * 256 + threadIdx.x) * 4;
+    if (j < limit) {
+      float4 t = xr[j >> 2];
+      if (j + 1 >= limit) t.y = -INFINITY;
+      if (j + 2 >= limit) t.z = -INFINITY;
+      if (j + 3 >= limit) t.w = -INFINITY;
+      v[it] = t;
+      m = fmaxf(m, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
+    } else {
+      v[it] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+  }
+  m = block_max_all(m, red);
+  float s = 0.0f;
+#pragma unroll
+  for (int it = 0; it < SM_VEC_ITERS; ++it) {
+    v[it].x = __expf(v[it].x - m); v[it].y = __expf(v[it].y - m); v[it].z = __expf(v[it].z - m); v[it].w = __expf(v[it].w - m);
+    s += (v[it].x + v[it].y) + (v[it].z + v[it].w);
+  }
+  s = block_sum_all(s, red);
+  const float inv = 1.0f / s;
+#pragma unroll
+  for (int it = 0; it < SM_VEC_ITERS; ++it) {
+    const int j = (it * 256 + threadIdx.x) * 4;
+    if (j < cols) yr[j >> 2] = make_float4(v[it].x * inv, v[it].y * inv, v[it].z * inv, v[it].w * inv);   // exp(-inf) = 0 beyond the limit
+  }
+}
+
+__global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(float* dx, const float* y, const float* dy, int cols, int causal, float scale) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const float4* yr = reinterpret_cast<const float4*>(y + row * cols);
+  const float4* dyr = reinterpret_cast<const float4*>(dy + row * cols);
+  float4* dxr = reinterpret_cast<float4*>(dx + row * cols);
+  const int limit = causal ? (int)(row % cols) + 1 : cols;
+  float4 yv[SM_VEC_ITERS], gv[SM_VEC_ITERS];
+  float dot = 0.0f;
+#pragma unroll
+  for (int it = 0; it < SM_VEC_ITERS; ++it) {
+    const int j = (it * 256 + threadIdx.x) * 4;
+    if (j < limit) {
+      float4 a = yr[j >> 2], g = dyr[j >> 2];
+      // beyond the diagonal y is 0 by construction, but dy may hold anything there
+      if (j + 1 >= limit) { a.y = 0.f; g.y = 0.f; }
+      if (j + 2 >= limit) { a.z = 0.f; g.z = 0.f; }
+      if (j + 3 >= limit) { a.w = 0.f; g.w = 0.f; }
+      yv[it] = a; gv[it] = g;
+      dot += (a.x * g.x + a.y * g.y) + (a.z * g.z + a.w * g.w);
+    } else {
+      yv[it] = make_float4(0.f, 0.f, 0.f, 0.f); gv[it] = yv[it];
+    }
+  }
+  dot = block_sum_all(dot, red);
+#pragma unroll
+  for (int it = 0; it < SM_VEC_ITERS; ++it) {
+    const int j = (it * 256 + threadIdx.x) * 4;
+    if (j < cols)
+      dxr[j >> 2] = make_float4(scale * yv[it].x * (gv[it].x - dot), scale * yv[it].y * (gv[it].y - dot),
+                                scale * yv[it].z * (gv[it].z - dot), scale * yv[it].w * (gv[it].w - dot));
+  }
+}
+
 // ---- LayerNorm ----------------------------------------------------------------------------------
 // y = (x - mean) * rstd * gamma + beta per row; mean and rstd are saved (two floats per row)
 // and x-hat is recomputed in the backward instead of being stored.
@@ -170,6 +246,68 @@ __global__ void __launch_bounds__(256) layernorm_bwd_kernel(float* __restrict__ 
       if (dgamma) atomicAdd(dgamma + j, pg[c]);
       if (dbeta) atomicAdd(dbeta + j, pb[c]);
     }
+  }
+}
+
+// Warp-per-row form for H = 128 * KV (KV <= 8), float4 access: no block-wide barrier per row; the
+// per-column partials of dgamma / dbeta stay in registers across the rows a warp visits and are
+// combined through shared memory once per block.
+template <int KV>
+__global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(float* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                                                 const float* __restrict__ dy, const float* __restrict__ x,
+                                                                 const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                                 const float* __restrict__ gamma, long long N, int dx_accumulate) {
+  constexpr int H = 128 * KV;
+  __shared__ float sg[H], sb[H];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int j = threadIdx.x; j < H; j += 256) { sg[j] = 0.0f; sb[j] = 0.0f; }
+  __syncthreads();
+  float4 gam[KV], pg[KV], pb[KV];
+#pragma unroll
+  for (int c = 0; c < KV; ++c) {
+    gam[c] = reinterpret_cast<const float4*>(gamma)[c * 32 + lane];
+    pg[c] = make_float4(0.f, 0.f, 0.f, 0.f); pb[c] = pg[c];
+  }
+  const long long warps_total = (long long)gridDim.x * 8;
+  for (long long row = (long long)blockIdx.x * 8 + warp; row < N; row += warps_total) {
+    const float mu = mean[row], rs = rstd[row];
+    const float4* xr = reinterpret_cast<const float4*>(x + row * H);
+    const float4* gr = reinterpret_cast<const float4*>(dy + row * H);
+    float4 xh[KV], dxh[KV];
+    float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+    for (int c = 0; c < KV; ++c) {
+      const float4 xv = xr[c * 32 + lane], g = gr[c * 32 + lane];
+      xh[c] = make_float4((xv.x - mu) * rs, (xv.y - mu) * rs, (xv.z - mu) * rs, (xv.w - mu) * rs);
+      dxh[c] = make_float4(g.x * gam[c].x, g.y * gam[c].y, g.z * gam[c].z, g.w * gam[c].w);
+      s1 += (dxh[c].x + dxh[c].y) + (dxh[c].z + dxh[c].w);
+      s2 += (dxh[c].x * xh[c].x + dxh[c].y * xh[c].y) + (dxh[c].z * xh[c].z + dxh[c].w * xh[c].w);
+      pg[c].x += g.x * xh[c].x; pg[c].y += g.y * xh[c].y; pg[c].z += g.z * xh[c].z; pg[c].w += g.w * xh[c].w;
+      pb[c].x += g.x; pb[c].y += g.y; pb[c].z += g.z; pb[c].w += g.w;
+    }
+    s1 = warp_sum(s1); s2 = warp_sum(s2);
+    if (dx) {
+      float4* dxr = reinterpret_cast<float4*>(dx + row * H);
+      const float k = rs / (float)H;
+#pragma unroll
+      for (int c = 0; c < KV; ++c) {
+        float4 v = make_float4(k * ((float)H * dxh[c].x - s1 - xh[c].x * s2), k * ((float)H * dxh[c].y - s1 - xh[c].y * s2),
+                               k * ((float)H * dxh[c].z - s1 - xh[c].z * s2), k * ((float)H * dxh[c].w - s1 - xh[c].w * s2));
+        if (dx_accumulate) { const float4 o = dxr[c * 32 + lane]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+        dxr[c * 32 + lane] = v;
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < KV; ++c) {
+    const int j = (c * 32 + lane) * 4;
+    atomicAdd(&sg[j], pg[c].x); atomicAdd(&sg[j + 1], pg[c].y); atomicAdd(&sg[j + 2], pg[c].z); atomicAdd(&sg[j + 3], pg[c].w);
+    atomicAdd(&sb[j], pb[c].x); atomicAdd(&sb[j + 1], pb[c].y); atomicAdd(&sb[j + 2], pb[c].z); atomicAdd(&sb[j + 3], pb[c].w);
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < H; j += 256) {
+    if (dgamma) atomicAdd(dgamma + j, sg[j]);
+    if (dbeta) atomicAdd(dbeta + j, sb[j]);
   }
 }
 
@@ -284,6 +422,44 @@ __global__ void __launch_bounds__(256) scale_by_device_scalar_kernel(float* __re
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= v;
 }
 
+// ---- multi-tensor forms -------------------------------------------------------------------------
+// One launch over a list of tensors instead of one launch per parameter (the reference launches
+// adamw_step once per tensor, gradtuity/optim/__init__.py:134-159, and clip_grad_norm_ runs a
+// multiply, a sum and a host read per tensor, gradtuity/optim/utils.py:38-45).  The list is a
+// device table of {p, g, m, v, n}; a second table maps each block to (tensor, first element).
+struct MtTensor { float* p; const float* g; float* m; float* v; long long n; };
+struct MtChunk { int tensor; int pad; long long start; };
+
+__global__ void __launch_bounds__(256) adamw_multi_kernel(const MtTensor* __restrict__ tensors, const MtChunk* __restrict__ chunks,
+                                                          long long chunk_elems, float lr, float beta1, float beta2, float eps,
+                                                          float wd, float bc1, float bc2, const float* __restrict__ grad_scale) {
+  const MtChunk c = chunks[blockIdx.x];
+  const MtTensor t = tensors[c.tensor];
+  const float gs = grad_scale ? *grad_scale : 1.0f;
+  long long end = c.start + chunk_elems; if (end > t.n) end = t.n;
+  for (long long i = c.start + threadIdx.x; i < end; i += blockDim.x) {
+    float pi = t.p[i];
+    const float gi = t.g[i] * gs;
+    const float mi = beta1 * t.m[i] + (1.0f - beta1) * gi;
+    const float vi = beta2 * t.v[i] + (1.0f - beta2) * gi * gi;
+    const float upd = (mi * bc1) / (sqrtf(vi * bc2) + eps);
+    pi = pi - lr * upd - lr * wd * pi;
+    t.m[i] = mi; t.v[i] = vi; t.p[i] = pi;
+  }
+}
+
+__global__ void __launch_bounds__(256) sumsq_multi_kernel(const MtTensor* __restrict__ tensors, const MtChunk* __restrict__ chunks,
+                                                          long long chunk_elems, float* __restrict__ partial) {
+  __shared__ float red[33];
+  const MtChunk c = chunks[blockIdx.x];
+  const MtTensor t = tensors[c.tensor];
+  long long end = c.start + chunk_elems; if (end > t.n) end = t.n;
+  float s = 0.0f;
+  for (long long i = c.start + threadIdx.x; i < end; i += blockDim.x) { const float v = t.g[i]; s += v * v; }
+  s = block_sum_all(s, red);
+  if (threadIdx.x == 0) partial[blockIdx.x] = s;
+}
+
 // ---- (B, d1, d2, D) -> (B, d2, d1, D) ------------------------------------------------------------
 __global__ void __launch_bounds__(256) transpose12_kernel(float* __restrict__ out, const float* __restrict__ in, int d1, int d2, int D, int accumulate) {
   // one block per (b, i1, i2) row of D elements
@@ -312,14 +488,18 @@ inline unsigned blocks_for(gt_ctx* ctx, long long n) {
 
 extern "C" int gt_softmax(gt_ctx* ctx, float* y, const float* x, int64_t rows, int64_t cols, int causal) {
   if (!ctx || !y || !x || rows <= 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return GT_ERR_INVALID_ARG;
-  softmax_fwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, y, rows, (int)cols, causal);
+  const bool vec = (cols % 4 == 0) && cols <= 256 * 4 * SM_VEC_ITERS && (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+  if (vec) softmax_fwd_vec_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, y, (int)cols, causal);
+  else softmax_fwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, y, rows, (int)cols, causal);
   GT_LAUNCH_CHECK(ctx, 1);
 }
 
 extern "C" int gt_softmax_backward(gt_ctx* ctx, float* dx, const float* y, const float* dy, int64_t rows, int64_t cols,
                                    int causal, float scale) {
   if (!ctx || !dx || !y || !dy || rows <= 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return GT_ERR_INVALID_ARG;
-  softmax_bwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(dx, y, dy, rows, (int)cols, causal, scale);
+  const bool vec = (cols % 4 == 0) && cols <= 256 * 4 * SM_VEC_ITERS && (((uintptr_t)dx | (uintptr_t)y | (uintptr_t)dy) & 15) == 0;
+  if (vec) softmax_bwd_vec_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(dx, y, dy, (int)cols, causal, scale);
+  else softmax_bwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(dx, y, dy, rows, (int)cols, causal, scale);
   GT_LAUNCH_CHECK(ctx, 1);
 }
 
@@ -335,6 +515,15 @@ extern "C" int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, floa
                                      int dx_accumulate) {
   if (!ctx || !dy || !x || !mean || !rstd || !gamma || N <= 0 || H <= 0 || N > 0x7fffffff) return GT_ERR_INVALID_ARG;
   if (H > 256 * LN_MAX_COLS_PER_THREAD) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "layernorm backward supports H <= %d, got %lld", 256 * LN_MAX_COLS_PER_THREAD, (long long)H);
+  const bool al = ((((uintptr_t)dx | (uintptr_t)dy | (uintptr_t)x | (uintptr_t)gamma) & 15) == 0);
+  if (al && H % 128 == 0 && H / 128 <= 8) {
+    long long wb = (N + 7) / 8, cap = (long long)ctx->sm_count * 4;
+    const unsigned nb = (unsigned)(wb < cap ? wb : cap);
+#define GT_LN_CASE(KV_) case KV_: layernorm_bwd_warp_kernel<KV_><<<nb, 256, 0, ctx->stream>>>(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, dx_accumulate); break
+    switch ((int)(H / 128)) { GT_LN_CASE(1); GT_LN_CASE(2); GT_LN_CASE(3); GT_LN_CASE(4); GT_LN_CASE(5); GT_LN_CASE(6); GT_LN_CASE(7); GT_LN_CASE(8); }
+#undef GT_LN_CASE
+    GT_LAUNCH_CHECK(ctx, 1);
+  }
   long long blocks = (long long)ctx->sm_count * 4;
   if (blocks > N) blocks = N;
   const int rpb = (int)((N + blocks - 1) / blocks);
@@ -411,4 +600,25 @@ extern "C" int gt_transpose12(gt_ctx* ctx, float* out, const float* in, int64_t 
   if (rows > 0x7fffffffLL || D > 0x7fffffff) return GT_ERR_INVALID_ARG;
   transpose12_kernel<<<(unsigned)rows, D >= 256 ? 256 : (D >= 128 ? 128 : 64), 0, ctx->stream>>>(out, in, (int)d1, (int)d2, (int)D, accumulate);
   GT_LAUNCH_CHECK(ctx, 1);
+}
+
+extern "C" int gt_adamw_multi(gt_ctx* ctx, const void* tensors, const void* chunks, int64_t n_chunks, int64_t chunk_elems,
+                              float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                              const float* grad_scale) {
+  if (!ctx || !tensors || !chunks || n_chunks <= 0 || n_chunks > 0x7fffffff || chunk_elems <= 0) return GT_ERR_INVALID_ARG;
+  adamw_multi_kernel<<<(unsigned)n_chunks, 256, 0, ctx->stream>>>((const MtTensor*)tensors, (const MtChunk*)chunks, chunk_elems, lr, beta1,
+                                                                  beta2, eps, weight_decay, bc1, bc2, grad_scale);
+  GT_LAUNCH_CHECK(ctx, 1);
+}
+
+// out[0] = sum over all listed gradients of g^2 (deterministic: per-chunk partials, then one block).
+extern "C" int gt_sumsq_multi(gt_ctx* ctx, float* out, const void* tensors, const void* chunks, int64_t n_chunks, int64_t chunk_elems) {
+  if (!ctx || !out || !tensors || !chunks || n_chunks <= 0 || chunk_elems <= 0) return GT_ERR_INVALID_ARG;
+  if (n_chunks > 4096) GT_FAIL(ctx, GT_ERR_TOO_LARGE, "gt_sumsq_multi: at most 4096 chunks, got %lld", (long long)n_chunks);
+  int rc = gt_workspace_reserve(ctx, 8192 * sizeof(float));
+  if (rc != GT_OK) return rc;
+  float* partial = (float*)ctx->workspace + 4096;
+  sumsq_multi_kernel<<<(unsigned)n_chunks, 256, 0, ctx->stream>>>((const MtTensor*)tensors, (const MtChunk*)chunks, chunk_elems, partial);
+  sum_partials_kernel<<<1, 256, 0, ctx->stream>>>(partial, out, (int)n_chunks, 0);
+  GT_LAUNCH_CHECK(ctx, 2);
 }

@@ -79,8 +79,11 @@ def _unique_id_file() -> str:
     return f"/tmp/gradtuity_nccl_{os.getpid()}_{int(time.time())}.bin"
 
 
-def exchange_unique_id(rank: int, make_id, uid_file: str, timeout: float = RENDEZVOUS_TIMEOUT_S) -> bytes:
-    """Rank 0 writes the id produced by make_id() to uid_file; the others poll for it."""
+def exchange_unique_id(rank: int, make_id, uid_file: str, timeout: float = RENDEZVOUS_TIMEOUT_S,
+                       not_before: float | None = None) -> bytes:
+    """Rank 0 writes the id produced by make_id() to uid_file; the others poll for it.
+    not_before: files last modified before this time (a leftover of an earlier job that used the
+    same path) are ignored."""
     if rank == 0:
         uid = make_id()
         if len(uid) != NCCL_UNIQUE_ID_BYTES:
@@ -93,7 +96,14 @@ def exchange_unique_id(rank: int, make_id, uid_file: str, timeout: float = RENDE
         os.replace(tmp, uid_file)
         return uid
     start = time.monotonic()
-    while not os.path.isfile(uid_file) or os.path.getsize(uid_file) != NCCL_UNIQUE_ID_BYTES:
+    def ready() -> bool:
+        try:
+            st = os.stat(uid_file)
+        except OSError:
+            return False
+        return st.st_size == NCCL_UNIQUE_ID_BYTES and (not_before is None or st.st_mtime >= not_before)
+
+    while not ready():
         if time.monotonic() - start > timeout:
             exists = os.path.isfile(uid_file)
             raise RuntimeError(
@@ -127,7 +137,9 @@ def init_process_group() -> None:
     if world == 1:
         return
     uid_file = _unique_id_file()
-    uid = exchange_unique_id(rank, _make_nccl_id, uid_file)
+    # Under the launcher the file name is unique to the job; otherwise guard against a leftover.
+    fresh = None if os.environ.get("GRADTUITY_LAUNCHER") == "1" else time.time() - 120.0
+    uid = exchange_unique_id(rank, _make_nccl_id, uid_file, not_before=fresh)
     _backend = NcclBackend(rank, world, uid)
     barrier()
     if rank == 0:

@@ -1,6 +1,8 @@
 """One-time broadcast of the initial parameters from one rank, with the strict signature check
 of gradtuity/dist/init_sync.py:38-104: (num_tensors, total_numel) travel first as 16 raw bytes
-and every rank compares them with its own before any parameter is overwritten."""
+and every rank compares them with its own before any parameter is overwritten.  Unlike the
+reference, the verdict is then shared (one all-reduced flag), so a mismatch raises on every rank
+instead of leaving the matching ranks blocked in the parameter broadcasts."""
 from __future__ import annotations
 
 import os
@@ -43,7 +45,13 @@ def init_sync(model_or_params, *, src: int = 0, sync_buffers: bool = True, bucke
         backend.broadcast(sig.ptr, 4, src)
         backend.wait(host_sync=True)
         root_tensors, root_numel = struct.unpack("qq", cuda_memcpy_dtoh(sig.ptr, 16))
-        if num_tensors != root_tensors or total_numel != root_numel:
+        mismatch = num_tensors != root_tensors or total_numel != root_numel
+        # Every rank learns whether ANY rank disagrees before a single parameter is sent, so that
+        # all of them stop here together and none is left waiting inside a collective.
+        flag = Tensor.from_numpy([1.0 if mismatch else 0.0])
+        backend.allreduce_async(flag.ptr, 1, average=False)
+        backend.wait(host_sync=True)
+        if flag.item() > 0:
             raise RuntimeError(
                 f"init_sync strict check failed: rank {rank} has num_tensors={num_tensors} total_numel={total_numel}, "
                 f"root has num_tensors={root_tensors} total_numel={root_numel}. Ensure same model architecture and "

@@ -18,6 +18,53 @@ def _call(name, *args):
     _lib.check(getattr(_lib.load_library(), name)(_lib.context(), *args), name)
 
 
+class _TensorTable:
+    """Device-side list {p, g, m, v, n} of a parameter set plus the block -> (tensor, offset) map
+    that the multi-tensor kernels read.  Rebuilt only when one of the pointers changes."""
+
+    CHUNK_MIN = 65536
+
+    def __init__(self) -> None:
+        self.key = None
+        self.tensors_ptr = 0
+        self.chunks_ptr = 0
+        self.n_chunks = 0
+        self.chunk_elems = 0
+
+    def update(self, entries: list[tuple[int, int, int, int, int]], max_chunks: int | None = None) -> None:
+        key = tuple(entries)
+        if key == self.key:
+            return
+        import numpy as np
+
+        from ..cuda_mem import cuda_free, cuda_malloc, cuda_memcpy_htod
+
+        total = sum(e[4] for e in entries)
+        chunk = self.CHUNK_MIN
+        if max_chunks is not None:
+            while sum((e[4] + chunk - 1) // chunk for e in entries) > max_chunks:
+                chunk *= 2
+        tens = np.zeros((len(entries), 5), dtype=np.int64)
+        for i, e in enumerate(entries):
+            tens[i] = e
+        rows = []
+        for i, e in enumerate(entries):
+            for start in range(0, e[4], chunk):
+                rows.append((i, start))
+        ch = np.zeros(len(rows), dtype=np.dtype([("tensor", "<i4"), ("pad", "<i4"), ("start", "<i8")]))
+        ch["tensor"] = [r[0] for r in rows]
+        ch["start"] = [r[1] for r in rows]
+        for old in (self.tensors_ptr, self.chunks_ptr):
+            if old:
+                cuda_free(old)
+        self.tensors_ptr = cuda_malloc(tens.nbytes)
+        self.chunks_ptr = cuda_malloc(ch.nbytes)
+        cuda_memcpy_htod(self.tensors_ptr, tens)
+        cuda_memcpy_htod(self.chunks_ptr, ch)
+        self.n_chunks, self.chunk_elems, self.key = len(rows), chunk, key
+        _ = total
+
+
 class Optimizer:
     def __init__(self, params: list[Tensor]) -> None:
         self.params = list(params)
@@ -57,6 +104,7 @@ class AdamW(Optimizer):
         self.m: list[Tensor | None] = [None] * n
         self.v: list[Tensor | None] = [None] * n
         self.step_count = 0
+        self._table = _TensorTable()
 
     def _validate_hyperparams(self) -> None:
         if self.lr <= 0:
@@ -79,6 +127,7 @@ class AdamW(Optimizer):
         bc1 = 1.0 / (1.0 - self.beta1 ** t)
         bc2 = 1.0 / (1.0 - self.beta2 ** t)
         gs = c_void_p(grad_scale.ptr) if grad_scale is not None else None
+        entries = []
         for i, p in enumerate(self.params):
             if p.grad is None:
                 continue
@@ -87,9 +136,17 @@ class AdamW(Optimizer):
             if self.m[i] is None:
                 self.m[i] = Tensor._zeros_like(p)
                 self.v[i] = Tensor._zeros_like(p)
-            _call("gt_adamw", c_void_p(p.ptr), c_void_p(p.grad.ptr), c_void_p(self.m[i].ptr), c_void_p(self.v[i].ptr),
-                  p.numel, float(self.lr), float(self.beta1), float(self.beta2), float(self.eps),
-                  float(self.weight_decay), float(bc1), float(bc2), gs)
+            entries.append((p.ptr, p.grad.ptr, self.m[i].ptr, self.v[i].ptr, p.numel))
+        if not entries:
+            return
+        # one launch for the whole list (the reference launches once per tensor)
+        self._table.update(entries)
+        _call("gt_adamw_multi", c_void_p(self._table.tensors_ptr), c_void_p(self._table.chunks_ptr), self._table.n_chunks,
+              self._table.chunk_elems, float(self.lr), float(self.beta1), float(self.beta2), float(self.eps),
+              float(self.weight_decay), float(bc1), float(bc2), gs)
+
+
+_clip_table = _TensorTable()
 
 
 def clip_grad_norm_(params, max_norm: float, eps: float = 1e-6, defer: bool = False):
@@ -99,13 +156,12 @@ def clip_grad_norm_(params, max_norm: float, eps: float = 1e-6, defer: bool = Fa
     defer=True skips the in-place scaling and the host read and returns `(norm_tensor,
     scale_tensor)` device tensors instead, for `AdamW.step(grad_scale=scale_tensor)`."""
     params = [p for p in params if p.grad is not None]
-    sumsq = empty_tensor((1,))
-    first = True
-    for p in params:
-        _call("gt_sumsq", c_void_p(sumsq.ptr), c_void_p(p.grad.ptr), p.grad.numel, 0 if first else 1)
-        first = False
-    if first:
+    if not params:
         return 0.0 if not defer else (None, None)
+    sumsq = empty_tensor((1,))
+    _clip_table.update([(0, p.grad.ptr, 0, 0, p.grad.numel) for p in params], max_chunks=4096)
+    _call("gt_sumsq_multi", c_void_p(sumsq.ptr), c_void_p(_clip_table.tensors_ptr), c_void_p(_clip_table.chunks_ptr),
+          _clip_table.n_chunks, _clip_table.chunk_elems)
     scale = empty_tensor((1,))
     norm = empty_tensor((1,))
     _call("gt_clip_scale", c_void_p(scale.ptr), c_void_p(norm.ptr), c_void_p(sumsq.ptr), float(max_norm), float(eps))

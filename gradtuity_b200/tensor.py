@@ -124,6 +124,28 @@ def accum_grad(t: "Tensor", g: "Tensor") -> None:
     _call("gt_scale", _vp(t.grad.ptr), _vp(g.ptr), 1.0, t.numel, 1)
 
 
+def pass_grad(t: "Tensor", g: "Tensor") -> None:
+    """t.grad (+)= g.  An interior node that has no gradient yet takes over g's buffer instead of
+    receiving a copy: g is the finished gradient of the node whose backward is running, nothing
+    reads it afterwards, and each backward hands its g to at most one parent this way.  Leaves
+    (parameters) always get their own buffer."""
+    if t.grad is None and t._backward is not None and g.numel == t.numel:
+        t.grad = Tensor._from_ptr(g.ptr, t.shape, owns_memory=False, base=g._st)
+    else:
+        accum_grad(t, g)
+
+
+def grad_target(t: "Tensor") -> tuple[int, bool]:
+    """Where a backward GEMM should put its contribution to t.grad: (pointer, accumulate).
+    A gradient that does not exist yet is allocated WITHOUT zero-filling and the GEMM writes it
+    (C = ...); an existing one is accumulated into (C += ...), which is the reference's contract
+    (gradtuity/tensor.py:152-155 zero-fills and always accumulates)."""
+    if t.grad is None:
+        t.grad = empty_tensor(t.shape, requires_grad=False)
+        return t.grad.ptr, False
+    return t.grad.ptr, True
+
+
 class Tensor:
     """A float32, contiguous, row-major tensor on the GPU with autograd support."""
 
@@ -339,7 +361,7 @@ class Tensor:
 
         def _backward(out_grad: "Tensor") -> None:
             if src.requires_grad:
-                accum_grad(src, out_grad)
+                pass_grad(src, out_grad)
 
         out._set_graph(parents=(self,), backward_fn=_backward)
         return out
@@ -366,11 +388,11 @@ class Tensor:
 
         def _backward(g: "Tensor") -> None:
             if a.requires_grad:
-                ensure_grad(a)
-                _gemm.gemm(LAYOUT_NT, M, K, N, g.ptr, N, b.ptr, N, a.grad.ptr, K, accumulate=True)
+                ptr, acc = grad_target(a)
+                _gemm.gemm(LAYOUT_NT, M, K, N, g.ptr, N, b.ptr, N, ptr, K, accumulate=acc)
             if b.requires_grad:
-                ensure_grad(b)
-                _gemm.gemm(LAYOUT_TN, K, N, M, a.ptr, K, g.ptr, N, b.grad.ptr, N, accumulate=True)
+                ptr, acc = grad_target(b)
+                _gemm.gemm(LAYOUT_TN, K, N, M, a.ptr, K, g.ptr, N, ptr, N, accumulate=acc)
 
         out._set_graph(parents=(self, other), backward_fn=_backward)
         return out
@@ -407,13 +429,13 @@ class Tensor:
 
         def _backward(g: "Tensor") -> None:
             if a.requires_grad:
-                ensure_grad(a)
+                ptr, acc = grad_target(a)
                 _gemm.gemm_batched(LAYOUT_NT, M, K, N, g.ptr, N, M * N, 0, b.ptr, N, K * N, 0,
-                                   a.grad.ptr, K, M * K, 0, Bf, accumulate=True)
+                                   ptr, K, M * K, 0, Bf, accumulate=acc)
             if b.requires_grad:
-                ensure_grad(b)
+                ptr, acc = grad_target(b)
                 _gemm.gemm_batched(LAYOUT_TN, K, N, M, a.ptr, K, M * K, 0, g.ptr, N, M * N, 0,
-                                   b.grad.ptr, N, K * N, 0, Bf, accumulate=True)
+                                   ptr, N, K * N, 0, Bf, accumulate=acc)
 
         out._set_graph(parents=(self, other), backward_fn=_backward)
         return out
@@ -433,11 +455,11 @@ class Tensor:
     def _linear_backward(self, x: "Tensor", weight: "Tensor", bias: "Tensor", dz_ptr: int, M: int, K: int, N: int) -> None:
         """dX += dZ·Wᵀ (NT), dW += Xᵀ·dZ (TN), db += column sums of dZ (gradtuity/tensor.py:1628-1679)."""
         if x.requires_grad:
-            ensure_grad(x)
-            _gemm.gemm(LAYOUT_NT, M, K, N, dz_ptr, N, weight.ptr, N, x.grad.ptr, K, accumulate=True)
+            ptr, acc = grad_target(x)
+            _gemm.gemm(LAYOUT_NT, M, K, N, dz_ptr, N, weight.ptr, N, ptr, K, accumulate=acc)
         if weight.requires_grad:
-            ensure_grad(weight)
-            _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dz_ptr, N, weight.grad.ptr, N, accumulate=True)
+            ptr, acc = grad_target(weight)
+            _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dz_ptr, N, ptr, N, accumulate=acc)
         if bias.requires_grad:
             ensure_grad(bias)
             _call("gt_colsum_acc", _vp(bias.grad.ptr), _vp(dz_ptr), M, N, N)
@@ -517,11 +539,11 @@ class Tensor:
 
         def _backward(g: "Tensor") -> None:
             if x.requires_grad:
-                ensure_grad(x)
-                _gemm.gemm(LAYOUT_NN, M, E, V, g.ptr, V, weight.ptr, E, x.grad.ptr, E, accumulate=True)
+                ptr, acc = grad_target(x)
+                _gemm.gemm(LAYOUT_NN, M, E, V, g.ptr, V, weight.ptr, E, ptr, E, accumulate=acc)
             if weight.requires_grad:
-                ensure_grad(weight)
-                _gemm.gemm(LAYOUT_TN, V, E, M, g.ptr, V, x.ptr, E, weight.grad.ptr, E, accumulate=True)
+                ptr, acc = grad_target(weight)
+                _gemm.gemm(LAYOUT_TN, V, E, M, g.ptr, V, x.ptr, E, ptr, E, accumulate=acc)
 
         out._set_graph(parents=(self, weight), backward_fn=_backward)
         return out
@@ -563,10 +585,10 @@ class Tensor:
         def _backward(g: "Tensor") -> None:
             need_qk = q.requires_grad or k.requires_grad
             if v.requires_grad:
-                ensure_grad(v)
+                ptr, acc = grad_target(v)
                 # dV[b, :, h, :] += P[b, h]^T dO[b, :, h, :]   (TN)
                 _gemm.gemm_batched(LAYOUT_TN, S, D, S, p.ptr, S, S * S, H * S * S, g.ptr, E, D, S * E,
-                                   v.grad.ptr, E, D, S * E, H, B, accumulate=True)
+                                   ptr, E, D, S * E, H, B, accumulate=acc)
             if need_qk:
                 with temp_storage(B * H * S * S * F32) as st:
                     # dP[b, h] = dO[b, :, h, :] V[b, :, h, :]^T   (NT); only the lower triangle is needed
@@ -575,15 +597,15 @@ class Tensor:
                     # dS = scale * P * (dP - sum P dP), zero above the diagonal, in place
                     _call("gt_softmax_backward", _vp(st.ptr), _vp(p.ptr), _vp(st.ptr), B * H * S, S, 1, scale)
                     if q.requires_grad:
-                        ensure_grad(q)
+                        ptr, acc = grad_target(q)
                         # dQ[b, :, h, :] += dS[b, h] K[b, :, h, :]   (NN)
                         _gemm.gemm_batched(LAYOUT_NN, S, D, S, st.ptr, S, S * S, H * S * S, k.ptr, E, D, S * E,
-                                           q.grad.ptr, E, D, S * E, H, B, accumulate=True)
+                                           ptr, E, D, S * E, H, B, accumulate=acc)
                     if k.requires_grad:
-                        ensure_grad(k)
+                        ptr, acc = grad_target(k)
                         # dK[b, :, h, :] += dS[b, h]^T Q[b, :, h, :]   (TN)
                         _gemm.gemm_batched(LAYOUT_TN, S, D, S, st.ptr, S, S * S, H * S * S, q.ptr, E, D, S * E,
-                                           k.grad.ptr, E, D, S * E, H, B, accumulate=True)
+                                           ptr, E, D, S * E, H, B, accumulate=acc)
 
         out._set_graph(parents=(q, k, v), backward_fn=_backward)
         return out
@@ -649,10 +671,9 @@ class Tensor:
         x = self
 
         def _backward(g: "Tensor") -> None:
-            dx_ptr = 0
+            dx_ptr, dx_acc = 0, True
             if x.requires_grad:
-                ensure_grad(x)
-                dx_ptr = x.grad.ptr
+                dx_ptr, dx_acc = grad_target(x)
             dg_ptr = db_ptr = 0
             if gamma.requires_grad:
                 ensure_grad(gamma)
@@ -661,7 +682,7 @@ class Tensor:
                 ensure_grad(beta)
                 db_ptr = beta.grad.ptr
             _call("gt_layernorm_backward", _vp(dx_ptr), _vp(dg_ptr), _vp(db_ptr), _vp(g.ptr), _vp(x.ptr), _vp(mean.ptr),
-                  _vp(rstd.ptr), _vp(gamma.ptr), Nr, Hd, 1)
+                  _vp(rstd.ptr), _vp(gamma.ptr), Nr, Hd, 1 if dx_acc else 0)
 
         out._set_graph(parents=(self, gamma, beta), backward_fn=_backward)
         return out
@@ -788,9 +809,9 @@ class Tensor:
 
         def _backward(g: "Tensor") -> None:
             if a.requires_grad:
-                accum_grad(a, g)
+                pass_grad(a, g)          # may take over g's buffer
             if b.requires_grad:
-                accum_grad(b, g)
+                accum_grad(b, g)         # always a copy / accumulate
 
         out._set_graph(parents=(self, other), backward_fn=_backward)
         return out

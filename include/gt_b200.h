@@ -147,8 +147,7 @@ int gt_gemm_batched(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
  *   - limit: 2 * (rows(A) * cols4(A) + rows(B) * cols4(B)) <= 8 Mi floats, cols4 = columns
  *     rounded up to a multiple of 4 (for example M = N = K = 1024, or 2048 x 1024 x 512);
  *     larger problems return GT_ERR_TOO_LARGE and launch nothing;
- *   - A and B must be 16-byte aligned with leading dimensions that are multiples of 4
- *     (else GT_ERR_UNSUPPORTED);
+ *   - any operand alignment and leading dimension is accepted (the split packs both operands);
  *   - the first call on each device looks up the array's device address; make that call
  *     before starting any stream capture;
  *   - all calls share the array: calls whose kernels may overlap on the GPU race on it.    */
@@ -228,6 +227,14 @@ int gt_sumsq(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate)
 int gt_clip_scale(gt_ctx* ctx, float* scale_out, float* norm_out, const float* sumsq, float max_norm, float eps);
 int gt_scale_by_device_scalar(gt_ctx* ctx, float* x, const float* s, int64_t n);
 int gt_transpose12(gt_ctx* ctx, float* out, const float* in, int64_t B, int64_t d1, int64_t d2, int64_t D, int accumulate);
+/* Multi-tensor forms: one launch for a whole parameter list.  `tensors` is a device array of
+ * {float* p; const float* g; float* m; float* v; int64 n} (40 bytes each), `chunks` a device array of
+ * {int32 tensor; int32 pad; int64 first_element} (16 bytes each) that assigns `chunk_elems` elements to
+ * each block.  Same arithmetic as gt_adamw / gt_sumsq (gt_sumsq_multi: at most 4096 chunks).       */
+int gt_adamw_multi(gt_ctx* ctx, const void* tensors, const void* chunks, int64_t n_chunks, int64_t chunk_elems,
+                   float lr, float beta1, float beta2, float eps, float weight_decay, float bc1, float bc2,
+                   const float* grad_scale);
+int gt_sumsq_multi(gt_ctx* ctx, float* out, const void* tensors, const void* chunks, int64_t n_chunks, int64_t chunk_elems);
 
 /* ---- data-parallel gradient exchange (single node, NCCL over NVLink / NVSwitch) ----------
  * Replaces the reference's libnccl binding and the calls built on it:

@@ -116,6 +116,64 @@ def test_padded_leading_dimensions(gt, layout, precision):
     assert O.rel_frobenius(out, O.gemm(a, b, layout)) <= U.TOL[precision]
 
 
+@pytest.mark.parametrize("precision", ["tf32", "3xtf32"])
+def test_odd_pitch_lm_head_shapes(gt, precision):
+    """The tied LM head with an odd vocabulary: logits / dlogits rows are not 16-byte aligned.
+    Forward (NT) stores C through the coalesced epilogue; the backward GEMMs read dlogits as an
+    unaligned K-major A (NN) and an unaligned MN-major A (TN), copied by the cp.async warps."""
+    rng = np.random.default_rng(12)
+    M, V, E = 300, 1001, 96
+    x = (rng.standard_normal((M, E)) / np.sqrt(E)).astype(np.float32)
+    w = (rng.standard_normal((V, E)) / np.sqrt(E)).astype(np.float32)
+    dl = (rng.standard_normal((M, V)) / np.sqrt(V)).astype(np.float32)
+    logits, path = U.run_gemm("NT", x, w, precision=precision, return_path=True)
+    assert path == 0 and O.rel_frobenius(logits, O.gemm(x, w, "NT")) <= U.TOL[precision]
+    dx0 = rng.standard_normal((M, E)).astype(np.float32)
+    dx, path = U.run_gemm("NN", dl, w, c0=dx0, precision=precision, return_path=True)          # dX += dL W
+    assert path == 0 and O.rel_frobenius(dx - dx0, O.gemm(dl, w, "NN")) <= U.TOL[precision]
+    dw, path = U.run_gemm("TN", dl, x, precision=precision, return_path=True)                   # dW = dL^T X
+    assert path == 0 and O.rel_frobenius(dw, O.gemm(dl, x, "TN")) <= U.TOL[precision]
+    # odd pitch plus epilogues on the coalesced path
+    bias = rng.standard_normal(V).astype(np.float32)
+    for epi in ("bias_gelu", "causal"):
+        out = U.run_gemm("NT", x, w, bias=bias if epi != "causal" else None, epilogue=epi, precision=precision)
+        ref = O.gemm(x, w, "NT", bias=bias, epilogue=epi)
+        keep = np.ones_like(ref, bool) if epi != "causal" else np.tril(np.ones(ref.shape, bool))
+        assert O.rel_frobenius(out[keep], ref[keep]) <= U.TOL[precision]
+        if epi == "causal":
+            assert np.all(out[~keep] == np.float32(O.CAUSAL_MASK_VALUE))
+
+
+def test_unaligned_a_with_misaligned_base(gt):
+    a, b, _ = U.make_operands("NN", 200, 128, 77, seed=6)          # lda = 77
+    from gradtuity_b200 import _lib, gemm as G
+    da = U.DeviceBuffer(a, offset_elems=3)                          # base 12 bytes off alignment
+    db = U.DeviceBuffer(b)
+    dc = U.DeviceBuffer(nbytes=200 * 128 * 4)
+    G.gemm(0, 200, 128, 77, da.ptr, 77, db.ptr, 128, dc.ptr, 128)
+    _lib.device_status()
+    assert O.rel_frobenius(dc.read((200, 128)), O.gemm(a, b, "NN")) <= U.TOL["tf32"]
+
+
+@pytest.mark.parametrize("layout,M,N,K,epilogue,acc", [
+    ("TN", 768, 768, 8192, "none", True),        # the dW GEMM of a 768-wide Linear at 8192 tokens
+    ("TN", 768, 3072, 4096, "none", True),
+    ("NN", 256, 264, 4100, "bias_relu", False),  # K tail, N tail
+    ("NT", 130, 500, 2048, "bias_gelu", False),
+])
+def test_split_k_shapes(gt, layout, M, N, K, epilogue, acc):
+    """Few output tiles and a long K: the K range is shared between CTAs and the partial sums are
+    added by a second kernel in a fixed order (deterministic, epilogue applied once)."""
+    a, b, rng = U.make_operands(layout, M, N, K, seed=K + N)
+    bias = rng.standard_normal(N).astype(np.float32) if epilogue != "none" else None
+    c0 = rng.standard_normal((M, N)).astype(np.float32) if acc else None
+    out = U.run_gemm(layout, a, b, bias=bias, c0=c0, epilogue=epilogue)
+    ref = O.gemm(a, b, layout, bias=bias, epilogue=epilogue, c0=c0)
+    base = c0 if acc else 0.0
+    assert O.rel_frobenius(out - base, ref - base) <= U.TOL["tf32"]
+    assert np.array_equal(out, U.run_gemm(layout, a, b, bias=bias, c0=c0, epilogue=epilogue))
+
+
 def test_bitwise_deterministic(gt):
     a, b, _ = U.make_operands("TN", 384, 512, 1024, seed=3)
     assert np.array_equal(U.run_gemm("TN", a, b), U.run_gemm("TN", a, b))
@@ -229,6 +287,37 @@ def test_full_size_sampled_rows_and_linearity(gt, precision, M, N, K):
     assert O.rel_frobenius(c1[rows], ref) <= U.TOL[precision]
     # two roundings of B versus one: the bound is twice the single-GEMM bar
     assert O.rel_frobenius(c_sum, c12) <= 2 * U.TOL[precision]
+
+
+@pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
+@pytest.mark.parametrize("M,N,K,epilogue,acc", [(4096, 4096, 520, "none", False), (4000, 4104, 768, "bias_gelu", False),
+                                                (3968, 4360, 1024, "none", True)])
+def test_big_tile_kernel(gt, layout, M, N, K, epilogue, acc):
+    """Problems with at least one wave of 256 x 256 tiles and K >= 512 run on the big-tile kernel:
+    ragged M / N / K, every layout, fused epilogue with stored pre-activation, accumulate."""
+    from gradtuity_b200 import _lib, gemm as G
+
+    a, b, rng = U.make_operands(layout, M, N, K, seed=M + K)
+    bias = rng.standard_normal(N).astype(np.float32) if epilogue != "none" else None
+    c0 = rng.standard_normal((M, N)).astype(np.float32) if acc else None
+    da, db = U.DeviceBuffer(a), U.DeviceBuffer(b)
+    dc = U.DeviceBuffer(c0 if acc else np.full((M, N), np.nan, np.float32))
+    dbias = U.DeviceBuffer(bias) if bias is not None else None
+    daux = U.DeviceBuffer(np.full((M, N), np.nan, np.float32)) if epilogue == "bias_gelu" else None
+    G.gemm(U.LAYOUTS[layout], M, N, K, da.ptr, a.shape[1], db.ptr, b.shape[1], dc.ptr, N,
+           bias_ptr=dbias.ptr if dbias else 0, aux_ptr=daux.ptr if daux else 0, accumulate=acc,
+           epilogue=U.EPILOGUES[epilogue])
+    _lib.device_status()
+    out = dc.read((M, N))
+    assert not np.isnan(out).any()
+    rows = np.unique(np.concatenate([np.arange(0, M, 97), [M - 1, 127, 128, 255, 256]]))
+    a_rows = a[:, rows].T if layout == "TN" else a[rows]
+    ref, pre = O.gemm(a_rows, b, "NT" if layout == "NT" else "NN", bias=bias, epilogue=epilogue,
+                      c0=c0[rows] if acc else None, return_pre=True)
+    base = c0[rows] if acc else 0.0
+    assert O.rel_frobenius(out[rows] - base, ref - base) <= U.TOL["tf32"]
+    if daux is not None:
+        assert O.rel_frobenius(daux.read((M, N))[rows], pre) <= U.TOL["tf32"]
 
 
 def test_3xtf32_error_does_not_grow_with_k(gt):
