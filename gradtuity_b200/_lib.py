@@ -24,6 +24,7 @@ LAYOUT_NN, LAYOUT_NT, LAYOUT_TN = 0, 1, 2
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_CAUSAL = 0, 1, 2, 3, 4
 PREC_TF32, PREC_TF32X3, PREC_FP32 = 0, 1, 2
 CAUSAL_MASK_VALUE = -1.0e9
+GEMM_A_LOWER, GEMM_AT_LOWER, GEMM_CAUSAL_SKIP_MASKED = 1, 2, 4
 
 GT_OK = 0
 GT_ERR_INVALID_ARG = -1
@@ -70,6 +71,12 @@ SIGNATURES = {
                                 c_void_p, c_int64, c_int64, c_int64,
                                 c_int64, c_int64,
                                 c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p]),
+    "gt_gemm_batched_ex": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
+                                   c_void_p, c_int64, c_int64, c_int64,
+                                   c_void_p, c_int64, c_int64, c_int64,
+                                   c_void_p, c_int64, c_int64, c_int64,
+                                   c_int64, c_int64,
+                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_void_p]),
     "gt_gemm_3xtf32_noalloc": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
                                        c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                        c_void_p, c_float, c_int, c_int, c_void_p]),

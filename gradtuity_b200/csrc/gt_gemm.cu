@@ -47,7 +47,7 @@ extern "C" int gt_gemm(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
                        float* C, int64_t ldc, const float* bias, float* aux,
                        float alpha, int accumulate, int epilogue, int precision, void* stream) {
   gt_gemm_args g;
-  g.layout = layout; g.epilogue = epilogue; g.precision = precision; g.accumulate = accumulate;
+  g.layout = layout; g.epilogue = epilogue; g.precision = precision; g.accumulate = accumulate; g.flags = 0;
   g.M = M; g.N = N; g.K = K;
   g.A = A; g.lda = lda; g.sA0 = 0; g.sA1 = 0;
   g.B = B; g.ldb = ldb; g.sB0 = 0; g.sB1 = 0;
@@ -64,8 +64,27 @@ extern "C" int gt_gemm_batched(gt_ctx* ctx, int layout, int64_t M, int64_t N, in
                                int64_t batch0, int64_t batch1,
                                const float* bias, float* aux, float alpha, int accumulate,
                                int epilogue, int precision, void* stream) {
+  return gt_gemm_batched_ex(ctx, layout, M, N, K, A, lda, strideA0, strideA1, B, ldb, strideB0, strideB1, C, ldc, strideC0,
+                            strideC1, batch0, batch1, bias, aux, alpha, accumulate, epilogue, precision, 0, stream);
+}
+
+extern "C" int gt_gemm_batched_ex(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                                  const float* A, int64_t lda, int64_t strideA0, int64_t strideA1,
+                                  const float* B, int64_t ldb, int64_t strideB0, int64_t strideB1,
+                                  float* C, int64_t ldc, int64_t strideC0, int64_t strideC1,
+                                  int64_t batch0, int64_t batch1,
+                                  const float* bias, float* aux, float alpha, int accumulate,
+                                  int epilogue, int precision, int flags, void* stream) {
+  if (ctx) {
+    if (flags & ~(GT_GEMM_A_LOWER | GT_GEMM_AT_LOWER | GT_GEMM_CAUSAL_SKIP_MASKED)) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: unknown flags 0x%x", flags);
+    if ((flags & (GT_GEMM_A_LOWER | GT_GEMM_AT_LOWER)) && M != K) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: triangular-A flags need a square A (M == K)");
+    if ((flags & GT_GEMM_A_LOWER) && (flags & GT_GEMM_AT_LOWER)) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: A_LOWER and AT_LOWER exclude each other");
+    if ((flags & GT_GEMM_A_LOWER) && layout == GT_LAYOUT_TN) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: A_LOWER describes an A stored (M, K)");
+    if ((flags & GT_GEMM_AT_LOWER) && layout != GT_LAYOUT_TN) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: AT_LOWER describes an A stored (K, M)");
+    if ((flags & GT_GEMM_CAUSAL_SKIP_MASKED) && epilogue != GT_EPI_CAUSAL) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: SKIP_MASKED needs the causal epilogue");
+  }
   gt_gemm_args g;
-  g.layout = layout; g.epilogue = epilogue; g.precision = precision; g.accumulate = accumulate;
+  g.layout = layout; g.epilogue = epilogue; g.precision = precision; g.accumulate = accumulate; g.flags = flags;
   g.M = M; g.N = N; g.K = K;
   g.A = A; g.lda = lda; g.sA0 = strideA0; g.sA1 = strideA1;
   g.B = B; g.ldb = ldb; g.sB0 = strideB0; g.sB1 = strideB1;

@@ -38,7 +38,8 @@ constexpr int BK = 32;                       // fp32 elements per k-block = 128 
 constexpr int UMMA_K = 8;                    // tf32 elements per tcgen05.mma
 constexpr int NUM_THREADS = 192;            // producer warp, MMA warp, 4 epilogue warps
 constexpr int NUM_THREADS_AGEN = 320;       // + 4 warps that copy an unaligned A operand with cp.async
-constexpr int EPI_SCRATCH_BYTES = 4 * 32 * 33 * 4;   // per-warp 32 x 33 staging tile of the coalesced epilogue
+constexpr int EPI_WARP_BYTES = 8192;                 // per epilogue warp: two 32 x 32 fp32 staging tiles for TMA stores
+constexpr int EPI_SCRATCH_BYTES = 4 * EPI_WARP_BYTES;  // (the coalesced fallback uses 32 x 33 floats of the same space)
 constexpr int MAX_STAGES = 8;
 constexpr int X3_CHUNK_KB = 8;                // 3xTF32: k-blocks accumulated in tensor memory before an fp32 register add
 constexpr int SMEM_BUDGET = 232448 - 1024 - 512 - EPI_SCRATCH_BYTES;   // 227 KB minus alignment slack, barriers, epilogue staging
@@ -55,6 +56,8 @@ struct UmmaParams {
   long long ks_stride;                   // split-K: element offset between the partial-sum planes of C
   int group_m;
   int epilogue, accumulate, vec_ok;
+  int flags;                             // GT_GEMM_* flags of gt_gemm_batched_ex
+  int c_tma;                             // C is written by TMA store / reduce-add through shared memory
   float alpha;
   int* status;
 };
@@ -135,6 +138,22 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
       : "r"(taddr)
       : "memory");
 }
+// C tile (32 columns x 32 rows, 128-byte swizzled in shared memory) -> global, clipped at the
+// tensor's edges by the TMA unit; `add` turns the store into an element-wise fp32 add (C += tile).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3, bool add) {
+  if (add) {
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"((uint64_t)map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  } else {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"((uint64_t)map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  }
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets
@@ -189,13 +208,26 @@ __device__ __forceinline__ void tile_coords(const UmmaParams& p, int unit, int& 
   tn = r / rows;
 }
 
+// k-blocks a work unit contracts over: its split-K share, narrowed when the caller has declared
+// A triangular (attention: P and dS are zero above the diagonal, so the products that read them
+// as A need only the k-blocks up to the tile's last row, and those that read them transposed
+// only the k-blocks from the tile's first row on).
+__device__ __forceinline__ void k_range(const UmmaParams& p, int tm, int ks, int num_kb, int& lo, int& hi) {
+  lo = ks * p.kb_per;
+  hi = min(num_kb, lo + p.kb_per);
+  if (p.flags & GT_GEMM_A_LOWER) hi = min(hi, ((tm + 1) * BM + BK - 1) / BK);
+  if (p.flags & GT_GEMM_AT_LOWER) lo = max(lo, (tm * BM) / BK);
+}
+
 template <int BN>
 __device__ __forceinline__ bool tile_is_masked(const UmmaParams& p, int tm, int tn) {
   return p.epilogue == GT_EPI_CAUSAL && (tn * BN > tm * BM + BM - 1);
 }
 
 // Fused epilogue for 32 consecutive columns of one output row: v holds the accumulator.
-__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float* v, int row, int nb, long long row_off) {
+// cpre: the 32 values of C this chunk accumulates into, loaded ahead of time (or null).
+__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float* v, int row, int nb, long long row_off,
+                                               const float4* cpre = nullptr) {
   const bool full_chunk = (nb + 32 <= p.N);
   float* cptr = p.C + row_off + nb;
   const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
@@ -221,7 +253,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float*
       }
       float4* dst = reinterpret_cast<float4*>(cptr + j);
       if (p.accumulate) {
-        const float4 o = *dst;
+        const float4 o = cpre ? cpre[j >> 2] : *dst;
         x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
       }
       *dst = x;
@@ -242,6 +274,69 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float*
       }
     }
   }
+}
+
+// Loads the 32 floats of C that chunk `nb` of this thread's row will accumulate into.  Issued one
+// chunk ahead (the first one before the accumulator is even ready), so the read latency of
+// `C += ...` hides behind the main loop and the previous chunk instead of stalling every chunk.
+__device__ __forceinline__ bool prefetch_c(const UmmaParams& p, bool enabled, int nb, long long row_off, float4* out) {
+  if (!enabled || nb + 32 > p.N) return false;
+  const float4* src = reinterpret_cast<const float4*>(p.C + row_off + nb);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) out[j] = src[j];
+  return true;
+}
+
+// Epilogue of one 32 x 32 block through shared memory and a TMA store.  Each lane owns one row:
+// it applies the fused epilogue in registers, writes its 128-byte row into the staging tile in the
+// 128-byte-swizzle order, and lane 0 hands the tile to the TMA unit, which writes whole rows,
+// clips at M and N, and for `C += ...` performs the addition in L2 (no read of C by the SM).
+// `stage` alternates between the warp's two tiles so that a store may still be reading the
+// previous one; with an aux output the pre-activation is stored directly from registers.
+__device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
+                                                   int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
+                                                   uint8_t* tile, uint32_t tile_u32) {
+  const int row = row0 + lane;
+  const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
+  if (lane == 0) tma_store_wait_read<1>();          // the store issued two chunks ago has read this tile
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    float4 x = make_float4(p.alpha * v[j], p.alpha * v[j + 1], p.alpha * v[j + 2], p.alpha * v[j + 3]);
+    if (has_bias) {
+      const int col = nb + j;                       // bias may end inside this chunk
+      if (col + 3 < p.N) {
+        const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
+        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+      } else {
+        if (col < p.N) x.x += p.bias[col];
+        if (col + 1 < p.N) x.y += p.bias[col + 1];
+        if (col + 2 < p.N) x.z += p.bias[col + 2];
+      }
+    }
+    if (p.aux && row_ok && nb + j + 3 < p.N) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
+    else if (p.aux && row_ok) {
+      float* a = p.aux + row_off + nb + j;
+      if (nb + j < p.N) a[0] = x.x;
+      if (nb + j + 1 < p.N) a[1] = x.y;
+      if (nb + j + 2 < p.N) a[2] = x.z;
+    }
+    if (p.epilogue == GT_EPI_BIAS_RELU) {
+      x.x = fmaxf(x.x, 0.0f); x.y = fmaxf(x.y, 0.0f); x.z = fmaxf(x.z, 0.0f); x.w = fmaxf(x.w, 0.0f);
+    } else if (p.epilogue == GT_EPI_BIAS_GELU) {
+      x.x = gt_gelu_tanh(x.x); x.y = gt_gelu_tanh(x.y); x.z = gt_gelu_tanh(x.z); x.w = gt_gelu_tanh(x.w);
+    } else if (p.epilogue == GT_EPI_CAUSAL) {
+      const int col = nb + j;
+      if (col > row) x.x = GT_CAUSAL_MASK_VALUE;
+      if (col + 1 > row) x.y = GT_CAUSAL_MASK_VALUE;
+      if (col + 2 > row) x.z = GT_CAUSAL_MASK_VALUE;
+      if (col + 3 > row) x.w = GT_CAUSAL_MASK_VALUE;
+    }
+    *reinterpret_cast<float4*>(tile + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4)) = x;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, p.accumulate != 0);
 }
 
 // Same epilogue for outputs whose rows are not 16-byte aligned (odd leading dimension, e.g. the
@@ -277,17 +372,17 @@ template <int BN, bool A_MN, bool B_MN, bool X3, bool A_GEN>
 __global__ void __launch_bounds__(A_GEN ? NUM_THREADS_AGEN : NUM_THREADS, 1)
 gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const __grid_constant__ CUtensorMap map_a_lo, const __grid_constant__ CUtensorMap map_b_lo,
-                    const UmmaParams p) {
+                    const __grid_constant__ CUtensorMap map_c, const UmmaParams p) {
   using C = Cfg<BN, X3>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint8_t* ctrl = smem_aligned + STAGES * C::STAGE_BYTES;
+  uint8_t* epi_scratch = smem_aligned + STAGES * C::STAGE_BYTES;   // 1024-byte aligned: the stages are multiples of 1 KB
+  uint8_t* ctrl = epi_scratch + EPI_SCRATCH_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);              // full[S], empty[S], tfull[2], tempty[2], drain
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * MAX_STAGES + 5));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* epi_scratch = reinterpret_cast<float*>(ctrl + 512);
 
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
@@ -332,7 +427,8 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         int batch, tm, tn, ks;
         tile_coords(p, tile, batch, tm, tn, ks);
-        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+        int kb_lo, kb_hi;
+        k_range(p, tm, ks, num_kb, kb_lo, kb_hi);
         if (tile_is_masked<BN>(p, tm, tn)) continue;
         const int i0 = batch % p.batch0, i1 = batch / p.batch0;
         const int m0 = tm * BM, n0 = tn * BN;
@@ -391,7 +487,8 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         int batch, tm, tn, ks;
         tile_coords(p, tile, batch, tm, tn, ks);
-        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+        int kb_lo, kb_hi;
+        k_range(p, tm, ks, num_kb, kb_lo, kb_hi);
         if (tile_is_masked<BN>(p, tm, tn)) continue;
         // tf32: one accumulator per tile.  3xTF32: a fresh accumulator every X3_CHUNK_KB k-blocks,
         // because the tensor core truncates on every accumulate and the bias grows with the
@@ -457,7 +554,8 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
       int batch, tm, tn, ks;
       tile_coords(p, tile, batch, tm, tn, ks);
-      const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+      int kb_lo, kb_hi;
+      k_range(p, tm, ks, num_kb, kb_lo, kb_hi);
       if (tile_is_masked<BN>(p, tm, tn)) continue;
       const int i0 = batch % p.batch0, i1 = batch / p.batch0;
       const float* Ab = p.A + (long long)i0 * p.sA0 + (long long)i1 * p.sA1;
@@ -501,14 +599,19 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    float* epi_tile = epi_scratch + (warp - 2) * (32 * 33);
+    uint8_t* epi_bytes = epi_scratch + (warp - 2) * EPI_WARP_BYTES;
+    float* epi_tile = reinterpret_cast<float*>(epi_bytes);
+    const uint32_t epi_u32 = smem_u32(epi_bytes);
+    int tma_slot = 0;                              // which of the warp's two staging tiles comes next
     int acc = 0; uint32_t aph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
       int batch, tm, tn, ks;
       tile_coords(p, tile, batch, tm, tn, ks);
-      const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+      int kb_lo, kb_hi;
+      k_range(p, tm, ks, num_kb, kb_lo, kb_hi);
       const bool masked = tile_is_masked<BN>(p, tm, tn);
+      if (masked && (p.flags & GT_GEMM_CAUSAL_SKIP_MASKED)) continue;     // the reader never looks above the diagonal
       const int i0 = batch % p.batch0, i1 = batch / p.batch0;
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * BN;
@@ -546,11 +649,18 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int c = 0; c < BN / 32; ++c) {
           const int nb = n0 + c * 32;
           if (nb < p.N) {
-            if (p.vec_ok) { if (row_ok) epilogue_chunk(p, &sum[c * 32], row, nb, row_off); }
+            if (p.c_tma) {
+              epilogue_chunk_tma(p, &map_c, &sum[c * 32], lane, tm * BM + q * 32, nb, i0, i1, row_off, row_ok,
+                                 epi_bytes + tma_slot * 4096, epi_u32 + tma_slot * 4096);
+              tma_slot ^= 1;
+            } else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, &sum[c * 32], row, nb, row_off); }
             else epilogue_chunk_coalesced(p, &sum[c * 32], epi_tile, lane, tm * BM + q * 32, nb, batch_off);
           }
         }
       } else {
+        const bool pre = p.accumulate && p.vec_ok && row_ok && !p.c_tma;
+        float4 cnext[8];
+        bool have_next = prefetch_c(p, pre, n0, row_off, cnext);
         if (!masked) {
           if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
@@ -559,6 +669,11 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int c = 0; c < BN / 32; ++c) {
           const int nb = n0 + c * 32;
           if (nb >= p.N) break;
+          float4 ccur[8];
+          const bool have = have_next;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ccur[j] = cnext[j];
+          have_next = (c + 1 < BN / 32) && prefetch_c(p, pre, nb + 32, row_off, cnext);
           float v[32];
           if (!masked) {
             tc_ld32(lane_base + (uint32_t)(acc * BN + c * 32), v);
@@ -567,7 +682,11 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.0f;
           }
-          if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off); }
+          if (p.c_tma) {
+            epilogue_chunk_tma(p, &map_c, v, lane, tm * BM + q * 32, nb, i0, i1, row_off, row_ok,
+                               epi_bytes + tma_slot * 4096, epi_u32 + tma_slot * 4096);
+            tma_slot ^= 1;
+          } else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off, have ? ccur : nullptr); }
           else epilogue_chunk_coalesced(p, v, epi_tile, lane, tm * BM + q * 32, nb, batch_off);
         }
         if (!masked) {
@@ -577,6 +696,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
     }
+    if (p.c_tma && lane == 0) tma_store_wait_all();   // staging tiles must outlive the stores that read them
   }
 
   tc_fence_before();
@@ -599,21 +719,22 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 constexpr int T256_STAGE_BYTES = 65536;
 constexpr int T256_STAGES = 3;
 constexpr int T256_THREADS = 320;
-constexpr int T256_SMEM_BYTES = T256_STAGES * T256_STAGE_BYTES + 1024 + 512 + 2 * EPI_SCRATCH_BYTES;
+constexpr int T256_SMEM_BYTES = T256_STAGES * T256_STAGE_BYTES + 1024 + 512 + EPI_SCRATCH_BYTES;   // 8 warps x one 4 KB staging tile
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(T256_THREADS, 1)
-gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const UmmaParams p) {
+gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_c, const UmmaParams p) {
   constexpr int STAGES = T256_STAGES;
   constexpr int TM = 256, TN = 256;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint8_t* ctrl = smem_aligned + STAGES * T256_STAGE_BYTES;
+  uint8_t* epi_scratch = smem_aligned + STAGES * T256_STAGE_BYTES;
+  uint8_t* ctrl = epi_scratch + EPI_SCRATCH_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * MAX_STAGES + 5));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* epi_scratch = reinterpret_cast<float*>(ctrl + 512);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
   const uint32_t bar_tfull = bar_empty + 8 * MAX_STAGES;     // [half]
@@ -729,7 +850,8 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int q = warp & 3;
     const int half = (warp - 2) >> 2;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * TN);
-    float* epi_tile = epi_scratch + (warp - 2) * (32 * 33);
+    uint8_t* epi_bytes = epi_scratch + (warp - 2) * 4096;
+    const uint32_t epi_u32 = smem_u32(epi_bytes);
     uint32_t tph = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       int batch, tm, tn, ks;
@@ -741,22 +863,35 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1;
       const long long row_off = batch_off + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
+      const bool pre = p.accumulate && p.vec_ok && row_ok && !p.c_tma;
+      float4 cnext[8];
+      bool have_next = prefetch_c(p, pre, n0, row_off, cnext);
       if (!mbar_wait(bar_tfull + 8 * half, tph, abort_flag, p.status)) break;
       tc_fence_after();
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
         const int nb = n0 + c * 32;
         if (nb >= p.N) break;
+        float4 ccur[8];
+        const bool have = have_next;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ccur[j] = cnext[j];
+        have_next = (c + 1 < TN / 32) && prefetch_c(p, pre, nb + 32, row_off, cnext);
         float v[32];
         tc_ld32(lane_base + (uint32_t)(c * 32), v);
         tc_wait_ld();
-        if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off); }
-        else if (row0 < p.M) epilogue_chunk_coalesced(p, v, epi_tile, lane, row0, nb, batch_off);
+        if (p.c_tma) {
+          if (lane == 0) tma_store_wait_read<0>();     // one staging tile per warp here: wait for the previous store to have read it
+          epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32);
+        } else if (row_ok) {
+          epilogue_chunk(p, v, row, nb, row_off, have ? ccur : nullptr);     // host guarantees aligned rows for this kernel
+        }
       }
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * half);
       tph ^= 1u;
     }
+    if (p.c_tma && lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -819,7 +954,7 @@ struct OperandView {
 };
 
 int encode_map(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int box_cols, int box_rows,
-               long long batch0, long long batch1, bool mn_major) {
+               long long batch0, long long batch1, bool mn_major, bool plain_f32 = false) {
   cuuint64_t dims[4] = {(cuuint64_t)v.cols, (cuuint64_t)v.rows, (cuuint64_t)batch0, (cuuint64_t)batch1};
   const cuuint64_t slice = (cuuint64_t)v.rows * (cuuint64_t)v.ld * 4ull;
   cuuint64_t strides[3] = {(cuuint64_t)v.ld * 4ull,
@@ -827,7 +962,7 @@ int encode_map(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int box_cols
                            batch1 > 1 ? (cuuint64_t)v.s1 * 4ull : slice * (cuuint64_t)batch0};
   cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
-  CUresult r = ctx->encode_tiled(map, ctx->tma_round ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+  CUresult r = ctx->encode_tiled(map, (ctx->tma_round && !plain_f32) ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                                  4, (void*)v.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -842,7 +977,7 @@ int encode_map(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int box_cols
 }
 
 template <int BN, bool A_MN, bool B_MN, bool X3, bool A_GEN>
-int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[4], const UmmaParams& p, int grid, cudaStream_t stream) {
+int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[5], const UmmaParams& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN, X3>;
   auto kern = gt_gemm_umma_kernel<BN, A_MN, B_MN, X3, A_GEN>;
   static bool attr_set = false;   // per instantiation; one caller thread per context
@@ -850,14 +985,14 @@ int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[4], const UmmaParams& p, int 
     GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     attr_set = true;
   }
-  kern<<<grid, A_GEN ? NUM_THREADS_AGEN : NUM_THREADS, C::SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], p);
+  kern<<<grid, A_GEN ? NUM_THREADS_AGEN : NUM_THREADS, C::SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return GT_OK;
 }
 
 template <int BN, bool X3, bool A_GEN>
-int launch_layout(gt_ctx* ctx, int layout, const CUtensorMap maps[4], const UmmaParams& p, int grid, cudaStream_t stream) {
+int launch_layout(gt_ctx* ctx, int layout, const CUtensorMap maps[5], const UmmaParams& p, int grid, cudaStream_t stream) {
   switch (layout) {
     case GT_LAYOUT_NN: return launch_cfg<BN, false, true, X3, A_GEN>(ctx, maps, p, grid, stream);
     case GT_LAYOUT_NT: return launch_cfg<BN, false, false, X3, A_GEN>(ctx, maps, p, grid, stream);
@@ -925,7 +1060,10 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   // Large tf32 problems (long K, at least one full wave of 256 x 256 tiles) take the big-tile kernel.
   const long long tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256) * nbatch;
   static const bool t256_off = getenv("GRADTUITY_GEMM_NO_T256") != nullptr;
-  const bool use256 = !t256_off && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && g.K >= 512 && tiles256 >= ctx->sm_count;
+  static const long long t256_min_k = getenv("GRADTUITY_GEMM_T256_MIN_K") ? atoll(getenv("GRADTUITY_GEMM_T256_MIN_K")) : 2048;
+  const bool use256 = !t256_off && g.flags == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && g.K >= t256_min_k && tiles256 >= ctx->sm_count &&
+                      tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (!g.aux || ((uintptr_t)g.aux & 15) == 0) &&
+                      (!g.bias || ((uintptr_t)g.bias & 15) == 0);
   const int bn = use256 ? 256 : pick_bn(g, ctx->sm_count, x3, a_gen);
   const int tile_m = use256 ? 256 : BM;
 
@@ -933,7 +1071,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   if (a_mn) va = {g.A, g.K, g.M, g.lda, g.sA0, g.sA1}; else va = {g.A, g.M, g.K, g.lda, g.sA0, g.sA1};
   if (b_mn) vb = {g.B, g.K, g.N, g.ldb, g.sB0, g.sB1}; else vb = {g.B, g.N, g.K, g.ldb, g.sB0, g.sB1};
 
-  CUtensorMap maps[4];
+  CUtensorMap maps[5];
   long long b0 = g.batch0, b1 = g.batch1;
   OperandView va_lo = va, vb_lo = vb;
   if (x3) {
@@ -1000,7 +1138,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   // partial sums go to the workspace and a second kernel adds them in a fixed order.
   const int num_kb = (int)((g.K + BK - 1) / BK);
   int ksplit = 1;
-  if (!x3 && g.epilogue != GT_EPI_CAUSAL && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
+  if (!x3 && g.epilogue != GT_EPI_CAUSAL && g.flags == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
     ksplit = (int)(ctx->sm_count / tiles);
     if (ksplit > num_kb / 8) ksplit = num_kb / 8;
     if (ksplit > 32) ksplit = 32;
@@ -1013,6 +1151,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   p.num_tiles = (int)(tiles * ksplit);
   p.epilogue = g.epilogue; p.accumulate = g.accumulate;
   p.alpha = g.alpha;
+  p.flags = g.flags;
   p.status = ctx->d_status;
   bool vec = (((uintptr_t)g.C & 15) == 0) && (g.ldc % 4 == 0) && (g.sC0 % 4 == 0) && (g.sC1 % 4 == 0);
   if (g.aux) vec = vec && (((uintptr_t)g.aux & 15) == 0);
@@ -1030,6 +1169,16 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     p.epilogue = GT_EPI_NONE; p.accumulate = 0; p.alpha = 1.0f;
     p.vec_ok = (g.N % 4 == 0) ? 1 : 0;
   }
+  // C through TMA (store, or reduce-add for C += ...) when its rows can be described; split-K partials
+  // and unaligned outputs keep the direct / coalesced stores.
+  static const bool c_tma_off = getenv("GRADTUITY_GEMM_NO_TMA_STORE") != nullptr;
+  p.c_tma = (!c_tma_off && ksplit == 1 && tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1)) ? 1 : 0;
+  if (p.c_tma) {
+    OperandView vc = {g.C, g.M, g.N, g.ldc, g.sC0, g.sC1};
+    if ((rc = encode_map(ctx, &maps[4], vc, 32, 32, b0, b1, false, /*plain_f32=*/true)) != GT_OK) return rc;
+  } else {
+    maps[4] = maps[1];
+  }
   const int grid = (int)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);
 
   if (use256) {
@@ -1039,7 +1188,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
         GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T256_SMEM_BYTES));
         attr_set[idx] = true;
       }
-      kern<<<grid, T256_THREADS, T256_SMEM_BYTES, stream>>>(maps[0], maps[1], p);
+      kern<<<grid, T256_THREADS, T256_SMEM_BYTES, stream>>>(maps[0], maps[1], maps[4], p);
       GT_CUDA_OK(ctx, cudaGetLastError());
       ctx->launches += 1;
       return GT_OK;
@@ -1105,7 +1254,7 @@ extern "C" int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_
                                       int accumulate, int epilogue, void* stream) {
   if (!ctx) return GT_ERR_INVALID_ARG;
   gt_gemm_args g;
-  g.layout = layout; g.epilogue = epilogue; g.precision = GT_PREC_TF32X3; g.accumulate = accumulate;
+  g.layout = layout; g.epilogue = epilogue; g.precision = GT_PREC_TF32X3; g.accumulate = accumulate; g.flags = 0;
   g.M = M; g.N = N; g.K = K;
   g.A = A; g.lda = lda; g.sA0 = 0; g.sA1 = 0;
   g.B = B; g.ldb = ldb; g.sB0 = 0; g.sB1 = 0;

@@ -45,7 +45,7 @@ struct gt_ctx {
 
 // One GEMM problem, fully resolved (used by both kernels).
 struct gt_gemm_args {
-  int layout, epilogue, precision, accumulate;
+  int layout, epilogue, precision, accumulate, flags;
   int64_t M, N, K;
   const float* A; int64_t lda, sA0, sA1;
   const float* B; int64_t ldb, sB0, sB1;
@@ -62,16 +62,11 @@ int gt_gemm_fma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 bool gt_gemm_umma_eligible(const gt_gemm_args& g);
 
-// GELU, tanh form, with the branch structure of the reference kernel
-// (gradtuity/kernels_cuda/elemwise_kernels.py:104-125).
+// GELU, tanh form: gradtuity/kernels_cuda/elemwise_kernels.py:104-125.
 __device__ __forceinline__ float gt_gelu_tanh(float x) {
-  float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  float t;
-  if (u >= 0.0f) {
-    t = 2.0f / (1.0f + __expf(-2.0f * u)) - 1.0f;
-  } else {
-    float e = __expf(2.0f * u);
-    t = (e - 1.0f) / (e + 1.0f);
-  }
+  // tanh(u) = 1 - 2 / (1 + exp(2u)): the same function as the reference's two-branch form, written
+  // without the branch and with the fast divide (exp overflow gives 2/inf = 0, i.e. tanh = 1).
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
   return 0.5f * x * (1.0f + t);
 }

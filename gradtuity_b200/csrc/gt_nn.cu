@@ -56,6 +56,15 @@ __device__ __forceinline__ float block_max_all(float v, float* red) {
   return red[32];
 }
 
+// causal == 1: everything beyond the diagonal is written as 0.  causal == 2: zeros are written only
+// up to the end of the row's 128-wide diagonal block; what lies beyond is left untouched, for
+// consumers that contract over k-blocks up to the diagonal only (GT_GEMM_A_LOWER / AT_LOWER).
+__device__ __forceinline__ int zero_end(int causal, int r, int cols) {
+  if (causal != 2) return cols;
+  const int e = (r / 128 + 1) * 128;
+  return e < cols ? e : cols;
+}
+
 // ---- softmax ------------------------------------------------------------------------------------
 // y = softmax(x) over the last dimension.  causal: row r of each (cols x cols) block keeps columns
 // j <= r % cols; the rest are written as exactly 0 and never read (they may hold anything, e.g.
@@ -73,7 +82,8 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const float* x, float*
   for (int j = threadIdx.x; j < limit; j += blockDim.x) s += __expf(xr[j] - m);
   s = block_sum_all(s, red);
   const float inv = 1.0f / s;
-  for (int j = threadIdx.x; j < cols; j += blockDim.x) yr[j] = j < limit ? __expf(xr[j] - m) * inv : 0.0f;
+  const int zend = zero_end(causal, (int)(row % cols), cols);
+  for (int j = threadIdx.x; j < zend; j += blockDim.x) yr[j] = j < limit ? __expf(xr[j] - m) * inv : 0.0f;
 }
 
 // dx = scale * y * (dy - sum_j y_j dy_j), written (not accumulated), as the reference's
@@ -89,7 +99,8 @@ __global__ void __launch_bounds__(256) softmax_bwd_kernel(float* dx, const float
   float dot = 0.0f;
   for (int j = threadIdx.x; j < limit; j += blockDim.x) dot += yr[j] * dyr[j];
   dot = block_sum_all(dot, red);
-  for (int j = threadIdx.x; j < cols; j += blockDim.x) dxr[j] = j < limit ? scale * yr[j] * (dyr[j] - dot) : 0.0f;
+  const int zend = zero_end(causal, (int)(row % cols), cols);
+  for (int j = threadIdx.x; j < zend; j += blockDim.x) dxr[j] = j < limit ? scale * yr[j] * (dyr[j] - dot) : 0.0f;
 }
 
 // Vectorised forms for rows of up to 4096 floats whose length is a multiple of 4: the row is read
@@ -127,10 +138,11 @@ __global__ void __launch_bounds__(256) softmax_fwd_vec_kernel(const float* x, fl
   }
   s = block_sum_all(s, red);
   const float inv = 1.0f / s;
+  const int zend = zero_end(causal, (int)(row % cols), cols);
 #pragma unroll
   for (int it = 0; it < SM_VEC_ITERS; ++it) {
     const int j = (it * 256 + threadIdx.x) * 4;
-    if (j < cols) yr[j >> 2] = make_float4(v[it].x * inv, v[it].y * inv, v[it].z * inv, v[it].w * inv);   // exp(-inf) = 0 beyond the limit
+    if (j < zend) yr[j >> 2] = make_float4(v[it].x * inv, v[it].y * inv, v[it].z * inv, v[it].w * inv);   // exp(-inf) = 0 beyond the limit
   }
 }
 
@@ -159,10 +171,11 @@ __global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(float* dx, const f
     }
   }
   dot = block_sum_all(dot, red);
+  const int zend = zero_end(causal, (int)(row % cols), cols);
 #pragma unroll
   for (int it = 0; it < SM_VEC_ITERS; ++it) {
     const int j = (it * 256 + threadIdx.x) * 4;
-    if (j < cols)
+    if (j < zend)
       dxr[j >> 2] = make_float4(scale * yv[it].x * (gv[it].x - dot), scale * yv[it].y * (gv[it].y - dot),
                                 scale * yv[it].z * (gv[it].z - dot), scale * yv[it].w * (gv[it].w - dot));
   }

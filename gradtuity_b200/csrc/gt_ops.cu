@@ -34,9 +34,7 @@ __device__ __forceinline__ float ew_apply(float a, float b, float s) {
   if (OP == OP_GELU) return gt_gelu_tanh(a);
   if (OP == OP_GELU_BWD) {                                        // a = dY, b = x
     float u = 0.7978845608028654f * (b + 0.044715f * b * b * b);
-    float t;
-    if (u >= 0.0f) { t = 2.0f / (1.0f + __expf(-2.0f * u)) - 1.0f; }
-    else { float e = __expf(2.0f * u); t = (e - 1.0f) / (e + 1.0f); }
+    float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
     float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * b * b);
     return a * (0.5f * (1.0f + t) + 0.5f * b * (1.0f - t * t) * du);
   }

@@ -45,14 +45,14 @@ def gemm_batched(layout: int, M: int, N: int, K: int,
                  b_ptr: int, ldb: int, sb0: int, sb1: int,
                  c_ptr: int, ldc: int, sc0: int, sc1: int,
                  batch0: int, batch1: int = 1, *, bias_ptr: int = 0, aux_ptr: int = 0, alpha: float = 1.0,
-                 accumulate: bool = False, epilogue: int = EPI_NONE, precision: int | None = None) -> None:
+                 accumulate: bool = False, epilogue: int = EPI_NONE, precision: int | None = None, flags: int = 0) -> None:
     lib = _lib.load_library()
     if precision is None:
         precision = default_precision()
-    _lib.check(lib.gt_gemm_batched(_lib.context(), layout, M, N, K, _p(a_ptr), lda, sa0, sa1, _p(b_ptr), ldb, sb0, sb1,
-                                   _p(c_ptr), ldc, sc0, sc1, batch0, batch1, _p(bias_ptr), _p(aux_ptr), alpha,
-                                   1 if accumulate else 0, epilogue, precision, None),
-               "gt_gemm_batched")
+    _lib.check(lib.gt_gemm_batched_ex(_lib.context(), layout, M, N, K, _p(a_ptr), lda, sa0, sa1, _p(b_ptr), ldb, sb0, sb1,
+                                      _p(c_ptr), ldc, sc0, sc1, batch0, batch1, _p(bias_ptr), _p(aux_ptr), alpha,
+                                      1 if accumulate else 0, epilogue, precision, flags, None),
+               "gt_gemm_batched_ex")
 
 
 def gemm_3xtf32_noalloc(layout: int, M: int, N: int, K: int, a_ptr: int, lda: int, b_ptr: int, ldb: int,

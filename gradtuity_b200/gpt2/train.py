@@ -2,8 +2,8 @@
 (forward, mean cross-entropy, zero_grad, backward, sync_grads, clip_grad_norm_, AdamW step) on the
 gradtuity_b200 modules.
 
-    python -m gradtuity_b200.launch --nproc N -m ...   is not needed for one GPU:
-    python -m gradtuity_b200.gpt2.train --steps 20 [--batch_size 8 --seq_len 1024]
+    python -m gradtuity_b200.gpt2.train --steps 20 [--batch_size 8 --seq_len 1024]          (one GPU)
+    python -m gradtuity_b200.launch --nproc N gradtuity_b200/gpt2/train.py --steps 20       (N GPUs)
 
 Tokens are uniform random ids (what gpt2/make_test_data.py:37-40 generates), weights are
 N(0, 0.02) from a seeded numpy generator, LayerNorm gains 1, biases 0, dropout 0.  Rank r of a
@@ -15,12 +15,18 @@ import argparse
 import math
 import time
 
+import os
+import sys
+
 import numpy as np
 
-from .. import _lib
-from ..optim import AdamW, clip_grad_norm_
-from ..tensor import Tensor
-from .model import GPT2Small
+if __package__ in (None, ""):          # run as a script (e.g. by the launcher): make the package importable
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from gradtuity_b200 import _lib
+from gradtuity_b200.gpt2.model import GPT2Small
+from gradtuity_b200.optim import AdamW, clip_grad_norm_
+from gradtuity_b200.tensor import Tensor
 
 
 def seeded_state(model: GPT2Small, seed: int = 3, std: float = 0.02) -> dict:
@@ -73,7 +79,7 @@ def train_step(model: GPT2Small, optimizer: AdamW, params: list, ids_t: Tensor, 
     optimizer.zero_grad()
     loss.backward()
     if world_size > 1:
-        from ..dist import sync_grads
+        from gradtuity_b200.dist import sync_grads
 
         sync_grads(params)
     _, scale = clip_grad_norm_(params, max_norm, eps=1e-6, defer=True)
@@ -94,12 +100,10 @@ def main() -> None:
     ap.add_argument("--vocab_size", type=int, default=50257)
     args = ap.parse_args()
 
-    import os
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if world > 1:
-        from .. import dist
+        from gradtuity_b200 import dist
 
         dist.init()
     model = build_model(vocab_size=args.vocab_size, seq_len=args.seq_len, n_layer=args.n_layer)

@@ -571,16 +571,26 @@ class Tensor:
             raise ValueError(f"embed_dim ({E}) must be divisible by num_heads ({H})")
         D = E // H
         scale = 1.0 / (D ** 0.5)
-        from ._lib import EPI_CAUSAL
+        from ._lib import EPI_CAUSAL, GEMM_A_LOWER, GEMM_AT_LOWER, GEMM_CAUSAL_SKIP_MASKED, PREC_FP32
+        # P and dS are zero above the diagonal.  When every operand can take the tensor-core path
+        # the GEMMs are told so: score tiles wholly above the diagonal are neither computed nor
+        # written, the softmax kernels write zeros only up to the end of each row's 128-wide
+        # diagonal block, and the products that read P / dS contract only over the k-blocks that can
+        # be non-zero.  That removes about 45 % of the (B, H, S, S) traffic; the values used are the same.
+        trimmed = (S % 4 == 0 and D % 4 == 0 and _gemm.default_precision() != PREC_FP32)
+        f_skip = GEMM_CAUSAL_SKIP_MASKED if trimmed else 0
+        f_lower = GEMM_A_LOWER if trimmed else 0
+        f_upper = GEMM_AT_LOWER if trimmed else 0
+        sm_mode = 2 if trimmed else 1
         p = empty_tensor((B, H, S, S))
         # scores[b, h] = scale * Q[b, :, h, :] K[b, :, h, :]^T, masked: NT, in-place heads
         _gemm.gemm_batched(LAYOUT_NT, S, S, D, q.ptr, E, D, S * E, k.ptr, E, D, S * E,
-                           p.ptr, S, S * S, H * S * S, H, B, alpha=scale, epilogue=EPI_CAUSAL)
-        _call("gt_softmax", _vp(p.ptr), _vp(p.ptr), B * H * S, S, 1)
+                           p.ptr, S, S * S, H * S * S, H, B, alpha=scale, epilogue=EPI_CAUSAL, flags=f_skip)
+        _call("gt_softmax", _vp(p.ptr), _vp(p.ptr), B * H * S, S, sm_mode)
         out = empty_tensor((B, S, E))
         # O[b, :, h, :] = P[b, h] V[b, :, h, :]: NN, output written straight into (B, S, H, d)
         _gemm.gemm_batched(LAYOUT_NN, S, D, S, p.ptr, S, S * S, H * S * S, v.ptr, E, D, S * E,
-                           out.ptr, E, D, S * E, H, B)
+                           out.ptr, E, D, S * E, H, B, flags=f_lower)
 
         def _backward(g: "Tensor") -> None:
             need_qk = q.requires_grad or k.requires_grad
@@ -588,24 +598,24 @@ class Tensor:
                 ptr, acc = grad_target(v)
                 # dV[b, :, h, :] += P[b, h]^T dO[b, :, h, :]   (TN)
                 _gemm.gemm_batched(LAYOUT_TN, S, D, S, p.ptr, S, S * S, H * S * S, g.ptr, E, D, S * E,
-                                   ptr, E, D, S * E, H, B, accumulate=acc)
+                                   ptr, E, D, S * E, H, B, accumulate=acc, flags=f_upper)
             if need_qk:
                 with temp_storage(B * H * S * S * F32) as st:
                     # dP[b, h] = dO[b, :, h, :] V[b, :, h, :]^T   (NT); only the lower triangle is needed
                     _gemm.gemm_batched(LAYOUT_NT, S, S, D, g.ptr, E, D, S * E, v.ptr, E, D, S * E,
-                                       st.ptr, S, S * S, H * S * S, H, B, epilogue=EPI_CAUSAL)
+                                       st.ptr, S, S * S, H * S * S, H, B, epilogue=EPI_CAUSAL, flags=f_skip)
                     # dS = scale * P * (dP - sum P dP), zero above the diagonal, in place
-                    _call("gt_softmax_backward", _vp(st.ptr), _vp(p.ptr), _vp(st.ptr), B * H * S, S, 1, scale)
+                    _call("gt_softmax_backward", _vp(st.ptr), _vp(p.ptr), _vp(st.ptr), B * H * S, S, sm_mode, scale)
                     if q.requires_grad:
                         ptr, acc = grad_target(q)
                         # dQ[b, :, h, :] += dS[b, h] K[b, :, h, :]   (NN)
                         _gemm.gemm_batched(LAYOUT_NN, S, D, S, st.ptr, S, S * S, H * S * S, k.ptr, E, D, S * E,
-                                           ptr, E, D, S * E, H, B, accumulate=acc)
+                                           ptr, E, D, S * E, H, B, accumulate=acc, flags=f_lower)
                     if k.requires_grad:
                         ptr, acc = grad_target(k)
                         # dK[b, :, h, :] += dS[b, h]^T Q[b, :, h, :]   (TN)
                         _gemm.gemm_batched(LAYOUT_TN, S, D, S, st.ptr, S, S * S, H * S * S, q.ptr, E, D, S * E,
-                                           ptr, E, D, S * E, H, B, accumulate=acc)
+                                           ptr, E, D, S * E, H, B, accumulate=acc, flags=f_upper)
 
         out._set_graph(parents=(q, k, v), backward_fn=_backward)
         return out

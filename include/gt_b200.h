@@ -138,6 +138,27 @@ int gt_gemm_batched(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
                     const float* bias, float* aux, float alpha, int accumulate,
                     int epilogue, int precision, void* stream);
 
+/* gt_gemm_batched with structure hints (bit flags) for the attention products, where P and dS are
+ * zero above the diagonal of every (T, T) slice:
+ *   GT_GEMM_A_LOWER             A is stored (M, K), square, and A[m, k] == 0 for k > m: row tile tm
+ *                               contracts only over k <= its last row        (O = P V, dQ = dS K)
+ *   GT_GEMM_AT_LOWER            A is stored (K, M), square, and A[k, m] == 0 for k < m: row tile tm
+ *                               contracts only over k >= its first row       (dV = P^T dO, dK = dS^T Q)
+ *   GT_GEMM_CAUSAL_SKIP_MASKED  with GT_EPI_CAUSAL: 128-row tiles wholly above the diagonal are not
+ *                               written at all (their contents are undefined); for consumers that
+ *                               never read above the diagonal
+ * The hints only remove work whose result is known to be zero / unused; results are unchanged.   */
+#define GT_GEMM_A_LOWER             1
+#define GT_GEMM_AT_LOWER            2
+#define GT_GEMM_CAUSAL_SKIP_MASKED  4
+int gt_gemm_batched_ex(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                       const float* A, int64_t lda, int64_t strideA0, int64_t strideA1,
+                       const float* B, int64_t ldb, int64_t strideB0, int64_t strideB1,
+                       float* C, int64_t ldc, int64_t strideC0, int64_t strideC1,
+                       int64_t batch0, int64_t batch1,
+                       const float* bias, float* aux, float alpha, int accumulate,
+                       int epilogue, int precision, int flags, void* stream);
+
 /* 3xTF32 GEMM for callers that must not cause a device allocation (no counterpart in the
  * reference, which allocates per tensor).  Same result as gt_gemm(..., GT_PREC_TF32X3) for a
  * single, non-batched problem without an aux output, but the hi/lo operand copies live in a
@@ -194,6 +215,8 @@ int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t
  *   gt_softmax(causal=0)          softmax_forward_kernel             kernels_cuda/softmax_kernels.py:22-58
  *   gt_softmax(causal=1)          softmax_with_causal_mask_forward   kernels_cuda/softmax_kernels.py:94-129
  *                                 (masked outputs exactly 0; masked inputs are never read)
+ *                                 causal=2: as 1, but zeros are written only up to the end of the row's
+ *                                 128-wide diagonal block (for GT_GEMM_A_LOWER / AT_LOWER consumers)
  *   gt_softmax_backward           softmax_backward_kernel            kernels_cuda/softmax_kernels.py:60-92
  *                                 (writes dx; `scale` folds the 1/sqrt(d) of attention; causal=1 reads
  *                                  only the kept columns and writes 0 elsewhere)

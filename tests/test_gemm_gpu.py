@@ -241,6 +241,43 @@ def test_batched_causal_scores_in_place_heads(gt):
     assert O.rel_frobenius(s[..., keep], ref[..., keep]) <= U.TOL["tf32"]
 
 
+def test_triangular_hints_trim_work_not_results(gt):
+    """gt_gemm_batched_ex flags: with A declared lower-triangular the k-blocks beyond a row tile's
+    diagonal block are never read (NaN there must not show), and causal score tiles wholly above the
+    diagonal are left unwritten."""
+    from gradtuity_b200 import _lib, gemm as G
+    from gradtuity_b200._lib import GEMM_A_LOWER, GEMM_AT_LOWER, GEMM_CAUSAL_SKIP_MASKED
+
+    rng = np.random.default_rng(17)
+    Bn, S, D = 3, 384, 64
+    tri = np.tril(rng.standard_normal((Bn, S, S))).astype(np.float32)
+    poisoned = tri.copy()
+    for i in range(S):                                   # beyond the end of row i's 128-wide diagonal block
+        poisoned[:, i, (i // 128 + 1) * 128:] = np.nan
+    v = rng.standard_normal((Bn, S, D)).astype(np.float32)
+    dA, dV, dC = U.DeviceBuffer(poisoned), U.DeviceBuffer(v), U.DeviceBuffer(nbytes=Bn * S * D * 4)
+    G.gemm_batched(0, S, D, S, dA.ptr, S, S * S, 0, dV.ptr, D, S * D, 0, dC.ptr, D, S * D, 0, Bn, flags=GEMM_A_LOWER)
+    _lib.device_status()
+    assert O.rel_frobenius(dC.read((Bn, S, D)), O.gemm(tri, v, "NN")) <= U.TOL["tf32"]
+    # transposed use: A stored (K, M) with A[k, m] = 0 for k < m  ->  C = A^T V
+    G.gemm_batched(2, S, D, S, dA.ptr, S, S * S, 0, dV.ptr, D, S * D, 0, dC.ptr, D, S * D, 0, Bn, flags=GEMM_AT_LOWER)
+    _lib.device_status()
+    assert O.rel_frobenius(dC.read((Bn, S, D)), O.gemm(tri, v, "TN")) <= U.TOL["tf32"]
+    # causal scores with masked tiles skipped
+    q = rng.standard_normal((Bn, S, D)).astype(np.float32); k = rng.standard_normal((Bn, S, D)).astype(np.float32)
+    dQ, dK = U.DeviceBuffer(q), U.DeviceBuffer(k)
+    dS = U.DeviceBuffer(np.full((Bn, S, S), 7.0, np.float32))
+    G.gemm_batched(1, S, S, D, dQ.ptr, D, S * D, 0, dK.ptr, D, S * D, 0, dS.ptr, S, S * S, 0, Bn,
+                   epilogue=U.EPILOGUES["causal"], flags=GEMM_CAUSAL_SKIP_MASKED)
+    _lib.device_status()
+    sc = dS.read((Bn, S, S))
+    keep = np.tril(np.ones((S, S), bool))
+    assert O.rel_frobenius(sc[:, keep], O.gemm(q, k, "NT")[:, keep]) <= U.TOL["tf32"]
+    assert np.all(sc[:, 0:128, 256:384] == 7.0)          # a tile wholly above the diagonal: untouched
+    with pytest.raises(RuntimeError, match="square"):
+        G.gemm_batched(0, S, D, 128, dA.ptr, S, S * S, 0, dV.ptr, D, S * D, 0, dC.ptr, D, S * D, 0, Bn, flags=GEMM_A_LOWER)
+
+
 # ---- error behaviour --------------------------------------------------------------------------
 
 def test_invalid_arguments_return_status_not_crash(gt):
@@ -290,10 +327,10 @@ def test_full_size_sampled_rows_and_linearity(gt, precision, M, N, K):
 
 
 @pytest.mark.parametrize("layout", ["NN", "NT", "TN"])
-@pytest.mark.parametrize("M,N,K,epilogue,acc", [(4096, 4096, 520, "none", False), (4000, 4104, 768, "bias_gelu", False),
-                                                (3968, 4360, 1024, "none", True)])
+@pytest.mark.parametrize("M,N,K,epilogue,acc", [(4096, 4096, 2056, "none", False), (4000, 4104, 2048, "bias_gelu", False),
+                                                (3968, 4360, 2304, "none", True)])
 def test_big_tile_kernel(gt, layout, M, N, K, epilogue, acc):
-    """Problems with at least one wave of 256 x 256 tiles and K >= 512 run on the big-tile kernel:
+    """Problems with at least one wave of 256 x 256 tiles and K >= 2048 run on the big-tile kernel:
     ragged M / N / K, every layout, fused epilogue with stored pre-activation, accumulate."""
     from gradtuity_b200 import _lib, gemm as G
 

@@ -243,6 +243,39 @@ def test_tiny_gpt2_training_tracks_the_float64_oracle(T, precision, monkeypatch)
         assert rel(t.numpy(), p[k]) < tol_p, k
 
 
+def test_200_step_loss_curve_tracks_the_oracle(T, monkeypatch):
+    """The end-to-end criterion at reduced size: 200 training steps (AdamW lr 3e-4, clip 1.0, fresh
+    uniform-random tokens every step) in tf32 mode; the loss stays within 1e-3 relative of the float64
+    oracle's at every step."""
+    from gradtuity_b200.gpt2 import GPT2Small
+    from gradtuity_b200.gpt2.train import train_step
+    from gradtuity_b200.optim import AdamW
+
+    monkeypatch.setenv("GRADTUITY_GEMM_PRECISION", "tf32")
+    rng = np.random.default_rng(3)
+    V, S, E, H, L, B = 128, 32, 32, 2, 2, 4
+    p0 = _tiny_params(rng, V, S, E, L)
+    p0 = {k: (v * 0.1 if v.ndim == 2 else v) for k, v in p0.items()}          # std 0.02, as in the configs
+    model = GPT2Small(vocab_size=V, n_positions=S, n_embd=E, n_layer=L, n_head=H, embd_pdrop=0, attn_pdrop=0, resid_pdrop=0)
+    model.load_state_dict({k: T.from_numpy(v, requires_grad=True) for k, v in p0.items()}, strict=False)
+    params = model.parameters()
+    opt = AdamW(params, lr=3e-4, weight_decay=0.01)
+    orc = GO.GPT2Oracle(L, H)
+    p = {k: v.astype(np.float64) for k, v in p0.items()}
+    m = {k: np.zeros_like(v) for k, v in p.items()}
+    vv = {k: np.zeros_like(v) for k, v in p.items()}
+    worst = 0.0
+    for step in range(1, 201):
+        ids = rng.integers(0, V, (B, S)); labels = rng.integers(0, V, B * S)
+        loss = train_step(model, opt, params, T.from_numpy(ids.astype(np.float32)), T.from_numpy(labels.astype(np.float32)), 1.0).item()
+        ref_loss, g = orc.loss_and_grads(p, ids, labels)
+        g, _ = GO.clip_grad_norm(g, 1.0)
+        for k in p:
+            p[k], m[k], vv[k] = GO.adamw_step(p[k], g[k], m[k], vv[k], step, 3e-4)
+        worst = max(worst, abs(loss - ref_loss) / abs(ref_loss))
+    assert worst <= 1e-3, worst
+
+
 def test_deferred_clip_equals_in_place_clip(T):
     from gradtuity_b200.optim import AdamW, clip_grad_norm_
 
