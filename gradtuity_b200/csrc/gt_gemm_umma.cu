@@ -36,10 +36,10 @@ namespace {
 constexpr int BM = 128;
 constexpr int BK = 32;                       // fp32 elements per k-block = 128 bytes
 constexpr int UMMA_K = 8;                    // tf32 elements per tcgen05.mma
-constexpr int NUM_THREADS = 192;            // producer warp, MMA warp, 4 epilogue warps
-constexpr int NUM_THREADS_AGEN = 320;       // + 4 warps that copy an unaligned A operand with cp.async
-constexpr int EPI_WARP_BYTES = 8192;                 // per epilogue warp: two 32 x 32 fp32 staging tiles for TMA stores
-constexpr int EPI_SCRATCH_BYTES = 4 * EPI_WARP_BYTES;  // (the coalesced fallback uses 32 x 33 floats of the same space)
+constexpr int NUM_THREADS = 320;            // producer warp, MMA warp, 8 epilogue warps (two per tensor-memory lane quarter)
+constexpr int NUM_THREADS_AGEN = 320;       // producer, MMA, 4 epilogue warps, 4 warps that copy an unaligned A with cp.async
+constexpr int EPI_WARP_BYTES = 4096;                 // per epilogue warp: one 32 x 32 fp32 staging tile (TMA store / coalesced fallback)
+constexpr int EPI_SCRATCH_BYTES = 8 * EPI_WARP_BYTES;
 constexpr int MAX_STAGES = 8;
 constexpr int X3_CHUNK_KB = 8;                // 3xTF32: k-blocks accumulated in tensor memory before an fp32 register add
 constexpr int SMEM_BUDGET = 232448 - 1024 - 512 - EPI_SCRATCH_BYTES;   // 227 KB minus alignment slack, barriers, epilogue staging
@@ -291,14 +291,14 @@ __device__ __forceinline__ bool prefetch_c(const UmmaParams& p, bool enabled, in
 // it applies the fused epilogue in registers, writes its 128-byte row into the staging tile in the
 // 128-byte-swizzle order, and lane 0 hands the tile to the TMA unit, which writes whole rows,
 // clips at M and N, and for `C += ...` performs the addition in L2 (no read of C by the SM).
-// `stage` alternates between the warp's two tiles so that a store may still be reading the
-// previous one; with an aux output the pre-activation is stored directly from registers.
+// Each epilogue warp has one staging tile; the other warps' stores hide the wait for it.  With an
+// aux output the pre-activation is stored directly from registers.
 __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
                                                    int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                    uint8_t* tile, uint32_t tile_u32) {
   const int row = row0 + lane;
   const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
-  if (lane == 0) tma_store_wait_read<1>();          // the store issued two chunks ago has read this tile
+  if (lane == 0) tma_store_wait_read<0>();          // the previous store of this warp has finished reading the tile
   __syncwarp();
 #pragma unroll
   for (int j = 0; j < 32; j += 4) {
@@ -345,7 +345,7 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CU
 __device__ __forceinline__ void epilogue_chunk_coalesced(const UmmaParams& p, const float* v, float* tile, int lane,
                                                          int row0, int nb, long long batch_off) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) tile[lane * 33 + j] = v[j];
+  for (int j = 0; j < 32; ++j) tile[lane * 32 + (j ^ lane)] = v[j];      // XOR keeps both phases free of bank conflicts
   __syncwarp();
   const int col = nb + lane;
   const bool col_ok = col < p.N;
@@ -356,7 +356,7 @@ __device__ __forceinline__ void epilogue_chunk_coalesced(const UmmaParams& p, co
     if (col_ok) {
       const int row = row0 + r;
       const long long off = batch_off + (long long)row * p.ldc + col;
-      float x = p.alpha * tile[r * 33 + lane] + b;
+      float x = p.alpha * tile[r * 32 + (lane ^ r)] + b;
       if (p.aux) p.aux[off] = x;
       if (p.epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
       else if (p.epilogue == GT_EPI_BIAS_GELU) x = gt_gelu_tanh(x);
@@ -375,6 +375,9 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const __grid_constant__ CUtensorMap map_c, const UmmaParams p) {
   using C = Cfg<BN, X3>;
   constexpr int STAGES = C::STAGES;
+  // Epilogue warp sets: two sets of four warps share a tile's 32-column chunks alternately; with
+  // the cp.async warps present there is room for one set only.
+  constexpr int EPI_SETS = A_GEN ? 1 : 2;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -400,7 +403,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 128);
+      mbar_init(bar_tempty + 8 * a, 128 * EPI_SETS);
     }
     mbar_init(bar_drain, 1);
     *abort_flag = 0;
@@ -598,11 +601,12 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
+    const int eset = (warp - 2) >> 2;             // which of the EPI_SETS warp sets this warp belongs to
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     uint8_t* epi_bytes = epi_scratch + (warp - 2) * EPI_WARP_BYTES;
     float* epi_tile = reinterpret_cast<float*>(epi_bytes);
     const uint32_t epi_u32 = smem_u32(epi_bytes);
-    int tma_slot = 0;                              // which of the warp's two staging tiles comes next
+    constexpr int MY_CHUNKS = (BN / 32 + EPI_SETS - 1) / EPI_SETS;     // chunks c = eset, eset + EPI_SETS, ...
     int acc = 0; uint32_t aph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
@@ -613,7 +617,8 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const bool masked = tile_is_masked<BN>(p, tm, tn);
       if (masked && (p.flags & GT_GEMM_CAUSAL_SKIP_MASKED)) continue;     // the reader never looks above the diagonal
       const int i0 = batch % p.batch0, i1 = batch / p.batch0;
-      const int row = tm * BM + q * 32 + lane;
+      const int row0 = tm * BM + q * 32;
+      const int row = row0 + lane;
       const int n0 = tn * BN;
       const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1 + (long long)ks * p.ks_stride;
       const long long row_off = batch_off + (long long)row * p.ldc;
@@ -621,22 +626,23 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if constexpr (X3) {
         // The accumulator arrives in K-chunks; they are summed here in fp32 registers
         // (round-to-nearest adds) before the fused epilogue runs once.
-        float sum[BN];
+        float sum[MY_CHUNKS * 32];
 #pragma unroll
-        for (int j = 0; j < BN; ++j) sum[j] = 0.0f;
+        for (int j = 0; j < MY_CHUNKS * 32; ++j) sum[j] = 0.0f;
         if (!masked) {
           const int nchunks = (kb_hi - kb_lo + X3_CHUNK_KB - 1) / X3_CHUNK_KB;
           for (int ch = 0; ch < nchunks; ++ch) {
             if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < BN / 32; ++c) {
-              if (n0 + c * 32 < p.N) {
+            for (int lc = 0; lc < MY_CHUNKS; ++lc) {
+              const int c = lc * EPI_SETS + eset;
+              if (c < BN / 32 && n0 + c * 32 < p.N) {
                 float v[32];
                 tc_ld32(lane_base + (uint32_t)(acc * BN + c * 32), v);
                 tc_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) sum[c * 32 + j] += v[j];
+                for (int j = 0; j < 32; ++j) sum[lc * 32 + j] += v[j];
               }
             }
             tc_fence_before();
@@ -646,34 +652,24 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (!ok) break;
         }
 #pragma unroll
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int lc = 0; lc < MY_CHUNKS; ++lc) {
+          const int c = lc * EPI_SETS + eset;
           const int nb = n0 + c * 32;
-          if (nb < p.N) {
-            if (p.c_tma) {
-              epilogue_chunk_tma(p, &map_c, &sum[c * 32], lane, tm * BM + q * 32, nb, i0, i1, row_off, row_ok,
-                                 epi_bytes + tma_slot * 4096, epi_u32 + tma_slot * 4096);
-              tma_slot ^= 1;
-            } else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, &sum[c * 32], row, nb, row_off); }
-            else epilogue_chunk_coalesced(p, &sum[c * 32], epi_tile, lane, tm * BM + q * 32, nb, batch_off);
+          if (c < BN / 32 && nb < p.N) {
+            if (p.c_tma) epilogue_chunk_tma(p, &map_c, &sum[lc * 32], lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32);
+            else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, &sum[lc * 32], row, nb, row_off); }
+            else epilogue_chunk_coalesced(p, &sum[lc * 32], epi_tile, lane, row0, nb, batch_off);
           }
         }
       } else {
-        const bool pre = p.accumulate && p.vec_ok && row_ok && !p.c_tma;
-        float4 cnext[8];
-        bool have_next = prefetch_c(p, pre, n0, row_off, cnext);
         if (!masked) {
           if (!mbar_wait(bar_tfull + 8 * acc, aph, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
         }
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = eset; c < BN / 32; c += EPI_SETS) {
           const int nb = n0 + c * 32;
           if (nb >= p.N) break;
-          float4 ccur[8];
-          const bool have = have_next;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) ccur[j] = cnext[j];
-          have_next = (c + 1 < BN / 32) && prefetch_c(p, pre, nb + 32, row_off, cnext);
           float v[32];
           if (!masked) {
             tc_ld32(lane_base + (uint32_t)(acc * BN + c * 32), v);
@@ -682,16 +678,13 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.0f;
           }
-          if (p.c_tma) {
-            epilogue_chunk_tma(p, &map_c, v, lane, tm * BM + q * 32, nb, i0, i1, row_off, row_ok,
-                               epi_bytes + tma_slot * 4096, epi_u32 + tma_slot * 4096);
-            tma_slot ^= 1;
-          } else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off, have ? ccur : nullptr); }
-          else epilogue_chunk_coalesced(p, v, epi_tile, lane, tm * BM + q * 32, nb, batch_off);
+          if (p.c_tma) epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32);
+          else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off); }
+          else epilogue_chunk_coalesced(p, v, epi_tile, lane, row0, nb, batch_off);
         }
         if (!masked) {
           tc_fence_before();
-          mbar_arrive(bar_tempty + 8 * acc);        // 128 arrivals hand the accumulator back
+          mbar_arrive(bar_tempty + 8 * acc);        // every epilogue thread hands the accumulator back
           if (++acc == 2) { acc = 0; aph ^= 1u; }
         }
       }
@@ -863,28 +856,19 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1;
       const long long row_off = batch_off + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
-      const bool pre = p.accumulate && p.vec_ok && row_ok && !p.c_tma;
-      float4 cnext[8];
-      bool have_next = prefetch_c(p, pre, n0, row_off, cnext);
       if (!mbar_wait(bar_tfull + 8 * half, tph, abort_flag, p.status)) break;
       tc_fence_after();
 #pragma unroll 1
       for (int c = 0; c < TN / 32; ++c) {
         const int nb = n0 + c * 32;
         if (nb >= p.N) break;
-        float4 ccur[8];
-        const bool have = have_next;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ccur[j] = cnext[j];
-        have_next = (c + 1 < TN / 32) && prefetch_c(p, pre, nb + 32, row_off, cnext);
         float v[32];
         tc_ld32(lane_base + (uint32_t)(c * 32), v);
         tc_wait_ld();
         if (p.c_tma) {
-          if (lane == 0) tma_store_wait_read<0>();     // one staging tile per warp here: wait for the previous store to have read it
           epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32);
         } else if (row_ok) {
-          epilogue_chunk(p, v, row, nb, row_off, have ? ccur : nullptr);     // host guarantees aligned rows for this kernel
+          epilogue_chunk(p, v, row, nb, row_off);     // host guarantees aligned rows for this kernel
         }
       }
       tc_fence_before();

@@ -181,6 +181,90 @@ __global__ void __launch_bounds__(256) softmax_bwd_vec_kernel(float* dx, const f
   }
 }
 
+// Warp-per-row forms for rows of 128 * NV floats (NV <= 16): a warp keeps its row in registers
+// (NV float4 per lane), reduces with shuffles only, eight rows per block.  The block-per-row kernels
+// above spend most of their time on block scheduling and barriers when a row is only 4 KB.
+template <int NV>
+__global__ void __launch_bounds__(256) softmax_fwd_warp_kernel(const float* x, float* y, long long rows, int causal) {
+  constexpr int cols = 128 * NV;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float4* xr = reinterpret_cast<const float4*>(x + row * cols);
+  float4* yr = reinterpret_cast<float4*>(y + row * cols);
+  const int r = (int)(row % cols);
+  const int limit = causal ? r + 1 : cols;
+  const int zend = zero_end(causal, r, cols);
+  float4 v[NV];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (i * 32 + lane) * 4;
+    if (j < limit) {
+      float4 t = xr[i * 32 + lane];
+      if (j + 1 >= limit) t.y = -INFINITY;
+      if (j + 2 >= limit) t.z = -INFINITY;
+      if (j + 3 >= limit) t.w = -INFINITY;
+      v[i] = t;
+      m = fmaxf(m, fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w)));
+    } else {
+      v[i] = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+  }
+  m = warp_max(m);
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    v[i].x = __expf(v[i].x - m); v[i].y = __expf(v[i].y - m); v[i].z = __expf(v[i].z - m); v[i].w = __expf(v[i].w - m);
+    s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  s = warp_sum(s);
+  const float inv = 1.0f / s;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (i * 32 + lane) * 4;
+    if (j < zend) yr[i * 32 + lane] = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) softmax_bwd_warp_kernel(float* dx, const float* y, const float* dy, long long rows, int causal, float scale) {
+  constexpr int cols = 128 * NV;
+  const int lane = threadIdx.x & 31;
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const float4* yr = reinterpret_cast<const float4*>(y + row * cols);
+  const float4* gr = reinterpret_cast<const float4*>(dy + row * cols);
+  float4* dxr = reinterpret_cast<float4*>(dx + row * cols);
+  const int r = (int)(row % cols);
+  const int limit = causal ? r + 1 : cols;
+  const int zend = zero_end(causal, r, cols);
+  float4 yv[NV], gv[NV];
+  float dot = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (i * 32 + lane) * 4;
+    if (j < limit) {
+      float4 a = yr[i * 32 + lane], g = gr[i * 32 + lane];
+      if (j + 1 >= limit) { a.y = 0.f; g.y = 0.f; }
+      if (j + 2 >= limit) { a.z = 0.f; g.z = 0.f; }
+      if (j + 3 >= limit) { a.w = 0.f; g.w = 0.f; }
+      yv[i] = a; gv[i] = g;
+      dot += (a.x * g.x + a.y * g.y) + (a.z * g.z + a.w * g.w);
+    } else {
+      yv[i] = make_float4(0.f, 0.f, 0.f, 0.f); gv[i] = yv[i];
+    }
+  }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int j = (i * 32 + lane) * 4;
+    if (j < zend)
+      dxr[i * 32 + lane] = make_float4(scale * yv[i].x * (gv[i].x - dot), scale * yv[i].y * (gv[i].y - dot),
+                                       scale * yv[i].z * (gv[i].z - dot), scale * yv[i].w * (gv[i].w - dot));
+  }
+}
+
 // ---- LayerNorm ----------------------------------------------------------------------------------
 // y = (x - mean) * rstd * gamma + beta per row; mean and rstd are saved (two floats per row)
 // and x-hat is recomputed in the backward instead of being stored.
@@ -501,7 +585,18 @@ inline unsigned blocks_for(gt_ctx* ctx, long long n) {
 
 extern "C" int gt_softmax(gt_ctx* ctx, float* y, const float* x, int64_t rows, int64_t cols, int causal) {
   if (!ctx || !y || !x || rows <= 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return GT_ERR_INVALID_ARG;
-  const bool vec = (cols % 4 == 0) && cols <= 256 * 4 * SM_VEC_ITERS && (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+  const bool al16 = ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
+  if (al16 && cols % 128 == 0 && cols <= 2048) {
+    const unsigned nb = (unsigned)((rows + 7) / 8);
+#define GT_SM_CASE(NV_) case NV_: softmax_fwd_warp_kernel<NV_><<<nb, 256, 0, ctx->stream>>>(x, y, rows, causal); break
+    switch ((int)(cols / 128)) {
+      GT_SM_CASE(1); GT_SM_CASE(2); GT_SM_CASE(3); GT_SM_CASE(4); GT_SM_CASE(5); GT_SM_CASE(6); GT_SM_CASE(7); GT_SM_CASE(8);
+      GT_SM_CASE(9); GT_SM_CASE(10); GT_SM_CASE(11); GT_SM_CASE(12); GT_SM_CASE(13); GT_SM_CASE(14); GT_SM_CASE(15); GT_SM_CASE(16);
+    }
+#undef GT_SM_CASE
+    GT_LAUNCH_CHECK(ctx, 1);
+  }
+  const bool vec = (cols % 4 == 0) && cols <= 256 * 4 * SM_VEC_ITERS && al16;
   if (vec) softmax_fwd_vec_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, y, (int)cols, causal);
   else softmax_fwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(x, y, rows, (int)cols, causal);
   GT_LAUNCH_CHECK(ctx, 1);
@@ -510,7 +605,18 @@ extern "C" int gt_softmax(gt_ctx* ctx, float* y, const float* x, int64_t rows, i
 extern "C" int gt_softmax_backward(gt_ctx* ctx, float* dx, const float* y, const float* dy, int64_t rows, int64_t cols,
                                    int causal, float scale) {
   if (!ctx || !dx || !y || !dy || rows <= 0 || cols <= 0 || cols > 0x7fffffff || rows > 0x7fffffff) return GT_ERR_INVALID_ARG;
-  const bool vec = (cols % 4 == 0) && cols <= 256 * 4 * SM_VEC_ITERS && (((uintptr_t)dx | (uintptr_t)y | (uintptr_t)dy) & 15) == 0;
+  const bool al16 = ((((uintptr_t)dx | (uintptr_t)y | (uintptr_t)dy) & 15) == 0);
+  if (al16 && cols % 128 == 0 && cols <= 2048) {
+    const unsigned nb = (unsigned)((rows + 7) / 8);
+#define GT_SM_CASE(NV_) case NV_: softmax_bwd_warp_kernel<NV_><<<nb, 256, 0, ctx->stream>>>(dx, y, dy, rows, causal, scale); break
+    switch ((int)(cols / 128)) {
+      GT_SM_CASE(1); GT_SM_CASE(2); GT_SM_CASE(3); GT_SM_CASE(4); GT_SM_CASE(5); GT_SM_CASE(6); GT_SM_CASE(7); GT_SM_CASE(8);
+      GT_SM_CASE(9); GT_SM_CASE(10); GT_SM_CASE(11); GT_SM_CASE(12); GT_SM_CASE(13); GT_SM_CASE(14); GT_SM_CASE(15); GT_SM_CASE(16);
+    }
+#undef GT_SM_CASE
+    GT_LAUNCH_CHECK(ctx, 1);
+  }
+  const bool vec = (cols % 4 == 0) && cols <= 256 * 4 * SM_VEC_ITERS && al16;
   if (vec) softmax_bwd_vec_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(dx, y, dy, (int)cols, causal, scale);
   else softmax_bwd_kernel<<<(unsigned)rows, 256, 0, ctx->stream>>>(dx, y, dy, rows, (int)cols, causal, scale);
   GT_LAUNCH_CHECK(ctx, 1);
