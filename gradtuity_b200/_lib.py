@@ -96,6 +96,7 @@ SIGNATURES = {
     "gt_add_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64]),
     "gt_sum_all": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int]),
     "gt_colsum_acc": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "gt_repack_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64]),
     "gt_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int]),
     "gt_softmax_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_float]),
     "gt_layernorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float]),

@@ -154,7 +154,27 @@ __global__ void __launch_bounds__(256) colsum_acc_kernel(float* __restrict__ db,
   }
 }
 
+// dst[r, c] = src[r, c] for rows of `cols` floats at different pitches (used to give a matrix with an
+// odd leading dimension a 16-byte aligned copy that TMA can read).
+__global__ void __launch_bounds__(256) repack_rows_kernel(float* __restrict__ dst, long long ld_dst, const float* __restrict__ src,
+                                                          long long ld_src, long long rows, int cols) {
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const float* s = src + r * ld_src;
+    float* d = dst + r * ld_dst;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) d[c] = s[c];
+  }
+}
+
 }  // namespace
+
+extern "C" int gt_repack_rows(gt_ctx* ctx, float* dst, int64_t ld_dst, const float* src, int64_t ld_src, int64_t rows, int64_t cols) {
+  if (!ctx || !dst || !src || rows <= 0 || cols <= 0 || cols > 0x7fffffff || ld_dst < cols || ld_src < cols) return GT_ERR_INVALID_ARG;
+  long long blocks = rows < (long long)ctx->sm_count * 16 ? rows : (long long)ctx->sm_count * 16;
+  repack_rows_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(dst, ld_dst, src, ld_src, rows, (int)cols);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
 
 extern "C" int gt_fill(gt_ctx* ctx, float* out, float value, int64_t n) {
   if (!ctx || !out || n < 0) return GT_ERR_INVALID_ARG;

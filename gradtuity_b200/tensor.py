@@ -538,12 +538,22 @@ class Tensor:
         x = self
 
         def _backward(g: "Tensor") -> None:
+            g_ptr, g_ld, tmp = g.ptr, V, None
+            if V % 4 != 0 and M * V >= (1 << 22) and (x.requires_grad and weight.requires_grad):
+                # dL is read by two large GEMMs and its rows are not 16-byte aligned (odd vocabulary):
+                # one copy to a padded pitch lets both take the TMA path instead of 4-byte copies.
+                g_ld = (V + 3) // 4 * 4
+                tmp = alloc_storage(M * g_ld * F32)
+                _call("gt_repack_rows", _vp(tmp.ptr), g_ld, _vp(g.ptr), V, M, V)
+                g_ptr = tmp.ptr
             if x.requires_grad:
                 ptr, acc = grad_target(x)
-                _gemm.gemm(LAYOUT_NN, M, E, V, g.ptr, V, weight.ptr, E, ptr, E, accumulate=acc)
+                _gemm.gemm(LAYOUT_NN, M, E, V, g_ptr, g_ld, weight.ptr, E, ptr, E, accumulate=acc)
             if weight.requires_grad:
                 ptr, acc = grad_target(weight)
-                _gemm.gemm(LAYOUT_TN, V, E, M, g.ptr, V, x.ptr, E, ptr, E, accumulate=acc)
+                _gemm.gemm(LAYOUT_TN, V, E, M, g_ptr, g_ld, x.ptr, E, ptr, E, accumulate=acc)
+            if tmp is not None:
+                tmp.free()
 
         out._set_graph(parents=(self, weight), backward_fn=_backward)
         return out

@@ -208,6 +208,7 @@ int gt_add_scalar(gt_ctx* ctx, float* dst, const float* scalar, int64_t n);     
 int gt_add_bias(gt_ctx* ctx, float* out, const float* x, const float* bias, int64_t rows, int64_t cols);
 int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate); /* deterministic */
 int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld); /* db[c] += sum_r dy[r,c] */
+int gt_repack_rows(gt_ctx* ctx, float* dst, int64_t ld_dst, const float* src, int64_t ld_src, int64_t rows, int64_t cols); /* copy rows to another pitch */
 
 /* ---- the non-GEMM kernels of the GPT-2 training step -----------------------------------
  * fp32, memory-bound, on the context's compute stream.  Each restates the reference kernel named

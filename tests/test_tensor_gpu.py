@@ -155,6 +155,23 @@ def test_linear_tied_values_and_grads(T):
     assert O.rel_frobenius(tw.grad.numpy(), ref["dw"]) <= 1e-3
 
 
+def test_linear_tied_large_odd_vocabulary_repack_path(T):
+    """M * V large enough and V odd: the backward copies dL once to a padded pitch so that both of
+    its GEMMs read it through TMA."""
+    rng = np.random.default_rng(1)
+    M, V, E = 2048, 2051, 64
+    x = (rng.standard_normal((M, E)) / 8).astype(np.float32)
+    w = (rng.standard_normal((V, E)) / 8).astype(np.float32)
+    dy = (rng.standard_normal((M, V)) / 45).astype(np.float32)
+    tx, tw = T.from_numpy(x, requires_grad=True), T.from_numpy(w, requires_grad=True)
+    y = tx.linear_tied(tw)
+    y.mul(T.from_numpy(dy)).sum().backward()
+    ref = O.linear_tied_forward_backward(x, w, dy)
+    assert O.rel_frobenius(y.numpy(), ref["y"]) <= 1e-3
+    assert O.rel_frobenius(tx.grad.numpy(), ref["dx"]) <= 1e-3
+    assert O.rel_frobenius(tw.grad.numpy(), ref["dw"]) <= 1e-3
+
+
 def test_config0_linear_784_128(T):
     """Config 0: Linear(784 -> 128), batch 128, X ~ U[0,1), W and b ~ U(-1/28, 1/28), dY ~ N(0,1),
     seed 0; y, dX, dW, db against the float64 oracle."""
