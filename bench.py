@@ -366,6 +366,28 @@ def run_micro(args) -> dict:
             "gbs": round(nbytes / t / 1e6, 1), "steps": args.steps, "warmup": args.warmup}
 
 
+def run_sweep(args) -> dict:
+    """Config 1: the square and rectangular GEMM sweep, every layout, plain / bias+ReLU / bias+GELU
+    epilogues in tf32 mode and the plain product in 3xTF32 mode; kernel-only TFLOP/s and the fraction
+    of the measured tf32 peak."""
+    import copy
+
+    peak, _ = _peaks()
+    shapes = [(1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (8192, 768, 3072), (8192, 3072, 768)]
+    rows = []
+    for (m, n, k) in shapes:
+        for layout in ("NN", "NT", "TN"):
+            for prec, epi in (("tf32", "none"), ("tf32", "bias_relu"), ("tf32", "bias_gelu"), ("3xtf32", "none")):
+                a = copy.copy(args)
+                a.shape, a.layout, a.precision, a.epilogue, a.accumulate = [m, n, k], layout, prec, epi, False
+                a.steps = 5 if m * n * k >= 8192 ** 3 else 20
+                a.warmup = 3
+                r = run_micro(a)
+                rows.append({"M": m, "N": n, "K": k, "layout": layout, "precision": prec, "epilogue": epi, "ms": r["ms"],
+                             "tflops": r["tflops"], "frac_of_measured_tf32_peak": round(r["tflops"] / peak, 3)})
+    return {"sweep": "config 1", "peak_tflops": peak, "rows": rows}
+
+
 def run_attn(args) -> dict:
     """Kernel-only timing of the batched attention products of config 2 (B=8, H=12, T=1024, d=64),
     reported as achieved GB/s: these GEMMs are HBM-bound (28 FLOP per byte)."""
@@ -490,9 +512,13 @@ def main():
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
     ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_relu", "bias_gelu", "causal"])
     ap.add_argument("--accumulate", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="kernel-only timing of the whole config-1 GEMM sweep")
     ap.add_argument("--attn", action="store_true", help="kernel-only timing of the batched attention products (GB/s)")
     ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the GPT-2 training leg")
     args = ap.parse_args()
+    if args.sweep:
+        print(json.dumps(run_sweep(args)), flush=True)
+        return
     if args.attn:
         print(json.dumps(run_attn(args)), flush=True)
         return

@@ -83,6 +83,7 @@ SIGNATURES = {
     "gt_gemm_path": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
                              c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                              c_int, POINTER(c_int)]),
+    "gt_selftest_bounded_wait": (c_int, [c_void_p, c_int64]),
     "gt_launch_count": (c_int, [c_void_p, POINTER(c_int64)]),
     "gt_fill": (c_int, [c_void_p, c_void_p, c_float, c_int64]),
     "gt_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int]),

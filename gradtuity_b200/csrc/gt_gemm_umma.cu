@@ -913,7 +913,34 @@ __global__ void gt_split_tf32_kernel(const float* __restrict__ x, float* __restr
 __global__ void __launch_bounds__(256) gt_splitk_reduce_kernel(const float* __restrict__ ws, int ksplit, long long plane,
                                                                float* C, const float* __restrict__ bias, float* aux,
                                                                int M, int N, int batch0, long long ldc, long long sC0, long long sC1,
-                                                               float alpha, int epilogue, int accumulate, long long total) {
+                                                               float alpha, int epilogue, int accumulate, long long total, int vec) {
+  const bool has_bias = epilogue >= GT_EPI_BIAS && epilogue <= GT_EPI_BIAS_GELU;
+  if (vec) {
+    // N, ldc and the batch strides are multiples of 4 and every base is 16-byte aligned: four columns at a time
+    const long long total4 = total >> 2;
+    for (long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i4 < total4; i4 += (long long)gridDim.x * blockDim.x) {
+      const long long i = i4 << 2;
+      const int n = (int)(i % N);
+      const long long t = i / N;
+      const int m = (int)(t % M);
+      const int b = (int)(t / M);
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s2 = 0; s2 < ksplit; ++s2) {
+        const float4 w = *reinterpret_cast<const float4*>(ws + (long long)s2 * plane + i);
+        acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;
+      }
+      float4 x = make_float4(alpha * acc.x, alpha * acc.y, alpha * acc.z, alpha * acc.w);
+      if (has_bias) { const float4 bb = *reinterpret_cast<const float4*>(bias + n); x.x += bb.x; x.y += bb.y; x.z += bb.z; x.w += bb.w; }
+      const long long off = (long long)(b % batch0) * sC0 + (long long)(b / batch0) * sC1 + (long long)m * ldc + n;
+      if (aux) *reinterpret_cast<float4*>(aux + off) = x;
+      if (epilogue == GT_EPI_BIAS_RELU) { x.x = fmaxf(x.x, 0.f); x.y = fmaxf(x.y, 0.f); x.z = fmaxf(x.z, 0.f); x.w = fmaxf(x.w, 0.f); }
+      else if (epilogue == GT_EPI_BIAS_GELU) { x.x = gt_gelu_tanh(x.x); x.y = gt_gelu_tanh(x.y); x.z = gt_gelu_tanh(x.z); x.w = gt_gelu_tanh(x.w); }
+      float4* dst = reinterpret_cast<float4*>(C + off);
+      if (accumulate) { const float4 o = *dst; x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w; }
+      *dst = x;
+    }
+    return;
+  }
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const int n = (int)(i % N);
     const long long t = i / N;
@@ -922,7 +949,7 @@ __global__ void __launch_bounds__(256) gt_splitk_reduce_kernel(const float* __re
     float acc = 0.0f;
     for (int s2 = 0; s2 < ksplit; ++s2) acc += ws[(long long)s2 * plane + i];
     float x = alpha * acc;
-    if (epilogue >= GT_EPI_BIAS && epilogue <= GT_EPI_BIAS_GELU) x += bias[n];
+    if (has_bias) x += bias[n];
     const long long off = (long long)(b % batch0) * sC0 + (long long)(b / batch0) * sC1 + (long long)m * ldc + n;
     if (aux) aux[off] = x;
     if (epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
@@ -1009,7 +1036,7 @@ int pick_bn(const gt_gemm_args& g, int sms, bool x3, bool a_gen) {
   // Cost in "column units per SM": waves x tile width x a per-width efficiency penalty.
   double best = 1e30; int best_bn = 256;
   const int cands[3] = {256, 128, 64};
-  const double pen[3] = {1.0, 1.12, 1.45};
+  const double pen[3] = {1.0, 1.4, 2.0};       // measured on GPT-2 shapes: wider tiles win unless they cost a whole extra wave
   for (int i = 0; i < 3; ++i) {
     if (x3 && cands[i] == 256) continue;            // 3xTF32 at 256 leaves only two stages
     const long long tiles = tm * ((g.N + cands[i] - 1) / cands[i]) * batches;
@@ -1048,7 +1075,9 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   const bool use256 = !t256_off && g.flags == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && g.K >= t256_min_k && tiles256 >= ctx->sm_count &&
                       tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (!g.aux || ((uintptr_t)g.aux & 15) == 0) &&
                       (!g.bias || ((uintptr_t)g.bias & 15) == 0);
-  const int bn = use256 ? 256 : pick_bn(g, ctx->sm_count, x3, a_gen);
+  static const int force_bn = getenv("GRADTUITY_GEMM_FORCE_BN") ? atoi(getenv("GRADTUITY_GEMM_FORCE_BN")) : 0;   // tuning aid
+  int bn = use256 ? 256 : pick_bn(g, ctx->sm_count, x3, a_gen);
+  if (!use256 && (force_bn == 64 || force_bn == 128 || (force_bn == 256 && !x3)) && g.N > force_bn / 2) bn = force_bn;
   const int tile_m = use256 ? 256 : BM;
 
   OperandView va, vb;
@@ -1194,11 +1223,12 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   else { GT_DISPATCH(64); }
 #undef GT_DISPATCH
   if (rc != GT_OK || ksplit == 1) return rc;
-  long long blocks = (plane + 255) / 256;
+  const int rvec = (vec && g.N % 4 == 0) ? 1 : 0;      // `vec`: C, aux and bias 16-byte aligned with strides that are multiples of 4
+  long long blocks = ((rvec ? plane / 4 : plane) + 255) / 256;
   if (blocks > (long long)ctx->sm_count * 8) blocks = (long long)ctx->sm_count * 8;
   gt_splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ws, ksplit, plane, g.C, g.bias, g.aux, (int)g.M, (int)g.N,
                                                                 (int)g.batch0, g.ldc, g.sC0, g.sC1, g.alpha, g.epilogue,
-                                                                g.accumulate, plane);
+                                                                g.accumulate, plane, rvec);
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return GT_OK;
@@ -1264,4 +1294,32 @@ extern "C" int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_
   }
   cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
   return umma_launch_impl(ctx, g, s, g_noalloc_scratch_ptr[ctx->device], GT_NOALLOC_SCRATCH_FLOATS);
+}
+
+// ---- bounded-wait self test ---------------------------------------------------------------------
+// One CTA waits on an mbarrier that nothing will ever arrive on, with the same polling loop the GEMM
+// kernels use but a caller-chosen cycle limit.  The wait must give up, record GT_ERR_TIMEOUT in the
+// status word and return, leaving the context usable: the host-visible half of "no wait in this
+// library can hang the GPU".
+__global__ void gt_selftest_wait_kernel(int* status, long long limit_cycles) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const long long t0 = clock64();
+    bool done = false;
+    while (!done) {
+      if (mbar_try_wait(b, 0)) done = true;
+      else if (clock64() - t0 > limit_cycles) { atomicExch(status, GT_ERR_TIMEOUT); done = true; }
+    }
+  }
+}
+
+extern "C" int gt_selftest_bounded_wait(gt_ctx* ctx, int64_t limit_cycles) {
+  if (!ctx || limit_cycles <= 0 || limit_cycles > 4000000000LL) return GT_ERR_INVALID_ARG;
+  gt_selftest_wait_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, limit_cycles);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
 }

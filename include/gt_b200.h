@@ -184,6 +184,12 @@ int gt_gemm_path(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
                  const float* A, int64_t lda, const float* B, int64_t ldb,
                  const float* C, int64_t ldc, int precision, int* path);
 
+/* Failure-detection self test (no counterpart in the reference): launches one CTA that waits, with
+ * the library's bounded polling loop and a limit of `limit_cycles` SM cycles, on a barrier nothing
+ * arrives on.  The wait gives up and records GT_ERR_TIMEOUT, which the next gt_device_status returns;
+ * the context stays usable.                                                                   */
+int gt_selftest_bounded_wait(gt_ctx* ctx, int64_t limit_cycles);
+
 /* Number of kernels this library has launched on behalf of `ctx` since gt_init. */
 int gt_launch_count(gt_ctx* ctx, int64_t* count);
 

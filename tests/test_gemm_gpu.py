@@ -280,6 +280,18 @@ def test_triangular_hints_trim_work_not_results(gt):
 
 # ---- error behaviour --------------------------------------------------------------------------
 
+def test_bounded_wait_gives_up_and_the_context_survives(gt):
+    """A wait that can never be satisfied (a barrier nothing arrives on) runs into its limit, the
+    kernel returns, the status word reports the timeout once, and the next GEMM is correct."""
+    lib = gt.load_library()
+    gt.check(lib.gt_selftest_bounded_wait(gt.context(), 2_000_000), "gt_selftest_bounded_wait")      # about 1 ms
+    with pytest.raises(RuntimeError, match="bounded device-side wait"):
+        gt.device_status()
+    assert gt.device_status() == 0                                  # the word was cleared by the read
+    a, b, _ = U.make_operands("NN", 256, 256, 256, seed=2)
+    assert O.rel_frobenius(U.run_gemm("NN", a, b), O.gemm(a, b, "NN")) <= U.TOL["tf32"]
+
+
 def test_invalid_arguments_return_status_not_crash(gt):
     from gradtuity_b200 import gemm as G
 
