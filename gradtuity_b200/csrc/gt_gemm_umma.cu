@@ -58,6 +58,7 @@ struct UmmaParams {
   int epilogue, accumulate, vec_ok;
   int flags;                             // GT_GEMM_* flags of gt_gemm_batched_ex
   int c_tma;                             // C is written by TMA store / reduce-add through shared memory
+  int a_onebox, b_onebox;                // MN-major operand described as (32, K, MN/32, b0, b1): one TMA box per stage
   float alpha;
   int* status;
 };
@@ -106,6 +107,15 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
       : "memory");
 }
 
@@ -445,20 +455,30 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           if (A_GEN) {
             // A arrives through the cp.async warps
           } else if (A_MN) {
+            if (p.a_onebox) {
+              tma_load_5d(sa, &map_a, full, 0, k0, m0 >> 5, i0, i1);
+              if (X3) tma_load_5d(sa + C::A_BYTES, &map_a_lo, full, 0, k0, m0 >> 5, i0, i1);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 32; ++j) {
-              tma_load_4d(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
-              if (X3) tma_load_4d(sa + C::A_BYTES + j * 4096, &map_a_lo, full, m0 + 32 * j, k0, i0, i1);
+              for (int j = 0; j < BM / 32; ++j) {
+                tma_load_4d(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
+                if (X3) tma_load_4d(sa + C::A_BYTES + j * 4096, &map_a_lo, full, m0 + 32 * j, k0, i0, i1);
+              }
             }
           } else {
             tma_load_4d(sa, &map_a, full, k0, m0, i0, i1);
             if (X3) tma_load_4d(sa + C::A_BYTES, &map_a_lo, full, k0, m0, i0, i1);
           }
           if (B_MN) {
+            if (p.b_onebox) {
+              tma_load_5d(sb, &map_b, full, 0, k0, n0 >> 5, i0, i1);
+              if (X3) tma_load_5d(sb + C::B_BYTES, &map_b_lo, full, 0, k0, n0 >> 5, i0, i1);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 32; ++j) {
-              tma_load_4d(sb + j * 4096, &map_b, full, n0 + 32 * j, k0, i0, i1);
-              if (X3) tma_load_4d(sb + C::B_BYTES + j * 4096, &map_b_lo, full, n0 + 32 * j, k0, i0, i1);
+              for (int j = 0; j < BN / 32; ++j) {
+                tma_load_4d(sb + j * 4096, &map_b, full, n0 + 32 * j, k0, i0, i1);
+                if (X3) tma_load_4d(sb + C::B_BYTES + j * 4096, &map_b_lo, full, n0 + 32 * j, k0, i0, i1);
+              }
             }
           } else {
             tma_load_4d(sb, &map_b, full, k0, n0, i0, i1);
@@ -773,14 +793,20 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
           const uint32_t sb = sa + A_BYTES;
           const int k0 = kb * BK;
           if (A_MN) {
+            if (p.a_onebox) tma_load_5d(sa, &map_a, full, 0, k0, m0 >> 5, i0, i1);
+            else {
 #pragma unroll
-            for (int j = 0; j < TM / 32; ++j) tma_load_4d(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
+              for (int j = 0; j < TM / 32; ++j) tma_load_4d(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
+            }
           } else {
             tma_load_4d(sa, &map_a, full, k0, m0, i0, i1);                  // one 32 x 256 box
           }
           if (B_MN) {
+            if (p.b_onebox) tma_load_5d(sb, &map_b, full, 0, k0, n0 >> 5, i0, i1);
+            else {
 #pragma unroll
-            for (int j = 0; j < TN / 32; ++j) tma_load_4d(sb + j * 4096, &map_b, full, n0 + 32 * j, k0, i0, i1);
+              for (int j = 0; j < TN / 32; ++j) tma_load_4d(sb + j * 4096, &map_b, full, n0 + 32 * j, k0, i0, i1);
+            }
           } else {
             tma_load_4d(sb, &map_b, full, k0, n0, i0, i1);
           }
@@ -987,6 +1013,25 @@ int encode_map(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int box_cols
   return GT_OK;
 }
 
+// An MN-major operand (stored (K, MN), MN contiguous, MN a multiple of 32) described as a 5-D tensor
+// (32, K, MN/32, batch0, batch1) with strides (4, ld*4, 128, ...) bytes: ONE box of (32, 32, chunks)
+// then fills the whole stage in the layout the MMA descriptors expect (chunk-major, 4 KB per chunk),
+// instead of `chunks` separate 32 x 32 boxes.  Returns false if the driver refuses the map.
+bool encode_map_mn5(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int chunks, long long batch0, long long batch1, bool plain_f32 = false) {
+  cuuint64_t dims[5] = {32, (cuuint64_t)v.rows, (cuuint64_t)(v.cols / 32), (cuuint64_t)batch0, (cuuint64_t)batch1};
+  const cuuint64_t slice = (cuuint64_t)v.rows * (cuuint64_t)v.ld * 4ull;
+  cuuint64_t strides[4] = {(cuuint64_t)v.ld * 4ull, 128ull,
+                           batch0 > 1 ? (cuuint64_t)v.s0 * 4ull : slice,
+                           batch1 > 1 ? (cuuint64_t)v.s1 * 4ull : slice * (cuuint64_t)batch0};
+  cuuint32_t box[5] = {32, 32, (cuuint32_t)chunks, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = ctx->encode_tiled(map, (ctx->tma_round && !plain_f32) ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                 5, (void*)v.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 template <int BN, bool A_MN, bool B_MN, bool X3, bool A_GEN>
 int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[5], const UmmaParams& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN, X3>;
@@ -1124,12 +1169,18 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   const int a_box_c = 32, a_box_r = a_mn ? 32 : tile_m;
   const int b_box_c = 32, b_box_r = b_mn ? 32 : bn;
   int rc;
-  if ((rc = encode_map(ctx, &maps[1], vb, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
+  static const bool onebox_off = getenv("GRADTUITY_GEMM_NO_ONEBOX") != nullptr;
+  // one-box form for MN-major operands whose MN extent is a multiple of 32 (else a box would run past a row's end)
+  bool a_one = !onebox_off && a_mn && !a_gen && (va.cols % 32 == 0);
+  bool b_one = !onebox_off && b_mn && (vb.cols % 32 == 0);
+  if (a_one) a_one = encode_map_mn5(ctx, &maps[0], va, tile_m / 32, b0, b1) && (!x3 || encode_map_mn5(ctx, &maps[2], va_lo, tile_m / 32, b0, b1));
+  if (b_one) b_one = encode_map_mn5(ctx, &maps[1], vb, bn / 32, b0, b1) && (!x3 || encode_map_mn5(ctx, &maps[3], vb_lo, bn / 32, b0, b1));
+  if (!b_one && (rc = encode_map(ctx, &maps[1], vb, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
   if (a_gen) maps[0] = maps[1];               // unused by the kernel in this mode
-  else if ((rc = encode_map(ctx, &maps[0], va, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
+  else if (!a_one && (rc = encode_map(ctx, &maps[0], va, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
   if (x3) {
-    if ((rc = encode_map(ctx, &maps[2], va_lo, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
-    if ((rc = encode_map(ctx, &maps[3], vb_lo, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
+    if (!a_one && (rc = encode_map(ctx, &maps[2], va_lo, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
+    if (!b_one && (rc = encode_map(ctx, &maps[3], vb_lo, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
   } else {
     maps[2] = maps[0];
     maps[3] = maps[1];
@@ -1147,8 +1198,14 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   if (tiles > 0x7fffffffLL) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: %lld tiles out of range", tiles);
   p.group_m = use256 ? 8 : 16;
   // Split-K: when the output has far fewer tiles than the GPU has SMs and K is long (the dW
-  // GEMMs: 768 x 768 output, K = 8192 -> 18 tiles), several CTAs share a tile's K range; their
-  // partial sums go to the workspace and a second kernel adds them in a fixed order.
+  // GEMMs: 768 x 768 output, K = 8192 -> 18 tiles), several CTAs share a tile's K range.  Two ways
+  // to combine the partial sums:
+  //  * direct: every CTA adds its partial into C with the TMA reduce-add of the epilogue (C is
+  //    zeroed first unless the call is C += ...).  No workspace, no second kernel; the order of
+  //    the fp32 additions, and so the last bits of C, can differ from run to run.
+  //  * ordered: partials go to the workspace and a second kernel adds them in a fixed order.
+  //    Taken with GRADTUITY_GEMM_DETERMINISTIC=1, with a bias / activation epilogue, or when C
+  //    cannot be described to TMA.
   const int num_kb = (int)((g.K + BK - 1) / BK);
   int ksplit = 1;
   if (!x3 && g.epilogue != GT_EPI_CAUSAL && g.flags == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
@@ -1165,6 +1222,8 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   p.epilogue = g.epilogue; p.accumulate = g.accumulate;
   p.alpha = g.alpha;
   p.flags = g.flags;
+  p.a_onebox = a_one ? 1 : 0;
+  p.b_onebox = b_one ? 1 : 0;
   p.status = ctx->d_status;
   bool vec = (((uintptr_t)g.C & 15) == 0) && (g.ldc % 4 == 0) && (g.sC0 % 4 == 0) && (g.sC1 % 4 == 0);
   if (g.aux) vec = vec && (((uintptr_t)g.aux & 15) == 0);
@@ -1172,7 +1231,15 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   p.vec_ok = vec ? 1 : 0;
   const long long plane = nbatch * g.M * g.N;
   float* ws = nullptr;
-  if (ksplit > 1) {
+  static const bool deterministic = getenv("GRADTUITY_GEMM_DETERMINISTIC") != nullptr;
+  static const bool c_tma_off = getenv("GRADTUITY_GEMM_NO_TMA_STORE") != nullptr;
+  const bool c_dense = g.ldc == g.N && (g.batch0 == 1 || g.sC0 == g.M * g.N) && (g.batch1 == 1 || g.sC1 == g.M * g.N * g.batch0);
+  const bool splitk_direct = ksplit > 1 && !deterministic && !c_tma_off && g.epilogue == GT_EPI_NONE && !g.aux &&
+                             tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (g.accumulate || c_dense);
+  if (splitk_direct) {
+    if (!g.accumulate) GT_CUDA_OK(ctx, cudaMemsetAsync(g.C, 0, (size_t)plane * sizeof(float), stream));
+    p.accumulate = 1;
+  } else if (ksplit > 1) {
     int rc2 = gt_workspace_reserve(ctx, (size_t)(8192 + plane * ksplit) * sizeof(float));
     if (rc2 != GT_OK) return rc2;
     ws = (float*)ctx->workspace + 8192;           // the first 8192 floats belong to the reductions
@@ -1184,8 +1251,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   }
   // C through TMA (store, or reduce-add for C += ...) when its rows can be described; split-K partials
   // and unaligned outputs keep the direct / coalesced stores.
-  static const bool c_tma_off = getenv("GRADTUITY_GEMM_NO_TMA_STORE") != nullptr;
-  p.c_tma = (!c_tma_off && ksplit == 1 && tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1)) ? 1 : 0;
+  p.c_tma = (!c_tma_off && (ksplit == 1 || splitk_direct) && tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1)) ? 1 : 0;
   if (p.c_tma) {
     OperandView vc = {g.C, g.M, g.N, g.ldc, g.sC0, g.sC1};
     if ((rc = encode_map(ctx, &maps[4], vc, 32, 32, b0, b1, false, /*plain_f32=*/true)) != GT_OK) return rc;
@@ -1222,7 +1288,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   else if (bn == 128) { GT_DISPATCH(128); }
   else { GT_DISPATCH(64); }
 #undef GT_DISPATCH
-  if (rc != GT_OK || ksplit == 1) return rc;
+  if (rc != GT_OK || ksplit == 1 || splitk_direct) return rc;
   const int rvec = (vec && g.N % 4 == 0) ? 1 : 0;      // `vec`: C, aux and bias 16-byte aligned with strides that are multiples of 4
   long long blocks = ((rvec ? plane / 4 : plane) + 255) / 256;
   if (blocks > (long long)ctx->sm_count * 8) blocks = (long long)ctx->sm_count * 8;

@@ -435,16 +435,37 @@ __global__ void __launch_bounds__(256) embedding_scatter_add_kernel(float* __res
 // Per row: lse = log sum exp(logits), loss_row = lse - logits[target].  One pass over the row
 // (online max / sum).  The per-row losses and lse values are kept; the mean is taken by a
 // deterministic reduction, and the backward reuses lse.
-__global__ void __launch_bounds__(512) cross_entropy_fwd_kernel(const float* __restrict__ logits, const float* __restrict__ targets,
+// One block per row.  VEC: the row starts on a 16-byte boundary (pitch a multiple of 4 floats), so the
+// body is read as float4 with a scalar tail; the running (max, sum) pair is rescaled once per vector.
+template <bool VEC>
+__global__ void __launch_bounds__(512) cross_entropy_fwd_kernel(const float* __restrict__ logits, long long ld,
+                                                                const float* __restrict__ targets,
                                                                 float* __restrict__ row_loss, float* __restrict__ row_lse,
                                                                 int C, int* status) {
   __shared__ float red[33];
   const long long row = blockIdx.x;
-  const float* xr = logits + row * C;
+  const float* xr = logits + row * ld;
   float m = -INFINITY, s = 0.0f;
-  for (int j = threadIdx.x; j < C; j += blockDim.x) {
-    const float v = xr[j];
-    if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+  if (VEC) {
+    const float4* x4 = reinterpret_cast<const float4*>(xr);
+    const int n4 = C >> 2;
+#pragma unroll 4
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+      const float4 v = x4[j];
+      const float vm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+      if (vm > m) { s *= __expf(m - vm); m = vm; }
+      s += (__expf(v.x - m) + __expf(v.y - m)) + (__expf(v.z - m) + __expf(v.w - m));
+    }
+    const int j = (n4 << 2) + threadIdx.x;
+    if (j < C) {
+      const float v = xr[j];
+      if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+    }
+  } else {
+    for (int j = threadIdx.x; j < C; j += blockDim.x) {
+      const float v = xr[j];
+      if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+    }
   }
   const float gm = block_max_all(m, red);
   s = (m == -INFINITY) ? 0.0f : s * __expf(m - gm);
@@ -458,16 +479,37 @@ __global__ void __launch_bounds__(512) cross_entropy_fwd_kernel(const float* __r
   }
 }
 // dlogits (+)= scale * (softmax - onehot)
-__global__ void __launch_bounds__(512) cross_entropy_bwd_kernel(float* __restrict__ dlogits, const float* __restrict__ logits,
+template <bool VEC>
+__global__ void __launch_bounds__(512) cross_entropy_bwd_kernel(float* __restrict__ dlogits, long long ld_d,
+                                                                const float* __restrict__ logits, long long ld_x,
                                                                 const float* __restrict__ targets, const float* __restrict__ row_lse,
                                                                 const float* __restrict__ upstream, float scale, int C, int accumulate) {
   const long long row = blockIdx.x;
-  const float* xr = logits + row * C;
-  float* dr = dlogits + row * C;
+  const float* xr = logits + row * ld_x;
+  float* dr = dlogits + row * ld_d;
   const float lse = row_lse[row];
   const int t = (int)targets[row];
   const float sc = scale * (upstream ? *upstream : 1.0f);
-  for (int j = threadIdx.x; j < C; j += blockDim.x) {
+  int j0 = 0;
+  if (VEC) {
+    const float4* x4 = reinterpret_cast<const float4*>(xr);
+    float4* d4 = reinterpret_cast<float4*>(dr);
+    const int n4 = C >> 2;
+#pragma unroll 4
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+      const float4 x = x4[j];
+      float4 v;
+      v.x = sc * __expf(x.x - lse); v.y = sc * __expf(x.y - lse); v.z = sc * __expf(x.z - lse); v.w = sc * __expf(x.w - lse);
+      if ((t >> 2) == j) {
+        const int k = t & 3;
+        if (k == 0) v.x -= sc; else if (k == 1) v.y -= sc; else if (k == 2) v.z -= sc; else v.w -= sc;
+      }
+      if (accumulate) { const float4 o = d4[j]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+      d4[j] = v;
+    }
+    j0 = n4 << 2;
+  }
+  for (int j = j0 + threadIdx.x; j < C; j += blockDim.x) {
     const float v = sc * (__expf(xr[j] - lse) - (j == t ? 1.0f : 0.0f));
     dr[j] = accumulate ? dr[j] + v : v;
   }
@@ -664,9 +706,13 @@ extern "C" int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, 
 }
 
 extern "C" int gt_cross_entropy(gt_ctx* ctx, float* loss, float* row_loss, float* row_lse, const float* logits,
-                                const float* targets, int64_t B, int64_t C, int mean) {
-  if (!ctx || !loss || !row_loss || !row_lse || !logits || !targets || B <= 0 || C <= 0 || B > 0x7fffffff || C > 0x7fffffff) return GT_ERR_INVALID_ARG;
-  cross_entropy_fwd_kernel<<<(unsigned)B, 512, 0, ctx->stream>>>(logits, targets, row_loss, row_lse, (int)C, ctx->d_status);
+                                int64_t ld_logits, const float* targets, int64_t B, int64_t C, int mean) {
+  if (!ctx || !loss || !row_loss || !row_lse || !logits || !targets || B <= 0 || C <= 0 || B > 0x7fffffff || C > 0x7fffffff ||
+      ld_logits < C) return GT_ERR_INVALID_ARG;
+  if ((((uintptr_t)logits & 15) == 0) && ld_logits % 4 == 0)
+    cross_entropy_fwd_kernel<true><<<(unsigned)B, 512, 0, ctx->stream>>>(logits, ld_logits, targets, row_loss, row_lse, (int)C, ctx->d_status);
+  else
+    cross_entropy_fwd_kernel<false><<<(unsigned)B, 512, 0, ctx->stream>>>(logits, ld_logits, targets, row_loss, row_lse, (int)C, ctx->d_status);
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
   int rc = gt_sum_all(ctx, loss, row_loss, B, 0);
@@ -675,11 +721,15 @@ extern "C" int gt_cross_entropy(gt_ctx* ctx, float* loss, float* row_loss, float
   return GT_OK;
 }
 
-extern "C" int gt_cross_entropy_backward(gt_ctx* ctx, float* dlogits, const float* logits, const float* targets,
-                                         const float* row_lse, const float* upstream, float scale, int64_t B, int64_t C,
-                                         int accumulate) {
-  if (!ctx || !dlogits || !logits || !targets || !row_lse || B <= 0 || C <= 0 || B > 0x7fffffff || C > 0x7fffffff) return GT_ERR_INVALID_ARG;
-  cross_entropy_bwd_kernel<<<(unsigned)B, 512, 0, ctx->stream>>>(dlogits, logits, targets, row_lse, upstream, scale, (int)C, accumulate);
+extern "C" int gt_cross_entropy_backward(gt_ctx* ctx, float* dlogits, int64_t ld_dlogits, const float* logits,
+                                         int64_t ld_logits, const float* targets, const float* row_lse,
+                                         const float* upstream, float scale, int64_t B, int64_t C, int accumulate) {
+  if (!ctx || !dlogits || !logits || !targets || !row_lse || B <= 0 || C <= 0 || B > 0x7fffffff || C > 0x7fffffff ||
+      ld_logits < C || ld_dlogits < C) return GT_ERR_INVALID_ARG;
+  if ((((uintptr_t)logits & 15) == 0) && ld_logits % 4 == 0 && (((uintptr_t)dlogits & 15) == 0) && ld_dlogits % 4 == 0)
+    cross_entropy_bwd_kernel<true><<<(unsigned)B, 512, 0, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_lse, upstream, scale, (int)C, accumulate);
+  else
+    cross_entropy_bwd_kernel<false><<<(unsigned)B, 512, 0, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_lse, upstream, scale, (int)C, accumulate);
   GT_LAUNCH_CHECK(ctx, 1);
 }
 

@@ -130,9 +130,26 @@ def pass_grad(t: "Tensor", g: "Tensor") -> None:
     reads it afterwards, and each backward hands its g to at most one parent this way.  Leaves
     (parameters) always get their own buffer."""
     if t.grad is None and t._backward is not None and g.numel == t.numel:
-        t.grad = Tensor._from_ptr(g.ptr, t.shape, owns_memory=False, base=g._st)
+        if g._pitch is not None and t.shape[-1] == g.shape[-1]:
+            # a padded-row gradient keeps its pitch on the way up (the view between the LM head and the loss)
+            t.grad = Tensor._wrap(Storage(g._st.ptr, g._st.nbytes, owns=False, base=g._st), t.shape)
+            t.grad._pitch = g._pitch
+        else:
+            t.grad = Tensor._from_ptr(g.ptr, t.shape, owns_memory=False, base=g._st)
     else:
         accum_grad(t, g)
+
+
+def empty_padded_tensor(shape: tuple[int, ...], pitch: int) -> "Tensor":
+    """A tensor whose rows (last dimension) sit `pitch` floats apart in memory.  Only the ops that
+    say so read such a tensor in place (linear_tied, cross_entropy, view with the last dimension
+    kept); any other access goes through `.ptr`, which first packs the rows."""
+    _validate_shape(shape)
+    rows = prod(shape) // shape[-1]
+    t = Tensor._wrap(alloc_storage(rows * pitch * F32), shape)
+    if pitch != shape[-1]:
+        t._pitch = pitch
+    return t
 
 
 def grad_target(t: "Tensor") -> tuple[int, bool]:
@@ -148,6 +165,9 @@ def grad_target(t: "Tensor") -> tuple[int, bool]:
 
 class Tensor:
     """A float32, contiguous, row-major tensor on the GPU with autograd support."""
+
+    # Row pitch in floats when the rows of the last dimension are padded in memory (None: packed).
+    _pitch = None
 
     def __init__(self, data, shape: tuple[int, ...] | None = None, requires_grad: bool = False, name: str = "") -> None:
         if shape is None:
@@ -247,7 +267,22 @@ class Tensor:
 
     @property
     def ptr(self) -> int:
+        if self._pitch is not None:
+            self._pack_rows()
         return self._st.ptr
+
+    def _pack_rows(self) -> None:
+        """Replace a padded-row buffer by a packed copy (for every op that expects contiguous data)."""
+        cols = self._shape[-1]
+        rows = self.numel // cols
+        packed = alloc_storage(rows * cols * F32)
+        _call("gt_repack_rows", _vp(packed.ptr), cols, _vp(self._st.ptr), self._pitch, rows, cols)
+        self._st = packed
+        self._pitch = None
+
+    def _rows(self) -> tuple[int, int]:
+        """(pointer, row pitch in floats) without packing."""
+        return self._st.ptr, (self._pitch if self._pitch is not None else self._shape[-1])
 
     @property
     def shape(self) -> tuple[int, ...]:
@@ -333,7 +368,9 @@ class Tensor:
 
     def detach(self) -> "Tensor":
         shared = Storage(self._st.ptr, self._st.nbytes, owns=False, base=self._st)
-        return Tensor._wrap(shared, self._shape, requires_grad=False, name=f"{self.name}_detached" if self.name else "")
+        out = Tensor._wrap(shared, self._shape, requires_grad=False, name=f"{self.name}_detached" if self.name else "")
+        out._pitch = self._pitch
+        return out
 
     def view(self, new_shape) -> "Tensor":
         """Same storage, different shape; one dimension may be -1/None (gradtuity/tensor.py:465-524)."""
@@ -356,7 +393,11 @@ class Tensor:
             dims[infer] = inferred
         elif product != self.numel:
             raise ValueError(f"view() shape {tuple(new_shape)} has {product} elements, but tensor has {self.numel} elements")
-        out = Tensor._from_ptr(self.ptr, tuple(dims), owns_memory=False, requires_grad=False, base=self._st)
+        if self._pitch is not None and dims[-1] == self._shape[-1]:
+            out = Tensor._wrap(Storage(self._st.ptr, self._st.nbytes, owns=False, base=self._st), tuple(dims))
+            out._pitch = self._pitch
+        else:
+            out = Tensor._from_ptr(self.ptr, tuple(dims), owns_memory=False, requires_grad=False, base=self._st)
         src = self
 
         def _backward(out_grad: "Tensor") -> None:
@@ -533,13 +574,21 @@ class Tensor:
             )
         M, E = self._shape
         V, _ = weight._shape
-        out = empty_tensor((M, V))
-        _gemm.gemm(LAYOUT_NT, M, V, E, self.ptr, E, weight.ptr, E, out.ptr, V)
+        if V % 4 != 0 and M * V >= (1 << 22):
+            # Large logits with an odd vocabulary (50257): rows padded to a 128-byte multiple, so the
+            # GEMM stores them through TMA, the loss kernels use vector loads and the two backward GEMMs
+            # read dlogits through TMA.  cross_entropy and view() keep the padding; anything else packs.
+            out = empty_padded_tensor((M, V), (V + 31) // 32 * 32)
+        else:
+            out = empty_tensor((M, V))
+        out_ptr, out_ld = out._rows()
+        _gemm.gemm(LAYOUT_NT, M, V, E, self.ptr, E, weight.ptr, E, out_ptr, out_ld)
         x = self
 
         def _backward(g: "Tensor") -> None:
-            g_ptr, g_ld, tmp = g.ptr, V, None
-            if V % 4 != 0 and M * V >= (1 << 22) and (x.requires_grad and weight.requires_grad):
+            g_ptr, g_ld = g._rows()
+            tmp = None
+            if g_ld % 4 != 0 and M * V >= (1 << 22) and (x.requires_grad and weight.requires_grad):
                 # dL is read by two large GEMMs and its rows are not 16-byte aligned (odd vocabulary):
                 # one copy to a padded pitch lets both take the TMA path instead of 4-byte copies.
                 g_ld = (V + 3) // 4 * 4
@@ -746,7 +795,8 @@ class Tensor:
         out = empty_tensor((1,))
         row_loss = empty_tensor((Bn,))
         row_lse = empty_tensor((Bn,))
-        _call("gt_cross_entropy", _vp(out.ptr), _vp(row_loss.ptr), _vp(row_lse.ptr), _vp(self.ptr), _vp(targets.ptr), Bn, C,
+        x_ptr, x_ld = self._rows()
+        _call("gt_cross_entropy", _vp(out.ptr), _vp(row_loss.ptr), _vp(row_lse.ptr), _vp(x_ptr), x_ld, _vp(targets.ptr), Bn, C,
               1 if reduction == "mean" else 0)
         logits = self
 
@@ -754,8 +804,11 @@ class Tensor:
             if logits.requires_grad:
                 fresh = logits.grad is None
                 if fresh:
-                    logits.grad = empty_tensor(logits.shape)      # written, not accumulated: no memset
-                _call("gt_cross_entropy_backward", _vp(logits.grad.ptr), _vp(logits.ptr), _vp(targets.ptr), _vp(row_lse.ptr),
+                    # written, not accumulated: no memset; padded like the logits so the LM-head GEMMs read it by TMA
+                    logits.grad = empty_padded_tensor(logits.shape, logits._rows()[1])
+                d_ptr, d_ld = logits.grad._rows()
+                lx_ptr, lx_ld = logits._rows()
+                _call("gt_cross_entropy_backward", _vp(d_ptr), d_ld, _vp(lx_ptr), lx_ld, _vp(targets.ptr), _vp(row_lse.ptr),
                       _vp(g.ptr), (1.0 / Bn) if reduction == "mean" else 1.0, Bn, C, 0 if fresh else 1)
 
         out._set_graph(parents=(self, targets), backward_fn=_backward)

@@ -246,11 +246,14 @@ int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, float* dbeta, c
                           int dx_accumulate);
 int gt_embedding(gt_ctx* ctx, float* out, const float* W, const float* idx, int64_t n, int64_t D, int64_t V);
 int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V);
+/* Rows of C logits may be padded: ld_logits / ld_dlogits are the row pitches in elements (>= C).  The tied
+ * LM head writes its 50257-wide logits at a 16-byte aligned pitch so that both kernels use vector loads
+ * and the GEMMs that read dlogits take the TMA path. */
 int gt_cross_entropy(gt_ctx* ctx, float* loss, float* row_loss, float* row_lse, const float* logits,
-                     const float* targets, int64_t B, int64_t C, int mean);
-int gt_cross_entropy_backward(gt_ctx* ctx, float* dlogits, const float* logits, const float* targets,
-                              const float* row_lse, const float* upstream, float scale, int64_t B, int64_t C,
-                              int accumulate);
+                     int64_t ld_logits, const float* targets, int64_t B, int64_t C, int mean);
+int gt_cross_entropy_backward(gt_ctx* ctx, float* dlogits, int64_t ld_dlogits, const float* logits,
+                              int64_t ld_logits, const float* targets, const float* row_lse,
+                              const float* upstream, float scale, int64_t B, int64_t C, int accumulate);
 int gt_adamw(gt_ctx* ctx, float* p, const float* g, float* m, float* v, int64_t n, float lr, float beta1,
              float beta2, float eps, float weight_decay, float bc1, float bc2, const float* grad_scale);
 int gt_sumsq(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate);

@@ -172,6 +172,38 @@ def test_linear_tied_large_odd_vocabulary_repack_path(T):
     assert O.rel_frobenius(tw.grad.numpy(), ref["dw"]) <= 1e-3
 
 
+def test_linear_tied_padded_logits_through_view_and_cross_entropy(T):
+    """Large logits with an odd vocabulary are stored with padded rows; view() and cross_entropy read
+    and write them in place (no packed copy), numpy() packs.  Loss, dX and dW against float64."""
+    rng = np.random.default_rng(5)
+    Bn, S, V, E = 2, 1024, 2051, 64
+    M = Bn * S
+    x = (rng.standard_normal((M, E)) / 4).astype(np.float32)
+    w = (rng.standard_normal((V, E)) / 4).astype(np.float32)
+    tgt = rng.integers(0, V, M)
+    tx, tw = T.from_numpy(x, requires_grad=True), T.from_numpy(w, requires_grad=True)
+    logits = tx.linear_tied(tw).view((Bn, S, V))
+    assert logits._pitch == 2080 and logits.shape == (Bn, S, V)
+    flat = logits.view((M, V))
+    assert flat._pitch == 2080
+    loss = flat.cross_entropy(T.from_numpy(tgt.astype(np.float32)), reduction="mean")
+    loss.backward()
+    z = x.astype(np.float64) @ w.astype(np.float64).T
+    zmax = z.max(axis=1, keepdims=True)
+    lse = zmax[:, 0] + np.log(np.exp(z - zmax).sum(axis=1))
+    ref_loss = float(np.mean(lse - z[np.arange(M), tgt]))
+    dz = np.exp(z - lse[:, None])
+    dz[np.arange(M), tgt] -= 1.0
+    dz /= M
+    assert abs(loss.item() - ref_loss) <= 1e-4 * abs(ref_loss)
+    assert O.rel_frobenius(tx.grad.numpy(), dz @ w.astype(np.float64)) <= 1e-3
+    assert O.rel_frobenius(tw.grad.numpy(), dz.T @ x.astype(np.float64)) <= 1e-3
+    # reading the logits packs the rows; the values are the GEMM's
+    out = logits.numpy()
+    assert out.shape == (Bn, S, V) and logits._pitch is None
+    assert O.rel_frobenius(out.reshape(M, V), z) <= 1e-3
+
+
 def test_config0_linear_784_128(T):
     """Config 0: Linear(784 -> 128), batch 128, X ~ U[0,1), W and b ~ U(-1/28, 1/28), dY ~ N(0,1),
     seed 0; y, dX, dW, db against the float64 oracle."""
