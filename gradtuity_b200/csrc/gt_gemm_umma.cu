@@ -301,11 +301,13 @@ __device__ __forceinline__ bool prefetch_c(const UmmaParams& p, bool enabled, in
 // it applies the fused epilogue in registers, writes its 128-byte row into the staging tile in the
 // 128-byte-swizzle order, and lane 0 hands the tile to the TMA unit, which writes whole rows,
 // clips at M and N, and for `C += ...` performs the addition in L2 (no read of C by the SM).
-// Each epilogue warp has one staging tile; the other warps' stores hide the wait for it.  With an
-// aux output the pre-activation is stored directly from registers.
-__device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
-                                                   int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                   uint8_t* tile, uint32_t tile_u32) {
+// Each epilogue warp has one staging tile (a second tile per warp, or requesting the next chunk's
+// accumulator columns early, measured no faster: the warps are bound by the instructions they issue,
+// not by these latencies).  With an aux output the pre-activation is stored directly from registers.
+// This is the general form: bias, aux and the output may end inside the chunk.
+__device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
+                                                       int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
+                                                       uint8_t* tile, uint32_t tile_u32) {
   const int row = row0 + lane;
   const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
   if (lane == 0) tma_store_wait_read<0>();          // the previous store of this warp has finished reading the tile
@@ -347,6 +349,81 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CU
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
   if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, p.accumulate != 0);
+}
+
+// The same for a chunk that lies wholly inside N, with the epilogue kind fixed at compile time: no
+// per-element branches, a third of the instructions of the general form.  The epilogue warps are
+// instruction-bound on short-K problems (the score products, the 768-deep Linear layers), so this
+// is what their throughput depends on.
+template <int EPI, bool AUX>
+__device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
+                                                        int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
+                                                        uint8_t* tile, uint32_t tile_u32) {
+  constexpr bool HAS_BIAS = EPI >= GT_EPI_BIAS && EPI <= GT_EPI_BIAS_GELU;
+  const int row = row0 + lane;
+  const float alpha = p.alpha;
+  const float4* bias4 = reinterpret_cast<const float4*>(p.bias + nb);
+  float4* aux4 = reinterpret_cast<float4*>(p.aux + row_off + nb);
+  uint8_t* my_row = tile + lane * 128;
+  const int sw = lane & 7;
+  if (lane == 0) tma_store_wait_read<0>();
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float4 x = make_float4(alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2], alpha * v[4 * j + 3]);
+    if (HAS_BIAS) {
+      const float4 b = bias4[j];
+      x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+    }
+    if (AUX) { if (row_ok) aux4[j] = x; }
+    if (EPI == GT_EPI_BIAS_RELU) {
+      x.x = fmaxf(x.x, 0.0f); x.y = fmaxf(x.y, 0.0f); x.z = fmaxf(x.z, 0.0f); x.w = fmaxf(x.w, 0.0f);
+    } else if (EPI == GT_EPI_BIAS_GELU) {
+      x.x = gt_gelu_tanh(x.x); x.y = gt_gelu_tanh(x.y); x.z = gt_gelu_tanh(x.z); x.w = gt_gelu_tanh(x.w);
+    } else if (EPI == GT_EPI_CAUSAL) {
+      const int col = nb + 4 * j;
+      if (col > row) x.x = GT_CAUSAL_MASK_VALUE;
+      if (col + 1 > row) x.y = GT_CAUSAL_MASK_VALUE;
+      if (col + 2 > row) x.z = GT_CAUSAL_MASK_VALUE;
+      if (col + 3 > row) x.w = GT_CAUSAL_MASK_VALUE;
+    }
+    *reinterpret_cast<float4*>(my_row + ((j ^ sw) << 4)) = x;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncwarp();
+  if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, p.accumulate != 0);
+}
+
+__device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
+                                                   int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
+                                                   uint8_t* tile, uint32_t tile_u32) {
+#define GT_EPI_FAST(E, X) epilogue_chunk_tma_fast<E, X>(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32)
+  if (nb + 32 <= p.N) {                              // warp-uniform
+    switch (p.epilogue) {
+      case GT_EPI_NONE:
+        if (!p.aux) { GT_EPI_FAST(GT_EPI_NONE, false); return; }
+        break;
+      case GT_EPI_BIAS:
+        if (p.aux) GT_EPI_FAST(GT_EPI_BIAS, true); else GT_EPI_FAST(GT_EPI_BIAS, false);
+        return;
+      case GT_EPI_BIAS_RELU:
+        if (p.aux) GT_EPI_FAST(GT_EPI_BIAS_RELU, true); else GT_EPI_FAST(GT_EPI_BIAS_RELU, false);
+        return;
+      case GT_EPI_BIAS_GELU:
+        if (p.aux) GT_EPI_FAST(GT_EPI_BIAS_GELU, true); else GT_EPI_FAST(GT_EPI_BIAS_GELU, false);
+        return;
+      case GT_EPI_CAUSAL:
+        if (!p.aux) {
+          // a 32 x 32 block whose last column is not right of its first row holds no masked element
+          if (nb + 31 > row0) GT_EPI_FAST(GT_EPI_CAUSAL, false); else GT_EPI_FAST(GT_EPI_NONE, false);
+          return;
+        }
+        break;
+      default: break;
+    }
+  }
+#undef GT_EPI_FAST
+  epilogue_chunk_tma_any(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32);
 }
 
 // Same epilogue for outputs whose rows are not 16-byte aligned (odd leading dimension, e.g. the
