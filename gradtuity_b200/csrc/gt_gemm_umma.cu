@@ -76,13 +76,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// The suspend-time hint lets the hardware park the waiting thread until the phase completes (or the
+// hint expires) instead of re-issuing the test: a spinning producer / MMA lane otherwise competes
+// for issue slots with the epilogue warps of its scheduler.
+constexpr uint32_t TRY_WAIT_SUSPEND_NS = 100000u;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(TRY_WAIT_SUSPEND_NS) : "memory");
   return ok != 0;
 }
 
@@ -1194,7 +1198,15 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   const long long tiles256 = ((g.M + 255) / 256) * ((g.N + 255) / 256) * nbatch;
   static const bool t256_off = getenv("GRADTUITY_GEMM_NO_T256") != nullptr;
   static const long long t256_min_k = getenv("GRADTUITY_GEMM_T256_MIN_K") ? atoll(getenv("GRADTUITY_GEMM_T256_MIN_K")) : 2048;
-  const bool use256 = !t256_off && g.flags == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && g.K >= t256_min_k && tiles256 >= ctx->sm_count &&
+  static const int t256_min_tiles = getenv("GRADTUITY_GEMM_T256_MIN_TILES") ? atoi(getenv("GRADTUITY_GEMM_T256_MIN_TILES")) : 0;   // tuning aid
+  // Measured: with K >= 2048 the big tiles win once they keep 60 % of the SMs busy ((8192, 768, 3072): 96
+  // tiles, +5 %; 2048^3: 64 tiles, half the speed); with a shorter K their epilogue, which does not overlap
+  // the next main loop, only pays off on outputs of many waves without a second (aux) output (the
+  // 8192 x 50272 x 768 logits: +5 %).
+  const bool big_enough = t256_min_tiles > 0 ? (g.K >= t256_min_k && tiles256 >= t256_min_tiles)
+                                             : ((g.K >= t256_min_k && tiles256 * 5 >= (long long)ctx->sm_count * 3) ||
+                                                (g.K >= 512 && tiles256 >= (long long)ctx->sm_count * 8 && !g.aux));
+  const bool use256 = !t256_off && g.flags == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && big_enough &&
                       tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (!g.aux || ((uintptr_t)g.aux & 15) == 0) &&
                       (!g.bias || ((uintptr_t)g.bias & 15) == 0);
   static const int force_bn = getenv("GRADTUITY_GEMM_FORCE_BN") ? atoi(getenv("GRADTUITY_GEMM_FORCE_BN")) : 0;   // tuning aid

@@ -287,6 +287,40 @@ __global__ void __launch_bounds__(256) layernorm_fwd_kernel(const float* __restr
   for (int j = threadIdx.x; j < H; j += blockDim.x) yr[j] = (xr[j] - mean) * rstd * gamma[j] + beta[j];
 }
 
+// Warp-per-row form for H = 128 * KV (KV <= 8) and 16-byte aligned rows: the row is read once into
+// registers as float4, mean and variance come from two warp reductions, no block-wide barrier.
+template <int KV>
+__global__ void __launch_bounds__(256) layernorm_fwd_warp_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
+                                                                 const float* __restrict__ beta, float* __restrict__ y,
+                                                                 float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                                 long long N, float eps) {
+  constexpr int H = 128 * KV;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long warps_total = (long long)gridDim.x * 8;
+  for (long long row = (long long)blockIdx.x * 8 + warp; row < N; row += warps_total) {
+    const float4* xr = reinterpret_cast<const float4*>(x + row * H);
+    float4 v[KV];
+    float s = 0.0f;
+#pragma unroll
+    for (int c = 0; c < KV; ++c) { v[c] = xr[c * 32 + lane]; s += (v[c].x + v[c].y) + (v[c].z + v[c].w); }
+    const float mean = warp_sum(s) / (float)H;
+    float q = 0.0f;
+#pragma unroll
+    for (int c = 0; c < KV; ++c) {
+      v[c].x -= mean; v[c].y -= mean; v[c].z -= mean; v[c].w -= mean;
+      q += (v[c].x * v[c].x + v[c].y * v[c].y) + (v[c].z * v[c].z + v[c].w * v[c].w);
+    }
+    const float rstd = rsqrtf(warp_sum(q) / (float)H + eps);
+    if (lane == 0) { mean_out[row] = mean; rstd_out[row] = rstd; }
+    float4* yr = reinterpret_cast<float4*>(y + row * H);
+#pragma unroll
+    for (int c = 0; c < KV; ++c) {
+      const float4 g = reinterpret_cast<const float4*>(gamma)[c * 32 + lane], b = reinterpret_cast<const float4*>(beta)[c * 32 + lane];
+      yr[c * 32 + lane] = make_float4(v[c].x * rstd * g.x + b.x, v[c].y * rstd * g.y + b.y, v[c].z * rstd * g.z + b.z, v[c].w * rstd * g.w + b.w);
+    }
+  }
+}
+
 // dx += rstd/H * (H*dxhat - sum(dxhat) - xhat*sum(dxhat*xhat)), dxhat = dy*gamma;
 // dgamma += sum_rows dy*xhat, dbeta += sum_rows dy.  Each block walks `rows_per_block` rows and
 // keeps its column partials in registers, so there is one atomic per column per block instead
@@ -667,6 +701,15 @@ extern "C" int gt_softmax_backward(gt_ctx* ctx, float* dx, const float* y, const
 extern "C" int gt_layernorm(gt_ctx* ctx, float* y, float* mean, float* rstd, const float* x, const float* gamma,
                             const float* beta, int64_t N, int64_t H, float eps) {
   if (!ctx || !y || !mean || !rstd || !x || !gamma || !beta || N <= 0 || H <= 0 || N > 0x7fffffff || H > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  const bool al = ((((uintptr_t)x | (uintptr_t)y | (uintptr_t)gamma | (uintptr_t)beta) & 15) == 0);
+  if (al && H % 128 == 0 && H / 128 <= 8) {
+    long long wb = (N + 7) / 8, cap = (long long)ctx->sm_count * 8;
+    const unsigned nb = (unsigned)(wb < cap ? wb : cap);
+#define GT_LNF_CASE(KV_) case KV_: layernorm_fwd_warp_kernel<KV_><<<nb, 256, 0, ctx->stream>>>(x, gamma, beta, y, mean, rstd, N, eps); break
+    switch ((int)(H / 128)) { GT_LNF_CASE(1); GT_LNF_CASE(2); GT_LNF_CASE(3); GT_LNF_CASE(4); GT_LNF_CASE(5); GT_LNF_CASE(6); GT_LNF_CASE(7); GT_LNF_CASE(8); }
+#undef GT_LNF_CASE
+    GT_LAUNCH_CHECK(ctx, 1);
+  }
   layernorm_fwd_kernel<<<(unsigned)N, 256, 0, ctx->stream>>>(x, gamma, beta, y, mean, rstd, (int)H, eps);
   GT_LAUNCH_CHECK(ctx, 1);
 }
@@ -678,9 +721,20 @@ extern "C" int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, floa
   if (H > 256 * LN_MAX_COLS_PER_THREAD) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "layernorm backward supports H <= %d, got %lld", 256 * LN_MAX_COLS_PER_THREAD, (long long)H);
   const bool al = ((((uintptr_t)dx | (uintptr_t)dy | (uintptr_t)x | (uintptr_t)gamma) & 15) == 0);
   if (al && H % 128 == 0 && H / 128 <= 8) {
-    long long wb = (N + 7) / 8, cap = (long long)ctx->sm_count * 4;
-    const unsigned nb = (unsigned)(wb < cap ? wb : cap);
-#define GT_LN_CASE(KV_) case KV_: layernorm_bwd_warp_kernel<KV_><<<nb, 256, 0, ctx->stream>>>(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, dx_accumulate); break
+    // One resident round of blocks (the kernel's registers allow one or two blocks per SM): every block
+    // pays the prologue and the dgamma / dbeta atomics once, and each warp walks several rows.
+    long long wb = (N + 7) / 8;
+    unsigned nb = 0;
+#define GT_LN_CASE(KV_) case KV_: { \
+      static int per_sm = 0; \
+      if (per_sm == 0) { \
+        int v = 0; \
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, layernorm_bwd_warp_kernel<KV_>, 256, 0) != cudaSuccess || v < 1) v = 1; \
+        per_sm = v; \
+      } \
+      const long long cap = (long long)ctx->sm_count * per_sm; \
+      nb = (unsigned)(wb < cap ? wb : cap); \
+      layernorm_bwd_warp_kernel<KV_><<<nb, 256, 0, ctx->stream>>>(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, dx_accumulate); } break
     switch ((int)(H / 128)) { GT_LN_CASE(1); GT_LN_CASE(2); GT_LN_CASE(3); GT_LN_CASE(4); GT_LN_CASE(5); GT_LN_CASE(6); GT_LN_CASE(7); GT_LN_CASE(8); }
 #undef GT_LN_CASE
     GT_LAUNCH_CHECK(ctx, 1);
