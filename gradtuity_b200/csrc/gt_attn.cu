@@ -1,0 +1,448 @@
+// Fused causal attention for sm_100a, head dimension 64, tf32 multiply / fp32 accumulate.
+//
+// The reference builds attention from separate launches (gradtuity/nn.py:511-554: three
+// transposes, bmm, scale_inplace, softmax_with_causal_mask, bmm) and keeps S, P, dP and dS, each
+// (B, H, T, T), in memory.  The kernels here compute the same quantities tile by tile in tensor
+// memory and shared memory:
+//
+//   gt_attn_fwd_kernel      O = softmax(scale * Q K^T + causal mask) V, row statistics (log-sum-exp)
+//                           saved; P is written out only on request.
+//   gt_attn_bwd_dq_kernel   per 128-query block: recomputes P from Q, K and the saved statistics,
+//                           dP = dO V^T, dS = scale * P (dP - delta), dQ = dS K; also writes
+//                           delta = rowsum(dO * O).
+//   gt_attn_bwd_dkv_kernel  per 128-key block: the transposed products S^T = K Q^T, dP^T = V dO^T,
+//                           dV = P^T dO, dK = dS^T Q.
+//
+// All three share one structure: a persistent CTA per SM walks (batch, head, block) items, heaviest
+// first; warp 0 issues TMA loads into a ring of 32 KB slots, lane 0 of warp 1 issues tcgen05.mma,
+// warps 2-9 (lane = row of the 128-row tile, two warps per tensor-memory lane quarter, each taking
+// every other 32-column chunk) do the softmax arithmetic between tensor memory and the shared-memory
+// tile that the next MMA reads as its A operand.  Q, K, V, dO are read in place from the
+// (B, T, H * 64) projection outputs; TMA rounds them to tf32.  The probabilities are rounded to tf32
+// (nearest) before they are written to shared memory, so the tensor core does not truncate them.
+//
+// Every wait is bounded (see mbar_wait): on a time-out the CTA raises the context's status word,
+// all roles leave their loops and tensor memory is released.
+
+#include <stdlib.h>
+
+#include "gt_internal.h"
+#include "gt_umma_common.cuh"
+
+namespace {
+
+constexpr int AT_D = 64;                        // head dimension
+constexpr int AT_TILE = 128;                    // queries per item, keys per tile
+constexpr int AT_THREADS = 320;                 // producer warp, MMA warp, 8 softmax warps
+constexpr int AT_SLOT_BYTES = 32768;            // one 128 x 64 fp32 operand tile
+constexpr int AT_SLOTS = 4;
+constexpr int AT_P_BYTES = 65536;               // 128 x 128 fp32 tile of P / dS (four 128-byte-swizzle atoms of 32 columns)
+constexpr int AT_SMEM_BYTES = AT_SLOT_BYTES /*Q*/ + AT_SLOTS * AT_SLOT_BYTES + AT_P_BYTES + 1024 + 512;
+constexpr float AT_LOG2E = 1.4426950408889634f;
+constexpr float AT_LN2 = 0.6931471805599453f;
+
+struct AttnParams {
+  int S, H, B;
+  int nblk;                 // S / 128
+  int num_items;            // B * H * nblk
+  float scale_log2;         // scale * log2(e)
+  float scale;
+  int write_p;
+  float* lse;               // (B, H, S) log-sum-exp of the scaled scores, natural log
+  float* delta;             // (B, H, S) rowsum(dO * O) (backward)
+  const float* o; const float* d_o;   // (B, S, H * 64), read directly by the dQ kernel for delta
+  int* status;
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+// Item order: the query blocks with the most key tiles first, so the tail of the persistent loop is light.
+__device__ __forceinline__ void item_coords(const AttnParams& p, int item, int& i, int& h, int& b) {
+  const int bh = p.B * p.H;
+  i = p.nblk - 1 - item / bh;
+  const int r = item % bh;
+  h = r % p.H;
+  b = r / p.H;
+}
+
+// S = A(128 x 64, K-major) * B(128 x 64, K-major)^T into 128 columns of tensor memory: 8 k-steps.
+__device__ __forceinline__ void mma_qk(uint32_t d_tmem, uint32_t sa, uint32_t sb) {
+  constexpr uint32_t idesc = make_idesc(128, false, false);
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    const uint32_t off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
+    tc_mma_tf32(d_tmem, make_smem_desc(sa + off, 16, 1024, 2), make_smem_desc(sb + off, 16, 1024, 2), idesc, kk ? 1u : 0u);
+  }
+}
+// D(128 x 64) (+)= A(128 x 128, K-major: four atoms of 32 columns) * B(128 x 64 stored (k, n), n contiguous:
+// MN-major, two 32-wide chunks 16 KB apart): 16 k-steps.
+__device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t sa, uint32_t sb, bool keep) {
+  constexpr uint32_t idesc = make_idesc(64, false, true);
+#pragma unroll
+  for (int kk = 0; kk < 16; ++kk) {
+    const uint32_t a_off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
+    tc_mma_tf32(d_tmem, make_smem_desc(sa + a_off, 16, 1024, 2), make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc,
+                (keep || kk) ? 1u : 0u);
+  }
+}
+
+struct AttnSmem {
+  uint32_t q, ring, ptile;                // shared-memory addresses (u32)
+  uint8_t* ptile_ptr;
+  uint32_t bar_q_full, bar_q_empty, bar_kv_full, bar_kv_empty, bar_s_full, bar_s_empty, bar_p_full, bar_p_empty, bar_o_full, bar_o_empty;
+  uint32_t bar_group, bar_drain;          // rendezvous of the eight softmax warps; completion of MMAs in flight on an abort
+  uint32_t* tmem_slot;
+  volatile int* abort_flag;
+  float* stats;                           // [2][128][2]: per column-half partial (max, sum) of each row
+};
+
+__device__ __forceinline__ AttnSmem carve(uint8_t* smem_raw) {
+  AttnSmem s;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  s.q = base;
+  s.ring = base + AT_SLOT_BYTES;
+  s.ptile = s.ring + AT_SLOTS * AT_SLOT_BYTES;
+  s.ptile_ptr = aligned + AT_SLOT_BYTES + AT_SLOTS * AT_SLOT_BYTES;
+  uint8_t* ctrl = s.ptile_ptr + AT_P_BYTES;
+  const uint32_t bars = smem_u32(ctrl);
+  s.bar_q_full = bars;            s.bar_q_empty = bars + 8;
+  s.bar_kv_full = bars + 16;      s.bar_kv_empty = bars + 16 + 8 * AT_SLOTS;
+  s.bar_s_full = bars + 16 + 16 * AT_SLOTS;   s.bar_s_empty = s.bar_s_full + 16;
+  s.bar_p_full = s.bar_s_empty + 16;          s.bar_p_empty = s.bar_p_full + 8;
+  s.bar_o_full = s.bar_p_empty + 8;           s.bar_o_empty = s.bar_o_full + 8;
+  s.bar_group = s.bar_o_empty + 8;            s.bar_drain = s.bar_group + 8;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 192);
+  s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 196);
+  // the statistics exchange reuses the first 2 KB of the P tile between the two passes (the tile is idle then)
+  s.stats = reinterpret_cast<float*>(s.ptile_ptr);
+  return s;
+}
+
+// ---- forward ---------------------------------------------------------------------------------
+// Two passes over the key tiles of a query block.  Pass 1 computes S tile by tile and keeps only each
+// row's running maximum and sum; pass 2 computes S again (K = 64: the products are cheap, the K
+// tiles come from L2), turns it into the final probabilities exp(s - max) / sum, writes them to
+// shared memory (and, on request, from there to P with a TMA store), and accumulates O += P V in
+// tensor memory, so O never needs rescaling.
+__global__ void __launch_bounds__(AT_THREADS, 1)
+gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_p,
+                   const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const AttnSmem sm = carve(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(sm.bar_q_full, 1); mbar_init(sm.bar_q_empty, 1);
+    for (int i = 0; i < AT_SLOTS; ++i) { mbar_init(sm.bar_kv_full + 8 * i, 1); mbar_init(sm.bar_kv_empty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(sm.bar_s_full + 8 * i, 1); mbar_init(sm.bar_s_empty + 8 * i, 8); }
+    mbar_init(sm.bar_p_full, 8); mbar_init(sm.bar_p_empty, 1);
+    mbar_init(sm.bar_o_full, 1); mbar_init(sm.bar_o_empty, 8);
+    mbar_init(sm.bar_group, 8); mbar_init(sm.bar_drain, 1);
+    *sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *sm.tmem_slot;
+  const uint32_t tmem_o = tmem_base + 256u;
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      long long ring_it = 0; int q_it = 0;
+      bool ok = true;
+      auto load_slot = [&](const CUtensorMap* map, bool is_v, int row0, int h, int b) -> bool {
+        const int slot = (int)(ring_it % AT_SLOTS);
+        const uint32_t par = (uint32_t)((ring_it / AT_SLOTS) & 1);
+        if (!mbar_wait(sm.bar_kv_empty + 8 * slot, par ^ 1u, sm.abort_flag, p.status)) return false;
+        const uint32_t dst = sm.ring + slot * AT_SLOT_BYTES, full = sm.bar_kv_full + 8 * slot;
+        mbar_expect_tx(full, AT_SLOT_BYTES);
+        if (is_v) {
+          tma_load_5d(dst, map, full, 0, row0, 0, h, b);
+        } else {
+          tma_load_4d(dst, map, full, 0, row0, h, b);
+          tma_load_4d(dst + 16384, map, full, 32, row0, h, b);
+        }
+        ++ring_it;
+        return true;
+      };
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int i, h, b;
+        item_coords(p, item, i, h, b);
+        if (!mbar_wait(sm.bar_q_empty, (uint32_t)(q_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        mbar_expect_tx(sm.bar_q_full, AT_SLOT_BYTES);
+        tma_load_4d(sm.q, &map_q, sm.bar_q_full, 0, i * AT_TILE, h, b);
+        tma_load_4d(sm.q + 16384, &map_q, sm.bar_q_full, 32, i * AT_TILE, h, b);
+        ++q_it;
+        for (int j = 0; ok && j <= i; ++j) ok = load_slot(&map_k, false, j * AT_TILE, h, b);           // pass 1
+        // pass 2, in the order the MMA lane consumes them: K0, K1, V0, K2, V1, ..., Ki, V(i-1), Vi
+        if (ok) ok = load_slot(&map_k, false, 0, h, b);
+        for (int j = 0; ok && j <= i; ++j) {
+          if (j + 1 <= i) ok = load_slot(&map_k, false, (j + 1) * AT_TILE, h, b);
+          if (ok) ok = load_slot(&map_v, true, j * AT_TILE, h, b);
+        }
+      }
+      if (!ok) {     // aborting: let the loads already issued land before shared memory is released
+        const long long first = ring_it > AT_SLOTS ? ring_it - AT_SLOTS : 0;
+        for (long long r = first; r < ring_it; ++r) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(sm.bar_kv_full + 8 * (int)(r % AT_SLOTS), (uint32_t)((r / AT_SLOTS) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      long long ring_it = 0; int q_it = 0, s_it = 0, p_it = 0, o_it = 0;
+      bool ok = true;
+      auto issue_s = [&]() -> bool {            // next ring slot holds a K tile
+        const int slot = (int)(ring_it % AT_SLOTS);
+        const int sb = s_it & 1;
+        if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / AT_SLOTS) & 1), sm.abort_flag, p.status)) return false;
+        if (!mbar_wait(sm.bar_s_empty + 8 * sb, (uint32_t)((s_it >> 1) & 1) ^ 1u, sm.abort_flag, p.status)) return false;
+        tc_fence_after();
+        mma_qk(tmem_base + (uint32_t)(sb * 128), sm.q, sm.ring + slot * AT_SLOT_BYTES);
+        tc_commit(sm.bar_kv_empty + 8 * slot);
+        tc_commit(sm.bar_s_full + 8 * sb);
+        ++ring_it; ++s_it;
+        return true;
+      };
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int i, h, b;
+        item_coords(p, item, i, h, b);
+        if (!mbar_wait(sm.bar_q_full, (uint32_t)(q_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        ++q_it;
+        for (int j = 0; ok && j <= i; ++j) ok = issue_s();          // pass 1
+        if (ok) ok = issue_s();                                     // pass 2: S_0
+        for (int j = 0; ok && j <= i; ++j) {
+          if (j + 1 <= i) { ok = issue_s(); if (!ok) break; }
+          if (j == i) tc_commit(sm.bar_q_empty);                    // every product with this Q has been issued
+          const int slot = (int)(ring_it % AT_SLOTS);
+          if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / AT_SLOTS) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(sm.bar_p_full, (uint32_t)(p_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (j == 0 && !mbar_wait(sm.bar_o_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          tc_fence_after();
+          mma_pv(tmem_o, sm.ptile, sm.ring + slot * AT_SLOT_BYTES, j != 0);
+          tc_commit(sm.bar_kv_empty + 8 * slot);
+          tc_commit(sm.bar_p_empty);
+          if (j == i) { tc_commit(sm.bar_o_full); ++o_it; }
+          ++ring_it; ++p_it;
+        }
+      }
+      if (!ok) {                    // aborting: wait (bounded) for the products in flight before tensor memory is released
+        tc_commit(sm.bar_drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(sm.bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    // ------------------------------ softmax warps ------------------------------
+    const int q = warp & 3;                    // tensor-memory lane quarter this warp may read
+    const int eset = (warp - 2) >> 2;          // takes chunks eset and eset + 2 of a tile's four 32-column chunks
+    const int r_local = q * 32 + lane;         // row inside the 128-row tile
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    int s_it = 0, p_it = 0, o_it = 0, g_it = 0;
+    bool ok = true;
+    // Rendezvous of the eight softmax warps on an mbarrier, so that it is bounded like every other wait.
+    auto group_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.bar_group);
+      const bool r = mbar_wait(sm.bar_group, (uint32_t)(g_it & 1), sm.abort_flag, p.status);
+      ++g_it;
+      return r;
+    };
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      int i, h, b;
+      item_coords(p, item, i, h, b);
+      const int row = i * AT_TILE + r_local;   // query index
+      // ---- pass 1: running maximum and sum of this warp's column chunks
+      float m = -INFINITY, l = 0.0f;
+      for (int j = 0; j <= i; ++j) {
+        const int sb = s_it & 1;
+        if (!mbar_wait(sm.bar_s_full + 8 * sb, (uint32_t)((s_it >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = eset + 2 * cc;
+          const int col0 = j * AT_TILE + c * 32;
+          if (j == i && col0 > i * AT_TILE + q * 32 + 31) continue;      // chunk wholly above the diagonal for this warp's rows
+          float v[32];
+          tc_ld32(lane_base + (uint32_t)(sb * 128 + c * 32), v);
+          tc_wait_ld();
+          const int nvalid = (j == i) ? min(32, row - col0 + 1) : 32;    // columns <= row
+          float mx = -INFINITY;
+#pragma unroll
+          for (int t = 0; t < 32; ++t) { v[t] = (t < nvalid) ? v[t] * p.scale_log2 : -INFINITY; mx = fmaxf(mx, v[t]); }
+          if (mx > -INFINITY) {
+            const float m_new = fmaxf(m, mx);
+            float acc = 0.0f;
+#pragma unroll
+            for (int t = 0; t < 32; ++t) acc += ex2(v[t] - m_new);
+            l = l * ex2(m - m_new) + acc;
+            m = m_new;
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_s_empty + 8 * sb);
+        ++s_it;
+      }
+      if (!ok) break;
+      // ---- combine the two column halves of every row (the P tile is idle: its last reader, the
+      // previous item's final PV product and P stores, is waited for first)
+      if (!mbar_wait(sm.bar_p_empty, (uint32_t)(p_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+      if (lane == 0) tma_store_wait_read<0>();
+      if (!group_sync()) { ok = false; break; }
+      sm.stats[(eset * 128 + r_local) * 2] = m;
+      sm.stats[(eset * 128 + r_local) * 2 + 1] = l;
+      if (!group_sync()) { ok = false; break; }
+      const float m_o = sm.stats[((eset ^ 1) * 128 + r_local) * 2], l_o = sm.stats[((eset ^ 1) * 128 + r_local) * 2 + 1];
+      const float M = fmaxf(m, m_o);
+      const float L = (m > -INFINITY ? l * ex2(m - M) : 0.0f) + (m_o > -INFINITY ? l_o * ex2(m_o - M) : 0.0f);
+      const float inv = 1.0f / L;
+      if (p.lse && eset == 0) p.lse[((long long)b * p.H + h) * p.S + row] = (M + log2f(L)) * AT_LN2;
+      if (!group_sync()) { ok = false; break; }   // the statistics have been read: the tile may be overwritten
+      // ---- pass 2: probabilities -> shared memory (-> P), O += P V
+      for (int j = 0; j <= i; ++j) {
+        const int sb = s_it & 1;
+        if (!mbar_wait(sm.bar_s_full + 8 * sb, (uint32_t)((s_it >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        if (j > 0) {
+          if (!mbar_wait(sm.bar_p_empty, (uint32_t)(p_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+        }
+        tc_fence_after();
+#pragma unroll 1
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = eset + 2 * cc;
+          const int col0 = j * AT_TILE + c * 32;
+          float v[32];
+          tc_ld32(lane_base + (uint32_t)(sb * 128 + c * 32), v);
+          tc_wait_ld();
+          const int nvalid = (j == i) ? min(32, row - col0 + 1) : 32;
+          uint8_t* my_row = sm.ptile_ptr + c * 16384 + r_local * 128;
+          const int sw = r_local & 7;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 x;
+            x.x = (4 * g < nvalid) ? to_tf32(ex2(v[4 * g] * p.scale_log2 - M) * inv) : 0.0f;
+            x.y = (4 * g + 1 < nvalid) ? to_tf32(ex2(v[4 * g + 1] * p.scale_log2 - M) * inv) : 0.0f;
+            x.z = (4 * g + 2 < nvalid) ? to_tf32(ex2(v[4 * g + 2] * p.scale_log2 - M) * inv) : 0.0f;
+            x.w = (4 * g + 3 < nvalid) ? to_tf32(ex2(v[4 * g + 3] * p.scale_log2 - M) * inv) : 0.0f;
+            *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = x;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (p.write_p && lane == 0)
+            tma_store_4d(&map_p, sm.ptile + (uint32_t)(c * 16384 + q * 4096), col0, i * AT_TILE + q * 32, h, b, false);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(sm.bar_p_full); mbar_arrive(sm.bar_s_empty + 8 * sb); }
+        ++s_it; ++p_it;
+      }
+      if (!ok) break;
+      // ---- O: 64 columns, this warp's half of them, through its (now idle) part of the P tile
+      if (!mbar_wait(sm.bar_o_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+      ++o_it;
+      tc_fence_after();
+      {
+        float v[32];
+        tc_ld32(tmem_o + ((uint32_t)(q * 32) << 16) + (uint32_t)(eset * 32), v);
+        tc_wait_ld();
+        tc_fence_before();
+        // the final PV product has completed (o_full), so the tile is no longer read by the tensor core;
+        // this warp's own P stores from its sub-tiles are waited for here
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+        uint8_t* my_row = sm.ptile_ptr + eset * 16384 + r_local * 128;
+        const int sw = r_local & 7;
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_4d(&map_o, sm.ptile + (uint32_t)(eset * 16384 + q * 4096), eset * 32, i * AT_TILE + q * 32, h, b, false);
+          mbar_arrive(sm.bar_o_empty);
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+int check_attn_args(gt_ctx* ctx, const void* q, const void* k, const void* v, int64_t B, int64_t S, int64_t H, int64_t D) {
+  if (!ctx || !q || !k || !v || B <= 0 || S <= 0 || H <= 0) return GT_ERR_INVALID_ARG;
+  if (D != AT_D) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "fused attention supports head dimension 64, got %lld", (long long)D);
+  if (S % AT_TILE != 0) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "fused attention needs a sequence length that is a multiple of 128, got %lld", (long long)S);
+  if (B * H * (S / AT_TILE) > 0x7fffffffLL || S > (1 << 24)) return GT_ERR_INVALID_ARG;
+  if ((((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15) != 0) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "fused attention needs 16-byte aligned q, k, v");
+  return GT_OK;
+}
+
+}  // namespace
+
+extern "C" int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* lse, const float* q, const float* k,
+                                    const float* v, int64_t B, int64_t S, int64_t H, int64_t D, float scale, void* stream_) {
+  int rc = check_attn_args(ctx, q, k, v, B, S, H, D);
+  if (rc != GT_OK) return rc;
+  if (!o || ((uintptr_t)o & 15) || (p_out && ((uintptr_t)p_out & 15))) return GT_ERR_INVALID_ARG;
+  cudaStream_t stream = stream_ ? (cudaStream_t)stream_ : ctx->stream;
+  const long long E = H * D;
+  CUtensorMap mq, mk, mv, mp, mo;
+  const OperandView vq = {q, S, D, E, D, S * E}, vk = {k, S, D, E, D, S * E}, vv = {v, S, D, E, D, S * E};
+  if ((rc = encode_map(ctx, &mq, vq, 32, AT_TILE, H, B, false)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mk, vk, 32, AT_TILE, H, B, false)) != GT_OK) return rc;
+  if (!encode_map_mn5(ctx, &mv, vv, 2, H, B, false, AT_TILE)) GT_FAIL(ctx, GT_ERR_CUDA, "fused attention: the tensor map of V was refused");
+  const OperandView vo = {o, S, D, E, D, S * E};
+  if ((rc = encode_map(ctx, &mo, vo, 32, 32, H, B, false, /*plain_f32=*/true)) != GT_OK) return rc;
+  if (p_out) {
+    const OperandView vp = {p_out, S, S, S, S * S, H * S * S};
+    if ((rc = encode_map(ctx, &mp, vp, 32, 32, H, B, false, true)) != GT_OK) return rc;
+  } else {
+    mp = mo;
+  }
+  AttnParams p;
+  p.S = (int)S; p.H = (int)H; p.B = (int)B;
+  p.nblk = (int)(S / AT_TILE);
+  p.num_items = (int)(B * H * p.nblk);
+  p.scale = scale; p.scale_log2 = scale * AT_LOG2E;
+  p.write_p = p_out ? 1 : 0;
+  p.lse = lse; p.delta = nullptr; p.o = nullptr; p.d_o = nullptr;
+  p.status = ctx->d_status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    GT_CUDA_OK(ctx, cudaFuncSetAttribute(gt_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES));
+    attr_set = true;
+  }
+  const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
+  gt_attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, mp, mo, p);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}

@@ -1,0 +1,205 @@
+// Pieces shared by the tcgen05 kernels of this library (GEMM, fused attention): PTX wrappers for
+// mbarriers, TMA loads / stores, tcgen05 MMA / commit / loads, the shared-memory and instruction
+// descriptors, and the host-side tensor-map encoders.  Everything sits in an unnamed namespace:
+// each translation unit gets its own copy.
+#pragma once
+
+#include "gt_internal.h"
+
+namespace {
+
+constexpr int BM = 128;                                  // rows of one tcgen05.mma (M = 128, one row per tensor-memory lane)
+constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;   // about 1.5 s at 1.9 GHz
+
+// ---- PTX wrappers -----------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// The suspend-time hint lets the hardware park the waiting thread until the phase completes (or the
+// hint expires) instead of re-issuing the test: a spinning producer / MMA lane otherwise competes
+// for issue slots with the epilogue warps of its scheduler.
+constexpr uint32_t TRY_WAIT_SUSPEND_NS = 100000u;
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(TRY_WAIT_SUSPEND_NS) : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another did).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      atomicExch(status, GT_ERR_TIMEOUT);
+      return false;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// C tile (32 columns x 32 rows, 128-byte swizzled in shared memory) -> global, clipped at the
+// tensor's edges by the TMA unit; `add` turns the store into an element-wise fp32 add (C += tile).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3, bool add) {
+  if (add) {
+    asm volatile("cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"((uint64_t)map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  } else {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 ::"l"((uint64_t)map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+  }
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets
+// (all >> 4), descriptor version 1 at bit 46, swizzle mode at bits 61-63.
+//   K-major operand : 128-byte swizzle of 16-byte chunks (mode 2); rows of 128 bytes, groups of
+//                     8 rows SBO = 1024 bytes apart; LBO unused.
+//   MN-major operand: fp32 allows only the 128-byte swizzle of 32-byte chunks (mode 1); k-rows of
+//                     128 bytes (32 MN elements), groups of 4 k-rows SBO = 512 bytes apart, the
+//                     next 32 MN elements LBO bytes further.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t swizzle_mode) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)swizzle_mode << 61;
+  return d;
+}
+
+// Instruction descriptor, kind::tf32: D = fp32 (1 at bit 4), A and B = tf32 (2 at bits 7
+// and 10), operand major bits 15 / 16 (1 = MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int n, bool a_mn, bool b_mn) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---- host side: tensor maps -----------------------------------------------------------------
+
+struct OperandView {
+  const float* ptr; long long rows, cols, ld, s0, s1;   // stored (rows, cols), cols contiguous
+};
+
+int encode_map(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int box_cols, int box_rows,
+               long long batch0, long long batch1, bool mn_major, bool plain_f32 = false) {
+  cuuint64_t dims[4] = {(cuuint64_t)v.cols, (cuuint64_t)v.rows, (cuuint64_t)batch0, (cuuint64_t)batch1};
+  const cuuint64_t slice = (cuuint64_t)v.rows * (cuuint64_t)v.ld * 4ull;
+  cuuint64_t strides[3] = {(cuuint64_t)v.ld * 4ull,
+                           batch0 > 1 ? (cuuint64_t)v.s0 * 4ull : slice,
+                           batch1 > 1 ? (cuuint64_t)v.s1 * 4ull : slice * (cuuint64_t)batch0};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = ctx->encode_tiled(map, (ctx->tma_round && !plain_f32) ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                 4, (void*)v.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    GT_FAIL(ctx, GT_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d): ptr=%p dims=(%llu,%llu,%llu,%llu) strides=(%llu,%llu,%llu) box=(%u,%u)",
+            (int)r, (const void*)v.ptr, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+            (unsigned long long)dims[3], (unsigned long long)strides[0], (unsigned long long)strides[1],
+            (unsigned long long)strides[2], box[0], box[1]);
+  }
+  return GT_OK;
+}
+
+// An MN-major operand (stored (K, MN), MN contiguous, MN a multiple of 32) described as a 5-D tensor
+// (32, K, MN/32, batch0, batch1) with strides (4, ld*4, 128, ...) bytes: ONE box of (32, 32, chunks)
+// then fills the whole stage in the layout the MMA descriptors expect (chunk-major, 4 KB per chunk),
+// instead of `chunks` separate 32 x 32 boxes.  Returns false if the driver refuses the map.
+bool encode_map_mn5(gt_ctx* ctx, CUtensorMap* map, const OperandView& v, int chunks, long long batch0, long long batch1, bool plain_f32 = false,
+                    int box_rows = 32) {
+  cuuint64_t dims[5] = {32, (cuuint64_t)v.rows, (cuuint64_t)(v.cols / 32), (cuuint64_t)batch0, (cuuint64_t)batch1};
+  const cuuint64_t slice = (cuuint64_t)v.rows * (cuuint64_t)v.ld * 4ull;
+  cuuint64_t strides[4] = {(cuuint64_t)v.ld * 4ull, 128ull,
+                           batch0 > 1 ? (cuuint64_t)v.s0 * 4ull : slice,
+                           batch1 > 1 ? (cuuint64_t)v.s1 * 4ull : slice * (cuuint64_t)batch0};
+  cuuint32_t box[5] = {32, (cuuint32_t)box_rows, (cuuint32_t)chunks, 1, 1};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = ctx->encode_tiled(map, (ctx->tma_round && !plain_f32) ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                                 5, (void*)v.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// Can TMA describe this operand?  16-byte aligned base, leading dimension and batch strides
+// multiples of four floats, strides below the 2^40-byte limit.
+bool tma_ok(const float* ptr, long long ld, long long s0, long long s1, long long batch0, long long batch1) {
+  if ((uintptr_t)ptr & 15) return false;
+  if (ld & 3) return false;
+  if (batch0 > 1 && (s0 & 3)) return false;
+  if (batch1 > 1 && (s1 & 3)) return false;
+  const long long lim = 1LL << 38;
+  return ld < lim && s0 < lim && s1 < lim;
+}
+
+}  // namespace

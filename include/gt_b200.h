@@ -178,6 +178,20 @@ int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_
                            float* C, int64_t ldc, const float* bias, float alpha,
                            int accumulate, int epilogue, void* stream);
 
+/* ---- fused causal attention (head dimension 64, sequence length a multiple of 128) ----------
+ * The reference composes attention from transposes, two bmm calls, scale_inplace and
+ * softmax_with_causal_mask (gradtuity/nn.py:511-554) and keeps the (B, H, T, T) scores in
+ * memory; these entry points compute the same result without materialising them.
+ * q, k, v, o (and dq, dk, dv, d_o) are (B, T, H * 64) row-major: the projection outputs, heads
+ * side by side, read in place.  scale multiplies Q K^T before the softmax.  lse (B, H, T)
+ * receives each row's log-sum-exp of the scaled, masked scores (needed by the backward).
+ * p_out, when not NULL, also receives the probabilities P (B, H, T, T): rows are written up to
+ * the end of their 128-wide diagonal block, exact zeros right of the diagonal inside it.
+ * Returns GT_ERR_UNSUPPORTED for another head dimension or sequence length.                  */
+int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* lse, const float* q,
+                         const float* k, const float* v, int64_t B, int64_t T, int64_t H,
+                         int64_t D, float scale, void* stream);
+
 /* Which kernel a call with these arguments would run: 0 = tcgen05/TMA kernel, 1 = fp32 FMA
  * kernel.  No launch.                                                                       */
 int gt_gemm_path(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
