@@ -418,6 +418,14 @@ def run_attn(args) -> dict:
         "dQ+=dS K (NN)": (lambda: G.gemm_batched(0, S, D, S, dp.ptr, S, S * S, H * S * S, k.ptr, E, D, S * E, o.ptr, E, D, S * E, H, B, accumulate=True),
                           4.0 * B * H * (S * S + 3 * S * D)),
     }
+    lse = Tensor._zeros((B, H, S))
+    def fused(p_out):
+        _lib.check(lib.gt_attention_forward(ctx, c_void_p(o.ptr), c_void_p(p_out) if p_out else None, c_void_p(lse.ptr),
+                                            c_void_p(q.ptr), c_void_p(k.ptr), c_void_p(v.ptr), B, S, H, D, c_float(0.125), None),
+                   "gt_attention_forward")
+    # fused forward: Q, K, V read, O written (+ the lower-triangular half of P when it is requested)
+    cases["fused forward, P written"] = (lambda: fused(p.ptr), 4.0 * B * H * (4 * S * D + S * (S + 128) // 2))
+    cases["fused forward, no P"] = (lambda: fused(0), 4.0 * B * H * 4 * S * D)
     out = {"attn": True, "config": "B=8 H=12 T=1024 d=64, heads read in place from (B,T,H*d)", "hbm_peak_gbs": hbm, "cases": {}}
     for name, (fn, nbytes) in cases.items():
         for _ in range(args.warmup):

@@ -15,8 +15,8 @@
 //
 // All three share one structure: a persistent CTA per SM walks (batch, head, block) items, heaviest
 // first; warp 0 issues TMA loads into a ring of 32 KB slots, lane 0 of warp 1 issues tcgen05.mma,
-// warps 2-9 (lane = row of the 128-row tile, two warps per tensor-memory lane quarter, each taking
-// every other 32-column chunk) do the softmax arithmetic between tensor memory and the shared-memory
+// warps 2-17 (lane = row of the 128-row tile, four warps per tensor-memory lane quarter, one per
+// 32-column chunk of a tile) do the softmax arithmetic between tensor memory and the shared-memory
 // tile that the next MMA reads as its A operand.  Q, K, V, dO are read in place from the
 // (B, T, H * 64) projection outputs; TMA rounds them to tf32.  The probabilities are rounded to tf32
 // (nearest) before they are written to shared memory, so the tensor core does not truncate them.
@@ -33,7 +33,8 @@ namespace {
 
 constexpr int AT_D = 64;                        // head dimension
 constexpr int AT_TILE = 128;                    // queries per item, keys per tile
-constexpr int AT_THREADS = 320;                 // producer warp, MMA warp, 8 softmax warps
+constexpr int AT_THREADS = 576;                 // producer warp, MMA warp, 16 softmax warps (four per tensor-memory lane quarter)
+constexpr int AT_SOFTMAX_WARPS = 16;
 constexpr int AT_SLOT_BYTES = 32768;            // one 128 x 64 fp32 operand tile
 constexpr int AT_SLOTS = 4;
 constexpr int AT_P_BYTES = 65536;               // 128 x 128 fp32 tile of P / dS (four 128-byte-swizzle atoms of 32 columns)
@@ -102,7 +103,7 @@ struct AttnSmem {
   uint32_t bar_group, bar_drain;          // rendezvous of the eight softmax warps; completion of MMAs in flight on an abort
   uint32_t* tmem_slot;
   volatile int* abort_flag;
-  float* stats;                           // [2][128][2]: per column-half partial (max, sum) of each row
+  float* stats;                           // [4][128][2]: per column-chunk partial (max, sum) of each row
 };
 
 __device__ __forceinline__ AttnSmem carve(uint8_t* smem_raw) {
@@ -123,7 +124,7 @@ __device__ __forceinline__ AttnSmem carve(uint8_t* smem_raw) {
   s.bar_group = s.bar_o_empty + 8;            s.bar_drain = s.bar_group + 8;
   s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 192);
   s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 196);
-  // the statistics exchange reuses the first 2 KB of the P tile between the two passes (the tile is idle then)
+  // the statistics exchange reuses the first 4 KB of the P tile between the two passes (the tile is idle then)
   s.stats = reinterpret_cast<float*>(s.ptile_ptr);
   return s;
 }
@@ -145,10 +146,10 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   if (threadIdx.x == 0) {
     mbar_init(sm.bar_q_full, 1); mbar_init(sm.bar_q_empty, 1);
     for (int i = 0; i < AT_SLOTS; ++i) { mbar_init(sm.bar_kv_full + 8 * i, 1); mbar_init(sm.bar_kv_empty + 8 * i, 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(sm.bar_s_full + 8 * i, 1); mbar_init(sm.bar_s_empty + 8 * i, 8); }
-    mbar_init(sm.bar_p_full, 8); mbar_init(sm.bar_p_empty, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(sm.bar_s_full + 8 * i, 1); mbar_init(sm.bar_s_empty + 8 * i, AT_SOFTMAX_WARPS); }
+    mbar_init(sm.bar_p_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_p_empty, 1);
     mbar_init(sm.bar_o_full, 1); mbar_init(sm.bar_o_empty, 8);
-    mbar_init(sm.bar_group, 8); mbar_init(sm.bar_drain, 1);
+    mbar_init(sm.bar_group, AT_SOFTMAX_WARPS); mbar_init(sm.bar_drain, 1);
     *sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -255,12 +256,15 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   } else {
     // ------------------------------ softmax warps ------------------------------
     const int q = warp & 3;                    // tensor-memory lane quarter this warp may read
-    const int eset = (warp - 2) >> 2;          // takes chunks eset and eset + 2 of a tile's four 32-column chunks
+    const int eset = (warp - 2) >> 2;          // the 32-column chunk of every tile this warp owns (0..3)
     const int r_local = q * 32 + lane;         // row inside the 128-row tile
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint8_t* const my_row = sm.ptile_ptr + eset * 16384 + r_local * 128;     // this thread's 128 bytes of the P tile
+    const uint32_t my_sub = sm.ptile + (uint32_t)(eset * 16384 + q * 4096);  // this warp's 32 x 32 part of it
+    const int sw = r_local & 7;
     int s_it = 0, p_it = 0, o_it = 0, g_it = 0;
     bool ok = true;
-    // Rendezvous of the eight softmax warps on an mbarrier, so that it is bounded like every other wait.
+    // Rendezvous of the softmax warps on an mbarrier, so that it is bounded like every other wait.
     auto group_sync = [&]() -> bool {
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.bar_group);
@@ -272,30 +276,35 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       int i, h, b;
       item_coords(p, item, i, h, b);
       const int row = i * AT_TILE + r_local;   // query index
-      // ---- pass 1: running maximum and sum of this warp's column chunks
+      // ---- pass 1: running maximum and sum over this warp's column chunk of every key tile
       float m = -INFINITY, l = 0.0f;
       for (int j = 0; j <= i; ++j) {
         const int sb = s_it & 1;
         if (!mbar_wait(sm.bar_s_full + 8 * sb, (uint32_t)((s_it >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-#pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = eset + 2 * cc;
-          const int col0 = j * AT_TILE + c * 32;
-          if (j == i && col0 > i * AT_TILE + q * 32 + 31) continue;      // chunk wholly above the diagonal for this warp's rows
+        const int col0 = j * AT_TILE + eset * 32;
+        if (j < i || col0 <= i * AT_TILE + q * 32 + 31) {        // else: wholly right of the diagonal for this warp's rows
           float v[32];
-          tc_ld32(lane_base + (uint32_t)(sb * 128 + c * 32), v);
+          tc_ld32(lane_base + (uint32_t)(sb * 128 + eset * 32), v);
           tc_wait_ld();
-          const int nvalid = (j == i) ? min(32, row - col0 + 1) : 32;    // columns <= row
           float mx = -INFINITY;
+          if (j < i) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) { v[t] = (t < nvalid) ? v[t] * p.scale_log2 : -INFINITY; mx = fmaxf(mx, v[t]); }
+            for (int t = 0; t < 32; ++t) mx = fmaxf(mx, v[t]);
+          } else {
+            const int nvalid = row - col0 + 1;                   // columns <= row
+#pragma unroll
+            for (int t = 0; t < 32; ++t) { if (t >= nvalid) v[t] = -INFINITY; mx = fmaxf(mx, v[t]); }
+          }
           if (mx > -INFINITY) {
-            const float m_new = fmaxf(m, mx);
-            float acc = 0.0f;
+            const float m_new = fmaxf(m, mx * p.scale_log2);
+            float a0 = 0.0f, a1 = 0.0f;
 #pragma unroll
-            for (int t = 0; t < 32; ++t) acc += ex2(v[t] - m_new);
-            l = l * ex2(m - m_new) + acc;
+            for (int t = 0; t < 32; t += 2) {
+              a0 += ex2(fmaf(v[t], p.scale_log2, -m_new));
+              a1 += ex2(fmaf(v[t + 1], p.scale_log2, -m_new));
+            }
+            l = l * ex2(m - m_new) + (a0 + a1);
             m = m_new;
           }
         }
@@ -305,19 +314,25 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         ++s_it;
       }
       if (!ok) break;
-      // ---- combine the two column halves of every row (the P tile is idle: its last reader, the
-      // previous item's final PV product and P stores, is waited for first)
+      // ---- combine the four column chunks of every row (the P tile is idle: its last reader, the
+      // previous item's final PV product and this warp's own stores from it, is waited for first)
       if (!mbar_wait(sm.bar_p_empty, (uint32_t)(p_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
       if (lane == 0) tma_store_wait_read<0>();
       if (!group_sync()) { ok = false; break; }
       sm.stats[(eset * 128 + r_local) * 2] = m;
       sm.stats[(eset * 128 + r_local) * 2 + 1] = l;
       if (!group_sync()) { ok = false; break; }
-      const float m_o = sm.stats[((eset ^ 1) * 128 + r_local) * 2], l_o = sm.stats[((eset ^ 1) * 128 + r_local) * 2 + 1];
-      const float M = fmaxf(m, m_o);
-      const float L = (m > -INFINITY ? l * ex2(m - M) : 0.0f) + (m_o > -INFINITY ? l_o * ex2(m_o - M) : 0.0f);
-      const float inv = 1.0f / L;
-      if (p.lse && eset == 0) p.lse[((long long)b * p.H + h) * p.S + row] = (M + log2f(L)) * AT_LN2;
+      float M = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) M = fmaxf(M, sm.stats[(e * 128 + r_local) * 2]);
+      float L = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float me = sm.stats[(e * 128 + r_local) * 2];
+        if (me > -INFINITY) L += sm.stats[(e * 128 + r_local) * 2 + 1] * ex2(me - M);
+      }
+      const float ML = M + log2f(L);           // p = 2^(s * scale * log2 e - ML)
+      if (p.lse && eset == 0) p.lse[((long long)b * p.H + h) * p.S + row] = ML * AT_LN2;
       if (!group_sync()) { ok = false; break; }   // the statistics have been read: the tile may be overwritten
       // ---- pass 2: probabilities -> shared memory (-> P), O += P V
       for (int j = 0; j <= i; ++j) {
@@ -329,58 +344,63 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           __syncwarp();
         }
         tc_fence_after();
-#pragma unroll 1
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = eset + 2 * cc;
-          const int col0 = j * AT_TILE + c * 32;
-          float v[32];
-          tc_ld32(lane_base + (uint32_t)(sb * 128 + c * 32), v);
-          tc_wait_ld();
-          const int nvalid = (j == i) ? min(32, row - col0 + 1) : 32;
-          uint8_t* my_row = sm.ptile_ptr + c * 16384 + r_local * 128;
-          const int sw = r_local & 7;
+        const int col0 = j * AT_TILE + eset * 32;
+        float v[32];
+        tc_ld32(lane_base + (uint32_t)(sb * 128 + eset * 32), v);
+        tc_wait_ld();
+        if (j < i) {
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             float4 x;
-            x.x = (4 * g < nvalid) ? to_tf32(ex2(v[4 * g] * p.scale_log2 - M) * inv) : 0.0f;
-            x.y = (4 * g + 1 < nvalid) ? to_tf32(ex2(v[4 * g + 1] * p.scale_log2 - M) * inv) : 0.0f;
-            x.z = (4 * g + 2 < nvalid) ? to_tf32(ex2(v[4 * g + 2] * p.scale_log2 - M) * inv) : 0.0f;
-            x.w = (4 * g + 3 < nvalid) ? to_tf32(ex2(v[4 * g + 3] * p.scale_log2 - M) * inv) : 0.0f;
+            x.x = to_tf32(ex2(fmaf(v[4 * g], p.scale_log2, -ML)));
+            x.y = to_tf32(ex2(fmaf(v[4 * g + 1], p.scale_log2, -ML)));
+            x.z = to_tf32(ex2(fmaf(v[4 * g + 2], p.scale_log2, -ML)));
+            x.w = to_tf32(ex2(fmaf(v[4 * g + 3], p.scale_log2, -ML)));
             *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = x;
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (p.write_p && lane == 0)
-            tma_store_4d(&map_p, sm.ptile + (uint32_t)(c * 16384 + q * 4096), col0, i * AT_TILE + q * 32, h, b, false);
+        } else {
+          const int nvalid = row - col0 + 1;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 x;
+            x.x = (4 * g < nvalid) ? to_tf32(ex2(fmaf(v[4 * g], p.scale_log2, -ML))) : 0.0f;
+            x.y = (4 * g + 1 < nvalid) ? to_tf32(ex2(fmaf(v[4 * g + 1], p.scale_log2, -ML))) : 0.0f;
+            x.z = (4 * g + 2 < nvalid) ? to_tf32(ex2(fmaf(v[4 * g + 2], p.scale_log2, -ML))) : 0.0f;
+            x.w = (4 * g + 3 < nvalid) ? to_tf32(ex2(fmaf(v[4 * g + 3], p.scale_log2, -ML))) : 0.0f;
+            *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = x;
+          }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) { mbar_arrive(sm.bar_p_full); mbar_arrive(sm.bar_s_empty + 8 * sb); }
+        if (lane == 0) {
+          if (p.write_p) tma_store_4d(&map_p, my_sub, col0, i * AT_TILE + q * 32, h, b, false);
+          mbar_arrive(sm.bar_p_full);
+          mbar_arrive(sm.bar_s_empty + 8 * sb);
+        }
         ++s_it; ++p_it;
       }
       if (!ok) break;
-      // ---- O: 64 columns, this warp's half of them, through its (now idle) part of the P tile
+      // ---- O: 64 columns = chunks 0 and 1; their owners pass them through their part of the P tile
       if (!mbar_wait(sm.bar_o_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
       ++o_it;
       tc_fence_after();
-      {
+      if (eset < 2) {
         float v[32];
-        tc_ld32(tmem_o + ((uint32_t)(q * 32) << 16) + (uint32_t)(eset * 32), v);
+        tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), v);
         tc_wait_ld();
         tc_fence_before();
-        // the final PV product has completed (o_full), so the tile is no longer read by the tensor core;
-        // this warp's own P stores from its sub-tiles are waited for here
+        // the final PV product has completed (o_full), so the tensor core no longer reads the tile;
+        // this warp's own P store from its part is waited for here
         if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
-        uint8_t* my_row = sm.ptile_ptr + eset * 16384 + r_local * 128;
-        const int sw = r_local & 7;
 #pragma unroll
         for (int g = 0; g < 8; ++g)
           *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
-          tma_store_4d(&map_o, sm.ptile + (uint32_t)(eset * 16384 + q * 4096), eset * 32, i * AT_TILE + q * 32, h, b, false);
+          tma_store_4d(&map_o, my_sub, eset * 32, i * AT_TILE + q * 32, h, b, false);
           mbar_arrive(sm.bar_o_empty);
         }
       }

@@ -19,6 +19,7 @@ no Triton, no backend switch and no CPU path.
 from __future__ import annotations
 
 import math
+import os
 import struct
 from contextlib import contextmanager
 from ctypes import c_void_p
@@ -642,14 +643,25 @@ class Tensor:
         f_upper = GEMM_AT_LOWER if trimmed else 0
         sm_mode = 2 if trimmed else 1
         p = empty_tensor((B, H, S, S))
-        # scores[b, h] = scale * Q[b, :, h, :] K[b, :, h, :]^T, masked: NT, in-place heads
-        _gemm.gemm_batched(LAYOUT_NT, S, S, D, q.ptr, E, D, S * E, k.ptr, E, D, S * E,
-                           p.ptr, S, S * S, H * S * S, H, B, alpha=scale, epilogue=EPI_CAUSAL, flags=f_skip)
-        _call("gt_softmax", _vp(p.ptr), _vp(p.ptr), B * H * S, S, sm_mode)
         out = empty_tensor((B, S, E))
-        # O[b, :, h, :] = P[b, h] V[b, :, h, :]: NN, output written straight into (B, S, H, d)
-        _gemm.gemm_batched(LAYOUT_NN, S, D, S, p.ptr, S, S * S, H * S * S, v.ptr, E, D, S * E,
-                           out.ptr, E, D, S * E, H, B, flags=f_lower)
+        # GRADTUITY_ATTENTION=materialized keeps the three-launch form (S, then P, then O) everywhere;
+        # otherwise head dimension 64 with S a multiple of 128 takes the fused forward kernel, which
+        # computes the same P (written out for the backward) and O in one launch without storing S.
+        from ._lib import PREC_TF32
+        fused = (trimmed and D == 64 and S % 128 == 0 and _gemm.default_precision() == PREC_TF32
+                 and os.environ.get("GRADTUITY_ATTENTION", "fused") != "materialized")
+        if fused:
+            lse = empty_tensor((B, H, S))
+            _call("gt_attention_forward", _vp(out.ptr), _vp(p.ptr), _vp(lse.ptr), _vp(q.ptr), _vp(k.ptr), _vp(v.ptr),
+                  B, S, H, D, scale, None)
+        else:
+            # scores[b, h] = scale * Q[b, :, h, :] K[b, :, h, :]^T, masked: NT, in-place heads
+            _gemm.gemm_batched(LAYOUT_NT, S, S, D, q.ptr, E, D, S * E, k.ptr, E, D, S * E,
+                               p.ptr, S, S * S, H * S * S, H, B, alpha=scale, epilogue=EPI_CAUSAL, flags=f_skip)
+            _call("gt_softmax", _vp(p.ptr), _vp(p.ptr), B * H * S, S, sm_mode)
+            # O[b, :, h, :] = P[b, h] V[b, :, h, :]: NN, output written straight into (B, S, H, d)
+            _gemm.gemm_batched(LAYOUT_NN, S, D, S, p.ptr, S, S * S, H * S * S, v.ptr, E, D, S * E,
+                               out.ptr, E, D, S * E, H, B, flags=f_lower)
 
         def _backward(g: "Tensor") -> None:
             need_qk = q.requires_grad or k.requires_grad

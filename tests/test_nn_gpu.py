@@ -110,9 +110,12 @@ def test_causal_attention_products(T, B, H, S, D):
     assert rel(tv.grad.numpy(), merge(ref["dv"])) < 1e-3
 
 
-def test_config2_full_size_attention_sampled_heads(T):
+@pytest.mark.parametrize("mode", ["materialized", "fused"])
+def test_config2_full_size_attention_sampled_heads(T, mode, monkeypatch):
     """Config 2 at full size (B=8, H=12, T=1024, d=64; Q, K, V ~ N(0,1), seed 2): forward and all
-    four backward products, checked on sampled (batch, head) slices against the float64 oracle."""
+    four backward products, checked on sampled (batch, head) slices against the float64 oracle.
+    Both forms of the forward: S, P, O as three launches, and the fused kernel."""
+    monkeypatch.setenv("GRADTUITY_ATTENTION", mode)
     rng = np.random.default_rng(2)
     B, H, S, D = 8, 12, 1024, 64
     E = H * D
