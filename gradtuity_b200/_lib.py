@@ -86,6 +86,9 @@ SIGNATURES = {
     "gt_selftest_bounded_wait": (c_int, [c_void_p, c_int64]),
     "gt_attention_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int64, c_int64, c_int64, c_int64, c_float, c_void_p]),
+    "gt_attention_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_int,
+                                      c_void_p]),
     "gt_launch_count": (c_int, [c_void_p, POINTER(c_int64)]),
     "gt_fill": (c_int, [c_void_p, c_void_p, c_float, c_int64]),
     "gt_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int]),

@@ -416,6 +416,501 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 }
 
+// ---- backward ----------------------------------------------------------------------------------
+// Both backward kernels hold two operand tiles for the whole item (Q and dO of the query block, or
+// K and V of the key block), stream the other side's tiles through a ring of three 32 KB slots, keep
+// S and dP (or their transposes) in tensor memory, and pass P / dS through one 64 KB shared-memory
+// tile that the following product reads as its K-major A operand.  The B operand of those products
+// (K, dO or Q, stored (rows, 64) with the head dimension contiguous) is MN-major: it is loaded a second
+// time with the five-dimensional map that lays it out in 32-wide chunks.
+constexpr int ATB_SLOTS = 3;
+constexpr int ATB_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATB_SLOTS * AT_SLOT_BYTES + AT_P_BYTES + 1024 + 512;
+
+struct BwdSmem {
+  uint32_t fix0, fix1, ring, tile;
+  uint8_t* tile_ptr;
+  uint32_t bar_fix_full, bar_fix_empty, bar_ring_full, bar_ring_empty, bar_sdp_full, bar_sdp_empty;
+  uint32_t bar_t1_full, bar_t1_empty, bar_t2_full, bar_t2_empty, bar_out_full, bar_out_empty, bar_group, bar_drain;
+  uint32_t* tmem_slot;
+  volatile int* abort_flag;
+  float* stats;
+};
+
+__device__ __forceinline__ BwdSmem carve_bwd(uint8_t* smem_raw) {
+  BwdSmem s;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  s.fix0 = base;
+  s.fix1 = base + AT_SLOT_BYTES;
+  s.ring = base + 2 * AT_SLOT_BYTES;
+  s.tile = s.ring + ATB_SLOTS * AT_SLOT_BYTES;
+  s.tile_ptr = aligned + (2 + ATB_SLOTS) * AT_SLOT_BYTES;
+  uint8_t* ctrl = s.tile_ptr + AT_P_BYTES;
+  const uint32_t bars = smem_u32(ctrl);
+  s.bar_fix_full = bars;        s.bar_fix_empty = bars + 8;
+  s.bar_ring_full = bars + 16;  s.bar_ring_empty = bars + 16 + 8 * ATB_SLOTS;
+  s.bar_sdp_full = bars + 64;   s.bar_sdp_empty = bars + 72;
+  s.bar_t1_full = bars + 80;    s.bar_t1_empty = bars + 88;
+  s.bar_t2_full = bars + 96;    s.bar_t2_empty = bars + 104;
+  s.bar_out_full = bars + 112;  s.bar_out_empty = bars + 120;
+  s.bar_group = bars + 128;     s.bar_drain = bars + 136;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 192);
+  s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 196);
+  s.stats = reinterpret_cast<float*>(s.tile_ptr);
+  return s;
+}
+
+__device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_arrivals) {
+  if (threadIdx.x == 0) {
+    mbar_init(sm.bar_fix_full, 1); mbar_init(sm.bar_fix_empty, 1);
+    for (int i = 0; i < ATB_SLOTS; ++i) { mbar_init(sm.bar_ring_full + 8 * i, 1); mbar_init(sm.bar_ring_empty + 8 * i, 1); }
+    mbar_init(sm.bar_sdp_full, 1); mbar_init(sm.bar_sdp_empty, AT_SOFTMAX_WARPS);
+    mbar_init(sm.bar_t1_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_t1_empty, 1);
+    mbar_init(sm.bar_t2_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_t2_empty, 1);
+    mbar_init(sm.bar_out_full, 1); mbar_init(sm.bar_out_empty, out_arrivals);
+    mbar_init(sm.bar_group, AT_SOFTMAX_WARPS); mbar_init(sm.bar_drain, 1);
+    *sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+}
+
+// One ring load: a K-major tile (two boxes of 32 columns) or an MN-major tile (one five-dimensional box).
+__device__ __forceinline__ bool bwd_ring_load(const BwdSmem& sm, const AttnParams& p, long long& ring_it, const CUtensorMap* map,
+                                              bool mn, int row0, int h, int b) {
+  const int slot = (int)(ring_it % ATB_SLOTS);
+  const uint32_t par = (uint32_t)((ring_it / ATB_SLOTS) & 1);
+  if (!mbar_wait(sm.bar_ring_empty + 8 * slot, par ^ 1u, sm.abort_flag, p.status)) return false;
+  const uint32_t dst = sm.ring + slot * AT_SLOT_BYTES, full = sm.bar_ring_full + 8 * slot;
+  mbar_expect_tx(full, AT_SLOT_BYTES);
+  if (mn) {
+    tma_load_5d(dst, map, full, 0, row0, 0, h, b);
+  } else {
+    tma_load_4d(dst, map, full, 0, row0, h, b);
+    tma_load_4d(dst + 16384, map, full, 32, row0, h, b);
+  }
+  ++ring_it;
+  return true;
+}
+__device__ __forceinline__ void bwd_ring_drain(const BwdSmem& sm, long long ring_it) {
+  const long long first = ring_it > ATB_SLOTS ? ring_it - ATB_SLOTS : 0;
+  for (long long r = first; r < ring_it; ++r) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(sm.bar_ring_full + 8 * (int)(r % ATB_SLOTS), (uint32_t)((r / ATB_SLOTS) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+  }
+}
+__device__ __forceinline__ bool bwd_ring_wait(const BwdSmem& sm, const AttnParams& p, long long ring_it) {
+  return mbar_wait(sm.bar_ring_full + 8 * (int)(ring_it % ATB_SLOTS), (uint32_t)((ring_it / ATB_SLOTS) & 1), sm.abort_flag, p.status);
+}
+
+// Item order of the key-block owner: key block 0 sees every query block, so it goes first.
+__device__ __forceinline__ void item_coords_kv(const AttnParams& p, int item, int& j, int& h, int& b) {
+  const int bh = p.B * p.H;
+  j = item / bh;
+  const int r = item % bh;
+  h = r % p.H;
+  b = r / p.H;
+}
+
+// dQ for one block of 128 queries; also delta = rowsum(dO * O).
+__global__ void __launch_bounds__(AT_THREADS, 1)
+gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const __grid_constant__ CUtensorMap map_kmn, const __grid_constant__ CUtensorMap map_dq,
+                      const AttnParams p, const int accumulate) {
+  extern __shared__ uint8_t smem_raw[];
+  const BwdSmem sm = carve_bwd(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  bwd_setup(sm, warp, 8);
+  const uint32_t tmem_base = *sm.tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      long long ring_it = 0; int f_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int i, h, b;
+        item_coords(p, item, i, h, b);
+        if (!mbar_wait(sm.bar_fix_empty, (uint32_t)(f_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        mbar_expect_tx(sm.bar_fix_full, 2 * AT_SLOT_BYTES);
+        tma_load_4d(sm.fix0, &map_q, sm.bar_fix_full, 0, i * AT_TILE, h, b);
+        tma_load_4d(sm.fix0 + 16384, &map_q, sm.bar_fix_full, 32, i * AT_TILE, h, b);
+        tma_load_4d(sm.fix1, &map_do, sm.bar_fix_full, 0, i * AT_TILE, h, b);
+        tma_load_4d(sm.fix1 + 16384, &map_do, sm.bar_fix_full, 32, i * AT_TILE, h, b);
+        ++f_it;
+        ok = bwd_ring_load(sm, p, ring_it, &map_k, false, 0, h, b) && bwd_ring_load(sm, p, ring_it, &map_v, false, 0, h, b);
+        for (int j = 0; ok && j <= i; ++j) {
+          if (j + 1 <= i)
+            ok = bwd_ring_load(sm, p, ring_it, &map_k, false, (j + 1) * AT_TILE, h, b) &&
+                 bwd_ring_load(sm, p, ring_it, &map_v, false, (j + 1) * AT_TILE, h, b);
+          if (ok) ok = bwd_ring_load(sm, p, ring_it, &map_kmn, true, j * AT_TILE, h, b);
+        }
+      }
+      if (!ok) bwd_ring_drain(sm, ring_it);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      long long ring_it = 0; int f_it = 0, sdp_it = 0, t1_it = 0, o_it = 0;
+      bool ok = true;
+      auto issue_sdp = [&]() -> bool {        // S = Q K^T and dP = dO V^T of the next key tile
+        if (!bwd_ring_wait(sm, p, ring_it)) return false;
+        if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(sdp_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
+        tc_fence_after();
+        int slot = (int)(ring_it % ATB_SLOTS);
+        mma_qk(tmem_base, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
+        tc_commit(sm.bar_ring_empty + 8 * slot);
+        ++ring_it;
+        if (!bwd_ring_wait(sm, p, ring_it)) return false;
+        tc_fence_after();
+        slot = (int)(ring_it % ATB_SLOTS);
+        mma_qk(tmem_base + 128u, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
+        tc_commit(sm.bar_ring_empty + 8 * slot);
+        ++ring_it;
+        tc_commit(sm.bar_sdp_full);
+        ++sdp_it;
+        return true;
+      };
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int i, h, b;
+        item_coords(p, item, i, h, b);
+        if (!mbar_wait(sm.bar_fix_full, (uint32_t)(f_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        ++f_it;
+        ok = issue_sdp();
+        for (int j = 0; ok && j <= i; ++j) {
+          if (j + 1 <= i) { ok = issue_sdp(); if (!ok) break; }
+          if (j == i) tc_commit(sm.bar_fix_empty);
+          if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
+          if (!mbar_wait(sm.bar_t1_full, (uint32_t)(t1_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (j == 0 && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          tc_fence_after();
+          const int slot = (int)(ring_it % ATB_SLOTS);
+          mma_pv(tmem_base + 256u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, j != 0);     // dQ (+)= dS K
+          tc_commit(sm.bar_ring_empty + 8 * slot);
+          tc_commit(sm.bar_t1_empty);
+          if (j == i) { tc_commit(sm.bar_out_full); ++o_it; }
+          ++ring_it; ++t1_it;
+        }
+      }
+      if (!ok) {
+        tc_commit(sm.bar_drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(sm.bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    const int q = warp & 3, eset = (warp - 2) >> 2;
+    const int r_local = q * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint8_t* const my_row = sm.tile_ptr + eset * 16384 + r_local * 128;
+    const uint32_t my_sub = sm.tile + (uint32_t)(eset * 16384 + q * 4096);
+    const int sw = r_local & 7;
+    const long long E = (long long)p.H * AT_D;
+    int sdp_it = 0, t1_it = 0, o_it = 0, g_it = 0;
+    bool ok = true;
+    auto group_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.bar_group);
+      const bool r = mbar_wait(sm.bar_group, (uint32_t)(g_it & 1), sm.abort_flag, p.status);
+      ++g_it;
+      return r;
+    };
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      int i, h, b;
+      item_coords(p, item, i, h, b);
+      const int row = i * AT_TILE + r_local;
+      // delta = rowsum(dO * O): each of the row's four threads takes 16 of the 64 columns
+      float part = 0.0f;
+      {
+        const long long off = ((long long)b * p.S + row) * E + (long long)h * AT_D + eset * 16;
+        const float4* o4 = reinterpret_cast<const float4*>(p.o + off);
+        const float4* g4 = reinterpret_cast<const float4*>(p.d_o + off);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float4 a = o4[t], g = g4[t];
+          part += (a.x * g.x + a.y * g.y) + (a.z * g.z + a.w * g.w);
+        }
+      }
+      const float lse2 = p.lse[((long long)b * p.H + h) * p.S + row] * AT_LOG2E;
+      // exchange through the (idle) dS tile: its last reader was the previous item's final dQ product
+      if (!mbar_wait(sm.bar_t1_empty, (uint32_t)(t1_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+      if (lane == 0) tma_store_wait_read<0>();
+      if (!group_sync()) { ok = false; break; }
+      sm.stats[eset * 128 + r_local] = part;
+      if (!group_sync()) { ok = false; break; }
+      const float delta = (sm.stats[r_local] + sm.stats[128 + r_local]) + (sm.stats[256 + r_local] + sm.stats[384 + r_local]);
+      if (eset == 0) p.delta[((long long)b * p.H + h) * p.S + row] = delta;
+      if (!group_sync()) { ok = false; break; }
+      for (int j = 0; j <= i; ++j) {
+        if (!mbar_wait(sm.bar_sdp_full, (uint32_t)(sdp_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const int col0 = j * AT_TILE + eset * 32;
+        const int nvalid = (j < i) ? 32 : row - col0 + 1;        // keys <= query
+        float pr[32], v[32];
+        tc_ld32(lane_base + (uint32_t)(eset * 32), v);
+        tc_wait_ld();
+#pragma unroll
+        for (int t = 0; t < 32; ++t) pr[t] = (t < nvalid) ? ex2(fmaf(v[t], p.scale_log2, -lse2)) : 0.0f;
+        tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
+        ++sdp_it;
+        if (j > 0 && !mbar_wait(sm.bar_t1_empty, (uint32_t)(t1_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          float4 x;
+          x.x = to_tf32(pr[4 * g] * (v[4 * g] - delta) * p.scale);
+          x.y = to_tf32(pr[4 * g + 1] * (v[4 * g + 1] - delta) * p.scale);
+          x.z = to_tf32(pr[4 * g + 2] * (v[4 * g + 2] - delta) * p.scale);
+          x.w = to_tf32(pr[4 * g + 3] * (v[4 * g + 3] - delta) * p.scale);
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = x;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_t1_full);
+        ++t1_it;
+      }
+      if (!ok) break;
+      if (!mbar_wait(sm.bar_out_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+      ++o_it;
+      tc_fence_after();
+      if (eset < 2) {
+        float v[32];
+        tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), v);
+        tc_wait_ld();
+        tc_fence_before();
+        if (lane == 0) tma_store_wait_read<0>();
+        __syncwarp();
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_4d(&map_dq, my_sub, eset * 32, i * AT_TILE + q * 32, h, b, accumulate != 0);
+          mbar_arrive(sm.bar_out_empty);
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+// dK and dV for one block of 128 keys: everything transposed, so that a thread owns a key.
+__global__ void __launch_bounds__(AT_THREADS, 1)
+gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                       const __grid_constant__ CUtensorMap map_qmn, const __grid_constant__ CUtensorMap map_domn,
+                       const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
+                       const AttnParams p, const int acc_dk, const int acc_dv) {
+  extern __shared__ uint8_t smem_raw[];
+  const BwdSmem sm = carve_bwd(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  bwd_setup(sm, warp, AT_SOFTMAX_WARPS);
+  const uint32_t tmem_base = *sm.tmem_slot;
+  const int nblk = p.nblk;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      long long ring_it = 0; int f_it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int j, h, b;
+        item_coords_kv(p, item, j, h, b);
+        if (!mbar_wait(sm.bar_fix_empty, (uint32_t)(f_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        mbar_expect_tx(sm.bar_fix_full, 2 * AT_SLOT_BYTES);
+        tma_load_4d(sm.fix0, &map_k, sm.bar_fix_full, 0, j * AT_TILE, h, b);
+        tma_load_4d(sm.fix0 + 16384, &map_k, sm.bar_fix_full, 32, j * AT_TILE, h, b);
+        tma_load_4d(sm.fix1, &map_v, sm.bar_fix_full, 0, j * AT_TILE, h, b);
+        tma_load_4d(sm.fix1 + 16384, &map_v, sm.bar_fix_full, 32, j * AT_TILE, h, b);
+        ++f_it;
+        ok = bwd_ring_load(sm, p, ring_it, &map_q, false, j * AT_TILE, h, b) && bwd_ring_load(sm, p, ring_it, &map_do, false, j * AT_TILE, h, b);
+        for (int i = j; ok && i < nblk; ++i) {
+          if (i + 1 < nblk)
+            ok = bwd_ring_load(sm, p, ring_it, &map_q, false, (i + 1) * AT_TILE, h, b) &&
+                 bwd_ring_load(sm, p, ring_it, &map_do, false, (i + 1) * AT_TILE, h, b);
+          if (ok) ok = bwd_ring_load(sm, p, ring_it, &map_domn, true, i * AT_TILE, h, b) &&
+                       bwd_ring_load(sm, p, ring_it, &map_qmn, true, i * AT_TILE, h, b);
+        }
+      }
+      if (!ok) bwd_ring_drain(sm, ring_it);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      long long ring_it = 0; int f_it = 0, sdp_it = 0, t_it = 0, o_it = 0;
+      bool ok = true;
+      auto issue_sdp = [&]() -> bool {        // S^T = K Q^T and dP^T = V dO^T of the next query tile
+        if (!bwd_ring_wait(sm, p, ring_it)) return false;
+        if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(sdp_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
+        tc_fence_after();
+        int slot = (int)(ring_it % ATB_SLOTS);
+        mma_qk(tmem_base, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
+        tc_commit(sm.bar_ring_empty + 8 * slot);
+        ++ring_it;
+        if (!bwd_ring_wait(sm, p, ring_it)) return false;
+        tc_fence_after();
+        slot = (int)(ring_it % ATB_SLOTS);
+        mma_qk(tmem_base + 128u, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
+        tc_commit(sm.bar_ring_empty + 8 * slot);
+        ++ring_it;
+        tc_commit(sm.bar_sdp_full);
+        ++sdp_it;
+        return true;
+      };
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int j, h, b;
+        item_coords_kv(p, item, j, h, b);
+        if (!mbar_wait(sm.bar_fix_full, (uint32_t)(f_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        ++f_it;
+        ok = issue_sdp();
+        for (int i = j; ok && i < nblk; ++i) {
+          if (i + 1 < nblk) { ok = issue_sdp(); if (!ok) break; }
+          if (i == nblk - 1) tc_commit(sm.bar_fix_empty);
+          // dV (+)= P^T dO
+          if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
+          if (!mbar_wait(sm.bar_t1_full, (uint32_t)(t_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (i == j && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          tc_fence_after();
+          int slot = (int)(ring_it % ATB_SLOTS);
+          mma_pv(tmem_base + 256u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, i != j);
+          tc_commit(sm.bar_ring_empty + 8 * slot);
+          tc_commit(sm.bar_t1_empty);
+          ++ring_it;
+          // dK (+)= dS^T Q
+          if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
+          if (!mbar_wait(sm.bar_t2_full, (uint32_t)(t_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          tc_fence_after();
+          slot = (int)(ring_it % ATB_SLOTS);
+          mma_pv(tmem_base + 320u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, i != j);
+          tc_commit(sm.bar_ring_empty + 8 * slot);
+          tc_commit(sm.bar_t2_empty);
+          if (i == nblk - 1) { tc_commit(sm.bar_out_full); ++o_it; }
+          ++ring_it; ++t_it;
+        }
+      }
+      if (!ok) {
+        tc_commit(sm.bar_drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(sm.bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    const int q = warp & 3, eset = (warp - 2) >> 2;
+    const int r_local = q * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint8_t* const my_row = sm.tile_ptr + eset * 16384 + r_local * 128;
+    const uint32_t my_sub = sm.tile + (uint32_t)(eset * 16384 + q * 4096);
+    const int sw = r_local & 7;
+    int sdp_it = 0, t_it = 0, o_it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      int j, h, b;
+      item_coords_kv(p, item, j, h, b);
+      const float* lse_bh = p.lse + ((long long)b * p.H + h) * p.S;
+      const float* delta_bh = p.delta + ((long long)b * p.H + h) * p.S;
+      for (int i = j; i < nblk; ++i) {
+        if (!mbar_wait(sm.bar_sdp_full, (uint32_t)(sdp_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const int q0 = i * AT_TILE + eset * 32;                   // query of this chunk's first column
+        const int first_valid = (i > j) ? 0 : r_local - eset * 32;   // columns (queries) >= this thread's key
+        const float4* l4 = reinterpret_cast<const float4*>(lse_bh + q0);
+        const float4* d4 = reinterpret_cast<const float4*>(delta_bh + q0);
+        float pr[32], v[32];
+        tc_ld32(lane_base + (uint32_t)(eset * 32), v);
+        tc_wait_ld();
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 l = l4[g];
+          pr[4 * g] = (4 * g >= first_valid) ? ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E)) : 0.0f;
+          pr[4 * g + 1] = (4 * g + 1 >= first_valid) ? ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E)) : 0.0f;
+          pr[4 * g + 2] = (4 * g + 2 >= first_valid) ? ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E)) : 0.0f;
+          pr[4 * g + 3] = (4 * g + 3 >= first_valid) ? ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E)) : 0.0f;
+        }
+        tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
+        ++sdp_it;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 d = d4[g];
+          v[4 * g] = pr[4 * g] * (v[4 * g] - d.x) * p.scale;
+          v[4 * g + 1] = pr[4 * g + 1] * (v[4 * g + 1] - d.y) * p.scale;
+          v[4 * g + 2] = pr[4 * g + 2] * (v[4 * g + 2] - d.z) * p.scale;
+          v[4 * g + 3] = pr[4 * g + 3] * (v[4 * g + 3] - d.w) * p.scale;
+        }
+        // P^T -> tile (free once the previous tile's dK product and this warp's own stores have read it)
+        if (!mbar_wait(sm.bar_t2_empty, (uint32_t)(t_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        if (i == j) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
+              make_float4(to_tf32(pr[4 * g]), to_tf32(pr[4 * g + 1]), to_tf32(pr[4 * g + 2]), to_tf32(pr[4 * g + 3]));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_t1_full);
+        // dS^T -> the same tile, once the dV product has read P^T
+        if (!mbar_wait(sm.bar_t1_empty, (uint32_t)(t_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
+              make_float4(to_tf32(v[4 * g]), to_tf32(v[4 * g + 1]), to_tf32(v[4 * g + 2]), to_tf32(v[4 * g + 3]));
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_t2_full);
+        ++t_it;
+      }
+      if (!ok) break;
+      if (!mbar_wait(sm.bar_out_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+      ++o_it;
+      tc_fence_after();
+      {
+        // chunks 0, 1: dV columns 0-31, 32-63; chunks 2, 3: dK columns 0-31, 32-63
+        float v[32];
+        tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), v);
+        tc_wait_ld();
+        tc_fence_before();
+#pragma unroll
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          if (eset < 2) tma_store_4d(&map_dv, my_sub, eset * 32, j * AT_TILE + q * 32, h, b, acc_dv != 0);
+          else tma_store_4d(&map_dk, my_sub, (eset - 2) * 32, j * AT_TILE + q * 32, h, b, acc_dk != 0);
+          mbar_arrive(sm.bar_out_empty);
+        }
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 int check_attn_args(gt_ctx* ctx, const void* q, const void* k, const void* v, int64_t B, int64_t S, int64_t H, int64_t D) {
   if (!ctx || !q || !k || !v || B <= 0 || S <= 0 || H <= 0) return GT_ERR_INVALID_ARG;
   if (D != AT_D) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "fused attention supports head dimension 64, got %lld", (long long)D);
@@ -464,5 +959,51 @@ extern "C" int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* 
   gt_attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, mp, mo, p);
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
+  return GT_OK;
+}
+
+extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* dv, const float* d_o, const float* q,
+                                     const float* k, const float* v, const float* o, const float* lse, float* delta,
+                                     int64_t B, int64_t S, int64_t H, int64_t D, float scale, int acc_dq, int acc_dk,
+                                     int acc_dv, void* stream_) {
+  int rc = check_attn_args(ctx, q, k, v, B, S, H, D);
+  if (rc != GT_OK) return rc;
+  if (!dq || !dk || !dv || !d_o || !o || !lse || !delta) return GT_ERR_INVALID_ARG;
+  if ((((uintptr_t)dq | (uintptr_t)dk | (uintptr_t)dv | (uintptr_t)d_o | (uintptr_t)o | (uintptr_t)lse | (uintptr_t)delta) & 15) != 0)
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "fused attention backward needs 16-byte aligned buffers");
+  cudaStream_t stream = stream_ ? (cudaStream_t)stream_ : ctx->stream;
+  const long long E = H * D;
+  auto view = [&](const float* ptr) { return OperandView{ptr, S, D, E, D, S * E}; };
+  CUtensorMap mq, mk, mv, mdo, mkmn, mqmn, mdomn, mdq, mdk, mdv;
+  if ((rc = encode_map(ctx, &mq, view(q), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mk, view(k), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mv, view(v), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mdo, view(d_o), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
+  if (!encode_map_mn5(ctx, &mkmn, view(k), 2, H, B, false, AT_TILE) || !encode_map_mn5(ctx, &mqmn, view(q), 2, H, B, false, AT_TILE) ||
+      !encode_map_mn5(ctx, &mdomn, view(d_o), 2, H, B, false, AT_TILE))
+    GT_FAIL(ctx, GT_ERR_CUDA, "fused attention backward: a tensor map was refused");
+  if ((rc = encode_map(ctx, &mdq, view(dq), 32, 32, H, B, false, true)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mdk, view(dk), 32, 32, H, B, false, true)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mdv, view(dv), 32, 32, H, B, false, true)) != GT_OK) return rc;
+  AttnParams p;
+  p.S = (int)S; p.H = (int)H; p.B = (int)B;
+  p.nblk = (int)(S / AT_TILE);
+  p.num_items = (int)(B * H * p.nblk);
+  p.scale = scale; p.scale_log2 = scale * AT_LOG2E;
+  p.write_p = 0;
+  p.lse = const_cast<float*>(lse); p.delta = delta; p.o = o; p.d_o = d_o;
+  p.status = ctx->d_status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    GT_CUDA_OK(ctx, cudaFuncSetAttribute(gt_attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATB_SMEM_BYTES));
+    GT_CUDA_OK(ctx, cudaFuncSetAttribute(gt_attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATB_SMEM_BYTES));
+    attr_set = true;
+  }
+  const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
+  gt_attn_bwd_dq_kernel<<<grid, AT_THREADS, ATB_SMEM_BYTES, stream>>>(mq, mdo, mk, mv, mkmn, mdq, p, acc_dq);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  gt_attn_bwd_dkv_kernel<<<grid, AT_THREADS, ATB_SMEM_BYTES, stream>>>(mk, mv, mq, mdo, mqmn, mdomn, mdk, mdv, p, acc_dk, acc_dv);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 2;
   return GT_OK;
 }

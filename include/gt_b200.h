@@ -191,6 +191,17 @@ int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_
 int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* lse, const float* q,
                          const float* k, const float* v, int64_t B, int64_t T, int64_t H,
                          int64_t D, float scale, void* stream);
+/* Backward of the above from q, k, v, o, lse and the upstream gradient d_o: two launches, one that
+ * owns blocks of 128 queries (dQ, and delta (B, H, T) = rowsum(d_o * o), a scratch output the
+ * second launch reads) and one that owns blocks of 128 keys (dK, dV).  P is recomputed from the
+ * saved statistics; no (B, H, T, T) buffer is read or written.  acc_* = 1 adds to the gradient
+ * buffer (dX += ..., the reference's accumulation contract, gradtuity/tensor.py:152-161), 0
+ * overwrites it.                                                                             */
+int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* dv, const float* d_o,
+                          const float* q, const float* k, const float* v, const float* o,
+                          const float* lse, float* delta, int64_t B, int64_t T, int64_t H,
+                          int64_t D, float scale, int acc_dq, int acc_dk, int acc_dv,
+                          void* stream);
 
 /* Which kernel a call with these arguments would run: 0 = tcgen05/TMA kernel, 1 = fp32 FMA
  * kernel.  No launch.                                                                       */

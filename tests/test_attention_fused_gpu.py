@@ -86,3 +86,49 @@ def test_unsupported_shapes_are_refused(gt):
     rc = lib.gt_attention_forward(ctx, c_void_p(buf.ptr), None, None, c_void_p(buf.ptr), c_void_p(buf.ptr),
                                   c_void_p(buf.ptr), 1, 128, 2, 32, c_float(0.125), None)
     assert rc == _lib.GT_ERR_UNSUPPORTED
+
+
+def run_backward(q, k, v, do, B, S, H, accumulate=False):
+    from gradtuity_b200 import _lib
+
+    lib, ctx = _lib.load_library(), _lib.context()
+    scale = 1.0 / np.sqrt(D)
+    bq, bk, bv, bdo = (U.DeviceBuffer(a) for a in (q, k, v, do))
+    bo = U.DeviceBuffer(np.zeros((B, S, H * D), np.float32))
+    bl = U.DeviceBuffer(np.zeros((B, H, S), np.float32))
+    bd = U.DeviceBuffer(np.full((B, H, S), np.nan, np.float32))
+    _lib.check(lib.gt_attention_forward(ctx, c_void_p(bo.ptr), None, c_void_p(bl.ptr), c_void_p(bq.ptr), c_void_p(bk.ptr),
+                                        c_void_p(bv.ptr), B, S, H, D, c_float(scale), None), "gt_attention_forward")
+    init = np.ones((B, S, H * D), np.float32) if accumulate else np.full((B, S, H * D), np.nan, np.float32)
+    gq, gk, gv = (U.DeviceBuffer(init) for _ in range(3))
+    acc = 1 if accumulate else 0
+    _lib.check(lib.gt_attention_backward(ctx, c_void_p(gq.ptr), c_void_p(gk.ptr), c_void_p(gv.ptr), c_void_p(bdo.ptr),
+                                         c_void_p(bq.ptr), c_void_p(bk.ptr), c_void_p(bv.ptr), c_void_p(bo.ptr),
+                                         c_void_p(bl.ptr), c_void_p(bd.ptr), B, S, H, D, c_float(scale), acc, acc, acc, None),
+               "gt_attention_backward")
+    _lib.device_status()
+    shape = (B, S, H * D)
+    return gq.read(shape), gk.read(shape), gv.read(shape), bd.read((B, H, S)), bo.read(shape)
+
+
+@pytest.mark.parametrize("B,H,S", [(1, 1, 128), (2, 3, 256), (1, 2, 512), (2, 12, 1024)])
+def test_backward_matches_oracle(gt, B, H, S):
+    rng = np.random.default_rng(7 * S + H)
+    q, k, v, do = (rng.standard_normal((B, S, H * D)).astype(np.float32) for _ in range(4))
+    dq, dk, dv, delta, o = run_backward(q, k, v, do, B, S, H)
+    ref = O.attention_forward_backward(*(heads(a, B, S, H) for a in (q, k, v, do)))
+    ref_delta = (heads(do, B, S, H).astype(np.float64) * ref["o"]).sum(-1)
+    assert np.allclose(delta, ref_delta, rtol=0, atol=5e-3 * np.abs(ref_delta).max())
+    assert O.rel_frobenius(dv, merge(ref["dv"], B, S, H)) <= 1e-3
+    assert O.rel_frobenius(dq, merge(ref["dq"], B, S, H)) <= 2e-3
+    assert O.rel_frobenius(dk, merge(ref["dk"], B, S, H)) <= 2e-3
+
+
+def test_backward_accumulates_into_existing_gradients(gt):
+    rng = np.random.default_rng(3)
+    B, H, S = 1, 2, 256
+    q, k, v, do = (rng.standard_normal((B, S, H * D)).astype(np.float32) for _ in range(4))
+    dq0, dk0, dv0, _, _ = run_backward(q, k, v, do, B, S, H)
+    dq1, dk1, dv1, _, _ = run_backward(q, k, v, do, B, S, H, accumulate=True)
+    for a0, a1 in ((dq0, dq1), (dk0, dk1), (dv0, dv1)):
+        assert np.allclose(a1 - 1.0, a0, rtol=0, atol=1e-5 * max(1.0, np.abs(a0).max()))
