@@ -642,14 +642,48 @@ class Tensor:
         f_lower = GEMM_A_LOWER if trimmed else 0
         f_upper = GEMM_AT_LOWER if trimmed else 0
         sm_mode = 2 if trimmed else 1
-        p = empty_tensor((B, H, S, S))
         out = empty_tensor((B, S, E))
-        # GRADTUITY_ATTENTION=materialized keeps the three-launch form (S, then P, then O) everywhere;
-        # otherwise head dimension 64 with S a multiple of 128 takes the fused forward kernel, which
-        # computes the same P (written out for the backward) and O in one launch without storing S.
+        # GRADTUITY_ATTENTION selects the form when the head dimension is 64, S a multiple of 128 and the
+        # GEMM precision tf32:
+        #   flash (default)   fused forward and backward kernels; no (B, H, S, S) tensor exists, only each
+        #                     row's log-sum-exp is kept and P is recomputed in the backward;
+        #   fused_forward     fused forward that also writes P, backward as four batched GEMMs + softmax backward;
+        #   materialized      S, then P, then O as three launches (the reference's structure), as for every
+        #                     other shape.
         from ._lib import PREC_TF32
-        fused = (trimmed and D == 64 and S % 128 == 0 and _gemm.default_precision() == PREC_TF32
-                 and os.environ.get("GRADTUITY_ATTENTION", "fused") != "materialized")
+        mode = os.environ.get("GRADTUITY_ATTENTION", "flash")
+        if mode not in ("flash", "fused_forward", "materialized"):
+            raise ValueError(f"GRADTUITY_ATTENTION must be flash, fused_forward or materialized, got {mode!r}")
+        fusable = trimmed and D == 64 and S % 128 == 0 and _gemm.default_precision() == PREC_TF32
+        if fusable and mode == "flash":
+            lse = empty_tensor((B, H, S))
+            _call("gt_attention_forward", _vp(out.ptr), None, _vp(lse.ptr), _vp(q.ptr), _vp(k.ptr), _vp(v.ptr),
+                  B, S, H, D, scale, None)
+            o_st = out._st          # the closure keeps the buffer, not the tensor (no reference cycle)
+
+            def _backward_flash(g: "Tensor") -> None:
+                if not (q.requires_grad or k.requires_grad or v.requires_grad):
+                    return
+                targets, scratch = [], []
+                for t in (q, k, v):
+                    if t.requires_grad:
+                        targets.append(grad_target(t))
+                    else:
+                        st = alloc_storage(B * S * E * F32)
+                        scratch.append(st)
+                        targets.append((st.ptr, False))
+                delta = alloc_storage(B * H * S * F32)
+                _call("gt_attention_backward", _vp(targets[0][0]), _vp(targets[1][0]), _vp(targets[2][0]), _vp(g.ptr),
+                      _vp(q.ptr), _vp(k.ptr), _vp(v.ptr), _vp(o_st.ptr), _vp(lse.ptr), _vp(delta.ptr), B, S, H, D, scale,
+                      int(targets[0][1]), int(targets[1][1]), int(targets[2][1]), None)
+                delta.free()
+                for st in scratch:
+                    st.free()
+
+            out._set_graph(parents=(q, k, v), backward_fn=_backward_flash)
+            return out
+        p = empty_tensor((B, H, S, S))
+        fused = fusable and mode == "fused_forward"
         if fused:
             lse = empty_tensor((B, H, S))
             _call("gt_attention_forward", _vp(out.ptr), _vp(p.ptr), _vp(lse.ptr), _vp(q.ptr), _vp(k.ptr), _vp(v.ptr),

@@ -110,7 +110,7 @@ def test_causal_attention_products(T, B, H, S, D):
     assert rel(tv.grad.numpy(), merge(ref["dv"])) < 1e-3
 
 
-@pytest.mark.parametrize("mode", ["materialized", "fused"])
+@pytest.mark.parametrize("mode", ["materialized", "fused_forward", "flash"])
 def test_config2_full_size_attention_sampled_heads(T, mode, monkeypatch):
     """Config 2 at full size (B=8, H=12, T=1024, d=64; Q, K, V ~ N(0,1), seed 2): forward and all
     four backward products, checked on sampled (batch, head) slices against the float64 oracle.
