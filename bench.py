@@ -39,8 +39,8 @@ ALG_BYTES = 4.0 * (M * K + K * N + M * N)
 # Rows of A used by the CPU legs: same K and N, a quarter of M (275 GFLOP per pass).
 CPU_SAMPLE_ROWS = 2048
 # DRAM bytes (read + write) per launch of the 8192^3 GEMM kernel, from the ncu capture summarised in
-# profiles/gemm_umma_nn_tf32_8192_dram_traffic.md (2.278 GB read + 0.254 GB written).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2531000000
+# profiles/gemm_umma256_nn_tf32_8192_dram_traffic.md (1.779 GB read + 0.237 GB written).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2015737344
 
 
 def _peaks():
@@ -426,6 +426,14 @@ def run_attn(args) -> dict:
     # fused forward: Q, K, V read, O written (+ the lower-triangular half of P when it is requested)
     cases["fused forward, P written"] = (lambda: fused(p.ptr), 4.0 * B * H * (4 * S * D + S * (S + 128) // 2))
     cases["fused forward, no P"] = (lambda: fused(0), 4.0 * B * H * 4 * S * D)
+    dq_, dk_, dv_ = (Tensor._zeros((B, S, E)) for _ in range(3))
+    delta = Tensor._zeros((B, H, S))
+    # fused backward (two launches): q, k, v, o, dO read (K, Q, dO a second time in the other layout), dq, dk, dv written
+    cases["fused backward (dQ + dK/dV kernels)"] = (
+        lambda: _lib.check(lib.gt_attention_backward(ctx, c_void_p(dq_.ptr), c_void_p(dk_.ptr), c_void_p(dv_.ptr), c_void_p(do.ptr),
+                                                     c_void_p(q.ptr), c_void_p(k.ptr), c_void_p(v.ptr), c_void_p(o.ptr),
+                                                     c_void_p(lse.ptr), c_void_p(delta.ptr), B, S, H, D, c_float(0.125), 0, 0, 0, None),
+                           "gt_attention_backward"), 4.0 * B * H * 8 * S * D)
     out = {"attn": True, "config": "B=8 H=12 T=1024 d=64, heads read in place from (B,T,H*d)", "hbm_peak_gbs": hbm, "cases": {}}
     for name, (fn, nbytes) in cases.items():
         for _ in range(args.warmup):
