@@ -200,7 +200,79 @@ __global__ void __launch_bounds__(256) repack_rows_kernel(float* __restrict__ ds
   }
 }
 
+// im2col for conv2d: col[(n, ho, wo), (c, kh, kw)] = x[n, c, ho*s - p + kh, wo*s - p + kw], zero outside
+// the image; rows of col are ld floats apart (gradtuity/kernels_cuda/conv_kernels.py im2col_kernel_2d,
+// as launched from gradtuity/tensor.py:1955-1972).
+__global__ void __launch_bounds__(256) im2col_kernel(float* __restrict__ col, const float* __restrict__ x, long long rows,
+                                                     int C, int H, int W, int kH, int kW, int stride, int pad,
+                                                     int H_out, int W_out, int ncols, long long ld) {
+  const long long total = rows * ncols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / ncols;
+    const int cc = (int)(i - r * ncols);
+    const int kw = cc % kW, kh = (cc / kW) % kH, c = cc / (kW * kH);
+    const int wo = (int)(r % W_out), ho = (int)((r / W_out) % H_out);
+    const long long n = r / ((long long)W_out * H_out);
+    const int h = ho * stride - pad + kh, w = wo * stride - pad + kw;
+    float v = 0.0f;
+    if (h >= 0 && h < H && w >= 0 && w < W) v = x[((n * C + c) * H + h) * (long long)W + w];
+    col[r * ld + cc] = v;
+  }
+}
+// col2im, gather form (no atomics): dx[n, c, h, w] += sum over the (kh, kw) whose output position exists
+// (gradtuity/tensor.py:2139-2158 launches the scatter form).
+__global__ void __launch_bounds__(256) col2im_kernel(float* __restrict__ dx, const float* __restrict__ dcol, long long N,
+                                                     int C, int H, int W, int kH, int kW, int stride, int pad,
+                                                     int H_out, int W_out, long long ld, int accumulate) {
+  const long long total = N * C * H * W;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int w = (int)(i % W), h = (int)((i / W) % H), c = (int)((i / ((long long)W * H)) % C);
+    const long long n = i / ((long long)W * H * C);
+    float s = 0.0f;
+    for (int kh = 0; kh < kH; ++kh) {
+      const int hs = h + pad - kh;
+      if (hs < 0 || hs % stride != 0) continue;
+      const int ho = hs / stride;
+      if (ho >= H_out) continue;
+      for (int kw = 0; kw < kW; ++kw) {
+        const int ws = w + pad - kw;
+        if (ws < 0 || ws % stride != 0) continue;
+        const int wo = ws / stride;
+        if (wo >= W_out) continue;
+        s += dcol[((n * H_out + ho) * W_out + wo) * ld + ((long long)c * kH + kh) * kW + kw];
+      }
+    }
+    dx[i] = accumulate ? dx[i] + s : s;
+  }
+}
+
 }  // namespace
+
+extern "C" int gt_im2col(gt_ctx* ctx, float* col, int64_t ld_col, const float* x, int64_t N, int64_t C, int64_t H, int64_t W,
+                         int64_t kH, int64_t kW, int64_t stride, int64_t pad) {
+  if (!ctx || !col || !x || N <= 0 || C <= 0 || H <= 0 || W <= 0 || kH <= 0 || kW <= 0 || stride <= 0 || pad < 0) return GT_ERR_INVALID_ARG;
+  const int64_t H_out = (H + 2 * pad - kH) / stride + 1, W_out = (W + 2 * pad - kW) / stride + 1;
+  const int64_t ncols = C * kH * kW;
+  if (H + 2 * pad < kH || W + 2 * pad < kW || ld_col < ncols || ncols > 0x7fffffff || H > 0x7fffffff || W > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  const long long rows = N * H_out * W_out;
+  im2col_kernel<<<ew_blocks(ctx, rows * ncols), EW_THREADS, 0, ctx->stream>>>(col, x, rows, (int)C, (int)H, (int)W, (int)kH, (int)kW,
+                                                                             (int)stride, (int)pad, (int)H_out, (int)W_out, (int)ncols, ld_col);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
+
+extern "C" int gt_col2im(gt_ctx* ctx, float* dx, const float* dcol, int64_t ld_col, int64_t N, int64_t C, int64_t H, int64_t W,
+                         int64_t kH, int64_t kW, int64_t stride, int64_t pad, int accumulate) {
+  if (!ctx || !dx || !dcol || N <= 0 || C <= 0 || H <= 0 || W <= 0 || kH <= 0 || kW <= 0 || stride <= 0 || pad < 0) return GT_ERR_INVALID_ARG;
+  const int64_t H_out = (H + 2 * pad - kH) / stride + 1, W_out = (W + 2 * pad - kW) / stride + 1;
+  if (H + 2 * pad < kH || W + 2 * pad < kW || ld_col < C * kH * kW || H > 0x7fffffff || W > 0x7fffffff || C > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  col2im_kernel<<<ew_blocks(ctx, N * C * H * W), EW_THREADS, 0, ctx->stream>>>(dx, dcol, N, (int)C, (int)H, (int)W, (int)kH, (int)kW,
+                                                                               (int)stride, (int)pad, (int)H_out, (int)W_out, ld_col, accumulate);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
 
 extern "C" int gt_repack_rows(gt_ctx* ctx, float* dst, int64_t ld_dst, const float* src, int64_t ld_src, int64_t rows, int64_t cols) {
   if (!ctx || !dst || !src || rows <= 0 || cols <= 0 || cols > 0x7fffffff || ld_dst < cols || ld_src < cols) return GT_ERR_INVALID_ARG;

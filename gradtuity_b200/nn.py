@@ -272,6 +272,30 @@ class CausalSelfAttention(Module):
         return f"CausalSelfAttention(embed_dim={self.embed_dim}, num_heads={self.num_heads})"
 
 
+class Conv2d(Module):
+    """2D convolution layer: weight (out_channels, in_channels, kH, kW) ~ N(0, 2 / (in_channels kH kW)), bias
+    zeros; forward is `Tensor.conv2d` (gradtuity/nn.py:572-629)."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride: int = 1, padding: int = 0) -> None:
+        super().__init__()
+        kH, kW = (kernel_size, kernel_size) if isinstance(kernel_size, int) else kernel_size
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.kernel_size = (kH, kW)
+        self.stride = stride
+        self.padding = padding
+        std = (2.0 / (in_channels * kH * kW)) ** 0.5
+        self.weight = randn((out_channels, in_channels, kH, kW), requires_grad=True, std=std)
+        self.bias = zeros((out_channels,), requires_grad=True)
+
+    def __call__(self, x: Tensor) -> Tensor:
+        return x.conv2d(self.weight, self.bias, stride=self.stride, padding=self.padding)
+
+    def __repr__(self) -> str:
+        return (f"Conv2d({self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, "
+                f"stride={self.stride}, padding={self.padding})")
+
+
 class LayerNorm(Module):
     """LayerNorm over the last dimension; gamma ones, beta zeros (gradtuity/nn.py:662-710)."""
 

@@ -860,6 +860,78 @@ class Tensor:
         out._set_graph(parents=(self, targets), backward_fn=_backward)
         return out
 
+    def conv2d(self, weight: "Tensor", bias: "Tensor", stride: int = 1, padding: int = 0) -> "Tensor":
+        """2D convolution as im2col + GEMM: input (N, C_in, H, W), weight (C_out, C_in, kH, kW), bias
+        (C_out,) -> (N, C_out, H_out, W_out), H_out = (H + 2*padding - kH) // stride + 1
+        (gradtuity/tensor.py:1906-2167; same argument checks and messages).
+
+        Forward: col = im2col(x), Y = col @ W_flat^T + b as one NT GEMM with the bias in the
+        epilogue, then (N, H_out*W_out, C_out) -> (N, C_out, H_out*W_out).  Backward: db = column sums
+        of dY, dW += dY^T @ col (TN, written straight in the weight's (C_out, C_in*kH*kW) layout),
+        dcol = dY @ W_flat (NN), dx += col2im(dcol).  Two things differ from the reference on purpose:
+        its forward passes the strides of W_flat where those of W_flat^T belong (reads past the
+        weight, noted in gradtuity/tests/test_nn.py:316-322), and it returns the (N*H_out*W_out, C_out)
+        product re-viewed as (N, C_out, H_out, W_out) without transposing; this is the NCHW convolution."""
+        x = self
+        if x.ndim != 4:
+            raise ValueError(f"conv2d requires 4D input, got shape {x._shape}")
+        if weight.ndim != 4:
+            raise ValueError(f"conv2d weight must be 4D, got shape {weight._shape}")
+        if bias.ndim != 1:
+            raise ValueError(f"conv2d bias must be 1D, got shape {bias._shape}")
+        N, C_in, H, W = x._shape
+        C_out, C_in_w, kH, kW = weight._shape
+        if C_in != C_in_w:
+            raise ValueError(f"conv2d input channels {C_in} != weight channels {C_in_w}")
+        if bias._shape[0] != C_out:
+            raise ValueError(f"conv2d bias size {bias._shape[0]} != out_channels {C_out}")
+        H_out = (H + 2 * padding - kH) // stride + 1
+        W_out = (W + 2 * padding - kW) // stride + 1
+        if H_out <= 0 or W_out <= 0:
+            raise ValueError(f"conv2d output spatial size invalid: H_out={H_out}, W_out={W_out}")
+        from ._lib import EPI_BIAS
+        rows, ncols, hw = N * H_out * W_out, C_in * kH * kW, H_out * W_out
+        ld_col = (ncols + 3) // 4 * 4                     # 16-byte aligned rows for the GEMMs that read col
+        col = alloc_storage(rows * ld_col * F32, zero=ld_col != ncols)
+        _call("gt_im2col", _vp(col.ptr), ld_col, _vp(x.ptr), N, C_in, H, W, kH, kW, stride, padding)
+        y_flat = alloc_storage(rows * C_out * F32)
+        _gemm.gemm(LAYOUT_NT, rows, C_out, ncols, col.ptr, ld_col, weight.ptr, ncols, y_flat.ptr, C_out,
+                   bias_ptr=bias.ptr, epilogue=EPI_BIAS)
+        out = empty_tensor((N, C_out, H_out, W_out))
+        _call("gt_transpose12", _vp(out.ptr), _vp(y_flat.ptr), N, hw, C_out, 1, 0)
+        y_flat.free()
+        if not (x.requires_grad or weight.requires_grad):
+            col.free()
+            col = None
+
+        def _backward(g: "Tensor") -> None:
+            nonlocal col
+            with temp_storage(rows * C_out * F32) as dy:
+                _call("gt_transpose12", _vp(dy.ptr), _vp(g.ptr), N, C_out, hw, 1, 0)      # (N, C_out, HW) -> (N*HW, C_out)
+                if bias.requires_grad:
+                    ensure_grad(bias)
+                    _call("gt_colsum_acc", _vp(bias.grad.ptr), _vp(dy.ptr), rows, C_out, C_out)
+                if weight.requires_grad:
+                    if col is None:
+                        col = alloc_storage(rows * ld_col * F32, zero=ld_col != ncols)
+                        _call("gt_im2col", _vp(col.ptr), ld_col, _vp(x.ptr), N, C_in, H, W, kH, kW, stride, padding)
+                    ptr, acc = grad_target(weight)
+                    _gemm.gemm(LAYOUT_TN, C_out, ncols, rows, dy.ptr, C_out, col.ptr, ld_col, ptr, ncols, accumulate=acc)
+                if col is not None:
+                    col.free()
+                    col = None
+                if x.requires_grad:
+                    with temp_storage(rows * ld_col * F32) as dcol:
+                        _gemm.gemm(LAYOUT_NN, rows, ncols, C_out, dy.ptr, C_out, weight.ptr, ncols, dcol.ptr, ld_col)
+                        fresh = x.grad is None
+                        if fresh:
+                            x.grad = empty_tensor(x.shape)
+                        _call("gt_col2im", _vp(x.grad.ptr), _vp(dcol.ptr), ld_col, N, C_in, H, W, kH, kW, stride, padding,
+                              0 if fresh else 1)
+
+        out._set_graph(parents=(self, weight, bias), backward_fn=_backward)
+        return out
+
     def transpose4d_12(self) -> "Tensor":
         """(B, d1, d2, D) -> (B, d2, d1, D), materialised (gradtuity/tensor.py:1227-1260)."""
         if self.ndim != 4:

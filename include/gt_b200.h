@@ -240,6 +240,13 @@ int gt_add_bias(gt_ctx* ctx, float* out, const float* x, const float* bias, int6
 int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate); /* deterministic */
 int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld); /* db[c] += sum_r dy[r,c] */
 int gt_repack_rows(gt_ctx* ctx, float* dst, int64_t ld_dst, const float* src, int64_t ld_src, int64_t rows, int64_t cols); /* copy rows to another pitch */
+/* conv2d as im2col + GEMM (gradtuity/tensor.py:1906-2167; im2col_kernel_2d / col2im_kernel of
+ * kernels_cuda/conv_kernels.py).  x is (N, C, H, W); col is (N * H_out * W_out, C * kH * kW) with rows
+ * ld_col floats apart, H_out = (H + 2 pad - kH) / stride + 1.  gt_col2im is the adjoint: dx (+)= ...   */
+int gt_im2col(gt_ctx* ctx, float* col, int64_t ld_col, const float* x, int64_t N, int64_t C, int64_t H, int64_t W,
+              int64_t kH, int64_t kW, int64_t stride, int64_t pad);
+int gt_col2im(gt_ctx* ctx, float* dx, const float* dcol, int64_t ld_col, int64_t N, int64_t C, int64_t H, int64_t W,
+              int64_t kH, int64_t kW, int64_t stride, int64_t pad, int accumulate);
 
 /* ---- the non-GEMM kernels of the GPT-2 training step -----------------------------------
  * fp32, memory-bound, on the context's compute stream.  Each restates the reference kernel named

@@ -149,6 +149,36 @@ def attention_forward_backward(q, k, v, do):
     return {"s": s, "p": p, "o": o, "dp": dp, "dv": dv, "ds": ds, "dq": dq, "dk": dk}
 
 
+def conv2d_forward_backward(x, w, b, dy, stride=1, padding=0):
+    """NCHW convolution and its gradients in float64: x (N, C, H, W), w (Co, C, kH, kW), b (Co,), dy
+    (N, Co, Ho, Wo).  The arithmetic of gradtuity/tensor.py:1906-2167 (im2col, col @ W_flat^T + b, dW =
+    dY^T col, dcol = dY W_flat, col2im) with the output laid out as a true (N, Co, Ho, Wo) tensor."""
+    x = np.asarray(x, np.float64); w = np.asarray(w, np.float64); b = np.asarray(b, np.float64); dy = np.asarray(dy, np.float64)
+    N, C, H, W = x.shape
+    Co, _, kH, kW = w.shape
+    Ho = (H + 2 * padding - kH) // stride + 1
+    Wo = (W + 2 * padding - kW) // stride + 1
+    xp = np.zeros((N, C, H + 2 * padding, W + 2 * padding))
+    xp[:, :, padding:padding + H, padding:padding + W] = x
+    col = np.empty((N, Ho, Wo, C, kH, kW))
+    for kh in range(kH):
+        for kw in range(kW):
+            col[:, :, :, :, kh, kw] = xp[:, :, kh:kh + stride * Ho:stride, kw:kw + stride * Wo:stride].transpose(0, 2, 3, 1)
+    colf = col.reshape(N * Ho * Wo, C * kH * kW)
+    wf = w.reshape(Co, -1)
+    y = (colf @ wf.T + b).reshape(N, Ho, Wo, Co).transpose(0, 3, 1, 2)
+    dyf = dy.transpose(0, 2, 3, 1).reshape(N * Ho * Wo, Co)
+    db = dyf.sum(0)
+    dw = (dyf.T @ colf).reshape(w.shape)
+    dcol = (dyf @ wf).reshape(N, Ho, Wo, C, kH, kW)
+    dxp = np.zeros_like(xp)
+    for kh in range(kH):
+        for kw in range(kW):
+            dxp[:, :, kh:kh + stride * Ho:stride, kw:kw + stride * Wo:stride] += dcol[:, :, :, :, kh, kw].transpose(0, 3, 1, 2)
+    dx = dxp[:, :, padding:padding + H, padding:padding + W]
+    return {"y": y, "dx": dx, "dw": dw, "db": db}
+
+
 def rel_frobenius(x, ref):
     """||x - ref||_F / ||ref||_F, the parity metric (<= 1e-3 tf32, <= 1e-5 3xTF32)."""
     x = np.asarray(x, np.float64); ref = np.asarray(ref, np.float64)

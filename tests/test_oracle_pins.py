@@ -121,3 +121,39 @@ def test_gpt2_oracle_backward_matches_finite_differences():
         q[key][idx] -= 2 * h
         lm = orc.loss_and_grads(q, ids, labels)[0]
         assert abs((lp - lm) / (2 * h) - g[key][idx]) < 1e-6, key
+
+
+def test_conv2d_oracle_against_the_defining_sum_and_finite_differences():
+    """The vectorised float64 convolution oracle equals the seven-loop definition, and its gradients
+    equal finite differences (no reference test holds conv2d values: gradtuity/tests/test_nn.py:325-380
+    checks shapes only)."""
+    rng = np.random.default_rng(0)
+    N, C, H, W, Co, kH, kW, s, p = 2, 3, 6, 7, 4, 3, 2, 2, 1
+    x = rng.standard_normal((N, C, H, W)); w = rng.standard_normal((Co, C, kH, kW)); b = rng.standard_normal(Co)
+    Ho, Wo = (H + 2 * p - kH) // s + 1, (W + 2 * p - kW) // s + 1
+    dy = rng.standard_normal((N, Co, Ho, Wo))
+    r = O.conv2d_forward_backward(x, w, b, dy, s, p)
+    y = np.zeros((N, Co, Ho, Wo))
+    for n in range(N):
+        for co in range(Co):
+            for ho in range(Ho):
+                for wo in range(Wo):
+                    acc = b[co]
+                    for c in range(C):
+                        for kh in range(kH):
+                            for kw in range(kW):
+                                h, ww = ho * s - p + kh, wo * s - p + kw
+                                if 0 <= h < H and 0 <= ww < W:
+                                    acc += x[n, c, h, ww] * w[co, c, kh, kw]
+                    y[n, co, ho, wo] = acc
+    assert np.abs(y - r["y"]).max() < 1e-12
+    eps = 1e-6
+    loss = lambda xx, ww_, bb: (O.conv2d_forward_backward(xx, ww_, bb, dy, s, p)["y"] * dy).sum()
+    base = loss(x, w, b)
+    for idx in [(1, 2, 3, 4), (0, 0, 0, 0)]:
+        xp = x.copy(); xp[idx] += eps
+        assert abs((loss(xp, w, b) - base) / eps - r["dx"][idx]) < 1e-4
+    wp = w.copy(); wp[2, 1, 1, 1] += eps
+    assert abs((loss(x, wp, b) - base) / eps - r["dw"][2, 1, 1, 1]) < 1e-4
+    bp = b.copy(); bp[3] += eps
+    assert abs((loss(x, w, bp) - base) / eps - r["db"][3]) < 1e-4

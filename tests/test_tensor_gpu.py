@@ -204,6 +204,50 @@ def test_linear_tied_padded_logits_through_view_and_cross_entropy(T):
     assert O.rel_frobenius(out.reshape(M, V), z) <= 1e-3
 
 
+@pytest.mark.parametrize("N,C,H,W,Co,k,stride,pad", [
+    (2, 1, 28, 28, 8, 3, 1, 1),        # first layer of the MNIST CNN: K = 9, the weight rows are not 16-byte aligned
+    (3, 32, 14, 14, 64, 3, 1, 1),      # K = 288: tensor-core path
+    (2, 4, 9, 11, 6, (3, 2), 2, 0),    # ragged: rectangular kernel, stride 2, no padding
+])
+def test_conv2d_forward_and_backward(T, N, C, H, W, Co, k, stride, pad):
+    """conv2d through im2col and the GEMM kernels (NT forward with bias, TN for dW, NN for dcol) against a
+    float64 NCHW convolution."""
+    kH, kW = (k, k) if isinstance(k, int) else k
+    rng = np.random.default_rng(N * 100 + C)
+    x = rng.standard_normal((N, C, H, W)).astype(np.float32)
+    w = (rng.standard_normal((Co, C, kH, kW)) / np.sqrt(C * kH * kW)).astype(np.float32)
+    b = rng.standard_normal(Co).astype(np.float32)
+    Ho, Wo = (H + 2 * pad - kH) // stride + 1, (W + 2 * pad - kW) // stride + 1
+    dy = rng.standard_normal((N, Co, Ho, Wo)).astype(np.float32)
+    tx, tw, tb = (T.from_numpy(a, requires_grad=True) for a in (x, w, b))
+    y = tx.conv2d(tw, tb, stride=stride, padding=pad)
+    assert y.shape == (N, Co, Ho, Wo)
+    ref = O.conv2d_forward_backward(x, w, b, dy, stride, pad)
+    assert O.rel_frobenius(y.numpy(), ref["y"]) <= 1e-3
+    y.mul(T.from_numpy(dy)).sum().backward()
+    assert O.rel_frobenius(tx.grad.numpy(), ref["dx"]) <= 1e-3
+    assert O.rel_frobenius(tw.grad.numpy(), ref["dw"]) <= 1e-3
+    assert O.rel_frobenius(tb.grad.numpy(), ref["db"]) <= 1e-3
+
+
+def test_conv2d_argument_errors_and_module(T):
+    from gradtuity_b200.nn import Conv2d
+
+    x = T.from_numpy(np.zeros((1, 2, 5, 5), np.float32))
+    with pytest.raises(ValueError, match="4D input"):
+        T.from_numpy(np.zeros((2, 5, 5), np.float32)).conv2d(x, x)
+    with pytest.raises(ValueError, match="input channels"):
+        x.conv2d(T.from_numpy(np.zeros((3, 1, 3, 3), np.float32)), T.from_numpy(np.zeros(3, np.float32)))
+    with pytest.raises(ValueError, match="bias size"):
+        x.conv2d(T.from_numpy(np.zeros((3, 2, 3, 3), np.float32)), T.from_numpy(np.zeros(4, np.float32)))
+    with pytest.raises(ValueError, match="spatial size invalid"):
+        x.conv2d(T.from_numpy(np.zeros((3, 2, 7, 7), np.float32)), T.from_numpy(np.zeros(3, np.float32)))
+    conv = Conv2d(1, 4, kernel_size=3, stride=1, padding=1)             # gradtuity/tests/test_nn.py:328-341
+    y = conv(T.from_numpy(np.ones((2, 1, 8, 8), np.float32)))
+    assert y.shape == (2, 4, 8, 8)
+    assert conv.weight.shape == (4, 1, 3, 3) and conv.bias.shape == (4,) and len(conv.parameters()) == 2
+
+
 def test_config0_linear_784_128(T):
     """Config 0: Linear(784 -> 128), batch 128, X ~ U[0,1), W and b ~ U(-1/28, 1/28), dY ~ N(0,1),
     seed 0; y, dX, dW, db against the float64 oracle."""
