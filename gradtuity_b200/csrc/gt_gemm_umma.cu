@@ -27,6 +27,7 @@
 // Replaces: gradtuity/kernels_triton/matmul_kernels.py:18-400 (five kernels, 32x32x32 tiles,
 // tl.dot) and gradtuity/kernels_cuda/matmul_kernels.py:21-236.
 
+#include <stdio.h>
 #include <stdlib.h>
 
 #include "gt_internal.h"
@@ -58,6 +59,9 @@ struct UmmaParams {
   int flags;                             // GT_GEMM_* flags of gt_gemm_batched_ex
   int c_tma;                             // C is written by TMA store / reduce-add through shared memory
   int a_onebox, b_onebox;                // MN-major operand described as (32, K, MN/32, b0, b1): one TMA box per stage
+  int tail_first, tail_split, tail_kb_per;   // last partial wave: tiles from tail_first on are cut into tail_split K shares
+  int tail_zero, tail_epoch;             // C is not accumulated into: CTA i zeroes the i-th last-wave tile first and
+  int* tail_flags;                       // publishes tail_flags[i] = tail_epoch; the shares wait for it before they add
   float alpha;
   int* status;
 };
@@ -76,8 +80,16 @@ struct Cfg {
 // Tile list order: groups of `group_m` row-tiles sweep all column-tiles before the next
 // group starts, so CTAs that run together share A and B panels in L2.
 __device__ __forceinline__ void tile_coords(const UmmaParams& p, int unit, int& batch, int& tm, int& tn, int& ks) {
-  ks = unit % p.ksplit;
-  const int tile = unit / p.ksplit;
+  int tile;
+  if (p.tail_split > 1) {
+    // Work units of the last, partial wave: each of its tiles is contracted by tail_split CTAs (ks = share),
+    // all other tiles by one CTA over the whole K (ks = -1).
+    if (unit < p.tail_first) { tile = unit; ks = -1; }
+    else { const int u = unit - p.tail_first; tile = p.tail_first + u / p.tail_split; ks = u % p.tail_split; }
+  } else {
+    ks = unit % p.ksplit;
+    tile = unit / p.ksplit;
+  }
   const int per_batch = p.tiles_m * p.tiles_n;
   batch = tile / per_batch;
   const int t = tile - batch * per_batch;
@@ -95,8 +107,13 @@ __device__ __forceinline__ void tile_coords(const UmmaParams& p, int unit, int& 
 // as A need only the k-blocks up to the tile's last row, and those that read them transposed
 // only the k-blocks from the tile's first row on).
 __device__ __forceinline__ void k_range(const UmmaParams& p, int tm, int ks, int num_kb, int& lo, int& hi) {
-  lo = ks * p.kb_per;
-  hi = min(num_kb, lo + p.kb_per);
+  if (p.tail_split > 1) {
+    lo = ks < 0 ? 0 : ks * p.tail_kb_per;
+    hi = ks < 0 ? num_kb : min(num_kb, lo + p.tail_kb_per);
+  } else {
+    lo = ks * p.kb_per;
+    hi = min(num_kb, lo + p.kb_per);
+  }
   if (p.flags & GT_GEMM_A_LOWER) hi = min(hi, ((tm + 1) * BM + BK - 1) / BK);
   if (p.flags & GT_GEMM_AT_LOWER) lo = max(lo, (tm * BM) / BK);
 }
@@ -179,9 +196,9 @@ __device__ __forceinline__ bool prefetch_c(const UmmaParams& p, bool enabled, in
 // This is the general form: bias, aux and the output may end inside the chunk.
 __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
                                                        int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                       uint8_t* tile, uint32_t tile_u32) {
+                                                       uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
   const int row = row0 + lane;
-  const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
+  const bool has_bias = epi >= GT_EPI_BIAS && epi <= GT_EPI_BIAS_GELU;
   if (lane == 0) tma_store_wait_read<0>();          // the previous store of this warp has finished reading the tile
   __syncwarp();
 #pragma unroll
@@ -205,11 +222,11 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
       if (nb + j + 1 < p.N) a[1] = x.y;
       if (nb + j + 2 < p.N) a[2] = x.z;
     }
-    if (p.epilogue == GT_EPI_BIAS_RELU) {
+    if (epi == GT_EPI_BIAS_RELU) {
       x.x = fmaxf(x.x, 0.0f); x.y = fmaxf(x.y, 0.0f); x.z = fmaxf(x.z, 0.0f); x.w = fmaxf(x.w, 0.0f);
-    } else if (p.epilogue == GT_EPI_BIAS_GELU) {
+    } else if (epi == GT_EPI_BIAS_GELU) {
       x.x = gt_gelu_tanh(x.x); x.y = gt_gelu_tanh(x.y); x.z = gt_gelu_tanh(x.z); x.w = gt_gelu_tanh(x.w);
-    } else if (p.epilogue == GT_EPI_CAUSAL) {
+    } else if (epi == GT_EPI_CAUSAL) {
       const int col = nb + j;
       if (col > row) x.x = GT_CAUSAL_MASK_VALUE;
       if (col + 1 > row) x.y = GT_CAUSAL_MASK_VALUE;
@@ -220,7 +237,7 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
-  if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, p.accumulate != 0);
+  if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, add);
 }
 
 // The same for a chunk that lies wholly inside N, with the epilogue kind fixed at compile time: no
@@ -230,7 +247,7 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
 template <int EPI, bool AUX>
 __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
                                                         int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                        uint8_t* tile, uint32_t tile_u32) {
+                                                        uint8_t* tile, uint32_t tile_u32, bool add) {
   constexpr bool HAS_BIAS = EPI >= GT_EPI_BIAS && EPI <= GT_EPI_BIAS_GELU;
   const int row = row0 + lane;
   const float alpha = p.alpha;
@@ -263,15 +280,15 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
-  if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, p.accumulate != 0);
+  if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, add);
 }
 
 __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
                                                    int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                   uint8_t* tile, uint32_t tile_u32) {
-#define GT_EPI_FAST(E, X) epilogue_chunk_tma_fast<E, X>(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32)
+                                                   uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
+#define GT_EPI_FAST(E, X) epilogue_chunk_tma_fast<E, X>(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add)
   if (nb + 32 <= p.N) {                              // warp-uniform
-    switch (p.epilogue) {
+    switch (epi) {
       case GT_EPI_NONE:
         if (!p.aux) { GT_EPI_FAST(GT_EPI_NONE, false); return; }
         break;
@@ -295,7 +312,7 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CU
     }
   }
 #undef GT_EPI_FAST
-  epilogue_chunk_tma_any(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32);
+  epilogue_chunk_tma_any(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, epi, add);
 }
 
 // Same epilogue for outputs whose rows are not 16-byte aligned (odd leading dimension, e.g. the
@@ -578,6 +595,33 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     constexpr int MY_CHUNKS = (BN / 32 + EPI_SETS - 1) / EPI_SETS;     // chunks c = eset, eset + EPI_SETS, ...
     int acc = 0; uint32_t aph = 0;
     bool ok = true;
+    // Last-wave split without C += ...: the shares of a last-wave tile ADD into C, so C must be zero under
+    // that tile.  CTA i zeroes the i-th such tile now, a whole wave before any share can reach its epilogue:
+    // one warp stores a zero-filled staging tile over it with TMA, waits for the stores to complete and
+    // publishes the launch's epoch in the tile's flag.
+    if (p.tail_split > 1 && p.tail_zero && warp == 2) {
+      const int n_tail = (p.num_tiles - p.tail_first) / p.tail_split;
+      if ((int)blockIdx.x < n_tail) {
+        int batch, tm, tn, ks;
+        tile_coords(p, p.tail_first + (int)blockIdx.x * p.tail_split, batch, tm, tn, ks);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) *reinterpret_cast<float4*>(epi_bytes + lane * 128 + (g << 4)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+          for (int r = 0; r < BM / 32; ++r)
+            for (int c = 0; c < BN / 32; ++c)
+              if (tn * BN + c * 32 < p.N && tm * BM + r * 32 < p.M)
+                tma_store_4d(&map_c, epi_u32, tn * BN + c * 32, tm * BM + r * 32, i0, i1, false);
+          tma_store_wait_all();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          atomicExch(p.tail_flags + blockIdx.x, p.tail_epoch);
+        }
+        __syncwarp();
+      }
+    }
     for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
       int batch, tm, tn, ks;
       tile_coords(p, tile, batch, tm, tn, ks);
@@ -592,6 +636,25 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1 + (long long)ks * p.ks_stride;
       const long long row_off = batch_off + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
+      // a K share of a last-wave tile adds its partial sum into C; the bias goes in with share 0
+      const bool tail_unit = p.tail_split > 1 && ks >= 0;
+      const bool unit_add = p.accumulate != 0 || tail_unit;
+      const int unit_epi = (tail_unit && ks > 0) ? (int)GT_EPI_NONE : p.epilogue;
+      if (tail_unit && p.tail_zero) {
+        // the tile must have been zeroed before this share adds into it (bounded wait; normally already true)
+        if (lane == 0) {
+          const volatile int* flag = p.tail_flags + (tile - p.tail_first) / p.tail_split;
+          const long long t0 = clock64();
+          while (*flag != p.tail_epoch) {
+            if (*abort_flag) break;
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicExch(p.status, GT_ERR_TIMEOUT); break; }
+          }
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        __syncwarp();
+        if (*abort_flag) { ok = false; break; }
+      }
       if constexpr (X3) {
         // The accumulator arrives in K-chunks; they are summed here in fp32 registers
         // (round-to-nearest adds) before the fused epilogue runs once.
@@ -625,7 +688,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const int c = lc * EPI_SETS + eset;
           const int nb = n0 + c * 32;
           if (c < BN / 32 && nb < p.N) {
-            if (p.c_tma) epilogue_chunk_tma(p, &map_c, &sum[lc * 32], lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32);
+            if (p.c_tma) epilogue_chunk_tma(p, &map_c, &sum[lc * 32], lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, p.epilogue, p.accumulate != 0);
             else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, &sum[lc * 32], row, nb, row_off); }
             else epilogue_chunk_coalesced(p, &sum[lc * 32], epi_tile, lane, row0, nb, batch_off);
           }
@@ -647,7 +710,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.0f;
           }
-          if (p.c_tma) epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32);
+          if (p.c_tma) epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, unit_epi, unit_add);
           else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off); }
           else epilogue_chunk_coalesced(p, v, epi_tile, lane, row0, nb, batch_off);
         }
@@ -841,7 +904,7 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tc_ld32(lane_base + (uint32_t)(c * 32), v);
         tc_wait_ld();
         if (p.c_tma) {
-          epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32);
+          epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, p.epilogue, p.accumulate != 0);
         } else if (row_ok) {
           epilogue_chunk(p, v, row, nb, row_off);     // host guarantees aligned rows for this kernel
         }
@@ -1124,6 +1187,8 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   p.flags = g.flags;
   p.a_onebox = a_one ? 1 : 0;
   p.b_onebox = b_one ? 1 : 0;
+  p.tail_first = 0; p.tail_split = 1; p.tail_kb_per = num_kb;
+  p.tail_zero = 0; p.tail_epoch = 0; p.tail_flags = nullptr;
   p.status = ctx->d_status;
   bool vec = (((uintptr_t)g.C & 15) == 0) && (g.ldc % 4 == 0) && (g.sC0 % 4 == 0) && (g.sC1 % 4 == 0);
   if (g.aux) vec = vec && (((uintptr_t)g.aux & 15) == 0);
@@ -1158,7 +1223,40 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   } else {
     maps[4] = maps[1];
   }
+  // Last partial wave.  A persistent CTA per SM walks the tiles round-robin, so T tiles on P SMs take
+  // ceil(T / P) rounds even when the last round has few tiles (the 768-wide projections of GPT-2: 192
+  // tiles on 148 SMs = a second round that is 30 % full).  When that round is at most half full its tiles
+  // are cut along K into `s` shares taken by different CTAs, which add their partial sums into C with the
+  // epilogue's TMA reduce-add (unless the call is C += ..., the kernel zeroes C under those tiles at its
+  // start and the shares wait for that; see the epilogue warps).
+  static const bool tail_off = getenv("GRADTUITY_GEMM_NO_TAIL_SPLIT") != nullptr;
+  if (!tail_off && !deterministic && !use256 && !x3 && !a_gen && ksplit == 1 && p.c_tma && nbatch == 1 && g.flags == 0 && !g.aux &&
+      (g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS) && num_kb >= 16 && tiles > ctx->sm_count) {
+    const int P = ctx->sm_count;
+    const int tail = (int)(tiles % P);
+    if (tail > 0 && tail * 2 <= P) {
+      int sp = P / tail;
+      if (sp > num_kb / 4) sp = num_kb / 4;
+      if (sp > 8) sp = 8;
+      if (sp >= 2) {
+        const int kb_per = (num_kb + sp - 1) / sp;
+        sp = (num_kb + kb_per - 1) / kb_per;
+        p.tail_first = (int)(tiles - tail);
+        p.tail_split = sp;
+        p.tail_kb_per = kb_per;
+        p.num_tiles = p.tail_first + tail * sp;
+        p.tail_zero = g.accumulate ? 0 : 1;
+        p.tail_epoch = ++ctx->tail_epoch;
+        p.tail_flags = ctx->d_status + 16;
+      }
+    }
+  }
   const int grid = (int)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);
+  static const bool trace = getenv("GRADTUITY_GEMM_TRACE") != nullptr;     // one line per launch on stderr
+  if (trace)
+    fprintf(stderr, "gt_gemm: layout %d M %lld N %lld K %lld batch %lld epi %d acc %d | tile %dx%d x3 %d a_gen %d ksplit %d direct %d tail_split %d (from tile %d) units %d grid %d c_tma %d onebox %d%d\n",
+            g.layout, (long long)g.M, (long long)g.N, (long long)g.K, nbatch, g.epilogue, g.accumulate, tile_m, bn, (int)x3, (int)a_gen,
+            ksplit, (int)splitk_direct, p.tail_split, p.tail_first, p.num_tiles, grid, p.c_tma, p.a_onebox, p.b_onebox);
 
   if (use256) {
     static bool attr_set[3] = {false, false, false};

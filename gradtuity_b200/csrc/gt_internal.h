@@ -18,7 +18,9 @@ struct gt_ctx {
   int device;
   int sm_count;
   cudaStream_t stream;        // compute stream (non-blocking)
-  int* d_status;              // device status word written by bounded waits that ran out
+  int* d_status;              // device status word written by bounded waits that ran out; the allocation is 4 KB:
+                              // ints 16..271 are the "C tile zeroed" flags of the GEMM's last-wave split
+  int tail_epoch;             // value those flags take in the next launch that uses them
   gt_encode_tiled_fn encode_tiled;
   void* workspace;            // scratch for operand splitting (TF32X3) and split-K partials
   size_t workspace_bytes;

@@ -610,7 +610,33 @@ __global__ void __launch_bounds__(256) adamw_multi_kernel(const MtTensor* __rest
   const MtTensor t = tensors[c.tensor];
   const float gs = grad_scale ? *grad_scale : 1.0f;
   long long end = c.start + chunk_elems; if (end > t.n) end = t.n;
-  for (long long i = c.start + threadIdx.x; i < end; i += blockDim.x) {
+  long long begin = c.start;
+  if (((((uintptr_t)t.p | (uintptr_t)t.g | (uintptr_t)t.m | (uintptr_t)t.v) & 15) == 0) && (c.start & 3) == 0) {
+    // 16-byte aligned tensors: the body of the chunk as float4 (seven 16-byte accesses per four elements)
+    const long long n4 = (end - c.start) >> 2;
+    float4* p4 = reinterpret_cast<float4*>(t.p + c.start);
+    const float4* g4 = reinterpret_cast<const float4*>(t.g + c.start);
+    float4* m4 = reinterpret_cast<float4*>(t.m + c.start);
+    float4* v4 = reinterpret_cast<float4*>(t.v + c.start);
+    for (long long i = threadIdx.x; i < n4; i += blockDim.x) {
+      float4 pv = p4[i], mv = m4[i], vv = v4[i];
+      const float4 gv = g4[i];
+      float* pp = reinterpret_cast<float*>(&pv); float* mm = reinterpret_cast<float*>(&mv); float* vq = reinterpret_cast<float*>(&vv);
+      const float* gg = reinterpret_cast<const float*>(&gv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gi = gg[k] * gs;
+        const float mi = beta1 * mm[k] + (1.0f - beta1) * gi;
+        const float vi = beta2 * vq[k] + (1.0f - beta2) * gi * gi;
+        const float upd = (mi * bc1) / (sqrtf(vi * bc2) + eps);
+        pp[k] = pp[k] - lr * upd - lr * wd * pp[k];
+        mm[k] = mi; vq[k] = vi;
+      }
+      p4[i] = pv; m4[i] = mv; v4[i] = vv;
+    }
+    begin = c.start + (n4 << 2);
+  }
+  for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
     float pi = t.p[i];
     const float gi = t.g[i] * gs;
     const float mi = beta1 * t.m[i] + (1.0f - beta1) * gi;

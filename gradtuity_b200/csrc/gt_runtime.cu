@@ -45,8 +45,9 @@ extern "C" int gt_init(int device, gt_ctx** out) {
   }
   ctx->sm_count = prop.multiProcessorCount;
   if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
-  if (cudaMalloc((void**)&ctx->d_status, sizeof(int)) != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
-  cudaMemset(ctx->d_status, 0, sizeof(int));
+  if (cudaMalloc((void**)&ctx->d_status, 4096) != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
+  cudaMemset(ctx->d_status, 0, 4096);
+  ctx->tail_epoch = 0;
 
   // Keep freed blocks in the pool instead of returning them to the driver at every sync.
   cudaMemPool_t pool;

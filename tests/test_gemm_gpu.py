@@ -182,6 +182,28 @@ def test_split_k_shapes(gt, layout, M, N, K, epilogue, acc):
         assert O.rel_frobenius(again - base, out - base) <= 1e-5
 
 
+@pytest.mark.parametrize("layout,M,N,K,epilogue,acc", [
+    ("NN", 8192, 768, 768, "bias", False),      # q/k/v/o projection of GPT-2: 192 tiles on 148 SMs, last wave cut in 3
+    ("NT", 8200, 768, 768, "none", True),       # dX with C +=, ragged last row tile
+    ("NT", 8192, 3072, 800, "none", False),     # 768 tiles: 28 in the last wave, K tail
+    ("TN", 8192, 776, 1024, "bias", False),     # N tail inside the last column tile
+])
+def test_last_wave_split_shapes(gt, layout, M, N, K, epilogue, acc):
+    """More tiles than SMs with a last wave at most half full: the tiles of that wave are cut along K
+    between CTAs that add their partial sums into C (zeroed under those tiles first unless C += ...)."""
+    a, b, rng = U.make_operands(layout, M, N, K, seed=M + K)
+    bias = rng.standard_normal(N).astype(np.float32) if epilogue != "none" else None
+    c0 = rng.standard_normal((M, N)).astype(np.float32) if acc else None
+    out = U.run_gemm(layout, a, b, bias=bias, c0=c0, epilogue=epilogue)
+    ref = O.gemm(a, b, layout, bias=bias, epilogue=epilogue, c0=c0)
+    base = c0 if acc else 0.0
+    assert O.rel_frobenius(out - base, ref - base) <= U.TOL["tf32"]
+    # every row block on its own, so that an error confined to the last wave's tiles cannot hide in the norm
+    for r0 in range(0, M, 1024):
+        sl = slice(r0, min(M, r0 + 1024))
+        assert O.rel_frobenius((out - base)[sl], (ref - base)[sl]) <= U.TOL["tf32"]
+
+
 def test_bitwise_deterministic(gt):
     # one CTA per output tile (no shared K range): the summation order is fixed
     a, b, _ = U.make_operands("TN", 1536, 2048, 512, seed=3)
