@@ -103,6 +103,8 @@ SIGNATURES = {
     "gt_sum_all": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int]),
     "gt_colsum_acc": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "gt_repack_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64]),
+    "gt_maxpool2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 8),
+    "gt_maxpool2d_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "gt_im2col": (c_int, [c_void_p, c_void_p, c_int64, c_void_p] + [c_int64] * 8),
     "gt_col2im": (c_int, [c_void_p, c_void_p, c_void_p, c_int64] + [c_int64] * 8 + [c_int]),
     "gt_softmax": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int]),

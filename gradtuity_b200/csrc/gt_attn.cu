@@ -135,7 +135,7 @@ __device__ __forceinline__ AttnSmem carve(uint8_t* smem_raw) {
 // tiles come from L2), turns it into the final probabilities exp(s - max) / sum, writes them to
 // shared memory (and, on request, from there to P with a TMA store), and accumulates O += P V in
 // tensor memory, so O never needs rescaling.
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __maxnreg__(112)
 gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_p,
                    const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
@@ -346,9 +346,15 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc_fence_after();
         const int col0 = j * AT_TILE + eset * 32;
         float v[32];
-        tc_ld32(lane_base + (uint32_t)(sb * 128 + eset * 32), v);
-        tc_wait_ld();
-        if (j < i) {
+        const bool dead = (j == i) && (eset > q);        // chunk wholly right of the diagonal for this warp's rows
+        if (!dead) {
+          tc_ld32(lane_base + (uint32_t)(sb * 128 + eset * 32), v);
+          tc_wait_ld();
+        }
+        if (dead) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else if (j < i) {
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             float4 x;
@@ -519,7 +525,7 @@ __device__ __forceinline__ void item_coords_kv(const AttnParams& p, int item, in
 }
 
 // dQ for one block of 128 queries; also delta = rowsum(dO * O).
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __maxnreg__(112)
 gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __grid_constant__ CUtensorMap map_kmn, const __grid_constant__ CUtensorMap map_dq,
@@ -652,13 +658,19 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tc_fence_after();
         const int col0 = j * AT_TILE + eset * 32;
         const int nvalid = (j < i) ? 32 : row - col0 + 1;        // keys <= query
+        const bool dead = (j == i) && (eset > q);                 // chunk wholly right of the diagonal for this warp's rows
         float pr[32], v[32];
-        tc_ld32(lane_base + (uint32_t)(eset * 32), v);
-        tc_wait_ld();
+        if (!dead) {
+          tc_ld32(lane_base + (uint32_t)(eset * 32), v);
+          tc_wait_ld();
 #pragma unroll
-        for (int t = 0; t < 32; ++t) pr[t] = (t < nvalid) ? ex2(fmaf(v[t], p.scale_log2, -lse2)) : 0.0f;
-        tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
-        tc_wait_ld();
+          for (int t = 0; t < 32; ++t) pr[t] = (t < nvalid) ? ex2(fmaf(v[t], p.scale_log2, -lse2)) : 0.0f;
+          tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) { pr[t] = 0.0f; v[t] = 0.0f; }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
@@ -712,7 +724,7 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 }
 
 // dK and dV for one block of 128 keys: everything transposed, so that a thread owns a key.
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __maxnreg__(112)
 gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                        const __grid_constant__ CUtensorMap map_qmn, const __grid_constant__ CUtensorMap map_domn,
@@ -832,7 +844,12 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const int first_valid = (i > j) ? 0 : r_local - eset * 32;   // columns (queries) >= this thread's key
         const float4* l4 = reinterpret_cast<const float4*>(lse_bh + q0);
         const float4* d4 = reinterpret_cast<const float4*>(delta_bh + q0);
+        const bool dead = (i == j) && (eset < q);                 // queries of this chunk all precede this warp's keys
         float pr[32], v[32];
+        if (dead) {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) { pr[t] = 0.0f; v[t] = 0.0f; }
+        } else {
         tc_ld32(lane_base + (uint32_t)(eset * 32), v);
         tc_wait_ld();
 #pragma unroll
@@ -845,10 +862,6 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
         tc_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
-        ++sdp_it;
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const float4 d = d4[g];
@@ -857,6 +870,11 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           v[4 * g + 2] = pr[4 * g + 2] * (v[4 * g + 2] - d.z) * p.scale;
           v[4 * g + 3] = pr[4 * g + 3] * (v[4 * g + 3] - d.w) * p.scale;
         }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
+        ++sdp_it;
         // P^T -> tile (free once the previous tile's dK product and this warp's own stores have read it)
         if (!mbar_wait(sm.bar_t2_empty, (uint32_t)(t_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
         if (i == j) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }

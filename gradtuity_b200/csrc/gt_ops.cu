@@ -246,7 +246,60 @@ __global__ void __launch_bounds__(256) col2im_kernel(float* __restrict__ dx, con
   }
 }
 
+// Max pooling over (kH, kW) windows of an (N, C, H, W) tensor; idx receives the flat offset of the
+// winning element inside its (H, W) plane, as a float (the engine has one dtype), for the backward
+// (gradtuity/tensor.py:2169-2260: maxpool2d_forward_kernel / maxpool2d_backward_kernel).  The first
+// maximum of a window wins.
+__global__ void __launch_bounds__(256) maxpool2d_fwd_kernel(float* __restrict__ out, float* __restrict__ idx, const float* __restrict__ x,
+                                                            long long planes, int H, int W, int kH, int kW, int sh, int sw,
+                                                            int H_out, int W_out) {
+  const long long total = planes * H_out * W_out;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int wo = (int)(i % W_out), ho = (int)((i / W_out) % H_out);
+    const long long pl = i / ((long long)W_out * H_out);
+    const float* xp = x + pl * H * W;
+    float best = -INFINITY; int arg = 0;
+    for (int kh = 0; kh < kH; ++kh)
+      for (int kw = 0; kw < kW; ++kw) {
+        const int off = (ho * sh + kh) * W + wo * sw + kw;
+        const float v = xp[off];
+        if (v > best) { best = v; arg = off; }
+      }
+    out[i] = best;
+    idx[i] = (float)arg;
+  }
+}
+// dx[plane, idx] += dy: windows may overlap (stride < kernel), so the scatter is atomic.
+__global__ void __launch_bounds__(256) maxpool2d_bwd_kernel(float* __restrict__ dx, const float* __restrict__ dy, const float* __restrict__ idx,
+                                                            long long planes, int HW, int HWo) {
+  const long long total = planes * HWo;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long pl = i / HWo;
+    atomicAdd(dx + pl * HW + (int)idx[i], dy[i]);
+  }
+}
+
 }  // namespace
+
+extern "C" int gt_maxpool2d(gt_ctx* ctx, float* out, float* idx, const float* x, int64_t N, int64_t C, int64_t H, int64_t W,
+                            int64_t kH, int64_t kW, int64_t stride_h, int64_t stride_w) {
+  if (!ctx || !out || !idx || !x || N <= 0 || C <= 0 || H <= 0 || W <= 0 || kH <= 0 || kW <= 0 || stride_h <= 0 || stride_w <= 0 ||
+      kH > H || kW > W || H * W >= (1 << 24)) return GT_ERR_INVALID_ARG;
+  const int64_t H_out = (H - kH) / stride_h + 1, W_out = (W - kW) / stride_w + 1;
+  maxpool2d_fwd_kernel<<<ew_blocks(ctx, N * C * H_out * W_out), EW_THREADS, 0, ctx->stream>>>(out, idx, x, N * C, (int)H, (int)W, (int)kH, (int)kW,
+                                                                                             (int)stride_h, (int)stride_w, (int)H_out, (int)W_out);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
+
+extern "C" int gt_maxpool2d_backward(gt_ctx* ctx, float* dx, const float* dy, const float* idx, int64_t planes, int64_t HW, int64_t HWo) {
+  if (!ctx || !dx || !dy || !idx || planes <= 0 || HW <= 0 || HWo <= 0 || HW >= (1 << 24)) return GT_ERR_INVALID_ARG;
+  maxpool2d_bwd_kernel<<<ew_blocks(ctx, planes * HWo), EW_THREADS, 0, ctx->stream>>>(dx, dy, idx, planes, (int)HW, (int)HWo);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return GT_OK;
+}
 
 extern "C" int gt_im2col(gt_ctx* ctx, float* col, int64_t ld_col, const float* x, int64_t N, int64_t C, int64_t H, int64_t W,
                          int64_t kH, int64_t kW, int64_t stride, int64_t pad) {

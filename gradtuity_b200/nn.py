@@ -296,6 +296,78 @@ class Conv2d(Module):
                 f"stride={self.stride}, padding={self.padding})")
 
 
+class Flatten(Module):
+    """Flatten the dimensions from start_dim on into one: (N, C, H, W) -> (N, C*H*W) (gradtuity/nn.py:229-275)."""
+
+    def __init__(self, start_dim: int = 1) -> None:
+        super().__init__()
+        self.start_dim = start_dim
+
+    def __call__(self, x: Tensor) -> Tensor:
+        s = x.shape
+        if len(s) < 2:
+            raise ValueError(f"Flatten requires at least 2D input, got shape {s}")
+        start_dim = len(s) + self.start_dim if self.start_dim < 0 else self.start_dim
+        if start_dim <= 0 or start_dim >= len(s):
+            raise ValueError(f"Flatten start_dim must be in [1, {len(s) - 1}], got {self.start_dim}")
+        flat = 1
+        for d in s[start_dim:]:
+            flat *= d
+        return x.view(s[:start_dim] + (flat,))
+
+    def parameters(self) -> list[Tensor]:
+        return []
+
+    def __repr__(self) -> str:
+        return f"Flatten(start_dim={self.start_dim})"
+
+
+class MaxPool2d(Module):
+    """2D max pooling (gradtuity/nn.py:632-659)."""
+
+    def __init__(self, kernel_size=2, stride=None) -> None:
+        super().__init__()
+        self.kernel_size = kernel_size
+        self.stride = stride
+
+    def __call__(self, x: Tensor) -> Tensor:
+        return x.maxpool2d(kernel_size=self.kernel_size, stride=self.stride)
+
+    def parameters(self) -> list[Tensor]:
+        return []
+
+    def __repr__(self) -> str:
+        return f"MaxPool2d(kernel_size={self.kernel_size}, stride={self.stride})"
+
+
+class CNN(Module):
+    """The reference's MNIST model: Conv -> ReLU -> Pool -> Conv -> ReLU -> Pool -> Flatten -> Linear -> ReLU ->
+    Linear; input (N, 1, 28, 28), output (N, 10) (gradtuity/nn.py:713-750)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.conv1 = Conv2d(1, 32, kernel_size=3, stride=1, padding=1)
+        self.pool1 = MaxPool2d(kernel_size=2, stride=2)
+        self.conv2 = Conv2d(32, 64, kernel_size=3, stride=1, padding=1)
+        self.pool2 = MaxPool2d(kernel_size=2, stride=2)
+        self.flatten = Flatten(start_dim=1)
+        self.fc1 = Linear(64 * 7 * 7, 128)
+        self.fc2 = Linear(128, 10)
+
+    def __call__(self, x: Tensor) -> Tensor:
+        x = self.pool1(self.conv1(x).relu())
+        x = self.pool2(self.conv2(x).relu())
+        x = self.flatten(x)
+        x = x.linear_relu(self.fc1.weight, self.fc1.bias)
+        return x.linear(self.fc2.weight, self.fc2.bias)
+
+    def parameters(self) -> list[Tensor]:
+        return self.conv1.parameters() + self.conv2.parameters() + self.fc1.parameters() + self.fc2.parameters()
+
+    def __repr__(self) -> str:
+        return "CNN(conv1->relu->pool1->conv2->relu->pool2->flatten->fc1->relu->fc2)"
+
+
 class LayerNorm(Module):
     """LayerNorm over the last dimension; gamma ones, beta zeros (gradtuity/nn.py:662-710)."""
 

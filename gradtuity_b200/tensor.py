@@ -932,6 +932,36 @@ class Tensor:
         out._set_graph(parents=(self, weight, bias), backward_fn=_backward)
         return out
 
+    def maxpool2d(self, kernel_size=2, stride=None) -> "Tensor":
+        """2D max pooling (N, C, H, W) -> (N, C, H_out, W_out); the stride defaults to the kernel size
+        (gradtuity/tensor.py:2169-2260)."""
+        x = self
+        if x.ndim != 4:
+            raise ValueError(f"maxpool2d requires 4D input, got shape {x._shape}")
+        kH, kW = (kernel_size, kernel_size) if isinstance(kernel_size, int) else kernel_size
+        if stride is None:
+            sh = sw = kH
+        elif isinstance(stride, int):
+            sh = sw = stride
+        else:
+            sh, sw = stride
+        N, C, H, W = x._shape
+        H_out = (H - kH) // sh + 1
+        W_out = (W - kW) // sw + 1
+        if H_out <= 0 or W_out <= 0:
+            raise ValueError(f"maxpool2d output size invalid: H_out={H_out}, W_out={W_out}")
+        out = empty_tensor((N, C, H_out, W_out))
+        idx = alloc_storage(out.numel * F32)
+        _call("gt_maxpool2d", _vp(out.ptr), _vp(idx.ptr), _vp(x.ptr), N, C, H, W, kH, kW, sh, sw)
+
+        def _backward(g: "Tensor") -> None:
+            if x.requires_grad:
+                ensure_grad(x)
+                _call("gt_maxpool2d_backward", _vp(x.grad.ptr), _vp(g.ptr), _vp(idx.ptr), N * C, H * W, H_out * W_out)
+
+        out._set_graph(parents=(self,), backward_fn=_backward)
+        return out
+
     def transpose4d_12(self) -> "Tensor":
         """(B, d1, d2, D) -> (B, d2, d1, D), materialised (gradtuity/tensor.py:1227-1260)."""
         if self.ndim != 4:

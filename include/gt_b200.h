@@ -247,6 +247,12 @@ int gt_im2col(gt_ctx* ctx, float* col, int64_t ld_col, const float* x, int64_t N
               int64_t kH, int64_t kW, int64_t stride, int64_t pad);
 int gt_col2im(gt_ctx* ctx, float* dx, const float* dcol, int64_t ld_col, int64_t N, int64_t C, int64_t H, int64_t W,
               int64_t kH, int64_t kW, int64_t stride, int64_t pad, int accumulate);
+/* maxpool2d_forward / backward (gradtuity/tensor.py:2169-2260).  idx holds, per output element, the offset
+ * of the winning input inside its (H, W) plane, float-encoded; the backward adds dy there (dx must hold
+ * the gradient accumulated so far, zeros for a fresh one).                                           */
+int gt_maxpool2d(gt_ctx* ctx, float* out, float* idx, const float* x, int64_t N, int64_t C, int64_t H, int64_t W,
+                 int64_t kH, int64_t kW, int64_t stride_h, int64_t stride_w);
+int gt_maxpool2d_backward(gt_ctx* ctx, float* dx, const float* dy, const float* idx, int64_t planes, int64_t HW, int64_t HWo);
 
 /* ---- the non-GEMM kernels of the GPT-2 training step -----------------------------------
  * fp32, memory-bound, on the context's compute stream.  Each restates the reference kernel named

@@ -179,6 +179,73 @@ def conv2d_forward_backward(x, w, b, dy, stride=1, padding=0):
     return {"y": y, "dx": dx, "dw": dw, "db": db}
 
 
+def maxpool2d_forward(x, k=2, stride=None):
+    """(N, C, H, W) -> pooled values and, per output, the flat (h * W + w) position of the first maximum of its
+    window (gradtuity/tensor.py:2169-2260)."""
+    x = np.asarray(x, np.float64)
+    kH, kW = (k, k) if isinstance(k, int) else k
+    sh, sw = (kH, kW) if stride is None else ((stride, stride) if isinstance(stride, int) else stride)
+    N, C, H, W = x.shape
+    Ho, Wo = (H - kH) // sh + 1, (W - kW) // sw + 1
+    out = np.full((N, C, Ho, Wo), -np.inf)
+    arg = np.zeros((N, C, Ho, Wo), np.int64)
+    for kh in range(kH):
+        for kw in range(kW):
+            win = x[:, :, kh:kh + sh * Ho:sh, kw:kw + sw * Wo:sw]
+            pos = (np.arange(Ho)[:, None] * sh + kh) * W + (np.arange(Wo)[None, :] * sw + kw)
+            better = win > out
+            out = np.where(better, win, out)
+            arg = np.where(better, pos[None, None], arg)
+    return out, arg
+
+
+def maxpool2d_backward(dy, arg, H, W):
+    dy = np.asarray(dy, np.float64)
+    N, C, Ho, Wo = dy.shape
+    dx = np.zeros((N, C, H * W))
+    n, c = np.meshgrid(np.arange(N), np.arange(C), indexing="ij")
+    np.add.at(dx, (n[:, :, None, None], c[:, :, None, None], arg), dy)
+    return dx.reshape(N, C, H, W)
+
+
+def cnn_loss_and_grads(params, x, targets):
+    """The reference's MNIST CNN (gradtuity/nn.py:713-750) with a mean cross-entropy loss, in float64:
+    params = dict(conv1.weight, conv1.bias, conv2.weight, conv2.bias, fc1.weight (in, out), fc1.bias, fc2.weight,
+    fc2.bias).  Returns the loss and the gradient of every parameter."""
+    P = {k: np.asarray(v, np.float64) for k, v in params.items()}
+    x = np.asarray(x, np.float64)
+    N = x.shape[0]
+    z1 = conv2d_forward_backward(x, P["conv1.weight"], P["conv1.bias"], np.zeros((N, 32, 28, 28)), 1, 1)["y"]
+    a1 = np.maximum(z1, 0)
+    p1, arg1 = maxpool2d_forward(a1, 2, 2)
+    z2 = conv2d_forward_backward(p1, P["conv2.weight"], P["conv2.bias"], np.zeros((N, 64, 14, 14)), 1, 1)["y"]
+    a2 = np.maximum(z2, 0)
+    p2, arg2 = maxpool2d_forward(a2, 2, 2)
+    f = p2.reshape(N, -1)
+    h_pre = f @ P["fc1.weight"] + P["fc1.bias"]
+    h = np.maximum(h_pre, 0)
+    logits = h @ P["fc2.weight"] + P["fc2.bias"]
+    zmax = logits.max(1, keepdims=True)
+    lse = zmax[:, 0] + np.log(np.exp(logits - zmax).sum(1))
+    t = np.asarray(targets, np.int64)
+    loss = float(np.mean(lse - logits[np.arange(N), t]))
+    dlogits = np.exp(logits - lse[:, None])
+    dlogits[np.arange(N), t] -= 1
+    dlogits /= N
+    g = {"fc2.weight": h.T @ dlogits, "fc2.bias": dlogits.sum(0)}
+    dh = (dlogits @ P["fc2.weight"].T) * (h_pre > 0)
+    g["fc1.weight"] = f.T @ dh
+    g["fc1.bias"] = dh.sum(0)
+    dp2 = (dh @ P["fc1.weight"].T).reshape(p2.shape)
+    dz2 = maxpool2d_backward(dp2, arg2, 14, 14) * (z2 > 0)
+    r2 = conv2d_forward_backward(p1, P["conv2.weight"], P["conv2.bias"], dz2, 1, 1)
+    g["conv2.weight"], g["conv2.bias"] = r2["dw"], r2["db"]
+    dz1 = maxpool2d_backward(r2["dx"], arg1, 28, 28) * (z1 > 0)
+    r1 = conv2d_forward_backward(x, P["conv1.weight"], P["conv1.bias"], dz1, 1, 1)
+    g["conv1.weight"], g["conv1.bias"] = r1["dw"], r1["db"]
+    return loss, g
+
+
 def rel_frobenius(x, ref):
     """||x - ref||_F / ||ref||_F, the parity metric (<= 1e-3 tf32, <= 1e-5 3xTF32)."""
     x = np.asarray(x, np.float64); ref = np.asarray(ref, np.float64)

@@ -248,6 +248,64 @@ def test_conv2d_argument_errors_and_module(T):
     assert conv.weight.shape == (4, 1, 3, 3) and conv.bias.shape == (4,) and len(conv.parameters()) == 2
 
 
+def test_maxpool2d_forward_and_backward(T):
+    rng = np.random.default_rng(9)
+    for shape, k, s in (((2, 3, 8, 10), 2, None), ((1, 2, 9, 9), 3, 2), ((2, 1, 7, 8), (2, 3), (1, 2))):
+        x = rng.standard_normal(shape).astype(np.float32)
+        tx = T.from_numpy(x, requires_grad=True)
+        y = tx.maxpool2d(kernel_size=k, stride=s)
+        ref, arg = O.maxpool2d_forward(x, k, s)
+        assert np.array_equal(y.numpy(), ref.astype(np.float32))
+        dy = rng.standard_normal(ref.shape).astype(np.float32)
+        y.mul(T.from_numpy(dy)).sum().backward()
+        assert np.allclose(tx.grad.numpy(), O.maxpool2d_backward(dy, arg, shape[2], shape[3]), rtol=0, atol=1e-6)
+    with pytest.raises(ValueError, match="4D input"):
+        T.from_numpy(np.zeros((3, 4, 4), np.float32)).maxpool2d()
+    with pytest.raises(ValueError, match="output size invalid"):
+        T.from_numpy(np.zeros((1, 1, 2, 2), np.float32)).maxpool2d(kernel_size=3)
+
+
+def test_mnist_cnn_loss_and_gradients_against_the_oracle(T):
+    """The reference's CNN (two conv + pool stages, two Linear layers) on MNIST-shaped synthetic input: loss and
+    the gradient of every parameter against float64; then a few SGD steps lower the loss."""
+    from gradtuity_b200.nn import CNN, Flatten
+    from gradtuity_b200.optim import SGD
+
+    rng = np.random.default_rng(21)
+    model = CNN()
+    names = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
+    params = dict(zip(names, model.parameters()))
+    assert len(model.parameters()) == 8
+    # biases start at zero in the module; give them values so that their gradients paths carry signal
+    host = {}
+    for k, p in params.items():
+        a = p.numpy() if p.ndim > 1 else (rng.standard_normal(p.shape) * 0.05).astype(np.float32)
+        host[k] = a
+        from gradtuity_b200.cuda_mem import cuda_memcpy_htod
+        cuda_memcpy_htod(p.ptr, np.ascontiguousarray(a))
+    N = 8
+    x = rng.random((N, 1, 28, 28), dtype=np.float32)
+    t = rng.integers(0, 10, N)
+    tt = T.from_numpy(t.astype(np.float32))
+    logits = model(T.from_numpy(x))
+    assert logits.shape == (N, 10)
+    loss = logits.cross_entropy(tt, reduction="mean")
+    loss.backward()
+    ref_loss, ref_g = O.cnn_loss_and_grads(host, x, t)
+    assert abs(loss.item() - ref_loss) <= 2e-3 * abs(ref_loss)
+    for k, p in params.items():
+        assert O.rel_frobenius(p.grad.numpy(), ref_g[k]) <= 5e-3, k
+    opt = SGD(model.parameters(), lr=0.05)
+    first = loss.item()
+    for _ in range(15):
+        model.zero_grad()
+        l2 = model(T.from_numpy(x)).cross_entropy(tt, reduction="mean")
+        l2.backward()
+        opt.step()
+    assert l2.item() < 0.7 * first
+    assert Flatten(1)(T.from_numpy(np.zeros((2, 3, 4, 5), np.float32))).shape == (2, 60)
+
+
 def test_config0_linear_784_128(T):
     """Config 0: Linear(784 -> 128), batch 128, X ~ U[0,1), W and b ~ U(-1/28, 1/28), dY ~ N(0,1),
     seed 0; y, dX, dW, db against the float64 oracle."""
