@@ -135,7 +135,7 @@ __device__ __forceinline__ AttnSmem carve(uint8_t* smem_raw) {
 // tiles come from L2), turns it into the final probabilities exp(s - max) / sum, writes them to
 // shared memory (and, on request, from there to P with a TMA store), and accumulates O += P V in
 // tensor memory, so O never needs rescaling.
-__global__ void __maxnreg__(112)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_p,
                    const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
@@ -525,7 +525,7 @@ __device__ __forceinline__ void item_coords_kv(const AttnParams& p, int item, in
 }
 
 // dQ for one block of 128 queries; also delta = rowsum(dO * O).
-__global__ void __maxnreg__(112)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __grid_constant__ CUtensorMap map_kmn, const __grid_constant__ CUtensorMap map_dq,
@@ -724,7 +724,7 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 }
 
 // dK and dV for one block of 128 keys: everything transposed, so that a thread owns a key.
-__global__ void __maxnreg__(112)
+__global__ void __launch_bounds__(AT_THREADS, 1)
 gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                        const __grid_constant__ CUtensorMap map_qmn, const __grid_constant__ CUtensorMap map_domn,
