@@ -24,7 +24,7 @@ LAYOUT_NN, LAYOUT_NT, LAYOUT_TN = 0, 1, 2
 EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_CAUSAL = 0, 1, 2, 3, 4
 PREC_TF32, PREC_TF32X3, PREC_FP32 = 0, 1, 2
 CAUSAL_MASK_VALUE = -1.0e9
-GEMM_A_LOWER, GEMM_AT_LOWER, GEMM_CAUSAL_SKIP_MASKED = 1, 2, 4
+GEMM_A_LOWER, GEMM_AT_LOWER, GEMM_CAUSAL_SKIP_MASKED, GEMM_BIAS_PER_BATCH = 1, 2, 4, 8
 
 GT_OK = 0
 GT_ERR_INVALID_ARG = -1

@@ -76,7 +76,7 @@ extern "C" int gt_gemm_batched_ex(gt_ctx* ctx, int layout, int64_t M, int64_t N,
                                   const float* bias, float* aux, float alpha, int accumulate,
                                   int epilogue, int precision, int flags, void* stream) {
   if (ctx) {
-    if (flags & ~(GT_GEMM_A_LOWER | GT_GEMM_AT_LOWER | GT_GEMM_CAUSAL_SKIP_MASKED)) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: unknown flags 0x%x", flags);
+    if (flags & ~(GT_GEMM_A_LOWER | GT_GEMM_AT_LOWER | GT_GEMM_CAUSAL_SKIP_MASKED | GT_GEMM_BIAS_PER_BATCH)) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: unknown flags 0x%x", flags);
     if ((flags & (GT_GEMM_A_LOWER | GT_GEMM_AT_LOWER)) && M != K) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: triangular-A flags need a square A (M == K)");
     if ((flags & GT_GEMM_A_LOWER) && (flags & GT_GEMM_AT_LOWER)) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: A_LOWER and AT_LOWER exclude each other");
     if ((flags & GT_GEMM_A_LOWER) && layout == GT_LAYOUT_TN) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_batched_ex: A_LOWER describes an A stored (M, K)");

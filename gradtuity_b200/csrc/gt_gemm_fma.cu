@@ -16,7 +16,7 @@ constexpr int TM = 64, TN = 64, TK = 16, THREADS = 256;
 struct FmaParams {
   const float* A; const float* B; float* C; const float* bias; float* aux;
   long long sam, sak, sbk, sbn, ldc;
-  long long sA0, sA1, sB0, sB1, sC0, sC1;
+  long long sA0, sA1, sB0, sB1, sC0, sC1, bias_stride;
   int M, N, K;
   int batch0;
   int tiles_m, tiles_n;
@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(THREADS) gt_gemm_fma_kernel(const FmaParams p)
       int gn = n0 + tx * 4 + j;
       if (gn >= p.N) continue;
       float v = p.alpha * acc[i][j];
-      if (p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU) v += p.bias[gn];
+      if (p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU) v += p.bias[(long long)batch * p.bias_stride + gn];
       long long off = coff + (long long)gm * p.ldc + gn;
       if (p.aux) p.aux[off] = v;
       if (p.epilogue == GT_EPI_BIAS_RELU) v = fmaxf(v, 0.0f);
@@ -117,6 +117,10 @@ int gt_gemm_fma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream) 
   p.tiles_m = (int)((g.M + TM - 1) / TM);
   p.tiles_n = (int)((g.N + TN - 1) / TN);
   p.epilogue = g.epilogue; p.accumulate = g.accumulate; p.alpha = g.alpha;
+  p.bias_stride = (g.flags & GT_GEMM_BIAS_PER_BATCH) ? g.N : 0;
+  // batch entries that share one C would race on a plain read-modify-write
+  if (g.batch0 * g.batch1 > 1 && ((g.batch0 > 1 && g.sC0 == 0) || (g.batch1 > 1 && g.sC1 == 0)))
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm_batched: batch entries sharing one C are served by the tensor-core kernel only (tf32, aligned operands)");
   long long blocks = (long long)p.tiles_m * p.tiles_n * g.batch0 * g.batch1;
   if (blocks <= 0 || blocks > 0x7fffffffLL) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "fma gemm: %lld tiles out of range", blocks);
   gt_gemm_fma_kernel<<<(unsigned)blocks, THREADS, 0, stream>>>(p);

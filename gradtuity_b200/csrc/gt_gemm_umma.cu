@@ -48,6 +48,7 @@ constexpr int SMEM_BUDGET = 232448 - 1024 - 512 - EPI_SCRATCH_BYTES;   // 227 KB
 struct UmmaParams {
   const float* A; long long lda, sA0, sA1;     // used only when A is copied with cp.async
   float* C; const float* bias; float* aux;
+  long long bias_stride;                 // elements between the bias rows of consecutive batch entries (0: one shared bias)
   long long ldc, sC0, sC1;
   int M, N, K;
   int batch0;
@@ -125,7 +126,7 @@ __device__ __forceinline__ bool tile_is_masked(const UmmaParams& p, int tm, int 
 
 // Fused epilogue for 32 consecutive columns of one output row: v holds the accumulator.
 // cpre: the 32 values of C this chunk accumulates into, loaded ahead of time (or null).
-__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float* v, int row, int nb, long long row_off,
+__device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float* bias, const float* v, int row, int nb, long long row_off,
                                                const float4* cpre = nullptr) {
   const bool full_chunk = (nb + 32 <= p.N);
   float* cptr = p.C + row_off + nb;
@@ -135,7 +136,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float*
     for (int j = 0; j < 32; j += 4) {
       float4 x = make_float4(p.alpha * v[j], p.alpha * v[j + 1], p.alpha * v[j + 2], p.alpha * v[j + 3]);
       if (has_bias) {
-        const float4 b = *reinterpret_cast<const float4*>(p.bias + nb + j);
+        const float4 b = *reinterpret_cast<const float4*>(bias + nb + j);
         x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
       }
       if (p.aux) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
@@ -163,7 +164,7 @@ __device__ __forceinline__ void epilogue_chunk(const UmmaParams& p, const float*
       const int col = nb + j;
       if (col < p.N) {
         float x = p.alpha * v[j];
-        if (has_bias) x += p.bias[col];
+        if (has_bias) x += bias[col];
         if (p.aux) p.aux[row_off + col] = x;
         if (p.epilogue == GT_EPI_BIAS_RELU) x = fmaxf(x, 0.0f);
         else if (p.epilogue == GT_EPI_BIAS_GELU) x = gt_gelu_tanh(x);
@@ -194,7 +195,7 @@ __device__ __forceinline__ bool prefetch_c(const UmmaParams& p, bool enabled, in
 // accumulator columns early, measured no faster: the warps are bound by the instructions they issue,
 // not by these latencies).  With an aux output the pre-activation is stored directly from registers.
 // This is the general form: bias, aux and the output may end inside the chunk.
-__device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
+__device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                        int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                        uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
   const int row = row0 + lane;
@@ -207,12 +208,12 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
     if (has_bias) {
       const int col = nb + j;                       // bias may end inside this chunk
       if (col + 3 < p.N) {
-        const float4 b = *reinterpret_cast<const float4*>(p.bias + col);
+        const float4 b = *reinterpret_cast<const float4*>(bias + col);
         x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
       } else {
-        if (col < p.N) x.x += p.bias[col];
-        if (col + 1 < p.N) x.y += p.bias[col + 1];
-        if (col + 2 < p.N) x.z += p.bias[col + 2];
+        if (col < p.N) x.x += bias[col];
+        if (col + 1 < p.N) x.y += bias[col + 1];
+        if (col + 2 < p.N) x.z += bias[col + 2];
       }
     }
     if (p.aux && row_ok && nb + j + 3 < p.N) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
@@ -245,13 +246,13 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
 // instruction-bound on short-K problems (the score products, the 768-deep Linear layers), so this
 // is what their throughput depends on.
 template <int EPI, bool AUX>
-__device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
+__device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                         int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                         uint8_t* tile, uint32_t tile_u32, bool add) {
   constexpr bool HAS_BIAS = EPI >= GT_EPI_BIAS && EPI <= GT_EPI_BIAS_GELU;
   const int row = row0 + lane;
   const float alpha = p.alpha;
-  const float4* bias4 = reinterpret_cast<const float4*>(p.bias + nb);
+  const float4* bias4 = reinterpret_cast<const float4*>(bias + nb);
   float4* aux4 = reinterpret_cast<float4*>(p.aux + row_off + nb);
   uint8_t* my_row = tile + lane * 128;
   const int sw = lane & 7;
@@ -283,10 +284,10 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
   if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, add);
 }
 
-__device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CUtensorMap* map_c, const float* v, int lane,
+__device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                    int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                    uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
-#define GT_EPI_FAST(E, X) epilogue_chunk_tma_fast<E, X>(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add)
+#define GT_EPI_FAST(E, X) epilogue_chunk_tma_fast<E, X>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add)
   if (nb + 32 <= p.N) {                              // warp-uniform
     switch (epi) {
       case GT_EPI_NONE:
@@ -312,13 +313,13 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const CU
     }
   }
 #undef GT_EPI_FAST
-  epilogue_chunk_tma_any(p, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, epi, add);
+  epilogue_chunk_tma_any(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, epi, add);
 }
 
 // Same epilogue for outputs whose rows are not 16-byte aligned (odd leading dimension, e.g. the
 // 50257-wide logits): the warp's 32 x 32 accumulator block goes through a shared-memory tile so
 // that each store instruction writes 32 consecutive floats of ONE row, whatever its alignment.
-__device__ __forceinline__ void epilogue_chunk_coalesced(const UmmaParams& p, const float* v, float* tile, int lane,
+__device__ __forceinline__ void epilogue_chunk_coalesced(const UmmaParams& p, const float* bias, const float* v, float* tile, int lane,
                                                          int row0, int nb, long long batch_off) {
 #pragma unroll
   for (int j = 0; j < 32; ++j) tile[lane * 32 + (j ^ lane)] = v[j];      // XOR keeps both phases free of bank conflicts
@@ -326,7 +327,7 @@ __device__ __forceinline__ void epilogue_chunk_coalesced(const UmmaParams& p, co
   const int col = nb + lane;
   const bool col_ok = col < p.N;
   const bool has_bias = p.epilogue >= GT_EPI_BIAS && p.epilogue <= GT_EPI_BIAS_GELU;
-  const float b = (has_bias && col_ok) ? p.bias[col] : 0.0f;
+  const float b = (has_bias && col_ok) ? bias[col] : 0.0f;
   const int rows = min(32, p.M - row0);
   for (int r = 0; r < rows; ++r) {
     if (col_ok) {
@@ -636,6 +637,7 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1 + (long long)ks * p.ks_stride;
       const long long row_off = batch_off + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
+      const float* unit_bias = p.bias ? p.bias + (long long)batch * p.bias_stride : nullptr;   // one bias row per batch entry when asked
       // a K share of a last-wave tile adds its partial sum into C; the bias goes in with share 0
       const bool tail_unit = p.tail_split > 1 && ks >= 0;
       const bool unit_add = p.accumulate != 0 || tail_unit;
@@ -688,9 +690,9 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           const int c = lc * EPI_SETS + eset;
           const int nb = n0 + c * 32;
           if (c < BN / 32 && nb < p.N) {
-            if (p.c_tma) epilogue_chunk_tma(p, &map_c, &sum[lc * 32], lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, p.epilogue, p.accumulate != 0);
-            else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, &sum[lc * 32], row, nb, row_off); }
-            else epilogue_chunk_coalesced(p, &sum[lc * 32], epi_tile, lane, row0, nb, batch_off);
+            if (p.c_tma) epilogue_chunk_tma(p, unit_bias, &map_c, &sum[lc * 32], lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, p.epilogue, p.accumulate != 0);
+            else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, unit_bias, &sum[lc * 32], row, nb, row_off); }
+            else epilogue_chunk_coalesced(p, unit_bias, &sum[lc * 32], epi_tile, lane, row0, nb, batch_off);
           }
         }
       } else {
@@ -710,9 +712,9 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.0f;
           }
-          if (p.c_tma) epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, unit_epi, unit_add);
-          else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, v, row, nb, row_off); }
-          else epilogue_chunk_coalesced(p, v, epi_tile, lane, row0, nb, batch_off);
+          if (p.c_tma) epilogue_chunk_tma(p, unit_bias, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, unit_epi, unit_add);
+          else if (p.vec_ok) { if (row_ok) epilogue_chunk(p, unit_bias, v, row, nb, row_off); }
+          else epilogue_chunk_coalesced(p, unit_bias, v, epi_tile, lane, row0, nb, batch_off);
         }
         if (!masked) {
           tc_fence_before();
@@ -894,6 +896,7 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1;
       const long long row_off = batch_off + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
+      const float* unit_bias = p.bias ? p.bias + (long long)batch * p.bias_stride : nullptr;
       if (!mbar_wait(bar_tfull + 8 * half, tph, abort_flag, p.status)) break;
       tc_fence_after();
 #pragma unroll 1
@@ -904,9 +907,9 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tc_ld32(lane_base + (uint32_t)(c * 32), v);
         tc_wait_ld();
         if (p.c_tma) {
-          epilogue_chunk_tma(p, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, p.epilogue, p.accumulate != 0);
+          epilogue_chunk_tma(p, unit_bias, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, p.epilogue, p.accumulate != 0);
         } else if (row_ok) {
-          epilogue_chunk(p, v, row, nb, row_off);     // host guarantees aligned rows for this kernel
+          epilogue_chunk(p, unit_bias, v, row, nb, row_off);     // host guarantees aligned rows for this kernel
         }
       }
       tc_fence_before();
@@ -1080,7 +1083,8 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   const bool big_enough = t256_min_tiles > 0 ? (g.K >= t256_min_k && tiles256 >= t256_min_tiles)
                                              : ((g.K >= t256_min_k && tiles256 * 5 >= (long long)ctx->sm_count * 3) ||
                                                 (g.K >= 512 && tiles256 >= (long long)ctx->sm_count * 8 && !g.aux));
-  const bool use256 = !t256_off && g.flags == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && big_enough &&
+  const int hints = g.flags & (GT_GEMM_A_LOWER | GT_GEMM_AT_LOWER | GT_GEMM_CAUSAL_SKIP_MASKED);
+  const bool use256 = !t256_off && hints == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && big_enough &&
                       tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (!g.aux || ((uintptr_t)g.aux & 15) == 0) &&
                       (!g.bias || ((uintptr_t)g.bias & 15) == 0);
   static const int force_bn = getenv("GRADTUITY_GEMM_FORCE_BN") ? atoi(getenv("GRADTUITY_GEMM_FORCE_BN")) : 0;   // tuning aid
@@ -1152,6 +1156,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   UmmaParams p;
   p.A = g.A; p.lda = g.lda; p.sA0 = g.sA0; p.sA1 = g.sA1;
   p.C = g.C; p.bias = g.bias; p.aux = g.aux;
+  p.bias_stride = (g.flags & GT_GEMM_BIAS_PER_BATCH) ? g.N : 0;
   p.ldc = g.ldc; p.sC0 = g.sC0; p.sC1 = g.sC1;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
   p.batch0 = (int)g.batch0;
@@ -1171,7 +1176,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   //    cannot be described to TMA.
   const int num_kb = (int)((g.K + BK - 1) / BK);
   int ksplit = 1;
-  if (!x3 && g.epilogue != GT_EPI_CAUSAL && g.flags == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
+  if (!x3 && g.epilogue != GT_EPI_CAUSAL && hints == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
     ksplit = (int)(ctx->sm_count / tiles);
     if (ksplit > num_kb / 8) ksplit = num_kb / 8;
     if (ksplit > 32) ksplit = 32;
@@ -1201,6 +1206,14 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   const bool c_dense = g.ldc == g.N && (g.batch0 == 1 || g.sC0 == g.M * g.N) && (g.batch1 == 1 || g.sC1 == g.M * g.N * g.batch0);
   const bool splitk_direct = ksplit > 1 && !deterministic && !c_tma_off && g.epilogue == GT_EPI_NONE && !g.aux &&
                              tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (g.accumulate || c_dense);
+  // Batch entries that share one C (batch stride 0, "C += sum over the batch") rely on the atomic TMA
+  // reduce-add of the epilogue; a per-batch bias is applied by the tensor-core kernel's epilogue only.
+  const bool c_shared = nbatch > 1 && ((g.batch0 > 1 && g.sC0 == 0) || (g.batch1 > 1 && g.sC1 == 0));
+  if (c_shared && (!g.accumulate || c_tma_off || !tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) || (ksplit > 1 && !splitk_direct) ||
+                   g.epilogue != GT_EPI_NONE || g.aux))
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm_batched: batch entries sharing one C need accumulate = 1, no epilogue and a 16-byte aligned C");
+  if ((g.flags & GT_GEMM_BIAS_PER_BATCH) && ksplit > 1 && !splitk_direct)
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm_batched: a per-batch bias is not available on this split-K path");
   if (splitk_direct) {
     if (!g.accumulate) GT_CUDA_OK(ctx, cudaMemsetAsync(g.C, 0, (size_t)plane * sizeof(float), stream));
     p.accumulate = 1;
@@ -1230,7 +1243,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   // epilogue's TMA reduce-add (unless the call is C += ..., the kernel zeroes C under those tiles at its
   // start and the shares wait for that; see the epilogue warps).
   static const bool tail_off = getenv("GRADTUITY_GEMM_NO_TAIL_SPLIT") != nullptr;
-  if (!tail_off && !deterministic && !use256 && !x3 && !a_gen && ksplit == 1 && p.c_tma && nbatch == 1 && g.flags == 0 && !g.aux &&
+  if (!tail_off && !deterministic && !use256 && !x3 && !a_gen && ksplit == 1 && p.c_tma && nbatch == 1 && hints == 0 && !g.aux &&
       (g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS) && num_kb >= 16 && tiles > ctx->sm_count) {
     const int P = ctx->sm_count;
     const int tail = (int)(tiles % P);

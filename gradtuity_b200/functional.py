@@ -58,10 +58,30 @@ def randn(shape, requires_grad: bool = False, seed: int | None = None, std: floa
 
 def zero_grad(params: list[Tensor]) -> None:
     """Zero every parameter's gradient, allocating it if absent (gradtuity/functional.py:206-229)."""
-    for p in params:
+    # Parameters that sit side by side in memory (the packed q / k / v weights of CausalSelfAttention) get
+    # their fresh gradients side by side too, so that a batched backward can address them as one batch.
+    i, n = 0, len(params)
+    while i < n:
+        p = params[i]
         if not p.requires_grad:
+            i += 1
             continue
-        if p.grad is None:
+        if p.grad is not None:
+            cuda_memset(p.grad.ptr, 0, p.grad.nbytes)
+            i += 1
+            continue
+        j = i + 1
+        while (j < n and params[j].requires_grad and params[j].grad is None
+               and params[j].ptr == params[j - 1].ptr + params[j - 1].numel * 4):
+            j += 1
+        if j - i == 1:
             p.grad = zeros(p.shape)
         else:
-            cuda_memset(p.grad.ptr, 0, p.grad.nbytes)
+            from .tensor import Storage, alloc_storage
+            total = sum(q.numel for q in params[i:j]) * 4
+            block = alloc_storage(total, zero=True)
+            off = 0
+            for q in params[i:j]:
+                q.grad = Tensor._from_ptr(block.ptr + off, q.shape, owns_memory=False, base=block)
+                off += q.numel * 4
+        i = j

@@ -99,6 +99,24 @@ class Module:
                 setattr(cur, parts[-1], tensor)
             except AttributeError as e:
                 raise ValueError(f"load_state_dict: cannot set key {key!r}") from e
+        # modules that keep several parameters in one buffer (CausalSelfAttention) restore that layout
+        seen: set[int] = set()
+
+        def visit(obj) -> None:
+            if id(obj) in seen:
+                return
+            seen.add(id(obj))
+            if isinstance(obj, Module):
+                hook = getattr(obj, "_after_load", None)
+                if hook is not None:
+                    hook()
+                for _, attr in obj._children():
+                    visit(attr)
+            elif isinstance(obj, (list, tuple)):
+                for item in obj:
+                    visit(item)
+
+        visit(self)
 
     def __call__(self, x: Tensor) -> Tensor:
         raise NotImplementedError("Subclasses must implement __call__")
@@ -248,6 +266,7 @@ class CausalSelfAttention(Module):
         self.bo = zeros((embed_dim,), requires_grad=True)
         self.attn_dropout = Dropout(p=attn_pdrop) if attn_pdrop > 0 else None
         self.resid_dropout = Dropout(p=resid_pdrop) if resid_pdrop > 0 else None
+        self._pack_qkv()
 
     def __call__(self, x: Tensor) -> Tensor:
         B, S, E = x.shape
@@ -255,10 +274,7 @@ class CausalSelfAttention(Module):
             raise ValueError(f"input last dim {E} must equal embed_dim {self.embed_dim}")
         if self.attn_dropout is not None and self.attn_dropout.p > 0 and self.training:
             raise NotImplementedError("attention dropout with p > 0 is not part of the GEMM path")
-        x_flat = x.view((B * S, E))
-        q = x_flat.linear(self.Wq, self.bq).view((B, S, E))
-        k = x_flat.linear(self.Wk, self.bk).view((B, S, E))
-        v = x_flat.linear(self.Wv, self.bv).view((B, S, E))
+        q, k, v = x.linear_qkv(self.Wq, self.Wk, self.Wv, self.bq, self.bk, self.bv)     # one batched launch when packed
         ctx = q.causal_attention(k, v, self.num_heads)
         out = ctx.view((B * S, E)).linear(self.Wo, self.bo)
         if self.resid_dropout is not None:
@@ -267,6 +283,30 @@ class CausalSelfAttention(Module):
 
     def parameters(self) -> list[Tensor]:
         return [self.Wq, self.Wk, self.Wv, self.Wo, self.bq, self.bk, self.bv, self.bo]
+
+    def _pack_qkv(self) -> None:
+        """Put Wq, Wk, Wv side by side in one buffer, and bq, bk, bv in another, so that `Tensor.linear_qkv`
+        can address them as a batch.  The parameters stay three tensors each (same names, shapes, values);
+        only where they live changes.  Called at construction and after `load_state_dict`, never later: an
+        optimizer holds on to the tensors it was given."""
+        from .cuda_mem import cuda_memcpy_dtod
+        from .tensor import F32, alloc_storage
+        for names in (("Wq", "Wk", "Wv"), ("bq", "bk", "bv")):
+            ts = [getattr(self, n) for n in names]
+            nbytes = ts[0].numel * F32
+            if any(t.shape != ts[0].shape for t in ts):
+                continue
+            if ts[1].ptr - ts[0].ptr == nbytes and ts[2].ptr - ts[1].ptr == nbytes:
+                continue
+            block = alloc_storage(3 * nbytes)
+            for i, (n, t) in enumerate(zip(names, ts)):
+                cuda_memcpy_dtod(block.ptr + i * nbytes, t.ptr, nbytes)
+                new = Tensor._from_ptr(block.ptr + i * nbytes, t.shape, owns_memory=False, requires_grad=t.requires_grad,
+                                       name=t.name, base=block)
+                setattr(self, n, new)
+
+    def _after_load(self) -> None:
+        self._pack_qkv()
 
     def __repr__(self) -> str:
         return f"CausalSelfAttention(embed_dim={self.embed_dim}, num_heads={self.num_heads})"

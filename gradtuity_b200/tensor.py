@@ -113,10 +113,35 @@ def empty_tensor(shape: tuple[int, ...], *, requires_grad: bool = False, zero: b
     return Tensor._wrap(st, shape, requires_grad=requires_grad, name=name)
 
 
+class _GradGroup:
+    """One buffer for the gradients of several tensors that a single backward wants to read as one batch
+    (the q, k, v outputs of `linear_qkv`): member i's gradient is slice i.  The buffer is allocated when the
+    first member's gradient is asked for; a slice nobody wrote is zeroed before the group's owner reads it."""
+
+    def __init__(self, members: int, numel_each: int) -> None:
+        self.members = members
+        self.numel_each = numel_each
+        self.storage: Storage | None = None
+        self.written = [False] * members
+
+    def slice_tensor(self, index: int, shape: tuple[int, ...], zero: bool) -> "Tensor":
+        if self.storage is None:
+            self.storage = alloc_storage(self.members * self.numel_each * F32)
+        ptr = self.storage.ptr + index * self.numel_each * F32
+        if zero:
+            cuda_memset(ptr, 0, self.numel_each * F32)
+        self.written[index] = True
+        return Tensor._from_ptr(ptr, shape, owns_memory=False, base=self.storage)
+
+
 def ensure_grad(t: "Tensor") -> None:
     """Allocate a zero grad tensor if t.grad is None (gradtuity/tensor.py:152-155)."""
     if t.grad is None:
-        t.grad = empty_tensor(t.shape, zero=True, requires_grad=False)
+        if t._grad_slot is not None:
+            group, index = t._grad_slot
+            t.grad = group.slice_tensor(index, t.shape, zero=True)
+        else:
+            t.grad = empty_tensor(t.shape, zero=True, requires_grad=False)
 
 
 def accum_grad(t: "Tensor", g: "Tensor") -> None:
@@ -130,7 +155,7 @@ def pass_grad(t: "Tensor", g: "Tensor") -> None:
     receiving a copy: g is the finished gradient of the node whose backward is running, nothing
     reads it afterwards, and each backward hands its g to at most one parent this way.  Leaves
     (parameters) always get their own buffer."""
-    if t.grad is None and t._backward is not None and g.numel == t.numel:
+    if t.grad is None and t._backward is not None and g.numel == t.numel and t._grad_slot is None:
         if g._pitch is not None and t.shape[-1] == g.shape[-1]:
             # a padded-row gradient keeps its pitch on the way up (the view between the LM head and the loss)
             t.grad = Tensor._wrap(Storage(g._st.ptr, g._st.nbytes, owns=False, base=g._st), t.shape)
@@ -159,7 +184,11 @@ def grad_target(t: "Tensor") -> tuple[int, bool]:
     (C = ...); an existing one is accumulated into (C += ...), which is the reference's contract
     (gradtuity/tensor.py:152-155 zero-fills and always accumulates)."""
     if t.grad is None:
-        t.grad = empty_tensor(t.shape, requires_grad=False)
+        if t._grad_slot is not None:
+            group, index = t._grad_slot
+            t.grad = group.slice_tensor(index, t.shape, zero=False)
+        else:
+            t.grad = empty_tensor(t.shape, requires_grad=False)
         return t.grad.ptr, False
     return t.grad.ptr, True
 
@@ -169,6 +198,8 @@ class Tensor:
 
     # Row pitch in floats when the rows of the last dimension are padded in memory (None: packed).
     _pitch = None
+    # (group, index) when this tensor's gradient must live in a slice of a shared buffer (see _GradGroup).
+    _grad_slot = None
 
     def __init__(self, data, shape: tuple[int, ...] | None = None, requires_grad: bool = False, name: str = "") -> None:
         if shape is None:
@@ -521,6 +552,89 @@ class Tensor:
 
         out._set_graph(parents=(self, weight, bias), backward_fn=_backward)
         return out
+
+    def linear_qkv(self, wq: "Tensor", wk: "Tensor", wv: "Tensor", bq: "Tensor", bk: "Tensor", bv: "Tensor"):
+        """(x @ Wq + bq, x @ Wk + bk, x @ Wv + bv) for x of shape (..., E): the three projections of
+        CausalSelfAttention (gradtuity/nn.py:534-536 calls `linear` three times).  When the three weights sit
+        at a uniform distance in memory and the three biases are adjacent (nn.CausalSelfAttention allocates
+        them that way), forward and backward are batched launches: one NN GEMM with a shared A and a bias row
+        per batch entry; dX as one NT launch whose three batch entries add into the same buffer; dW as one TN
+        launch with a shared A.  Otherwise this is three `linear` calls.  Results are the same either way."""
+        x = self
+        lead = x._shape[:-1]
+        K = x._shape[-1]
+        M = x.numel // K
+        for w, b in ((wq, bq), (wk, bk), (wv, bv)):
+            if w.ndim != 2 or b.ndim != 1 or w._shape[0] != K or w._shape != wq._shape or b._shape[0] != w._shape[1]:
+                raise ValueError(f"linear_qkv shape mismatch: input {x._shape}, weight {w._shape}, bias {b._shape}")
+        N = wq._shape[1]
+        out_shape = lead + (N,)
+        sw = wk.ptr - wq.ptr
+        batched = (x.ndim >= 2 and sw > 0 and wv.ptr - wk.ptr == sw and sw % 16 == 0 and bk.ptr - bq.ptr == N * F32
+                   and bv.ptr - bk.ptr == N * F32 and N % 4 == 0 and K % 4 == 0 and wq.ptr % 16 == 0 and x.ptr % 16 == 0
+                   and bq.ptr % 16 == 0 and _gemm.default_precision() != _lib.PREC_FP32)
+        if not batched:
+            x2 = x.view((M, K))
+            return tuple(x2.linear(w, b).view(out_shape) for w, b in ((wq, bq), (wk, bk), (wv, bv)))
+        from ._lib import GEMM_BIAS_PER_BATCH
+        sw //= F32
+        y3 = alloc_storage(3 * M * N * F32)
+        _gemm.gemm_batched(LAYOUT_NN, M, N, K, x.ptr, K, 0, 0, wq.ptr, N, sw, 0, y3.ptr, N, M * N, 0, 3, 1,
+                           bias_ptr=bq.ptr, epilogue=EPI_BIAS, flags=GEMM_BIAS_PER_BATCH)
+        outs = [Tensor._from_ptr(y3.ptr + i * M * N * F32, out_shape, owns_memory=False, base=y3) for i in range(3)]
+        ws, bs = (wq, wk, wv), (bq, bk, bv)
+        if not (x.requires_grad or any(w.requires_grad for w in ws) or any(b.requires_grad for b in bs)):
+            return tuple(outs)
+        # Graph: a hidden node holds the batched backward; q, k, v are its children and their gradients are
+        # the three slices of one buffer, so the backward reads them as one batch without copying.
+        hub = Tensor._from_ptr(y3.ptr, (3, M, N), owns_memory=False, base=y3)
+        group = _GradGroup(3, M * N)
+
+        def _hub_backward(_g: "Tensor") -> None:
+            for i in range(3):
+                if not group.written[i]:
+                    group.slice_tensor(i, (M, N), zero=True)
+            dy = group.storage.ptr
+            if x.requires_grad:
+                ptr, acc = grad_target(x)
+                if not acc:
+                    cuda_memset(ptr, 0, M * K * F32)
+                _gemm.gemm_batched(LAYOUT_NT, M, K, N, dy, N, M * N, 0, wq.ptr, N, sw, 0, ptr, K, 0, 0, 3, 1, accumulate=True)
+            if any(w.requires_grad for w in ws):
+                if all(w.requires_grad and w.grad is None for w in ws):
+                    blk = alloc_storage(3 * K * N * F32)
+                    for i, w in enumerate(ws):
+                        w.grad = Tensor._from_ptr(blk.ptr + i * K * N * F32, w.shape, owns_memory=False, base=blk)
+                    g0, sg, acc = blk.ptr, K * N, False
+                else:
+                    for w in ws:
+                        if w.requires_grad:
+                            ensure_grad(w)
+                    ptrs = [w.grad.ptr if w.requires_grad else 0 for w in ws]
+                    sg = ptrs[1] - ptrs[0]
+                    uniform = all(w.requires_grad for w in ws) and sg > 0 and ptrs[2] - ptrs[1] == sg and sg % 16 == 0
+                    g0, sg, acc = (ptrs[0], sg // F32, True) if uniform else (0, 0, True)
+                if g0:
+                    _gemm.gemm_batched(LAYOUT_TN, K, N, M, x.ptr, K, 0, 0, dy, N, M * N, 0, g0, N, sg, 0, 3, 1, accumulate=acc)
+                else:
+                    for i, w in enumerate(ws):
+                        if w.requires_grad:
+                            _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dy + i * M * N * F32, N, w.grad.ptr, N, accumulate=True)
+            for i, b in enumerate(bs):
+                if b.requires_grad:
+                    ensure_grad(b)
+                    _call("gt_colsum_acc", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
+
+        hub._set_graph(parents=(x,) + ws + bs, backward_fn=_hub_backward)
+
+        def _child_backward(_g: "Tensor") -> None:
+            if hub.grad is None:                       # the slices already hold the gradients: only wake the hub
+                hub.grad = Tensor._from_ptr(group.storage.ptr, (3, M, N), owns_memory=False, base=group.storage)
+
+        for i, o in enumerate(outs):
+            o._grad_slot = (group, i)
+            o._set_graph(parents=(hub,), backward_fn=_child_backward)
+        return tuple(outs)
 
     def linear_relu(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
         """Y = relu(X @ W + b), one kernel; backward masks dY by [Y > 0] into a temporary and

@@ -147,10 +147,16 @@ int gt_gemm_batched(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
  *   GT_GEMM_CAUSAL_SKIP_MASKED  with GT_EPI_CAUSAL: 128-row tiles wholly above the diagonal are not
  *                               written at all (their contents are undefined); for consumers that
  *                               never read above the diagonal
- * The hints only remove work whose result is known to be zero / unused; results are unchanged.   */
+ * The hints only remove work whose result is known to be zero / unused; results are unchanged.
+ *   GT_GEMM_BIAS_PER_BATCH      (not a hint) bias holds batch0 * batch1 rows of N: batch entry
+ *                               (i0, i1) uses row i0 + i1 * batch0 instead of one row shared by all.
+ * Batch strides of 0 are allowed.  An operand with stride 0 is shared by the batch entries (the q, k
+ * and v projections of one input are one launch with strideA0 = 0).  A C with stride 0 receives the
+ * SUM over the batch entries: that needs accumulate = 1, no epilogue, and the tensor-core path.  */
 #define GT_GEMM_A_LOWER             1
 #define GT_GEMM_AT_LOWER            2
 #define GT_GEMM_CAUSAL_SKIP_MASKED  4
+#define GT_GEMM_BIAS_PER_BATCH      8
 int gt_gemm_batched_ex(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
                        const float* A, int64_t lda, int64_t strideA0, int64_t strideA1,
                        const float* B, int64_t ldb, int64_t strideB0, int64_t strideB1,

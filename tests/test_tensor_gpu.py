@@ -265,16 +265,19 @@ def test_maxpool2d_forward_and_backward(T):
         T.from_numpy(np.zeros((1, 1, 2, 2), np.float32)).maxpool2d(kernel_size=3)
 
 
-def test_mnist_cnn_loss_and_gradients_against_the_oracle(T):
+@pytest.mark.parametrize("precision,tol", [("3xtf32", 2e-4), ("tf32", 3e-2)])
+def test_mnist_cnn_loss_and_gradients_against_the_oracle(T, precision, tol, monkeypatch):
     """The reference's CNN (two conv + pool stages, two Linear layers) on MNIST-shaped synthetic input: loss and
-    the gradient of every parameter against float64; then a few SGD steps lower the loss."""
+    the gradient of every parameter against float64; then a few SGD steps lower the loss.  In tf32 mode a
+    rounding difference can flip a ReLU mask or the winner of a pooling window, which moves the early layers'
+    gradients by about a percent; the 3xTF32 run holds the tight bar."""
+    monkeypatch.setenv("GRADTUITY_GEMM_PRECISION", precision)
     from gradtuity_b200.nn import CNN, Flatten
     from gradtuity_b200.optim import SGD
 
     rng = np.random.default_rng(21)
     model = CNN()
-    names = ["conv1.weight", "conv1.bias", "conv2.weight", "conv2.bias", "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias"]
-    params = dict(zip(names, model.parameters()))
+    params = {f"{m}.{a}": getattr(getattr(model, m), a) for m in ("conv1", "conv2", "fc1", "fc2") for a in ("weight", "bias")}
     assert len(model.parameters()) == 8
     # biases start at zero in the module; give them values so that their gradients paths carry signal
     host = {}
@@ -294,7 +297,7 @@ def test_mnist_cnn_loss_and_gradients_against_the_oracle(T):
     ref_loss, ref_g = O.cnn_loss_and_grads(host, x, t)
     assert abs(loss.item() - ref_loss) <= 2e-3 * abs(ref_loss)
     for k, p in params.items():
-        assert O.rel_frobenius(p.grad.numpy(), ref_g[k]) <= 5e-3, k
+        assert O.rel_frobenius(p.grad.numpy(), ref_g[k]) <= tol, k
     opt = SGD(model.parameters(), lr=0.05)
     first = loss.item()
     for _ in range(15):
@@ -304,6 +307,85 @@ def test_mnist_cnn_loss_and_gradients_against_the_oracle(T):
         opt.step()
     assert l2.item() < 0.7 * first
     assert Flatten(1)(T.from_numpy(np.zeros((2, 3, 4, 5), np.float32))).shape == (2, 60)
+
+
+@pytest.mark.parametrize("packed", [True, False])
+def test_linear_qkv_matches_three_linears(T, packed):
+    """The batched q / k / v projection (shared A, a bias row per batch entry; backward with three batch entries
+    adding into one dX and a shared-A dW launch) against the float64 oracle, for parameters that sit side by side
+    in memory and for parameters that do not (three `linear` calls)."""
+    from gradtuity_b200.nn import CausalSelfAttention
+
+    rng = np.random.default_rng(31)
+    Bn, S, E = 2, 192, 128
+    attn = CausalSelfAttention(E, 4)
+    ws = [(rng.standard_normal((E, E)) / np.sqrt(E)).astype(np.float32) for _ in range(3)]
+    bs = [rng.standard_normal(E).astype(np.float32) for _ in range(3)]
+    if packed:
+        from gradtuity_b200.cuda_mem import cuda_memcpy_htod
+        tws, tbs = [attn.Wq, attn.Wk, attn.Wv], [attn.bq, attn.bk, attn.bv]
+        assert tws[1].ptr - tws[0].ptr == E * E * 4 and tbs[2].ptr - tbs[1].ptr == E * 4      # the module packs them
+        for t, a in zip(tws + tbs, ws + bs):
+            cuda_memcpy_htod(t.ptr, a)
+    else:
+        pad = T.from_numpy(np.zeros(7, np.float32))                                     # breaks the adjacency on purpose
+        tws = [T.from_numpy(w, requires_grad=True) for w in ws]
+        tbs = [T.from_numpy(b, requires_grad=True) for b in (bs[0], bs[2], bs[1])]
+        tbs = [tbs[0], tbs[2], tbs[1]]
+        del pad
+    x = rng.standard_normal((Bn, S, E)).astype(np.float32)
+    dys = [rng.standard_normal((Bn, S, E)).astype(np.float32) for _ in range(3)]
+    tx = T.from_numpy(x, requires_grad=True)
+    for rep in range(2):                                                                   # second pass accumulates
+        outs = tx.linear_qkv(tws[0], tws[1], tws[2], tbs[0], tbs[1], tbs[2])
+        loss = None
+        for o, dy in zip(outs, dys):
+            assert o.shape == (Bn, S, E)
+            term = o.mul(T.from_numpy(dy)).sum()
+            loss = term if loss is None else loss.add(term)
+        loss.backward()
+    x2 = x.reshape(-1, E)
+    refs = [O.linear_forward_backward(x2, w, b, dy.reshape(-1, E)) for w, b, dy in zip(ws, bs, dys)]
+    for o, r in zip(outs, refs):
+        assert O.rel_frobenius(o.numpy().reshape(-1, E), r["y"]) <= 1e-3
+    assert O.rel_frobenius(tx.grad.numpy().reshape(-1, E), 2 * sum(r["dx"] for r in refs)) <= 1e-3
+    for tw, tb, r in zip(tws, tbs, refs):
+        assert O.rel_frobenius(tw.grad.numpy(), 2 * r["dw"]) <= 1e-3
+        assert O.rel_frobenius(tb.grad.numpy(), 2 * r["db"]) <= 1e-3
+
+
+def test_linear_qkv_with_one_unused_output(T):
+    """Only q feeds the loss: the slices of k and v in the shared gradient buffer are zeroed before the batched
+    backward reads them."""
+    from gradtuity_b200.nn import CausalSelfAttention
+
+    rng = np.random.default_rng(32)
+    E = 64
+    attn = CausalSelfAttention(E, 1)
+    x = rng.standard_normal((3, 40, E)).astype(np.float32)
+    dy = rng.standard_normal((3, 40, E)).astype(np.float32)
+    tx = T.from_numpy(x, requires_grad=True)
+    q, k, v = tx.linear_qkv(attn.Wq, attn.Wk, attn.Wv, attn.bq, attn.bk, attn.bv)
+    q.mul(T.from_numpy(dy)).sum().backward()
+    r = O.linear_forward_backward(x.reshape(-1, E), attn.Wq.numpy(), attn.bq.numpy(), dy.reshape(-1, E))
+    assert O.rel_frobenius(tx.grad.numpy().reshape(-1, E), r["dx"]) <= 1e-3
+    assert O.rel_frobenius(attn.Wq.grad.numpy(), r["dw"]) <= 1e-3
+    assert np.all(attn.Wk.grad.numpy() == 0.0) and np.all(attn.bv.grad.numpy() == 0.0)
+
+
+def test_load_state_dict_keeps_qkv_packed(T):
+    from gradtuity_b200.nn import CausalSelfAttention
+
+    rng = np.random.default_rng(33)
+    E = 32
+    attn = CausalSelfAttention(E, 2)
+    state = {k: T.from_numpy(rng.standard_normal(v.shape).astype(np.float32), requires_grad=True) for k, v in attn.state_dict().items()}
+    host = {k: v.numpy() for k, v in state.items()}
+    attn.load_state_dict(state)
+    assert attn.Wk.ptr - attn.Wq.ptr == E * E * 4 and attn.Wv.ptr - attn.Wk.ptr == E * E * 4
+    assert attn.bk.ptr - attn.bq.ptr == E * 4
+    for k, v in attn.state_dict().items():
+        assert np.array_equal(v.numpy(), host[k]) and v.requires_grad
 
 
 def test_config0_linear_784_128(T):
