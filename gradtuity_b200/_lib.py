@@ -21,7 +21,7 @@ DEFAULT_LIBRARY = os.path.join(_HERE, "libgt_b200.so")
 
 # enums of include/gt_b200.h
 LAYOUT_NN, LAYOUT_NT, LAYOUT_TN = 0, 1, 2
-EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_CAUSAL = 0, 1, 2, 3, 4
+EPI_NONE, EPI_BIAS, EPI_BIAS_RELU, EPI_BIAS_GELU, EPI_CAUSAL, EPI_BIAS_ADD, EPI_GELU_GRAD = 0, 1, 2, 3, 4, 5, 6
 PREC_TF32, PREC_TF32X3, PREC_FP32 = 0, 1, 2
 CAUSAL_MASK_VALUE = -1.0e9
 GEMM_A_LOWER, GEMM_AT_LOWER, GEMM_CAUSAL_SKIP_MASKED, GEMM_BIAS_PER_BATCH = 1, 2, 4, 8

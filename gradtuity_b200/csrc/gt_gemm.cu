@@ -11,12 +11,13 @@
 
 int gt_gemm_validate(gt_ctx* ctx, const gt_gemm_args& g) {
   if (g.layout < GT_LAYOUT_NN || g.layout > GT_LAYOUT_TN) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: layout %d is not NN/NT/TN", g.layout);
-  if (g.epilogue < GT_EPI_NONE || g.epilogue > GT_EPI_CAUSAL) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: unknown epilogue %d", g.epilogue);
+  if (g.epilogue < GT_EPI_NONE || g.epilogue > GT_EPI_GELU_GRAD) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: unknown epilogue %d", g.epilogue);
   if (g.precision < GT_PREC_TF32 || g.precision > GT_PREC_FP32) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: unknown precision %d", g.precision);
   if (g.M <= 0 || g.N <= 0 || g.K <= 0) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: M, N, K must be positive, got %lld %lld %lld", (long long)g.M, (long long)g.N, (long long)g.K);
   if (g.batch0 <= 0 || g.batch1 <= 0) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: batch counts must be positive");
   if (!g.A || !g.B || !g.C) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: null operand pointer");
-  const bool needs_bias = g.epilogue >= GT_EPI_BIAS && g.epilogue <= GT_EPI_BIAS_GELU;
+  const bool needs_bias = (g.epilogue >= GT_EPI_BIAS && g.epilogue <= GT_EPI_BIAS_GELU) || g.epilogue == GT_EPI_BIAS_ADD;
+  if ((g.epilogue == GT_EPI_BIAS_ADD || g.epilogue == GT_EPI_GELU_GRAD) && !g.aux) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: this epilogue reads aux, which is null");
   if (needs_bias && !g.bias) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: bias epilogue without a bias pointer");
   if (!needs_bias && g.bias) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: bias pointer given but the epilogue does not use it");
   if (g.accumulate != 0 && g.accumulate != 1) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm: accumulate must be 0 or 1");
@@ -37,6 +38,8 @@ int run(gt_ctx* ctx, const gt_gemm_args& g, void* stream) {
   if (rc != GT_OK) return rc;
   cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
   if (gt_gemm_umma_eligible(g)) return gt_gemm_umma_launch(ctx, g, s);
+  if (g.epilogue == GT_EPI_BIAS_ADD || g.epilogue == GT_EPI_GELU_GRAD)
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm: the aux-reading epilogues need the tensor-core path (tf32 / 3xtf32, aligned B)");
   return gt_gemm_fma_launch(ctx, g, s);
 }
 

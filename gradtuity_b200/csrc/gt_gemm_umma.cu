@@ -199,7 +199,8 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
                                                        int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                        uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
   const int row = row0 + lane;
-  const bool has_bias = epi >= GT_EPI_BIAS && epi <= GT_EPI_BIAS_GELU;
+  const bool has_bias = (epi >= GT_EPI_BIAS && epi <= GT_EPI_BIAS_GELU) || epi == GT_EPI_BIAS_ADD;
+  const bool aux_in = epi == GT_EPI_BIAS_ADD || epi == GT_EPI_GELU_GRAD;       // aux is read, not written
   if (lane == 0) tma_store_wait_read<0>();          // the previous store of this warp has finished reading the tile
   __syncwarp();
 #pragma unroll
@@ -216,7 +217,15 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
         if (col + 2 < p.N) x.z += bias[col + 2];
       }
     }
-    if (p.aux && row_ok && nb + j + 3 < p.N) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
+    if (aux_in) {
+      float a4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (row_ok) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) if (nb + j + t < p.N) a4[t] = p.aux[row_off + nb + j + t];
+      }
+      if (epi == GT_EPI_BIAS_ADD) { x.x += a4[0]; x.y += a4[1]; x.z += a4[2]; x.w += a4[3]; }
+      else { x.x *= gt_gelu_tanh_grad(a4[0]); x.y *= gt_gelu_tanh_grad(a4[1]); x.z *= gt_gelu_tanh_grad(a4[2]); x.w *= gt_gelu_tanh_grad(a4[3]); }
+    } else if (p.aux && row_ok && nb + j + 3 < p.N) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
     else if (p.aux && row_ok) {
       float* a = p.aux + row_off + nb + j;
       if (nb + j < p.N) a[0] = x.x;
@@ -249,7 +258,8 @@ template <int EPI, bool AUX>
 __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                         int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                         uint8_t* tile, uint32_t tile_u32, bool add) {
-  constexpr bool HAS_BIAS = EPI >= GT_EPI_BIAS && EPI <= GT_EPI_BIAS_GELU;
+  constexpr bool HAS_BIAS = (EPI >= GT_EPI_BIAS && EPI <= GT_EPI_BIAS_GELU) || EPI == GT_EPI_BIAS_ADD;
+  constexpr bool AUX_IN = EPI == GT_EPI_BIAS_ADD || EPI == GT_EPI_GELU_GRAD;     // aux is read, not written
   const int row = row0 + lane;
   const float alpha = p.alpha;
   const float4* bias4 = reinterpret_cast<const float4*>(bias + nb);
@@ -265,7 +275,11 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
       const float4 b = bias4[j];
       x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
     }
-    if (AUX) { if (row_ok) aux4[j] = x; }
+    if (AUX_IN) {
+      const float4 a = row_ok ? aux4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (EPI == GT_EPI_BIAS_ADD) { x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
+      else { x.x *= gt_gelu_tanh_grad(a.x); x.y *= gt_gelu_tanh_grad(a.y); x.z *= gt_gelu_tanh_grad(a.z); x.w *= gt_gelu_tanh_grad(a.w); }
+    } else if (AUX) { if (row_ok) aux4[j] = x; }
     if (EPI == GT_EPI_BIAS_RELU) {
       x.x = fmaxf(x.x, 0.0f); x.y = fmaxf(x.y, 0.0f); x.z = fmaxf(x.z, 0.0f); x.w = fmaxf(x.w, 0.0f);
     } else if (EPI == GT_EPI_BIAS_GELU) {
@@ -302,6 +316,8 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const fl
       case GT_EPI_BIAS_GELU:
         if (p.aux) GT_EPI_FAST(GT_EPI_BIAS_GELU, true); else GT_EPI_FAST(GT_EPI_BIAS_GELU, false);
         return;
+      case GT_EPI_BIAS_ADD: GT_EPI_FAST(GT_EPI_BIAS_ADD, false); return;
+      case GT_EPI_GELU_GRAD: GT_EPI_FAST(GT_EPI_GELU_GRAD, false); return;
       case GT_EPI_CAUSAL:
         if (!p.aux) {
           // a 32 x 32 block whose last column is not right of its first row holds no masked element
@@ -1035,7 +1051,7 @@ int pick_bn(const gt_gemm_args& g, int sms, bool x3, bool a_gen) {
   const long long batches = g.batch0 * g.batch1;
   const long long tm = (g.M + BM - 1) / BM;
   // Few output tiles and a long K: take the widest tile, split-K fills the remaining SMs.
-  if (!x3 && g.epilogue != GT_EPI_CAUSAL && g.K >= 32 * BK && tm * ((g.N + 255) / 256) * batches * 2 <= sms) return 256;
+  if (!x3 && g.epilogue < GT_EPI_CAUSAL && g.K >= 32 * BK && tm * ((g.N + 255) / 256) * batches * 2 <= sms) return 256;
   // Cost in "column units per SM": waves x tile width x a per-width efficiency penalty.
   double best = 1e30; int best_bn = 256;
   const int cands[3] = {256, 128, 64};
@@ -1176,7 +1192,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   //    cannot be described to TMA.
   const int num_kb = (int)((g.K + BK - 1) / BK);
   int ksplit = 1;
-  if (!x3 && g.epilogue != GT_EPI_CAUSAL && hints == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
+  if (!x3 && g.epilogue < GT_EPI_CAUSAL && hints == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
     ksplit = (int)(ctx->sm_count / tiles);
     if (ksplit > num_kb / 8) ksplit = num_kb / 8;
     if (ksplit > 32) ksplit = 32;
@@ -1229,7 +1245,10 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   }
   // C through TMA (store, or reduce-add for C += ...) when its rows can be described; split-K partials
   // and unaligned outputs keep the direct / coalesced stores.
-  p.c_tma = (!c_tma_off && (ksplit == 1 || splitk_direct) && tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1)) ? 1 : 0;
+  p.c_tma = (!c_tma_off && (ksplit == 1 || splitk_direct) && tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) &&
+             (!g.aux || ((uintptr_t)g.aux & 15) == 0) && (!g.bias || ((uintptr_t)g.bias & 15) == 0)) ? 1 : 0;   // the TMA epilogue uses float4 on aux and bias
+  if (!p.c_tma && (g.epilogue == GT_EPI_BIAS_ADD || g.epilogue == GT_EPI_GELU_GRAD))
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm: the aux-reading epilogues need a C that TMA can describe (16-byte aligned, ldc a multiple of 4)");
   if (p.c_tma) {
     OperandView vc = {g.C, g.M, g.N, g.ldc, g.sC0, g.sC1};
     if ((rc = encode_map(ctx, &maps[4], vc, 32, 32, b0, b1, false, /*plain_f32=*/true)) != GT_OK) return rc;

@@ -64,6 +64,14 @@ int gt_gemm_fma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 bool gt_gemm_umma_eligible(const gt_gemm_args& g);
 
+// d/dx of the tanh-form GELU (gradtuity/kernels_cuda/elemwise_kernels.py:127-137).
+__device__ __forceinline__ float gt_gelu_tanh_grad(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
+  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
+
 // GELU, tanh form: gradtuity/kernels_cuda/elemwise_kernels.py:104-125.
 __device__ __forceinline__ float gt_gelu_tanh(float x) {
   // tanh(u) = 1 - 2 / (1 + exp(2u)): the same function as the reference's two-branch form, written

@@ -268,7 +268,9 @@ class CausalSelfAttention(Module):
         self.resid_dropout = Dropout(p=resid_pdrop) if resid_pdrop > 0 else None
         self._pack_qkv()
 
-    def __call__(self, x: Tensor) -> Tensor:
+    def __call__(self, x: Tensor, residual: Tensor | None = None) -> Tensor:
+        """attention(x); with `residual` (same shape as x) the result is residual + attention(x), the add done in
+        the output projection's epilogue (the reference's block adds afterwards, gpt2/model.py:64-66)."""
         B, S, E = x.shape
         if E != self.embed_dim:
             raise ValueError(f"input last dim {E} must equal embed_dim {self.embed_dim}")
@@ -276,10 +278,13 @@ class CausalSelfAttention(Module):
             raise NotImplementedError("attention dropout with p > 0 is not part of the GEMM path")
         q, k, v = x.linear_qkv(self.Wq, self.Wk, self.Wv, self.bq, self.bk, self.bv)     # one batched launch when packed
         ctx = q.causal_attention(k, v, self.num_heads)
+        if residual is not None and self.resid_dropout is None:
+            return ctx.view((B * S, E)).linear_add(self.Wo, self.bo, residual)
         out = ctx.view((B * S, E)).linear(self.Wo, self.bo)
         if self.resid_dropout is not None:
             out = self.resid_dropout(out)
-        return out.view((B, S, E))
+        out = out.view((B, S, E))
+        return out if residual is None else residual.add(out)
 
     def parameters(self) -> list[Tensor]:
         return [self.Wq, self.Wk, self.Wv, self.Wo, self.bq, self.bk, self.bv, self.bo]

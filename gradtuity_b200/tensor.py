@@ -572,7 +572,8 @@ class Tensor:
         sw = wk.ptr - wq.ptr
         batched = (x.ndim >= 2 and sw > 0 and wv.ptr - wk.ptr == sw and sw % 16 == 0 and bk.ptr - bq.ptr == N * F32
                    and bv.ptr - bk.ptr == N * F32 and N % 4 == 0 and K % 4 == 0 and wq.ptr % 16 == 0 and x.ptr % 16 == 0
-                   and bq.ptr % 16 == 0 and _gemm.default_precision() != _lib.PREC_FP32)
+                   and bq.ptr % 16 == 0 and _gemm.default_precision() != _lib.PREC_FP32
+                   and "GRADTUITY_GEMM_DETERMINISTIC" not in os.environ)      # the shared-dX launch adds in no fixed order
         if not batched:
             x2 = x.view((M, K))
             return tuple(x2.linear(w, b).view(out_shape) for w, b in ((wq, bq), (wk, bk), (wv, bv)))
@@ -635,6 +636,93 @@ class Tensor:
             o._grad_slot = (group, i)
             o._set_graph(parents=(hub,), backward_fn=_child_backward)
         return tuple(outs)
+
+    @staticmethod
+    def _aux_epilogue_ok(ptrs, dims) -> bool:
+        """The aux-reading GEMM epilogues need the tensor-core path: tf32 / 3xtf32, 16-byte aligned buffers,
+        leading dimensions that are multiples of 4."""
+        if _gemm.default_precision() == _lib.PREC_FP32:
+            return False
+        return all(p % 16 == 0 for p in ptrs) and all(d % 4 == 0 for d in dims)
+
+    def linear_add(self, weight: "Tensor", bias: "Tensor", residual: "Tensor") -> "Tensor":
+        """residual + X @ W + b.  A Linear layer and the residual add that follows it in a transformer block
+        (gpt2/model.py:64-71: `x = x + attn(...)`, `x = x + mlp(...)`) as one GEMM whose epilogue reads the
+        residual; otherwise `residual.add(x.linear(w, b))`.  `residual` may have any shape with M * N elements;
+        the result has its shape."""
+        self._linear_checks(weight, bias, "linear_add")
+        M, K = self._shape
+        _, N = weight._shape
+        if residual.numel != M * N:
+            raise ValueError(f"linear_add: residual shape {residual._shape} does not hold {M} x {N} elements")
+        if not self._aux_epilogue_ok((self.ptr, weight.ptr, bias.ptr, residual.ptr), (K, N)):
+            return residual.add(self.linear(weight, bias).view(residual._shape))
+        from ._lib import EPI_BIAS_ADD
+        out = empty_tensor(residual._shape)
+        _gemm.gemm(LAYOUT_NN, M, N, K, self.ptr, K, weight.ptr, N, out.ptr, N, bias_ptr=bias.ptr, aux_ptr=residual.ptr,
+                   epilogue=EPI_BIAS_ADD)
+        x = self
+
+        def _backward(g: "Tensor") -> None:
+            self._linear_backward(x, weight, bias, g.ptr, M, K, N)
+            if residual.requires_grad:
+                pass_grad(residual, g)
+
+        out._set_graph(parents=(self, weight, bias, residual), backward_fn=_backward)
+        return out
+
+    def mlp_gelu(self, w1: "Tensor", b1: "Tensor", w2: "Tensor", b2: "Tensor", residual: "Tensor | None" = None) -> "Tensor":
+        """(residual +) gelu(X @ W1 + b1) @ W2 + b2: the MLP of a GPT-2 block (gpt2/model.py:68-71).  Forward: the
+        first GEMM stores the pre-activation beside the activation, the second adds the residual in its epilogue.
+        Backward: the dX GEMM of the second layer multiplies by gelu'(pre-activation) in its epilogue, so the
+        separate GELU-backward pass over the (M, inner) tensor and its temporary disappear."""
+        self._linear_checks(w1, b1, "mlp_gelu")
+        M, K = self._shape
+        _, I = w1._shape
+        if w2.ndim != 2 or b2.ndim != 1 or w2._shape[0] != I or b2._shape[0] != w2._shape[1]:
+            raise ValueError(f"mlp_gelu shape mismatch: hidden {I}, second weight {w2._shape}, second bias {b2._shape}")
+        N = w2._shape[1]
+        if residual is not None and residual.numel != M * N:
+            raise ValueError(f"mlp_gelu: residual shape {residual._shape} does not hold {M} x {N} elements")
+        ptrs = [self.ptr, w1.ptr, b1.ptr, w2.ptr, b2.ptr] + ([residual.ptr] if residual is not None else [])
+        if not self._aux_epilogue_ok(ptrs, (K, I, N)):
+            y = self.linear_gelu(w1, b1).linear(w2, b2)
+            return y if residual is None else residual.add(y.view(residual._shape))
+        from ._lib import EPI_BIAS_ADD, EPI_GELU_GRAD
+        h = alloc_storage(M * I * F32)
+        pre = alloc_storage(M * I * F32)
+        _gemm.gemm(LAYOUT_NN, M, I, K, self.ptr, K, w1.ptr, I, h.ptr, I, bias_ptr=b1.ptr, aux_ptr=pre.ptr, epilogue=EPI_BIAS_GELU)
+        out = empty_tensor(residual._shape if residual is not None else (M, N))
+        if residual is not None:
+            _gemm.gemm(LAYOUT_NN, M, N, I, h.ptr, I, w2.ptr, N, out.ptr, N, bias_ptr=b2.ptr, aux_ptr=residual.ptr, epilogue=EPI_BIAS_ADD)
+        else:
+            _gemm.gemm(LAYOUT_NN, M, N, I, h.ptr, I, w2.ptr, N, out.ptr, N, bias_ptr=b2.ptr, epilogue=EPI_BIAS)
+        x = self
+        if not (x.requires_grad or w1.requires_grad or b1.requires_grad or w2.requires_grad or b2.requires_grad
+                or (residual is not None and residual.requires_grad)):
+            h.free(); pre.free()
+
+        def _backward(g: "Tensor") -> None:
+            if w2.requires_grad:
+                ptr, acc = grad_target(w2)
+                _gemm.gemm(LAYOUT_TN, I, N, M, h.ptr, I, g.ptr, N, ptr, N, accumulate=acc)
+            if b2.requires_grad:
+                ensure_grad(b2)
+                _call("gt_colsum_acc", _vp(b2.grad.ptr), _vp(g.ptr), M, N, N)
+            h.free()
+            if x.requires_grad or w1.requires_grad or b1.requires_grad:
+                with temp_storage(M * I * F32) as dpre:
+                    # d(pre-activation) = (dY @ W2^T) * gelu'(pre), the product in the GEMM's epilogue
+                    _gemm.gemm(LAYOUT_NT, M, I, N, g.ptr, N, w2.ptr, N, dpre.ptr, I, aux_ptr=pre.ptr, epilogue=EPI_GELU_GRAD)
+                    pre.free()
+                    self._linear_backward(x, w1, b1, dpre.ptr, M, K, I)
+            else:
+                pre.free()
+            if residual is not None and residual.requires_grad:
+                pass_grad(residual, g)
+
+        out._set_graph(parents=(self, w1, b1, w2, b2) + ((residual,) if residual is not None else ()), backward_fn=_backward)
+        return out
 
     def linear_relu(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
         """Y = relu(X @ W + b), one kernel; backward masks dY by [Y > 0] into a temporary and

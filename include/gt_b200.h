@@ -61,12 +61,21 @@ typedef struct gt_ctx gt_ctx;
  *   BIAS_GELU   matmul_bias + gelu_kernel, tanh form (kernels_cuda/elemwise_kernels.py:104-125)
  *   CAUSAL      per batch slice, entries with n > m are written as GT_CAUSAL_MASK_VALUE
  *               (the NEG_INF of reference causal_mask_inplace, gradtuity/tensor.py:1316);
- *               tiles wholly above the diagonal skip the contraction.                      */
+ *               tiles wholly above the diagonal skip the contraction.
+ * Two kinds READ aux (same shape and leading dimension as C) instead of writing it:
+ *   BIAS_ADD    C = alpha * acc + bias[n] + aux[m, n]: a Linear layer and the residual add that follows
+ *               it in one launch (gpt2/model.py:64-71 adds the branch output to the stream afterwards)
+ *   GELU_GRAD   C = alpha * acc * gelu'(aux[m, n]), aux = the stored pre-activation: dX of the second
+ *               MLP layer and the GELU backward that follows it (gelu_backward_kernel,
+ *               kernels_cuda/elemwise_kernels.py:127-137) in one launch; no bias.
+ * Both need the tensor-core path with a 16-byte aligned C and aux (else GT_ERR_UNSUPPORTED).     */
 #define GT_EPI_NONE       0
 #define GT_EPI_BIAS       1
 #define GT_EPI_BIAS_RELU  2
 #define GT_EPI_BIAS_GELU  3
 #define GT_EPI_CAUSAL     4
+#define GT_EPI_BIAS_ADD   5
+#define GT_EPI_GELU_GRAD  6
 #define GT_CAUSAL_MASK_VALUE (-1.0e9f)
 
 /* Multiply precision (accumulation is always fp32).

@@ -29,6 +29,9 @@ def grads_of(model, ids, labels):
 
 def main():
     mode = sys.argv[1]
+    # The sync_grads check recomputes each gradient a second time and compares at 1e-5: that needs sums in a
+    # fixed order (no reduce-add split-K, no last-wave split, no shared-C batch launch).
+    os.environ["GRADTUITY_GEMM_DETERMINISTIC"] = "1"
     from gradtuity_b200 import _lib, dist
     from gradtuity_b200.dist import comm, ddp
     from gradtuity_b200.gpt2.train import seeded_state, synthetic_batch

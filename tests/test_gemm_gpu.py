@@ -204,6 +204,44 @@ def test_last_wave_split_shapes(gt, layout, M, N, K, epilogue, acc):
         assert O.rel_frobenius((out - base)[sl], (ref - base)[sl]) <= U.TOL["tf32"]
 
 
+@pytest.mark.parametrize("layout,M,N,K", [("NN", 300, 200, 96), ("NT", 8192, 3072, 768), ("NN", 8192, 768, 3072), ("TN", 260, 132, 64)])
+@pytest.mark.parametrize("kind", ["bias_add", "gelu_grad"])
+def test_aux_reading_epilogues(gt, layout, M, N, K, kind):
+    """BIAS_ADD: C = A B + bias + aux (Linear + residual add); GELU_GRAD: C = (A B) * gelu'(aux) (dX of the second
+    MLP layer with the GELU backward).  Shapes with partial chunks (general form) and the two GPT-2 MLP shapes
+    (128 x 256 tiles and the 256 x 256-tile kernel)."""
+    from gradtuity_b200 import _lib, gemm as G
+
+    a, b, rng = U.make_operands(layout, M, N, K, seed=M + N)
+    aux = rng.standard_normal((M, N)).astype(np.float32)
+    bias = rng.standard_normal(N).astype(np.float32) if kind == "bias_add" else None
+    da, db, dx = U.DeviceBuffer(a), U.DeviceBuffer(b), U.DeviceBuffer(aux)
+    dc = U.DeviceBuffer(np.full((M, N), np.nan, np.float32))
+    dbias = U.DeviceBuffer(bias) if bias is not None else None
+    epi = _lib.EPI_BIAS_ADD if kind == "bias_add" else _lib.EPI_GELU_GRAD
+    G.gemm(U.LAYOUTS[layout], M, N, K, da.ptr, a.shape[1], db.ptr, b.shape[1], dc.ptr, N,
+           bias_ptr=dbias.ptr if dbias else 0, aux_ptr=dx.ptr, epilogue=epi)
+    _lib.device_status()
+    out = dc.read((M, N))
+    prod = O.gemm(a, b, layout)
+    ref = prod + bias + aux if kind == "bias_add" else prod * O.gelu_tanh_grad(aux.astype(np.float64))
+    assert O.rel_frobenius(out, ref) <= U.TOL["tf32"]
+    assert np.array_equal(dx.read((M, N)), aux)                     # aux is read, never written
+
+
+def test_aux_reading_epilogue_needs_aux_and_tensor_core_path(gt):
+    from gradtuity_b200 import _lib, gemm as G
+
+    a, b, _ = U.make_operands("NN", 64, 64, 64, seed=1)
+    da, db = U.DeviceBuffer(a), U.DeviceBuffer(b)
+    dc = U.DeviceBuffer(np.zeros((64, 64), np.float32))
+    with pytest.raises(RuntimeError, match="reads aux"):
+        G.gemm(0, 64, 64, 64, da.ptr, 64, db.ptr, 64, dc.ptr, 64, epilogue=_lib.EPI_GELU_GRAD)
+    with pytest.raises(RuntimeError, match="tensor-core path"):
+        G.gemm(0, 64, 64, 64, da.ptr, 64, db.ptr, 64, dc.ptr, 64, aux_ptr=dc.ptr, epilogue=_lib.EPI_GELU_GRAD,
+               precision=U.PRECISIONS["fp32"])
+
+
 def test_bitwise_deterministic(gt):
     # one CTA per output tile (no shared K range): the summation order is fixed
     a, b, _ = U.make_operands("TN", 1536, 2048, 512, seed=3)

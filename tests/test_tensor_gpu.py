@@ -388,6 +388,46 @@ def test_load_state_dict_keeps_qkv_packed(T):
         assert np.array_equal(v.numpy(), host[k]) and v.requires_grad
 
 
+@pytest.mark.parametrize("M,K,I,N", [(256, 64, 192, 64), (100, 20, 36, 12)])
+def test_mlp_gelu_and_linear_add_against_the_oracle(T, M, K, I, N):
+    """x + fc2(gelu(fc1(h))) with the residual add and the GELU backward inside GEMM epilogues, and
+    residual + linear(x), against float64 (second shape: 3xTF32-free general form with partial chunks)."""
+    rng = np.random.default_rng(M + I)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w1 = (rng.standard_normal((K, I)) / np.sqrt(K)).astype(np.float32); b1 = rng.standard_normal(I).astype(np.float32)
+    w2 = (rng.standard_normal((I, N)) / np.sqrt(I)).astype(np.float32); b2 = rng.standard_normal(N).astype(np.float32)
+    res = rng.standard_normal((2, M // 2, N)).astype(np.float32)
+    dy = rng.standard_normal((2, M // 2, N)).astype(np.float32)
+    tx, tw1, tb1, tw2, tb2, tr = (T.from_numpy(a, requires_grad=True) for a in (x, w1, b1, w2, b2, res))
+    y = tx.mlp_gelu(tw1, tb1, tw2, tb2, residual=tr)
+    assert y.shape == res.shape
+    y.mul(T.from_numpy(dy)).sum().backward()
+    x64, dy64 = x.astype(np.float64), dy.reshape(M, N).astype(np.float64)
+    pre = x64 @ w1 + b1
+    h = O.gelu_tanh(pre)
+    ref_y = h @ w2 + b2 + res.reshape(M, N)
+    dh = dy64 @ w2.T.astype(np.float64)
+    dpre = dh * O.gelu_tanh_grad(pre)
+    assert O.rel_frobenius(y.numpy().reshape(M, N), ref_y) <= 1e-3
+    assert O.rel_frobenius(tw2.grad.numpy(), h.T @ dy64) <= 1e-3
+    assert O.rel_frobenius(tb2.grad.numpy(), dy64.sum(0)) <= 1e-3
+    assert O.rel_frobenius(tw1.grad.numpy(), x64.T @ dpre) <= 2e-3
+    assert O.rel_frobenius(tb1.grad.numpy(), dpre.sum(0)) <= 2e-3
+    assert O.rel_frobenius(tx.grad.numpy(), dpre @ w1.T.astype(np.float64)) <= 2e-3
+    assert O.rel_frobenius(tr.grad.numpy().reshape(M, N), dy64) <= 1e-6
+    # linear_add
+    tx2, tw, tb, tr2 = (T.from_numpy(a, requires_grad=True) for a in (x, w1, b1, rng.standard_normal((M, I)).astype(np.float32)))
+    r_host = tr2.numpy()
+    z = tx2.linear_add(tw, tb, tr2)
+    dz = rng.standard_normal((M, I)).astype(np.float32)
+    z.mul(T.from_numpy(dz)).sum().backward()
+    ref = O.linear_forward_backward(x, w1, b1, dz)
+    assert O.rel_frobenius(z.numpy(), ref["y"] + r_host) <= 1e-3
+    assert O.rel_frobenius(tx2.grad.numpy(), ref["dx"]) <= 1e-3
+    assert O.rel_frobenius(tw.grad.numpy(), ref["dw"]) <= 1e-3
+    assert O.rel_frobenius(tr2.grad.numpy(), dz) <= 1e-6
+
+
 def test_config0_linear_784_128(T):
     """Config 0: Linear(784 -> 128), batch 128, X ~ U[0,1), W and b ~ U(-1/28, 1/28), dY ~ N(0,1),
     seed 0; y, dX, dW, db against the float64 oracle."""
