@@ -1,21 +1,31 @@
 // TF32 / 3xTF32 GEMM for sm_100a: TMA-fed shared-memory tiles, tcgen05.mma accumulating in
 // tensor memory, fused epilogue.
 //
-// One persistent CTA per SM walks a list of 128 x BN output tiles.  Inside a CTA:
+// One persistent CTA (320 threads) per SM walks a list of 128 x BN output tiles (BN = 64, 128, 256;
+// gt_gemm_umma256_kernel holds 256 x 256 tiles for large problems).  Inside a CTA:
 //   warp 0     producer   one lane issues cp.async.bulk.tensor (TMA) loads of A and B k-blocks
 //                         (32 fp32 = one 128-byte swizzle row per k-block) into a ring of stages
 //   warp 1     MMA        one lane issues tcgen05.mma.kind::tf32 (K = 8 per instruction) into
 //                         one of two tensor-memory accumulators; tcgen05.commit hands stages
 //                         back to the producer and finished accumulators to the epilogue
-//   warps 2-5  epilogue   tcgen05.ld the accumulator (lane = row), apply alpha / bias /
-//                         ReLU / GELU / causal mask / accumulate, store to global
-// so the epilogue of tile i overlaps the main loop of tile i+1.
+//   warps 2-9  epilogue   two warps per tensor-memory lane quarter share a tile's 32-column chunks:
+//                         tcgen05.ld the accumulator (lane = row), apply alpha / bias / ReLU / GELU /
+//                         causal mask / residual add / gelu', write the 32 x 32 block into a swizzled
+//                         staging tile and hand it to TMA (store, or reduce-add for C += ...)
+// so the epilogue of tile i overlaps the main loop of tile i+1.  With an A that TMA cannot describe,
+// warps 6-9 copy it with cp.async instead and warps 2-5 are the epilogue.
+//
+// Work units: normally one tile each.  Few tiles and a long K: every tile is cut into K shares
+// (split-K).  A last wave that is at most half full: only its tiles are cut.  Shares add into C with
+// the TMA reduce-add (or, on request, go through a workspace and an ordered second kernel).
 //
 // NN / NT / TN are read straight from the row-major buffers: an operand whose contraction
 // index is contiguous in memory is "K-major" (one TMA box of 32 x rows), the other kind is
-// "MN-major" (rows/32 boxes of 32 x 32, 4 KB each, in the 32-byte-chunk swizzle that fp32
-// MN-major operands require); the instruction descriptor's major bits tell the tensor core
-// which is which.  No transpose is materialised.
+// "MN-major" (32-wide chunks of 4 KB in the 32-byte-chunk swizzle that fp32 MN-major operands
+// require, loaded as one five-dimensional box when the extent allows, else chunk by chunk); the
+// instruction descriptor's major bits tell the tensor core which is which.  No transpose is
+// materialised.  Batch strides may be 0 (operand shared by the batch entries, or a C that receives
+// their sum).
 //
 // 3xTF32: the operands are split beforehand into hi = x & 0xffffe000 and lo = x - hi (both
 // exact); each k-step issues lo*hi, hi*lo, hi*hi into the same accumulator.

@@ -239,10 +239,13 @@ class TiedLMHead(Module):
 class CausalSelfAttention(Module):
     """Multi-head causal self-attention, (B, S, E) -> (B, S, E) (gradtuity/nn.py:462-569).
 
-    Same parameters (Wq, Wk, Wv, Wo as (E, E); bq, bk, bv, bo) and the same mathematics.  The
-    part between the projections runs as `Tensor.causal_attention`: three strided-batched GEMM
-    launches and one softmax launch forward, instead of three materialised transposes, 96
-    per-slice transposes, two Python loops of 96 GEMM launches, a scale kernel and a softmax."""
+    Same parameters (Wq, Wk, Wv, Wo as (E, E); bq, bk, bv, bo) and the same mathematics.  The three
+    input projections are one batched launch (`Tensor.linear_qkv`; the three weights, and the three
+    biases, live side by side in memory).  The part between the projections runs as
+    `Tensor.causal_attention`: fused forward and backward kernels for head dimension 64, else three
+    strided-batched GEMM launches and one softmax launch, instead of the reference's three materialised
+    transposes, 96 per-slice transposes, two Python loops of 96 GEMM launches, a scale kernel and a
+    softmax."""
 
     def __init__(self, embed_dim: int, num_heads: int, attn_pdrop: float = 0.0, resid_pdrop: float = 0.0) -> None:
         if embed_dim <= 0 or num_heads <= 0:

@@ -817,12 +817,14 @@ class Tensor:
 
         Computes exactly what the reference's CausalSelfAttention computes between its
         projections (gradtuity/nn.py:534-549): S = Q Kᵀ / sqrt(d) per head, P = causal softmax,
-        O = P V, heads merged back to (B, S, E).  Here the three batched products and their four
-        backward products are single strided-batched GEMM launches that address the per-head
-        slices of the (B, S, H, d) buffers in place, so none of transpose4d_12 /
-        transpose4d_last2 / scale_inplace runs and no (B, H, S, d) copy exists; the 1/sqrt(d)
-        scale and the causal mask sit in the score GEMM's epilogue (tiles wholly above the diagonal
-        are not computed).  P (B, H, S, S) is kept for the backward, as in the reference.
+        O = P V, heads merged back to (B, S, E).  The per-head slices of the (B, S, H, d) buffers are
+        addressed in place, so none of transpose4d_12 / transpose4d_last2 / scale_inplace runs and no
+        (B, H, S, d) copy exists.  Two forms (see GRADTUITY_ATTENTION below): fused forward and backward
+        kernels that keep only each row's log-sum-exp (head dimension 64, S a multiple of 128, tf32),
+        or, for every other shape, the three batched products and their four backward products as single
+        strided-batched GEMM launches, with the 1/sqrt(d) scale and the causal mask in the score GEMM's
+        epilogue (tiles wholly above the diagonal are not computed) and P (B, H, S, S) kept for the
+        backward, as in the reference.
         """
         q = self
         if q.ndim != 3 or k.shape != q.shape or v.shape != q.shape:
