@@ -84,6 +84,8 @@ SIGNATURES = {
                              c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                              c_int, POINTER(c_int)]),
     "gt_selftest_bounded_wait": (c_int, [c_void_p, c_int64]),
+    "gt_gemm_host": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                             c_void_p, c_float, c_int, c_int, c_int]),
     "gt_attention_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_int64, c_int64, c_int64, c_int64, c_float, c_void_p]),
     "gt_attention_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

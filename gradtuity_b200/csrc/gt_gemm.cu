@@ -111,3 +111,89 @@ extern "C" int gt_gemm_path(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64
   *path = gt_gemm_umma_eligible(g) ? 0 : 1;
   return GT_OK;
 }
+
+// ---- GEMM on host buffers, copies overlapped with the product -----------------------------------
+// C (host) = epilogue(alpha * op(A) op(B) (+ bias)) for A, B, C in HOST memory (pinned memory for the
+// copies to overlap).  B goes to the device once; A is cut into row blocks of C, and the upload of
+// block i + 1, the product of block i and the download of block i - 1 run at the same time on three
+// streams (PCIe is full duplex), with two device buffers each for the A and C blocks.  The call
+// returns when C is complete in host memory.  This is the form in which a caller with host data, such
+// as the reference's `Tensor(list).matmul(...).to_list()` (gradtuity/tensor.py:192-220, 530-657), pays
+// the least for the PCIe link: max(upload, download) instead of their sum.
+extern "C" int gt_gemm_host(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                            const float* hA, int64_t lda, const float* hB, int64_t ldb, float* hC, int64_t ldc,
+                            const float* h_bias, float alpha, int epilogue, int precision, int chunks) {
+  if (!ctx || !hA || !hB || !hC || M <= 0 || N <= 0 || K <= 0 || chunks <= 0) return GT_ERR_INVALID_ARG;
+  if (layout < GT_LAYOUT_NN || layout > GT_LAYOUT_TN) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_host: layout %d is not NN/NT/TN", layout);
+  if (epilogue < GT_EPI_NONE || epilogue > GT_EPI_BIAS_GELU) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_host: epilogue %d is not none / bias / bias+ReLU / bias+GELU", epilogue);
+  if ((epilogue != GT_EPI_NONE) != (h_bias != nullptr)) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_host: bias pointer and epilogue do not agree");
+  const int64_t a_rows = layout == GT_LAYOUT_TN ? K : M, a_cols = layout == GT_LAYOUT_TN ? M : K;
+  const int64_t b_rows = layout == GT_LAYOUT_NT ? N : K, b_cols = layout == GT_LAYOUT_NT ? K : N;
+  if (lda < a_cols || ldb < b_cols || ldc < N) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_host: a leading dimension is smaller than its row length");
+  (void)a_rows;
+  if (!ctx->h2d_stream) {
+    GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->h2d_stream, cudaStreamNonBlocking));
+    GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 8; ++i) GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->host_ev[i], cudaEventDisableTiming));
+  }
+  cudaStream_t cs = ctx->stream, up = ctx->h2d_stream, down = ctx->d2h_stream;
+  cudaEvent_t ev_alloc = ctx->host_ev[0], ev_b = ctx->host_ev[1];
+  cudaEvent_t ev_a[2] = {ctx->host_ev[2], ctx->host_ev[3]}, ev_g[2] = {ctx->host_ev[4], ctx->host_ev[5]},
+              ev_d[2] = {ctx->host_ev[6], ctx->host_ev[7]};
+  // row blocks of C: multiples of 128 rows (the kernels' tile height)
+  int64_t rows_per = (M + chunks - 1) / chunks;
+  rows_per = (rows_per + 127) / 128 * 128;
+  const int nblk = (int)((M + rows_per - 1) / rows_per);
+  // compact device copies; leading dimensions padded to a multiple of 4 floats so that TMA can describe them
+  const int64_t ldb_d = (b_cols + 3) / 4 * 4, ldc_d = (N + 3) / 4 * 4;
+  const int64_t lda_d = layout == GT_LAYOUT_TN ? rows_per : (K + 3) / 4 * 4;      // TN: a block is (K, rows_per)
+  const size_t a_blk = (size_t)(layout == GT_LAYOUT_TN ? K * lda_d : rows_per * lda_d), c_blk = (size_t)(rows_per * ldc_d);
+  float *dB = nullptr, *dA[2] = {nullptr, nullptr}, *dC[2] = {nullptr, nullptr}, *d_bias = nullptr;
+  GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dB, (size_t)(b_rows * ldb_d) * sizeof(float), cs));
+  for (int i = 0; i < 2; ++i) {
+    GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dA[i], a_blk * sizeof(float), cs));
+    GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dC[i], c_blk * sizeof(float), cs));
+  }
+  if (h_bias) GT_CUDA_OK(ctx, cudaMallocAsync((void**)&d_bias, (size_t)N * sizeof(float), cs));
+  GT_CUDA_OK(ctx, cudaEventRecord(ev_alloc, cs));
+  GT_CUDA_OK(ctx, cudaStreamWaitEvent(up, ev_alloc, 0));
+  GT_CUDA_OK(ctx, cudaStreamWaitEvent(down, ev_alloc, 0));
+  GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dB, (size_t)ldb_d * 4, hB, (size_t)ldb * 4, (size_t)b_cols * 4, (size_t)b_rows, cudaMemcpyHostToDevice, up));
+  if (h_bias) GT_CUDA_OK(ctx, cudaMemcpyAsync(d_bias, h_bias, (size_t)N * 4, cudaMemcpyHostToDevice, up));
+  GT_CUDA_OK(ctx, cudaEventRecord(ev_b, up));
+  int rc = GT_OK;
+  for (int i = 0; i < nblk && rc == GT_OK; ++i) {
+    const int buf = i & 1;
+    const int64_t m0 = (int64_t)i * rows_per, rows = (M - m0) < rows_per ? (M - m0) : rows_per;
+    if (i >= 2) GT_CUDA_OK(ctx, cudaStreamWaitEvent(up, ev_g[buf], 0));             // the product that read this A buffer is done
+    if (layout == GT_LAYOUT_TN)
+      GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dA[buf], (size_t)lda_d * 4, hA + m0, (size_t)lda * 4, (size_t)rows * 4, (size_t)K, cudaMemcpyHostToDevice, up));
+    else
+      GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dA[buf], (size_t)lda_d * 4, hA + m0 * lda, (size_t)lda * 4, (size_t)K * 4, (size_t)rows, cudaMemcpyHostToDevice, up));
+    GT_CUDA_OK(ctx, cudaEventRecord(ev_a[buf], up));
+    GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_a[buf], 0));
+    if (i == 0) GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_b, 0));
+    if (i >= 2) GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_d[buf], 0));             // this C buffer has been downloaded
+    gt_gemm_args g;
+    g.layout = layout; g.epilogue = epilogue; g.precision = precision; g.accumulate = 0; g.flags = 0;
+    g.M = rows; g.N = N; g.K = K;
+    g.A = dA[buf]; g.lda = lda_d; g.sA0 = 0; g.sA1 = 0;
+    g.B = dB; g.ldb = ldb_d; g.sB0 = 0; g.sB1 = 0;
+    g.C = dC[buf]; g.ldc = ldc_d; g.sC0 = 0; g.sC1 = 0;
+    g.batch0 = 1; g.batch1 = 1; g.bias = d_bias; g.aux = nullptr; g.alpha = alpha;
+    rc = run(ctx, g, cs);
+    if (rc != GT_OK) break;
+    GT_CUDA_OK(ctx, cudaEventRecord(ev_g[buf], cs));
+    GT_CUDA_OK(ctx, cudaStreamWaitEvent(down, ev_g[buf], 0));
+    GT_CUDA_OK(ctx, cudaMemcpy2DAsync(hC + m0 * ldc, (size_t)ldc * 4, dC[buf], (size_t)ldc_d * 4, (size_t)N * 4, (size_t)rows, cudaMemcpyDeviceToHost, down));
+    GT_CUDA_OK(ctx, cudaEventRecord(ev_d[buf], down));
+  }
+  // everything in flight must finish before the buffers go back to the pool and the caller reads C
+  cudaError_t e1 = cudaStreamSynchronize(up), e2 = cudaStreamSynchronize(cs), e3 = cudaStreamSynchronize(down);
+  cudaFreeAsync(dB, cs);
+  for (int i = 0; i < 2; ++i) { cudaFreeAsync(dA[i], cs); cudaFreeAsync(dC[i], cs); }
+  if (d_bias) cudaFreeAsync(d_bias, cs);
+  if (rc != GT_OK) return rc;
+  GT_CUDA_OK(ctx, e1); GT_CUDA_OK(ctx, e2); GT_CUDA_OK(ctx, e3);
+  return GT_OK;
+}

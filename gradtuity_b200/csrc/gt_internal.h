@@ -21,6 +21,8 @@ struct gt_ctx {
   int* d_status;              // device status word written by bounded waits that ran out; the allocation is 4 KB:
                               // ints 16..271 are the "C tile zeroed" flags of the GEMM's last-wave split
   int tail_epoch;             // value those flags take in the next launch that uses them
+  cudaStream_t h2d_stream, d2h_stream;   // copy streams of gt_gemm_host (created on first use)
+  cudaEvent_t host_ev[8];                // its events
   gt_encode_tiled_fn encode_tiled;
   void* workspace;            // scratch for operand splitting (TF32X3) and split-K partials
   size_t workspace_bytes;

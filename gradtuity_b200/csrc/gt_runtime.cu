@@ -79,6 +79,11 @@ extern "C" int gt_destroy(gt_ctx* ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->workspace) cudaFree(ctx->workspace);
+  if (ctx->h2d_stream) {
+    cudaStreamDestroy(ctx->h2d_stream);
+    cudaStreamDestroy(ctx->d2h_stream);
+    for (int i = 0; i < 8; ++i) cudaEventDestroy(ctx->host_ev[i]);
+  }
   cudaFree(ctx->d_status);
   cudaStreamDestroy(ctx->stream);
   free(ctx);

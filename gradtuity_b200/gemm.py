@@ -67,3 +67,38 @@ def gemm_3xtf32_noalloc(layout: int, M: int, N: int, K: int, a_ptr: int, lda: in
     _lib.check(lib.gt_gemm_3xtf32_noalloc(_lib.context(), layout, M, N, K, _p(a_ptr), lda, _p(b_ptr), ldb, _p(c_ptr), ldc,
                                           _p(bias_ptr), alpha, 1 if accumulate else 0, epilogue, None),
                "gt_gemm_3xtf32_noalloc")
+
+
+def matmul_host(a, b, out=None, *, layout: int = LAYOUT_NN, bias=None, alpha: float = 1.0, epilogue: int = EPI_NONE,
+                precision: int | None = None, chunks: int = 8):
+    """op(a) @ op(b) for numpy float32 arrays in HOST memory, result in `out` (host): the copies over PCIe are
+    overlapped with the product block by block (`gt_gemm_host`).  a, b are the stored-layout 2-D arrays of the
+    layout (NN: (M, K), (K, N); NT: (M, K), (N, K); TN: (K, M), (K, N)).  Pinned arrays make the overlap real;
+    pageable ones work, with serialised copies."""
+    import numpy as np
+
+    for name, arr in (("a", a), ("b", b)):
+        if arr.dtype != np.float32 or arr.ndim != 2 or arr.strides[1] != 4:
+            raise ValueError(f"matmul_host: {name} must be a 2-D float32 array with contiguous rows")
+    M = a.shape[1] if layout == LAYOUT_TN else a.shape[0]
+    K = a.shape[0] if layout == LAYOUT_TN else a.shape[1]
+    N = b.shape[0] if layout == LAYOUT_NT else b.shape[1]
+    kb = b.shape[1] if layout == LAYOUT_NT else b.shape[0]
+    if kb != K:
+        raise ValueError(f"matmul_host shape mismatch: inner dimensions {K} vs {kb}")
+    if out is None:
+        out = np.empty((M, N), dtype=np.float32)
+    elif out.dtype != np.float32 or out.shape != (M, N) or out.strides[1] != 4:
+        raise ValueError("matmul_host: out must be a float32 (M, N) array with contiguous rows")
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=np.float32)
+        if bias.shape != (N,):
+            raise ValueError(f"matmul_host: bias must have shape ({N},)")
+    if precision is None:
+        precision = default_precision()
+    lib = _lib.load_library()
+    _lib.check(lib.gt_gemm_host(_lib.context(), layout, M, N, K, c_void_p(a.ctypes.data), a.strides[0] // 4,
+                                c_void_p(b.ctypes.data), b.strides[0] // 4, c_void_p(out.ctypes.data), out.strides[0] // 4,
+                                c_void_p(bias.ctypes.data) if bias is not None else None, alpha, epilogue, precision, chunks),
+               "gt_gemm_host")
+    return out

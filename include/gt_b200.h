@@ -218,6 +218,16 @@ int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* dv, const fl
                           int64_t D, float scale, int acc_dq, int acc_dk, int acc_dv,
                           void* stream);
 
+/* The GEMM on HOST buffers: hA, hB, hC, h_bias point to host memory (pinned, for the copies to
+ * overlap); leading dimensions in elements.  B is uploaded once, A in `chunks` row blocks of C; the
+ * upload of one block, the product of the previous one and the download of the one before that run
+ * concurrently, so the call costs about max(upload, download) of PCIe time instead of their sum.
+ * It returns when hC is complete.  Epilogues: NONE, BIAS, BIAS_RELU, BIAS_GELU.  The host-data
+ * counterpart of `Tensor(list).matmul(...).to_list()` (gradtuity/tensor.py:192-220, 530-657).   */
+int gt_gemm_host(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                 const float* hA, int64_t lda, const float* hB, int64_t ldb, float* hC, int64_t ldc,
+                 const float* h_bias, float alpha, int epilogue, int precision, int chunks);
+
 /* Which kernel a call with these arguments would run: 0 = tcgen05/TMA kernel, 1 = fp32 FMA
  * kernel.  No launch.                                                                       */
 int gt_gemm_path(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,

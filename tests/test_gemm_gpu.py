@@ -242,6 +242,22 @@ def test_aux_reading_epilogue_needs_aux_and_tensor_core_path(gt):
                precision=U.PRECISIONS["fp32"])
 
 
+@pytest.mark.parametrize("layout,M,N,K,chunks,epilogue", [
+    ("NN", 1000, 260, 200, 3, "none"), ("NT", 512, 128, 96, 1, "bias_relu"), ("TN", 900, 300, 130, 4, "bias"), ("NN", 4096, 512, 256, 8, "bias_gelu")])
+def test_gemm_on_host_buffers(gt, layout, M, N, K, chunks, epilogue):
+    """gt_gemm_host: operands and result in host memory, uploads / products / downloads of row blocks overlapped."""
+    from gradtuity_b200 import gemm as G
+
+    a, b, rng = U.make_operands(layout, M, N, K, seed=M + K + chunks)
+    bias = rng.standard_normal(N).astype(np.float32) if epilogue != "none" else None
+    out = np.full((M, N + 5), np.nan, np.float32)[:, :N]                 # a row pitch larger than N
+    G.matmul_host(a, b, out=out, layout=U.LAYOUTS[layout], bias=bias, epilogue=U.EPILOGUES[epilogue], chunks=chunks)
+    ref = O.gemm(a, b, layout, bias=bias, epilogue=epilogue)
+    assert O.rel_frobenius(out, ref) <= U.TOL["tf32"]
+    out2 = G.matmul_host(a, b, layout=U.LAYOUTS[layout], bias=bias, epilogue=U.EPILOGUES[epilogue], chunks=chunks, precision=U.PRECISIONS["3xtf32"])
+    assert O.rel_frobenius(out2, ref) <= (2e-5 if epilogue == "bias_gelu" else U.TOL["3xtf32"])
+
+
 def test_bitwise_deterministic(gt):
     # one CTA per output tile (no shared K range): the summation order is fixed
     a, b, _ = U.make_operands("TN", 1536, 2048, 512, seed=3)
