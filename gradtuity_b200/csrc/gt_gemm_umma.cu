@@ -207,7 +207,7 @@ __device__ __forceinline__ bool prefetch_c(const UmmaParams& p, bool enabled, in
 // This is the general form: bias, aux and the output may end inside the chunk.
 __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                        int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                       uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
+                                                       uint8_t* tile, uint32_t tile_u32, int epi, bool add, bool aux_out) {
   const int row = row0 + lane;
   const bool has_bias = (epi >= GT_EPI_BIAS && epi <= GT_EPI_BIAS_GELU) || epi == GT_EPI_BIAS_ADD;
   const bool aux_in = epi == GT_EPI_BIAS_ADD || epi == GT_EPI_GELU_GRAD;       // aux is read, not written
@@ -235,8 +235,8 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
       }
       if (epi == GT_EPI_BIAS_ADD) { x.x += a4[0]; x.y += a4[1]; x.z += a4[2]; x.w += a4[3]; }
       else { x.x *= gt_gelu_tanh_grad(a4[0]); x.y *= gt_gelu_tanh_grad(a4[1]); x.z *= gt_gelu_tanh_grad(a4[2]); x.w *= gt_gelu_tanh_grad(a4[3]); }
-    } else if (p.aux && row_ok && nb + j + 3 < p.N) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
-    else if (p.aux && row_ok) {
+    } else if (aux_out && row_ok && nb + j + 3 < p.N) *reinterpret_cast<float4*>(p.aux + row_off + nb + j) = x;
+    else if (aux_out && row_ok) {
       float* a = p.aux + row_off + nb + j;
       if (nb + j < p.N) a[0] = x.x;
       if (nb + j + 1 < p.N) a[1] = x.y;
@@ -311,25 +311,27 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
 __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                    int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                    uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
+  // aux is an OUTPUT (pre-activation) only for the kinds that produce one, and never for a K share that merely adds
+  const bool aux_out = p.aux != nullptr && epi == p.epilogue && epi != GT_EPI_BIAS_ADD && epi != GT_EPI_GELU_GRAD;
 #define GT_EPI_FAST(E, X) epilogue_chunk_tma_fast<E, X>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add)
   if (nb + 32 <= p.N) {                              // warp-uniform
     switch (epi) {
       case GT_EPI_NONE:
-        if (!p.aux) { GT_EPI_FAST(GT_EPI_NONE, false); return; }
+        if (!aux_out) { GT_EPI_FAST(GT_EPI_NONE, false); return; }
         break;
       case GT_EPI_BIAS:
-        if (p.aux) GT_EPI_FAST(GT_EPI_BIAS, true); else GT_EPI_FAST(GT_EPI_BIAS, false);
+        if (aux_out) GT_EPI_FAST(GT_EPI_BIAS, true); else GT_EPI_FAST(GT_EPI_BIAS, false);
         return;
       case GT_EPI_BIAS_RELU:
-        if (p.aux) GT_EPI_FAST(GT_EPI_BIAS_RELU, true); else GT_EPI_FAST(GT_EPI_BIAS_RELU, false);
+        if (aux_out) GT_EPI_FAST(GT_EPI_BIAS_RELU, true); else GT_EPI_FAST(GT_EPI_BIAS_RELU, false);
         return;
       case GT_EPI_BIAS_GELU:
-        if (p.aux) GT_EPI_FAST(GT_EPI_BIAS_GELU, true); else GT_EPI_FAST(GT_EPI_BIAS_GELU, false);
+        if (aux_out) GT_EPI_FAST(GT_EPI_BIAS_GELU, true); else GT_EPI_FAST(GT_EPI_BIAS_GELU, false);
         return;
       case GT_EPI_BIAS_ADD: GT_EPI_FAST(GT_EPI_BIAS_ADD, false); return;
       case GT_EPI_GELU_GRAD: GT_EPI_FAST(GT_EPI_GELU_GRAD, false); return;
       case GT_EPI_CAUSAL:
-        if (!p.aux) {
+        if (!aux_out) {
           // a 32 x 32 block whose last column is not right of its first row holds no masked element
           if (nb + 31 > row0) GT_EPI_FAST(GT_EPI_CAUSAL, false); else GT_EPI_FAST(GT_EPI_NONE, false);
           return;
@@ -339,7 +341,7 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const fl
     }
   }
 #undef GT_EPI_FAST
-  epilogue_chunk_tma_any(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, epi, add);
+  epilogue_chunk_tma_any(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, epi, add, aux_out);
 }
 
 // Same epilogue for outputs whose rows are not 16-byte aligned (odd leading dimension, e.g. the
@@ -825,7 +827,8 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tile_coords(p, tile, batch, tm, tn, ks);
         const int i0 = batch % p.batch0, i1 = batch / p.batch0;
         const int m0 = tm * TM, n0 = tn * TN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);      // this unit's share of K (all of it without split-K)
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status)) { ok = false; break; }
           const uint32_t full = bar_full + 8 * s;
           mbar_expect_tx(full, T256_STAGE_BYTES);
@@ -872,7 +875,9 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         if (!mbar_wait(bar_tempty, tph ^ 1u, abort_flag, p.status)) { ok = false; break; }
         if (!mbar_wait(bar_tempty + 8, tph ^ 1u, abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int ks = tile % p.ksplit;
+        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_base + s * T256_STAGE_BYTES;
@@ -882,7 +887,7 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint32_t a_off = A_MN ? kk * 1024 : kk * 32;
             const uint32_t b_off = B_MN ? kk * 1024 : kk * 32;
             const uint64_t bd = make_smem_desc(sb + b_off, B_MN ? 4096 : 16, B_MN ? 512 : 1024, B_MN ? 1 : 2);
-            const uint32_t keep = (kb | kk) != 0 ? 1u : 0u;
+            const uint32_t keep = (kb != kb_lo || kk != 0) ? 1u : 0u;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               // rows 128 h .. 128 h + 127 of the A tile: 16 KB further (K-major) or four 4 KB column blocks further (MN-major)
@@ -933,7 +938,9 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tc_ld32(lane_base + (uint32_t)(c * 32), v);
         tc_wait_ld();
         if (p.c_tma) {
-          epilogue_chunk_tma(p, unit_bias, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, p.epilogue, p.accumulate != 0);
+          // with split-K every share adds its partial sum into C; bias / residual go in with share 0
+          epilogue_chunk_tma(p, unit_bias, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32,
+                             (p.ksplit > 1 && ks > 0) ? (int)GT_EPI_NONE : p.epilogue, p.accumulate != 0 || p.ksplit > 1);
         } else if (row_ok) {
           epilogue_chunk(p, unit_bias, v, row, nb, row_off);     // host guarantees aligned rows for this kernel
         }
@@ -1208,6 +1215,19 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     if (ksplit > 32) ksplit = 32;
     if (ksplit < 1) ksplit = 1;
   }
+  // Big tiles that do not fill the SMs (96 tiles of 256 x 256 for the (8192, 768, K) products): the tiles are cut
+  // along K so that about two waves of shares exist; the shares add into C with the TMA reduce-add (C zeroed
+  // first unless the call is C += ...), bias / residual with share 0.
+  static const bool deterministic256 = getenv("GRADTUITY_GEMM_DETERMINISTIC") != nullptr;
+  bool split256 = false;
+  if (use256 && !deterministic256 && tiles < ctx->sm_count && nbatch == 1 && g.ldc == g.N &&
+      (g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS || g.epilogue == GT_EPI_BIAS_ADD) &&
+      (g.epilogue == GT_EPI_BIAS_ADD || !g.aux) && getenv("GRADTUITY_GEMM_NO_TMA_STORE") == nullptr) {
+    int want = (int)((2LL * ctx->sm_count) / tiles);
+    if (want > num_kb / 16) want = num_kb / 16;
+    if (want > 8) want = 8;
+    if (want >= 2) { ksplit = want; split256 = true; }
+  }
   p.kb_per = (num_kb + ksplit - 1) / ksplit;
   ksplit = (num_kb + p.kb_per - 1) / p.kb_per;
   p.ksplit = ksplit;
@@ -1230,8 +1250,8 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   static const bool deterministic = getenv("GRADTUITY_GEMM_DETERMINISTIC") != nullptr;
   static const bool c_tma_off = getenv("GRADTUITY_GEMM_NO_TMA_STORE") != nullptr;
   const bool c_dense = g.ldc == g.N && (g.batch0 == 1 || g.sC0 == g.M * g.N) && (g.batch1 == 1 || g.sC1 == g.M * g.N * g.batch0);
-  const bool splitk_direct = ksplit > 1 && !deterministic && !c_tma_off && g.epilogue == GT_EPI_NONE && !g.aux &&
-                             tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (g.accumulate || c_dense);
+  const bool splitk_direct = split256 || (ksplit > 1 && !deterministic && !c_tma_off && g.epilogue == GT_EPI_NONE && !g.aux &&
+                                          tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (g.accumulate || c_dense));
   // Batch entries that share one C (batch stride 0, "C += sum over the batch") rely on the atomic TMA
   // reduce-add of the epilogue; a per-batch bias is applied by the tensor-core kernel's epilogue only.
   const bool c_shared = nbatch > 1 && ((g.batch0 > 1 && g.sC0 == 0) || (g.batch1 > 1 && g.sC1 == 0));

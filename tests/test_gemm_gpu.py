@@ -187,6 +187,8 @@ def test_split_k_shapes(gt, layout, M, N, K, epilogue, acc):
     ("NT", 8200, 768, 768, "none", True),       # dX with C +=, ragged last row tile
     ("NT", 8192, 3072, 800, "none", False),     # 768 tiles: 28 in the last wave, K tail
     ("TN", 8192, 776, 1024, "bias", False),     # N tail inside the last column tile
+    ("NN", 8192, 768, 4096, "bias", False),     # 96 tiles of 256 x 256: the big-tile kernel with its tiles cut along K
+    ("NT", 8192, 768, 2048, "none", True),      # the same with C += ...
 ])
 def test_last_wave_split_shapes(gt, layout, M, N, K, epilogue, acc):
     """More tiles than SMs with a last wave at most half full: the tiles of that wave are cut along K

@@ -296,3 +296,33 @@ def test_deferred_clip_equals_in_place_clip(T):
             opt.step()
         res.append(w.numpy())
     np.testing.assert_allclose(res[0], res[1], rtol=1e-6, atol=1e-7)
+
+
+def test_full_size_gpt2_fast_paths_track_the_conservative_paths():
+    """GPT-2-small at full size (config 3: batch 8 x 1024, 12 layers) for six steps, twice in fresh processes:
+    with every fast path on (fused attention, batched q/k/v, K shares added with reduce-adds, residual adds and
+    GELU backward in GEMM epilogues, big-tile split-K) and with GRADTUITY_GEMM_DETERMINISTIC=1 and
+    GRADTUITY_ATTENTION=materialized (ordered sums, S / P / O as three launches).  The loss curves must agree
+    to 1e-3 relative at every step: what the fast paths change is the order of fp32 additions, not the math."""
+    import os
+    import re
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def losses(extra_env):
+        env = dict(os.environ, **extra_env)
+        env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+        r = subprocess.run([sys.executable, "-m", "gradtuity_b200.gpt2.train", "--steps", "6", "--log_every", "1"],
+                           cwd=root, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-2000:]
+        out = [float(m) for m in re.findall(r"loss=([0-9.]+)", r.stdout)]
+        assert len(out) == 6, r.stdout
+        return out
+
+    fast = losses({})
+    slow = losses({"GRADTUITY_GEMM_DETERMINISTIC": "1", "GRADTUITY_ATTENTION": "materialized"})
+    for a, b in zip(fast, slow):
+        assert abs(a - b) <= 1e-3 * abs(b), (fast, slow)
+    assert abs(fast[0] - np.log(50257.0)) < 0.2          # a freshly initialised model predicts about uniformly
