@@ -49,6 +49,7 @@ struct AttnParams {
   float scale_log2;         // scale * log2(e)
   float scale;
   int write_p;
+  int online;               // forward: single pass with a running maximum (no P output)
   float* lse;               // (B, H, S) log-sum-exp of the scaled scores, natural log
   float* delta;             // (B, H, S) rowsum(dO * O) (backward)
   const float* o; const float* d_o;   // (B, S, H * 64), read directly by the dQ kernel for delta
@@ -162,6 +163,9 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *sm.tmem_slot;
   const uint32_t tmem_o = tmem_base + 256u;
+  // Online mode streams K and V through three ring slots; the fourth slot's memory holds the statistics the
+  // softmax warps exchange every tile.
+  const int nslots = p.online ? 3 : AT_SLOTS;
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
@@ -169,8 +173,8 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       long long ring_it = 0; int q_it = 0;
       bool ok = true;
       auto load_slot = [&](const CUtensorMap* map, bool is_v, int row0, int h, int b) -> bool {
-        const int slot = (int)(ring_it % AT_SLOTS);
-        const uint32_t par = (uint32_t)((ring_it / AT_SLOTS) & 1);
+        const int slot = (int)(ring_it % nslots);
+        const uint32_t par = (uint32_t)((ring_it / nslots) & 1);
         if (!mbar_wait(sm.bar_kv_empty + 8 * slot, par ^ 1u, sm.abort_flag, p.status)) return false;
         const uint32_t dst = sm.ring + slot * AT_SLOT_BYTES, full = sm.bar_kv_full + 8 * slot;
         mbar_expect_tx(full, AT_SLOT_BYTES);
@@ -191,7 +195,8 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_load_4d(sm.q, &map_q, sm.bar_q_full, 0, i * AT_TILE, h, b);
         tma_load_4d(sm.q + 16384, &map_q, sm.bar_q_full, 32, i * AT_TILE, h, b);
         ++q_it;
-        for (int j = 0; ok && j <= i; ++j) ok = load_slot(&map_k, false, j * AT_TILE, h, b);           // pass 1
+        if (!p.online)
+          for (int j = 0; ok && j <= i; ++j) ok = load_slot(&map_k, false, j * AT_TILE, h, b);         // pass 1
         // pass 2, in the order the MMA lane consumes them: K0, K1, V0, K2, V1, ..., Ki, V(i-1), Vi
         if (ok) ok = load_slot(&map_k, false, 0, h, b);
         for (int j = 0; ok && j <= i; ++j) {
@@ -200,10 +205,10 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
       }
       if (!ok) {     // aborting: let the loads already issued land before shared memory is released
-        const long long first = ring_it > AT_SLOTS ? ring_it - AT_SLOTS : 0;
+        const long long first = ring_it > nslots ? ring_it - nslots : 0;
         for (long long r = first; r < ring_it; ++r) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(sm.bar_kv_full + 8 * (int)(r % AT_SLOTS), (uint32_t)((r / AT_SLOTS) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+          while (!mbar_try_wait(sm.bar_kv_full + 8 * (int)(r % nslots), (uint32_t)((r / nslots) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
         }
       }
     }
@@ -213,9 +218,9 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       long long ring_it = 0; int q_it = 0, s_it = 0, p_it = 0, o_it = 0;
       bool ok = true;
       auto issue_s = [&]() -> bool {            // next ring slot holds a K tile
-        const int slot = (int)(ring_it % AT_SLOTS);
+        const int slot = (int)(ring_it % nslots);
         const int sb = s_it & 1;
-        if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / AT_SLOTS) & 1), sm.abort_flag, p.status)) return false;
+        if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / nslots) & 1), sm.abort_flag, p.status)) return false;
         if (!mbar_wait(sm.bar_s_empty + 8 * sb, (uint32_t)((s_it >> 1) & 1) ^ 1u, sm.abort_flag, p.status)) return false;
         tc_fence_after();
         mma_qk(tmem_base + (uint32_t)(sb * 128), sm.q, sm.ring + slot * AT_SLOT_BYTES);
@@ -229,13 +234,14 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         item_coords(p, item, i, h, b);
         if (!mbar_wait(sm.bar_q_full, (uint32_t)(q_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
         ++q_it;
-        for (int j = 0; ok && j <= i; ++j) ok = issue_s();          // pass 1
-        if (ok) ok = issue_s();                                     // pass 2: S_0
+        if (!p.online)
+          for (int j = 0; ok && j <= i; ++j) ok = issue_s();        // pass 1
+        if (ok) ok = issue_s();                                     // pass 2 (the only pass when online): S_0
         for (int j = 0; ok && j <= i; ++j) {
           if (j + 1 <= i) { ok = issue_s(); if (!ok) break; }
           if (j == i) tc_commit(sm.bar_q_empty);                    // every product with this Q has been issued
-          const int slot = (int)(ring_it % AT_SLOTS);
-          if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / AT_SLOTS) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          const int slot = (int)(ring_it % nslots);
+          if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / nslots) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (!mbar_wait(sm.bar_p_full, (uint32_t)(p_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (j == 0 && !mbar_wait(sm.bar_o_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -272,6 +278,108 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       ++g_it;
       return r;
     };
+    if (p.online) {
+      // ---- single pass (no P output): O and the row sums are kept relative to a running reference maximum
+      // m_ref; when a tile's maximum exceeds it by more than 8 (log2 units) the accumulated O and sum are
+      // rescaled once, otherwise the stale reference stays (p <= 2^8 is harmless in fp32).  Every tile the
+      // four warps of a row exchange their chunk maxima through shared memory.
+      float* const ostats = reinterpret_cast<float*>(sm.ptile_ptr - AT_SLOT_BYTES);   // the fourth ring slot: [3][4][128]
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int i, h, b;
+        item_coords(p, item, i, h, b);
+        const int row = i * AT_TILE + r_local;
+        float m_ref = -INFINITY, l = 0.0f;
+        for (int j = 0; j <= i; ++j) {
+          const int sb = s_it & 1;
+          if (!mbar_wait(sm.bar_s_full + 8 * sb, (uint32_t)((s_it >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const int col0 = j * AT_TILE + eset * 32;
+          const bool dead = (j == i) && (eset > q);
+          const int nvalid = (j < i) ? 32 : row - col0 + 1;
+          float v[32];
+          float mx = -INFINITY;
+          if (!dead) {
+            tc_ld32(lane_base + (uint32_t)(sb * 128 + eset * 32), v);
+            tc_wait_ld();
+#pragma unroll
+            for (int t = 0; t < 32; ++t) { v[t] = (t < nvalid) ? v[t] * p.scale_log2 : -INFINITY; mx = fmaxf(mx, v[t]); }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm.bar_s_empty + 8 * sb);      // the accumulator columns are in registers now
+          ++s_it;
+          const int par = g_it & 1;
+          ostats[(par * 4 + eset) * 128 + r_local] = mx;
+          if (!group_sync()) { ok = false; break; }
+          float m_tile = fmaxf(fmaxf(ostats[(par * 4 + 0) * 128 + r_local], ostats[(par * 4 + 1) * 128 + r_local]),
+                               fmaxf(ostats[(par * 4 + 2) * 128 + r_local], ostats[(par * 4 + 3) * 128 + r_local]));
+          float f = 1.0f;
+          if (m_tile > m_ref + 8.0f) { f = ex2(m_ref - m_tile); m_ref = m_tile; }
+          l *= f;
+          // the P tile is free once the previous PV product (and this warp's stores from it) have read it
+          if (!mbar_wait(sm.bar_p_empty, (uint32_t)(p_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+          if (j > 0 && eset < 2 && __any_sync(0xffffffffu, f != 1.0f)) {
+            // rescale this warp's 32 columns of O (the previous PV product has completed: p_empty)
+            float o[32];
+            tc_fence_after();
+            tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), o);
+            tc_wait_ld();
+#pragma unroll
+            for (int t = 0; t < 32; ++t) o[t] *= f;
+            tc_st32(lane_base + 256u + (uint32_t)(eset * 32), o);
+            tc_wait_st();
+          }
+          float acc = 0.0f;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!dead) {
+              x.x = to_tf32(ex2(v[4 * g] - m_ref)); x.y = to_tf32(ex2(v[4 * g + 1] - m_ref));
+              x.z = to_tf32(ex2(v[4 * g + 2] - m_ref)); x.w = to_tf32(ex2(v[4 * g + 3] - m_ref));
+              acc += (x.x + x.y) + (x.z + x.w);
+            }
+            *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = x;
+          }
+          l += acc;
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sm.bar_p_full);
+          ++p_it;
+        }
+        if (!ok) break;
+        // ---- row sums of the four chunks, then O / sum
+        ostats[(2 * 4 + eset) * 128 + r_local] = l;
+        if (!group_sync()) { ok = false; break; }
+        const float L = (ostats[(2 * 4 + 0) * 128 + r_local] + ostats[(2 * 4 + 1) * 128 + r_local]) +
+                        (ostats[(2 * 4 + 2) * 128 + r_local] + ostats[(2 * 4 + 3) * 128 + r_local]);
+        const float inv = 1.0f / L;
+        if (p.lse && eset == 0) p.lse[((long long)b * p.H + h) * p.S + row] = (m_ref + log2f(L)) * AT_LN2;
+        if (!mbar_wait(sm.bar_o_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        ++o_it;
+        tc_fence_after();
+        if (eset < 2) {
+          float v[32];
+          tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), v);
+          tc_wait_ld();
+          tc_fence_before();
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
+                make_float4(v[4 * g] * inv, v[4 * g + 1] * inv, v[4 * g + 2] * inv, v[4 * g + 3] * inv);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_4d(&map_o, my_sub, eset * 32, i * AT_TILE + q * 32, h, b, false);
+            mbar_arrive(sm.bar_o_empty);
+          }
+        }
+      }
+    } else
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       int i, h, b;
       item_coords(p, item, i, h, b);
@@ -966,6 +1074,8 @@ extern "C" int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* 
   p.num_items = (int)(B * H * p.nblk);
   p.scale = scale; p.scale_log2 = scale * AT_LOG2E;
   p.write_p = p_out ? 1 : 0;
+  static const bool two_pass = getenv("GRADTUITY_ATTENTION_TWO_PASS") != nullptr;   // tuning aid: the two-pass forward also without P
+  p.online = (!p_out && !two_pass) ? 1 : 0;
   p.lse = lse; p.delta = nullptr; p.o = nullptr; p.d_o = nullptr;
   p.status = ctx->d_status;
   static bool attr_set = false;
@@ -1008,7 +1118,7 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   p.nblk = (int)(S / AT_TILE);
   p.num_items = (int)(B * H * p.nblk);
   p.scale = scale; p.scale_log2 = scale * AT_LOG2E;
-  p.write_p = 0;
+  p.write_p = 0; p.online = 0;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.o = o; p.d_o = d_o;
   p.status = ctx->d_status;
   static bool attr_set = false;
