@@ -1078,11 +1078,7 @@ extern "C" int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* 
   p.online = (!p_out && !two_pass) ? 1 : 0;
   p.lse = lse; p.delta = nullptr; p.o = nullptr; p.d_o = nullptr;
   p.status = ctx->d_status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    GT_CUDA_OK(ctx, cudaFuncSetAttribute(gt_attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM_BYTES));
-    attr_set = true;
-  }
+  GT_SMEM_OPT_IN(ctx, gt_attn_fwd_kernel, AT_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
   gt_attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, mp, mo, p);
   GT_CUDA_OK(ctx, cudaGetLastError());
@@ -1121,12 +1117,8 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   p.write_p = 0; p.online = 0;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.o = o; p.d_o = d_o;
   p.status = ctx->d_status;
-  static bool attr_set = false;
-  if (!attr_set) {
-    GT_CUDA_OK(ctx, cudaFuncSetAttribute(gt_attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATB_SMEM_BYTES));
-    GT_CUDA_OK(ctx, cudaFuncSetAttribute(gt_attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATB_SMEM_BYTES));
-    attr_set = true;
-  }
+  GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dq_kernel, ATB_SMEM_BYTES);
+  GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATB_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
   gt_attn_bwd_dq_kernel<<<grid, AT_THREADS, ATB_SMEM_BYTES, stream>>>(mq, mdo, mk, mv, mkmn, mdq, p, acc_dq);
   GT_CUDA_OK(ctx, cudaGetLastError());

@@ -149,49 +149,57 @@ extern "C" int gt_gemm_host(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64
   const int64_t lda_d = layout == GT_LAYOUT_TN ? rows_per : (K + 3) / 4 * 4;      // TN: a block is (K, rows_per)
   const size_t a_blk = (size_t)(layout == GT_LAYOUT_TN ? K * lda_d : rows_per * lda_d), c_blk = (size_t)(rows_per * ldc_d);
   float *dB = nullptr, *dA[2] = {nullptr, nullptr}, *dC[2] = {nullptr, nullptr}, *d_bias = nullptr;
-  GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dB, (size_t)(b_rows * ldb_d) * sizeof(float), cs));
-  for (int i = 0; i < 2; ++i) {
-    GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dA[i], a_blk * sizeof(float), cs));
-    GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dC[i], c_blk * sizeof(float), cs));
-  }
-  if (h_bias) GT_CUDA_OK(ctx, cudaMallocAsync((void**)&d_bias, (size_t)N * sizeof(float), cs));
-  GT_CUDA_OK(ctx, cudaEventRecord(ev_alloc, cs));
-  GT_CUDA_OK(ctx, cudaStreamWaitEvent(up, ev_alloc, 0));
-  GT_CUDA_OK(ctx, cudaStreamWaitEvent(down, ev_alloc, 0));
-  GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dB, (size_t)ldb_d * 4, hB, (size_t)ldb * 4, (size_t)b_cols * 4, (size_t)b_rows, cudaMemcpyHostToDevice, up));
-  if (h_bias) GT_CUDA_OK(ctx, cudaMemcpyAsync(d_bias, h_bias, (size_t)N * 4, cudaMemcpyHostToDevice, up));
-  GT_CUDA_OK(ctx, cudaEventRecord(ev_b, up));
-  int rc = GT_OK;
-  for (int i = 0; i < nblk && rc == GT_OK; ++i) {
-    const int buf = i & 1;
-    const int64_t m0 = (int64_t)i * rows_per, rows = (M - m0) < rows_per ? (M - m0) : rows_per;
-    if (i >= 2) GT_CUDA_OK(ctx, cudaStreamWaitEvent(up, ev_g[buf], 0));             // the product that read this A buffer is done
-    if (layout == GT_LAYOUT_TN)
-      GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dA[buf], (size_t)lda_d * 4, hA + m0, (size_t)lda * 4, (size_t)rows * 4, (size_t)K, cudaMemcpyHostToDevice, up));
-    else
-      GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dA[buf], (size_t)lda_d * 4, hA + m0 * lda, (size_t)lda * 4, (size_t)K * 4, (size_t)rows, cudaMemcpyHostToDevice, up));
-    GT_CUDA_OK(ctx, cudaEventRecord(ev_a[buf], up));
-    GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_a[buf], 0));
-    if (i == 0) GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_b, 0));
-    if (i >= 2) GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_d[buf], 0));             // this C buffer has been downloaded
-    gt_gemm_args g;
-    g.layout = layout; g.epilogue = epilogue; g.precision = precision; g.accumulate = 0; g.flags = 0;
-    g.M = rows; g.N = N; g.K = K;
-    g.A = dA[buf]; g.lda = lda_d; g.sA0 = 0; g.sA1 = 0;
-    g.B = dB; g.ldb = ldb_d; g.sB0 = 0; g.sB1 = 0;
-    g.C = dC[buf]; g.ldc = ldc_d; g.sC0 = 0; g.sC1 = 0;
-    g.batch0 = 1; g.batch1 = 1; g.bias = d_bias; g.aux = nullptr; g.alpha = alpha;
-    rc = run(ctx, g, cs);
-    if (rc != GT_OK) break;
-    GT_CUDA_OK(ctx, cudaEventRecord(ev_g[buf], cs));
-    GT_CUDA_OK(ctx, cudaStreamWaitEvent(down, ev_g[buf], 0));
-    GT_CUDA_OK(ctx, cudaMemcpy2DAsync(hC + m0 * ldc, (size_t)ldc * 4, dC[buf], (size_t)ldc_d * 4, (size_t)N * 4, (size_t)rows, cudaMemcpyDeviceToHost, down));
-    GT_CUDA_OK(ctx, cudaEventRecord(ev_d[buf], down));
-  }
+  // Everything that can fail after the first allocation runs inside this lambda: a failure returns from the
+  // lambda only, so the drain-and-free block below runs on every path.
+  auto enqueue = [&]() -> int {
+    GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dB, (size_t)(b_rows * ldb_d) * sizeof(float), cs));
+    for (int i = 0; i < 2; ++i) {
+      GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dA[i], a_blk * sizeof(float), cs));
+      GT_CUDA_OK(ctx, cudaMallocAsync((void**)&dC[i], c_blk * sizeof(float), cs));
+    }
+    if (h_bias) GT_CUDA_OK(ctx, cudaMallocAsync((void**)&d_bias, (size_t)N * sizeof(float), cs));
+    GT_CUDA_OK(ctx, cudaEventRecord(ev_alloc, cs));
+    GT_CUDA_OK(ctx, cudaStreamWaitEvent(up, ev_alloc, 0));
+    GT_CUDA_OK(ctx, cudaStreamWaitEvent(down, ev_alloc, 0));
+    GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dB, (size_t)ldb_d * 4, hB, (size_t)ldb * 4, (size_t)b_cols * 4, (size_t)b_rows, cudaMemcpyHostToDevice, up));
+    if (h_bias) GT_CUDA_OK(ctx, cudaMemcpyAsync(d_bias, h_bias, (size_t)N * 4, cudaMemcpyHostToDevice, up));
+    GT_CUDA_OK(ctx, cudaEventRecord(ev_b, up));
+    for (int i = 0; i < nblk; ++i) {
+      const int buf = i & 1;
+      const int64_t m0 = (int64_t)i * rows_per, rows = (M - m0) < rows_per ? (M - m0) : rows_per;
+      if (i >= 2) GT_CUDA_OK(ctx, cudaStreamWaitEvent(up, ev_g[buf], 0));             // the product that read this A buffer is done
+      if (layout == GT_LAYOUT_TN)
+        GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dA[buf], (size_t)lda_d * 4, hA + m0, (size_t)lda * 4, (size_t)rows * 4, (size_t)K, cudaMemcpyHostToDevice, up));
+      else
+        GT_CUDA_OK(ctx, cudaMemcpy2DAsync(dA[buf], (size_t)lda_d * 4, hA + m0 * lda, (size_t)lda * 4, (size_t)K * 4, (size_t)rows, cudaMemcpyHostToDevice, up));
+      GT_CUDA_OK(ctx, cudaEventRecord(ev_a[buf], up));
+      GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_a[buf], 0));
+      if (i == 0) GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_b, 0));
+      if (i >= 2) GT_CUDA_OK(ctx, cudaStreamWaitEvent(cs, ev_d[buf], 0));             // this C buffer has been downloaded
+      gt_gemm_args g;
+      g.layout = layout; g.epilogue = epilogue; g.precision = precision; g.accumulate = 0; g.flags = 0;
+      g.M = rows; g.N = N; g.K = K;
+      g.A = dA[buf]; g.lda = lda_d; g.sA0 = 0; g.sA1 = 0;
+      g.B = dB; g.ldb = ldb_d; g.sB0 = 0; g.sB1 = 0;
+      g.C = dC[buf]; g.ldc = ldc_d; g.sC0 = 0; g.sC1 = 0;
+      g.batch0 = 1; g.batch1 = 1; g.bias = d_bias; g.aux = nullptr; g.alpha = alpha;
+      const int grc = run(ctx, g, cs);
+      if (grc != GT_OK) return grc;
+      GT_CUDA_OK(ctx, cudaEventRecord(ev_g[buf], cs));
+      GT_CUDA_OK(ctx, cudaStreamWaitEvent(down, ev_g[buf], 0));
+      GT_CUDA_OK(ctx, cudaMemcpy2DAsync(hC + m0 * ldc, (size_t)ldc * 4, dC[buf], (size_t)ldc_d * 4, (size_t)N * 4, (size_t)rows, cudaMemcpyDeviceToHost, down));
+      GT_CUDA_OK(ctx, cudaEventRecord(ev_d[buf], down));
+    }
+    return GT_OK;
+  };
+  const int rc = enqueue();
   // everything in flight must finish before the buffers go back to the pool and the caller reads C
   cudaError_t e1 = cudaStreamSynchronize(up), e2 = cudaStreamSynchronize(cs), e3 = cudaStreamSynchronize(down);
-  cudaFreeAsync(dB, cs);
-  for (int i = 0; i < 2; ++i) { cudaFreeAsync(dA[i], cs); cudaFreeAsync(dC[i], cs); }
+  if (dB) cudaFreeAsync(dB, cs);
+  for (int i = 0; i < 2; ++i) {
+    if (dA[i]) cudaFreeAsync(dA[i], cs);
+    if (dC[i]) cudaFreeAsync(dC[i], cs);
+  }
   if (d_bias) cudaFreeAsync(d_bias, cs);
   if (rc != GT_OK) return rc;
   GT_CUDA_OK(ctx, e1); GT_CUDA_OK(ctx, e2); GT_CUDA_OK(ctx, e3);

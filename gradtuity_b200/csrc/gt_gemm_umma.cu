@@ -1038,11 +1038,7 @@ template <int BN, bool A_MN, bool B_MN, bool X3, bool A_GEN>
 int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[5], const UmmaParams& p, int grid, cudaStream_t stream) {
   using C = Cfg<BN, X3>;
   auto kern = gt_gemm_umma_kernel<BN, A_MN, B_MN, X3, A_GEN>;
-  static bool attr_set = false;   // per instantiation; one caller thread per context
-  if (!attr_set) {
-    GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-    attr_set = true;
-  }
+  GT_SMEM_OPT_IN(ctx, kern, C::SMEM_BYTES);
   kern<<<grid, A_GEN ? NUM_THREADS_AGEN : NUM_THREADS, C::SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
@@ -1144,7 +1140,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
                 fixed_scratch_floats * sizeof(float));
       a_hi = fixed_scratch;
     } else {
-      int rc = gt_workspace_reserve(ctx, need);
+      int rc = gt_workspace_reserve(ctx, need, stream);
       if (rc != GT_OK) return rc;
       a_hi = (float*)ctx->workspace;
     }
@@ -1264,7 +1260,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     if (!g.accumulate) GT_CUDA_OK(ctx, cudaMemsetAsync(g.C, 0, (size_t)plane * sizeof(float), stream));
     p.accumulate = 1;
   } else if (ksplit > 1) {
-    int rc2 = gt_workspace_reserve(ctx, (size_t)(8192 + plane * ksplit) * sizeof(float));
+    int rc2 = gt_workspace_reserve(ctx, (size_t)(8192 + plane * ksplit) * sizeof(float), stream);
     if (rc2 != GT_OK) return rc2;
     ws = (float*)ctx->workspace + 8192;           // the first 8192 floats belong to the reductions
     p.C = ws; p.bias = nullptr; p.aux = nullptr;
@@ -1310,6 +1306,8 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
         p.tail_zero = g.accumulate ? 0 : 1;
         p.tail_epoch = ++ctx->tail_epoch;
         p.tail_flags = ctx->d_status + 16;
+        // the flags are shared by every launch of this context: one on another stream waits for the previous user
+        if ((rc = gt_scratch_acquire(ctx, stream)) != GT_OK) return rc;
       }
     }
   }
@@ -1321,12 +1319,9 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
             ksplit, (int)splitk_direct, p.tail_split, p.tail_first, p.num_tiles, grid, p.c_tma, p.a_onebox, p.b_onebox);
 
   if (use256) {
-    static bool attr_set[3] = {false, false, false};
-    auto launch256 = [&](auto kern, int idx) -> int {
-      if (!attr_set[idx]) {
-        GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, T256_SMEM_BYTES));
-        attr_set[idx] = true;
-      }
+    auto launch256 = [&](auto kern, int idx) -> int {      // generic lambda: one instantiation (and one static) per kernel
+      (void)idx;
+      GT_SMEM_OPT_IN(ctx, kern, T256_SMEM_BYTES);
       kern<<<grid, T256_THREADS, T256_SMEM_BYTES, stream>>>(maps[0], maps[1], maps[4], p);
       GT_CUDA_OK(ctx, cudaGetLastError());
       ctx->launches += 1;
@@ -1379,8 +1374,10 @@ int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream)
 // The array is a file-scope __device__ object: every GPU that loads the library keeps
 // GT_NOALLOC_SCRATCH_BYTES of it until the process exits.  In host code its name is only a
 // handle; the device address is looked up with cudaGetSymbolAddress once per device, with
-// that device current, on the first call made for that device.  That first call should
-// therefore come before any stream capture begins.  All calls share the array and it keeps
+// that device current, on the first call made for that device (the caller's current device is
+// restored).  That first call should therefore come before any stream capture begins and outside
+// any timed region: with lazy module loading it can be the moment the array is placed on the GPU,
+// so "allocates nothing" is a property of every call after the first one on a device.  All calls share the array and it keeps
 // the previous call's contents: the split kernels overwrite every element the GEMM reads
 // (padding columns included), so nothing needs clearing, but two calls whose kernels overlap
 // on the GPU (different streams without an ordering between them) race on it.
@@ -1413,9 +1410,17 @@ extern "C" int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_
             "gt_gemm_3xtf32_noalloc: A and B need %.0f floats of split scratch, the built-in array holds %zu (32 MiB); use gt_gemm",
             need, GT_NOALLOC_SCRATCH_FLOATS);
   if (!g_noalloc_scratch_ptr[ctx->device]) {
-    GT_CUDA_OK(ctx, cudaSetDevice(ctx->device));
+    // One-time set-up for this device: the symbol's address is per device and is looked up with that device
+    // current; the caller's current device is put back afterwards.  (With CUDA's lazy module loading this
+    // look-up may also be the moment the driver places the array on the GPU.)
+    int previous = -1;
+    GT_CUDA_OK(ctx, cudaGetDevice(&previous));
+    if (previous != ctx->device) GT_CUDA_OK(ctx, cudaSetDevice(ctx->device));
     float* p = nullptr;
-    GT_CUDA_OK(ctx, cudaGetSymbolAddress((void**)&p, gt_noalloc_scratch));
+    const cudaError_t e = cudaGetSymbolAddress((void**)&p, gt_noalloc_scratch);
+    if (previous != ctx->device) cudaSetDevice(previous);
+    GT_CUDA_OK(ctx, e);
+    if (!p) GT_FAIL(ctx, GT_ERR_CUDA, "gt_gemm_3xtf32_noalloc: the scratch array has no device address on device %d", ctx->device);
     g_noalloc_scratch_ptr[ctx->device] = p;
   }
   cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;

@@ -26,6 +26,8 @@ struct gt_ctx {
   gt_encode_tiled_fn encode_tiled;
   void* workspace;            // scratch for operand splitting (TF32X3) and split-K partials
   size_t workspace_bytes;
+  cudaStream_t scratch_stream;   // stream of the last launch that used the workspace or the tail flags (null: none yet)
+  cudaEvent_t scratch_event;     // orders a launch on another stream behind that one (created on first switch)
   int64_t launches;
   int tma_round;              // 1: tensor maps use the TFLOAT32 data type (TMA rounds), 0: FLOAT32
   char last_error[256];
@@ -47,6 +49,19 @@ struct gt_ctx {
     return (code);                                                                         \
   } while (0)
 
+// Opt a kernel in to `bytes` of dynamic shared memory, once per DEVICE: the attribute belongs to the device's
+// copy of the function, so a second context on another device of the same process needs its own call.
+// The remembered set is a static of the enclosing function (or template instantiation): one per kernel.
+#define GT_SMEM_OPT_IN(ctx, kern, bytes)                                                                   \
+  do {                                                                                                     \
+    static unsigned long long _gt_done = 0ull;                                                             \
+    const unsigned long long _gt_bit = 1ull << ((ctx)->device & 63);                                       \
+    if (!(_gt_done & _gt_bit)) {                                                                           \
+      GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (bytes)));   \
+      _gt_done |= _gt_bit;                                                                                 \
+    }                                                                                                      \
+  } while (0)
+
 // One GEMM problem, fully resolved (used by both kernels).
 struct gt_gemm_args {
   int layout, epilogue, precision, accumulate, flags;
@@ -60,7 +75,12 @@ struct gt_gemm_args {
   float alpha;
 };
 
-int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes);
+// The context's shared scratch (the workspace and the last-wave flags behind d_status) serves one launch at a
+// time.  Launches on one stream are ordered by the stream; a launch on a DIFFERENT stream than the previous
+// user is made to wait for everything enqueued so far on that stream.  Call before the launch that uses it.
+int gt_scratch_acquire(gt_ctx* ctx, cudaStream_t stream);
+// gt_scratch_acquire + make the workspace at least nbytes large.
+int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes, cudaStream_t stream);
 int gt_gemm_validate(gt_ctx* ctx, const gt_gemm_args& g);
 int gt_gemm_fma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);

@@ -822,7 +822,7 @@ extern "C" int gt_adamw(gt_ctx* ctx, float* p, const float* g, float* m, float* 
 
 extern "C" int gt_sumsq(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate) {
   if (!ctx || !out || !x || n <= 0) return GT_ERR_INVALID_ARG;
-  int rc = gt_workspace_reserve(ctx, 8192 * sizeof(float));
+  int rc = gt_workspace_reserve(ctx, 8192 * sizeof(float), ctx->stream);
   if (rc != GT_OK) return rc;
   float* partial = (float*)ctx->workspace + 4096;
   const unsigned blocks = blocks_for(ctx, n);
@@ -864,7 +864,7 @@ extern "C" int gt_adamw_multi(gt_ctx* ctx, const void* tensors, const void* chun
 extern "C" int gt_sumsq_multi(gt_ctx* ctx, float* out, const void* tensors, const void* chunks, int64_t n_chunks, int64_t chunk_elems) {
   if (!ctx || !out || !tensors || !chunks || n_chunks <= 0 || chunk_elems <= 0) return GT_ERR_INVALID_ARG;
   if (n_chunks > 4096) GT_FAIL(ctx, GT_ERR_TOO_LARGE, "gt_sumsq_multi: at most 4096 chunks, got %lld", (long long)n_chunks);
-  int rc = gt_workspace_reserve(ctx, 8192 * sizeof(float));
+  int rc = gt_workspace_reserve(ctx, 8192 * sizeof(float), ctx->stream);
   if (rc != GT_OK) return rc;
   float* partial = (float*)ctx->workspace + 4096;
   sumsq_multi_kernel<<<(unsigned)n_chunks, 256, 0, ctx->stream>>>((const MtTensor*)tensors, (const MtChunk*)chunks, chunk_elems, partial);

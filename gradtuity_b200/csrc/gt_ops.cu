@@ -372,7 +372,7 @@ extern "C" int gt_add_bias(gt_ctx* ctx, float* out, const float* x, const float*
 extern "C" int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate) {
   if (!ctx || !out || !x || n <= 0) return GT_ERR_INVALID_ARG;
   const unsigned blocks = ew_blocks(ctx, n);
-  int rc = gt_workspace_reserve(ctx, 4096 * sizeof(float));
+  int rc = gt_workspace_reserve(ctx, 4096 * sizeof(float), ctx->stream);
   if (rc != GT_OK) return rc;
   float* partial = (float*)ctx->workspace;
   sum_partial_kernel<<<blocks, EW_THREADS, 0, ctx->stream>>>(x, partial, n);

@@ -78,6 +78,7 @@ extern "C" int gt_destroy(gt_ctx* ctx) {
   if (!ctx) return GT_ERR_INVALID_ARG;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->scratch_event) cudaEventDestroy(ctx->scratch_event);
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->h2d_stream) {
     cudaStreamDestroy(ctx->h2d_stream);
@@ -109,11 +110,25 @@ extern "C" int gt_launch_count(gt_ctx* ctx, int64_t* count) {
   return GT_OK;
 }
 
-int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes) {
+int gt_scratch_acquire(gt_ctx* ctx, cudaStream_t stream) {
+  if (ctx->scratch_stream && ctx->scratch_stream != stream) {
+    if (!ctx->scratch_event) GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->scratch_event, cudaEventDisableTiming));
+    GT_CUDA_OK(ctx, cudaEventRecord(ctx->scratch_event, ctx->scratch_stream));
+    GT_CUDA_OK(ctx, cudaStreamWaitEvent(stream, ctx->scratch_event, 0));
+  }
+  ctx->scratch_stream = stream;
+  return GT_OK;
+}
+
+int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes, cudaStream_t stream) {
+  const cudaStream_t previous = ctx->scratch_stream;
+  int rc = gt_scratch_acquire(ctx, stream);
+  if (rc != GT_OK) return rc;
   if (nbytes <= ctx->workspace_bytes) return GT_OK;
   // Growing is rare (first call at a new largest size); it orders itself against earlier
-  // users of the old block by synchronising the compute stream.
-  GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  // users of the old block by synchronising the streams that may still read it.
+  if (previous) GT_CUDA_OK(ctx, cudaStreamSynchronize(previous));
+  GT_CUDA_OK(ctx, cudaStreamSynchronize(stream));
   if (ctx->workspace) GT_CUDA_OK(ctx, cudaFree(ctx->workspace));
   ctx->workspace = nullptr;
   ctx->workspace_bytes = 0;

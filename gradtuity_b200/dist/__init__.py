@@ -42,8 +42,9 @@ def print_rank(message: str = "", ranks: list[int] = [0], **kwargs) -> None:
         print(message, **kwargs)
 
 
+no_sync = ddp.no_sync            # added: backward calls inside it send no gradient buckets
 distributed_indices = sampler.distributed_indices
 shard_size = sampler.shard_size
 
 __all__ = ["init", "destroy_process_group", "sync_grads", "init_sync", "get_rank", "get_world_size", "get_local_rank",
-           "get_master_addr", "get_master_port", "get_env_ranks", "barrier", "distributed_indices", "shard_size", "print_rank"]
+           "get_master_addr", "get_master_port", "get_env_ranks", "barrier", "distributed_indices", "shard_size", "print_rank", "no_sync"]

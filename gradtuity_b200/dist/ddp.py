@@ -14,6 +14,14 @@ overrides it; the result is the mean over ranks).  What differs is how the bucke
   enqueues what is left (parameters that were not in the graph) and makes the compute stream wait.
 
 The API does not change: `sync_grads` is still called after `backward()` (gpt2/train.py:127-128).
+
+Several backward calls per sync (gradient accumulation, two losses).  Only the FIRST backward after a
+`sync_grads` sends buckets early; any further backward before the next `sync_grads` first makes the
+compute stream wait for the collectives already in flight (its `grad +=` kernels write the same arena),
+sends nothing itself, and `sync_grads` then reduces every bucket again.  Averaging is linear, so a bucket
+that was averaged after the first backward and then received local additions still ends as the mean over
+ranks of the summed gradients.  A backward that is never followed by `sync_grads` (a "no sync" micro-step,
+where the reference does not communicate at all) must run inside `no_sync()`, which keeps it from sending.
 """
 from __future__ import annotations
 
@@ -101,6 +109,7 @@ class GradPlan:
             end = self.offsets[idxs[-1]] + numels[idxs[-1]]
             self.ranges.append((self.arena.ptr + start * F32, end - start))
         # per-step state
+        self.armed = False          # set by finish(): the next backward (and only that one) may send early
         self.active = False
         self.launched: set[int] = set()
         self.launch_order: list[int] = []
@@ -113,9 +122,14 @@ class GradPlan:
 
     # ---- called by Tensor.backward() ------------------------------------------------------------
     def begin(self, topo: list) -> None:
+        if self.launched:
+            # a backward since the last sync_grads sent these buckets: this backward adds into the same
+            # arena, so it must run behind them; finish() will reduce every bucket again
+            comm._require().wait()
         self.launched.clear()
         self.launch_order.clear()
-        self.active = self.intact()
+        self.active = self.armed and not _no_sync_depth and self.intact()
+        self.armed = False
         if not self.active:
             return
         cons = {}
@@ -166,11 +180,28 @@ class GradPlan:
             self._launch(b)
         comm._require().wait()
         self.active = False
+        self.armed = True
         self.launched = set()
 
 
 _plans: dict[tuple, GradPlan] = {}
 _mem_ops = None            # tests may install host memory ops
+_no_sync_depth = 0
+
+
+class no_sync:
+    """Context manager: backward calls inside it send no gradient buckets (for micro-steps that are not
+    followed by `sync_grads`).  Not in the reference, whose backward never communicates."""
+
+    def __enter__(self):
+        global _no_sync_depth
+        _no_sync_depth += 1
+        return self
+
+    def __exit__(self, *exc):
+        global _no_sync_depth
+        _no_sync_depth -= 1
+        return False
 
 
 def _observer_install(plan: GradPlan | None) -> None:

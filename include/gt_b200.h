@@ -184,8 +184,10 @@ int gt_gemm_batched_ex(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
  *     rounded up to a multiple of 4 (for example M = N = K = 1024, or 2048 x 1024 x 512);
  *     larger problems return GT_ERR_TOO_LARGE and launch nothing;
  *   - any operand alignment and leading dimension is accepted (the split packs both operands);
- *   - the first call on each device looks up the array's device address; make that call
- *     before starting any stream capture;
+ *   - the first call on each device looks up the array's device address (and, when the CUDA
+ *     module is loaded lazily, may be the moment the driver places the 32 MiB array on that
+ *     GPU): make that call before starting any stream capture and outside any timed region;
+ *     every later call on the device touches no allocator at all;
  *   - all calls share the array: calls whose kernels may overlap on the GPU race on it.    */
 #define GT_NOALLOC_SCRATCH_BYTES (32u << 20)
 int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,

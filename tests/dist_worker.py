@@ -54,6 +54,49 @@ def main():
             np.testing.assert_allclose(p.grad.array, (mine[i] + other[i]) / 2, rtol=1e-6, atol=1e-7)
         dist.destroy_process_group()
         return
+    if mode == "accumulate":
+        # backward(); backward(); sync_grads() must give the mean over ranks of the SUMMED gradients,
+        # although the first backward already sent (and averaged) its buckets.
+        import torch.distributed as dist
+        from gradtuity_b200.dist import comm, ddp
+        from tests._dist_host import FakeTensor, GlooBackend, HostMemoryOps
+
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['MASTER_PORT']}", rank=rank, world_size=world)
+        comm.set_backend(GlooBackend())
+        ddp._mem_ops = HostMemoryOps()
+        shapes = [(6,), (3, 5), (40,)]
+        params = [FakeTensor(np.zeros(s), requires_grad=True) for s in shapes]
+        os.environ["GRADTUITY_BUCKET_MB"] = str(64 / (1024 * 1024))
+        ddp.sync_grads(params)                                   # builds the plan (zeros)
+        plan = next(iter(ddp._plans.values()))
+
+        def grads(r, k):
+            g = np.random.default_rng(1000 * k + r)
+            return [g.standard_normal(s).astype(np.float32) for s in shapes]
+
+        def backward(k):
+            nodes = []
+            for p in params:
+                n = FakeTensor(np.zeros(1)); n._parents = (p,); nodes.append(n)
+            topo = [x for pair in zip(params, nodes) for x in pair]
+            plan.begin(topo)
+            for p, n, g in reversed(list(zip(params, nodes, grads(rank, k)))):
+                p.grad.array[...] += g                          # the node's grad += kernel
+                plan.node_done(n._parents)
+            plan.end()
+
+        for p in params:
+            p.grad.array[...] = 0
+        backward(1)
+        assert len(plan.launched) == len(plan.buckets)           # the first backward sent everything early
+        backward(2)
+        assert not plan.launched
+        ddp.sync_grads(params)
+        for i, p in enumerate(params):
+            want = sum(grads(r, k)[i] for r in range(world) for k in (1, 2)) / world
+            np.testing.assert_allclose(p.grad.array, want, rtol=1e-5, atol=1e-6)
+        dist.destroy_process_group()
+        return
     raise SystemExit(f"unknown mode {mode}")
 
 

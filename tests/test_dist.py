@@ -125,6 +125,45 @@ def test_backward_observer_sends_buckets_as_soon_as_their_last_consumer_ran(monk
     assert next(iter(ddp._plans.values())) is not plan
 
 
+def test_only_the_first_backward_after_a_sync_sends_buckets(monkeypatch):
+    """backward(); backward(); sync_grads(): the second backward waits for the first one's collectives,
+    sends nothing, and sync_grads reduces every bucket again; inside no_sync() nothing is sent at all."""
+    params, be = _plan(monkeypatch, [(4,), (4,)], 16)                    # one parameter per bucket
+    ddp.sync_grads(params)
+    plan = next(iter(ddp._plans.values()))
+
+    def node(*parents):
+        n = FakeTensor(np.zeros(1)); n._parents = parents; return n
+
+    def backward():
+        n0, n1 = node(params[0]), node(params[1])
+        plan.begin([params[0], n0, params[1], n1])
+        plan.node_done(n1._parents)
+        plan.node_done(n0._parents)
+        plan.end()
+
+    be.calls.clear(); waits = be.waits
+    backward()
+    assert len(be.calls) == 2 and be.waits == waits          # first backward after a sync: both buckets early
+    backward()
+    assert len(be.calls) == 2 and be.waits == waits + 1      # second: nothing sent, compute ordered behind the comm stream
+    ddp.sync_grads(params)
+    assert len(be.calls) == 4                                # every bucket reduced again
+    be.calls.clear()
+    with ddp.no_sync():
+        backward()
+    assert be.calls == []
+    backward()                                               # the arming was used up by the no_sync backward
+    assert be.calls == []
+    ddp.sync_grads(params)
+    assert len(be.calls) == 2
+
+
+def test_two_ranks_accumulate_two_backwards_then_sync_over_gloo():
+    r = _launch("accumulate")
+    assert r.returncode == 0, r.stderr[-3000:]
+
+
 def test_rendezvous_times_out_with_a_diagnostic(tmp_path):
     with pytest.raises(RuntimeError, match="did not reach 128 bytes"):
         comm.exchange_unique_id(1, None, str(tmp_path / "never.bin"), timeout=0.2)

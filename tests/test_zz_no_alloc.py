@@ -52,6 +52,40 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point(gt):
         assert O.rel_frobenius(new - base, want - base) <= U.TOL["3xtf32"]
 
 
+def _free_device_bytes():
+    """Free bytes on the current device as the CUDA runtime reports them."""
+    import ctypes
+
+    rt = ctypes.CDLL("libcudart.so.12")
+    free, total = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    assert rt.cudaMemGetInfo(ctypes.byref(free), ctypes.byref(total)) == 0
+    return free.value
+
+
+def test_a_call_after_the_first_leaves_free_device_memory_unchanged(gt):
+    """The property the entry point exists for: once its one-time set-up has run, a call reserves no
+    device memory, even for the largest problem it accepts (which in gt_gemm's 3xTF32 mode would
+    grow the library's workspace in a fresh process)."""
+    from gradtuity_b200 import gemm as G
+
+    small = [U.DeviceBuffer(np.ones((64, 64), np.float32)) for _ in range(3)]
+    G.gemm_3xtf32_noalloc(0, 64, 64, 64, small[0].ptr, 64, small[1].ptr, 64, small[2].ptr, 64)     # set-up call
+    gt.device_status()
+    M = N = K = 1024                                   # 2 * (1 Mi + 1 Mi) * 2 = exactly the 8 Mi floats the array holds
+    a, b, _ = U.make_operands("NN", M, N, K, seed=9)
+    da, db, dc = U.DeviceBuffer(a), U.DeviceBuffer(b), U.DeviceBuffer(nbytes=M * N * 4)
+    gt.device_status()
+    for attempt in range(2):                           # a second try in case something else on the box moved memory
+        before = _free_device_bytes()
+        G.gemm_3xtf32_noalloc(0, M, N, K, da.ptr, K, db.ptr, N, dc.ptr, N)
+        gt.device_status()
+        after = _free_device_bytes()
+        if after == before:
+            break
+    assert after == before, f"free device memory changed by {before - after} bytes across the call"
+    assert O.rel_frobenius(dc.read((M, N)), O.gemm(a, b, "NN")) <= U.TOL["3xtf32"]
+
+
 def test_oversize_problem_is_refused_and_nothing_is_written(gt):
     from gradtuity_b200 import gemm as G
 
