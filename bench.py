@@ -41,9 +41,10 @@ FLOPS = 2.0 * M * N * K
 ALG_BYTES = 4.0 * (M * K + K * N + M * N)
 # Rows of A used by the CPU legs: same K and N, a quarter of M (275 GFLOP per pass).
 CPU_SAMPLE_ROWS = 2048
-# DRAM bytes (read + write) per launch of the 8192^3 GEMM kernel, from the ncu capture summarised in
-# profiles/gemm_umma256_nn_tf32_8192_dram_traffic.md (1.779 GB read + 0.237 GB written).
+# DRAM bytes (read + write) per launch of the 8192^3 GEMM kernel: an ncu `dram__bytes_read.sum +
+# dram__bytes_write.sum` capture at the bench size (1.779 GB read + 0.237 GB written).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 2015737344
+SUSTAINED_SECONDS = 4.0
 
 
 def _peaks():
@@ -54,6 +55,16 @@ def _peaks():
         # The file holds a measured dense bf16 GEMM rate; kind::tf32 runs at half the bf16 rate.
         return p["bf16_tflops"] / 2.0, "measured: MEASURED_PEAKS.json bf16_tflops (burst) / 2 for tf32"
     return 1590.0 / 2.0, "fallback: 1.59 PFLOP/s bf16 / 2 for tf32"
+
+
+def _peaks_sustained():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        if "bf16_tflops_sustained" in p:
+            return p["bf16_tflops_sustained"] / 2.0, "measured: MEASURED_PEAKS.json bf16_tflops_sustained / 2 for tf32"
+    return 1400.0 / 2.0, "fallback: 1.4 PFLOP/s sustained bf16 / 2 for tf32"
 
 
 def _operands():
@@ -183,6 +194,48 @@ def run_ours(args) -> dict:
     launches = _lib.launch_count() - launches0
     total_ms = _barrier_max(dist, ms.value)
     _lib.device_status()
+    # parity of the device-resident C that was just timed: sampled rows against float64
+    rows_dev = np.unique(np.concatenate([np.arange(0, M, M // 16), [1, 127, 128, M - 129, M - 1]]))
+    c_dev = tc.numpy()
+    ref_dev = a_host[rows_dev].astype(np.float64) @ b_host.astype(np.float64)
+    err_dev = float(np.linalg.norm(c_dev[rows_dev] - ref_dev) / np.linalg.norm(ref_dev))
+    del c_dev
+    if err_dev > 1e-3:
+        raise SystemExit(f"parity failure in bench (device-resident C): relative error {err_dev}")
+
+    # ---- sustained: the same GEMM back to back for >= SUSTAINED_SECONDS, clocks sampled meanwhile ----
+    sustained = None
+    if not args.no_sustained:
+        burst_ms = ms.value / args.steps
+        n_sus = int(SUSTAINED_SECONDS * 1.6 / (burst_ms * 1e-3))      # headroom: the clock drops under the power cap
+        n_sus = max(8, (n_sus + 7) // 8 * 8)
+        marks = [ev() for _ in range(9)]
+        sus_sampler = ClockSampler(local)
+        sus_sampler.start()
+        lib.gt_event_record(ctx, marks[0])
+        for part in range(8):
+            for _ in range(n_sus // 8):
+                step()
+            lib.gt_event_record(ctx, marks[part + 1])
+        _lib.check(lib.gt_sync(ctx), "gt_sync")
+        sus_clocks = sus_sampler.stop()
+        part_ms = []
+        for part in range(8):
+            pm = c_float()
+            _lib.check(lib.gt_event_elapsed_ms(ctx, marks[part], marks[part + 1], byref(pm)), "gt_event_elapsed_ms")
+            part_ms.append(pm.value)
+        sus_total = _barrier_max(dist, sum(part_ms))
+        sus_step_ms = sus_total / n_sus
+        sus_tflops = FLOPS / (sus_step_ms * 1e-3) / 1e12
+        peak_s, peak_s_src = _peaks_sustained()
+        mhz = sus_clocks.get("sm_mhz")
+        sustained = {"seconds": round(sus_total * 1e-3, 2), "launches": n_sus, "ms_per_step": round(sus_step_ms, 4),
+                     "tflops": round(sus_tflops, 2), "tflops_by_eighth": [round(FLOPS * (n_sus // 8) / (x * 1e-3) / 1e12, 1) for x in part_ms],
+                     "clocks": sus_clocks, "ms_times_mhz": round(sus_step_ms * mhz, 1) if mhz else None,
+                     "burst_ms_times_max_mhz": None,
+                     "peak": round(peak_s, 2), "peak_source": peak_s_src, "frac": round(sus_tflops / peak_s, 4),
+                     "frac_of_nominal_1125": round(sus_tflops / 1125.0, 4)}
+        _lib.device_status()
 
     # ---- end to end through the Tensor API with host buffers ----
     def pinned(shape):
@@ -260,13 +313,26 @@ def run_ours(args) -> dict:
                      "peak_source": peak_src, "algorithmic_flops_per_launch": FLOPS,
                      "algorithmic_bytes_per_launch": ALG_BYTES,
                      "frac_of_nominal_1125": round(achieved / 1125.0, 4)},
-        "parity_check": {"rel_frobenius_8_rows_vs_float64": err},
+        "parity_check": {"rel_frobenius_8_rows_vs_float64": err, "device_resident_rows_vs_float64": err_dev,
+                         "device_resident_rows": int(len(rows_dev))},
     }
+    if sustained is not None:
+        if clocks and clocks.get("sm_max_mhz"):
+            sustained["burst_ms_times_max_mhz"] = round(ms.value / args.steps * clocks["sm_max_mhz"], 1)
+        out["sustained"] = sustained
+    if rank == 0 and world == 1 and not args.no_library_peak:
+        ta = tb = tc = None
+        lib_peak = library_tf32_peak()
+        out["library_tf32"] = lib_peak
+        if "burst_tflops" in lib_peak:
+            out["roofline"]["frac_of_library_tf32_burst"] = round(achieved / lib_peak["burst_tflops"], 4)
+            if sustained is not None and lib_peak.get("sustained_tflops"):
+                sustained["frac_of_library_tf32_sustained"] = round(sustained["tflops"] / lib_peak["sustained_tflops"], 4)
     if rank == 0 and world == 1:
         out["cpu_baseline"] = cpu_baseline(a_host, b_host, reps=3)
     if not args.no_train:
         # free the GEMM operands before the model is built
-        del ta, tb, tc
+        ta = tb = tc = None
         for ptr_ in (pa, pb, pc):
             lib.gt_host_free(ctx, ptr_)
         train = run_train(args, world, rank, lambda v: _barrier_max(dist, v))
@@ -275,6 +341,45 @@ def run_ours(args) -> dict:
         dist.barrier()
         dist.destroy_process_group()
     return out if rank == 0 else None
+
+
+def library_tf32_peak() -> dict:
+    """The TF32 figure a library GEMM reaches on this GPU, measured the way MEASURED_PEAKS.json measured
+    bf16: torch.matmul (cuBLAS, allow_tf32) at 8192^3, best of 10 (burst) and back to back for 4 s
+    (sustained).  A yardstick beside the roofline only; torch is never on the product path."""
+    try:
+        import torch
+
+        torch.backends.cuda.matmul.allow_tf32 = True
+        dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        a = torch.randn(M, K, device=dev) / K ** 0.5
+        b = torch.randn(K, N, device=dev) / K ** 0.5
+        c = torch.empty(M, N, device=dev)
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); torch.matmul(a, b, out=c); e1.record(); e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        n = max(8, int(SUSTAINED_SECONDS * 1.6 / (best * 1e-3)))
+        sampler = ClockSampler(dev.index or 0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            torch.matmul(a, b, out=c)
+        e1.record(); e1.synchronize()
+        clocks = sampler.stop()
+        sus_ms = e0.elapsed_time(e1) / n
+        del a, b, c
+        torch.cuda.empty_cache()
+        return {"what": "torch.matmul fp32 with allow_tf32 (cuBLAS), 8192^3", "burst_ms": round(best, 4),
+                "burst_tflops": round(FLOPS / (best * 1e-3) / 1e12, 2), "sustained_seconds": round(sus_ms * n * 1e-3, 2),
+                "sustained_tflops": round(FLOPS / (sus_ms * 1e-3) / 1e12, 2), "sustained_clocks": clocks, "torch": torch.__version__}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": repr(e)[:200]}
 
 
 TRAIN_FLOPS_PER_STEP = 6.0 * 123532032 * 8192 + 3 * 12 * 2 * (2.0 * 96 * 1024 * 1024 * 64)   # 7.00 TFLOP per GPU
@@ -302,7 +407,7 @@ def run_train(args, world: int, rank: int, barrier_max) -> dict:
     if world > 1:
         gdist.init_sync(model)
     opt = AdamW(params, lr=3e-4, weight_decay=0.01)
-    steps = max(2, min(args.steps, 10))
+    steps = max(2, args.steps)
     warm = 3
     batches = [synthetic_batch(i, rank, 8, 1024, 50257) for i in range(warm + steps)]
     losses = []
@@ -495,6 +600,7 @@ def cpu_baseline(a, b, reps: int) -> dict:
     """numpy float32 matmul (the oracle's `matmul_f32`) on a row slice of the same operands."""
     from oracle import gemm_oracle as O
 
+    _use_all_host_cores()
     a_s = a[:CPU_SAMPLE_ROWS]
     flops = 2.0 * CPU_SAMPLE_ROWS * N * K
     best = float("inf")
@@ -507,10 +613,80 @@ def cpu_baseline(a, b, reps: int) -> dict:
             "seconds_per_pass": round(best, 4)}
 
 
+def _use_all_host_cores() -> int:
+    """Give the BLAS behind numpy every core this process may run on.  Launchers such as
+    torch.distributed.run export OMP_NUM_THREADS=1, which would turn the CPU arm into a one-thread run."""
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_limits
+
+        threadpool_limits(limits=cores, user_api="blas")
+    except Exception:
+        pass
+    return _blas_threads()
+
+
+def reference_triton_gemm(iters: int = 5) -> dict:
+    """The reference's own GPU GEMM (its Triton `matmul_kernel`, 32x32x32 tiles: gradtuity/tensor.py:569-593,
+    gradtuity/kernels_triton/matmul_kernels.py:18-90) on the bench's 8192^3 operands, launched by raw pointer
+    from an unmodified copy of the reference under baseline/_ref when that copy and a GPU are present."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "gradtuity")):
+        return {"unavailable": "no copy of the reference under baseline/_ref"}
+    try:
+        import glob
+        import site
+
+        import torch
+
+        if not torch.cuda.is_available():
+            return {"unavailable": "no GPU"}
+        sp = site.getsitepackages()
+        cudart = sorted(sum((glob.glob(x + "/nvidia/cuda_runtime/lib/libcudart.so*") for x in sp), [])) or ["libcudart.so"]
+        os.environ.setdefault("GRADTUITY_LIBCUDART_LIBRARY", cudart[0])
+        os.environ.setdefault("GRADTUITY_KERNEL_BACKEND", "triton")
+        if ref not in sys.path:
+            sys.path.insert(0, ref)
+        import triton
+        from gradtuity.kernels_triton.matmul_kernels import matmul_kernel
+
+        a = torch.randn(M, K, device="cuda") / K ** 0.5
+        b = torch.randn(K, N, device="cuda") / K ** 0.5
+        c = torch.empty(M, N, device="cuda")
+        grid = (triton.cdiv(M, 32), triton.cdiv(N, 32))
+
+        def launch():
+            matmul_kernel[grid](a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, K, 1, N, 1, N, 1, BLOCK_M=32, BLOCK_N=32, BLOCK_K=32)
+
+        launch()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); launch(); e1.record(); e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        rows = torch.arange(0, M, M // 8, device="cuda")
+        want = a[rows].double() @ b.double()
+        err = float(torch.linalg.norm(c[rows].double() - want) / torch.linalg.norm(want))
+        return {"what": "reference Triton matmul_kernel[grid], BLOCK 32x32x32, fp32 in / tf32 tl.dot, 8192^3 NN, operands resident",
+                "ms": round(ms, 3), "tflops": round(FLOPS / (ms * 1e-3) / 1e12, 2), "iters": iters,
+                "rel_frobenius_8_rows_vs_float64": err, "triton": triton.__version__}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": repr(e)[:300]}
+
+
 def run_reference(args) -> dict | None:
+    """The reference arm.  The reference has no CPU implementation of the path (it is Triton / NVRTC only), so the
+    CPU figure is the numpy float32 matmul its tests check against; the reference's own GPU kernel, which is the
+    speed baseline its README implies, is reported beside it under `reference_triton` when it can run here."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
+    cores = _use_all_host_cores()
     from oracle import gemm_oracle as O
 
     a, b = _operands()
@@ -523,16 +699,19 @@ def run_reference(args) -> dict | None:
         O.matmul_f32(a_s, b)
     dt = (time.perf_counter() - t0) / args.steps
     value = round(flops / dt / 1e12, 4)
-    sample = f"numpy float32 A[:{CPU_SAMPLE_ROWS}] @ B of the 8192^3 operands per step ({flops / 1e9:.0f} GFLOP)"
-    return {
+    sample = f"numpy float32 A[:{CPU_SAMPLE_ROWS}] @ B of the 8192^3 operands per step ({flops / 1e9:.0f} GFLOP), {cores} BLAS threads"
+    out = {
         "impl": "reference", "metric": "gemm_tf32_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "fp32 GEMM sweep, M=N=K=8192, NN (CPU: bounded row slice of the same operands)"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": _blas_threads(), "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if not args.no_reference_gpu:
+        out["reference_triton"] = reference_triton_gemm()
+    return out
 
 
 def main():
@@ -549,6 +728,10 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="kernel-only timing of the whole config-1 GEMM sweep")
     ap.add_argument("--attn", action="store_true", help="kernel-only timing of the batched attention products (GB/s)")
     ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the GPT-2 training leg")
+    ap.add_argument("--no-reference-gpu", dest="no_reference_gpu", action="store_true",
+                    help="--impl reference: skip the reference's own Triton GEMM on the GPU")
+    ap.add_argument("--no-sustained", dest="no_sustained", action="store_true", help="skip the 4 s back-to-back leg")
+    ap.add_argument("--no-library-peak", dest="no_library_peak", action="store_true", help="skip the cuBLAS TF32 yardstick")
     args = ap.parse_args()
     if args.sweep:
         print(json.dumps(run_sweep(args)), flush=True)

@@ -9,12 +9,27 @@
 //     (gradtuity/dist/comm.py:129-131);
 //   * the 1/world_size scale is folded into the collective (ncclAvg) instead of a separate kernel
 //     (gradtuity/dist/ddp.py:94-97);
+//   * nothing on the host waits without a limit: communicator creation runs in a helper thread that the caller
+//     joins against a deadline, and a host-side wait polls the communication stream and
+//     ncclCommGetAsyncError against the same deadline (GRADTUITY_NCCL_TIMEOUT_S, default 120 s); when it runs
+//     out, or NCCL reports an asynchronous error (a peer that died), the communicator is aborted with
+//     ncclCommAbort, which also ends its kernels, and the call returns GT_ERR_TIMEOUT / GT_ERR_NCCL.  The
+//     communicator stays a blocking one: a non-blocking communicator hands every collective's launch to a
+//     background thread, which costs the overlap with backward the side stream exists for;
 //   * NCCL is opened with dlopen (GRADTUITY_NCCL_LIBRARY, default libnccl.so.2) with local symbol
 //     scope, so it never clashes with another NCCL copy in the process.
 // No kernel of this library reads a peer GPU's memory; inter-GPU traffic is NCCL's.
 
 #include <dlfcn.h>
+#include <sched.h>
 #include <stdlib.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <condition_variable>
+#include <memory>
+#include <mutex>
+#include <thread>
 
 #include "gt_internal.h"
 
@@ -22,7 +37,7 @@ namespace {
 
 typedef struct ncclComm* ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
-enum { ncclSuccess = 0 };
+enum { ncclSuccess = 0, ncclInProgress = 7 };
 enum { ncclFloat32 = 7 };
 enum { ncclSum = 0, ncclAvg = 4 };
 
@@ -34,6 +49,8 @@ struct NcclApi {
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
+  int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;      // optional (NCCL >= 2.4)
+  int (*CommAbort)(ncclComm_t) = nullptr;                    // optional
 };
 
 NcclApi g_nccl;
@@ -57,6 +74,8 @@ int load_nccl(char* err, size_t errlen) {
   GT_SYM(Broadcast, "ncclBroadcast");
   GT_SYM(GetErrorString, "ncclGetErrorString");
 #undef GT_SYM
+  *(void**)(&g_nccl.CommGetAsyncError) = dlsym(h, "ncclCommGetAsyncError");
+  *(void**)(&g_nccl.CommAbort) = dlsym(h, "ncclCommAbort");
   g_nccl.handle = h;
   return GT_OK;
 }
@@ -71,6 +90,53 @@ struct DistState {
 };
 
 DistState* g_dist[64] = {nullptr};
+
+double host_timeout_seconds() {
+  const char* v = getenv("GRADTUITY_NCCL_TIMEOUT_S");
+  const double t = v ? atof(v) : 0.0;
+  return t > 0.0 ? t : 120.0;
+}
+
+double seconds_since(std::chrono::steady_clock::time_point t0) {
+  return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+}
+
+void abort_comm(DistState* st) {
+  if (st->comm && g_nccl.CommAbort) g_nccl.CommAbort(st->comm);
+  st->comm = nullptr;
+}
+
+// Blocks the calling thread until the communication stream is idle, an asynchronous NCCL error shows up, or
+// the deadline passes.  Yields for the first couple of milliseconds (short collectives), then sleeps.
+int wait_for_stream(gt_ctx* ctx, DistState* st, const char* what) {
+  const auto t0 = std::chrono::steady_clock::now();
+  const double limit = host_timeout_seconds();
+  for (long long it = 0;; ++it) {
+    const cudaError_t q = cudaStreamQuery(st->stream);
+    if (q == cudaSuccess) return GT_OK;
+    if (q != cudaErrorNotReady) GT_CUDA_OK(ctx, q);
+    if (st->comm && g_nccl.CommGetAsyncError && (it & 63) == 0) {
+      int async_rc = ncclSuccess;
+      const int r = g_nccl.CommGetAsyncError(st->comm, &async_rc);
+      if (r != ncclSuccess || (async_rc != ncclSuccess && async_rc != ncclInProgress)) {
+        const int bad = r != ncclSuccess ? r : async_rc;
+        snprintf(ctx->last_error, sizeof(ctx->last_error), "%s: NCCL reported an asynchronous error (%s); communicator aborted", what,
+                 g_nccl.GetErrorString(bad));
+        abort_comm(st);
+        return GT_ERR_NCCL;
+      }
+    }
+    const double waited = seconds_since(t0);
+    if (waited > limit) {
+      snprintf(ctx->last_error, sizeof(ctx->last_error),
+               "%s: collectives still running after %.1f s (GRADTUITY_NCCL_TIMEOUT_S); a peer rank is probably gone; communicator aborted",
+               what, waited);
+      abort_comm(st);
+      return GT_ERR_TIMEOUT;
+    }
+    if (waited < 2e-3) sched_yield(); else usleep(100);
+  }
+}
 
 DistState* state_of(gt_ctx* ctx) { return (ctx && ctx->device >= 0 && ctx->device < 64) ? g_dist[ctx->device] : nullptr; }
 
@@ -107,11 +173,34 @@ extern "C" int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128
   st->rank = rank; st->world = world;
   ncclUniqueId id;
   memcpy(id.internal, uid128, 128);
-  int r = g_nccl.CommInitRank(&st->comm, world, id, rank);
-  if (r != ncclSuccess) {
-    snprintf(ctx->last_error, sizeof(ctx->last_error), "ncclCommInitRank(rank %d of %d): %s", rank, world, g_nccl.GetErrorString(r));
-    delete st;
-    return GT_ERR_NCCL;
+  // ncclCommInitRank blocks until every rank has called it.  It runs in a helper thread that is joined against
+  // a deadline, so a rank that never arrives gives an error here instead of a process that sits forever.
+  struct InitJob { std::mutex m; std::condition_variable cv; bool done = false; int rc = 0; ncclComm_t comm = nullptr; };
+  auto job = std::make_shared<InitJob>();
+  const int device = ctx->device;
+  std::thread([job, device, world, id, rank]() {
+    ncclComm_t c = nullptr;
+    int r = cudaSetDevice(device) == cudaSuccess ? g_nccl.CommInitRank(&c, world, id, rank) : -1;
+    std::lock_guard<std::mutex> lk(job->m);
+    job->rc = r; job->comm = c; job->done = true;
+    job->cv.notify_all();
+  }).detach();
+  {
+    std::unique_lock<std::mutex> lk(job->m);
+    const double limit = host_timeout_seconds();
+    if (!job->cv.wait_for(lk, std::chrono::duration<double>(limit), [&] { return job->done; })) {
+      snprintf(ctx->last_error, sizeof(ctx->last_error),
+               "ncclCommInitRank(rank %d of %d) did not complete within %.1f s (GRADTUITY_NCCL_TIMEOUT_S): a rank never joined", rank, world, limit);
+      delete st;
+      return GT_ERR_TIMEOUT;
+    }
+    if (job->rc != ncclSuccess) {
+      snprintf(ctx->last_error, sizeof(ctx->last_error), "ncclCommInitRank(rank %d of %d): %s", rank, world,
+               job->rc > 0 ? g_nccl.GetErrorString(job->rc) : "cudaSetDevice failed in the helper thread");
+      delete st;
+      return GT_ERR_NCCL;
+    }
+    st->comm = job->comm;
   }
   GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking));
   GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&st->ready, cudaEventDisableTiming));
@@ -123,7 +212,7 @@ extern "C" int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128
 extern "C" int gt_dist_destroy(gt_ctx* ctx) {
   DistState* st = state_of(ctx);
   if (!st) return GT_OK;
-  cudaStreamSynchronize(st->stream);
+  if (st->comm && wait_for_stream(ctx, st, "gt_dist_destroy") != GT_OK) cudaGetLastError();   // on failure the communicator is already aborted
   if (st->comm) g_nccl.CommDestroy(st->comm);
   cudaEventDestroy(st->ready);
   cudaEventDestroy(st->done);
@@ -140,6 +229,7 @@ extern "C" int gt_dist_allreduce(gt_ctx* ctx, float* ptr, int64_t count, int ave
   DistState* st = state_of(ctx);
   if (!ctx || !ptr || count <= 0) return GT_ERR_INVALID_ARG;
   if (!st) GT_FAIL(ctx, GT_ERR_NOT_INIT, "gt_dist_allreduce: process group not initialised");
+  if (!st->comm) GT_FAIL(ctx, GT_ERR_NCCL, "gt_dist_allreduce: the communicator was aborted after an error or a time-out");
   GT_CUDA_OK(ctx, cudaEventRecord(st->ready, ctx->stream));
   GT_CUDA_OK(ctx, cudaStreamWaitEvent(st->stream, st->ready, 0));
   GT_NCCL_OK(ctx, g_nccl.AllReduce(ptr, ptr, (size_t)count, ncclFloat32, average ? ncclAvg : ncclSum, st->comm, st->stream));
@@ -152,6 +242,7 @@ extern "C" int gt_dist_broadcast(gt_ctx* ctx, float* ptr, int64_t count, int roo
   if (!ctx || !ptr || count <= 0) return GT_ERR_INVALID_ARG;
   if (!st) GT_FAIL(ctx, GT_ERR_NOT_INIT, "gt_dist_broadcast: process group not initialised");
   if (root < 0 || root >= st->world) return GT_ERR_INVALID_ARG;
+  if (!st->comm) GT_FAIL(ctx, GT_ERR_NCCL, "gt_dist_broadcast: the communicator was aborted after an error or a time-out");
   GT_CUDA_OK(ctx, cudaEventRecord(st->ready, ctx->stream));
   GT_CUDA_OK(ctx, cudaStreamWaitEvent(st->stream, st->ready, 0));
   GT_NCCL_OK(ctx, g_nccl.Broadcast(ptr, ptr, (size_t)count, ncclFloat32, root, st->comm, st->stream));
@@ -170,7 +261,7 @@ extern "C" int gt_dist_wait(gt_ctx* ctx, int host_sync) {
     GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, st->done, 0));
     st->pending = 0;
   }
-  if (host_sync) GT_CUDA_OK(ctx, cudaStreamSynchronize(st->stream));
+  if (host_sync) return wait_for_stream(ctx, st, "gt_dist_wait");
   return GT_OK;
 }
 

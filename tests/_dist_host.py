@@ -97,3 +97,43 @@ class GlooBackend:
 
     def wait(self, host_sync=False):
         pass
+
+
+class HostArenaOps:
+    """Host stand-in for gradtuity_b200.dist.init_sync.DeviceArenaOps: parameters are FakeTensors whose
+    `_st` is a small storage record (ptr, nbytes, base), the arena a numpy array."""
+
+    class St:
+        def __init__(self, array, base=None):
+            self.array = array
+            self.ptr = array.ctypes.data
+            self.nbytes = array.nbytes
+            self.base = base
+            self.owns = base is None
+
+    def alloc(self, numel):
+        t = FakeTensor(np.zeros(numel, np.float32))
+        t._st = HostArenaOps.St(t.array)
+        return t
+
+    def copy(self, dst_ptr, src_ptr, nbytes):
+        ctypes.memmove(dst_ptr, src_ptr, nbytes)
+
+    def whole(self, base, numel):
+        t = FakeTensor.__new__(FakeTensor)
+        t.array = base.array[:numel]
+        t.requires_grad, t.grad, t._parents, t._st = False, None, (), base
+        return t
+
+    def rebind(self, t, arena, offset_elems):
+        n = t.numel
+        shape = t.shape
+        t.array = arena.array[offset_elems:offset_elems + n].reshape(shape)
+        t._st = HostArenaOps.St(t.array, base=arena._st)
+
+
+def host_param(array, base=None):
+    """A FakeTensor parameter with a storage record, optionally a view into `base` (another host_param's storage)."""
+    t = FakeTensor(array, requires_grad=True)
+    t._st = HostArenaOps.St(t.array, base=base)
+    return t

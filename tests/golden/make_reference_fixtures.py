@@ -251,7 +251,12 @@ def cmd_gemm(args) -> None:
             ms_ours = time_ours(lambda: ours(_lib.PREC_TF32, t_ours), 50)
             rec.update({"reference_triton_ms": ms_ref, "reference_triton_tflops": flops / ms_ref / 1e9, "reference_iters": iters,
                         "ours_tf32_ms": ms_ours, "ours_tf32_tflops": flops / ms_ours / 1e9, "speedup": ms_ref / ms_ours})
-        if save:
+        if save == "outputs":          # inputs come from a seed the test repeats; keep the first rows of wide outputs
+            keep = 32 if c_ref.size > 128 * 128 else c_ref.shape[0]
+            saved[tag + "/ref_triton"] = c_ref[:keep]
+            if tag + "/ref_cuda" in saved:
+                saved[tag + "/ref_cuda"] = saved[tag + "/ref_cuda"][:keep]
+        elif save:
             saved[tag + "/a"], saved[tag + "/b"], saved[tag + "/ref_triton"] = a, b, c_ref
             if bias is not None:
                 saved[tag + "/bias"] = bias
@@ -279,9 +284,9 @@ def cmd_gemm(args) -> None:
     w = rng.uniform(-1 / 28, 1 / 28, (784, 128)).astype(np.float32)
     bvec = rng.uniform(-1 / 28, 1 / 28, (128,)).astype(np.float32)
     dy = rng.standard_normal((128, 128)).astype(np.float32)
-    one_case("config0_y", "nn", 128, 128, 784, x, w, kind="bias", bias=bvec, save=True, cuda_too=True)
-    one_case("config0_dx", "nt", 128, 784, 128, dy, w, c0=np.zeros((128, 784), np.float32), save=True, cuda_too=True)
-    one_case("config0_dw", "tn", 784, 128, 128, x, dy, c0=np.zeros((784, 128), np.float32), save=True, cuda_too=True)
+    one_case("config0_y", "nn", 128, 128, 784, x, w, kind="bias", bias=bvec, save="outputs", cuda_too=True)
+    one_case("config0_dx", "nt", 128, 784, 128, dy, w, c0=np.zeros((128, 784), np.float32), save="outputs", cuda_too=True)
+    one_case("config0_dw", "tn", 784, 128, 128, x, dy, c0=np.zeros((784, 128), np.float32), save="outputs", cuda_too=True)
     np.savez_compressed(os.path.join(args.out, "reference_gemm_outputs.npz"), **saved)
 
     # 3. config 1: the sweep shapes, three layouts, operands ~ N(0, 1/sqrt(K)), seed 1
@@ -344,7 +349,8 @@ def cmd_train(args) -> None:
                                                   "n_head": args.n_head, "lr": args.lr, "weight_decay": args.weight_decay, "max_norm": args.max_norm,
                                                   "dropout": 0.0, "weights": "numpy default_rng(3): matrices N(0, 0.02), gamma 1, vectors 0",
                                                   "tokens": "numpy default_rng((3, step, 0)).integers(0, V, (B, S + 1))"},
-           "backend": os.environ["GRADTUITY_KERNEL_BACKEND"], "parameters": n_params, "loss": [], "ms_per_step": []}
+           "backend": os.environ["GRADTUITY_KERNEL_BACKEND"], "parameters": n_params,
+           "param_shapes": {k: list(state[k].shape) for k in sorted(state) if not k.startswith("lm_head.")}, "loss": [], "ms_per_step": []}
     os.makedirs(args.out, exist_ok=True)
     path = os.path.join(args.out, args.name)
     for step in range(args.steps):

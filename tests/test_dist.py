@@ -164,6 +164,44 @@ def test_two_ranks_accumulate_two_backwards_then_sync_over_gloo():
     assert r.returncode == 0, r.stderr[-3000:]
 
 
+def test_parameters_move_into_one_arena_and_travel_in_one_broadcast(monkeypatch):
+    """init_sync: strict signature check, then ONE broadcast over a flat arena that holds every parameter;
+    tensors that shared an allocation before (packed q/k/v weights) stay adjacent; a second call reuses the arena."""
+    import importlib
+
+    from tests._dist_host import HostArenaOps, host_param
+
+    isync = importlib.import_module("gradtuity_b200.dist.init_sync")      # the package re-exports the function under this name
+
+    monkeypatch.setenv("RANK", "0"); monkeypatch.setenv("WORLD_SIZE", "2"); monkeypatch.setenv("LOCAL_RANK", "0")
+    rng = np.random.default_rng(0)
+    block = host_param(rng.standard_normal(3 * 64))                      # one allocation holding q, k, v
+    q, k, v = (host_param(block.array[i * 64:(i + 1) * 64], base=block._st) for i in range(3))
+    a, o, b = host_param(rng.standard_normal((5, 3))), host_param(rng.standard_normal(70)), host_param(rng.standard_normal(2))
+    params = [a, k, o, q, v, b]                                          # sorted-name order separates q, k, v
+    before = [p.array.copy() for p in params]
+    order, offsets, total = isync.arena_layout(params)
+    assert [params[j] for j in order] == [a, q, k, v, o, b]
+    assert offsets == [0, 64, 128, 192, 256, 384] and total == 448
+    arena = isync.flatten_parameters(params, mem=HostArenaOps())
+    for p, want in zip(params, before):
+        np.testing.assert_array_equal(p.array, want)                     # values and shapes survive the move
+        assert p._st.base is arena._st
+    assert k.ptr - q.ptr == 64 * 4 and v.ptr - k.ptr == 64 * 4          # still side by side
+    again = isync.flatten_parameters(params, mem=HostArenaOps())
+    assert again.ptr == arena.ptr and again.numel == total                # recognised, not copied again
+
+    class Bcast(RecordingBackend):
+        def broadcast(self, ptr, numel, src):
+            self.calls.append(("bcast", ptr, numel, src))
+
+    be = Bcast()
+    comm.set_backend(be)
+    monkeypatch.setattr(isync, "_arena_ops", HostArenaOps())
+    isync.init_sync(params, strict=False)
+    assert be.calls == [("bcast", arena.ptr, total, 0)]                   # one collective for all six tensors
+
+
 def test_rendezvous_times_out_with_a_diagnostic(tmp_path):
     with pytest.raises(RuntimeError, match="did not reach 128 bytes"):
         comm.exchange_unique_id(1, None, str(tmp_path / "never.bin"), timeout=0.2)

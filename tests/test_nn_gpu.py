@@ -105,8 +105,8 @@ def test_causal_attention_products(T, B, H, S, D):
     ref = O.attention_forward_backward(heads(q), heads(k), heads(v), heads(do))
     assert rel(o.numpy(), merge(ref["o"])) < 1e-3
     o.mul(T.from_numpy(do)).sum().backward()
-    assert rel(tq.grad.numpy(), merge(ref["dq"])) < 2e-3
-    assert rel(tk.grad.numpy(), merge(ref["dk"])) < 2e-3
+    assert rel(tq.grad.numpy(), merge(ref["dq"])) < 1e-3
+    assert rel(tk.grad.numpy(), merge(ref["dk"])) < 1e-3
     assert rel(tv.grad.numpy(), merge(ref["dv"])) < 1e-3
 
 
@@ -130,8 +130,8 @@ def test_config2_full_size_attention_sampled_heads(T, mode, monkeypatch):
         ref = O.attention_forward_backward(pick(q), pick(k), pick(v), pick(do))
         assert rel(pick(on), ref["o"]) < 1e-3
         assert rel(pick(dvn), ref["dv"]) < 1e-3
-        assert rel(pick(dqn), ref["dq"]) < 2e-3
-        assert rel(pick(dkn), ref["dk"]) < 2e-3
+        assert rel(pick(dqn), ref["dq"]) < 1e-3
+        assert rel(pick(dkn), ref["dk"]) < 1e-3
 
 
 def test_attention_module_matches_unfused_reference_formulation(T):
@@ -202,7 +202,7 @@ def test_tiny_gpt2_training_tracks_the_float64_oracle(T, precision, monkeypatch)
     from gradtuity_b200.optim import AdamW, clip_grad_norm_
 
     monkeypatch.setenv("GRADTUITY_GEMM_PRECISION", precision)
-    tol_g, tol_curve = (5e-3, 1e-3) if precision == "tf32" else (1e-4, 1e-4)
+    tol_g, tol_curve = (1e-3, 1e-3) if precision == "tf32" else (1e-4, 1e-4)
     rng = np.random.default_rng(3)
     V, S, E, H, L, B = 257, 64, 64, 2, 2, 4
     p0 = _tiny_params(rng, V, S, E, L)
