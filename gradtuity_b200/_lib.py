@@ -131,6 +131,7 @@ SIGNATURES = {
     "gt_dist_broadcast": (c_int, [c_void_p, c_void_p, c_int64, c_int]),
     "gt_dist_wait": (c_int, [c_void_p, c_int]),
     "gt_dist_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int)]),
+    "gt_dist_timeline": (c_int, [c_void_p, POINTER(c_float), c_int, POINTER(c_int)]),
     "gt_adamw_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_float, c_float, c_float, c_float,
                                c_float, c_float, c_void_p]),
     "gt_sumsq_multi": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64]),

@@ -87,6 +87,14 @@ struct DistState {
   cudaEvent_t done = nullptr;        // comm -> compute: "the collective has finished"
   int rank = 0, world = 1;
   int pending = 0;                   // collectives enqueued since the last wait
+  // optional per-step timeline (GRADTUITY_DIST_TIMELINE=1): timed events around every collective since the last wait
+  bool timeline = false;
+  static constexpr int TL_MAX = 64;
+  int tl_n = 0;
+  long long tl_count[TL_MAX];
+  cudaEvent_t tl_ready[TL_MAX], tl_start[TL_MAX], tl_end[TL_MAX];   // compute stream; comm stream before / after
+  cudaEvent_t tl_resume = nullptr;   // compute stream, right after it was made to wait for the collectives
+  bool tl_closed = false;
 };
 
 DistState* g_dist[64] = {nullptr};
@@ -205,6 +213,16 @@ extern "C" int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128
   GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&st->stream, cudaStreamNonBlocking));
   GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&st->ready, cudaEventDisableTiming));
   GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&st->done, cudaEventDisableTiming));
+  const char* tl = getenv("GRADTUITY_DIST_TIMELINE");
+  if (tl && tl[0] == '1') {
+    st->timeline = true;
+    for (int i = 0; i < DistState::TL_MAX; ++i) {
+      GT_CUDA_OK(ctx, cudaEventCreate(&st->tl_ready[i]));
+      GT_CUDA_OK(ctx, cudaEventCreate(&st->tl_start[i]));
+      GT_CUDA_OK(ctx, cudaEventCreate(&st->tl_end[i]));
+    }
+    GT_CUDA_OK(ctx, cudaEventCreate(&st->tl_resume));
+  }
   g_dist[ctx->device] = st;
   return GT_OK;
 }
@@ -232,7 +250,18 @@ extern "C" int gt_dist_allreduce(gt_ctx* ctx, float* ptr, int64_t count, int ave
   if (!st->comm) GT_FAIL(ctx, GT_ERR_NCCL, "gt_dist_allreduce: the communicator was aborted after an error or a time-out");
   GT_CUDA_OK(ctx, cudaEventRecord(st->ready, ctx->stream));
   GT_CUDA_OK(ctx, cudaStreamWaitEvent(st->stream, st->ready, 0));
+  int slot = -1;
+  if (st->timeline) {
+    if (st->tl_closed) { st->tl_n = 0; st->tl_closed = false; }       // first collective after a wait: a new window
+    if (st->tl_n < DistState::TL_MAX) {
+      slot = st->tl_n++;
+      st->tl_count[slot] = count;
+      GT_CUDA_OK(ctx, cudaEventRecord(st->tl_ready[slot], ctx->stream));
+      GT_CUDA_OK(ctx, cudaEventRecord(st->tl_start[slot], st->stream));
+    }
+  }
   GT_NCCL_OK(ctx, g_nccl.AllReduce(ptr, ptr, (size_t)count, ncclFloat32, average ? ncclAvg : ncclSum, st->comm, st->stream));
+  if (slot >= 0) GT_CUDA_OK(ctx, cudaEventRecord(st->tl_end[slot], st->stream));
   st->pending += 1;
   return GT_OK;
 }
@@ -260,8 +289,43 @@ extern "C" int gt_dist_wait(gt_ctx* ctx, int host_sync) {
     GT_CUDA_OK(ctx, cudaEventRecord(st->done, st->stream));
     GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, st->done, 0));
     st->pending = 0;
+    if (st->timeline && !st->tl_closed && st->tl_n > 0) {
+      GT_CUDA_OK(ctx, cudaEventRecord(st->tl_resume, ctx->stream));
+      st->tl_closed = true;
+    }
   }
   if (host_sync) return wait_for_stream(ctx, st, "gt_dist_wait");
+  return GT_OK;
+}
+
+// Timeline of the collectives between the last two waits (only with GRADTUITY_DIST_TIMELINE=1 at init; else *n = 0).
+// Row i of `out` (4 floats): element count, then milliseconds relative to the first collective's enqueue point
+// on the compute stream: when the compute stream reached collective i's enqueue point, when the communication
+// stream started it, when it finished.  One more row at the end: (0, time the compute stream resumed after the
+// wait, 0, 0).  Synchronises both streams.  Measurement aid; the reference has no counterpart.
+extern "C" int gt_dist_timeline(gt_ctx* ctx, float* out, int max_rows, int* n) {
+  DistState* st = state_of(ctx);
+  if (!ctx || !out || !n || max_rows < 0) return GT_ERR_INVALID_ARG;
+  *n = 0;
+  if (!st || !st->timeline || !st->tl_closed || st->tl_n == 0) return GT_OK;
+  GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+  int rc = wait_for_stream(ctx, st, "gt_dist_timeline");
+  if (rc != GT_OK) return rc;
+  int rows = 0;
+  for (int i = 0; i < st->tl_n && rows < max_rows; ++i, ++rows) {
+    float a = 0, b = 0, c = 0;
+    GT_CUDA_OK(ctx, cudaEventElapsedTime(&a, st->tl_ready[0], st->tl_ready[i]));
+    GT_CUDA_OK(ctx, cudaEventElapsedTime(&b, st->tl_ready[0], st->tl_start[i]));
+    GT_CUDA_OK(ctx, cudaEventElapsedTime(&c, st->tl_ready[0], st->tl_end[i]));
+    out[4 * rows] = (float)st->tl_count[i]; out[4 * rows + 1] = a; out[4 * rows + 2] = b; out[4 * rows + 3] = c;
+  }
+  if (rows < max_rows) {
+    float r = 0;
+    GT_CUDA_OK(ctx, cudaEventElapsedTime(&r, st->tl_ready[0], st->tl_resume));
+    out[4 * rows] = 0; out[4 * rows + 1] = r; out[4 * rows + 2] = 0; out[4 * rows + 3] = 0;
+    ++rows;
+  }
+  *n = rows;
   return GT_OK;
 }
 

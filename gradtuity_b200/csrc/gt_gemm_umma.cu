@@ -960,6 +960,225 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   }
 }
 
+// ---- 256 x 256 tiles held by a CTA PAIR (tcgen05 cta_group::2) -------------------------------------
+// Two CTAs of a cluster, on two SMs, share one 256 x 256 output tile.  Each CTA loads its own half of both
+// operands into its own shared memory (rows m0 + 128 r of A, columns n0 + 128 r of B for the CTA of rank r:
+// 16 KB + 16 KB per k-block, straight from this GPU's memory, no multicast) and holds the accumulator of its
+// own 128 rows (128 tensor-memory lanes x 256 columns).  One thread of the leader CTA (rank 0) issues
+// tcgen05.mma.cta_group::2 for both: the tensor cores of the two SMs read A from their own CTA and B from both.
+// Per SM that is 32 KB of operands per k-block for a 128 x 256 x 32 product: the 64 bytes per cycle the
+// SM's L2 path sustains, where a single CTA's 128 x 256 tile needs 96.  Against the one-CTA 256 x 256 kernel
+// above the stage is half as large (six stages instead of three) and the accumulator only half of tensor
+// memory, so it is double-buffered and a tile's epilogue overlaps the next main loop, which is what the
+// short-K (768) GEMMs of the GPT-2 step need.
+//   barriers (all in shared memory, "leader's" = the copy in the CTA of rank 0):
+//     full[s]   leader's only: one arrive.expect_tx by the leader's producer for the bytes of BOTH CTAs; all four
+//               TMA loads of a k-block (two per CTA) complete on it
+//     empty[s]  one per CTA: the leader's MMA thread commits to its own and to the peer's
+//     tfull[a]  one per CTA, same; tempty[a] leader's only: one arrival per epilogue warp of either CTA
+// Every wait is bounded as elsewhere; the CTAs leave together through a cluster barrier, so neither frees
+// shared or tensor memory the other may still touch.
+constexpr int PAIR_STAGE_BYTES = 32768;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_THREADS = 320;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 512 + EPI_SCRATCH_BYTES;
+static_assert(PAIR_SMEM_BYTES <= 232448, "CTA-pair kernel exceeds the 227 KB of shared memory a CTA may use");
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_c, const UmmaParams p) {
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int TM = 256, TN = 256, HALF = 128;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint8_t* epi_scratch = smem_aligned + STAGES * PAIR_STAGE_BYTES;
+  uint8_t* ctrl = epi_scratch + EPI_SCRATCH_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ctrl);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 8 * (2 * MAX_STAGES + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * MAX_STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * MAX_STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  const uint32_t bar_drain = bar_tempty + 16;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();                 // 0: leader
+  const bool cta_wait = (p.flags & (1 << 30)) != 0;        // tuning aid: CTA-scope waits where no generic-proxy data crosses CTAs
+  auto wait_x = [&](uint32_t bar, uint32_t parity) -> bool {
+    return cta_wait ? mbar_wait(bar, parity, abort_flag, p.status) : mbar_wait_cluster(bar, parity, abort_flag, p.status);
+  };
+  const int first_unit = (int)cluster_id_x(), unit_step = (int)nclusters_x();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 16); }   // 8 epilogue warps x 2 CTAs
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {      // the same warp in both CTAs, with the same destination slot
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncwarp();
+  cluster_sync_all();                    // both CTAs' barriers exist before either signals the other's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const uint32_t leader_full = map_to_cta(bar_full, 0);
+  const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
+
+  if (warp == 0) {
+    // ------------------------------ producer (one per CTA) ------------------------------
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int unit = first_unit; ok && unit < p.num_tiles; unit += unit_step) {
+        int batch, tm, tn, ks;
+        tile_coords(p, unit, batch, tm, tn, ks);
+        const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+        const int m0 = tm * TM + (int)rank * HALF, n0 = tn * TN + (int)rank * HALF;     // this CTA's halves
+        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!wait_x(bar_empty + 8 * s, ph ^ 1u)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * PAIR_STAGE_BYTES);
+          const uint32_t full = leader_full + 8 * s;
+          const uint32_t sa = smem_base + s * PAIR_STAGE_BYTES;
+          const uint32_t sb = sa + HALF * BK * 4;
+          const int k0 = kb * BK;
+          if (A_MN) {
+            if (p.a_onebox) tma_load_5d_pair(sa, &map_a, full, 0, k0, m0 >> 5, i0, i1);
+            else {
+#pragma unroll
+              for (int j = 0; j < HALF / 32; ++j) tma_load_4d_pair(sa + j * 4096, &map_a, full, m0 + 32 * j, k0, i0, i1);
+            }
+          } else {
+            tma_load_4d_pair(sa, &map_a, full, k0, m0, i0, i1);                 // one 32 x 128 box
+          }
+          if (B_MN) {
+            if (p.b_onebox) tma_load_5d_pair(sb, &map_b, full, 0, k0, n0 >> 5, i0, i1);
+            else {
+#pragma unroll
+              for (int j = 0; j < HALF / 32; ++j) tma_load_4d_pair(sb + j * 4096, &map_b, full, n0 + 32 * j, k0, i0, i1);
+            }
+          } else {
+            tma_load_4d_pair(sb, &map_b, full, k0, n0, i0, i1);
+          }
+          ++issued;
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (!ok && rank == 0) {
+        // Aborting: the loads already issued (by either CTA) complete on these barriers; give them time to land.
+        long long first = issued > STAGES ? issued - STAGES : 0;
+        for (long long i = first; i < issued; ++i) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar_full + 8 * (int)(i % STAGES), (uint32_t)((i / STAGES) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_pair(TN, A_MN, B_MN);
+      const uint32_t peer_empty = map_to_cta(bar_empty, 1), peer_tfull = map_to_cta(bar_tfull, 1);
+      const uint32_t own_empty = map_to_cta(bar_empty, 0), own_tfull = map_to_cta(bar_tfull, 0);
+      int s = 0; uint32_t ph = 0;
+      int acc = 0; uint32_t aph = 0;
+      bool ok = true, any_issued = false;
+      for (int unit = first_unit; ok && unit < p.num_tiles; unit += unit_step) {
+        const int ks = unit % p.ksplit;
+        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+        if (!mbar_wait_cluster(bar_tempty + 8 * acc, aph ^ 1u, abort_flag, p.status)) { ok = false; break; }   // both CTAs drained it
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+          if (!wait_x(bar_full + 8 * s, ph)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * PAIR_STAGE_BYTES;
+          const uint32_t sb = sa + HALF * BK * 4;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint32_t a_off = A_MN ? kk * 1024 : kk * 32;
+            const uint32_t b_off = B_MN ? kk * 1024 : kk * 32;
+            const uint64_t ad = make_smem_desc(sa + a_off, A_MN ? 4096 : 16, A_MN ? 512 : 1024, A_MN ? 1 : 2);
+            const uint64_t bd = make_smem_desc(sb + b_off, B_MN ? 4096 : 16, B_MN ? 512 : 1024, B_MN ? 1 : 2);
+            tc_mma_tf32_pair(d_tmem, ad, bd, idesc, (kb != kb_lo || kk != 0) ? 1u : 0u);
+          }
+          any_issued = true;
+          tc_commit_pair(own_empty + 8 * s);          // both CTAs may refill the stage once these MMAs have read it
+          tc_commit_pair(peer_empty + 8 * s);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair(own_tfull + 8 * acc);          // both halves of the accumulator are complete
+        tc_commit_pair(peer_tfull + 8 * acc);
+        if (++acc == 2) { acc = 0; aph ^= 1u; }
+      }
+      if (!ok && any_issued) {
+        tc_commit_pair(map_to_cta(bar_drain, 0));
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (eight warps per CTA, its own 128 rows) ------------------------------
+    const int q = warp & 3;
+    const int eset = (warp - 2) >> 2;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    uint8_t* epi_bytes = epi_scratch + (warp - 2) * EPI_WARP_BYTES;
+    const uint32_t epi_u32 = smem_u32(epi_bytes);
+    int acc = 0; uint32_t aph = 0;
+    for (int unit = first_unit; unit < p.num_tiles; unit += unit_step) {
+      int batch, tm, tn, ks;
+      tile_coords(p, unit, batch, tm, tn, ks);
+      const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+      const int row0 = tm * TM + (int)rank * HALF + q * 32;
+      const int row = row0 + lane;
+      const int n0 = tn * TN;
+      const long long batch_off = (long long)i0 * p.sC0 + (long long)i1 * p.sC1;
+      const long long row_off = batch_off + (long long)row * p.ldc;
+      const bool row_ok = row < p.M;
+      const float* unit_bias = p.bias ? p.bias + (long long)batch * p.bias_stride : nullptr;
+      // with split-K every share adds its partial sum into C; bias / residual go in with share 0
+      const int unit_epi = (p.ksplit > 1 && ks > 0) ? (int)GT_EPI_NONE : p.epilogue;
+      const bool unit_add = p.accumulate != 0 || p.ksplit > 1;
+      if (!wait_x(bar_tfull + 8 * acc, aph)) break;
+      tc_fence_after();
+      if (row0 < p.M) {                       // warp-uniform: a 32-row block wholly below M has nothing to write
+#pragma unroll 1
+        for (int c = eset; c < TN / 32; c += 2) {
+          const int nb = n0 + c * 32;
+          if (nb >= p.N) break;
+          float v[32];
+          tc_ld32(lane_base + (uint32_t)(acc * TN + c * 32), v);
+          tc_wait_ld();
+          epilogue_chunk_tma(p, unit_bias, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, unit_epi, unit_add);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * acc);      // this warp is done with the accumulator
+      if (++acc == 2) { acc = 0; aph ^= 1u; }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  tc_fence_before();
+  __syncwarp();                          // the cluster barrier is a warp-wide instruction: lanes that skipped a role loop rejoin here
+  cluster_sync_all();                    // nobody leaves while the peer may still signal or read this CTA
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // ---- operand splitting for 3xTF32 ---------------------------------------------------------
 // hi keeps the 19 bits a tf32 operand carries (sign, exponent, 10 mantissa bits), lo = x - hi
 // is exact in fp32.  Rows of `cols` elements with pitch `ld` are packed at pitch `cols_pad`.
@@ -1055,6 +1274,68 @@ int launch_layout(gt_ctx* ctx, int layout, const CUtensorMap maps[5], const Umma
   return GT_ERR_INVALID_ARG;
 }
 
+// ---- CTA-pair kernel: launch as clusters of two ---------------------------------------------------
+template <class Kern>
+void pair_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int clusters, cudaStream_t stream) {
+  memset(cfg, 0, sizeof(*cfg));
+  cfg->gridDim = dim3(2u * (unsigned)clusters, 1, 1);
+  cfg->blockDim = dim3(PAIR_THREADS, 1, 1);
+  cfg->dynamicSmemBytes = PAIR_SMEM_BYTES;
+  cfg->stream = stream;
+  attr->id = cudaLaunchAttributeClusterDimension;
+  attr->val.clusterDim.x = 2; attr->val.clusterDim.y = 1; attr->val.clusterDim.z = 1;
+  cfg->attrs = attr;
+  cfg->numAttrs = 1;
+}
+
+template <class Kern>
+int pair_launch(gt_ctx* ctx, Kern kern, int clusters, cudaStream_t stream, const CUtensorMap maps[5], const UmmaParams& p) {
+  GT_SMEM_OPT_IN(ctx, kern, PAIR_SMEM_BYTES);
+  cudaLaunchConfig_t cfg; cudaLaunchAttribute attr;
+  pair_launch_config<Kern>(&cfg, &attr, clusters, stream);
+  GT_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[4], p));
+  ctx->launches += 1;
+  return GT_OK;
+}
+
+// How many two-CTA clusters of the pair kernel the device can hold at once (each CTA takes a whole SM, and a
+// cluster needs two free SMs of one GPC, so this can be less than half the SM count).  Asked once per device
+// and layout; 0 when the query fails, which turns the pair kernel off.
+template <class Kern>
+int pair_clusters_query(gt_ctx* ctx, Kern kern) {
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return 0; }
+  cudaLaunchConfig_t cfg; cudaLaunchAttribute attr;
+  pair_launch_config<Kern>(&cfg, &attr, ctx->sm_count / 2, ctx->stream);
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+  return n;
+}
+
+int pair_max_clusters(gt_ctx* ctx, int layout) {
+  static int cached[64][3];
+  static bool known[64][3];
+  if (ctx->device < 0 || ctx->device >= 64 || layout < 0 || layout > 2) return 0;
+  if (!known[ctx->device][layout]) {
+    int n = 0;
+    if (layout == GT_LAYOUT_NN) n = pair_clusters_query(ctx, gt_gemm_pair_kernel<false, true>);
+    else if (layout == GT_LAYOUT_NT) n = pair_clusters_query(ctx, gt_gemm_pair_kernel<false, false>);
+    else n = pair_clusters_query(ctx, gt_gemm_pair_kernel<true, true>);
+    cached[ctx->device][layout] = n;
+    known[ctx->device][layout] = true;
+  }
+  return cached[ctx->device][layout];
+}
+
+// When the pair kernel is taken without being forced: problems with at least a 256 x 256 output whose
+// 256 x 256 tiles (times a possible K split) can keep most pairs busy.
+bool pair_rule(const gt_gemm_args& g, long long tiles256, int clusters, int sms) {
+  (void)sms;
+  if (g.M < 256 || g.N < 256 || g.K < 256) return false;
+  const long long kb = (g.K + BK - 1) / BK;
+  const long long shares = kb / 16 > 8 ? 8 : (kb / 16 < 1 ? 1 : kb / 16);      // what split-K could add
+  return tiles256 * shares * 4 >= (long long)clusters * 3;
+}
+
 int pick_bn(const gt_gemm_args& g, int sms, bool x3, bool a_gen) {
   if (g.N <= 64) return 64;
   if (g.N <= 128) return 128;
@@ -1094,7 +1375,7 @@ bool gt_gemm_umma_eligible(const gt_gemm_args& g) {
 // fixed_scratch: when non-null, the 3xTF32 operand split goes there (capacity
 // fixed_scratch_floats) instead of into the context's growable workspace.
 static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream,
-                            float* fixed_scratch, size_t fixed_scratch_floats) {
+                            float* fixed_scratch, size_t fixed_scratch_floats, bool allow_pair = true) {
   const bool x3 = g.precision == GT_PREC_TF32X3;
   const bool a_mn = g.layout == GT_LAYOUT_TN;
   const bool b_mn = g.layout != GT_LAYOUT_NT;
@@ -1113,9 +1394,20 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
                                              : ((g.K >= t256_min_k && tiles256 * 5 >= (long long)ctx->sm_count * 3) ||
                                                 (g.K >= 512 && tiles256 >= (long long)ctx->sm_count * 8 && !g.aux));
   const int hints = g.flags & (GT_GEMM_A_LOWER | GT_GEMM_AT_LOWER | GT_GEMM_CAUSAL_SKIP_MASKED);
-  const bool use256 = !t256_off && hints == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && big_enough &&
+  bool use256 = !t256_off && hints == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL && big_enough &&
                       tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (!g.aux || ((uintptr_t)g.aux & 15) == 0) &&
                       (!g.bias || ((uintptr_t)g.bias & 15) == 0);
+  // CTA pairs (256 x 256 tile over two SMs).  GRADTUITY_GEMM_PAIR: 0 = never, 1 = whenever the kernel can serve
+  // the problem, unset = the rule below.
+  static const int pair_mode = getenv("GRADTUITY_GEMM_PAIR") ? atoi(getenv("GRADTUITY_GEMM_PAIR")) : 0;
+  const int pair_clusters = (allow_pair && pair_mode != 0) ? pair_max_clusters(ctx, g.layout) : 0;
+  const bool pair_can = pair_clusters > 0 && hints == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL &&
+                        getenv("GRADTUITY_GEMM_NO_TMA_STORE") == nullptr &&
+                        tma_ok(g.C, g.ldc, g.sC0, g.sC1, g.batch0, g.batch1) && (!g.aux || ((uintptr_t)g.aux & 15) == 0) &&
+                        (!g.bias || ((uintptr_t)g.bias & 15) == 0);
+  const bool pair = pair_can && (pair_mode == 1 || pair_rule(g, tiles256, pair_clusters, ctx->sm_count));
+  if (pair) use256 = true;
+  const int workers = pair ? pair_clusters : ctx->sm_count;      // tiles that are worked on at the same time
   static const int force_bn = getenv("GRADTUITY_GEMM_FORCE_BN") ? atoi(getenv("GRADTUITY_GEMM_FORCE_BN")) : 0;   // tuning aid
   int bn = use256 ? 256 : pick_bn(g, ctx->sm_count, x3, a_gen);
   if (!use256 && (force_bn == 64 || force_bn == 128 || (force_bn == 256 && !x3)) && g.N > force_bn / 2) bn = force_bn;
@@ -1162,15 +1454,17 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     vb_lo = vb; vb_lo.ptr = b_lo;
   }
 
-  const int a_box_c = 32, a_box_r = a_mn ? 32 : tile_m;
-  const int b_box_c = 32, b_box_r = b_mn ? 32 : bn;
+  // rows of one TMA box: a whole tile side, or the half one CTA of a pair loads
+  const int a_side = pair ? 128 : tile_m, b_side = pair ? 128 : bn;
+  const int a_box_c = 32, a_box_r = a_mn ? 32 : a_side;
+  const int b_box_c = 32, b_box_r = b_mn ? 32 : b_side;
   int rc;
   static const bool onebox_off = getenv("GRADTUITY_GEMM_NO_ONEBOX") != nullptr;
   // one-box form for MN-major operands whose MN extent is a multiple of 32 (else a box would run past a row's end)
   bool a_one = !onebox_off && a_mn && !a_gen && (va.cols % 32 == 0);
   bool b_one = !onebox_off && b_mn && (vb.cols % 32 == 0);
-  if (a_one) a_one = encode_map_mn5(ctx, &maps[0], va, tile_m / 32, b0, b1) && (!x3 || encode_map_mn5(ctx, &maps[2], va_lo, tile_m / 32, b0, b1));
-  if (b_one) b_one = encode_map_mn5(ctx, &maps[1], vb, bn / 32, b0, b1) && (!x3 || encode_map_mn5(ctx, &maps[3], vb_lo, bn / 32, b0, b1));
+  if (a_one) a_one = encode_map_mn5(ctx, &maps[0], va, a_side / 32, b0, b1) && (!x3 || encode_map_mn5(ctx, &maps[2], va_lo, a_side / 32, b0, b1));
+  if (b_one) b_one = encode_map_mn5(ctx, &maps[1], vb, b_side / 32, b0, b1) && (!x3 || encode_map_mn5(ctx, &maps[3], vb_lo, b_side / 32, b0, b1));
   if (!b_one && (rc = encode_map(ctx, &maps[1], vb, b_box_c, b_box_r, b0, b1, b_mn)) != GT_OK) return rc;
   if (a_gen) maps[0] = maps[1];               // unused by the kernel in this mode
   else if (!a_one && (rc = encode_map(ctx, &maps[0], va, a_box_c, a_box_r, b0, b1, a_mn)) != GT_OK) return rc;
@@ -1205,8 +1499,8 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   //    cannot be described to TMA.
   const int num_kb = (int)((g.K + BK - 1) / BK);
   int ksplit = 1;
-  if (!x3 && g.epilogue < GT_EPI_CAUSAL && hints == 0 && tiles * 2 <= ctx->sm_count && num_kb >= 32) {
-    ksplit = (int)(ctx->sm_count / tiles);
+  if (!x3 && g.epilogue < GT_EPI_CAUSAL && hints == 0 && tiles * 2 <= workers && num_kb >= 32) {
+    ksplit = (int)(workers / tiles);
     if (ksplit > num_kb / 8) ksplit = num_kb / 8;
     if (ksplit > 32) ksplit = 32;
     if (ksplit < 1) ksplit = 1;
@@ -1216,10 +1510,10 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   // first unless the call is C += ...), bias / residual with share 0.
   static const bool deterministic256 = getenv("GRADTUITY_GEMM_DETERMINISTIC") != nullptr;
   bool split256 = false;
-  if (use256 && !deterministic256 && tiles < ctx->sm_count && nbatch == 1 && g.ldc == g.N &&
+  if (use256 && !deterministic256 && tiles < workers && nbatch == 1 && g.ldc == g.N &&
       (g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS || g.epilogue == GT_EPI_BIAS_ADD) &&
       (g.epilogue == GT_EPI_BIAS_ADD || !g.aux) && getenv("GRADTUITY_GEMM_NO_TMA_STORE") == nullptr) {
-    int want = (int)((2LL * ctx->sm_count) / tiles);
+    int want = (int)((2LL * workers) / tiles);
     if (want > num_kb / 16) want = num_kb / 16;
     if (want > 8) want = 8;
     if (want >= 2) { ksplit = want; split256 = true; }
@@ -1232,6 +1526,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   p.epilogue = g.epilogue; p.accumulate = g.accumulate;
   p.alpha = g.alpha;
   p.flags = g.flags;
+  if (pair && getenv("GRADTUITY_GEMM_PAIR_CTA_WAIT") != nullptr) p.flags |= (1 << 30);
   p.a_onebox = a_one ? 1 : 0;
   p.b_onebox = b_one ? 1 : 0;
   p.tail_first = 0; p.tail_split = 1; p.tail_kb_per = num_kb;
@@ -1256,6 +1551,8 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm_batched: batch entries sharing one C need accumulate = 1, no epilogue and a 16-byte aligned C");
   if ((g.flags & GT_GEMM_BIAS_PER_BATCH) && ksplit > 1 && !splitk_direct)
     GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm_batched: a per-batch bias is not available on this split-K path");
+  // the pair kernel writes C through TMA only: an ordered (workspace) split-K goes to the one-CTA kernels
+  if (pair && ksplit > 1 && !splitk_direct) return umma_launch_impl(ctx, g, stream, fixed_scratch, fixed_scratch_floats, false);
   if (splitk_direct) {
     if (!g.accumulate) GT_CUDA_OK(ctx, cudaMemsetAsync(g.C, 0, (size_t)plane * sizeof(float), stream));
     p.accumulate = 1;
@@ -1318,6 +1615,15 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
             g.layout, (long long)g.M, (long long)g.N, (long long)g.K, nbatch, g.epilogue, g.accumulate, tile_m, bn, (int)x3, (int)a_gen,
             ksplit, (int)splitk_direct, p.tail_split, p.tail_first, p.num_tiles, grid, p.c_tma, p.a_onebox, p.b_onebox);
 
+  if (pair) {
+    const int clusters = p.num_tiles < pair_clusters ? p.num_tiles : pair_clusters;
+    if (trace) fprintf(stderr, "gt_gemm:   CTA pairs: %d clusters of 2 (at most %d fit)\n", clusters, pair_clusters);
+    switch (g.layout) {
+      case GT_LAYOUT_NN: return pair_launch(ctx, gt_gemm_pair_kernel<false, true>, clusters, stream, maps, p);
+      case GT_LAYOUT_NT: return pair_launch(ctx, gt_gemm_pair_kernel<false, false>, clusters, stream, maps, p);
+      default: return pair_launch(ctx, gt_gemm_pair_kernel<true, true>, clusters, stream, maps, p);
+    }
+  }
   if (use256) {
     auto launch256 = [&](auto kern, int idx) -> int {      // generic lambda: one instantiation (and one static) per kernel
       (void)idx;

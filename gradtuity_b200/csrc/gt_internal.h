@@ -49,17 +49,15 @@ struct gt_ctx {
     return (code);                                                                         \
   } while (0)
 
-// Opt a kernel in to `bytes` of dynamic shared memory, once per DEVICE: the attribute belongs to the device's
-// copy of the function, so a second context on another device of the same process needs its own call.
-// The remembered set is a static of the enclosing function (or template instantiation): one per kernel.
-#define GT_SMEM_OPT_IN(ctx, kern, bytes)                                                                   \
-  do {                                                                                                     \
-    static unsigned long long _gt_done = 0ull;                                                             \
-    const unsigned long long _gt_bit = 1ull << ((ctx)->device & 63);                                       \
-    if (!(_gt_done & _gt_bit)) {                                                                           \
-      GT_CUDA_OK(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (bytes)));   \
-      _gt_done |= _gt_bit;                                                                                 \
-    }                                                                                                      \
+// Opt a kernel in to `bytes` of dynamic shared memory, once per (kernel, device): the attribute belongs to the
+// device's copy of the function, so a second context on another device of the same process needs its own call.
+// Keyed by the kernel's address: kernels of one signature share a function-pointer TYPE, so a static flag inside
+// a template or a generic lambda would be shared between them.
+int gt_smem_opt_in(gt_ctx* ctx, const void* kernel, int bytes);
+#define GT_SMEM_OPT_IN(ctx, kern, bytes)                                        \
+  do {                                                                          \
+    int _gt_rc = gt_smem_opt_in((ctx), (const void*)(kern), (int)(bytes));      \
+    if (_gt_rc != GT_OK) return _gt_rc;                                         \
   } while (0)
 
 // One GEMM problem, fully resolved (used by both kernels).

@@ -6,6 +6,9 @@
 // allocator (the reference calls cudaMalloc/cudaFree once per tensor,
 // gradtuity/tensor.py:122-126), and every call reports a status instead of ignoring it.
 
+#include <mutex>
+#include <unordered_map>
+
 #include <stdlib.h>
 
 #include "gt_internal.h"
@@ -107,6 +110,18 @@ extern "C" int gt_device_status(gt_ctx* ctx, int* status) {
 extern "C" int gt_launch_count(gt_ctx* ctx, int64_t* count) {
   if (!ctx || !count) return GT_ERR_INVALID_ARG;
   *count = ctx->launches;
+  return GT_OK;
+}
+
+int gt_smem_opt_in(gt_ctx* ctx, const void* kernel, int bytes) {
+  static std::mutex lock;
+  static std::unordered_map<const void*, unsigned long long> done;       // kernel -> devices already served
+  std::lock_guard<std::mutex> guard(lock);
+  unsigned long long& mask = done[kernel];
+  const unsigned long long bit = 1ull << (ctx->device & 63);
+  if (mask & bit) return GT_OK;
+  GT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  mask |= bit;
   return GT_OK;
 }
 

@@ -57,6 +57,16 @@ class NcclBackend(Backend):
         lib = self._lib.load_library()
         self._lib.check(lib.gt_dist_wait(self._lib.context(), 1 if host_sync else 0), "gt_dist_wait")
 
+    def timeline(self) -> list[tuple[int, float, float, float]]:
+        """Collectives between the last two waits as (elements, enqueue ms, start ms, end ms), then a row
+        (0, compute-stream resume ms, 0, 0); empty unless GRADTUITY_DIST_TIMELINE=1 was set before init()."""
+        from ctypes import byref, c_float, c_int
+
+        buf = (c_float * (4 * 80))()
+        n = c_int(0)
+        self._lib.check(self._lib.load_library().gt_dist_timeline(self._lib.context(), buf, 80, byref(n)), "gt_dist_timeline")
+        return [(int(buf[4 * i]), buf[4 * i + 1], buf[4 * i + 2], buf[4 * i + 3]) for i in range(n.value)]
+
     def destroy(self) -> None:
         self._lib.load_library().gt_dist_destroy(self._lib.context())
 

@@ -126,6 +126,15 @@ def main() -> None:
         dt = time.perf_counter() - t0
         n = args.steps - 1 - s0
         print(f"{n} steps in {dt:.3f} s: {dt / n * 1e3:.1f} ms/step, {world * args.batch_size * args.seq_len * n / dt:.0f} tokens/s on {world} GPU(s)")
+    if world > 1 and os.environ.get("GRADTUITY_DIST_TIMELINE") == "1" and rank == 0:
+        from gradtuity_b200.dist import comm
+
+        rows = comm.get_backend().timeline()
+        print("collectives of the last step (MB, enqueued / started / finished, ms after the first one was enqueued):")
+        for n, t_enq, t_start, t_end in rows[:-1]:
+            print(f"  {n * 4 / 1e6:8.1f} MB  {t_enq:8.3f} {t_start:8.3f} {t_end:8.3f}   ({t_end - t_start:.3f} ms, {n * 4 / 1e6 / max(t_end - t_start, 1e-6):.0f} GB/s)")
+        if rows:
+            print(f"  compute stream resumed at {rows[-1][1]:.3f} ms; last collective was enqueued at {rows[-2][1]:.3f} ms")
     if world > 1:
         dist.destroy_process_group()
 

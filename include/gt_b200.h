@@ -343,7 +343,17 @@ int gt_sumsq_multi(gt_ctx* ctx, float* out, const void* tensors, const void* chu
  *   gt_dist_broadcast      _nccl_broadcast_inplace   gradtuity/dist/nccl.py:163-178, dist/comm.py:134-147
  * Collectives are enqueued on a separate communication stream behind the work already given to
  * the compute stream and return at once; gt_dist_wait orders the compute stream behind them.
- * `average` != 0 divides by the world size inside the collective (ncclAvg).                   */
+ * `average` != 0 divides by the world size inside the collective (ncclAvg).
+ * Nothing on the host waits without a limit: gt_dist_init joins communicator creation, and gt_dist_wait with
+ * host_sync != 0 polls the communication stream and ncclCommGetAsyncError, against GRADTUITY_NCCL_TIMEOUT_S
+ * seconds (default 120); past it, or on an asynchronous NCCL error, the communicator is aborted and the call
+ * returns GT_ERR_TIMEOUT / GT_ERR_NCCL (the reference waits 60 s for the id file, gradtuity/dist/comm.py:74-84,
+ * and without limit in cudaDeviceSynchronize after that).
+ * gt_dist_timeline (no counterpart in the reference; a measurement aid, active only when the process group was
+ * created with GRADTUITY_DIST_TIMELINE=1): device times of the collectives between the last two waits, four
+ * floats per row: element count, then ms from the first collective's enqueue point on the compute stream to
+ * (this collective's enqueue point, its start on the communication stream, its end); a last row holds in its
+ * second float when the compute stream resumed after the wait.                                 */
 int gt_dist_get_unique_id(gt_ctx* ctx, char* out128);
 int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128);
 int gt_dist_destroy(gt_ctx* ctx);
@@ -351,6 +361,7 @@ int gt_dist_allreduce(gt_ctx* ctx, float* ptr, int64_t count, int average);
 int gt_dist_broadcast(gt_ctx* ctx, float* ptr, int64_t count, int root);
 int gt_dist_wait(gt_ctx* ctx, int host_sync);
 int gt_dist_info(gt_ctx* ctx, int* rank, int* world);
+int gt_dist_timeline(gt_ctx* ctx, float* out, int max_rows, int* n);
 
 #ifdef __cplusplus
 }
