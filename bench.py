@@ -431,7 +431,11 @@ def run_train(args, world: int, rank: int, barrier_max) -> dict:
         gdist.destroy_process_group()
     step_ms = total_ms / steps
     tokens = world * 8 * 1024
-    return {"metric": "gpt2_small_train_tokens_per_s", "value": round(tokens / (step_ms * 1e-3), 1), "unit": "tokens/s",
+    ref = reference_train_fixture()
+    if ref is not None:
+        ref["vs_reference_triton"] = round(tokens / (step_ms * 1e-3) / ref["tokens_per_s"], 2)
+        ref["vs_reference_triton_per_gpu"] = round(8 * 1024 / (step_ms * 1e-3) / ref["tokens_per_s"], 2)
+    return {"reference_triton": ref, "metric": "gpt2_small_train_tokens_per_s", "value": round(tokens / (step_ms * 1e-3), 1), "unit": "tokens/s",
             "ms_per_step": round(step_ms, 3), "steps": steps, "warmup": warm, "n_gpus": world,
             "tflops_per_gpu": round(TRAIN_FLOPS_PER_STEP / (step_ms * 1e-3) / 1e12, 2),
             "frac_of_tf32_peak_measured": round(TRAIN_FLOPS_PER_STEP / (step_ms * 1e-3) / 1e12 / _peaks()[0], 4),
@@ -440,6 +444,21 @@ def run_train(args, world: int, rank: int, barrier_max) -> dict:
             "config": {"workload": "GPT-2-small train step, batch 8x1024 per GPU, fp32 storage, tf32 GEMMs, AdamW, clip 1.0",
                        "parallelism": f"dp{world}" if world > 1 else "single GPU",
                        "sync": "sync_grads: NCCL all-reduce (avg) of 25 MiB buckets on a side stream, overlapped with backward" if world > 1 else "none"}}
+
+
+def reference_train_fixture() -> dict | None:
+    """The reference's own GPT-2-small train step (its Triton backend, unmodified, one B200), as recorded by
+    tests/golden/make_reference_fixtures.py: the 1-GPU figure the tokens/s target is stated against."""
+    path = os.path.join(ROOT, "tests", "golden", "reference_gpt2_loss_curve.json")
+    try:
+        with open(path) as f:
+            fx = json.load(f)
+        return {"tokens_per_s": round(fx["tokens_per_s"], 1), "ms_per_step": round(fx["ms_per_step_median_after_20"], 1),
+                "steps": fx["steps_run"], "n_gpus": 1, "gpu": fx["versions"].get("gpu"), "triton": fx["versions"].get("triton"),
+                "source": "tests/golden/reference_gpt2_loss_curve.json (unmodified reference, GRADTUITY_KERNEL_BACKEND=triton, "
+                          "same seeded weights and batches, median of the steps after the 20th)"}
+    except (OSError, KeyError, ValueError):
+        return None
 
 
 def run_micro(args) -> dict:

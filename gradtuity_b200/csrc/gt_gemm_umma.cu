@@ -1344,8 +1344,11 @@ int pick_bn(const gt_gemm_args& g, int sms, bool x3, bool a_gen) {
   if (a_gen && g.N >= 256) return 256;
   const long long batches = g.batch0 * g.batch1;
   const long long tm = (g.M + BM - 1) / BM;
-  // Few output tiles and a long K: take the widest tile, split-K fills the remaining SMs.
-  if (!x3 && g.epilogue < GT_EPI_CAUSAL && g.K >= 32 * BK && tm * ((g.N + 255) / 256) * batches * 2 <= sms) return 256;
+  // Few output tiles and a long K: take the widest tile, split-K fills the remaining SMs.  Not for a short K
+  // (<= 2048) whose 64-wide tiles already occupy half the SMs: there the memset and the reduce-adds of the split
+  // cost more than the narrow tile's extra operand traffic (1024^3: 16.5 -> 14.4 us, with bias + GELU 24.7 -> 15.3 us).
+  const bool narrow_fills = g.K <= 2048 && tm * ((g.N + 63) / 64) * batches * 2 >= sms;
+  if (!x3 && g.epilogue < GT_EPI_CAUSAL && g.K >= 32 * BK && tm * ((g.N + 255) / 256) * batches * 2 <= sms && !narrow_fills) return 256;
   // Cost in "column units per SM": waves x tile width x a per-width efficiency penalty.
   double best = 1e30; int best_bn = 256;
   const int cands[3] = {256, 128, 64};

@@ -21,29 +21,48 @@ class Module:
     def __init__(self) -> None:
         self.training = True
 
-    def _children(self):
+    # One walker serves every tree operation below.  The order is the contract: public attributes in dir() order
+    # (alphabetical), sub-modules entered depth-first, lists of modules indexed by position, so that paths such
+    # as "blocks.3.attn.Wq" and the order of parameters() agree with gradtuity/nn.py:87-114 on every rank.
+    def _walk(self, prefix: str = ""):
+        """Yields (path, owner, attribute_name, value) for every public attribute of this module and, recursively,
+        of its sub-modules; list entries that are modules are walked under "<name>.<index>."."""
         for name in dir(self):
             if name.startswith("_"):
                 continue
             try:
-                attr = getattr(self, name)
+                value = getattr(self, name)
             except AttributeError:
                 continue
-            yield name, attr
+            yield prefix + name, self, name, value
+            if isinstance(value, Module):
+                yield from value._walk(prefix + name + ".")
+            elif isinstance(value, list):
+                for i, item in enumerate(value):
+                    if isinstance(item, Module):
+                        yield from item._walk(f"{prefix}{name}.{i}.")
+
+    def _submodules(self):
+        """This module and every module below it, each once."""
+        seen = {id(self)}
+        yield self
+        for _, _, _, value in self._walk():
+            for m in (value if isinstance(value, list) else [value]):
+                if isinstance(m, Module) and id(m) not in seen:
+                    seen.add(id(m))
+                    yield m
 
     def train(self, mode: bool = True) -> "Module":
-        self.training = mode
-        for _, attr in self._children():
-            if isinstance(attr, Module):
-                attr.train(mode)
-            elif isinstance(attr, list):
-                for item in attr:
-                    if isinstance(item, Module):
-                        item.train(mode)
+        for m in self._submodules():
+            m.training = mode
         return self
 
     def eval(self) -> "Module":
         return self.train(False)
+
+    def state_dict(self) -> dict[str, Tensor]:
+        """Trainable tensors by dot-separated path, list indices as numeric segments."""
+        return {path: value for path, _, _, value in self._walk() if isinstance(value, Tensor) and value.requires_grad}
 
     def parameters(self) -> list[Tensor]:
         """All trainable tensors in sorted state_dict key order (identical on every rank)."""
@@ -53,70 +72,30 @@ class Module:
     def zero_grad(self) -> None:
         zero_grad(self.parameters())
 
-    def state_dict(self) -> dict[str, Tensor]:
-        """Dot-separated parameter paths, list indices as numeric segments (gradtuity/nn.py:87-114)."""
-        result: dict[str, Tensor] = {}
-
-        def visit(obj, prefix: str) -> None:
-            for name in dir(obj):
-                if name.startswith("_"):
-                    continue
-                try:
-                    attr = getattr(obj, name)
-                except AttributeError:
-                    continue
-                if isinstance(attr, Tensor) and attr.requires_grad:
-                    result[prefix + name] = attr
-                elif isinstance(attr, Module):
-                    visit(attr, prefix + name + ".")
-                elif isinstance(attr, list):
-                    for i, item in enumerate(attr):
-                        if isinstance(item, Module):
-                            visit(item, prefix + name + "." + str(i) + ".")
-
-        visit(self, "")
-        return result
-
     def load_state_dict(self, state: dict[str, Tensor], strict: bool = True) -> None:
-        own = set(self.state_dict().keys())
-        given = set(state.keys())
+        """Replace parameters by the tensors of `state` (keys as in state_dict()).  strict: the key sets must agree;
+        otherwise keys this module does not have are ignored.  Error texts follow gradtuity/nn.py:116-158."""
+        slots = {path: (owner, name) for path, owner, name, value in self._walk()
+                 if isinstance(value, Tensor) and value.requires_grad}
         if strict:
-            if given - own:
-                raise ValueError(f"load_state_dict: unexpected key(s) in state: {given - own}")
-            if own - given:
-                raise ValueError(f"load_state_dict: missing key(s) in state: {own - given}")
+            extra, lacking = set(state) - set(slots), set(slots) - set(state)
+            if extra:
+                raise ValueError(f"load_state_dict: unexpected key(s) in state: {extra}")
+            if lacking:
+                raise ValueError(f"load_state_dict: missing key(s) in state: {lacking}")
         for key, tensor in state.items():
-            if key not in own:
+            if key not in slots:
                 continue
-            parts = key.split(".")
-            cur = self
-            for seg in parts[:-1]:
-                try:
-                    cur = cur[int(seg)] if seg.isdigit() else getattr(cur, seg)
-                except (AttributeError, IndexError, KeyError) as e:
-                    raise ValueError(f"load_state_dict: cannot resolve key {key!r}") from e
+            owner, name = slots[key]
             try:
-                setattr(cur, parts[-1], tensor)
+                setattr(owner, name, tensor)
             except AttributeError as e:
                 raise ValueError(f"load_state_dict: cannot set key {key!r}") from e
         # modules that keep several parameters in one buffer (CausalSelfAttention) restore that layout
-        seen: set[int] = set()
-
-        def visit(obj) -> None:
-            if id(obj) in seen:
-                return
-            seen.add(id(obj))
-            if isinstance(obj, Module):
-                hook = getattr(obj, "_after_load", None)
-                if hook is not None:
-                    hook()
-                for _, attr in obj._children():
-                    visit(attr)
-            elif isinstance(obj, (list, tuple)):
-                for item in obj:
-                    visit(item)
-
-        visit(self)
+        for m in self._submodules():
+            hook = getattr(m, "_after_load", None)
+            if hook is not None:
+                hook()
 
     def __call__(self, x: Tensor) -> Tensor:
         raise NotImplementedError("Subclasses must implement __call__")

@@ -208,22 +208,45 @@ def maxpool2d_backward(dy, arg, H, W):
     return dx.reshape(N, C, H, W)
 
 
-def cnn_loss_and_grads(params, x, targets):
+def _pool_take(a, arg):
+    """Values of a (N, C, H, W) at the flat window positions `arg` (N, C, Ho, Wo): pooling with given winners."""
+    N, C, H, W = a.shape
+    return np.take_along_axis(a.reshape(N, C, H * W), arg.reshape(N, C, -1), axis=2).reshape(arg.shape)
+
+
+def cnn_loss_and_grads(params, x, targets, decisions=None):
     """The reference's MNIST CNN (gradtuity/nn.py:713-750) with a mean cross-entropy loss, in float64:
     params = dict(conv1.weight, conv1.bias, conv2.weight, conv2.bias, fc1.weight (in, out), fc1.bias, fc2.weight,
-    fc2.bias).  Returns the loss and the gradient of every parameter."""
+    fc2.bias).  Returns the loss and the gradient of every parameter.
+
+    ReLU and max-pooling are piecewise linear: which piece an element is on (sign of the pre-activation, winner of
+    a pooling window) is a DISCRETE decision, and an implementation whose products carry tf32 rounding can take a
+    different piece for the few elements that lie within rounding error of a boundary, which moves gradients by
+    far more than the rounding error itself.  `decisions` = dict(relu1, arg1, relu2, arg2, relu3) fixes those
+    choices (boolean masks and window positions, e.g. taken from the implementation under test), so that what is
+    compared is the arithmetic along the same piece."""
     P = {k: np.asarray(v, np.float64) for k, v in params.items()}
     x = np.asarray(x, np.float64)
     N = x.shape[0]
+    D = decisions
     z1 = conv2d_forward_backward(x, P["conv1.weight"], P["conv1.bias"], np.zeros((N, 32, 28, 28)), 1, 1)["y"]
-    a1 = np.maximum(z1, 0)
-    p1, arg1 = maxpool2d_forward(a1, 2, 2)
+    relu1 = (z1 > 0) if D is None else np.asarray(D["relu1"], bool)
+    a1 = z1 * relu1
+    if D is None:
+        p1, arg1 = maxpool2d_forward(a1, 2, 2)
+    else:
+        arg1 = np.asarray(D["arg1"], np.int64); p1 = _pool_take(a1, arg1)
     z2 = conv2d_forward_backward(p1, P["conv2.weight"], P["conv2.bias"], np.zeros((N, 64, 14, 14)), 1, 1)["y"]
-    a2 = np.maximum(z2, 0)
-    p2, arg2 = maxpool2d_forward(a2, 2, 2)
+    relu2 = (z2 > 0) if D is None else np.asarray(D["relu2"], bool)
+    a2 = z2 * relu2
+    if D is None:
+        p2, arg2 = maxpool2d_forward(a2, 2, 2)
+    else:
+        arg2 = np.asarray(D["arg2"], np.int64); p2 = _pool_take(a2, arg2)
     f = p2.reshape(N, -1)
     h_pre = f @ P["fc1.weight"] + P["fc1.bias"]
-    h = np.maximum(h_pre, 0)
+    relu3 = (h_pre > 0) if D is None else np.asarray(D["relu3"], bool)
+    h = h_pre * relu3
     logits = h @ P["fc2.weight"] + P["fc2.bias"]
     zmax = logits.max(1, keepdims=True)
     lse = zmax[:, 0] + np.log(np.exp(logits - zmax).sum(1))
@@ -233,14 +256,14 @@ def cnn_loss_and_grads(params, x, targets):
     dlogits[np.arange(N), t] -= 1
     dlogits /= N
     g = {"fc2.weight": h.T @ dlogits, "fc2.bias": dlogits.sum(0)}
-    dh = (dlogits @ P["fc2.weight"].T) * (h_pre > 0)
+    dh = (dlogits @ P["fc2.weight"].T) * relu3
     g["fc1.weight"] = f.T @ dh
     g["fc1.bias"] = dh.sum(0)
     dp2 = (dh @ P["fc1.weight"].T).reshape(p2.shape)
-    dz2 = maxpool2d_backward(dp2, arg2, 14, 14) * (z2 > 0)
+    dz2 = maxpool2d_backward(dp2, arg2, 14, 14) * relu2
     r2 = conv2d_forward_backward(p1, P["conv2.weight"], P["conv2.bias"], dz2, 1, 1)
     g["conv2.weight"], g["conv2.bias"] = r2["dw"], r2["db"]
-    dz1 = maxpool2d_backward(r2["dx"], arg1, 28, 28) * (z1 > 0)
+    dz1 = maxpool2d_backward(r2["dx"], arg1, 28, 28) * relu1
     r1 = conv2d_forward_backward(x, P["conv1.weight"], P["conv1.bias"], dz1, 1, 1)
     g["conv1.weight"], g["conv1.bias"] = r1["dw"], r1["db"]
     return loss, g

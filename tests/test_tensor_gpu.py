@@ -265,13 +265,15 @@ def test_maxpool2d_forward_and_backward(T):
         T.from_numpy(np.zeros((1, 1, 2, 2), np.float32)).maxpool2d(kernel_size=3)
 
 
-@pytest.mark.parametrize("precision,tol", [("3xtf32", 2e-4), ("tf32", 8e-2)])
+@pytest.mark.parametrize("precision,tol", [("3xtf32", 2e-4), ("tf32", 1e-3)])
 def test_mnist_cnn_loss_and_gradients_against_the_oracle(T, precision, tol, monkeypatch):
     """The reference's CNN (two conv + pool stages, two Linear layers) on MNIST-shaped synthetic input: loss and
     the gradient of every parameter against float64; then a few SGD steps lower the loss.  In tf32 mode a
-    rounding difference can flip a ReLU mask or the winner of a pooling window, which moves the early layers'
-    gradients by a few percent (measured 1-5 % on conv1.weight over random draws); the 3xTF32 run holds the
-    tight bar.  All parameter values come from the test's seeded generator."""
+    rounding difference can flip a ReLU mask or the winner of a pooling window for the few elements that sit on a
+    boundary, which moves the early layers' gradients by percents although every product is within 1e-3; so the
+    tf32 run hands the oracle the masks and winners the GPU run actually took and holds the arithmetic along
+    those pieces to 1e-3, while the 3xTF32 run is compared with the oracle's own decisions.  All parameter
+    values come from the test's seeded generator."""
     monkeypatch.setenv("GRADTUITY_GEMM_PRECISION", precision)
     from gradtuity_b200.nn import CNN, Flatten
     from gradtuity_b200.optim import SGD
@@ -291,12 +293,21 @@ def test_mnist_cnn_loss_and_gradients_against_the_oracle(T, precision, tol, monk
     x = rng.random((N, 1, 28, 28), dtype=np.float32)
     t = rng.integers(0, 10, N)
     tt = T.from_numpy(t.astype(np.float32))
-    logits = model(T.from_numpy(x))
+    # the model's own forward (CNN.__call__), layer by layer so that the pre-activations can be read back
+    z1 = model.conv1(T.from_numpy(x)); a1 = z1.relu(); p1 = model.pool1(a1)
+    z2 = model.conv2(p1); a2 = z2.relu(); p2 = model.pool2(a2)
+    h = model.flatten(p2).linear_relu(model.fc1.weight, model.fc1.bias)
+    logits = h.linear(model.fc2.weight, model.fc2.bias)
     assert logits.shape == (N, 10)
+    assert np.array_equal(logits.numpy(), model(T.from_numpy(x)).numpy())          # same kernels, same order
     loss = logits.cross_entropy(tt, reduction="mean")
     loss.backward()
-    ref_loss, ref_g = O.cnn_loss_and_grads(host, x, t)
-    assert abs(loss.item() - ref_loss) <= 2e-3 * abs(ref_loss)
+    decisions = None
+    if precision == "tf32":
+        decisions = {"relu1": z1.numpy() > 0, "arg1": O.maxpool2d_forward(a1.numpy(), 2, 2)[1],
+                     "relu2": z2.numpy() > 0, "arg2": O.maxpool2d_forward(a2.numpy(), 2, 2)[1], "relu3": h.numpy() > 0}
+    ref_loss, ref_g = O.cnn_loss_and_grads(host, x, t, decisions=decisions)
+    assert abs(loss.item() - ref_loss) <= 1e-3 * abs(ref_loss)
     for k, p in params.items():
         assert O.rel_frobenius(p.grad.numpy(), ref_g[k]) <= tol, k
     opt = SGD(model.parameters(), lr=0.05)
