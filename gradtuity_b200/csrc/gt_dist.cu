@@ -224,6 +224,7 @@ extern "C" int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128
     GT_CUDA_OK(ctx, cudaEventCreate(&st->tl_resume));
   }
   g_dist[ctx->device] = st;
+  ctx->dist_active = 1;
   return GT_OK;
 }
 
@@ -237,6 +238,7 @@ extern "C" int gt_dist_destroy(gt_ctx* ctx) {
   cudaStreamDestroy(st->stream);
   delete st;
   g_dist[ctx->device] = nullptr;
+  ctx->dist_active = 0;
   return GT_OK;
 }
 

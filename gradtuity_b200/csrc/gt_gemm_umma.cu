@@ -75,7 +75,55 @@ struct UmmaParams {
   int* tail_flags;                       // publishes tail_flags[i] = tail_epoch; the shares wait for it before they add
   float alpha;
   int* status;
+  // Dynamic tile scheduling: after its first unit (its block index) a CTA takes `gridDim.x + atomicAdd(sched, 1)`,
+  // so a CTA that starts late (its SM was busy with another kernel, e.g. a collective) takes less work instead of
+  // making the launch wait for its fixed share.  Null: static round-robin.  sched_reset: the counter of a later
+  // launch, zeroed by this one.
+  int* sched;
+  int* sched_reset;
 };
+
+// Shared-memory ring through which the producer thread, which draws the work units, hands them to the MMA thread
+// and the epilogue (and cp.async) warps of its CTA.
+constexpr int SCHED_SLOTS = 4;
+constexpr int SCHED_CONSUMERS = 9;            // the MMA thread + eight warps (epilogue, or epilogue + cp.async)
+struct SchedRing {
+  uint32_t full, empty;                       // SCHED_SLOTS mbarriers each
+  volatile int* units;                        // SCHED_SLOTS ints
+  bool dynamic;
+};
+
+// Producer side: publish `unit` (-1: no more work).  False when the CTA is aborting.
+__device__ __forceinline__ bool sched_publish(const SchedRing& r, int unit, int& slot, uint32_t& ph, volatile int* abort_flag, int* status) {
+  if (!r.dynamic) return true;
+  if (!mbar_wait(r.empty + 8 * slot, ph ^ 1u, abort_flag, status)) return false;
+  r.units[slot] = unit;
+  mbar_arrive(r.full + 8 * slot);
+  if (++slot == SCHED_SLOTS) { slot = 0; ph ^= 1u; }
+  return true;
+}
+
+// Consumer side, called by every thread of a consuming warp (or by the lone MMA thread with whole_warp = false):
+// the next unit of this CTA, -1 when there is none, -2 when the CTA is aborting.  `k` counts the units taken.
+__device__ __forceinline__ int sched_take(const SchedRing& r, int num_units, int& k, int& slot, uint32_t& ph, bool whole_warp,
+                                          volatile int* abort_flag, int* status) {
+  if (!r.dynamic) {
+    const long long u = (long long)blockIdx.x + (long long)k * gridDim.x;
+    ++k;
+    return u < num_units ? (int)u : -1;
+  }
+  if (!mbar_wait(r.full + 8 * slot, ph, abort_flag, status)) return -2;
+  const int unit = r.units[slot];
+  if (whole_warp) {
+    __syncwarp();                              // every lane has read the slot
+    if ((threadIdx.x & 31) == 0) mbar_arrive(r.empty + 8 * slot);
+  } else {
+    mbar_arrive(r.empty + 8 * slot);
+  }
+  if (++slot == SCHED_SLOTS) { slot = 0; ph ^= 1u; }
+  ++k;
+  return unit;
+}
 
 template <int BN, bool X3>
 struct Cfg {
@@ -397,11 +445,18 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t bar_tfull = bar_empty + 8 * MAX_STAGES;
   const uint32_t bar_tempty = bar_tfull + 16;
   const uint32_t bar_drain = bar_tempty + 16;
+  SchedRing ring;
+  ring.full = smem_u32(ctrl + 192);
+  ring.empty = ring.full + 8 * SCHED_SLOTS;
+  ring.units = reinterpret_cast<volatile int*>(ctrl + 192 + 16 * SCHED_SLOTS);
+  ring.dynamic = p.sched != nullptr;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    if (p.sched_reset && blockIdx.x == 0) *p.sched_reset = 0;
+    for (int s = 0; s < SCHED_SLOTS; ++s) { mbar_init(ring.full + 8 * s, 1); mbar_init(ring.empty + 8 * s, SCHED_CONSUMERS); }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, A_GEN ? 1 + 128 : 1);   // TMA issuer (+ one arrival per cp.async thread)
       mbar_init(bar_empty + 8 * s, 1);
@@ -432,7 +487,14 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int s = 0; uint32_t ph = 0;
       long long issued = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int sslot = 0; uint32_t sph = 0;
+      long long next_unit = blockIdx.x;                 // the first unit is the CTA's own index, later ones are drawn
+      while (ok) {
+        const int tile = next_unit < p.num_tiles ? (int)next_unit : -1;
+        if (!sched_publish(ring, tile, sslot, sph, abort_flag, p.status)) { ok = false; break; }
+        if (tile < 0) break;
+        // drawn now, needed only after this unit's loads have been issued: the atomic's latency hides behind them
+        next_unit = ring.dynamic ? (long long)gridDim.x + atomicAdd(p.sched, 1) : next_unit + gridDim.x;
         int batch, tm, tn, ks;
         tile_coords(p, tile, batch, tm, tn, ks);
         int kb_lo, kb_hi;
@@ -502,7 +564,10 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int acc = 0; uint32_t aph = 0;
       bool ok = true;
       bool any_issued = false;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int sk = 0, sslot = 0; uint32_t sph = 0;
+      while (ok) {
+        const int tile = sched_take(ring, p.num_tiles, sk, sslot, sph, false, abort_flag, p.status);
+        if (tile < 0) { ok = tile == -1; break; }
         int batch, tm, tn, ks;
         tile_coords(p, tile, batch, tm, tn, ks);
         int kb_lo, kb_hi;
@@ -569,7 +634,10 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int t = threadIdx.x - 192;
     int s = 0; uint32_t ph = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    int sk = 0, sslot = 0; uint32_t sph = 0;
+    while (ok) {
+      const int tile = sched_take(ring, p.num_tiles, sk, sslot, sph, true, abort_flag, p.status);
+      if (tile < 0) break;
       int batch, tm, tn, ks;
       tile_coords(p, tile, batch, tm, tn, ks);
       int kb_lo, kb_hi;
@@ -651,7 +719,10 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         __syncwarp();
       }
     }
-    for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+    int sk = 0, sslot = 0; uint32_t sph = 0;
+    while (ok) {
+      const int tile = sched_take(ring, p.num_tiles, sk, sslot, sph, true, abort_flag, p.status);
+      if (tile < 0) break;
       int batch, tm, tn, ks;
       tile_coords(p, tile, batch, tm, tn, ks);
       int kb_lo, kb_hi;
@@ -795,10 +866,17 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   const uint32_t bar_tfull = bar_empty + 8 * MAX_STAGES;     // [half]
   const uint32_t bar_tempty = bar_tfull + 16;                // [half]
   const uint32_t bar_drain = bar_tempty + 16;
+  SchedRing ring;
+  ring.full = smem_u32(ctrl + 192);
+  ring.empty = ring.full + 8 * SCHED_SLOTS;
+  ring.units = reinterpret_cast<volatile int*>(ctrl + 192 + 16 * SCHED_SLOTS);
+  ring.dynamic = p.sched != nullptr;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
+    if (p.sched_reset && blockIdx.x == 0) *p.sched_reset = 0;
+    for (int s = 0; s < SCHED_SLOTS; ++s) { mbar_init(ring.full + 8 * s, 1); mbar_init(ring.empty + 8 * s, SCHED_CONSUMERS); }
     for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int h = 0; h < 2; ++h) { mbar_init(bar_tfull + 8 * h, 1); mbar_init(bar_tempty + 8 * h, 128); }
     mbar_init(bar_drain, 1);
@@ -822,7 +900,13 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       int s = 0; uint32_t ph = 0;
       long long issued = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int sslot = 0; uint32_t sph = 0;
+      long long next_unit = blockIdx.x;
+      while (ok) {
+        const int tile = next_unit < p.num_tiles ? (int)next_unit : -1;
+        if (!sched_publish(ring, tile, sslot, sph, abort_flag, p.status)) { ok = false; break; }
+        if (tile < 0) break;
+        next_unit = ring.dynamic ? (long long)gridDim.x + atomicAdd(p.sched, 1) : next_unit + gridDim.x;
         int batch, tm, tn, ks;
         tile_coords(p, tile, batch, tm, tn, ks);
         const int i0 = batch % p.batch0, i1 = batch / p.batch0;
@@ -870,7 +954,10 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
       constexpr uint32_t idesc = make_idesc(TN, A_MN, B_MN);
       int s = 0; uint32_t ph = 0, tph = 0;
       bool ok = true, any_issued = false;
-      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+      int sk = 0, sslot = 0; uint32_t sph = 0;
+      while (ok) {
+        const int tile = sched_take(ring, p.num_tiles, sk, sslot, sph, false, abort_flag, p.status);
+        if (tile < 0) { ok = tile == -1; break; }
         // both accumulators must have been drained by the previous tile's epilogue
         if (!mbar_wait(bar_tempty, tph ^ 1u, abort_flag, p.status)) { ok = false; break; }
         if (!mbar_wait(bar_tempty + 8, tph ^ 1u, abort_flag, p.status)) { ok = false; break; }
@@ -917,7 +1004,10 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     uint8_t* epi_bytes = epi_scratch + (warp - 2) * 4096;
     const uint32_t epi_u32 = smem_u32(epi_bytes);
     uint32_t tph = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+    int sk = 0, sslot = 0; uint32_t sph = 0;
+    while (true) {
+      const int tile = sched_take(ring, p.num_tiles, sk, sslot, sph, true, abort_flag, p.status);
+      if (tile < 0) break;
       int batch, tm, tn, ks;
       tile_coords(p, tile, batch, tm, tn, ks);
       const int i0 = batch % p.batch0, i1 = batch / p.batch0;
@@ -1535,6 +1625,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   p.tail_first = 0; p.tail_split = 1; p.tail_kb_per = num_kb;
   p.tail_zero = 0; p.tail_epoch = 0; p.tail_flags = nullptr;
   p.status = ctx->d_status;
+  p.sched = nullptr; p.sched_reset = nullptr;
   bool vec = (((uintptr_t)g.C & 15) == 0) && (g.ldc % 4 == 0) && (g.sC0 % 4 == 0) && (g.sC1 % 4 == 0);
   if (g.aux) vec = vec && (((uintptr_t)g.aux & 15) == 0);
   if (g.bias) vec = vec && (((uintptr_t)g.bias & 15) == 0);
@@ -1612,6 +1703,19 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     }
   }
   const int grid = (int)(p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count);
+  // Optional dynamic scheduling (GRADTUITY_GEMM_DYNAMIC_SCHED=1): with more units than CTAs, the CTAs draw their later
+  // units from a counter instead of taking every grid-th one, so a CTA whose SM is still held by another kernel
+  // when the launch starts (an all-reduce on the communication stream) takes less work instead of making the launch
+  // wait for its fixed share.  Measured on the data-parallel GPT-2 step (2 GPUs): 21.0 ms against 20.9 ms with the
+  // fixed assignment, and alone on a GPU 0-6 % slower per GEMM (the atomics; the last-wave split no longer meets the
+  // wave it planned for), so the fixed assignment stays the default.
+  static const bool dynamic_sched = getenv("GRADTUITY_GEMM_DYNAMIC_SCHED") != nullptr && atoi(getenv("GRADTUITY_GEMM_DYNAMIC_SCHED")) != 0;
+  if (dynamic_sched && !pair && p.num_tiles > grid && ctx->d_sched) {
+    if ((rc = gt_scratch_acquire(ctx, stream)) != GT_OK) return rc;      // the counter ring serves one stream at a time
+    const int slot = (int)(ctx->sched_seq++ % GT_SCHED_RING);
+    p.sched = ctx->d_sched + slot;
+    p.sched_reset = ctx->d_sched + (slot + GT_SCHED_RING / 2) % GT_SCHED_RING;
+  }
   static const bool trace = getenv("GRADTUITY_GEMM_TRACE") != nullptr;     // one line per launch on stderr
   if (trace)
     fprintf(stderr, "gt_gemm: layout %d M %lld N %lld K %lld batch %lld epi %d acc %d | tile %dx%d x3 %d a_gen %d ksplit %d direct %d tail_split %d (from tile %d) units %d grid %d c_tma %d onebox %d%d\n",

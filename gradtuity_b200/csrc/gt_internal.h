@@ -21,6 +21,9 @@ struct gt_ctx {
   int* d_status;              // device status word written by bounded waits that ran out; the allocation is 4 KB:
                               // ints 16..271 are the "C tile zeroed" flags of the GEMM's last-wave split
   int tail_epoch;             // value those flags take in the next launch that uses them
+  int* d_sched;               // ring of GT_SCHED_RING work-unit counters for dynamically scheduled launches (zero when idle)
+  long long sched_seq;        // launches that took a counter so far
+  int dist_active;            // a process group exists: collectives may hold SMs while GEMMs are launched
   cudaStream_t h2d_stream, d2h_stream;   // copy streams of gt_gemm_host (created on first use)
   cudaEvent_t host_ev[8];                // its events
   gt_encode_tiled_fn encode_tiled;
@@ -32,6 +35,8 @@ struct gt_ctx {
   int tma_round;              // 1: tensor maps use the TFLOAT32 data type (TMA rounds), 0: FLOAT32
   char last_error[256];
 };
+
+#define GT_SCHED_RING 1024     // launch n uses counter n % 1024 and zeroes counter (n + 512) % 1024 for a later launch
 
 #define GT_CUDA_OK(ctx, expr)                                                              \
   do {                                                                                     \

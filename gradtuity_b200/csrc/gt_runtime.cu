@@ -51,6 +51,9 @@ extern "C" int gt_init(int device, gt_ctx** out) {
   if (cudaMalloc((void**)&ctx->d_status, 4096) != cudaSuccess) { free(ctx); return GT_ERR_CUDA; }
   cudaMemset(ctx->d_status, 0, 4096);
   ctx->tail_epoch = 0;
+  if (cudaMalloc((void**)&ctx->d_sched, GT_SCHED_RING * sizeof(int)) != cudaSuccess) { cudaFree(ctx->d_status); free(ctx); return GT_ERR_CUDA; }
+  cudaMemset(ctx->d_sched, 0, GT_SCHED_RING * sizeof(int));
+  ctx->sched_seq = 0;
 
   // Keep freed blocks in the pool instead of returning them to the driver at every sync.
   cudaMemPool_t pool;
@@ -89,6 +92,7 @@ extern "C" int gt_destroy(gt_ctx* ctx) {
     for (int i = 0; i < 8; ++i) cudaEventDestroy(ctx->host_ev[i]);
   }
   cudaFree(ctx->d_status);
+  cudaFree(ctx->d_sched);
   cudaStreamDestroy(ctx->stream);
   free(ctx);
   return GT_OK;

@@ -122,6 +122,16 @@ class GradPlan:
 
     # ---- called by Tensor.backward() ------------------------------------------------------------
     def begin(self, topo: list) -> None:
+        cons = {}
+        for node in topo:
+            for par in node._parents:
+                i = self.index.get(id(par))
+                if i is not None:
+                    cons[i] = cons.get(i, 0) + 1
+        if not cons:
+            # a graph that touches none of this plan's parameters (another model, a metric): not our backward
+            self.active = False
+            return
         if self.launched:
             # a backward since the last sync_grads sent these buckets: this backward adds into the same
             # arena, so it must run behind them; finish() will reduce every bucket again
@@ -132,12 +142,6 @@ class GradPlan:
         self.armed = False
         if not self.active:
             return
-        cons = {}
-        for node in topo:
-            for par in node._parents:
-                i = self.index.get(id(par))
-                if i is not None:
-                    cons[i] = cons.get(i, 0) + 1
         self._consumers = cons
         self._bucket_left = [sum(1 for i in idxs if i in cons) for idxs in self.buckets]
         self._in_graph = [any(i in cons for i in idxs) for idxs in self.buckets]

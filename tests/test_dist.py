@@ -143,6 +143,11 @@ def test_only_the_first_backward_after_a_sync_sends_buckets(monkeypatch):
         plan.end()
 
     be.calls.clear(); waits = be.waits
+    other = FakeTensor(np.zeros(3), requires_grad=True)      # a backward through another model's graph in between
+    plan.begin([other, node(other)])
+    plan.node_done((other,))
+    plan.end()
+    assert be.calls == [] and plan.armed                     # ... is not this plan's backward and leaves it armed
     backward()
     assert len(be.calls) == 2 and be.waits == waits          # first backward after a sync: both buckets early
     backward()
