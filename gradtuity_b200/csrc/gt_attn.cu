@@ -158,10 +158,12 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  gt_let_next_kernel_start();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *sm.tmem_slot;
+  gt_wait_for_previous_kernel();         // set-up above overlaps the previous kernel's tail; global memory from here on
   const uint32_t tmem_o = tmem_base + 256u;
   // Online mode streams K and V through three ring slots; the fourth slot's memory holds the statistics the
   // softmax warps exchange every tile.
@@ -590,9 +592,11 @@ __device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_a
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  gt_let_next_kernel_start();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  gt_wait_for_previous_kernel();         // set-up above overlaps the previous kernel's tail; global memory from here on
 }
 
 // One ring load: a K-major tile (two boxes of 32 columns) or an MN-major tile (one five-dimensional box).
@@ -1080,8 +1084,7 @@ extern "C" int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* 
   p.status = ctx->d_status;
   GT_SMEM_OPT_IN(ctx, gt_attn_fwd_kernel, AT_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
-  gt_attn_fwd_kernel<<<grid, AT_THREADS, AT_SMEM_BYTES, stream>>>(mq, mk, mv, mp, mo, p);
-  GT_CUDA_OK(ctx, cudaGetLastError());
+  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_fwd_kernel, dim3(grid), dim3(AT_THREADS), AT_SMEM_BYTES, stream, mq, mk, mv, mp, mo, p));
   ctx->launches += 1;
   return GT_OK;
 }
@@ -1120,10 +1123,9 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dq_kernel, ATB_SMEM_BYTES);
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATB_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
-  gt_attn_bwd_dq_kernel<<<grid, AT_THREADS, ATB_SMEM_BYTES, stream>>>(mq, mdo, mk, mv, mkmn, mdq, p, acc_dq);
-  GT_CUDA_OK(ctx, cudaGetLastError());
-  gt_attn_bwd_dkv_kernel<<<grid, AT_THREADS, ATB_SMEM_BYTES, stream>>>(mk, mv, mq, mdo, mqmn, mdomn, mdk, mdv, p, acc_dk, acc_dv);
-  GT_CUDA_OK(ctx, cudaGetLastError());
+  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dq_kernel, dim3(grid), dim3(AT_THREADS), ATB_SMEM_BYTES, stream, mq, mdo, mk, mv, mkmn, mdq, p, acc_dq));
+  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dkv_kernel, dim3(grid), dim3(AT_THREADS), ATB_SMEM_BYTES, stream, mk, mv, mq, mdo, mqmn, mdomn, mdk, mdv,
+                                       p, acc_dk, acc_dv));
   ctx->launches += 2;
   return GT_OK;
 }

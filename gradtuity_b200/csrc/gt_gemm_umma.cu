@@ -455,7 +455,6 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    if (p.sched_reset && blockIdx.x == 0) *p.sched_reset = 0;
     for (int s = 0; s < SCHED_SLOTS; ++s) { mbar_init(ring.full + 8 * s, 1); mbar_init(ring.empty + 8 * s, SCHED_CONSUMERS); }
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, A_GEN ? 1 + 128 : 1);   // TMA issuer (+ one arrival per cp.async thread)
@@ -474,10 +473,13 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  gt_let_next_kernel_start();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  gt_wait_for_previous_kernel();         // everything above ran beside the previous kernel's tail; global memory from here on
+  if (p.sched_reset && threadIdx.x == 0 && blockIdx.x == 0) *p.sched_reset = 0;
 
   const int num_kb = (p.K + BK - 1) / BK;
 
@@ -875,7 +877,6 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    if (p.sched_reset && blockIdx.x == 0) *p.sched_reset = 0;
     for (int s = 0; s < SCHED_SLOTS; ++s) { mbar_init(ring.full + 8 * s, 1); mbar_init(ring.empty + 8 * s, SCHED_CONSUMERS); }
     for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int h = 0; h < 2; ++h) { mbar_init(bar_tfull + 8 * h, 1); mbar_init(bar_tempty + 8 * h, 128); }
@@ -888,10 +889,13 @@ gt_gemm_umma256_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  gt_let_next_kernel_start();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  gt_wait_for_previous_kernel();
+  if (p.sched_reset && threadIdx.x == 0 && blockIdx.x == 0) *p.sched_reset = 0;
   const int num_kb = (p.K + BK - 1) / BK;
   constexpr uint32_t A_BYTES = TM * BK * 4;      // 32 KB
 
@@ -1114,11 +1118,13 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
   }
+  gt_let_next_kernel_start();
   tc_fence_before();
   __syncwarp();
   cluster_sync_all();                    // both CTAs' barriers exist before either signals the other's
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  gt_wait_for_previous_kernel();
   const int num_kb = (p.K + BK - 1) / BK;
   const uint32_t leader_full = map_to_cta(bar_full, 0);
   const uint32_t leader_tempty = map_to_cta(bar_tempty, 0);
@@ -1348,8 +1354,8 @@ int launch_cfg(gt_ctx* ctx, const CUtensorMap maps[5], const UmmaParams& p, int 
   using C = Cfg<BN, X3>;
   auto kern = gt_gemm_umma_kernel<BN, A_MN, B_MN, X3, A_GEN>;
   GT_SMEM_OPT_IN(ctx, kern, C::SMEM_BYTES);
-  kern<<<grid, A_GEN ? NUM_THREADS_AGEN : NUM_THREADS, C::SMEM_BYTES, stream>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p);
-  GT_CUDA_OK(ctx, cudaGetLastError());
+  GT_CUDA_OK(ctx, gt_launch_overlapped(kern, dim3(grid), dim3(A_GEN ? NUM_THREADS_AGEN : NUM_THREADS), C::SMEM_BYTES, stream,
+                                       maps[0], maps[1], maps[2], maps[3], maps[4], p));
   ctx->launches += 1;
   return GT_OK;
 }
@@ -1372,17 +1378,19 @@ void pair_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int 
   cfg->blockDim = dim3(PAIR_THREADS, 1, 1);
   cfg->dynamicSmemBytes = PAIR_SMEM_BYTES;
   cfg->stream = stream;
-  attr->id = cudaLaunchAttributeClusterDimension;
-  attr->val.clusterDim.x = 2; attr->val.clusterDim.y = 1; attr->val.clusterDim.z = 1;
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = gt_pdl_enabled() ? 1 : 0;
   cfg->attrs = attr;
-  cfg->numAttrs = 1;
+  cfg->numAttrs = 2;
 }
 
 template <class Kern>
 int pair_launch(gt_ctx* ctx, Kern kern, int clusters, cudaStream_t stream, const CUtensorMap maps[5], const UmmaParams& p) {
   GT_SMEM_OPT_IN(ctx, kern, PAIR_SMEM_BYTES);
-  cudaLaunchConfig_t cfg; cudaLaunchAttribute attr;
-  pair_launch_config<Kern>(&cfg, &attr, clusters, stream);
+  cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
+  pair_launch_config<Kern>(&cfg, attr, clusters, stream);
   GT_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[4], p));
   ctx->launches += 1;
   return GT_OK;
@@ -1394,8 +1402,9 @@ int pair_launch(gt_ctx* ctx, Kern kern, int clusters, cudaStream_t stream, const
 template <class Kern>
 int pair_clusters_query(gt_ctx* ctx, Kern kern) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return 0; }
-  cudaLaunchConfig_t cfg; cudaLaunchAttribute attr;
-  pair_launch_config<Kern>(&cfg, &attr, ctx->sm_count / 2, ctx->stream);
+  cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
+  pair_launch_config<Kern>(&cfg, attr, ctx->sm_count / 2, ctx->stream);
+  cfg.numAttrs = 1;                      // the occupancy question concerns the cluster shape only
   int n = 0;
   if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
   return n;
@@ -1735,8 +1744,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     auto launch256 = [&](auto kern, int idx) -> int {      // generic lambda: one instantiation (and one static) per kernel
       (void)idx;
       GT_SMEM_OPT_IN(ctx, kern, T256_SMEM_BYTES);
-      kern<<<grid, T256_THREADS, T256_SMEM_BYTES, stream>>>(maps[0], maps[1], maps[4], p);
-      GT_CUDA_OK(ctx, cudaGetLastError());
+      GT_CUDA_OK(ctx, gt_launch_overlapped(kern, dim3(grid), dim3(T256_THREADS), T256_SMEM_BYTES, stream, maps[0], maps[1], maps[4], p));
       ctx->launches += 1;
       return GT_OK;
     };

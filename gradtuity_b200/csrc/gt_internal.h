@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "gt_b200.h"
@@ -64,6 +65,36 @@ int gt_smem_opt_in(gt_ctx* ctx, const void* kernel, int bytes);
     int _gt_rc = gt_smem_opt_in((ctx), (const void*)(kern), (int)(bytes));      \
     if (_gt_rc != GT_OK) return _gt_rc;                                         \
   } while (0)
+
+// ---- programmatic dependent launch -------------------------------------------------------------------------
+// A kernel launched with gt_launch_overlapped may have its CTAs placed on SMs while the previous kernel of the
+// stream is still finishing (as that kernel's CTAs leave), run its set-up there (barrier initialisation, tensor
+// memory allocation, index arithmetic) and must then call gt_wait_for_previous_kernel() before it touches global
+// memory: the call returns once the previous kernel has completed and its writes are visible.  A kernel calls
+// gt_let_next_kernel_start() early so that its successor may be placed this way; both calls are no-ops in a
+// launch that has no such dependency.  Hides the launch latency and the prologue of ~300 short kernels per
+// training step.  GRADTUITY_NO_PDL=1 launches everything in plain stream order.
+#ifdef __CUDACC__
+__device__ __forceinline__ void gt_let_next_kernel_start() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void gt_wait_for_previous_kernel() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool gt_pdl_enabled() {
+  static const bool on = getenv("GRADTUITY_NO_PDL") == nullptr;
+  return on;
+}
+
+template <class... KArgs, class... Args>
+inline cudaError_t gt_launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = gt_pdl_enabled() ? 1 : 0;
+  cfg.attrs = &attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
 
 // One GEMM problem, fully resolved (used by both kernels).
 struct gt_gemm_args {

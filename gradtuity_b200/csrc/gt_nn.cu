@@ -295,6 +295,8 @@ __global__ void __launch_bounds__(256) layernorm_fwd_warp_kernel(const float* __
                                                                  float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                                  long long N, float eps) {
   constexpr int H = 128 * KV;
+  gt_let_next_kernel_start();
+  gt_wait_for_previous_kernel();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long warps_total = (long long)gridDim.x * 8;
   for (long long row = (long long)blockIdx.x * 8 + warp; row < N; row += warps_total) {
@@ -390,9 +392,11 @@ __global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(float* __restri
                                                                  const float* __restrict__ gamma, long long N, int dx_accumulate) {
   constexpr int H = 128 * KV;
   __shared__ float sg[H], sb[H];
+  gt_let_next_kernel_start();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int j = threadIdx.x; j < H; j += 256) { sg[j] = 0.0f; sb[j] = 0.0f; }
   __syncthreads();
+  gt_wait_for_previous_kernel();
   float4 gam[KV], pg[KV], pb[KV];
 #pragma unroll
   for (int c = 0; c < KV; ++c) {
@@ -731,7 +735,7 @@ extern "C" int gt_layernorm(gt_ctx* ctx, float* y, float* mean, float* rstd, con
   if (al && H % 128 == 0 && H / 128 <= 8) {
     long long wb = (N + 7) / 8, cap = (long long)ctx->sm_count * 8;
     const unsigned nb = (unsigned)(wb < cap ? wb : cap);
-#define GT_LNF_CASE(KV_) case KV_: layernorm_fwd_warp_kernel<KV_><<<nb, 256, 0, ctx->stream>>>(x, gamma, beta, y, mean, rstd, N, eps); break
+#define GT_LNF_CASE(KV_) case KV_: GT_CUDA_OK(ctx, gt_launch_overlapped(layernorm_fwd_warp_kernel<KV_>, dim3(nb), dim3(256), 0, ctx->stream, x, gamma, beta, y, mean, rstd, N, eps)); break
     switch ((int)(H / 128)) { GT_LNF_CASE(1); GT_LNF_CASE(2); GT_LNF_CASE(3); GT_LNF_CASE(4); GT_LNF_CASE(5); GT_LNF_CASE(6); GT_LNF_CASE(7); GT_LNF_CASE(8); }
 #undef GT_LNF_CASE
     GT_LAUNCH_CHECK(ctx, 1);
@@ -760,7 +764,7 @@ extern "C" int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, floa
       } \
       const long long cap = (long long)ctx->sm_count * per_sm; \
       nb = (unsigned)(wb < cap ? wb : cap); \
-      layernorm_bwd_warp_kernel<KV_><<<nb, 256, 0, ctx->stream>>>(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, dx_accumulate); } break
+      GT_CUDA_OK(ctx, gt_launch_overlapped(layernorm_bwd_warp_kernel<KV_>, dim3(nb), dim3(256), 0, ctx->stream, dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, dx_accumulate)); } break
     switch ((int)(H / 128)) { GT_LN_CASE(1); GT_LN_CASE(2); GT_LN_CASE(3); GT_LN_CASE(4); GT_LN_CASE(5); GT_LN_CASE(6); GT_LN_CASE(7); GT_LN_CASE(8); }
 #undef GT_LN_CASE
     GT_LAUNCH_CHECK(ctx, 1);

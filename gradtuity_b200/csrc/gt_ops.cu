@@ -159,6 +159,8 @@ __global__ void __launch_bounds__(256) colsum_acc_kernel(float* __restrict__ db,
 __global__ void __launch_bounds__(256) colsum_acc_vec_kernel(float* __restrict__ db, const float* __restrict__ dy,
                                                              long long rows, int cols, long long ld, int rows_per_block) {
   __shared__ float4 red[8][32];
+  gt_let_next_kernel_start();
+  gt_wait_for_previous_kernel();
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int c = (blockIdx.x * 32 + cx) * 4;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
@@ -393,8 +395,7 @@ extern "C" int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t ro
     if (want > 65535) want = 65535;
     const int rpbv = (int)((rows + want - 1) / want);
     const unsigned gyv = (unsigned)((rows + rpbv - 1) / rpbv);
-    colsum_acc_vec_kernel<<<dim3(gxv, gyv), 256, 0, ctx->stream>>>(db, dy, rows, (int)cols, ld, rpbv);
-    GT_CUDA_OK(ctx, cudaGetLastError());
+    GT_CUDA_OK(ctx, gt_launch_overlapped(colsum_acc_vec_kernel, dim3(gxv, gyv), dim3(256), 0, ctx->stream, db, dy, rows, (int)cols, ld, rpbv));
     ctx->launches += 1;
     return GT_OK;
   }
