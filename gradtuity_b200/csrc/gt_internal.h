@@ -25,6 +25,7 @@ struct gt_ctx {
   int* d_sched;               // ring of GT_SCHED_RING work-unit counters for dynamically scheduled launches (zero when idle)
   long long sched_seq;        // launches that took a counter so far
   int dist_active;            // a process group exists: collectives may hold SMs while GEMMs are launched
+  void* block_cache;          // host-side free lists of gt_malloc blocks, by size (gt_runtime.cu)
   cudaStream_t h2d_stream, d2h_stream;   // copy streams of gt_gemm_host (created on first use)
   cudaEvent_t host_ev[8];                // its events
   gt_encode_tiled_fn encode_tiled;
@@ -120,19 +121,33 @@ int gt_gemm_fma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 int gt_gemm_umma_launch(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t stream);
 bool gt_gemm_umma_eligible(const gt_gemm_args& g);
 
-// d/dx of the tanh-form GELU (gradtuity/kernels_cuda/elemwise_kernels.py:127-137).
-__device__ __forceinline__ float gt_gelu_tanh_grad(float x) {
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
-  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
-  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+// GELU, tanh form (gradtuity/kernels_cuda/elemwise_kernels.py:104-137):
+//     gelu(x) = 0.5 x (1 + tanh(u)),  u = sqrt(2/pi) (x + 0.044715 x^3).
+// With tanh(u) = 1 - 2 r, r = 1 / (1 + e^(2u)), this is gelu(x) = x - x r = x s with s = 1 - r the logistic function of
+// 2u, and d/dx gelu = s + x s r (2 u'), 2u' = 2 sqrt(2/pi) (1 + 3 * 0.044715 x^2).  The same function as the
+// reference's two-branch form, in 7 (forward) and 12 (derivative) instructions with one ex2 and one rcp each: the
+// GEMM epilogues that apply them are bound by the instructions they issue.  e^(2u) overflowing to +inf gives r = 0
+// (gelu = x), underflowing to 0 gives r = 1 (gelu = 0); both products with r stay finite.
+#ifdef __CUDACC__
+__device__ __forceinline__ float gt_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float gt_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+// r = 1 / (1 + e^(2u)); the constants fold 2 sqrt(2/pi) log2(e) into the cubic's coefficients
+__device__ __forceinline__ float gt_gelu_r(float x, float x2) {
+  const float w = x * fmaf(x2, 0.1029432395800235f, 2.302208198144325f);
+  return gt_rcp(1.0f + gt_ex2(w));
 }
 
-// GELU, tanh form: gradtuity/kernels_cuda/elemwise_kernels.py:104-125.
-__device__ __forceinline__ float gt_gelu_tanh(float x) {
-  // tanh(u) = 1 - 2 / (1 + exp(2u)): the same function as the reference's two-branch form, written
-  // without the branch and with the fast divide (exp overflow gives 2/inf = 0, i.e. tanh = 1).
-  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = 1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * u));
-  return 0.5f * x * (1.0f + t);
+__device__ __forceinline__ float gt_gelu_tanh_grad(float x) {
+  const float x2 = x * x;
+  const float r = gt_gelu_r(x, x2);
+  const float s = 1.0f - r;
+  const float du2 = fmaf(x2, 0.21406444881780076f, 1.5957691216057308f);
+  return fmaf(x * s, r * du2, s);
 }
+
+__device__ __forceinline__ float gt_gelu_tanh(float x) {
+  const float r = gt_gelu_r(x, x * x);
+  return fmaf(-x, r, x);
+}
+#endif

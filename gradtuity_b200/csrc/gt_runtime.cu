@@ -8,6 +8,7 @@
 
 #include <mutex>
 #include <unordered_map>
+#include <vector>
 
 #include <stdlib.h>
 
@@ -29,6 +30,25 @@ extern "C" const char* gt_strerror(int status) {
 }
 
 extern "C" const char* gt_last_error(gt_ctx* ctx) { return ctx ? ctx->last_error : "null context"; }
+
+namespace {
+struct BlockCache {
+  std::mutex lock;
+  std::unordered_map<size_t, std::vector<void*>> free_by_size;
+  std::unordered_map<void*, size_t> size_of;       // blocks handed out by gt_malloc, live or cached
+  size_t cached_bytes = 0;
+  size_t limit_bytes = (size_t)65536 << 20;
+  bool enabled = true;
+};
+
+void block_cache_flush(gt_ctx* ctx, BlockCache* bc) {
+  for (auto& kv : bc->free_by_size) {
+    for (void* q : kv.second) { cudaFreeAsync(q, ctx->stream); bc->size_of.erase(q); }
+    kv.second.clear();
+  }
+  bc->cached_bytes = 0;
+}
+}  // namespace
 
 extern "C" int gt_init(int device, gt_ctx** out) {
   if (!out || device < 0) return GT_ERR_INVALID_ARG;
@@ -54,6 +74,13 @@ extern "C" int gt_init(int device, gt_ctx** out) {
   if (cudaMalloc((void**)&ctx->d_sched, GT_SCHED_RING * sizeof(int)) != cudaSuccess) { cudaFree(ctx->d_status); free(ctx); return GT_ERR_CUDA; }
   cudaMemset(ctx->d_sched, 0, GT_SCHED_RING * sizeof(int));
   ctx->sched_seq = 0;
+  {
+    BlockCache* bc = new BlockCache();
+    bc->enabled = getenv("GRADTUITY_NO_ALLOC_CACHE") == nullptr;
+    const char* mb = getenv("GRADTUITY_ALLOC_CACHE_MB");
+    if (mb && atoll(mb) > 0) bc->limit_bytes = (size_t)atoll(mb) << 20;
+    ctx->block_cache = bc;
+  }
 
   // Keep freed blocks in the pool instead of returning them to the driver at every sync.
   cudaMemPool_t pool;
@@ -84,6 +111,12 @@ extern "C" int gt_destroy(gt_ctx* ctx) {
   if (!ctx) return GT_ERR_INVALID_ARG;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->block_cache) {
+    BlockCache* bc = (BlockCache*)ctx->block_cache;
+    block_cache_flush(ctx, bc);
+    delete bc;
+    ctx->block_cache = nullptr;
+  }
   if (ctx->scratch_event) cudaEventDestroy(ctx->scratch_event);
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->h2d_stream) {
@@ -159,22 +192,66 @@ int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes, cudaStream_t stream) {
 
 // ---- memory ---------------------------------------------------------------------------
 
+// gt_malloc / gt_free keep freed blocks in host-side free lists keyed by (rounded) size and hand them out again
+// without any CUDA call.  Every block is used on the context's compute stream, so a block freed after kernel A was
+// enqueued and handed to kernel B is ordered by the stream itself; this is the ordering the stream-ordered pool
+// underneath gave before, minus two driver calls per tensor, and, above all, minus the stream operations between
+// consecutive kernel launches that kept one kernel's set-up from overlapping its predecessor's tail.  A training
+// step asks for the same sizes every time, so after the first step every request is a hit.  The cache is emptied
+// (blocks go back to the CUDA pool) when it holds more than GRADTUITY_ALLOC_CACHE_MB (default 65536) or when the
+// pool cannot serve a new size.  GRADTUITY_NO_ALLOC_CACHE=1 turns it off.
+
 extern "C" int gt_malloc(gt_ctx* ctx, size_t nbytes, void** ptr) {
   if (!ctx || !ptr) return GT_ERR_INVALID_ARG;
   *ptr = nullptr;
   if (nbytes == 0) nbytes = 16;
-  cudaError_t e = cudaMallocAsync(ptr, nbytes, ctx->stream);
+  BlockCache* bc = (BlockCache*)ctx->block_cache;
+  const size_t rounded = (nbytes + 511) & ~(size_t)511;
+  if (bc && bc->enabled) {
+    std::lock_guard<std::mutex> guard(bc->lock);
+    auto it = bc->free_by_size.find(rounded);
+    if (it != bc->free_by_size.end() && !it->second.empty()) {
+      *ptr = it->second.back();
+      it->second.pop_back();
+      bc->cached_bytes -= rounded;
+      return GT_OK;
+    }
+  }
+  cudaError_t e = cudaMallocAsync(ptr, rounded, ctx->stream);
+  if (e == cudaErrorMemoryAllocation && bc && bc->enabled) {
+    // the pool is exhausted while we sit on cached blocks of other sizes: give them back and try once more
+    cudaGetLastError();
+    std::lock_guard<std::mutex> guard(bc->lock);
+    block_cache_flush(ctx, bc);
+    cudaStreamSynchronize(ctx->stream);
+    e = cudaMallocAsync(ptr, rounded, ctx->stream);
+  }
   if (e == cudaErrorMemoryAllocation) {
     cudaGetLastError();
     GT_FAIL(ctx, GT_ERR_NOMEM, "cudaMallocAsync(%zu bytes): out of memory", nbytes);
   }
   GT_CUDA_OK(ctx, e);
+  if (bc && bc->enabled) {
+    std::lock_guard<std::mutex> guard(bc->lock);
+    bc->size_of[*ptr] = rounded;
+  }
   return GT_OK;
 }
 
 extern "C" int gt_free(gt_ctx* ctx, void* ptr) {
   if (!ctx) return GT_ERR_INVALID_ARG;
   if (!ptr) return GT_OK;
+  BlockCache* bc = (BlockCache*)ctx->block_cache;
+  if (bc && bc->enabled) {
+    std::lock_guard<std::mutex> guard(bc->lock);
+    auto it = bc->size_of.find(ptr);
+    if (it != bc->size_of.end()) {
+      bc->free_by_size[it->second].push_back(ptr);
+      bc->cached_bytes += it->second;
+      if (bc->cached_bytes > bc->limit_bytes) block_cache_flush(ctx, bc);
+      return GT_OK;
+    }
+  }
   GT_CUDA_OK(ctx, cudaFreeAsync(ptr, ctx->stream));
   return GT_OK;
 }
