@@ -312,7 +312,7 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
 // per-element branches, a third of the instructions of the general form.  The epilogue warps are
 // instruction-bound on short-K problems (the score products, the 768-deep Linear layers), so this
 // is what their throughput depends on.
-template <int EPI, bool AUX>
+template <int EPI, bool AUX, bool UNIT_ALPHA>
 __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                         int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
                                                         uint8_t* tile, uint32_t tile_u32, bool add) {
@@ -328,7 +328,8 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
   __syncwarp();
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    float4 x = make_float4(alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2], alpha * v[4 * j + 3]);
+    float4 x = UNIT_ALPHA ? make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3])
+                          : make_float4(alpha * v[4 * j], alpha * v[4 * j + 1], alpha * v[4 * j + 2], alpha * v[4 * j + 3]);
     if (HAS_BIAS) {
       const float4 b = bias4[j];
       x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
@@ -361,7 +362,12 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const fl
                                                    uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
   // aux is an OUTPUT (pre-activation) only for the kinds that produce one, and never for a K share that merely adds
   const bool aux_out = p.aux != nullptr && epi == p.epilogue && epi != GT_EPI_BIAS_ADD && epi != GT_EPI_GELU_GRAD;
-#define GT_EPI_FAST(E, X) epilogue_chunk_tma_fast<E, X>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add)
+  // alpha == 1 (every Linear layer): the multiply is left out of the per-element work (warp-uniform choice)
+#define GT_EPI_FAST(E, X)                                                                                                       \
+  do {                                                                                                                          \
+    if (p.alpha == 1.0f) epilogue_chunk_tma_fast<E, X, true>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add);  \
+    else epilogue_chunk_tma_fast<E, X, false>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add); \
+  } while (0)
   if (nb + 32 <= p.N) {                              // warp-uniform
     switch (epi) {
       case GT_EPI_NONE:
@@ -1140,7 +1146,8 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tile_coords(p, unit, batch, tm, tn, ks);
         const int i0 = batch % p.batch0, i1 = batch / p.batch0;
         const int m0 = tm * TM + (int)rank * HALF, n0 = tn * TN + (int)rank * HALF;     // this CTA's halves
-        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+        int kb_lo, kb_hi;
+        k_range(p, tm, ks, num_kb, kb_lo, kb_hi);
         for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!wait_x(bar_empty + 8 * s, ph ^ 1u)) { ok = false; break; }
           if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * PAIR_STAGE_BYTES);
@@ -1189,8 +1196,10 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int acc = 0; uint32_t aph = 0;
       bool ok = true, any_issued = false;
       for (int unit = first_unit; ok && unit < p.num_tiles; unit += unit_step) {
-        const int ks = unit % p.ksplit;
-        const int kb_lo = ks * p.kb_per, kb_hi = min(num_kb, kb_lo + p.kb_per);
+        int batch, tm, tn, ks;
+        tile_coords(p, unit, batch, tm, tn, ks);
+        int kb_lo, kb_hi;
+        k_range(p, tm, ks, num_kb, kb_lo, kb_hi);
         if (!mbar_wait_cluster(bar_tempty + 8 * acc, aph ^ 1u, abort_flag, p.status)) { ok = false; break; }   // both CTAs drained it
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
@@ -1231,6 +1240,32 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint8_t* epi_bytes = epi_scratch + (warp - 2) * EPI_WARP_BYTES;
     const uint32_t epi_u32 = smem_u32(epi_bytes);
     int acc = 0; uint32_t aph = 0;
+    // Last-wave split (see gt_gemm_umma_kernel): the K shares of a last-wave tile ADD into C, so unless the call is
+    // C += ..., pair i zeroes the i-th such tile first, each CTA its own 128 rows, and publishes flag 2 i + rank.
+    if (p.tail_split > 1 && p.tail_zero && warp == 2) {
+      const int n_tail = (p.num_tiles - p.tail_first) / p.tail_split;
+      if (first_unit < n_tail) {
+        int batch, tm, tn, ks;
+        tile_coords(p, p.tail_first + first_unit * p.tail_split, batch, tm, tn, ks);
+#pragma unroll
+        for (int g = 0; g < 8; ++g) *reinterpret_cast<float4*>(epi_bytes + lane * 128 + (g << 4)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          const int i0 = batch % p.batch0, i1 = batch / p.batch0;
+          const int r_base = tm * TM + (int)rank * HALF;
+          for (int r = 0; r < HALF / 32; ++r)
+            for (int c = 0; c < TN / 32; ++c)
+              if (tn * TN + c * 32 < p.N && r_base + r * 32 < p.M)
+                tma_store_4d(&map_c, epi_u32, tn * TN + c * 32, r_base + r * 32, i0, i1, false);
+          tma_store_wait_all();
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          atomicExch(p.tail_flags + 2 * first_unit + (int)rank, p.tail_epoch);
+        }
+        __syncwarp();
+      }
+    }
     for (int unit = first_unit; unit < p.num_tiles; unit += unit_step) {
       int batch, tm, tn, ks;
       tile_coords(p, unit, batch, tm, tn, ks);
@@ -1242,9 +1277,27 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const long long row_off = batch_off + (long long)row * p.ldc;
       const bool row_ok = row < p.M;
       const float* unit_bias = p.bias ? p.bias + (long long)batch * p.bias_stride : nullptr;
-      // with split-K every share adds its partial sum into C; bias / residual go in with share 0
-      const int unit_epi = (p.ksplit > 1 && ks > 0) ? (int)GT_EPI_NONE : p.epilogue;
-      const bool unit_add = p.accumulate != 0 || p.ksplit > 1;
+      // a K share (split-K, or the split of a last-wave tile) adds its partial sum into C; bias / residual go in with share 0
+      const bool tail_unit = p.tail_split > 1 && ks >= 0;
+      const bool share = p.ksplit > 1 || tail_unit;
+      const int unit_epi = (share && ks > 0) ? (int)GT_EPI_NONE : p.epilogue;
+      const bool unit_add = p.accumulate != 0 || share;
+      if (tail_unit && p.tail_zero) {
+        // this CTA's half of the tile must have been zeroed before the share adds into it (bounded wait; normally long true)
+        bool gave_up = false;
+        if (lane == 0) {
+          const volatile int* flag = p.tail_flags + 2 * ((unit - p.tail_first) / p.tail_split) + (int)rank;
+          const long long t0 = clock64();
+          while (*flag != p.tail_epoch) {
+            if (*abort_flag) { gave_up = true; break; }
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) { *abort_flag = 1; atomicExch(p.status, GT_ERR_TIMEOUT); gave_up = true; break; }
+          }
+          __threadfence();
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
+        gave_up = __shfl_sync(0xffffffffu, gave_up ? 1 : 0, 0) != 0;
+        if (gave_up) break;
+      }
       if (!wait_x(bar_tfull + 8 * acc, aph)) break;
       tc_fence_after();
       if (row0 < p.M) {                       // warp-uniform: a 32-row block wholly below M has nothing to write
@@ -1688,11 +1741,11 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   // epilogue's TMA reduce-add (unless the call is C += ..., the kernel zeroes C under those tiles at its
   // start and the shares wait for that; see the epilogue warps).
   static const bool tail_off = getenv("GRADTUITY_GEMM_NO_TAIL_SPLIT") != nullptr;
-  if (!tail_off && !deterministic && !use256 && !x3 && !a_gen && ksplit == 1 && p.c_tma && nbatch == 1 && hints == 0 && !g.aux &&
-      (g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS) && num_kb >= 16 && tiles > ctx->sm_count) {
-    const int P = ctx->sm_count;
+  if (!tail_off && !deterministic && (!use256 || pair) && !x3 && !a_gen && ksplit == 1 && p.c_tma && nbatch == 1 && hints == 0 && !g.aux &&
+      (g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS) && num_kb >= 16 && tiles > workers) {
+    const int P = workers;                       // a pair counts once and uses two flags per tile
     const int tail = (int)(tiles % P);
-    if (tail > 0 && tail * 2 <= P) {
+    if (tail > 0 && tail * 2 <= P && tail * (pair ? 2 : 1) <= 240) {
       int sp = P / tail;
       if (sp > num_kb / 4) sp = num_kb / 4;
       if (sp > 8) sp = 8;

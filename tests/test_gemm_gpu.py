@@ -462,3 +462,40 @@ def test_3xtf32_error_does_not_grow_with_k(gt):
     for K in (1024, 8192):
         a, b, _ = U.make_operands("NT", 256, 256, K, seed=K)
         assert O.rel_frobenius(U.run_gemm("NT", a, b, precision="3xtf32"), O.gemm(a, b, "NT")) <= 5e-6
+
+
+def test_two_streams_share_one_context(gt):
+    """GEMMs of ONE context enqueued alternately on two streams: the scratch they share (the 3xTF32 operand copies,
+    the last-wave flags) is handed from stream to stream in order, so every result is right although nothing on the
+    host waits between the calls."""
+    import ctypes
+    from ctypes import byref, c_void_p
+
+    from gradtuity_b200 import _lib
+
+    rt = ctypes.CDLL("libcudart.so.12")
+    rt.cudaStreamCreateWithFlags.argtypes = [ctypes.POINTER(c_void_p), ctypes.c_uint]
+    rt.cudaStreamSynchronize.argtypes = [c_void_p]
+    rt.cudaStreamDestroy.argtypes = [c_void_p]
+    side = c_void_p()
+    assert rt.cudaStreamCreateWithFlags(byref(side), 1) == 0             # non-blocking
+    lib, ctx = _lib.load_library(), _lib.context()
+    cases = []
+    for i, (layout, M, N, K, prec) in enumerate([("NN", 384, 640, 520, "3xtf32"), ("NT", 8192, 768, 768, "tf32"),
+                                                 ("TN", 200, 136, 96, "3xtf32"), ("NN", 8192, 768, 768, "tf32"),
+                                                 ("NT", 640, 384, 1032, "3xtf32"), ("TN", 768, 768, 4096, "tf32")]):
+        a, b, _ = U.make_operands(layout, M, N, K, seed=70 + i)
+        da, db = U.DeviceBuffer(a), U.DeviceBuffer(b)
+        dc = U.DeviceBuffer(np.full((M, N), np.nan, np.float32))
+        cases.append((layout, M, N, K, prec, a, b, da, db, dc))
+    gt.device_status()
+    for rep in range(2):
+        for i, (layout, M, N, K, prec, a, b, da, db, dc) in enumerate(cases):
+            stream = side if (i + rep) % 2 else None                       # None: the context's own stream
+            _lib.check(lib.gt_gemm(ctx, U.LAYOUTS[layout], M, N, K, c_void_p(da.ptr), a.shape[1], c_void_p(db.ptr), b.shape[1],
+                                   c_void_p(dc.ptr), N, None, None, 1.0, 0, 0, U.PRECISIONS[prec], stream), "gt_gemm")
+    assert rt.cudaStreamSynchronize(side) == 0
+    gt.device_status()
+    for layout, M, N, K, prec, a, b, da, db, dc in cases:
+        assert O.rel_frobenius(dc.read((M, N)), O.gemm(a, b, layout)) <= U.TOL[prec], (layout, M, N, K, prec)
+    rt.cudaStreamDestroy(side)
