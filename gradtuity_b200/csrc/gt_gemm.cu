@@ -37,7 +37,11 @@ int run(gt_ctx* ctx, const gt_gemm_args& g, void* stream) {
   int rc = gt_gemm_validate(ctx, g);
   if (rc != GT_OK) return rc;
   cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
-  if (gt_gemm_umma_eligible(g)) return gt_gemm_umma_launch(ctx, g, s);
+  if (gt_gemm_umma_eligible(g)) {
+    rc = gt_gemm_umma_launch(ctx, g, s);
+    const int rel = gt_scratch_release(ctx, s);      // a caller's stream that used the context's scratch: mark the hand-over point
+    return rc != GT_OK ? rc : rel;
+  }
   if (g.epilogue == GT_EPI_BIAS_ADD || g.epilogue == GT_EPI_GELU_GRAD)
     GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm: the aux-reading epilogues need the tensor-core path (tf32 / 3xtf32, aligned B)");
   return gt_gemm_fma_launch(ctx, g, s);

@@ -1478,14 +1478,15 @@ int pair_max_clusters(gt_ctx* ctx, int layout) {
   return cached[ctx->device][layout];
 }
 
-// When the pair kernel is taken without being forced: problems with at least a 256 x 256 output whose
-// 256 x 256 tiles (times a possible K split) can keep most pairs busy.
+// When the pair kernel is taken without being forced.  Measured against the one-CTA kernels (tf32, NN / NT):
+// (8192, 3072, 768) +7 %, with bias + GELU +8 %, (8192, 2304, 768) +7 %, (8192, 768, 3072) +17 %, (8192, 768, 768) +3 %,
+// 4096^3 +2 %; but 2048^3 -26 % (64 tiles leave ten of the 74 pairs idle) and 8192^3 -5 % (a long main loop gains
+// nothing from the overlapped epilogue and pays the pair's extra signalling hops).  So: at least one full wave of
+// 256 x 256 tiles, and K up to 4096.
 bool pair_rule(const gt_gemm_args& g, long long tiles256, int clusters, int sms) {
   (void)sms;
   if (g.M < 256 || g.N < 256 || g.K < 256) return false;
-  const long long kb = (g.K + BK - 1) / BK;
-  const long long shares = kb / 16 > 8 ? 8 : (kb / 16 < 1 ? 1 : kb / 16);      // what split-K could add
-  return tiles256 * shares * 4 >= (long long)clusters * 3;
+  return tiles256 >= clusters && g.K <= 4096;
 }
 
 int pick_bn(const gt_gemm_args& g, int sms, bool x3, bool a_gen) {
@@ -1554,7 +1555,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
                       (!g.bias || ((uintptr_t)g.bias & 15) == 0);
   // CTA pairs (256 x 256 tile over two SMs).  GRADTUITY_GEMM_PAIR: 0 = never, 1 = whenever the kernel can serve
   // the problem, unset = the rule below.
-  static const int pair_mode = getenv("GRADTUITY_GEMM_PAIR") ? atoi(getenv("GRADTUITY_GEMM_PAIR")) : 0;
+  static const int pair_mode = getenv("GRADTUITY_GEMM_PAIR") ? atoi(getenv("GRADTUITY_GEMM_PAIR")) : 2;
   const int pair_clusters = (allow_pair && pair_mode != 0) ? pair_max_clusters(ctx, g.layout) : 0;
   const bool pair_can = pair_clusters > 0 && hints == 0 && !x3 && !a_gen && g.epilogue != GT_EPI_CAUSAL &&
                         getenv("GRADTUITY_GEMM_NO_TMA_STORE") == nullptr &&
@@ -1898,7 +1899,9 @@ extern "C" int gt_gemm_3xtf32_noalloc(gt_ctx* ctx, int layout, int64_t M, int64_
     g_noalloc_scratch_ptr[ctx->device] = p;
   }
   cudaStream_t s = stream ? (cudaStream_t)stream : ctx->stream;
-  return umma_launch_impl(ctx, g, s, g_noalloc_scratch_ptr[ctx->device], GT_NOALLOC_SCRATCH_FLOATS);
+  rc = umma_launch_impl(ctx, g, s, g_noalloc_scratch_ptr[ctx->device], GT_NOALLOC_SCRATCH_FLOATS);
+  const int rel = gt_scratch_release(ctx, s);
+  return rc != GT_OK ? rc : rel;
 }
 
 // ---- bounded-wait self test ---------------------------------------------------------------------

@@ -114,6 +114,10 @@ struct gt_gemm_args {
 // time.  Launches on one stream are ordered by the stream; a launch on a DIFFERENT stream than the previous
 // user is made to wait for everything enqueued so far on that stream.  Call before the launch that uses it.
 int gt_scratch_acquire(gt_ctx* ctx, cudaStream_t stream);
+// Call when an entry point that was given a caller's stream returns: records, on that stream, the point the next
+// user of the scratch on another stream has to wait for.  The caller's stream is never touched again afterwards,
+// so it may be destroyed once its work is done.
+int gt_scratch_release(gt_ctx* ctx, cudaStream_t stream);
 // gt_scratch_acquire + make the workspace at least nbytes large.
 int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes, cudaStream_t stream);
 int gt_gemm_validate(gt_ctx* ctx, const gt_gemm_args& g);

@@ -163,12 +163,22 @@ int gt_smem_opt_in(gt_ctx* ctx, const void* kernel, int bytes) {
 }
 
 int gt_scratch_acquire(gt_ctx* ctx, cudaStream_t stream) {
-  if (ctx->scratch_stream && ctx->scratch_stream != stream) {
-    if (!ctx->scratch_event) GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->scratch_event, cudaEventDisableTiming));
-    GT_CUDA_OK(ctx, cudaEventRecord(ctx->scratch_event, ctx->scratch_stream));
+  if (ctx->scratch_stream == stream) return GT_OK;
+  if (!ctx->scratch_event) GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->scratch_event, cudaEventDisableTiming));
+  if (ctx->scratch_stream) {
+    // The previous user's stream is touched only if it is the context's own (always alive); a caller's stream had
+    // the event recorded on it when its call returned (gt_scratch_release) and may be gone by now.
+    if (ctx->scratch_stream == ctx->stream) GT_CUDA_OK(ctx, cudaEventRecord(ctx->scratch_event, ctx->stream));
     GT_CUDA_OK(ctx, cudaStreamWaitEvent(stream, ctx->scratch_event, 0));
   }
   ctx->scratch_stream = stream;
+  return GT_OK;
+}
+
+int gt_scratch_release(gt_ctx* ctx, cudaStream_t stream) {
+  if (ctx->scratch_stream != stream || stream == ctx->stream) return GT_OK;
+  if (!ctx->scratch_event) GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->scratch_event, cudaEventDisableTiming));
+  GT_CUDA_OK(ctx, cudaEventRecord(ctx->scratch_event, stream));
   return GT_OK;
 }
 
@@ -177,9 +187,12 @@ int gt_workspace_reserve(gt_ctx* ctx, size_t nbytes, cudaStream_t stream) {
   int rc = gt_scratch_acquire(ctx, stream);
   if (rc != GT_OK) return rc;
   if (nbytes <= ctx->workspace_bytes) return GT_OK;
-  // Growing is rare (first call at a new largest size); it orders itself against earlier
-  // users of the old block by synchronising the streams that may still read it.
-  if (previous) GT_CUDA_OK(ctx, cudaStreamSynchronize(previous));
+  // Growing is rare (first call at a new largest size); it orders itself against earlier users of the old block
+  // on the host: the previous user's work (its event, if it was a caller's stream) and this stream's.
+  if (previous && previous != stream) {
+    if (previous == ctx->stream) GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    else GT_CUDA_OK(ctx, cudaEventSynchronize(ctx->scratch_event));
+  }
   GT_CUDA_OK(ctx, cudaStreamSynchronize(stream));
   if (ctx->workspace) GT_CUDA_OK(ctx, cudaFree(ctx->workspace));
   ctx->workspace = nullptr;
