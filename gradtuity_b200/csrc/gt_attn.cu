@@ -303,8 +303,13 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
           if (!dead) {
             tc_ld32(lane_base + (uint32_t)(sb * 128 + eset * 32), v);
             tc_wait_ld();
+            if (j < i) {                     // warp-uniform: no masked element left of the diagonal
 #pragma unroll
-            for (int t = 0; t < 32; ++t) { v[t] = (t < nvalid) ? v[t] * p.scale_log2 : -INFINITY; mx = fmaxf(mx, v[t]); }
+              for (int t = 0; t < 32; ++t) { v[t] *= p.scale_log2; mx = fmaxf(mx, v[t]); }
+            } else {
+#pragma unroll
+              for (int t = 0; t < 32; ++t) { v[t] = (t < nvalid) ? v[t] * p.scale_log2 : -INFINITY; mx = fmaxf(mx, v[t]); }
+            }
           }
           tc_fence_before();
           __syncwarp();
@@ -775,8 +780,13 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (!dead) {
           tc_ld32(lane_base + (uint32_t)(eset * 32), v);
           tc_wait_ld();
+          if (j < i) {                       // warp-uniform: a tile left of the diagonal has no masked element
 #pragma unroll
-          for (int t = 0; t < 32; ++t) pr[t] = (t < nvalid) ? ex2(fmaf(v[t], p.scale_log2, -lse2)) : 0.0f;
+            for (int t = 0; t < 32; ++t) pr[t] = ex2(fmaf(v[t], p.scale_log2, -lse2));
+          } else {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) pr[t] = (t < nvalid) ? ex2(fmaf(v[t], p.scale_log2, -lse2)) : 0.0f;
+          }
           tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
           tc_wait_ld();
         } else {
@@ -791,10 +801,11 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           float4 x;
-          x.x = to_tf32(pr[4 * g] * (v[4 * g] - delta) * p.scale);
-          x.y = to_tf32(pr[4 * g + 1] * (v[4 * g + 1] - delta) * p.scale);
-          x.z = to_tf32(pr[4 * g + 2] * (v[4 * g + 2] - delta) * p.scale);
-          x.w = to_tf32(pr[4 * g + 3] * (v[4 * g + 3] - delta) * p.scale);
+          // dS without its factor `scale`: dQ = scale * sum_j (P (dP - delta)) K takes it once, at the output
+          x.x = to_tf32(pr[4 * g] * (v[4 * g] - delta));
+          x.y = to_tf32(pr[4 * g + 1] * (v[4 * g + 1] - delta));
+          x.z = to_tf32(pr[4 * g + 2] * (v[4 * g + 2] - delta));
+          x.w = to_tf32(pr[4 * g + 3] * (v[4 * g + 3] - delta));
           *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = x;
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -815,7 +826,8 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         __syncwarp();
 #pragma unroll
         for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
+              make_float4(p.scale * v[4 * g], p.scale * v[4 * g + 1], p.scale * v[4 * g + 2], p.scale * v[4 * g + 3]);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
@@ -964,23 +976,35 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         } else {
         tc_ld32(lane_base + (uint32_t)(eset * 32), v);
         tc_wait_ld();
+        if (i > j) {                         // warp-uniform: every query of the block may see every key of ours
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 l = l4[g];
-          pr[4 * g] = (4 * g >= first_valid) ? ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E)) : 0.0f;
-          pr[4 * g + 1] = (4 * g + 1 >= first_valid) ? ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E)) : 0.0f;
-          pr[4 * g + 2] = (4 * g + 2 >= first_valid) ? ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E)) : 0.0f;
-          pr[4 * g + 3] = (4 * g + 3 >= first_valid) ? ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E)) : 0.0f;
+          for (int g = 0; g < 8; ++g) {
+            const float4 l = l4[g];
+            pr[4 * g] = ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E));
+            pr[4 * g + 1] = ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E));
+            pr[4 * g + 2] = ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E));
+            pr[4 * g + 3] = ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E));
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const float4 l = l4[g];
+            pr[4 * g] = (4 * g >= first_valid) ? ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E)) : 0.0f;
+            pr[4 * g + 1] = (4 * g + 1 >= first_valid) ? ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E)) : 0.0f;
+            pr[4 * g + 2] = (4 * g + 2 >= first_valid) ? ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E)) : 0.0f;
+            pr[4 * g + 3] = (4 * g + 3 >= first_valid) ? ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E)) : 0.0f;
+          }
         }
         tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
         tc_wait_ld();
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const float4 d = d4[g];
-          v[4 * g] = pr[4 * g] * (v[4 * g] - d.x) * p.scale;
-          v[4 * g + 1] = pr[4 * g + 1] * (v[4 * g + 1] - d.y) * p.scale;
-          v[4 * g + 2] = pr[4 * g + 2] * (v[4 * g + 2] - d.z) * p.scale;
-          v[4 * g + 3] = pr[4 * g + 3] * (v[4 * g + 3] - d.w) * p.scale;
+          // dS^T without its factor `scale`: dK = scale * sum_i (P (dP - delta))^T Q takes it once, at the output
+          v[4 * g] = pr[4 * g] * (v[4 * g] - d.x);
+          v[4 * g + 1] = pr[4 * g + 1] * (v[4 * g + 1] - d.y);
+          v[4 * g + 2] = pr[4 * g + 2] * (v[4 * g + 2] - d.z);
+          v[4 * g + 3] = pr[4 * g + 3] * (v[4 * g + 3] - d.w);
         }
         }
         tc_fence_before();
@@ -1018,9 +1042,11 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), v);
         tc_wait_ld();
         tc_fence_before();
+        const float out_scale = eset < 2 ? 1.0f : p.scale;       // dK carries the factor its dS^T tiles left out
 #pragma unroll
         for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
+              make_float4(out_scale * v[4 * g], out_scale * v[4 * g + 1], out_scale * v[4 * g + 2], out_scale * v[4 * g + 3]);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) {
