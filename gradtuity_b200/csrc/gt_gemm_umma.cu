@@ -748,7 +748,8 @@ gt_gemm_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // a K share of a last-wave tile adds its partial sum into C; the bias goes in with share 0
       const bool tail_unit = p.tail_split > 1 && ks >= 0;
       const bool unit_add = p.accumulate != 0 || tail_unit;
-      const int unit_epi = (tail_unit && ks > 0) ? (int)GT_EPI_NONE : p.epilogue;
+      // bias and residual belong to one share; the gelu' factor multiplies the whole sum, so every share applies it
+      const int unit_epi = (tail_unit && ks > 0 && p.epilogue != GT_EPI_GELU_GRAD) ? (int)GT_EPI_NONE : p.epilogue;
       if (tail_unit && p.tail_zero) {
         // the tile must have been zeroed before this share adds into it (bounded wait; normally already true)
         if (lane == 0) {
@@ -1280,7 +1281,8 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // a K share (split-K, or the split of a last-wave tile) adds its partial sum into C; bias / residual go in with share 0
       const bool tail_unit = p.tail_split > 1 && ks >= 0;
       const bool share = p.ksplit > 1 || tail_unit;
-      const int unit_epi = (share && ks > 0) ? (int)GT_EPI_NONE : p.epilogue;
+      // the gelu' factor multiplies the whole sum, so every share applies it
+      const int unit_epi = (share && ks > 0 && p.epilogue != GT_EPI_GELU_GRAD) ? (int)GT_EPI_NONE : p.epilogue;
       const bool unit_add = p.accumulate != 0 || share;
       if (tail_unit && p.tail_zero) {
         // this CTA's half of the tile must have been zeroed before the share adds into it (bounded wait; normally long true)
@@ -1742,8 +1744,13 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   // epilogue's TMA reduce-add (unless the call is C += ..., the kernel zeroes C under those tiles at its
   // start and the shares wait for that; see the epilogue warps).
   static const bool tail_off = getenv("GRADTUITY_GEMM_NO_TAIL_SPLIT") != nullptr;
-  if (!tail_off && !deterministic && (!use256 || pair) && !x3 && !a_gen && ksplit == 1 && p.c_tma && nbatch == 1 && hints == 0 && !g.aux &&
-      (g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS) && num_kb >= 16 && tiles > workers) {
+  // Epilogues that survive a cut along K: none, bias and residual add (applied by share 0 only) and the gelu' factor (a
+  // product with the whole sum: every share applies it); an aux OUTPUT (stored pre-activation) does not.
+  const bool tail_epi_ok = g.epilogue == GT_EPI_NONE || g.epilogue == GT_EPI_BIAS || g.epilogue == GT_EPI_BIAS_ADD ||
+                           g.epilogue == GT_EPI_GELU_GRAD;
+  const bool aux_is_input = g.epilogue == GT_EPI_BIAS_ADD || g.epilogue == GT_EPI_GELU_GRAD;
+  if (!tail_off && !deterministic && (!use256 || pair) && !x3 && !a_gen && ksplit == 1 && p.c_tma && nbatch == 1 && hints == 0 &&
+      (!g.aux || aux_is_input) && tail_epi_ok && num_kb >= 16 && tiles > workers) {
     const int P = workers;                       // a pair counts once and uses two flags per tile
     const int tail = (int)(tiles % P);
     if (tail > 0 && tail * 2 <= P && tail * (pair ? 2 : 1) <= 240) {

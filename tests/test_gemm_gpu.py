@@ -206,12 +206,14 @@ def test_last_wave_split_shapes(gt, layout, M, N, K, epilogue, acc):
         assert O.rel_frobenius((out - base)[sl], (ref - base)[sl]) <= U.TOL["tf32"]
 
 
-@pytest.mark.parametrize("layout,M,N,K", [("NN", 300, 200, 96), ("NT", 8192, 3072, 768), ("NN", 8192, 768, 3072), ("TN", 260, 132, 64)])
+@pytest.mark.parametrize("layout,M,N,K", [("NN", 300, 200, 96), ("NT", 8192, 3072, 768), ("NN", 8192, 768, 3072), ("TN", 260, 132, 64),
+                                          ("NT", 2560, 2048, 4128), ("NN", 8192, 768, 768)])
 @pytest.mark.parametrize("kind", ["bias_add", "gelu_grad"])
 def test_aux_reading_epilogues(gt, layout, M, N, K, kind):
     """BIAS_ADD: C = A B + bias + aux (Linear + residual add); GELU_GRAD: C = (A B) * gelu'(aux) (dX of the second
-    MLP layer with the GELU backward).  Shapes with partial chunks (general form) and the two GPT-2 MLP shapes
-    (128 x 256 tiles and the 256 x 256-tile kernel)."""
+    MLP layer with the GELU backward).  Shapes with partial chunks (general form), the two GPT-2 MLP shapes and
+    the 768-wide projection (CTA pairs with their last wave cut along K: the residual goes in with share 0, the
+    gelu' factor with every share), and a long-K shape that takes the same split in the one-CTA kernel."""
     from gradtuity_b200 import _lib, gemm as G
 
     a, b, rng = U.make_operands(layout, M, N, K, seed=M + N)
