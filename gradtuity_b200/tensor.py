@@ -527,15 +527,16 @@ class Tensor:
 
     def _linear_backward(self, x: "Tensor", weight: "Tensor", bias: "Tensor", dz_ptr: int, M: int, K: int, N: int) -> None:
         """dX += dZ·Wᵀ (NT), dW += Xᵀ·dZ (TN), db += column sums of dZ (gradtuity/tensor.py:1628-1679)."""
+        if bias.requires_grad:
+            # first, while dZ (just written by the previous kernel) is still in L2: the column sums are memory-bound
+            ensure_grad(bias)
+            _call("gt_colsum_acc", _vp(bias.grad.ptr), _vp(dz_ptr), M, N, N)
         if x.requires_grad:
             ptr, acc = grad_target(x)
             _gemm.gemm(LAYOUT_NT, M, K, N, dz_ptr, N, weight.ptr, N, ptr, K, accumulate=acc)
         if weight.requires_grad:
             ptr, acc = grad_target(weight)
             _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dz_ptr, N, ptr, N, accumulate=acc)
-        if bias.requires_grad:
-            ensure_grad(bias)
-            _call("gt_colsum_acc", _vp(bias.grad.ptr), _vp(dz_ptr), M, N, N)
 
     def linear(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
         """Y = X @ W + b with W stored (in_features, out_features); bias fused into the GEMM
@@ -596,6 +597,10 @@ class Tensor:
                 if not group.written[i]:
                     group.slice_tensor(i, (M, N), zero=True)
             dy = group.storage.ptr
+            for i, b in enumerate(bs):          # first: dq / dk / dv were just written by the attention backward
+                if b.requires_grad:
+                    ensure_grad(b)
+                    _call("gt_colsum_acc", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
             if x.requires_grad:
                 ptr, acc = grad_target(x)
                 if not acc:
@@ -621,10 +626,6 @@ class Tensor:
                     for i, w in enumerate(ws):
                         if w.requires_grad:
                             _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dy + i * M * N * F32, N, w.grad.ptr, N, accumulate=True)
-            for i, b in enumerate(bs):
-                if b.requires_grad:
-                    ensure_grad(b)
-                    _call("gt_colsum_acc", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
 
         hub._set_graph(parents=(x,) + ws + bs, backward_fn=_hub_backward)
 
@@ -703,12 +704,12 @@ class Tensor:
             h.free(); pre.free()
 
         def _backward(g: "Tensor") -> None:
+            if b2.requires_grad:             # first: g is still in L2
+                ensure_grad(b2)
+                _call("gt_colsum_acc", _vp(b2.grad.ptr), _vp(g.ptr), M, N, N)
             if w2.requires_grad:
                 ptr, acc = grad_target(w2)
                 _gemm.gemm(LAYOUT_TN, I, N, M, h.ptr, I, g.ptr, N, ptr, N, accumulate=acc)
-            if b2.requires_grad:
-                ensure_grad(b2)
-                _call("gt_colsum_acc", _vp(b2.grad.ptr), _vp(g.ptr), M, N, N)
             h.free()
             if x.requires_grad or w1.requires_grad or b1.requires_grad:
                 with temp_storage(M * I * F32) as dpre:
