@@ -34,6 +34,8 @@ namespace {
 constexpr int AT_D = 64;                        // head dimension
 constexpr int AT_TILE = 128;                    // queries per item, keys per tile
 constexpr int AT_THREADS = 576;                 // producer warp, MMA warp, 16 softmax warps (four per tensor-memory lane quarter)
+// 576 threads = 18 warps, which the register file allots as 20: 96 registers per thread is the most a launch accepts
+// (112 is refused: "too many resources requested"), hence the few spilled values in the softmax loops.
 constexpr int AT_SOFTMAX_WARPS = 16;
 constexpr int AT_SLOT_BYTES = 32768;            // one 128 x 64 fp32 operand tile
 constexpr int AT_SLOTS = 4;
