@@ -2,7 +2,8 @@
 // tensor memory, fused epilogue.
 //
 // One persistent CTA (320 threads) per SM walks a list of 128 x BN output tiles (BN = 64, 128, 256;
-// gt_gemm_umma256_kernel holds 256 x 256 tiles for large problems).  Inside a CTA:
+// gt_gemm_umma256_kernel holds 256 x 256 tiles for large, long-K problems; gt_gemm_pair_kernel holds a
+// 256 x 256 tile on a PAIR of CTAs, tcgen05 cta_group::2, for problems with K up to 4096).  Inside a CTA:
 //   warp 0     producer   one lane issues cp.async.bulk.tensor (TMA) loads of A and B k-blocks
 //                         (32 fp32 = one 128-byte swizzle row per k-block) into a ring of stages
 //   warp 1     MMA        one lane issues tcgen05.mma.kind::tf32 (K = 8 per instruction) into

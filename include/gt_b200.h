@@ -100,7 +100,11 @@ int         gt_sm_count(gt_ctx* ctx);
  * (0, or GT_ERR_TIMEOUT if a kernel's bounded wait ran out) and clears it.               */
 int         gt_device_status(gt_ctx* ctx, int* status);
 
-int gt_malloc(gt_ctx* ctx, size_t nbytes, void** ptr);   /* stream-ordered, pooled          */
+/* gt_malloc / gt_free: blocks come from the CUDA stream-ordered pool, ordered on the context's compute stream; freed
+ * blocks are kept in host-side free lists by size and handed out again without a CUDA call (GRADTUITY_NO_ALLOC_CACHE=1
+ * turns that off, GRADTUITY_ALLOC_CACHE_MB bounds it).  A block must only be used by work on the compute stream, or by
+ * work ordered behind it.                                                                                            */
+int gt_malloc(gt_ctx* ctx, size_t nbytes, void** ptr);
 int gt_free(gt_ctx* ctx, void* ptr);
 int gt_memset(gt_ctx* ctx, void* ptr, int value, size_t nbytes);
 int gt_memcpy_h2d(gt_ctx* ctx, void* dst, const void* src, size_t nbytes);   /* blocking   */
@@ -128,6 +132,13 @@ int gt_event_elapsed_ms(gt_ctx* ctx, void* start, void* stop, float* ms); /* syn
  *   accumulate = 1 : C += epilogue(alpha * A*B)      (reference *_acc kernels)
  *   bias : length N, required for the BIAS* epilogues, else NULL
  *   aux  : optional (M,N) buffer, leading dimension ldc, that receives the pre-activation
+ *   stream : NULL = the context's compute stream.  One context serves one stream at a time: the scratch the
+ *            context owns (3xTF32 operand copies, split-K partials, last-wave flags) is handed from stream to
+ *            stream in order (a launch on another stream than the previous user waits, on the device, for what
+ *            that stream had been given); a caller's stream is not touched again after the call returns.
+ * Kernel choice (tile 128 x 64 / 128 / 256 on one CTA, 256 x 256 on one CTA or on a CTA pair, K shares) follows
+ * the problem's shape; GRADTUITY_GEMM_TRACE=1 prints it per launch, GRADTUITY_GEMM_PAIR=0|1,
+ * GRADTUITY_GEMM_DETERMINISTIC=1, GRADTUITY_GEMM_NO_TAIL_SPLIT=1 and GRADTUITY_NO_PDL=1 override parts of it.
  */
 int gt_gemm(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
             const float* A, int64_t lda, const float* B, int64_t ldb,
