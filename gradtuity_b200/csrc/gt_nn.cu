@@ -516,6 +516,79 @@ __global__ void __launch_bounds__(512) cross_entropy_fwd_kernel(const float* __r
     row_loss[row] = lse - xr[t];
   }
 }
+// Loss and gradient in one launch: pass 1 as cross_entropy_fwd_kernel, then, the row still being in L2 (the launch
+// asks for enough shared memory that only two 512-thread blocks share an SM: about 300 rows of 200 KB in flight, read
+// and written, against 126 MB of L2), pass 2 writes dlogits = scale * (softmax - onehot).  Saves the second pass over
+// HBM (1.65 GB for GPT-2's logits) and a launch; valid when the loss's upstream gradient is known at forward time.
+constexpr int CE_FUSED_SMEM = 100 * 1024;
+template <bool VEC>
+__global__ void __launch_bounds__(512) cross_entropy_fused_kernel(float* __restrict__ dlogits, long long ld_d,
+                                                                  const float* __restrict__ logits, long long ld_x,
+                                                                  const float* __restrict__ targets, float* __restrict__ row_loss,
+                                                                  float* __restrict__ row_lse, float scale, int C, int* status) {
+  __shared__ float red[33];
+  __shared__ float s_lse;
+  __shared__ int s_t;
+  const long long row = blockIdx.x;
+  const float* xr = logits + row * ld_x;
+  float* dr = dlogits + row * ld_d;
+  float m = -INFINITY, s = 0.0f;
+  if (VEC) {
+    const float4* x4 = reinterpret_cast<const float4*>(xr);
+    const int n4 = C >> 2;
+#pragma unroll 4
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+      const float4 v = x4[j];
+      const float vm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+      if (vm > m) { s *= __expf(m - vm); m = vm; }
+      s += (__expf(v.x - m) + __expf(v.y - m)) + (__expf(v.z - m) + __expf(v.w - m));
+    }
+    const int j = (n4 << 2) + threadIdx.x;
+    if (j < C) {
+      const float v = xr[j];
+      if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+    }
+  } else {
+    for (int j = threadIdx.x; j < C; j += blockDim.x) {
+      const float v = xr[j];
+      if (v > m) { s = s * __expf(m - v) + 1.0f; m = v; } else { s += __expf(v - m); }
+    }
+  }
+  const float gm = block_max_all(m, red);
+  s = (m == -INFINITY) ? 0.0f : s * __expf(m - gm);
+  s = block_sum_all(s, red);
+  if (threadIdx.x == 0) {
+    int t = (int)targets[row];
+    if (t < 0 || t >= C) { atomicExch(status, GT_ERR_INVALID_ARG); t = t < 0 ? 0 : C - 1; }
+    const float lse = gm + logf(s);
+    row_lse[row] = lse;
+    row_loss[row] = lse - xr[t];
+    s_lse = lse;
+    s_t = t;
+  }
+  __syncthreads();
+  const float lse = s_lse;
+  const int t = s_t;
+  int j0 = 0;
+  if (VEC) {
+    const float4* x4 = reinterpret_cast<const float4*>(xr);
+    float4* d4 = reinterpret_cast<float4*>(dr);
+    const int n4 = C >> 2;
+#pragma unroll 4
+    for (int j = threadIdx.x; j < n4; j += blockDim.x) {
+      const float4 x = x4[j];
+      float4 v;
+      v.x = scale * __expf(x.x - lse); v.y = scale * __expf(x.y - lse); v.z = scale * __expf(x.z - lse); v.w = scale * __expf(x.w - lse);
+      if ((t >> 2) == j) {
+        const int k = t & 3;
+        if (k == 0) v.x -= scale; else if (k == 1) v.y -= scale; else if (k == 2) v.z -= scale; else v.w -= scale;
+      }
+      d4[j] = v;
+    }
+    j0 = n4 << 2;
+  }
+  for (int j = j0 + threadIdx.x; j < C; j += blockDim.x) dr[j] = scale * (__expf(xr[j] - lse) - (j == t ? 1.0f : 0.0f));
+}
 // dlogits (+)= scale * (softmax - onehot)
 template <bool VEC>
 __global__ void __launch_bounds__(512) cross_entropy_bwd_kernel(float* __restrict__ dlogits, long long ld_d,
@@ -797,6 +870,31 @@ extern "C" int gt_cross_entropy(gt_ctx* ctx, float* loss, float* row_loss, float
     cross_entropy_fwd_kernel<true><<<(unsigned)B, 512, 0, ctx->stream>>>(logits, ld_logits, targets, row_loss, row_lse, (int)C, ctx->d_status);
   else
     cross_entropy_fwd_kernel<false><<<(unsigned)B, 512, 0, ctx->stream>>>(logits, ld_logits, targets, row_loss, row_lse, (int)C, ctx->d_status);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  int rc = gt_sum_all(ctx, loss, row_loss, B, 0);
+  if (rc != GT_OK) return rc;
+  if (mean) return gt_scale(ctx, loss, loss, 1.0f / (float)B, 1, 0);
+  return GT_OK;
+}
+
+// gt_cross_entropy and, in the same launch, dlogits = grad_scale * (softmax - onehot): grad_scale = upstream / B for a
+// mean loss whose upstream gradient is known (1 when the loss is what backward() starts from), upstream for a sum.
+extern "C" int gt_cross_entropy_fused(gt_ctx* ctx, float* loss, float* row_loss, float* row_lse, float* dlogits, int64_t ld_dlogits,
+                                      const float* logits, int64_t ld_logits, const float* targets, int64_t B, int64_t C, int mean,
+                                      float grad_scale) {
+  if (!ctx || !loss || !row_loss || !row_lse || !dlogits || !logits || !targets || B <= 0 || C <= 0 || B > 0x7fffffff ||
+      C > 0x7fffffff || ld_logits < C || ld_dlogits < C) return GT_ERR_INVALID_ARG;
+  const bool vec = (((uintptr_t)logits & 15) == 0) && ld_logits % 4 == 0 && (((uintptr_t)dlogits & 15) == 0) && ld_dlogits % 4 == 0;
+  if (vec) {
+    GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<true>, CE_FUSED_SMEM);
+    cross_entropy_fused_kernel<true><<<(unsigned)B, 512, CE_FUSED_SMEM, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss,
+                                                                                      row_lse, grad_scale, (int)C, ctx->d_status);
+  } else {
+    GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<false>, CE_FUSED_SMEM);
+    cross_entropy_fused_kernel<false><<<(unsigned)B, 512, CE_FUSED_SMEM, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss,
+                                                                                       row_lse, grad_scale, (int)C, ctx->d_status);
+  }
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
   int rc = gt_sum_all(ctx, loss, row_loss, B, 0);

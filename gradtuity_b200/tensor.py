@@ -355,6 +355,7 @@ class Tensor:
                 "backward() called on a tensor that doesn't require grad. Set requires_grad=True on leaf tensors."
             )
         self.grad = Tensor._ones_like(self)
+        self.grad._unit_seed = True          # ops that prepared their gradient for an upstream of exactly 1 check this
 
         visited: set[int] = set()
         topo: list[Tensor] = []
@@ -1047,11 +1048,30 @@ class Tensor:
         row_loss = empty_tensor((Bn,))
         row_lse = empty_tensor((Bn,))
         x_ptr, x_ld = self._rows()
-        _call("gt_cross_entropy", _vp(out.ptr), _vp(row_loss.ptr), _vp(row_lse.ptr), _vp(x_ptr), x_ld, _vp(targets.ptr), Bn, C,
-              1 if reduction == "mean" else 0)
+        grad_scale = (1.0 / Bn) if reduction == "mean" else 1.0
+        # When the logits will need a gradient and have none yet, the loss kernel writes it in the same launch (the row
+        # is read from HBM once instead of twice), for an upstream gradient of 1: what backward() seeds when this loss
+        # is where it starts.  Any other upstream value rescales the stored gradient in the backward.
+        early = None
+        if self.requires_grad and self.grad is None and Bn * C >= (1 << 20) and os.environ.get("GRADTUITY_CE_UNFUSED") is None:
+            early = empty_padded_tensor(self.shape, x_ld)
+            e_ptr, e_ld = early._rows()
+            _call("gt_cross_entropy_fused", _vp(out.ptr), _vp(row_loss.ptr), _vp(row_lse.ptr), _vp(e_ptr), e_ld, _vp(x_ptr), x_ld,
+                  _vp(targets.ptr), Bn, C, 1 if reduction == "mean" else 0, grad_scale)
+        else:
+            _call("gt_cross_entropy", _vp(out.ptr), _vp(row_loss.ptr), _vp(row_lse.ptr), _vp(x_ptr), x_ld, _vp(targets.ptr), Bn, C,
+                  1 if reduction == "mean" else 0)
         logits = self
 
         def _backward(g: "Tensor") -> None:
+            nonlocal early
+            if logits.requires_grad and early is not None and logits.grad is None:
+                if not getattr(g, "_unit_seed", False):
+                    e_ptr, e_ld = early._rows()
+                    _call("gt_scale_by_device_scalar", _vp(e_ptr), _vp(g.ptr), Bn * e_ld)
+                logits.grad, early = early, None
+                return
+            early = None
             if logits.requires_grad:
                 fresh = logits.grad is None
                 if fresh:

@@ -327,6 +327,13 @@ int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, const float
  * and the GEMMs that read dlogits take the TMA path. */
 int gt_cross_entropy(gt_ctx* ctx, float* loss, float* row_loss, float* row_lse, const float* logits,
                      int64_t ld_logits, const float* targets, int64_t B, int64_t C, int mean);
+/* gt_cross_entropy plus, in the same launch, dlogits = grad_scale * (softmax - onehot), written (not accumulated) at
+ * pitch ld_dlogits: the loss kernel and the gradient kernel of the reference (cross_entropy_kernel and
+ * cross_entropy_backward_kernel, gradtuity/tensor.py:1452-1525) share one pass over HBM.  For callers that know the
+ * loss's upstream gradient when they compute the loss (grad_scale = upstream / B for mean, upstream for sum).       */
+int gt_cross_entropy_fused(gt_ctx* ctx, float* loss, float* row_loss, float* row_lse, float* dlogits, int64_t ld_dlogits,
+                           const float* logits, int64_t ld_logits, const float* targets, int64_t B, int64_t C, int mean,
+                           float grad_scale);
 int gt_cross_entropy_backward(gt_ctx* ctx, float* dlogits, int64_t ld_dlogits, const float* logits,
                               int64_t ld_logits, const float* targets, const float* row_lse,
                               const float* upstream, float scale, int64_t B, int64_t C, int accumulate);

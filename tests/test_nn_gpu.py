@@ -92,6 +92,34 @@ def test_cross_entropy(T):
         T([1.0, 2.0]).cross_entropy(T([0.0]))
 
 
+@pytest.mark.parametrize("C", [30000, 32001])
+def test_cross_entropy_with_the_gradient_written_by_the_loss_kernel(T, C):
+    """Large logits: the loss kernel also writes dlogits (for an upstream gradient of 1); a loss that is scaled before
+    backward() starts gets the stored gradient rescaled; both against the float64 oracle, and against the two-kernel
+    path (GRADTUITY_CE_UNFUSED)."""
+    rng = np.random.default_rng(11)
+    B = 40
+    logits = (rng.standard_normal((B, C)) * 3).astype(np.float32)
+    tgt = rng.integers(0, C, B)
+    lr, probs = GO.cross_entropy_forward(logits.astype(np.float64), tgt)
+    want = GO.cross_entropy_backward(probs, tgt)
+    for factor in (None, 0.25):
+        tl = T.from_numpy(logits, requires_grad=True)
+        loss = tl.cross_entropy(T.from_numpy(tgt.astype(np.float32)))
+        assert loss.item() == pytest.approx(lr, rel=1e-6)
+        (loss if factor is None else loss.scale(factor)).backward()
+        assert rel(tl.grad.numpy(), want * (1.0 if factor is None else factor)) < 1e-5
+    s = T.from_numpy(logits, requires_grad=True)
+    ls = s.cross_entropy(T.from_numpy(tgt.astype(np.float32)), reduction="sum")
+    ls.backward()
+    assert ls.item() == pytest.approx(lr * B, rel=1e-6) and rel(s.grad.numpy(), want * B) < 1e-5
+    # a logits tensor that already holds a gradient takes the two-kernel path and accumulates
+    a = T.from_numpy(logits, requires_grad=True)
+    a.grad = T.from_numpy(np.ones((B, C), np.float32))
+    a.cross_entropy(T.from_numpy(tgt.astype(np.float32))).backward()
+    assert rel(a.grad.numpy(), want + 1.0) < 1e-5
+
+
 @pytest.mark.parametrize("B,H,S,D", [(2, 3, 256, 64), (1, 2, 200, 32), (2, 12, 128, 64)])
 def test_causal_attention_products(T, B, H, S, D):
     """Config 2 at reduced size: S = Q K^T/sqrt(d) masked, P, O = P V and dQ, dK, dV."""
