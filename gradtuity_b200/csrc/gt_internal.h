@@ -33,6 +33,10 @@ struct gt_ctx {
   size_t workspace_bytes;
   cudaStream_t scratch_stream;   // stream of the last launch that used the workspace or the tail flags (null: none yet)
   cudaEvent_t scratch_event;     // orders a launch on another stream behind that one (created on first switch)
+  cudaStream_t side_stream;      // second compute stream for small memory-bound kernels that run beside the GEMMs reading the same
+  cudaEvent_t side_fork;         // input (gt_colsum_acc_beside): forks from `stream` at side_fork, joins again at side_done
+  cudaEvent_t side_done;
+  int side_pending;              // work was put on side_stream since the last gt_join_beside
   int64_t launches;
   int tma_round;              // 1: tensor maps use the TFLOAT32 data type (TMA rounds), 0: FLOAT32
   char last_error[256];
@@ -61,6 +65,9 @@ struct gt_ctx {
 // Keyed by the kernel's address: kernels of one signature share a function-pointer TYPE, so a static flag inside
 // a template or a generic lambda would be shared between them.
 int gt_smem_opt_in(gt_ctx* ctx, const void* kernel, int bytes);
+
+// Makes ctx->stream wait for whatever was put on the side stream (gt_colsum_acc_beside); no-op when nothing was.
+extern "C" int gt_join_beside(gt_ctx* ctx);
 #define GT_SMEM_OPT_IN(ctx, kern, bytes)                                        \
   do {                                                                          \
     int _gt_rc = gt_smem_opt_in((ctx), (const void*)(kern), (int)(bytes));      \

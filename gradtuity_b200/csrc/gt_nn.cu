@@ -886,9 +886,10 @@ extern "C" int gt_cross_entropy_fused(gt_ctx* ctx, float* loss, float* row_loss,
   if (!ctx || !loss || !row_loss || !row_lse || !dlogits || !logits || !targets || B <= 0 || C <= 0 || B > 0x7fffffff ||
       C > 0x7fffffff || ld_logits < C || ld_dlogits < C) return GT_ERR_INVALID_ARG;
   const bool vec = (((uintptr_t)logits & 15) == 0) && ld_logits % 4 == 0 && (((uintptr_t)dlogits & 15) == 0) && ld_dlogits % 4 == 0;
+  static const int smem_kb = [] { const char* e = getenv("GRADTUITY_CE_FUSED_SMEM_KB"); return e ? atoi(e) : CE_FUSED_SMEM / 1024; }();
   if (vec) {
-    GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<true>, CE_FUSED_SMEM);
-    cross_entropy_fused_kernel<true><<<(unsigned)B, 512, CE_FUSED_SMEM, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss,
+    GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<true>, 200 * 1024);
+    cross_entropy_fused_kernel<true><<<(unsigned)B, 512, smem_kb * 1024, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss,
                                                                                       row_lse, grad_scale, (int)C, ctx->d_status);
   } else {
     GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<false>, CE_FUSED_SMEM);

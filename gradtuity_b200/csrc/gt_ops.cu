@@ -384,7 +384,45 @@ extern "C" int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, in
   return GT_OK;
 }
 
+static int colsum_acc_on(gt_ctx* ctx, cudaStream_t stream, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld);
+
 extern "C" int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  return colsum_acc_on(ctx, ctx->stream, db, dy, rows, cols, ld);
+}
+
+// The column sums of a Linear layer's dY are memory-bound, read what the dX and dW GEMMs that follow read, and write
+// only the bias gradient: put on a second stream that forks here, they run beside those GEMMs (whose persistent CTAs
+// leave room for small blocks on every SM) instead of in front of them.  gt_join_beside makes the compute stream wait
+// for them; call it before dY is freed or rewritten and before the bias gradient is read.
+extern "C" int gt_colsum_acc_beside(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  static const bool off = getenv("GRADTUITY_NO_SIDE_STREAM") != nullptr;
+  if (off) return colsum_acc_on(ctx, ctx->stream, db, dy, rows, cols, ld);
+  if (!ctx->side_stream) {
+    GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+    GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->side_fork, cudaEventDisableTiming));
+    GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->side_done, cudaEventDisableTiming));
+  }
+  GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_fork, ctx->stream));
+  GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->side_fork, 0));
+  const int rc = colsum_acc_on(ctx, ctx->side_stream, db, dy, rows, cols, ld);
+  // recorded even when the launch failed: a join must never wait on an event that was not recorded after its fork
+  GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_done, ctx->side_stream));
+  ctx->side_pending = 1;
+  return rc;
+}
+
+extern "C" int gt_join_beside(gt_ctx* ctx) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  if (ctx->side_pending) {
+    GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->side_done, 0));
+    ctx->side_pending = 0;
+  }
+  return GT_OK;
+}
+
+static int colsum_acc_on(gt_ctx* ctx, cudaStream_t stream, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld) {
   if (!ctx || !db || !dy || rows <= 0 || cols <= 0 || cols > 0x7fffffff || ld < cols) return GT_ERR_INVALID_ARG;
   if ((((uintptr_t)dy & 15) == 0) && cols % 4 == 0 && ld % 4 == 0) {
     const unsigned gxv = (unsigned)((cols + 127) / 128);
@@ -395,7 +433,7 @@ extern "C" int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t ro
     if (want > 65535) want = 65535;
     const int rpbv = (int)((rows + want - 1) / want);
     const unsigned gyv = (unsigned)((rows + rpbv - 1) / rpbv);
-    GT_CUDA_OK(ctx, gt_launch_overlapped(colsum_acc_vec_kernel, dim3(gxv, gyv), dim3(256), 0, ctx->stream, db, dy, rows, (int)cols, ld, rpbv));
+    GT_CUDA_OK(ctx, gt_launch_overlapped(colsum_acc_vec_kernel, dim3(gxv, gyv), dim3(256), 0, stream, db, dy, rows, (int)cols, ld, rpbv));
     ctx->launches += 1;
     return GT_OK;
   }
@@ -407,7 +445,7 @@ extern "C" int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t ro
   if (want_y > 65535) want_y = 65535;
   const int rpb = (int)((rows + want_y - 1) / want_y);
   const unsigned gy = (unsigned)((rows + rpb - 1) / rpb);
-  colsum_acc_kernel<<<dim3(gx, gy), 256, 0, ctx->stream>>>(db, dy, rows, (int)cols, ld, rpb);
+  colsum_acc_kernel<<<dim3(gx, gy), 256, 0, stream>>>(db, dy, rows, (int)cols, ld, rpb);
   GT_CUDA_OK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return GT_OK;

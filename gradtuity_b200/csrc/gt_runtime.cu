@@ -118,6 +118,12 @@ extern "C" int gt_destroy(gt_ctx* ctx) {
     ctx->block_cache = nullptr;
   }
   if (ctx->scratch_event) cudaEventDestroy(ctx->scratch_event);
+  if (ctx->side_stream) {
+    cudaStreamSynchronize(ctx->side_stream);
+    cudaStreamDestroy(ctx->side_stream);
+    cudaEventDestroy(ctx->side_fork);
+    cudaEventDestroy(ctx->side_done);
+  }
   if (ctx->workspace) cudaFree(ctx->workspace);
   if (ctx->h2d_stream) {
     cudaStreamDestroy(ctx->h2d_stream);
@@ -136,6 +142,7 @@ extern "C" int gt_sm_count(gt_ctx* ctx) { return ctx ? ctx->sm_count : 0; }
 
 extern "C" int gt_device_status(gt_ctx* ctx, int* status) {
   if (!ctx || !status) return GT_ERR_INVALID_ARG;
+  gt_join_beside(ctx);
   GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
   int h = 0;
   GT_CUDA_OK(ctx, cudaMemcpy(&h, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
@@ -254,6 +261,7 @@ extern "C" int gt_malloc(gt_ctx* ctx, size_t nbytes, void** ptr) {
 extern "C" int gt_free(gt_ctx* ctx, void* ptr) {
   if (!ctx) return GT_ERR_INVALID_ARG;
   if (!ptr) return GT_OK;
+  if (ctx->side_pending) gt_join_beside(ctx);     // the side stream may still read this block
   BlockCache* bc = (BlockCache*)ctx->block_cache;
   if (bc && bc->enabled) {
     std::lock_guard<std::mutex> guard(bc->lock);
@@ -284,6 +292,7 @@ extern "C" int gt_memcpy_h2d(gt_ctx* ctx, void* dst, const void* src, size_t nby
 
 extern "C" int gt_memcpy_d2h(gt_ctx* ctx, void* dst, const void* src, size_t nbytes) {
   if (!ctx || ((!dst || !src) && nbytes)) return GT_ERR_INVALID_ARG;
+  gt_join_beside(ctx);
   GT_CUDA_OK(ctx, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
   GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
   return GT_OK;
@@ -297,6 +306,7 @@ extern "C" int gt_memcpy_h2d_async(gt_ctx* ctx, void* dst, const void* src, size
 
 extern "C" int gt_memcpy_d2h_async(gt_ctx* ctx, void* dst, const void* src, size_t nbytes) {
   if (!ctx || ((!dst || !src) && nbytes)) return GT_ERR_INVALID_ARG;
+  gt_join_beside(ctx);
   GT_CUDA_OK(ctx, cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, ctx->stream));
   return GT_OK;
 }
@@ -309,6 +319,7 @@ extern "C" int gt_memcpy_d2d(gt_ctx* ctx, void* dst, const void* src, size_t nby
 
 extern "C" int gt_sync(gt_ctx* ctx) {
   if (!ctx) return GT_ERR_INVALID_ARG;
+  gt_join_beside(ctx);
   GT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
   return GT_OK;
 }

@@ -94,6 +94,8 @@ class GradPlan:
         numels = [p.numel for p in self.params]
         self.offsets, total = arena_offsets(numels)
         self.arena = self.mem.alloc_zeroed(max(total, 1))
+        if hasattr(self.arena, "_st"):
+            self.arena._st.grads_only = True          # zero_grad may clear neighbouring gradients with one memset
         for p, off in zip(self.params, self.offsets):
             self.mem.ensure_grad(p)
             self.mem.copy(self.arena.ptr + off * F32, p.grad.ptr, p.numel * F32)

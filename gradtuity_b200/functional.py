@@ -56,32 +56,49 @@ def randn(shape, requires_grad: bool = False, seed: int | None = None, std: floa
     return Tensor.from_numpy(a, requires_grad=requires_grad)
 
 
+GRAD_ALIGN = 256          # bytes; every gradient inside a block of gradients starts on this boundary
+
+
 def zero_grad(params: list[Tensor]) -> None:
-    """Zero every parameter's gradient, allocating it if absent (gradtuity/functional.py:206-229)."""
-    # Parameters that sit side by side in memory (the packed q / k / v weights of CausalSelfAttention) get
-    # their fresh gradients side by side too, so that a batched backward can address them as one batch.
-    i, n = 0, len(params)
-    while i < n:
-        p = params[i]
-        if not p.requires_grad:
-            i += 1
+    """Zero every parameter's gradient, allocating it if absent (gradtuity/functional.py:206-229).
+
+    Gradients that do not exist yet are carved out of ONE zero-filled block, in the order of `params` (so the
+    gradients of parameters that sit side by side in memory, the packed q / k / v weights of CausalSelfAttention,
+    sit side by side too and a batched backward can address them as one batch).  Existing gradients that are
+    neighbours inside such a block (or inside the data-parallel gradient arena) are cleared by one memset per run of
+    neighbours instead of one per parameter: one memset for a whole model after the first step."""
+    from .tensor import Storage, alloc_storage
+
+    fresh = [p for p in params if p.requires_grad and p.grad is None]
+    if fresh:
+        offsets, total = [], 0
+        for p in fresh:
+            offsets.append(total)
+            total += -(-p.numel * 4 // GRAD_ALIGN) * GRAD_ALIGN
+        block = alloc_storage(total, zero=True)
+        block.grads_only = True
+        for p, off in zip(fresh, offsets):
+            p.grad = Tensor._from_ptr(block.ptr + off, p.shape, owns_memory=False, base=block)
+        fresh_ids = {id(p) for p in fresh}
+    else:
+        fresh_ids = set()
+    runs: dict[int, list[tuple[int, int]]] = {}
+    for p in params:
+        if not p.requires_grad or id(p) in fresh_ids:
             continue
-        if p.grad is not None:
-            cuda_memset(p.grad.ptr, 0, p.grad.nbytes)
-            i += 1
-            continue
-        j = i + 1
-        while (j < n and params[j].requires_grad and params[j].grad is None
-               and params[j].ptr == params[j - 1].ptr + params[j - 1].numel * 4):
-            j += 1
-        if j - i == 1:
-            p.grad = zeros(p.shape)
+        base = p.grad._st.base
+        if base is not None and getattr(base, "grads_only", False):
+            runs.setdefault(id(base), []).append((p.grad._st.ptr, p.grad.nbytes))
         else:
-            from .tensor import Storage, alloc_storage
-            total = sum(q.numel for q in params[i:j]) * 4
-            block = alloc_storage(total, zero=True)
-            off = 0
-            for q in params[i:j]:
-                q.grad = Tensor._from_ptr(block.ptr + off, q.shape, owns_memory=False, base=block)
-                off += q.numel * 4
-        i = j
+            cuda_memset(p.grad.ptr, 0, p.grad.nbytes)
+    for spans in runs.values():
+        spans.sort()
+        start, end = spans[0][0], spans[0][0] + spans[0][1]
+        for ptr, nbytes in spans[1:]:
+            # a gap shorter than the alignment in front of an aligned start is padding: nothing else can live there
+            if ptr - end < GRAD_ALIGN and (ptr % GRAD_ALIGN == 0 or ptr == end) and ptr >= end:
+                end = ptr + nbytes
+            else:
+                cuda_memset(start, 0, end - start)
+                start, end = ptr, ptr + nbytes
+        cuda_memset(start, 0, end - start)

@@ -56,7 +56,7 @@ def _vp(ptr: int):
 class Storage:
     """GPU memory buffer: ptr, nbytes, and ownership (gradtuity/tensor.py:87-101)."""
 
-    __slots__ = ("ptr", "nbytes", "owns", "base")
+    __slots__ = ("ptr", "nbytes", "owns", "base", "grads_only")
 
     def __init__(self, ptr: int, nbytes: int, owns: bool = True, base: "Storage | None" = None) -> None:
         self.ptr = ptr
@@ -65,6 +65,9 @@ class Storage:
         # A non-owning view keeps its owner alive; with a pooled, stream-ordered allocator a
         # freed block can be handed out again at once, so a view must never outlive its owner.
         self.base = base
+        # True for a block that holds nothing but parameter gradients, each starting on a 256-byte boundary
+        # (functional.zero_grad, the data-parallel arena): neighbours in it may be cleared with one memset.
+        self.grads_only = False
 
     def free(self) -> None:
         if self.owns and self.ptr:
@@ -529,15 +532,17 @@ class Tensor:
     def _linear_backward(self, x: "Tensor", weight: "Tensor", bias: "Tensor", dz_ptr: int, M: int, K: int, N: int) -> None:
         """dX += dZ·Wᵀ (NT), dW += Xᵀ·dZ (TN), db += column sums of dZ (gradtuity/tensor.py:1628-1679)."""
         if bias.requires_grad:
-            # first, while dZ (just written by the previous kernel) is still in L2: the column sums are memory-bound
+            # the column sums are memory-bound and read what the two GEMMs read: they run beside them, on the side stream
             ensure_grad(bias)
-            _call("gt_colsum_acc", _vp(bias.grad.ptr), _vp(dz_ptr), M, N, N)
+            _call("gt_colsum_acc_beside", _vp(bias.grad.ptr), _vp(dz_ptr), M, N, N)
         if x.requires_grad:
             ptr, acc = grad_target(x)
             _gemm.gemm(LAYOUT_NT, M, K, N, dz_ptr, N, weight.ptr, N, ptr, K, accumulate=acc)
         if weight.requires_grad:
             ptr, acc = grad_target(weight)
             _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dz_ptr, N, ptr, N, accumulate=acc)
+        if bias.requires_grad:
+            _call("gt_join_beside")          # before dZ can be freed and the bias gradient read
 
     def linear(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
         """Y = X @ W + b with W stored (in_features, out_features); bias fused into the GEMM
@@ -601,7 +606,7 @@ class Tensor:
             for i, b in enumerate(bs):          # first: dq / dk / dv were just written by the attention backward
                 if b.requires_grad:
                     ensure_grad(b)
-                    _call("gt_colsum_acc", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
+                    _call("gt_colsum_acc_beside", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
             if x.requires_grad:
                 ptr, acc = grad_target(x)
                 if not acc:
@@ -627,6 +632,7 @@ class Tensor:
                     for i, w in enumerate(ws):
                         if w.requires_grad:
                             _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dy + i * M * N * F32, N, w.grad.ptr, N, accumulate=True)
+            _call("gt_join_beside")
 
         hub._set_graph(parents=(x,) + ws + bs, backward_fn=_hub_backward)
 
@@ -705,9 +711,9 @@ class Tensor:
             h.free(); pre.free()
 
         def _backward(g: "Tensor") -> None:
-            if b2.requires_grad:             # first: g is still in L2
+            if b2.requires_grad:             # beside the GEMMs that follow
                 ensure_grad(b2)
-                _call("gt_colsum_acc", _vp(b2.grad.ptr), _vp(g.ptr), M, N, N)
+                _call("gt_colsum_acc_beside", _vp(b2.grad.ptr), _vp(g.ptr), M, N, N)
             if w2.requires_grad:
                 ptr, acc = grad_target(w2)
                 _gemm.gemm(LAYOUT_TN, I, N, M, h.ptr, I, g.ptr, N, ptr, N, accumulate=acc)
@@ -720,6 +726,7 @@ class Tensor:
                     self._linear_backward(x, w1, b1, dpre.ptr, M, K, I)
             else:
                 pre.free()
+            _call("gt_join_beside")
             if residual is not None and residual.requires_grad:
                 pass_grad(residual, g)
 

@@ -277,6 +277,13 @@ int gt_add_scalar(gt_ctx* ctx, float* dst, const float* scalar, int64_t n);     
 int gt_add_bias(gt_ctx* ctx, float* out, const float* x, const float* bias, int64_t rows, int64_t cols);
 int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, int accumulate); /* deterministic */
 int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld); /* db[c] += sum_r dy[r,c] */
+/* The same sums put on a second stream of the context that forks from the compute stream at this call, so that they run
+ * beside the kernels launched next (the dX and dW GEMMs of the same Linear layer, which read the same dy) instead of in
+ * front of them.  gt_join_beside makes the compute stream wait for every such launch: call it before dy is freed or
+ * rewritten and before db is read by anything but another gt_colsum_acc_beside.  gt_sync, gt_device_status and the
+ * device-to-host copies join by themselves.  GRADTUITY_NO_SIDE_STREAM=1 turns the pair into gt_colsum_acc and a no-op. */
+int gt_colsum_acc_beside(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld);
+int gt_join_beside(gt_ctx* ctx);
 int gt_repack_rows(gt_ctx* ctx, float* dst, int64_t ld_dst, const float* src, int64_t ld_src, int64_t rows, int64_t cols); /* copy rows to another pitch */
 /* conv2d as im2col + GEMM (gradtuity/tensor.py:1906-2167; im2col_kernel_2d / col2im_kernel of
  * kernels_cuda/conv_kernels.py).  x is (N, C, H, W); col is (N * H_out * W_out, C * kH * kW) with rows

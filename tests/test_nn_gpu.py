@@ -359,3 +359,75 @@ def test_full_size_gpt2_fast_paths_track_the_conservative_paths():
     for a, b in zip(fast, slow):
         assert abs(a - b) <= 1e-3 * abs(b), (fast, slow)
     assert abs(fast[0] - np.log(50257.0)) < 0.2          # a freshly initialised model predicts about uniformly
+
+
+def test_column_sums_on_the_side_stream_and_the_join(gt, T):
+    """gt_colsum_acc_beside adds the same sums as gt_colsum_acc; the join orders the compute stream behind them, a free
+    of the summed buffer joins by itself, and a Linear backward (which uses the pair) gives the bias gradient of the
+    plain formula."""
+    from ctypes import c_void_p
+
+    from gradtuity_b200 import _lib
+    lib, ctx = _lib.load_library(), _lib.context()
+    rng = np.random.default_rng(5)
+    for rows, cols in [(8192, 768), (1000, 36), (33, 3072)]:
+        dy = rng.standard_normal((rows, cols)).astype(np.float32)
+        start = rng.standard_normal(cols).astype(np.float32)
+        d, a, b = T.from_numpy(dy), T.from_numpy(start), T.from_numpy(start)
+        for _ in range(3):            # several forks before one join
+            _lib.check(lib.gt_colsum_acc_beside(ctx, c_void_p(a.ptr), c_void_p(d.ptr), rows, cols, cols), "beside")
+            _lib.check(lib.gt_colsum_acc(ctx, c_void_p(b.ptr), c_void_p(d.ptr), rows, cols, cols), "plain")
+        _lib.check(lib.gt_join_beside(ctx), "join")
+        want = start.astype(np.float64) + 3 * dy.astype(np.float64).sum(0)
+        assert rel(a.numpy(), want) < 1e-5 and rel(b.numpy(), want) < 1e-5
+    # freed while the side stream may still read it: the free joins, and the block's next user cannot overtake the sums
+    big = rng.standard_normal((8192, 3072)).astype(np.float32)
+    d, acc = T.from_numpy(big), T.from_numpy(np.zeros(3072, np.float32))
+    _lib.check(lib.gt_colsum_acc_beside(ctx, c_void_p(acc.ptr), c_void_p(d.ptr), 8192, 3072, 3072), "beside")
+    d._st.free()
+    again = T.from_numpy(np.zeros((8192, 3072), np.float32))          # most likely the same block, rewritten at once
+    assert rel(acc.numpy(), big.astype(np.float64).sum(0)) < 1e-5
+    del again
+    x = rng.standard_normal((256, 64)).astype(np.float32)
+    w = rng.standard_normal((64, 48)).astype(np.float32) * 0.1
+    g = rng.standard_normal((256, 48)).astype(np.float32)
+    xt, wt, bt = T.from_numpy(x, requires_grad=True), T.from_numpy(w, requires_grad=True), T.from_numpy(np.zeros(48, np.float32), requires_grad=True)
+    xt.linear(wt, bt).mul(T.from_numpy(g)).sum().backward()
+    assert rel(bt.grad.numpy(), g.astype(np.float64).sum(0)) < 1e-5
+
+
+def test_zero_grad_clears_a_model_with_one_memset(gt, T, monkeypatch):
+    """Fresh gradients come out of one zero-filled block; later calls clear neighbours with one memset per run, leave a
+    gradient that lives elsewhere to its own memset, and never touch memory between two runs."""
+    from gradtuity_b200 import functional as F
+
+    rng = np.random.default_rng(6)
+    shapes = [(64, 48), (48,), (5, 7), (3,), (128, 128)]
+    params = [T.from_numpy(rng.standard_normal(s).astype(np.float32), requires_grad=True) for s in shapes]
+    frozen = T.from_numpy(np.ones((4, 4), np.float32))
+    F.zero_grad(params + [frozen])
+    assert frozen.grad is None
+    base = params[0].grad._st.base
+    assert all(p.grad._st.base is base and p.grad.ptr % 256 == 0 for p in params)
+    assert all(not p.grad.numpy().any() for p in params)
+    calls = []
+    real = F.cuda_memset
+    monkeypatch.setattr(F, "cuda_memset", lambda ptr, v, n: (calls.append((ptr, n)), real(ptr, v, n))[1])
+
+    def dirty():
+        for p in params:
+            p.grad = p.grad                       # keep the views
+            from gradtuity_b200.cuda_mem import cuda_memcpy_htod
+            cuda_memcpy_htod(p.grad.ptr, np.full(p.shape, 3.0, np.float32))
+    dirty()
+    F.zero_grad(params)
+    assert len(calls) == 1 and all(not p.grad.numpy().any() for p in params)
+    # a gradient that lives in its own buffer, and a hole in the middle of the block's parameters
+    del calls[:]
+    dirty()
+    own = T.from_numpy(np.full(shapes[1], 3.0, np.float32))
+    params[1].grad = own
+    F.zero_grad([params[0], params[1], params[3], params[4]])        # params[2] is not being cleared
+    assert len(calls) == 3                                            # [0]; [3..4]; the lone buffer
+    assert not own.numpy().any() and not params[0].grad.numpy().any() and not params[4].grad.numpy().any()
+    assert np.all(params[2].grad.numpy() == 3.0)
