@@ -63,11 +63,9 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float to_tf32(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
+// Round to tf32 (nearest, ties away from zero: what cvt.rna.tf32.f32 gives) with two integer instructions; the
+// conversion instruction shares the 16-lane unit with ex2, which these kernels already keep busy.
+__device__ __forceinline__ float to_tf32(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u); }
 
 // Item order: the query blocks with the most key tiles first, so the tail of the persistent loop is light.
 __device__ __forceinline__ void item_coords(const AttnParams& p, int item, int& i, int& h, int& b) {
@@ -97,6 +95,14 @@ __device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t sa, uint32_t sb
     tc_mma_tf32(d_tmem, make_smem_desc(sa + a_off, 16, 1024, 2), make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc,
                 (keep || kk) ? 1u : 0u);
   }
+}
+
+// D(128 x 64) (+)= A(128 x 128 in tensor memory, columns a_tmem .. a_tmem + 127) * B(128 x 64, MN-major as in mma_pv).
+__device__ __forceinline__ void mma_pv_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t sb, bool keep) {
+  constexpr uint32_t idesc = make_idesc(64, false, true);
+#pragma unroll
+  for (int kk = 0; kk < 16; ++kk)
+    tc_mma_tf32_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc, (keep || kk) ? 1u : 0u);
 }
 
 struct AttnSmem {
@@ -546,10 +552,14 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // tile that the following product reads as its K-major A operand.  The B operand of those products
 // (K, dO or Q, stored (rows, 64) with the head dimension contiguous) is MN-major: it is loaded a second
 // time with the five-dimensional map that lays it out in 32-wide chunks.
-constexpr int ATB_SLOTS = 3;
-constexpr int ATB_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATB_SLOTS * AT_SLOT_BYTES + AT_P_BYTES + 1024 + 512;
+constexpr int ATB_SLOTS = 3;                   // dK / dV kernel: ring slots beside K, V and the 64 KB P^T / dS^T tile
+constexpr int ATQ_SLOTS = 4;                   // dQ kernel: dS lives in tensor memory, so the ring gets a fourth slot
+constexpr int ATB_CTRL_BYTES = 1536;           // barriers, the tensor-memory address, the abort flag, 2 x 128 floats of statistics
+constexpr int ATB_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATB_SLOTS * AT_SLOT_BYTES + AT_P_BYTES + 1024 + ATB_CTRL_BYTES;
+constexpr int ATQ_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATQ_SLOTS * AT_SLOT_BYTES + AT_SLOT_BYTES + 1024 + ATB_CTRL_BYTES;
 
 struct BwdSmem {
+  int nslots;
   uint32_t fix0, fix1, ring, tile;
   uint8_t* tile_ptr;
   uint32_t bar_fix_full, bar_fix_empty, bar_ring_full, bar_ring_empty, bar_sdp_full, bar_sdp_empty;
@@ -559,34 +569,36 @@ struct BwdSmem {
   float* stats;
 };
 
-__device__ __forceinline__ BwdSmem carve_bwd(uint8_t* smem_raw) {
+// Layout: two fixed operand tiles | `nslots` ring slots | a tile of `tile_bytes` (P^T / dS^T, or the output staging) | control.
+__device__ __forceinline__ BwdSmem carve_bwd(uint8_t* smem_raw, int nslots, int tile_bytes) {
   BwdSmem s;
+  s.nslots = nslots;
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
   s.fix0 = base;
   s.fix1 = base + AT_SLOT_BYTES;
   s.ring = base + 2 * AT_SLOT_BYTES;
-  s.tile = s.ring + ATB_SLOTS * AT_SLOT_BYTES;
-  s.tile_ptr = aligned + (2 + ATB_SLOTS) * AT_SLOT_BYTES;
-  uint8_t* ctrl = s.tile_ptr + AT_P_BYTES;
+  s.tile = s.ring + nslots * AT_SLOT_BYTES;
+  s.tile_ptr = aligned + (2 + nslots) * AT_SLOT_BYTES;
+  uint8_t* ctrl = s.tile_ptr + tile_bytes;
   const uint32_t bars = smem_u32(ctrl);
   s.bar_fix_full = bars;        s.bar_fix_empty = bars + 8;
-  s.bar_ring_full = bars + 16;  s.bar_ring_empty = bars + 16 + 8 * ATB_SLOTS;
-  s.bar_sdp_full = bars + 64;   s.bar_sdp_empty = bars + 72;
-  s.bar_t1_full = bars + 80;    s.bar_t1_empty = bars + 88;
-  s.bar_t2_full = bars + 96;    s.bar_t2_empty = bars + 104;
-  s.bar_out_full = bars + 112;  s.bar_out_empty = bars + 120;
-  s.bar_group = bars + 128;     s.bar_drain = bars + 136;
-  s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 192);
-  s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 196);
-  s.stats = reinterpret_cast<float*>(s.tile_ptr);
+  s.bar_ring_full = bars + 16;  s.bar_ring_empty = bars + 16 + 8 * nslots;       // up to six slots below offset 128
+  s.bar_sdp_full = bars + 128;  s.bar_sdp_empty = bars + 136;
+  s.bar_t1_full = bars + 144;   s.bar_t1_empty = bars + 152;
+  s.bar_t2_full = bars + 160;   s.bar_t2_empty = bars + 168;
+  s.bar_out_full = bars + 176;  s.bar_out_empty = bars + 184;
+  s.bar_group = bars + 192;     s.bar_drain = bars + 200;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
+  s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 260);
+  s.stats = reinterpret_cast<float*>(ctrl + 512);
   return s;
 }
 
 __device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_arrivals) {
   if (threadIdx.x == 0) {
     mbar_init(sm.bar_fix_full, 1); mbar_init(sm.bar_fix_empty, 1);
-    for (int i = 0; i < ATB_SLOTS; ++i) { mbar_init(sm.bar_ring_full + 8 * i, 1); mbar_init(sm.bar_ring_empty + 8 * i, 1); }
+    for (int i = 0; i < sm.nslots; ++i) { mbar_init(sm.bar_ring_full + 8 * i, 1); mbar_init(sm.bar_ring_empty + 8 * i, 1); }
     mbar_init(sm.bar_sdp_full, 1); mbar_init(sm.bar_sdp_empty, AT_SOFTMAX_WARPS);
     mbar_init(sm.bar_t1_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_t1_empty, 1);
     mbar_init(sm.bar_t2_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_t2_empty, 1);
@@ -609,8 +621,8 @@ __device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_a
 // One ring load: a K-major tile (two boxes of 32 columns) or an MN-major tile (one five-dimensional box).
 __device__ __forceinline__ bool bwd_ring_load(const BwdSmem& sm, const AttnParams& p, long long& ring_it, const CUtensorMap* map,
                                               bool mn, int row0, int h, int b) {
-  const int slot = (int)(ring_it % ATB_SLOTS);
-  const uint32_t par = (uint32_t)((ring_it / ATB_SLOTS) & 1);
+  const int slot = (int)(ring_it % sm.nslots);
+  const uint32_t par = (uint32_t)((ring_it / sm.nslots) & 1);
   if (!mbar_wait(sm.bar_ring_empty + 8 * slot, par ^ 1u, sm.abort_flag, p.status)) return false;
   const uint32_t dst = sm.ring + slot * AT_SLOT_BYTES, full = sm.bar_ring_full + 8 * slot;
   mbar_expect_tx(full, AT_SLOT_BYTES);
@@ -624,14 +636,14 @@ __device__ __forceinline__ bool bwd_ring_load(const BwdSmem& sm, const AttnParam
   return true;
 }
 __device__ __forceinline__ void bwd_ring_drain(const BwdSmem& sm, long long ring_it) {
-  const long long first = ring_it > ATB_SLOTS ? ring_it - ATB_SLOTS : 0;
+  const long long first = ring_it > sm.nslots ? ring_it - sm.nslots : 0;
   for (long long r = first; r < ring_it; ++r) {
     const long long t0 = clock64();
-    while (!mbar_try_wait(sm.bar_ring_full + 8 * (int)(r % ATB_SLOTS), (uint32_t)((r / ATB_SLOTS) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+    while (!mbar_try_wait(sm.bar_ring_full + 8 * (int)(r % sm.nslots), (uint32_t)((r / sm.nslots) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
   }
 }
 __device__ __forceinline__ bool bwd_ring_wait(const BwdSmem& sm, const AttnParams& p, long long ring_it) {
-  return mbar_wait(sm.bar_ring_full + 8 * (int)(ring_it % ATB_SLOTS), (uint32_t)((ring_it / ATB_SLOTS) & 1), sm.abort_flag, p.status);
+  return mbar_wait(sm.bar_ring_full + 8 * (int)(ring_it % sm.nslots), (uint32_t)((ring_it / sm.nslots) & 1), sm.abort_flag, p.status);
 }
 
 // Item order of the key-block owner: key block 0 sees every query block, so it goes first.
@@ -650,7 +662,7 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
                       const __grid_constant__ CUtensorMap map_kmn, const __grid_constant__ CUtensorMap map_dq,
                       const AttnParams p, const int accumulate) {
   extern __shared__ uint8_t smem_raw[];
-  const BwdSmem sm = carve_bwd(smem_raw);
+  const BwdSmem sm = carve_bwd(smem_raw, ATQ_SLOTS, AT_SLOT_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   bwd_setup(sm, warp, 8);
   const uint32_t tmem_base = *sm.tmem_slot;
@@ -687,13 +699,13 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(sdp_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
         tc_fence_after();
-        int slot = (int)(ring_it % ATB_SLOTS);
+        int slot = (int)(ring_it % sm.nslots);
         mma_qk(tmem_base, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
-        slot = (int)(ring_it % ATB_SLOTS);
+        slot = (int)(ring_it % sm.nslots);
         mma_qk(tmem_base + 128u, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
@@ -713,10 +725,9 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
           if (!mbar_wait(sm.bar_t1_full, (uint32_t)(t1_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (j == 0 && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           tc_fence_after();
-          const int slot = (int)(ring_it % ATB_SLOTS);
-          mma_pv(tmem_base + 256u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, j != 0);     // dQ (+)= dS K
+          const int slot = (int)(ring_it % sm.nslots);
+          mma_pv_ts(tmem_base + 256u, tmem_base + 320u, sm.ring + slot * AT_SLOT_BYTES, j != 0);     // dQ (+)= dS K, dS from tensor memory
           tc_commit(sm.bar_ring_empty + 8 * slot);
           tc_commit(sm.bar_t1_empty);
           if (j == i) { tc_commit(sm.bar_out_full); ++o_it; }
@@ -750,28 +761,26 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       int i, h, b;
       item_coords(p, item, i, h, b);
       const int row = i * AT_TILE + r_local;
-      // delta = rowsum(dO * O): each of the row's four threads takes 16 of the 64 columns
-      float part = 0.0f;
-      {
-        const long long off = ((long long)b * p.S + row) * E + (long long)h * AT_D + eset * 16;
+      // delta = rowsum(dO * O), computed by the first of the row's four threads and handed to the others through
+      // shared memory (two sets of 128 values, by item parity, so one rendezvous per item is enough)
+      float* const dstat = sm.stats + (g_it & 1) * 128;
+      if (eset == 0) {
+        const long long off = ((long long)b * p.S + row) * E + (long long)h * AT_D;
         const float4* o4 = reinterpret_cast<const float4*>(p.o + off);
         const float4* g4 = reinterpret_cast<const float4*>(p.d_o + off);
+        float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float4 a = o4[t], g = g4[t];
-          part += (a.x * g.x + a.y * g.y) + (a.z * g.z + a.w * g.w);
+        for (int t = 0; t < 16; t += 2) {
+          const float4 a = o4[t], g = g4[t], a2 = o4[t + 1], g2 = g4[t + 1];
+          s0 += (a.x * g.x + a.y * g.y) + (a.z * g.z + a.w * g.w);
+          s1 += (a2.x * g2.x + a2.y * g2.y) + (a2.z * g2.z + a2.w * g2.w);
         }
+        dstat[r_local] = s0 + s1;
+        p.delta[((long long)b * p.H + h) * p.S + row] = s0 + s1;
       }
       const float lse2 = p.lse[((long long)b * p.H + h) * p.S + row] * AT_LOG2E;
-      // exchange through the (idle) dS tile: its last reader was the previous item's final dQ product
-      if (!mbar_wait(sm.bar_t1_empty, (uint32_t)(t1_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
-      if (lane == 0) tma_store_wait_read<0>();
       if (!group_sync()) { ok = false; break; }
-      sm.stats[eset * 128 + r_local] = part;
-      if (!group_sync()) { ok = false; break; }
-      const float delta = (sm.stats[r_local] + sm.stats[128 + r_local]) + (sm.stats[256 + r_local] + sm.stats[384 + r_local]);
-      if (eset == 0) p.delta[((long long)b * p.H + h) * p.S + row] = delta;
-      if (!group_sync()) { ok = false; break; }
+      const float delta = dstat[r_local];
       for (int j = 0; j <= i; ++j) {
         if (!mbar_wait(sm.bar_sdp_full, (uint32_t)(sdp_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
@@ -799,18 +808,15 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         __syncwarp();
         if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
         ++sdp_it;
-        if (j > 0 && !mbar_wait(sm.bar_t1_empty, (uint32_t)(t1_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        // dS without its factor `scale`: dQ = scale * sum_j (P (dP - delta)) K takes it once, at the output
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          float4 x;
-          // dS without its factor `scale`: dQ = scale * sum_j (P (dP - delta)) K takes it once, at the output
-          x.x = to_tf32(pr[4 * g] * (v[4 * g] - delta));
-          x.y = to_tf32(pr[4 * g + 1] * (v[4 * g + 1] - delta));
-          x.z = to_tf32(pr[4 * g + 2] * (v[4 * g + 2] - delta));
-          x.w = to_tf32(pr[4 * g + 3] * (v[4 * g + 3] - delta));
-          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) = x;
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int t = 0; t < 32; ++t) v[t] = to_tf32(pr[t] * (v[t] - delta));
+        // the dS columns of tensor memory are free once the previous dQ product (this item's or the last one's) has read them
+        if (!mbar_wait(sm.bar_t1_empty, (uint32_t)(t1_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        tc_st32(lane_base + 320u + (uint32_t)(eset * 32), v);
+        tc_wait_st();
+        tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(sm.bar_t1_full);
         ++t1_it;
@@ -857,7 +863,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                        const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
                        const AttnParams p, const int acc_dk, const int acc_dv) {
   extern __shared__ uint8_t smem_raw[];
-  const BwdSmem sm = carve_bwd(smem_raw);
+  const BwdSmem sm = carve_bwd(smem_raw, ATB_SLOTS, AT_P_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   bwd_setup(sm, warp, AT_SOFTMAX_WARPS);
   const uint32_t tmem_base = *sm.tmem_slot;
@@ -896,13 +902,13 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(sdp_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
         tc_fence_after();
-        int slot = (int)(ring_it % ATB_SLOTS);
+        int slot = (int)(ring_it % sm.nslots);
         mma_qk(tmem_base, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
-        slot = (int)(ring_it % ATB_SLOTS);
+        slot = (int)(ring_it % sm.nslots);
         mma_qk(tmem_base + 128u, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
@@ -925,7 +931,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           if (i == j && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           tc_fence_after();
-          int slot = (int)(ring_it % ATB_SLOTS);
+          int slot = (int)(ring_it % sm.nslots);
           mma_pv(tmem_base + 256u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, i != j);
           tc_commit(sm.bar_ring_empty + 8 * slot);
           tc_commit(sm.bar_t1_empty);
@@ -935,7 +941,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           if (!mbar_wait(sm.bar_t2_full, (uint32_t)(t_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           tc_fence_after();
-          slot = (int)(ring_it % ATB_SLOTS);
+          slot = (int)(ring_it % sm.nslots);
           mma_pv(tmem_base + 320u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, i != j);
           tc_commit(sm.bar_ring_empty + 8 * slot);
           tc_commit(sm.bar_t2_empty);
@@ -1148,10 +1154,10 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   p.write_p = 0; p.online = 0;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.o = o; p.d_o = d_o;
   p.status = ctx->d_status;
-  GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dq_kernel, ATB_SMEM_BYTES);
+  GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dq_kernel, ATQ_SMEM_BYTES);
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATB_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
-  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dq_kernel, dim3(grid), dim3(AT_THREADS), ATB_SMEM_BYTES, stream, mq, mdo, mk, mv, mkmn, mdq, p, acc_dq));
+  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dq_kernel, dim3(grid), dim3(AT_THREADS), ATQ_SMEM_BYTES, stream, mq, mdo, mk, mv, mkmn, mdq, p, acc_dq));
   GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dkv_kernel, dim3(grid), dim3(AT_THREADS), ATB_SMEM_BYTES, stream, mk, mv, mq, mdo, mqmn, mdomn, mdk, mdv,
                                        p, acc_dk, acc_dv));
   ctx->launches += 2;
