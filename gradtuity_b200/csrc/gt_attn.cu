@@ -564,6 +564,7 @@ struct BwdSmem {
   uint8_t* tile_ptr;
   uint32_t bar_fix_full, bar_fix_empty, bar_ring_full, bar_ring_empty, bar_sdp_full, bar_sdp_empty;
   uint32_t bar_t1_full, bar_t1_empty, bar_t2_full, bar_t2_empty, bar_out_full, bar_out_empty, bar_group, bar_drain;
+  uint32_t bar_s_full, bar_dp_full, bar_pa_full, bar_pb_full;      // dK / dV kernel (s_full, pa_full, pb_full: two barriers each)
   uint32_t* tmem_slot;
   volatile int* abort_flag;
   float* stats;
@@ -589,8 +590,10 @@ __device__ __forceinline__ BwdSmem carve_bwd(uint8_t* smem_raw, int nslots, int 
   s.bar_t2_full = bars + 160;   s.bar_t2_empty = bars + 168;
   s.bar_out_full = bars + 176;  s.bar_out_empty = bars + 184;
   s.bar_group = bars + 192;     s.bar_drain = bars + 200;
-  s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
-  s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 260);
+  s.bar_s_full = bars + 208;    /* two */  s.bar_dp_full = bars + 224;
+  s.bar_pa_full = bars + 232;   /* two */  s.bar_pb_full = bars + 248;   /* two */
+  s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 384);
+  s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 388);
   s.stats = reinterpret_cast<float*>(ctrl + 512);
   return s;
 }
@@ -604,6 +607,11 @@ __device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_a
     mbar_init(sm.bar_t2_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_t2_empty, 1);
     mbar_init(sm.bar_out_full, 1); mbar_init(sm.bar_out_empty, out_arrivals);
     mbar_init(sm.bar_group, AT_SOFTMAX_WARPS); mbar_init(sm.bar_drain, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(sm.bar_s_full + 8 * i, 1);
+      mbar_init(sm.bar_pa_full + 8 * i, AT_SOFTMAX_WARPS); mbar_init(sm.bar_pb_full + 8 * i, AT_SOFTMAX_WARPS);
+    }
+    mbar_init(sm.bar_dp_full, 1);
     *sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -856,14 +864,25 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 }
 
 // dK and dV for one block of 128 keys: everything transposed, so that a thread owns a key.
+//
+// Tensor memory: S^T in two buffers (columns 0 and 128), dP^T (256), dV (384), dK (448).  The softmax warps turn S^T
+// into P^T and dP^T into dS^T IN PLACE, and the dV / dK products read them from there as their A operand, so neither
+// passes through shared memory and the ring gets the room.  The MMA thread issues, per query tile i,
+//     S^T(i+1)   dV += P^T(i) dO(i)   dK += dS^T(i) Q(i)   dP^T(i+1)
+// and relies on the tensor core executing one thread's products in issue order: S^T(i+1) may overwrite the buffer
+// whose P^T(i-1) the earlier dV product read, and dP^T(i+1) may overwrite dS^T(i) behind the dK product, with no
+// "empty" barrier in between.  While dV(i) and dK(i) run, the softmax warps already work on S^T(i+1).
+constexpr uint32_t KV_ST = 0, KV_DPT = 256, KV_DV = 384, KV_DK = 448;
+constexpr int ATK_SLOTS = 5;
+constexpr int ATK_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATK_SLOTS * AT_SLOT_BYTES + 1024 + ATB_CTRL_BYTES;
+
 __global__ void __launch_bounds__(AT_THREADS, 1)
 gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                        const __grid_constant__ CUtensorMap map_qmn, const __grid_constant__ CUtensorMap map_domn,
-                       const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
-                       const AttnParams p, const int acc_dk, const int acc_dv) {
+                       float* __restrict__ dk, float* __restrict__ dv, const AttnParams p, const int acc_dk, const int acc_dv) {
   extern __shared__ uint8_t smem_raw[];
-  const BwdSmem sm = carve_bwd(smem_raw, ATB_SLOTS, AT_P_BYTES);
+  const BwdSmem sm = carve_bwd(smem_raw, ATK_SLOTS, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   bwd_setup(sm, warp, AT_SOFTMAX_WARPS);
   const uint32_t tmem_base = *sm.tmem_slot;
@@ -883,37 +902,40 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tma_load_4d(sm.fix1, &map_v, sm.bar_fix_full, 0, j * AT_TILE, h, b);
         tma_load_4d(sm.fix1 + 16384, &map_v, sm.bar_fix_full, 32, j * AT_TILE, h, b);
         ++f_it;
+        // in the order the MMA thread consumes them: Q(j), dO(j); then per tile Q(i+1), dO(i) MN-major, Q(i) MN-major, dO(i+1)
         ok = bwd_ring_load(sm, p, ring_it, &map_q, false, j * AT_TILE, h, b) && bwd_ring_load(sm, p, ring_it, &map_do, false, j * AT_TILE, h, b);
         for (int i = j; ok && i < nblk; ++i) {
-          if (i + 1 < nblk)
-            ok = bwd_ring_load(sm, p, ring_it, &map_q, false, (i + 1) * AT_TILE, h, b) &&
-                 bwd_ring_load(sm, p, ring_it, &map_do, false, (i + 1) * AT_TILE, h, b);
+          if (i + 1 < nblk) ok = bwd_ring_load(sm, p, ring_it, &map_q, false, (i + 1) * AT_TILE, h, b);
           if (ok) ok = bwd_ring_load(sm, p, ring_it, &map_domn, true, i * AT_TILE, h, b) &&
                        bwd_ring_load(sm, p, ring_it, &map_qmn, true, i * AT_TILE, h, b);
+          if (ok && i + 1 < nblk) ok = bwd_ring_load(sm, p, ring_it, &map_do, false, (i + 1) * AT_TILE, h, b);
         }
       }
       if (!ok) bwd_ring_drain(sm, ring_it);
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      long long ring_it = 0; int f_it = 0, sdp_it = 0, t_it = 0, o_it = 0;
+      long long ring_it = 0; int f_it = 0, tt = 0 /* tiles issued so far: S^T buffer and barrier parities */, o_it = 0;
+      int s_tt = 0;                         // S^T products issued so far
       bool ok = true;
-      auto issue_sdp = [&]() -> bool {        // S^T = K Q^T and dP^T = V dO^T of the next query tile
-        if (!bwd_ring_wait(sm, p, ring_it)) return false;
-        if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(sdp_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
-        tc_fence_after();
-        int slot = (int)(ring_it % sm.nslots);
-        mma_qk(tmem_base, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
-        tc_commit(sm.bar_ring_empty + 8 * slot);
-        ++ring_it;
+      auto issue_st = [&]() -> bool {       // S^T = K Q^T of the next query tile into buffer s_tt & 1
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
-        slot = (int)(ring_it % sm.nslots);
-        mma_qk(tmem_base + 128u, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
+        const int slot = (int)(ring_it % sm.nslots);
+        mma_qk(tmem_base + KV_ST + (uint32_t)((s_tt & 1) * 128), sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
+        tc_commit(sm.bar_s_full + 8 * (s_tt & 1));
+        ++ring_it; ++s_tt;
+        return true;
+      };
+      auto issue_dpt = [&]() -> bool {      // dP^T = V dO^T of the same tile
+        if (!bwd_ring_wait(sm, p, ring_it)) return false;
+        tc_fence_after();
+        const int slot = (int)(ring_it % sm.nslots);
+        mma_qk(tmem_base + KV_DPT, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
+        tc_commit(sm.bar_ring_empty + 8 * slot);
+        tc_commit(sm.bar_dp_full);
         ++ring_it;
-        tc_commit(sm.bar_sdp_full);
-        ++sdp_it;
         return true;
       };
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
@@ -921,32 +943,32 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         item_coords_kv(p, item, j, h, b);
         if (!mbar_wait(sm.bar_fix_full, (uint32_t)(f_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
         ++f_it;
-        ok = issue_sdp();
+        ok = issue_st() && issue_dpt();
+        if (ok && j == nblk - 1) tc_commit(sm.bar_fix_empty);           // a one-tile item: K and V have been read
         for (int i = j; ok && i < nblk; ++i) {
-          if (i + 1 < nblk) { ok = issue_sdp(); if (!ok) break; }
-          if (i == nblk - 1) tc_commit(sm.bar_fix_empty);
+          if (i + 1 < nblk) { ok = issue_st(); if (!ok) break; }
           // dV (+)= P^T dO
           if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
-          if (!mbar_wait(sm.bar_t1_full, (uint32_t)(t_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(sm.bar_pa_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (i == j && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           tc_fence_after();
           int slot = (int)(ring_it % sm.nslots);
-          mma_pv(tmem_base + 256u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, i != j);
+          mma_pv_ts(tmem_base + KV_DV, tmem_base + KV_ST + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, i != j);
           tc_commit(sm.bar_ring_empty + 8 * slot);
-          tc_commit(sm.bar_t1_empty);
           ++ring_it;
           // dK (+)= dS^T Q
           if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
-          if (!mbar_wait(sm.bar_t2_full, (uint32_t)(t_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          if (!mbar_wait(sm.bar_pb_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
           slot = (int)(ring_it % sm.nslots);
-          mma_pv(tmem_base + 320u, sm.tile, sm.ring + slot * AT_SLOT_BYTES, i != j);
+          mma_pv_ts(tmem_base + KV_DK, tmem_base + KV_DPT, sm.ring + slot * AT_SLOT_BYTES, i != j);
           tc_commit(sm.bar_ring_empty + 8 * slot);
-          tc_commit(sm.bar_t2_empty);
+          ++ring_it; ++tt;
           if (i == nblk - 1) { tc_commit(sm.bar_out_full); ++o_it; }
-          ++ring_it; ++t_it;
+          if (i + 1 < nblk) {
+            ok = issue_dpt();                                          // behind dK(i) in the pipe: dS^T(i) has been read
+            if (ok && i + 1 == nblk - 1) tc_commit(sm.bar_fix_empty);  // the item's last product with K and V has been issued
+          }
         }
       }
       if (!ok) {
@@ -959,10 +981,8 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int q = warp & 3, eset = (warp - 2) >> 2;
     const int r_local = q * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint8_t* const my_row = sm.tile_ptr + eset * 16384 + r_local * 128;
-    const uint32_t my_sub = sm.tile + (uint32_t)(eset * 16384 + q * 4096);
-    const int sw = r_local & 7;
-    int sdp_it = 0, t_it = 0, o_it = 0;
+    const long long E = (long long)p.H * AT_D;
+    int tt = 0, o_it = 0;
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       int j, h, b;
@@ -970,101 +990,102 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       const float* lse_bh = p.lse + ((long long)b * p.H + h) * p.S;
       const float* delta_bh = p.delta + ((long long)b * p.H + h) * p.S;
       for (int i = j; i < nblk; ++i) {
-        if (!mbar_wait(sm.bar_sdp_full, (uint32_t)(sdp_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
+        const uint32_t st_col = KV_ST + (uint32_t)((tt & 1) * 128 + eset * 32);
         const int q0 = i * AT_TILE + eset * 32;                   // query of this chunk's first column
         const int first_valid = (i > j) ? 0 : r_local - eset * 32;   // columns (queries) >= this thread's key
         const float4* l4 = reinterpret_cast<const float4*>(lse_bh + q0);
         const float4* d4 = reinterpret_cast<const float4*>(delta_bh + q0);
         const bool dead = (i == j) && (eset < q);                 // queries of this chunk all precede this warp's keys
         float pr[32], v[32];
+        // ---- S^T -> P^T, in place
+        if (!mbar_wait(sm.bar_s_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
         if (dead) {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) { pr[t] = 0.0f; v[t] = 0.0f; }
+          for (int t = 0; t < 32; ++t) pr[t] = 0.0f;
         } else {
-        tc_ld32(lane_base + (uint32_t)(eset * 32), v);
-        tc_wait_ld();
-        if (i > j) {                         // warp-uniform: every query of the block may see every key of ours
+          tc_ld32(lane_base + st_col, v);
+          tc_wait_ld();
+          if (i > j) {                       // warp-uniform: every query of the block may see every key of ours
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const float4 l = l4[g];
-            pr[4 * g] = ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E));
-            pr[4 * g + 1] = ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E));
-            pr[4 * g + 2] = ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E));
-            pr[4 * g + 3] = ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E));
+            for (int g = 0; g < 8; ++g) {
+              const float4 l = l4[g];
+              pr[4 * g] = ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E));
+              pr[4 * g + 1] = ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E));
+              pr[4 * g + 2] = ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E));
+              pr[4 * g + 3] = ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E));
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              const float4 l = l4[g];
+              pr[4 * g] = (4 * g >= first_valid) ? ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E)) : 0.0f;
+              pr[4 * g + 1] = (4 * g + 1 >= first_valid) ? ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E)) : 0.0f;
+              pr[4 * g + 2] = (4 * g + 2 >= first_valid) ? ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E)) : 0.0f;
+              pr[4 * g + 3] = (4 * g + 3 >= first_valid) ? ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E)) : 0.0f;
+            }
           }
-        } else {
+        }
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            const float4 l = l4[g];
-            pr[4 * g] = (4 * g >= first_valid) ? ex2(fmaf(v[4 * g], p.scale_log2, -l.x * AT_LOG2E)) : 0.0f;
-            pr[4 * g + 1] = (4 * g + 1 >= first_valid) ? ex2(fmaf(v[4 * g + 1], p.scale_log2, -l.y * AT_LOG2E)) : 0.0f;
-            pr[4 * g + 2] = (4 * g + 2 >= first_valid) ? ex2(fmaf(v[4 * g + 2], p.scale_log2, -l.z * AT_LOG2E)) : 0.0f;
-            pr[4 * g + 3] = (4 * g + 3 >= first_valid) ? ex2(fmaf(v[4 * g + 3], p.scale_log2, -l.w * AT_LOG2E)) : 0.0f;
-          }
-        }
-        tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
-        tc_wait_ld();
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 d = d4[g];
-          // dS^T without its factor `scale`: dK = scale * sum_i (P (dP - delta))^T Q takes it once, at the output
-          v[4 * g] = pr[4 * g] * (v[4 * g] - d.x);
-          v[4 * g + 1] = pr[4 * g + 1] * (v[4 * g + 1] - d.y);
-          v[4 * g + 2] = pr[4 * g + 2] * (v[4 * g + 2] - d.z);
-          v[4 * g + 3] = pr[4 * g + 3] * (v[4 * g + 3] - d.w);
-        }
-        }
+        for (int t = 0; t < 32; ++t) v[t] = to_tf32(pr[t]);
+        tc_st32(lane_base + st_col, v);
+        tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
-        ++sdp_it;
-        // P^T -> tile (free once the previous tile's dK product and this warp's own stores have read it)
-        if (!mbar_wait(sm.bar_t2_empty, (uint32_t)(t_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
-        if (i == j) { if (lane == 0) tma_store_wait_read<0>(); __syncwarp(); }
+        if (lane == 0) mbar_arrive(sm.bar_pa_full + 8 * (tt & 1));
+        // ---- dP^T -> dS^T, in place (without the factor `scale`: dK takes it once, at the output)
+        if (!mbar_wait(sm.bar_dp_full, (uint32_t)(tt & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        if (dead) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
-              make_float4(to_tf32(pr[4 * g]), to_tf32(pr[4 * g + 1]), to_tf32(pr[4 * g + 2]), to_tf32(pr[4 * g + 3]));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sm.bar_t1_full);
-        // dS^T -> the same tile, once the dV product has read P^T
-        if (!mbar_wait(sm.bar_t1_empty, (uint32_t)(t_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          for (int t = 0; t < 32; ++t) v[t] = 0.0f;
+        } else {
+          tc_ld32(lane_base + KV_DPT + (uint32_t)(eset * 32), v);
+          tc_wait_ld();
 #pragma unroll
-        for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
-              make_float4(to_tf32(v[4 * g]), to_tf32(v[4 * g + 1]), to_tf32(v[4 * g + 2]), to_tf32(v[4 * g + 3]));
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          for (int g = 0; g < 8; ++g) {
+            const float4 d = d4[g];
+            v[4 * g] = to_tf32(pr[4 * g] * (v[4 * g] - d.x));
+            v[4 * g + 1] = to_tf32(pr[4 * g + 1] * (v[4 * g + 1] - d.y));
+            v[4 * g + 2] = to_tf32(pr[4 * g + 2] * (v[4 * g + 2] - d.z));
+            v[4 * g + 3] = to_tf32(pr[4 * g + 3] * (v[4 * g + 3] - d.w));
+          }
+        }
+        tc_st32(lane_base + KV_DPT + (uint32_t)(eset * 32), v);
+        tc_wait_st();
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(sm.bar_t2_full);
-        ++t_it;
+        if (lane == 0) mbar_arrive(sm.bar_pb_full + 8 * (tt & 1));
+        ++tt;
       }
       if (!ok) break;
       if (!mbar_wait(sm.bar_out_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
       ++o_it;
       tc_fence_after();
       {
-        // chunks 0, 1: dV columns 0-31, 32-63; chunks 2, 3: dK columns 0-31, 32-63
+        // chunks 0, 1: dV columns 0-31, 32-63; chunks 2, 3: dK columns 0-31, 32-63.  A thread owns 32 consecutive
+        // floats of one key's row: eight 16-byte stores (or vector adds) straight from registers.
         float v[32];
-        tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), v);
+        tc_ld32(lane_base + (eset < 2 ? KV_DV : KV_DK) + (uint32_t)((eset & 1) * 32), v);
         tc_wait_ld();
         tc_fence_before();
-        const float out_scale = eset < 2 ? 1.0f : p.scale;       // dK carries the factor its dS^T tiles left out
-#pragma unroll
-        for (int g = 0; g < 8; ++g)
-          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
-              make_float4(out_scale * v[4 * g], out_scale * v[4 * g + 1], out_scale * v[4 * g + 2], out_scale * v[4 * g + 3]);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) {
-          if (eset < 2) tma_store_4d(&map_dv, my_sub, eset * 32, j * AT_TILE + q * 32, h, b, acc_dv != 0);
-          else tma_store_4d(&map_dk, my_sub, (eset - 2) * 32, j * AT_TILE + q * 32, h, b, acc_dk != 0);
-          mbar_arrive(sm.bar_out_empty);
+        if (lane == 0) mbar_arrive(sm.bar_out_empty);
+        const float out_scale = eset < 2 ? 1.0f : p.scale;       // dK carries the factor its dS^T tiles left out
+        float* dst = (eset < 2 ? dv : dk) + ((long long)b * p.S + j * AT_TILE + r_local) * E + (long long)h * AT_D + (eset & 1) * 32;
+        const bool add = (eset < 2 ? acc_dv : acc_dk) != 0;
+        if (add) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * g), "f"(out_scale * v[4 * g]), "f"(out_scale * v[4 * g + 1]),
+                         "f"(out_scale * v[4 * g + 2]), "f"(out_scale * v[4 * g + 3]) : "memory");
+        } else {
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *reinterpret_cast<float4*>(dst + 4 * g) = make_float4(out_scale * v[4 * g], out_scale * v[4 * g + 1], out_scale * v[4 * g + 2], out_scale * v[4 * g + 3]);
         }
       }
     }
-    if (lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -1135,7 +1156,7 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   cudaStream_t stream = stream_ ? (cudaStream_t)stream_ : ctx->stream;
   const long long E = H * D;
   auto view = [&](const float* ptr) { return OperandView{ptr, S, D, E, D, S * E}; };
-  CUtensorMap mq, mk, mv, mdo, mkmn, mqmn, mdomn, mdq, mdk, mdv;
+  CUtensorMap mq, mk, mv, mdo, mkmn, mqmn, mdomn, mdq;
   if ((rc = encode_map(ctx, &mq, view(q), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
   if ((rc = encode_map(ctx, &mk, view(k), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
   if ((rc = encode_map(ctx, &mv, view(v), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
@@ -1144,8 +1165,6 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
       !encode_map_mn5(ctx, &mdomn, view(d_o), 2, H, B, false, AT_TILE))
     GT_FAIL(ctx, GT_ERR_CUDA, "fused attention backward: a tensor map was refused");
   if ((rc = encode_map(ctx, &mdq, view(dq), 32, 32, H, B, false, true)) != GT_OK) return rc;
-  if ((rc = encode_map(ctx, &mdk, view(dk), 32, 32, H, B, false, true)) != GT_OK) return rc;
-  if ((rc = encode_map(ctx, &mdv, view(dv), 32, 32, H, B, false, true)) != GT_OK) return rc;
   AttnParams p;
   p.S = (int)S; p.H = (int)H; p.B = (int)B;
   p.nblk = (int)(S / AT_TILE);
@@ -1155,10 +1174,10 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   p.lse = const_cast<float*>(lse); p.delta = delta; p.o = o; p.d_o = d_o;
   p.status = ctx->d_status;
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dq_kernel, ATQ_SMEM_BYTES);
-  GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATB_SMEM_BYTES);
+  GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATK_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
   GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dq_kernel, dim3(grid), dim3(AT_THREADS), ATQ_SMEM_BYTES, stream, mq, mdo, mk, mv, mkmn, mdq, p, acc_dq));
-  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dkv_kernel, dim3(grid), dim3(AT_THREADS), ATB_SMEM_BYTES, stream, mk, mv, mq, mdo, mqmn, mdomn, mdk, mdv,
+  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dkv_kernel, dim3(grid), dim3(AT_THREADS), ATK_SMEM_BYTES, stream, mk, mv, mq, mdo, mqmn, mdomn, dk, dv,
                                        p, acc_dk, acc_dv));
   ctx->launches += 2;
   return GT_OK;
