@@ -105,6 +105,12 @@ __device__ __forceinline__ void mma_pv_ts(uint32_t d_tmem, uint32_t a_tmem, uint
     tc_mma_tf32_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc, (keep || kk) ? 1u : 0u);
 }
 
+// One 128 x 64 operand tile (two boxes of 32 columns) into L2.
+__device__ __forceinline__ void prefetch_tile(const CUtensorMap* map, int row0, int h, int b) {
+  tma_prefetch_l2_4d(map, 0, row0, h, b);
+  tma_prefetch_l2_4d(map, 32, row0, h, b);
+}
+
 struct AttnSmem {
   uint32_t q, ring, ptile;                // shared-memory addresses (u32)
   uint8_t* ptile_ptr;
@@ -205,6 +211,11 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tma_load_4d(sm.q, &map_q, sm.bar_q_full, 0, i * AT_TILE, h, b);
         tma_load_4d(sm.q + 16384, &map_q, sm.bar_q_full, 32, i * AT_TILE, h, b);
         ++q_it;
+        if (item + (int)gridDim.x < p.num_items) {     // the next item's Q towards L2
+          int i2, h2, b2;
+          item_coords(p, item + (int)gridDim.x, i2, h2, b2);
+          prefetch_tile(&map_q, i2 * AT_TILE, h2, b2);
+        }
         if (!p.online)
           for (int j = 0; ok && j <= i; ++j) ok = load_slot(&map_k, false, j * AT_TILE, h, b);         // pass 1
         // pass 2, in the order the MMA lane consumes them: K0, K1, V0, K2, V1, ..., Ki, V(i-1), Vi
@@ -682,14 +693,22 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
         int i, h, b;
         item_coords(p, item, i, h, b);
-        if (!mbar_wait(sm.bar_fix_empty, (uint32_t)(f_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        // the first ring tiles need only free slots, which the end of the previous item leaves: they go out before the
+        // wait for the fixed tiles, which are busy until that item's last S / dP product has completed
+        ok = bwd_ring_load(sm, p, ring_it, &map_k, false, 0, h, b) && bwd_ring_load(sm, p, ring_it, &map_v, false, 0, h, b);
+        if (!ok || !mbar_wait(sm.bar_fix_empty, (uint32_t)(f_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
         mbar_expect_tx(sm.bar_fix_full, 2 * AT_SLOT_BYTES);
         tma_load_4d(sm.fix0, &map_q, sm.bar_fix_full, 0, i * AT_TILE, h, b);
         tma_load_4d(sm.fix0 + 16384, &map_q, sm.bar_fix_full, 32, i * AT_TILE, h, b);
         tma_load_4d(sm.fix1, &map_do, sm.bar_fix_full, 0, i * AT_TILE, h, b);
         tma_load_4d(sm.fix1 + 16384, &map_do, sm.bar_fix_full, 32, i * AT_TILE, h, b);
         ++f_it;
-        ok = bwd_ring_load(sm, p, ring_it, &map_k, false, 0, h, b) && bwd_ring_load(sm, p, ring_it, &map_v, false, 0, h, b);
+        if (item + (int)gridDim.x < p.num_items) {     // the next item's Q and dO: nobody has read them yet, so start them towards L2 now
+          int i2, h2, b2;
+          item_coords(p, item + (int)gridDim.x, i2, h2, b2);
+          prefetch_tile(&map_q, i2 * AT_TILE, h2, b2);
+          prefetch_tile(&map_do, i2 * AT_TILE, h2, b2);
+        }
         for (int j = 0; ok && j <= i; ++j) {
           if (j + 1 <= i)
             ok = bwd_ring_load(sm, p, ring_it, &map_k, false, (j + 1) * AT_TILE, h, b) &&
@@ -880,7 +899,8 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                        const __grid_constant__ CUtensorMap map_qmn, const __grid_constant__ CUtensorMap map_domn,
-                       float* __restrict__ dk, float* __restrict__ dv, const AttnParams p, const int acc_dk, const int acc_dv) {
+                       const __grid_constant__ CUtensorMap map_dk, const __grid_constant__ CUtensorMap map_dv,
+                       const AttnParams p, const int acc_dk, const int acc_dv) {
   extern __shared__ uint8_t smem_raw[];
   const BwdSmem sm = carve_bwd(smem_raw, ATK_SLOTS, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -895,15 +915,22 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
         int j, h, b;
         item_coords_kv(p, item, j, h, b);
-        if (!mbar_wait(sm.bar_fix_empty, (uint32_t)(f_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        // Ring tiles in the order the MMA thread consumes them: Q(j), dO(j); then per tile Q(i+1), dO(i) MN-major, Q(i)
+        // MN-major, dO(i+1).  The first two need only free slots and go out before the wait for the fixed tiles.
+        ok = bwd_ring_load(sm, p, ring_it, &map_q, false, j * AT_TILE, h, b) && bwd_ring_load(sm, p, ring_it, &map_do, false, j * AT_TILE, h, b);
+        if (!ok || !mbar_wait(sm.bar_fix_empty, (uint32_t)(f_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
         mbar_expect_tx(sm.bar_fix_full, 2 * AT_SLOT_BYTES);
         tma_load_4d(sm.fix0, &map_k, sm.bar_fix_full, 0, j * AT_TILE, h, b);
         tma_load_4d(sm.fix0 + 16384, &map_k, sm.bar_fix_full, 32, j * AT_TILE, h, b);
         tma_load_4d(sm.fix1, &map_v, sm.bar_fix_full, 0, j * AT_TILE, h, b);
         tma_load_4d(sm.fix1 + 16384, &map_v, sm.bar_fix_full, 32, j * AT_TILE, h, b);
         ++f_it;
-        // in the order the MMA thread consumes them: Q(j), dO(j); then per tile Q(i+1), dO(i) MN-major, Q(i) MN-major, dO(i+1)
-        ok = bwd_ring_load(sm, p, ring_it, &map_q, false, j * AT_TILE, h, b) && bwd_ring_load(sm, p, ring_it, &map_do, false, j * AT_TILE, h, b);
+        if (item + (int)gridDim.x < p.num_items) {     // the next item's K and V: nobody has read them yet, so start them towards L2 now
+          int j2, h2, b2;
+          item_coords_kv(p, item + (int)gridDim.x, j2, h2, b2);
+          prefetch_tile(&map_k, j2 * AT_TILE, h2, b2);
+          prefetch_tile(&map_v, j2 * AT_TILE, h2, b2);
+        }
         for (int i = j; ok && i < nblk; ++i) {
           if (i + 1 < nblk) ok = bwd_ring_load(sm, p, ring_it, &map_q, false, (i + 1) * AT_TILE, h, b);
           if (ok) ok = bwd_ring_load(sm, p, ring_it, &map_domn, true, i * AT_TILE, h, b) &&
@@ -954,7 +981,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           tc_fence_after();
           int slot = (int)(ring_it % sm.nslots);
           mma_pv_ts(tmem_base + KV_DV, tmem_base + KV_ST + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, i != j);
-          tc_commit(sm.bar_ring_empty + 8 * slot);
+          if (i < nblk - 1) tc_commit(sm.bar_ring_empty + 8 * slot);     // the item's last two slots stage its outputs: released there
           ++ring_it;
           // dK (+)= dS^T Q
           if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
@@ -962,7 +989,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           tc_fence_after();
           slot = (int)(ring_it % sm.nslots);
           mma_pv_ts(tmem_base + KV_DK, tmem_base + KV_DPT, sm.ring + slot * AT_SLOT_BYTES, i != j);
-          tc_commit(sm.bar_ring_empty + 8 * slot);
+          if (i < nblk - 1) tc_commit(sm.bar_ring_empty + 8 * slot);
           ++ring_it; ++tt;
           if (i == nblk - 1) { tc_commit(sm.bar_out_full); ++o_it; }
           if (i + 1 < nblk) {
@@ -981,8 +1008,9 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int q = warp & 3, eset = (warp - 2) >> 2;
     const int r_local = q * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    const long long E = (long long)p.H * AT_D;
-    int tt = 0, o_it = 0;
+    const int sw = r_local & 7;
+    int tt = 0, o_it = 0, g_it = 0;
+    long long ring_base = 0;                   // ring loads of the items so far: 4 per tile
     bool ok = true;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       int j, h, b;
@@ -1063,29 +1091,42 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       ++o_it;
       tc_fence_after();
       {
-        // chunks 0, 1: dV columns 0-31, 32-63; chunks 2, 3: dK columns 0-31, 32-63.  A thread owns 32 consecutive
-        // floats of one key's row: eight 16-byte stores (or vector adds) straight from registers.
+        // chunks 0, 1: dV columns 0-31, 32-63; chunks 2, 3: dK columns 0-31, 32-63.  They leave through the ring slots
+        // of the item's last two loads (dO and Q of the last tile, MN-major), whose readers, the last dV and dK
+        // products, have completed: the MMA thread left those two slots unreleased, and they are handed back to the
+        // producer below, once the TMA stores have read them.
         float v[32];
         tc_ld32(lane_base + (eset < 2 ? KV_DV : KV_DK) + (uint32_t)((eset & 1) * 32), v);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(sm.bar_out_empty);
+        ring_base += 4LL * (nblk - j);
+        const int slot_dv = (int)((ring_base - 2) % sm.nslots), slot_dk = (int)((ring_base - 1) % sm.nslots);
+        const uint32_t stage_off = (uint32_t)((eset < 2 ? slot_dv : slot_dk) * AT_SLOT_BYTES + (eset & 1) * 16384);
+        uint8_t* const my_row = sm.tile_ptr - sm.nslots * AT_SLOT_BYTES + stage_off + r_local * 128;    // the ring ends where the tile would start
+        const uint32_t my_sub = sm.ring + stage_off + (uint32_t)(q * 4096);
         const float out_scale = eset < 2 ? 1.0f : p.scale;       // dK carries the factor its dS^T tiles left out
-        float* dst = (eset < 2 ? dv : dk) + ((long long)b * p.S + j * AT_TILE + r_local) * E + (long long)h * AT_D + (eset & 1) * 32;
-        const bool add = (eset < 2 ? acc_dv : acc_dk) != 0;
-        if (add) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * g), "f"(out_scale * v[4 * g]), "f"(out_scale * v[4 * g + 1]),
-                         "f"(out_scale * v[4 * g + 2]), "f"(out_scale * v[4 * g + 3]) : "memory");
-        } else {
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            *reinterpret_cast<float4*>(dst + 4 * g) = make_float4(out_scale * v[4 * g], out_scale * v[4 * g + 1], out_scale * v[4 * g + 2], out_scale * v[4 * g + 3]);
+        for (int g = 0; g < 8; ++g)
+          *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
+              make_float4(out_scale * v[4 * g], out_scale * v[4 * g + 1], out_scale * v[4 * g + 2], out_scale * v[4 * g + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          if (eset < 2) tma_store_4d(&map_dv, my_sub, eset * 32, j * AT_TILE + q * 32, h, b, acc_dv != 0);
+          else tma_store_4d(&map_dk, my_sub, (eset - 2) * 32, j * AT_TILE + q * 32, h, b, acc_dk != 0);
+          tma_store_wait_read<0>();
         }
+        // every warp's store has read its part: the two slots go back to the producer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_group);
+        if (!mbar_wait(sm.bar_group, (uint32_t)(g_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        ++g_it;
+        if (warp == 2 && lane == 0) { mbar_arrive(sm.bar_ring_empty + 8 * slot_dv); mbar_arrive(sm.bar_ring_empty + 8 * slot_dk); }
       }
     }
+    if (lane == 0) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -1156,7 +1197,7 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   cudaStream_t stream = stream_ ? (cudaStream_t)stream_ : ctx->stream;
   const long long E = H * D;
   auto view = [&](const float* ptr) { return OperandView{ptr, S, D, E, D, S * E}; };
-  CUtensorMap mq, mk, mv, mdo, mkmn, mqmn, mdomn, mdq;
+  CUtensorMap mq, mk, mv, mdo, mkmn, mqmn, mdomn, mdq, mdk, mdv;
   if ((rc = encode_map(ctx, &mq, view(q), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
   if ((rc = encode_map(ctx, &mk, view(k), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
   if ((rc = encode_map(ctx, &mv, view(v), 32, AT_TILE, H, B, false)) != GT_OK) return rc;
@@ -1165,6 +1206,8 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
       !encode_map_mn5(ctx, &mdomn, view(d_o), 2, H, B, false, AT_TILE))
     GT_FAIL(ctx, GT_ERR_CUDA, "fused attention backward: a tensor map was refused");
   if ((rc = encode_map(ctx, &mdq, view(dq), 32, 32, H, B, false, true)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mdk, view(dk), 32, 32, H, B, false, true)) != GT_OK) return rc;
+  if ((rc = encode_map(ctx, &mdv, view(dv), 32, 32, H, B, false, true)) != GT_OK) return rc;
   AttnParams p;
   p.S = (int)S; p.H = (int)H; p.B = (int)B;
   p.nblk = (int)(S / AT_TILE);
@@ -1177,7 +1220,7 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATK_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
   GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dq_kernel, dim3(grid), dim3(AT_THREADS), ATQ_SMEM_BYTES, stream, mq, mdo, mk, mv, mkmn, mdq, p, acc_dq));
-  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dkv_kernel, dim3(grid), dim3(AT_THREADS), ATK_SMEM_BYTES, stream, mk, mv, mq, mdo, mqmn, mdomn, dk, dv,
+  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dkv_kernel, dim3(grid), dim3(AT_THREADS), ATK_SMEM_BYTES, stream, mk, mv, mq, mdo, mqmn, mdomn, mdk, mdv,
                                        p, acc_dk, acc_dv));
   ctx->launches += 2;
   return GT_OK;

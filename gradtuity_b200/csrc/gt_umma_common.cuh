@@ -71,6 +71,13 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// Asks the TMA unit to bring one box of the tensor into L2 (no shared-memory destination, no barrier): used ahead of a
+// load whose data nobody has touched yet, so that the load itself finds the lines in L2.
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+               ::"l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+
 // ---- CTA pairs (tcgen05 cta_group::2): two CTAs of a cluster work on one tile -------------------
 // The pair's TMA loads (each CTA loads its own operand halves from this GPU's memory: no multicast) all
 // signal ONE mbarrier, the leader CTA's, which the `.cta_group::2` form of the load allows.
