@@ -564,10 +564,8 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 // (K, dO or Q, stored (rows, 64) with the head dimension contiguous) is MN-major: it is loaded a second
 // time with the five-dimensional map that lays it out in 32-wide chunks.
 constexpr int ATB_SLOTS = 3;                   // dK / dV kernel: ring slots beside K, V and the 64 KB P^T / dS^T tile
-constexpr int ATQ_SLOTS = 4;                   // dQ kernel: dS lives in tensor memory, so the ring gets a fourth slot
 constexpr int ATB_CTRL_BYTES = 1536;           // barriers, the tensor-memory address, the abort flag, 2 x 128 floats of statistics
 constexpr int ATB_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATB_SLOTS * AT_SLOT_BYTES + AT_P_BYTES + 1024 + ATB_CTRL_BYTES;
-constexpr int ATQ_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATQ_SLOTS * AT_SLOT_BYTES + AT_SLOT_BYTES + 1024 + ATB_CTRL_BYTES;
 
 struct BwdSmem {
   int nslots;
@@ -576,6 +574,7 @@ struct BwdSmem {
   uint32_t bar_fix_full, bar_fix_empty, bar_ring_full, bar_ring_empty, bar_sdp_full, bar_sdp_empty;
   uint32_t bar_t1_full, bar_t1_empty, bar_t2_full, bar_t2_empty, bar_out_full, bar_out_empty, bar_group, bar_drain;
   uint32_t bar_s_full, bar_dp_full, bar_pa_full, bar_pb_full;      // dK / dV kernel (s_full, pa_full, pb_full: two barriers each)
+  uint32_t bar_ds_full, bar_delta_full, bar_delta_empty;           // dQ kernel (two barriers each)
   uint32_t* tmem_slot;
   volatile int* abort_flag;
   float* stats;
@@ -603,6 +602,7 @@ __device__ __forceinline__ BwdSmem carve_bwd(uint8_t* smem_raw, int nslots, int 
   s.bar_group = bars + 192;     s.bar_drain = bars + 200;
   s.bar_s_full = bars + 208;    /* two */  s.bar_dp_full = bars + 224;
   s.bar_pa_full = bars + 232;   /* two */  s.bar_pb_full = bars + 248;   /* two */
+  s.bar_ds_full = bars + 264;   /* two */  s.bar_delta_full = bars + 280;   /* two */  s.bar_delta_empty = bars + 296;   /* two */
   s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 384);
   s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 388);
   s.stats = reinterpret_cast<float*>(ctrl + 512);
@@ -621,6 +621,8 @@ __device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_a
     for (int i = 0; i < 2; ++i) {
       mbar_init(sm.bar_s_full + 8 * i, 1);
       mbar_init(sm.bar_pa_full + 8 * i, AT_SOFTMAX_WARPS); mbar_init(sm.bar_pb_full + 8 * i, AT_SOFTMAX_WARPS);
+      mbar_init(sm.bar_ds_full + 8 * i, AT_SOFTMAX_WARPS);
+      mbar_init(sm.bar_delta_full + 8 * i, 2); mbar_init(sm.bar_delta_empty + 8 * i, AT_SOFTMAX_WARPS);
     }
     mbar_init(sm.bar_dp_full, 1);
     *sm.abort_flag = 0;
@@ -675,14 +677,29 @@ __device__ __forceinline__ void item_coords_kv(const AttnParams& p, int item, in
 }
 
 // dQ for one block of 128 queries; also delta = rowsum(dO * O).
-__global__ void __launch_bounds__(AT_THREADS, 1)
+//
+// Tensor memory: S (columns 0-127), dP in two buffers (128, 256), dQ (384-447).  The softmax warps turn dP into dS in
+// place and the dQ product reads it from there; per key tile j the MMA thread issues
+//     S(j+1)   dP(j+1) -> the other buffer   dQ += dS(j) K(j)
+// so that the softmax arithmetic of tile j+1 runs beside the dQ product of tile j.  dP(j+1) overwrites the buffer whose
+// dS(j-1) the earlier dQ product read (the tensor core executes one thread's products in issue order); S is single
+// and waits for the softmax warps to have loaded it.
+// Two extra warps run one item ahead and compute delta for the block's 128 queries (two rows per thread), handing it
+// over through shared memory, so the softmax warps do not wait for global memory at the start of an item.
+constexpr uint32_t DQ_S = 0, DQ_DP = 128, DQ_ACC = 384;
+constexpr int ATQ_THREADS = AT_THREADS + 64;
+constexpr int ATQ_SLOTS = 5;
+constexpr int ATQ_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATQ_SLOTS * AT_SLOT_BYTES + 1024 + ATB_CTRL_BYTES;
+
+__global__ void __launch_bounds__(ATQ_THREADS, 1)
 gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                       const __grid_constant__ CUtensorMap map_kmn, const __grid_constant__ CUtensorMap map_dq,
                       const AttnParams p, const int accumulate) {
   extern __shared__ uint8_t smem_raw[];
-  const BwdSmem sm = carve_bwd(smem_raw, ATQ_SLOTS, AT_SLOT_BYTES);
+  const BwdSmem sm = carve_bwd(smem_raw, ATQ_SLOTS, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t bar_delta_full = sm.bar_delta_full, bar_delta_empty = sm.bar_delta_empty;   // "delta ready" (two delta warps), "delta read" (softmax warps)
   bwd_setup(sm, warp, 8);
   const uint32_t tmem_base = *sm.tmem_slot;
 
@@ -709,6 +726,7 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           prefetch_tile(&map_q, i2 * AT_TILE, h2, b2);
           prefetch_tile(&map_do, i2 * AT_TILE, h2, b2);
         }
+        // in the order the MMA thread consumes them: K(0), V(0); then per tile K(j+1), V(j+1), K(j) MN-major
         for (int j = 0; ok && j <= i; ++j) {
           if (j + 1 <= i)
             ok = bwd_ring_load(sm, p, ring_it, &map_k, false, (j + 1) * AT_TILE, h, b) &&
@@ -720,24 +738,25 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      long long ring_it = 0; int f_it = 0, sdp_it = 0, t1_it = 0, o_it = 0;
+      long long ring_it = 0; int f_it = 0, s_it = 0 /* S / dP pairs issued */, tt = 0 /* dQ products issued */, o_it = 0;
       bool ok = true;
       auto issue_sdp = [&]() -> bool {        // S = Q K^T and dP = dO V^T of the next key tile
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
-        if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(sdp_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
+        // S is single: the softmax warps must have loaded the previous tile's
+        if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(s_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
         tc_fence_after();
         int slot = (int)(ring_it % sm.nslots);
-        mma_qk(tmem_base, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
+        mma_qk(tmem_base + DQ_S, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
         slot = (int)(ring_it % sm.nslots);
-        mma_qk(tmem_base + 128u, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
+        mma_qk(tmem_base + DQ_DP + (uint32_t)((s_it & 1) * 128), sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
         tc_commit(sm.bar_sdp_full);
-        ++sdp_it;
+        ++s_it;
         return true;
       };
       for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
@@ -748,17 +767,16 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         ok = issue_sdp();
         for (int j = 0; ok && j <= i; ++j) {
           if (j + 1 <= i) { ok = issue_sdp(); if (!ok) break; }
-          if (j == i) tc_commit(sm.bar_fix_empty);
+          if (j == i) tc_commit(sm.bar_fix_empty);          // the item's last product with Q and dO has been issued
           if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
-          if (!mbar_wait(sm.bar_t1_full, (uint32_t)(t1_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(sm.bar_ds_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (j == 0 && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
           const int slot = (int)(ring_it % sm.nslots);
-          mma_pv_ts(tmem_base + 256u, tmem_base + 320u, sm.ring + slot * AT_SLOT_BYTES, j != 0);     // dQ (+)= dS K, dS from tensor memory
-          tc_commit(sm.bar_ring_empty + 8 * slot);
-          tc_commit(sm.bar_t1_empty);
+          mma_pv_ts(tmem_base + DQ_ACC, tmem_base + DQ_DP + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, j != 0);     // dQ (+)= dS K
+          if (j < i) tc_commit(sm.bar_ring_empty + 8 * slot);      // the item's last slot stages its output: released there
           if (j == i) { tc_commit(sm.bar_out_full); ++o_it; }
-          ++ring_it; ++t1_it;
+          ++ring_it; ++tt;
         }
       }
       if (!ok) {
@@ -767,57 +785,70 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         while (!mbar_try_wait(sm.bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
       }
     }
-  } else {
-    const int q = warp & 3, eset = (warp - 2) >> 2;
-    const int r_local = q * 32 + lane;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-    uint8_t* const my_row = sm.tile_ptr + eset * 16384 + r_local * 128;
-    const uint32_t my_sub = sm.tile + (uint32_t)(eset * 16384 + q * 4096);
-    const int sw = r_local & 7;
+  } else if (warp >= 2 + AT_SOFTMAX_WARPS) {
+    // ------------------------------ delta warps: rows t and t + 64 of every item, one item ahead ------------------------------
+    const int t = threadIdx.x - (2 + AT_SOFTMAX_WARPS) * 32;       // 0 .. 63
     const long long E = (long long)p.H * AT_D;
-    int sdp_it = 0, t1_it = 0, o_it = 0, g_it = 0;
+    int n_it = 0;
     bool ok = true;
-    auto group_sync = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(sm.bar_group);
-      const bool r = mbar_wait(sm.bar_group, (uint32_t)(g_it & 1), sm.abort_flag, p.status);
-      ++g_it;
-      return r;
-    };
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++n_it) {
       int i, h, b;
       item_coords(p, item, i, h, b);
-      const int row = i * AT_TILE + r_local;
-      // delta = rowsum(dO * O), computed by the first of the row's four threads and handed to the others through
-      // shared memory (two sets of 128 values, by item parity, so one rendezvous per item is enough)
-      float* const dstat = sm.stats + (g_it & 1) * 128;
-      if (eset == 0) {
-        const long long off = ((long long)b * p.S + row) * E + (long long)h * AT_D;
+      const int par = n_it & 1;
+      if (!mbar_wait(bar_delta_empty + 8 * par, (uint32_t)((n_it >> 1) & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = t + half * 64;
+        const long long off = ((long long)b * p.S + i * AT_TILE + r) * E + (long long)h * AT_D;
         const float4* o4 = reinterpret_cast<const float4*>(p.o + off);
         const float4* g4 = reinterpret_cast<const float4*>(p.d_o + off);
         float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll
-        for (int t = 0; t < 16; t += 2) {
-          const float4 a = o4[t], g = g4[t], a2 = o4[t + 1], g2 = g4[t + 1];
+        for (int c = 0; c < 16; c += 2) {
+          const float4 a = o4[c], g = g4[c], a2 = o4[c + 1], g2 = g4[c + 1];
           s0 += (a.x * g.x + a.y * g.y) + (a.z * g.z + a.w * g.w);
           s1 += (a2.x * g2.x + a2.y * g2.y) + (a2.z * g2.z + a2.w * g2.w);
         }
-        dstat[r_local] = s0 + s1;
-        p.delta[((long long)b * p.H + h) * p.S + row] = s0 + s1;
+        sm.stats[par * 128 + r] = s0 + s1;
+        p.delta[((long long)b * p.H + h) * p.S + i * AT_TILE + r] = s0 + s1;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_delta_full + 8 * par);
+    }
+  } else {
+    const int q = warp & 3, eset = (warp - 2) >> 2;
+    const int r_local = q * 32 + lane;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    const int sw = r_local & 7;
+    int tt = 0, o_it = 0, g_it = 0, n_it = 0;
+    long long ring_base = 0;                   // ring loads of the items so far: 3 per tile
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x, ++n_it) {
+      int i, h, b;
+      item_coords(p, item, i, h, b);
+      const int row = i * AT_TILE + r_local;
       const float lse2 = p.lse[((long long)b * p.H + h) * p.S + row] * AT_LOG2E;
-      if (!group_sync()) { ok = false; break; }
-      const float delta = dstat[r_local];
+      const int par = n_it & 1;
+      if (!mbar_wait(bar_delta_full + 8 * par, (uint32_t)((n_it >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+      const float delta = sm.stats[par * 128 + r_local];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_delta_empty + 8 * par);
       for (int j = 0; j <= i; ++j) {
-        if (!mbar_wait(sm.bar_sdp_full, (uint32_t)(sdp_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        if (!mbar_wait(sm.bar_sdp_full, (uint32_t)(tt & 1), sm.abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
         const int col0 = j * AT_TILE + eset * 32;
         const int nvalid = (j < i) ? 32 : row - col0 + 1;        // keys <= query
         const bool dead = (j == i) && (eset > q);                 // chunk wholly right of the diagonal for this warp's rows
+        const uint32_t dp_col = DQ_DP + (uint32_t)((tt & 1) * 128 + eset * 32);
         float pr[32], v[32];
         if (!dead) {
-          tc_ld32(lane_base + (uint32_t)(eset * 32), v);
+          tc_ld32(lane_base + DQ_S + (uint32_t)(eset * 32), v);
           tc_wait_ld();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_sdp_empty);             // S is in registers: the next tile's may be issued
+        if (!dead) {
           if (j < i) {                       // warp-uniform: a tile left of the diagonal has no masked element
 #pragma unroll
             for (int t = 0; t < 32; ++t) pr[t] = ex2(fmaf(v[t], p.scale_log2, -lse2));
@@ -825,40 +856,40 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
             for (int t = 0; t < 32; ++t) pr[t] = (t < nvalid) ? ex2(fmaf(v[t], p.scale_log2, -lse2)) : 0.0f;
           }
-          tc_ld32(lane_base + 128u + (uint32_t)(eset * 32), v);
+          tc_ld32(lane_base + dp_col, v);
           tc_wait_ld();
+          // dS without its factor `scale`: dQ = scale * sum_j (P (dP - delta)) K takes it once, at the output
+#pragma unroll
+          for (int t = 0; t < 32; ++t) v[t] = to_tf32(pr[t] * (v[t] - delta));
         } else {
 #pragma unroll
-          for (int t = 0; t < 32; ++t) { pr[t] = 0.0f; v[t] = 0.0f; }
+          for (int t = 0; t < 32; ++t) v[t] = 0.0f;
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sm.bar_sdp_empty);
-        ++sdp_it;
-        // dS without its factor `scale`: dQ = scale * sum_j (P (dP - delta)) K takes it once, at the output
-#pragma unroll
-        for (int t = 0; t < 32; ++t) v[t] = to_tf32(pr[t] * (v[t] - delta));
-        // the dS columns of tensor memory are free once the previous dQ product (this item's or the last one's) has read them
-        if (!mbar_wait(sm.bar_t1_empty, (uint32_t)(t1_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
-        tc_fence_after();
-        tc_st32(lane_base + 320u + (uint32_t)(eset * 32), v);
+        tc_st32(lane_base + dp_col, v);                           // dS over dP, in place
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(sm.bar_t1_full);
-        ++t1_it;
+        if (lane == 0) mbar_arrive(sm.bar_ds_full + 8 * (tt & 1));
+        ++tt;
       }
       if (!ok) break;
       if (!mbar_wait(sm.bar_out_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
       ++o_it;
       tc_fence_after();
+      // dQ (64 columns: chunks 0 and 1) leaves through the ring slot of the item's last load (K of the last tile,
+      // MN-major), whose reader, the last dQ product, has completed; the slot goes back to the producer below.
+      ring_base += 3LL * (i + 1);
+      const int slot_out = (int)((ring_base - 1) % sm.nslots);
       if (eset < 2) {
         float v[32];
-        tc_ld32(lane_base + 256u + (uint32_t)(eset * 32), v);
+        tc_ld32(lane_base + DQ_ACC + (uint32_t)(eset * 32), v);
         tc_wait_ld();
         tc_fence_before();
-        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_out_empty);
+        const uint32_t stage_off = (uint32_t)(slot_out * AT_SLOT_BYTES + eset * 16384);
+        uint8_t* const my_row = sm.tile_ptr - sm.nslots * AT_SLOT_BYTES + stage_off + r_local * 128;
+        const uint32_t my_sub = sm.ring + stage_off + (uint32_t)(q * 4096);
 #pragma unroll
         for (int g = 0; g < 8; ++g)
           *reinterpret_cast<float4*>(my_row + ((g ^ sw) << 4)) =
@@ -867,9 +898,14 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         __syncwarp();
         if (lane == 0) {
           tma_store_4d(&map_dq, my_sub, eset * 32, i * AT_TILE + q * 32, h, b, accumulate != 0);
-          mbar_arrive(sm.bar_out_empty);
+          tma_store_wait_read<0>();
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.bar_group);
+      if (!mbar_wait(sm.bar_group, (uint32_t)(g_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+      ++g_it;
+      if (warp == 2 && lane == 0) mbar_arrive(sm.bar_ring_empty + 8 * slot_out);
     }
     if (lane == 0) tma_store_wait_all();
   }
@@ -1219,7 +1255,7 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dq_kernel, ATQ_SMEM_BYTES);
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATK_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
-  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dq_kernel, dim3(grid), dim3(AT_THREADS), ATQ_SMEM_BYTES, stream, mq, mdo, mk, mv, mkmn, mdq, p, acc_dq));
+  GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dq_kernel, dim3(grid), dim3(ATQ_THREADS), ATQ_SMEM_BYTES, stream, mq, mdo, mk, mv, mkmn, mdq, p, acc_dq));
   GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_bwd_dkv_kernel, dim3(grid), dim3(AT_THREADS), ATK_SMEM_BYTES, stream, mk, mv, mq, mdo, mqmn, mdomn, mdk, mdv,
                                        p, acc_dk, acc_dv));
   ctx->launches += 2;
