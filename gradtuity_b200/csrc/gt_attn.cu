@@ -556,6 +556,321 @@ gt_attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 }
 
+// ---- forward, single pass (no P output) ----------------------------------------------------------------
+// The kernel the training step uses.  Tensor memory: S in two buffers (columns 0 and 128) and FOUR 64-column O
+// accumulators (256 ... 511), one per 32-key chunk of a tile.  The softmax warp that owns rows r and key chunk e of
+// every tile keeps its own running reference maximum and row sum for that chunk, turns S into P = 2^(s - reference)
+// in place, and the P V product adds chunk e's part (four of its sixteen k-steps) into accumulator e: no warp ever
+// needs another warp's maximum while the tiles stream by.  When a tile's maximum exceeds the reference by more than 8
+// (log2 units) the warp rescales its own accumulator once; otherwise the stale reference stays (p <= 2^8).  At the
+// end of the item the four (reference, sum) pairs of a row meet in shared memory and the output is the weighted sum
+// of the four accumulators.  The MMA thread issues S(j+1), P(j) V(j) per tile and relies on the tensor core's issue
+// order: S(j+1) overwrites the buffer whose P(j-1) the earlier P V product read.
+constexpr uint32_t FW_S = 0, FW_O = 256;
+constexpr int ATF_SLOTS = 5;
+constexpr int ATF_STATS_BYTES = 4096;          // [4 chunks][128 rows][reference, sum]
+constexpr int ATF_SMEM_BYTES = AT_SLOT_BYTES + ATF_SLOTS * AT_SLOT_BYTES + ATF_STATS_BYTES + 1024 + 512;
+
+struct FwdSmem {
+  uint32_t q, ring;
+  uint8_t* ring_ptr;
+  float* stats;
+  uint32_t bar_q_full, bar_q_empty, bar_kv_full, bar_kv_empty, bar_s_full, bar_p_full, bar_pv_done, bar_o_full, bar_o_empty, bar_group, bar_drain;
+  uint32_t* tmem_slot;
+  volatile int* abort_flag;
+};
+
+__device__ __forceinline__ FwdSmem carve_fwd(uint8_t* smem_raw) {
+  FwdSmem s;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  s.q = base;
+  s.ring = base + AT_SLOT_BYTES;
+  s.ring_ptr = aligned + AT_SLOT_BYTES;
+  s.stats = reinterpret_cast<float*>(s.ring_ptr + ATF_SLOTS * AT_SLOT_BYTES);
+  uint8_t* ctrl = s.ring_ptr + ATF_SLOTS * AT_SLOT_BYTES + ATF_STATS_BYTES;
+  const uint32_t bars = smem_u32(ctrl);
+  s.bar_q_full = bars;           s.bar_q_empty = bars + 8;
+  s.bar_kv_full = bars + 16;     s.bar_kv_empty = bars + 64;       // up to six slots each
+  s.bar_s_full = bars + 112;     /* two */  s.bar_p_full = bars + 128;   /* two */
+  s.bar_pv_done = bars + 144;    s.bar_o_full = bars + 152;        s.bar_o_empty = bars + 160;
+  s.bar_group = bars + 168;      s.bar_drain = bars + 176;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(ctrl + 256);
+  s.abort_flag = reinterpret_cast<volatile int*>(ctrl + 260);
+  return s;
+}
+
+// O_e(128 x 64) (+)= P(128 x 128 in tensor memory)[:, 32 e .. 32 e + 31] * V[32 e .. 32 e + 31, :] for the four chunks e.
+__device__ __forceinline__ void mma_pv_chunks(uint32_t o_tmem, uint32_t p_tmem, uint32_t sb, bool keep) {
+  constexpr uint32_t idesc = make_idesc(64, false, true);
+#pragma unroll
+  for (int kk = 0; kk < 16; ++kk)
+    tc_mma_tf32_ts(o_tmem + (uint32_t)(kk >> 2) * 64u, p_tmem + (uint32_t)kk * 8u, make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc,
+                   (keep || (kk & 3)) ? 1u : 0u);
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                          const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const FwdSmem sm = carve_fwd(smem_raw);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    mbar_init(sm.bar_q_full, 1); mbar_init(sm.bar_q_empty, 1);
+    for (int i = 0; i < ATF_SLOTS; ++i) { mbar_init(sm.bar_kv_full + 8 * i, 1); mbar_init(sm.bar_kv_empty + 8 * i, 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(sm.bar_s_full + 8 * i, 1); mbar_init(sm.bar_p_full + 8 * i, AT_SOFTMAX_WARPS); }
+    mbar_init(sm.bar_pv_done, 1);
+    mbar_init(sm.bar_o_full, 1); mbar_init(sm.bar_o_empty, AT_SOFTMAX_WARPS);
+    mbar_init(sm.bar_group, AT_SOFTMAX_WARPS); mbar_init(sm.bar_drain, 1);
+    *sm.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(sm.tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  gt_let_next_kernel_start();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *sm.tmem_slot;
+  gt_wait_for_previous_kernel();         // set-up above overlaps the previous kernel's tail; global memory from here on
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) {
+      long long ring_it = 0; int q_it = 0;
+      bool ok = true;
+      auto load_slot = [&](const CUtensorMap* map, bool is_v, int row0, int h, int b) -> bool {
+        const int slot = (int)(ring_it % ATF_SLOTS);
+        const uint32_t par = (uint32_t)((ring_it / ATF_SLOTS) & 1);
+        if (!mbar_wait(sm.bar_kv_empty + 8 * slot, par ^ 1u, sm.abort_flag, p.status)) return false;
+        const uint32_t dst = sm.ring + slot * AT_SLOT_BYTES, full = sm.bar_kv_full + 8 * slot;
+        mbar_expect_tx(full, AT_SLOT_BYTES);
+        if (is_v) {
+          tma_load_5d(dst, map, full, 0, row0, 0, h, b);
+        } else {
+          tma_load_4d(dst, map, full, 0, row0, h, b);
+          tma_load_4d(dst + 16384, map, full, 32, row0, h, b);
+        }
+        ++ring_it;
+        return true;
+      };
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int i, h, b;
+        item_coords(p, item, i, h, b);
+        // ring order: K0; then per tile K(j+1), V(j).  K0 needs only a free slot and goes out before the wait for Q's tile.
+        ok = load_slot(&map_k, false, 0, h, b);
+        if (!ok || !mbar_wait(sm.bar_q_empty, (uint32_t)(q_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+        mbar_expect_tx(sm.bar_q_full, AT_SLOT_BYTES);
+        tma_load_4d(sm.q, &map_q, sm.bar_q_full, 0, i * AT_TILE, h, b);
+        tma_load_4d(sm.q + 16384, &map_q, sm.bar_q_full, 32, i * AT_TILE, h, b);
+        ++q_it;
+        if (item + (int)gridDim.x < p.num_items) {     // the next item's Q towards L2
+          int i2, h2, b2;
+          item_coords(p, item + (int)gridDim.x, i2, h2, b2);
+          prefetch_tile(&map_q, i2 * AT_TILE, h2, b2);
+        }
+        for (int j = 0; ok && j <= i; ++j) {
+          if (j + 1 <= i) ok = load_slot(&map_k, false, (j + 1) * AT_TILE, h, b);
+          if (ok) ok = load_slot(&map_v, true, j * AT_TILE, h, b);
+        }
+      }
+      if (!ok) {     // aborting: let the loads already issued land before shared memory is released
+        const long long first = ring_it > ATF_SLOTS ? ring_it - ATF_SLOTS : 0;
+        for (long long r = first; r < ring_it; ++r) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(sm.bar_kv_full + 8 * (int)(r % ATF_SLOTS), (uint32_t)((r / ATF_SLOTS) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      long long ring_it = 0; int q_it = 0, s_it = 0 /* S products issued */, tt = 0 /* P V products issued */, o_it = 0;
+      bool ok = true;
+      auto issue_s = [&]() -> bool {            // next ring slot holds a K tile; S goes to buffer s_it & 1
+        const int slot = (int)(ring_it % ATF_SLOTS);
+        if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / ATF_SLOTS) & 1), sm.abort_flag, p.status)) return false;
+        tc_fence_after();
+        mma_qk(tmem_base + FW_S + (uint32_t)((s_it & 1) * 128), sm.q, sm.ring + slot * AT_SLOT_BYTES);
+        tc_commit(sm.bar_kv_empty + 8 * slot);
+        tc_commit(sm.bar_s_full + 8 * (s_it & 1));
+        ++ring_it; ++s_it;
+        return true;
+      };
+      for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+        int i, h, b;
+        item_coords(p, item, i, h, b);
+        if (!mbar_wait(sm.bar_q_full, (uint32_t)(q_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        ++q_it;
+        ok = issue_s();
+        for (int j = 0; ok && j <= i; ++j) {
+          if (j + 1 <= i) { ok = issue_s(); if (!ok) break; }
+          if (j == i) tc_commit(sm.bar_q_empty);                    // every product with this Q has been issued
+          const int slot = (int)(ring_it % ATF_SLOTS);
+          if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / ATF_SLOTS) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (!mbar_wait(sm.bar_p_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          if (j == 0 && !mbar_wait(sm.bar_o_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          mma_pv_chunks(tmem_base + FW_O, tmem_base + FW_S + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, j != 0);
+          if (j < i) tc_commit(sm.bar_kv_empty + 8 * slot);         // the item's last slot stages its output: released there
+          tc_commit(sm.bar_pv_done);
+          if (j == i) { tc_commit(sm.bar_o_full); ++o_it; }
+          ++ring_it; ++tt;
+        }
+      }
+      if (!ok) {                    // aborting: wait (bounded) for the products in flight before tensor memory is released
+        tc_commit(sm.bar_drain);
+        const long long t0 = clock64();
+        while (!mbar_try_wait(sm.bar_drain, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
+      }
+    }
+  } else {
+    // ------------------------------ softmax warps ------------------------------
+    const int q = warp & 3;                    // tensor-memory lane quarter this warp may read
+    const int eset = (warp - 2) >> 2;          // the 32-key chunk of every tile this warp owns (0..3)
+    const int r_local = q * 32 + lane;         // row inside the 128-row tile
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    const uint32_t my_o = lane_base + FW_O + (uint32_t)(eset * 64);      // this warp's accumulator
+    const int sw = r_local & 7;
+    int tt = 0, o_it = 0, g_it = 0;
+    long long ring_base = 0;                   // ring loads of the items so far: 2 per tile
+    bool ok = true;
+    auto group_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.bar_group);
+      const bool r = mbar_wait(sm.bar_group, (uint32_t)(g_it & 1), sm.abort_flag, p.status);
+      ++g_it;
+      return r;
+    };
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      int i, h, b;
+      item_coords(p, item, i, h, b);
+      const int row = i * AT_TILE + r_local;
+      float m_ref = -INFINITY, l = 0.0f;       // of this thread's chunk of the row
+      for (int j = 0; j <= i; ++j) {
+        const int sb = tt & 1;
+        if (!mbar_wait(sm.bar_s_full + 8 * sb, (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+        tc_fence_after();
+        const int col0 = j * AT_TILE + eset * 32;
+        const bool dead = (j == i) && (eset > q);              // chunk wholly right of the diagonal for this warp's rows
+        const int nvalid = (j < i) ? 32 : row - col0 + 1;      // keys <= query
+        const uint32_t s_col = lane_base + FW_S + (uint32_t)(sb * 128 + eset * 32);
+        float v[32];
+        float mx = -INFINITY;
+        if (!dead) {
+          tc_ld32(s_col, v);
+          tc_wait_ld();
+          if (j < i) {                     // warp-uniform: no masked element left of the diagonal
+#pragma unroll
+            for (int t = 0; t < 32; ++t) { v[t] *= p.scale_log2; mx = fmaxf(mx, v[t]); }
+          } else {
+#pragma unroll
+            for (int t = 0; t < 32; ++t) { v[t] = (t < nvalid) ? v[t] * p.scale_log2 : -INFINITY; mx = fmaxf(mx, v[t]); }
+          }
+        }
+        float f = 1.0f;
+        if (mx > m_ref + 8.0f) { f = ex2(m_ref - mx); m_ref = mx; }
+        l *= f;
+        if (j > 0 && __any_sync(0xffffffffu, f != 1.0f)) {
+          // rescale this warp's accumulator: the previous P V product must have completed (no later one has been issued)
+          if (!mbar_wait(sm.bar_pv_done, (uint32_t)(tt & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int part = 0; part < 4; ++part) {
+            float o[16];
+            tc_ld16(my_o + (uint32_t)(part * 16), o);
+            tc_wait_ld();
+#pragma unroll
+            for (int t = 0; t < 16; ++t) o[t] *= f;
+            tc_st16(my_o + (uint32_t)(part * 16), o);
+            tc_wait_st();
+          }
+        }
+        float acc = 0.0f;
+        if (dead || m_ref == -INFINITY) {                      // nothing of this row's chunk is visible (yet)
+#pragma unroll
+          for (int t = 0; t < 32; ++t) v[t] = 0.0f;
+        } else {
+#pragma unroll
+          for (int t = 0; t < 32; ++t) { v[t] = to_tf32(ex2(v[t] - m_ref)); acc += v[t]; }
+        }
+        l += acc;
+        tc_st32(s_col, v);                                     // P over S, in place
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sm.bar_p_full + 8 * sb);
+        ++tt;
+      }
+      if (!ok) break;
+      // ---- the row's four (reference, sum) pairs meet; weights of the four accumulators
+      sm.stats[(eset * 128 + r_local) * 2] = m_ref;
+      sm.stats[(eset * 128 + r_local) * 2 + 1] = l;
+      if (!group_sync()) { ok = false; break; }
+      float M = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) M = fmaxf(M, sm.stats[(e * 128 + r_local) * 2]);
+      float L = 0.0f, w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float me = sm.stats[(e * 128 + r_local) * 2];
+        w[e] = (me > -INFINITY) ? ex2(me - M) : 0.0f;
+        L += sm.stats[(e * 128 + r_local) * 2 + 1] * w[e];
+      }
+      const float inv = 1.0f / L;
+      if (p.lse && eset == 0) p.lse[((long long)b * p.H + h) * p.S + row] = (M + log2f(L)) * AT_LN2;
+      if (!mbar_wait(sm.bar_o_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
+      ++o_it;
+      tc_fence_after();
+      // this thread's 16 output columns: the weighted sum over the four accumulators
+      float out[16];
+#pragma unroll
+      for (int t = 0; t < 16; ++t) out[t] = 0.0f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float o[16];
+        tc_ld16(lane_base + FW_O + (uint32_t)(e * 64 + eset * 16), o);
+        tc_wait_ld();
+        const float we = w[e] * inv;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) out[t] = fmaf(we, o[t], out[t]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(sm.bar_o_empty);
+      // O leaves through the ring slot of the item's last load (V of the last tile), whose reader has completed
+      ring_base += 2LL * (i + 1);
+      const int slot_out = (int)((ring_base - 1) % ATF_SLOTS);
+      {
+        uint8_t* const my_row = sm.ring_ptr + slot_out * AT_SLOT_BYTES + (eset >> 1) * 16384 + r_local * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<float4*>(my_row + ((((eset & 1) * 4 + g) ^ sw) << 4)) = make_float4(out[4 * g], out[4 * g + 1], out[4 * g + 2], out[4 * g + 3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      if (!group_sync()) { ok = false; break; }                  // both warps of every 32 x 32 box have written it (and the statistics have been read)
+      if ((eset & 1) == 0 && lane == 0) {
+        const uint32_t my_sub = sm.ring + (uint32_t)(slot_out * AT_SLOT_BYTES + (eset >> 1) * 16384 + q * 4096);
+        tma_store_4d(&map_o, my_sub, (eset >> 1) * 32, i * AT_TILE + q * 32, h, b, false);
+        tma_store_wait_read<0>();
+      }
+      if (!group_sync()) { ok = false; break; }                  // every store has read its box: the slot goes back to the producer
+      if (warp == 2 && lane == 0) mbar_arrive(sm.bar_kv_empty + 8 * slot_out);
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // ---- backward ----------------------------------------------------------------------------------
 // Both backward kernels hold two operand tiles for the whole item (Q and dO of the query block, or
 // K and V of the key block), stream the other side's tiles through a ring of three 32 KB slots, keep
@@ -1214,8 +1529,14 @@ extern "C" int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* 
   p.online = (!p_out && !two_pass) ? 1 : 0;
   p.lse = lse; p.delta = nullptr; p.o = nullptr; p.d_o = nullptr;
   p.status = ctx->d_status;
-  GT_SMEM_OPT_IN(ctx, gt_attn_fwd_kernel, AT_SMEM_BYTES);
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
+  if (p.online) {
+    GT_SMEM_OPT_IN(ctx, gt_attn_fwd_online_kernel, ATF_SMEM_BYTES);
+    GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_fwd_online_kernel, dim3(grid), dim3(AT_THREADS), ATF_SMEM_BYTES, stream, mq, mk, mv, mo, p));
+    ctx->launches += 1;
+    return GT_OK;
+  }
+  GT_SMEM_OPT_IN(ctx, gt_attn_fwd_kernel, AT_SMEM_BYTES);
   GT_CUDA_OK(ctx, gt_launch_overlapped(gt_attn_fwd_kernel, dim3(grid), dim3(AT_THREADS), AT_SMEM_BYTES, stream, mq, mk, mv, mp, mo, p));
   ctx->launches += 1;
   return GT_OK;
