@@ -76,33 +76,39 @@ __device__ __forceinline__ void item_coords(const AttnParams& p, int item, int& 
   b = r / p.H;
 }
 
+// The products below are issued by ONE thread that shares its scheduler with four busy softmax warps, so every
+// instruction in front of a tcgen05.mma delays it: the descriptors of a k-step are the first k-step's plus a
+// compile-time constant (the start-address field counts 16-byte units and never carries out of its 14 bits here).
+
 // S = A(128 x 64, K-major) * B(128 x 64, K-major)^T into 128 columns of tensor memory: 8 k-steps.
 __device__ __forceinline__ void mma_qk(uint32_t d_tmem, uint32_t sa, uint32_t sb) {
   constexpr uint32_t idesc = make_idesc(128, false, false);
+  const uint64_t da = make_smem_desc(sa, 16, 1024, 2), db = make_smem_desc(sb, 16, 1024, 2);
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
-    const uint32_t off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
-    tc_mma_tf32(d_tmem, make_smem_desc(sa + off, 16, 1024, 2), make_smem_desc(sb + off, 16, 1024, 2), idesc, kk ? 1u : 0u);
+    const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+    tc_mma_tf32(d_tmem, da + off, db + off, idesc, kk ? 1u : 0u);
   }
 }
 // D(128 x 64) (+)= A(128 x 128, K-major: four atoms of 32 columns) * B(128 x 64 stored (k, n), n contiguous:
 // MN-major, two 32-wide chunks 16 KB apart): 16 k-steps.
 __device__ __forceinline__ void mma_pv(uint32_t d_tmem, uint32_t sa, uint32_t sb, bool keep) {
   constexpr uint32_t idesc = make_idesc(64, false, true);
+  const uint64_t da = make_smem_desc(sa, 16, 1024, 2), db = make_smem_desc(sb, 16384, 512, 1);
 #pragma unroll
   for (int kk = 0; kk < 16; ++kk) {
-    const uint32_t a_off = (uint32_t)(kk >> 2) * 16384u + (uint32_t)(kk & 3) * 32u;
-    tc_mma_tf32(d_tmem, make_smem_desc(sa + a_off, 16, 1024, 2), make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc,
-                (keep || kk) ? 1u : 0u);
+    const uint64_t a_off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+    tc_mma_tf32(d_tmem, da + a_off, db + (uint64_t)(kk * 64), idesc, (keep || kk) ? 1u : 0u);
   }
 }
 
 // D(128 x 64) (+)= A(128 x 128 in tensor memory, columns a_tmem .. a_tmem + 127) * B(128 x 64, MN-major as in mma_pv).
 __device__ __forceinline__ void mma_pv_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t sb, bool keep) {
   constexpr uint32_t idesc = make_idesc(64, false, true);
+  const uint64_t db = make_smem_desc(sb, 16384, 512, 1);
 #pragma unroll
   for (int kk = 0; kk < 16; ++kk)
-    tc_mma_tf32_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc, (keep || kk) ? 1u : 0u);
+    tc_mma_tf32_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, db + (uint64_t)(kk * 64), idesc, (keep || kk) ? 1u : 0u);
 }
 
 // One 128 x 64 operand tile (two boxes of 32 columns) into L2.
@@ -603,10 +609,10 @@ __device__ __forceinline__ FwdSmem carve_fwd(uint8_t* smem_raw) {
 // O_e(128 x 64) (+)= P(128 x 128 in tensor memory)[:, 32 e .. 32 e + 31] * V[32 e .. 32 e + 31, :] for the four chunks e.
 __device__ __forceinline__ void mma_pv_chunks(uint32_t o_tmem, uint32_t p_tmem, uint32_t sb, bool keep) {
   constexpr uint32_t idesc = make_idesc(64, false, true);
+  const uint64_t db = make_smem_desc(sb, 16384, 512, 1);
 #pragma unroll
   for (int kk = 0; kk < 16; ++kk)
-    tc_mma_tf32_ts(o_tmem + (uint32_t)(kk >> 2) * 64u, p_tmem + (uint32_t)kk * 8u, make_smem_desc(sb + (uint32_t)kk * 1024u, 16384, 512, 1), idesc,
-                   (keep || (kk & 3)) ? 1u : 0u);
+    tc_mma_tf32_ts(o_tmem + (uint32_t)(kk >> 2) * 64u, p_tmem + (uint32_t)kk * 8u, db + (uint64_t)(kk * 64), idesc, (keep || (kk & 3)) ? 1u : 0u);
 }
 
 __global__ void __launch_bounds__(AT_THREADS, 1)
