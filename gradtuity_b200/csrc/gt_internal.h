@@ -37,6 +37,7 @@ struct gt_ctx {
   cudaEvent_t side_fork;         // input (gt_colsum_acc_beside): forks from `stream` at side_fork, joins again at side_done
   cudaEvent_t side_done;
   int side_pending;              // work was put on side_stream since the last gt_join_beside
+  void* attn_schedules;          // item tables of the attention kernels, by problem shape (gt_attn.cu)
   int64_t launches;
   int tma_round;              // 1: tensor maps use the TFLOAT32 data type (TMA rounds), 0: FLOAT32
   char last_error[256];
@@ -65,6 +66,9 @@ struct gt_ctx {
 // Keyed by the kernel's address: kernels of one signature share a function-pointer TYPE, so a static flag inside
 // a template or a generic lambda would be shared between them.
 int gt_smem_opt_in(gt_ctx* ctx, const void* kernel, int bytes);
+
+// Frees the attention kernels' item tables (gt_destroy).
+void gt_attn_release(gt_ctx* ctx);
 
 // Makes ctx->stream wait for whatever was put on the side stream (gt_colsum_acc_beside); no-op when nothing was.
 extern "C" int gt_join_beside(gt_ctx* ctx);

@@ -117,6 +117,7 @@ extern "C" int gt_destroy(gt_ctx* ctx) {
     delete bc;
     ctx->block_cache = nullptr;
   }
+  gt_attn_release(ctx);
   if (ctx->scratch_event) cudaEventDestroy(ctx->scratch_event);
   if (ctx->side_stream) {
     cudaStreamSynchronize(ctx->side_stream);
