@@ -122,6 +122,21 @@ __device__ __forceinline__ void mma_pv_ts(uint32_t d_tmem, uint32_t a_tmem, uint
     tc_mma_tf32_ts(d_tmem, a_tmem + (uint32_t)kk * 8u, db + (uint64_t)(kk * 64), idesc, (keep || kk) ? 1u : 0u);
 }
 
+// Position in a ring of `n` shared-memory slots: the slot, the parity of the round, the number of steps so far.
+// (Kept as three counters: slot = count % n and parity = (count / n) & 1 would be a 64-bit division per access, on a
+// thread whose every instruction delays the next tcgen05.mma or TMA load.)
+struct RingPos {
+  int slot, n;
+  uint32_t phase;
+  long long count;
+  __device__ __forceinline__ explicit RingPos(int n_) : slot(0), n(n_), phase(0), count(0) {}
+  __device__ __forceinline__ RingPos& operator++() {
+    ++count;
+    if (++slot == n) { slot = 0; phase ^= 1u; }
+    return *this;
+  }
+};
+
 // One 128 x 64 operand tile (two boxes of 32 columns) into L2.
 __device__ __forceinline__ void prefetch_tile(const CUtensorMap* map, int row0, int h, int b) {
   tma_prefetch_l2_4d(map, 0, row0, h, b);
@@ -546,11 +561,11 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
-      long long ring_it = 0; int q_it = 0;
+      RingPos ring_it(ATF_SLOTS); int q_it = 0;
       bool ok = true;
       auto load_slot = [&](const CUtensorMap* map, bool is_v, int row0, int h, int b) -> bool {
-        const int slot = (int)(ring_it % ATF_SLOTS);
-        const uint32_t par = (uint32_t)((ring_it / ATF_SLOTS) & 1);
+        const int slot = ring_it.slot;
+        const uint32_t par = ring_it.phase;
         if (!mbar_wait(sm.bar_kv_empty + 8 * slot, par ^ 1u, sm.abort_flag, p.status)) return false;
         const uint32_t dst = sm.ring + slot * AT_SLOT_BYTES, full = sm.bar_kv_full + 8 * slot;
         mbar_expect_tx(full, AT_SLOT_BYTES);
@@ -584,8 +599,8 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         }
       }
       if (!ok) {     // aborting: let the loads already issued land before shared memory is released
-        const long long first = ring_it > ATF_SLOTS ? ring_it - ATF_SLOTS : 0;
-        for (long long r = first; r < ring_it; ++r) {
+        const long long first = ring_it.count > ATF_SLOTS ? ring_it.count - ATF_SLOTS : 0;
+        for (long long r = first; r < ring_it.count; ++r) {
           const long long t0 = clock64();
           while (!mbar_try_wait(sm.bar_kv_full + 8 * (int)(r % ATF_SLOTS), (uint32_t)((r / ATF_SLOTS) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
         }
@@ -594,11 +609,11 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      long long ring_it = 0; int q_it = 0, s_it = 0 /* S products issued */, tt = 0 /* P V products issued */, o_it = 0;
+      RingPos ring_it(ATF_SLOTS); int q_it = 0, s_it = 0 /* S products issued */, tt = 0 /* P V products issued */, o_it = 0;
       bool ok = true;
       auto issue_s = [&]() -> bool {            // next ring slot holds a K tile; S goes to buffer s_it & 1
-        const int slot = (int)(ring_it % ATF_SLOTS);
-        if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / ATF_SLOTS) & 1), sm.abort_flag, p.status)) return false;
+        const int slot = ring_it.slot;
+        if (!mbar_wait(sm.bar_kv_full + 8 * slot, ring_it.phase, sm.abort_flag, p.status)) return false;
         tc_fence_after();
         mma_qk(tmem_base + FW_S + (uint32_t)((s_it & 1) * 128), sm.q, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_kv_empty + 8 * slot);
@@ -615,8 +630,8 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         for (int j = 0; ok && j <= i; ++j) {
           if (j + 1 <= i) { ok = issue_s(); if (!ok) break; }
           if (j == i) tc_commit(sm.bar_q_empty);                    // every product with this Q has been issued
-          const int slot = (int)(ring_it % ATF_SLOTS);
-          if (!mbar_wait(sm.bar_kv_full + 8 * slot, (uint32_t)((ring_it / ATF_SLOTS) & 1), sm.abort_flag, p.status)) { ok = false; break; }
+          const int slot = ring_it.slot;
+          if (!mbar_wait(sm.bar_kv_full + 8 * slot, ring_it.phase, sm.abort_flag, p.status)) { ok = false; break; }
           if (!mbar_wait(sm.bar_p_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (j == 0 && !mbar_wait(sm.bar_o_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
@@ -861,10 +876,10 @@ __device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_a
 }
 
 // One ring load: a K-major tile (two boxes of 32 columns) or an MN-major tile (one five-dimensional box).
-__device__ __forceinline__ bool bwd_ring_load(const BwdSmem& sm, const AttnParams& p, long long& ring_it, const CUtensorMap* map,
+__device__ __forceinline__ bool bwd_ring_load(const BwdSmem& sm, const AttnParams& p, RingPos& ring_it, const CUtensorMap* map,
                                               bool mn, int row0, int h, int b) {
-  const int slot = (int)(ring_it % sm.nslots);
-  const uint32_t par = (uint32_t)((ring_it / sm.nslots) & 1);
+  const int slot = ring_it.slot;
+  const uint32_t par = ring_it.phase;
   if (!mbar_wait(sm.bar_ring_empty + 8 * slot, par ^ 1u, sm.abort_flag, p.status)) return false;
   const uint32_t dst = sm.ring + slot * AT_SLOT_BYTES, full = sm.bar_ring_full + 8 * slot;
   mbar_expect_tx(full, AT_SLOT_BYTES);
@@ -877,15 +892,15 @@ __device__ __forceinline__ bool bwd_ring_load(const BwdSmem& sm, const AttnParam
   ++ring_it;
   return true;
 }
-__device__ __forceinline__ void bwd_ring_drain(const BwdSmem& sm, long long ring_it) {
-  const long long first = ring_it > sm.nslots ? ring_it - sm.nslots : 0;
-  for (long long r = first; r < ring_it; ++r) {
+__device__ __forceinline__ void bwd_ring_drain(const BwdSmem& sm, const RingPos& ring_it) {
+  const long long first = ring_it.count > sm.nslots ? ring_it.count - sm.nslots : 0;
+  for (long long r = first; r < ring_it.count; ++r) {
     const long long t0 = clock64();
     while (!mbar_try_wait(sm.bar_ring_full + 8 * (int)(r % sm.nslots), (uint32_t)((r / sm.nslots) & 1)) && clock64() - t0 < WAIT_LIMIT_CYCLES) {}
   }
 }
-__device__ __forceinline__ bool bwd_ring_wait(const BwdSmem& sm, const AttnParams& p, long long ring_it) {
-  return mbar_wait(sm.bar_ring_full + 8 * (int)(ring_it % sm.nslots), (uint32_t)((ring_it / sm.nslots) & 1), sm.abort_flag, p.status);
+__device__ __forceinline__ bool bwd_ring_wait(const BwdSmem& sm, const AttnParams& p, const RingPos& ring_it) {
+  return mbar_wait(sm.bar_ring_full + 8 * ring_it.slot, ring_it.phase, sm.abort_flag, p.status);
 }
 
 // Item order of the key-block owner: key block 0 sees every query block, so it goes first.
@@ -926,7 +941,7 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   if (warp == 0) {
     if (lane == 0) {
-      long long ring_it = 0; int f_it = 0;
+      RingPos ring_it(sm.nslots); int f_it = 0;
       bool ok = true;
       for (int k_ = 0, item; ok && (item = sched_item(p, k_)) >= 0; ++k_) {
         int i, h, b;
@@ -959,20 +974,20 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      long long ring_it = 0; int f_it = 0, s_it = 0 /* S / dP pairs issued */, tt = 0 /* dQ products issued */, o_it = 0;
+      RingPos ring_it(sm.nslots); int f_it = 0, s_it = 0 /* S / dP pairs issued */, tt = 0 /* dQ products issued */, o_it = 0;
       bool ok = true;
       auto issue_sdp = [&]() -> bool {        // S = Q K^T and dP = dO V^T of the next key tile
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         // S is single: the softmax warps must have loaded the previous tile's
         if (!mbar_wait(sm.bar_sdp_empty, (uint32_t)(s_it & 1) ^ 1u, sm.abort_flag, p.status)) return false;
         tc_fence_after();
-        int slot = (int)(ring_it % sm.nslots);
+        int slot = ring_it.slot;
         mma_qk(tmem_base + DQ_S, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
-        slot = (int)(ring_it % sm.nslots);
+        slot = ring_it.slot;
         mma_qk(tmem_base + DQ_DP + (uint32_t)((s_it & 1) * 128), sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
@@ -993,7 +1008,7 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           if (!mbar_wait(sm.bar_ds_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (j == 0 && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
-          const int slot = (int)(ring_it % sm.nslots);
+          const int slot = ring_it.slot;
           mma_pv_ts(tmem_base + DQ_ACC, tmem_base + DQ_DP + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, j != 0);     // dQ (+)= dS K
           if (j < i) tc_commit(sm.bar_ring_empty + 8 * slot);      // the item's last slot stages its output: released there
           if (j == i) { tc_commit(sm.bar_out_full); ++o_it; }
@@ -1167,7 +1182,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   if (warp == 0) {
     if (lane == 0) {
-      long long ring_it = 0; int f_it = 0;
+      RingPos ring_it(sm.nslots); int f_it = 0;
       bool ok = true;
       for (int k_ = 0, item; ok && (item = sched_item(p, k_)) >= 0; ++k_) {
         int j, h, b;
@@ -1199,13 +1214,13 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      long long ring_it = 0; int f_it = 0, tt = 0 /* tiles issued so far: S^T buffer and barrier parities */, o_it = 0;
+      RingPos ring_it(sm.nslots); int f_it = 0, tt = 0 /* tiles issued so far: S^T buffer and barrier parities */, o_it = 0;
       int s_tt = 0;                         // S^T products issued so far
       bool ok = true;
       auto issue_st = [&]() -> bool {       // S^T = K Q^T of the next query tile into buffer s_tt & 1
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
-        const int slot = (int)(ring_it % sm.nslots);
+        const int slot = ring_it.slot;
         mma_qk(tmem_base + KV_ST + (uint32_t)((s_tt & 1) * 128), sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         tc_commit(sm.bar_s_full + 8 * (s_tt & 1));
@@ -1215,7 +1230,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       auto issue_dpt = [&]() -> bool {      // dP^T = V dO^T of the same tile
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
-        const int slot = (int)(ring_it % sm.nslots);
+        const int slot = ring_it.slot;
         mma_qk(tmem_base + KV_DPT, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
         tc_commit(sm.bar_ring_empty + 8 * slot);
         tc_commit(sm.bar_dp_full);
@@ -1236,7 +1251,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           if (!mbar_wait(sm.bar_pa_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           if (i == j && !mbar_wait(sm.bar_out_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
-          int slot = (int)(ring_it % sm.nslots);
+          int slot = ring_it.slot;
           mma_pv_ts(tmem_base + KV_DV, tmem_base + KV_ST + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, i != j);
           if (i < nblk - 1) tc_commit(sm.bar_ring_empty + 8 * slot);     // the item's last two slots stage its outputs: released there
           ++ring_it;
@@ -1244,7 +1259,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
           if (!mbar_wait(sm.bar_pb_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
-          slot = (int)(ring_it % sm.nslots);
+          slot = ring_it.slot;
           mma_pv_ts(tmem_base + KV_DK, tmem_base + KV_DPT, sm.ring + slot * AT_SLOT_BYTES, i != j);
           if (i < nblk - 1) tc_commit(sm.bar_ring_empty + 8 * slot);
           ++ring_it; ++tt;
