@@ -589,6 +589,155 @@ __global__ void __launch_bounds__(512) cross_entropy_fused_kernel(float* __restr
   }
   for (int j = j0 + threadIdx.x; j < C; j += blockDim.x) dr[j] = scale * (__expf(xr[j] - lse) - (j == t ? 1.0f : 0.0f));
 }
+// The same with the row held in shared memory, for rows of up to 56 000 classes that start on 16-byte boundaries
+// (GPT-2's 50257 at a pitch of 50272): one persistent block per SM takes rows in turn; the bulk-copy engine brings a
+// row in as eight chunks (an mbarrier each, so the first pass starts on chunk 0 while chunk 7 is still in flight), the
+// second pass overwrites it in place with the gradient, and the engine writes it out chunk by chunk; a chunk of the
+// next row is requested as soon as the store of the same chunk has been read out of shared memory.  Every byte of
+// the logits crosses HBM once in each direction, whatever the L2 holds.
+constexpr int CE_ROW_CHUNKS = 8;
+constexpr int CE_ROW_THREADS = 1024;
+constexpr int CE_ROW_MAX_CLASSES = 56000;
+
+__device__ __forceinline__ void ce_bar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void ce_bar_expect(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool ce_bar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded: after about a second the block gives up, raises the status word and every thread leaves its loops.
+__device__ __forceinline__ bool ce_bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  if (ce_bar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (ce_bar_test(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > 2000000000LL) { *abort_flag = 1; atomicExch(status, GT_ERR_TIMEOUT); return false; }
+  }
+}
+
+__global__ void __launch_bounds__(CE_ROW_THREADS, 1)
+cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, const float* __restrict__ logits, long long ld_x,
+                                 const float* __restrict__ targets, float* __restrict__ row_loss, float* __restrict__ row_lse,
+                                 float scale, int C, long long rows, int* status) {
+  extern __shared__ __align__(128) uint8_t ce_smem[];
+  __shared__ float red[33];
+  __shared__ __align__(8) unsigned long long bars[CE_ROW_CHUNKS];
+  __shared__ int abort_word;
+  __shared__ float s_lse;
+  __shared__ int s_t;
+  volatile int* abort_flag = &abort_word;
+  float4* const row4 = reinterpret_cast<float4*>(ce_smem);
+  const uint32_t row_addr = (uint32_t)__cvta_generic_to_shared(ce_smem);
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  const int n4 = (C + 3) >> 2;                               // 16-byte units of a row (the pitch covers the last one)
+  const int q4 = (n4 + CE_ROW_CHUNKS - 1) / CE_ROW_CHUNKS;   // units per chunk (none is empty: the caller admits C >= 4096 only)
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    for (int c = 0; c < CE_ROW_CHUNKS; ++c) ce_bar_init(bar0 + 8 * c, 1);
+    abort_word = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  auto request = [&](long long row, int c) {                 // chunk c of `row` -> shared memory
+    const int u0 = c * q4, u1 = min(u0 + q4, n4);
+    const uint32_t bytes = (uint32_t)(u1 - u0) * 16u;
+    ce_bar_expect(bar0 + 8 * c, bytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(row_addr + (uint32_t)u0 * 16u), "l"(logits + row * ld_x + (long long)u0 * 4), "r"(bytes), "r"(bar0 + 8 * c) : "memory");
+  };
+  long long row = blockIdx.x;
+  if (tid == 0 && row < rows)
+    for (int c = 0; c < CE_ROW_CHUNKS; ++c) request(row, c);
+  bool ok = true;
+  uint32_t failed_parity = 0;
+  for (int it = 0; ok && row < rows; row += gridDim.x, ++it) {
+    const uint32_t parity = (uint32_t)(it & 1);
+    // ---- pass 1: running maximum and sum, chunk by chunk as they arrive
+    float m = -INFINITY, sum = 0.0f;
+    for (int c = 0; c < CE_ROW_CHUNKS; ++c) {
+      if (!ce_bar_wait(bar0 + 8 * c, parity, abort_flag, status)) { ok = false; break; }     // leaves the chunk loop only
+      const int u1 = min((c + 1) * q4, n4);
+      for (int u = c * q4 + tid; u < u1; u += CE_ROW_THREADS) {
+        float4 v = row4[u];
+        if (4 * u + 3 >= C) {                                // the last unit of the row: columns beyond C do not exist
+          if (4 * u + 1 >= C) v.y = -INFINITY;
+          if (4 * u + 2 >= C) v.z = -INFINITY;
+          v.w = -INFINITY;
+        }
+        const float vm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+        if (vm > m) { sum *= __expf(m - vm); m = vm; }
+        sum += (__expf(v.x - m) + __expf(v.y - m)) + (__expf(v.z - m) + __expf(v.w - m));
+      }
+    }
+    if (!__syncthreads_and(ok)) { ok = false; failed_parity = parity; break; }     // all threads leave together, or none
+    const float gm = block_max_all(m, red);
+    sum = (m == -INFINITY) ? 0.0f : sum * __expf(m - gm);
+    sum = block_sum_all(sum, red);
+    if (tid == 0) {
+      int t = (int)targets[row];
+      if (t < 0 || t >= C) { atomicExch(status, GT_ERR_INVALID_ARG); t = t < 0 ? 0 : C - 1; }
+      const float lse = gm + logf(sum);
+      row_lse[row] = lse;
+      row_loss[row] = lse - reinterpret_cast<const float*>(ce_smem)[t];
+      s_lse = lse;
+      s_t = t;
+    }
+    __syncthreads();
+    const float lse = s_lse;
+    const int t = s_t;
+    // ---- pass 2: the gradient over the row, in place; each chunk leaves as soon as the whole block has written it
+    const long long next = row + gridDim.x;
+    for (int c = 0; c < CE_ROW_CHUNKS; ++c) {
+      const int u0 = c * q4, u1 = min(u0 + q4, n4);
+      for (int u = u0 + tid; u < u1; u += CE_ROW_THREADS) {
+        const float4 x = row4[u];
+        float4 g;
+        g.x = scale * __expf(x.x - lse); g.y = scale * __expf(x.y - lse); g.z = scale * __expf(x.z - lse); g.w = scale * __expf(x.w - lse);
+        if ((t >> 2) == u) {
+          const int k = t & 3;
+          if (k == 0) g.x -= scale; else if (k == 1) g.y -= scale; else if (k == 2) g.z -= scale; else g.w -= scale;
+        }
+        if (4 * u + 3 >= C) {
+          if (4 * u + 1 >= C) g.y = 0.0f;
+          if (4 * u + 2 >= C) g.z = 0.0f;
+          g.w = 0.0f;
+        }
+        row4[u] = g;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncthreads();
+      if (tid == 0) {
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                     ::"l"(dlogits + row * ld_d + (long long)u0 * 4), "r"(row_addr + (uint32_t)u0 * 16u), "r"((uint32_t)(u1 - u0) * 16u) : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      }
+    }
+    // ---- chunk c of the next row may come in once the store of chunk c has been read out of shared memory
+    if (tid == 0 && next < rows) {
+      asm volatile("cp.async.bulk.wait_group.read 7;" ::: "memory"); request(next, 0);
+      asm volatile("cp.async.bulk.wait_group.read 6;" ::: "memory"); request(next, 1);
+      asm volatile("cp.async.bulk.wait_group.read 5;" ::: "memory"); request(next, 2);
+      asm volatile("cp.async.bulk.wait_group.read 4;" ::: "memory"); request(next, 3);
+      asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); request(next, 4);
+      asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); request(next, 5);
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); request(next, 6);
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); request(next, 7);
+    }
+  }
+  if (tid == 0) {
+    if (!ok) {     // giving up: let the copies of the row that was being waited for land (bounded) before shared memory is released
+      const long long t0 = clock64();
+      for (int c = 0; c < CE_ROW_CHUNKS; ++c)
+        while (!ce_bar_test(bar0 + 8 * c, failed_parity) && clock64() - t0 < 2000000000LL) {}
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+}
+
 // dlogits (+)= scale * (softmax - onehot)
 template <bool VEC>
 __global__ void __launch_bounds__(512) cross_entropy_bwd_kernel(float* __restrict__ dlogits, long long ld_d,
@@ -886,10 +1035,16 @@ extern "C" int gt_cross_entropy_fused(gt_ctx* ctx, float* loss, float* row_loss,
   if (!ctx || !loss || !row_loss || !row_lse || !dlogits || !logits || !targets || B <= 0 || C <= 0 || B > 0x7fffffff ||
       C > 0x7fffffff || ld_logits < C || ld_dlogits < C) return GT_ERR_INVALID_ARG;
   const bool vec = (((uintptr_t)logits & 15) == 0) && ld_logits % 4 == 0 && (((uintptr_t)dlogits & 15) == 0) && ld_dlogits % 4 == 0;
-  static const int smem_kb = [] { const char* e = getenv("GRADTUITY_CE_FUSED_SMEM_KB"); return e ? atoi(e) : CE_FUSED_SMEM / 1024; }();
-  if (vec) {
-    GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<true>, 200 * 1024);
-    cross_entropy_fused_kernel<true><<<(unsigned)B, 512, smem_kb * 1024, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss,
+  static const bool row_in_smem = getenv("GRADTUITY_CE_NO_ROW_IN_SMEM") == nullptr;
+  if (vec && row_in_smem && C >= 4096 && C <= CE_ROW_MAX_CLASSES) {
+    const int bytes = (int)((C + 3) / 4 * 16);
+    GT_SMEM_OPT_IN(ctx, cross_entropy_row_in_smem_kernel, CE_ROW_MAX_CLASSES * 4);      // once, for the widest row admitted
+    const unsigned grid = (unsigned)(B < ctx->sm_count ? B : ctx->sm_count);
+    cross_entropy_row_in_smem_kernel<<<grid, CE_ROW_THREADS, bytes, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss, row_lse,
+                                                                                  grad_scale, (int)C, (long long)B, ctx->d_status);
+  } else if (vec) {
+    GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<true>, CE_FUSED_SMEM);
+    cross_entropy_fused_kernel<true><<<(unsigned)B, 512, CE_FUSED_SMEM, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss,
                                                                                       row_lse, grad_scale, (int)C, ctx->d_status);
   } else {
     GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<false>, CE_FUSED_SMEM);

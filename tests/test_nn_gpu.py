@@ -5,6 +5,7 @@ import pytest
 
 from oracle import gemm_oracle as O
 from oracle import gpt2_oracle as GO
+from tests import _util as U
 
 pytestmark = pytest.mark.gpu
 
@@ -431,3 +432,35 @@ def test_zero_grad_clears_a_model_with_one_memset(gt, T, monkeypatch):
     assert len(calls) == 3                                            # [0]; [3..4]; the lone buffer
     assert not own.numpy().any() and not params[0].grad.numpy().any() and not params[4].grad.numpy().any()
     assert np.all(params[2].grad.numpy() == 3.0)
+
+
+@pytest.mark.parametrize("B,C,pitch", [(300, 5003, 5004), (149, 4096, 4096), (7, 50257, 50272), (150, 8190, 8192)])
+def test_cross_entropy_with_the_row_held_in_shared_memory(gt, B, C, pitch):
+    """gt_cross_entropy_fused on wide rows (4096 <= C <= 56000, 16-byte aligned pitch): a persistent block per SM holds a
+    row in shared memory between the two passes.  More rows than SMs (a block takes several), a class count that is not
+    a multiple of four (the last 16-byte unit is partly padding: it must not count, and the padding of dlogits is
+    written as zero), a pitch beyond C; against the float64 oracle."""
+    from ctypes import c_float, c_void_p
+
+    from gradtuity_b200 import _lib
+    lib, ctx = _lib.load_library(), _lib.context()
+    rng = np.random.default_rng(12)
+    logits = np.full((B, pitch), 7.0e3, np.float32)              # the padding holds large values: they must not be read as classes
+    logits[:, :C] = (rng.standard_normal((B, C)) * 3).astype(np.float32)
+    tgt = rng.integers(0, C, B)
+    tgt[0], tgt[-1] = C - 1, 0
+    lr, probs = GO.cross_entropy_forward(logits[:, :C].astype(np.float64), tgt)
+    want = GO.cross_entropy_backward(probs, tgt)
+    dl, dd, dt = U.DeviceBuffer(logits), U.DeviceBuffer(np.full((B, pitch), -1.0, np.float32)), U.DeviceBuffer(tgt.astype(np.float32))
+    loss, row_loss, row_lse = U.DeviceBuffer(np.zeros(1, np.float32)), U.DeviceBuffer(np.zeros(B, np.float32)), U.DeviceBuffer(np.zeros(B, np.float32))
+    _lib.check(lib.gt_cross_entropy_fused(ctx, c_void_p(loss.ptr), c_void_p(row_loss.ptr), c_void_p(row_lse.ptr), c_void_p(dd.ptr), pitch,
+                                          c_void_p(dl.ptr), pitch, c_void_p(dt.ptr), B, C, 1, c_float(1.0 / B)), "gt_cross_entropy_fused")
+    assert _lib.device_status() == 0
+    assert loss.read((1,))[0] == pytest.approx(lr, rel=1e-6)
+    got = dd.read((B, pitch))
+    assert rel(got[:, :C], want) < 1e-5
+    upto = (C + 3) // 4 * 4
+    assert not got[:, C:upto].any() and np.all(got[:, upto:] == -1.0)      # padding inside the last unit zeroed, the rest untouched
+    x64 = logits[:, :C].astype(np.float64)
+    lse = np.log(np.exp(x64 - x64.max(1, keepdims=True)).sum(1)) + x64.max(1)
+    assert np.allclose(row_lse.read((B,)), lse, rtol=1e-6, atol=1e-5)
