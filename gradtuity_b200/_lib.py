@@ -105,6 +105,7 @@ SIGNATURES = {
     "gt_sum_all": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int]),
     "gt_colsum_acc": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "gt_colsum_acc_beside": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "gt_colsum_acc_batched_beside": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64]),
     "gt_join_beside": (c_int, [c_void_p]),
     "gt_repack_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64]),
     "gt_maxpool2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 8),

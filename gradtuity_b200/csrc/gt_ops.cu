@@ -157,10 +157,13 @@ __global__ void __launch_bounds__(256) colsum_acc_kernel(float* __restrict__ db,
 // The same for 16-byte aligned rows with cols % 4 == 0: a block covers 128 columns (one float4 per
 // lane) x 8 row lanes, four rows in flight per thread.
 __global__ void __launch_bounds__(256) colsum_acc_vec_kernel(float* __restrict__ db, const float* __restrict__ dy,
-                                                             long long rows, int cols, long long ld, int rows_per_block) {
+                                                             long long rows, int cols, long long ld, int rows_per_block,
+                                                             long long db_stride, long long dy_stride) {
   __shared__ float4 red[8][32];
   gt_let_next_kernel_start();
   gt_wait_for_previous_kernel();
+  db += blockIdx.z * db_stride;          // batch entry z: its own matrix and its own sums
+  dy += blockIdx.z * dy_stride;
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int c = (blockIdx.x * 32 + cx) * 4;
   const long long r0 = (long long)blockIdx.y * rows_per_block;
@@ -384,7 +387,8 @@ extern "C" int gt_sum_all(gt_ctx* ctx, float* out, const float* x, int64_t n, in
   return GT_OK;
 }
 
-static int colsum_acc_on(gt_ctx* ctx, cudaStream_t stream, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld);
+static int colsum_acc_on(gt_ctx* ctx, cudaStream_t stream, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld,
+                         int64_t batch = 1, int64_t db_stride = 0, int64_t dy_stride = 0);
 
 extern "C" int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld) {
   if (!ctx) return GT_ERR_INVALID_ARG;
@@ -396,9 +400,16 @@ extern "C" int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t ro
 // leave room for small blocks on every SM) instead of in front of them.  gt_join_beside makes the compute stream wait
 // for them; call it before dY is freed or rewritten and before the bias gradient is read.
 extern "C" int gt_colsum_acc_beside(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld) {
-  if (!ctx) return GT_ERR_INVALID_ARG;
+  return gt_colsum_acc_batched_beside(ctx, db, 0, dy, 0, rows, cols, ld, 1);
+}
+
+// `batch` matrices dy + i * dy_stride (rows x cols each) summed into db + i * db_stride in one launch: the q, k, v
+// gradients of an attention layer, which sit in one buffer, and their three adjacent bias gradients.
+extern "C" int gt_colsum_acc_batched_beside(gt_ctx* ctx, float* db, int64_t db_stride, const float* dy, int64_t dy_stride, int64_t rows,
+                                            int64_t cols, int64_t ld, int64_t batch) {
+  if (!ctx || batch <= 0 || batch > 65535) return GT_ERR_INVALID_ARG;
   static const bool off = getenv("GRADTUITY_NO_SIDE_STREAM") != nullptr;
-  if (off) return colsum_acc_on(ctx, ctx->stream, db, dy, rows, cols, ld);
+  if (off) return colsum_acc_on(ctx, ctx->stream, db, dy, rows, cols, ld, batch, db_stride, dy_stride);
   if (!ctx->side_stream) {
     GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
     GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->side_fork, cudaEventDisableTiming));
@@ -406,7 +417,7 @@ extern "C" int gt_colsum_acc_beside(gt_ctx* ctx, float* db, const float* dy, int
   }
   GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_fork, ctx->stream));
   GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->side_fork, 0));
-  const int rc = colsum_acc_on(ctx, ctx->side_stream, db, dy, rows, cols, ld);
+  const int rc = colsum_acc_on(ctx, ctx->side_stream, db, dy, rows, cols, ld, batch, db_stride, dy_stride);
   // recorded even when the launch failed: a join must never wait on an event that was not recorded after its fork
   GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_done, ctx->side_stream));
   ctx->side_pending = 1;
@@ -422,18 +433,27 @@ extern "C" int gt_join_beside(gt_ctx* ctx) {
   return GT_OK;
 }
 
-static int colsum_acc_on(gt_ctx* ctx, cudaStream_t stream, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld) {
+static int colsum_acc_on(gt_ctx* ctx, cudaStream_t stream, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld,
+                         int64_t batch, int64_t db_stride, int64_t dy_stride) {
   if (!ctx || !db || !dy || rows <= 0 || cols <= 0 || cols > 0x7fffffff || ld < cols) return GT_ERR_INVALID_ARG;
+  if (batch > 1 && !((((uintptr_t)dy & 15) == 0) && cols % 4 == 0 && ld % 4 == 0 && dy_stride % 4 == 0)) {
+    for (int64_t i = 0; i < batch; ++i) {                 // the scalar kernel takes one matrix at a time
+      const int rc = colsum_acc_on(ctx, stream, db + i * db_stride, dy + i * dy_stride, rows, cols, ld, 1, 0, 0);
+      if (rc != GT_OK) return rc;
+    }
+    return GT_OK;
+  }
   if ((((uintptr_t)dy & 15) == 0) && cols % 4 == 0 && ld % 4 == 0) {
     const unsigned gxv = (unsigned)((cols + 127) / 128);
-    long long want = ((long long)ctx->sm_count * 4 + gxv - 1) / gxv;
+    long long want = ((long long)ctx->sm_count * 4 + gxv * batch - 1) / (gxv * batch);
     const long long most = (rows + 31) / 32;
     if (want > most) want = most;
     if (want < 1) want = 1;
     if (want > 65535) want = 65535;
     const int rpbv = (int)((rows + want - 1) / want);
     const unsigned gyv = (unsigned)((rows + rpbv - 1) / rpbv);
-    GT_CUDA_OK(ctx, gt_launch_overlapped(colsum_acc_vec_kernel, dim3(gxv, gyv), dim3(256), 0, stream, db, dy, rows, (int)cols, ld, rpbv));
+    GT_CUDA_OK(ctx, gt_launch_overlapped(colsum_acc_vec_kernel, dim3(gxv, gyv, (unsigned)batch), dim3(256), 0, stream, db, dy, rows, (int)cols, ld, rpbv,
+                                         (long long)db_stride, (long long)dy_stride));
     ctx->launches += 1;
     return GT_OK;
   }

@@ -603,10 +603,21 @@ class Tensor:
                 if not group.written[i]:
                     group.slice_tensor(i, (M, N), zero=True)
             dy = group.storage.ptr
-            for i, b in enumerate(bs):          # first: dq / dk / dv were just written by the attention backward
-                if b.requires_grad:
+            # the three bias gradients: one launch when they sit N floats apart (they do when zero_grad made them), beside the GEMMs
+            if all(b.requires_grad for b in bs):
+                for b in bs:
                     ensure_grad(b)
-                    _call("gt_colsum_acc_beside", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
+                gp = [b.grad.ptr for b in bs]
+                if gp[1] - gp[0] == gp[2] - gp[1] and (gp[1] - gp[0]) % F32 == 0:
+                    _call("gt_colsum_acc_batched_beside", _vp(gp[0]), (gp[1] - gp[0]) // F32, _vp(dy), M * N, M, N, N, 3)
+                else:
+                    for i, b in enumerate(bs):
+                        _call("gt_colsum_acc_beside", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
+            else:
+                for i, b in enumerate(bs):
+                    if b.requires_grad:
+                        ensure_grad(b)
+                        _call("gt_colsum_acc_beside", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
             if x.requires_grad:
                 ptr, acc = grad_target(x)
                 if not acc:

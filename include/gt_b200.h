@@ -283,6 +283,9 @@ int gt_colsum_acc(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t
  * rewritten and before db is read by anything but another gt_colsum_acc_beside.  gt_sync, gt_device_status and the
  * device-to-host copies join by themselves.  GRADTUITY_NO_SIDE_STREAM=1 turns the pair into gt_colsum_acc and a no-op. */
 int gt_colsum_acc_beside(gt_ctx* ctx, float* db, const float* dy, int64_t rows, int64_t cols, int64_t ld);
+/* `batch` matrices dy + i * dy_stride (floats) summed into db + i * db_stride in ONE launch on the side stream. */
+int gt_colsum_acc_batched_beside(gt_ctx* ctx, float* db, int64_t db_stride, const float* dy, int64_t dy_stride,
+                                 int64_t rows, int64_t cols, int64_t ld, int64_t batch);
 int gt_join_beside(gt_ctx* ctx);
 int gt_repack_rows(gt_ctx* ctx, float* dst, int64_t ld_dst, const float* src, int64_t ld_src, int64_t rows, int64_t cols); /* copy rows to another pitch */
 /* conv2d as im2col + GEMM (gradtuity/tensor.py:1906-2167; im2col_kernel_2d / col2im_kernel of

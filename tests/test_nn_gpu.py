@@ -381,6 +381,15 @@ def test_column_sums_on_the_side_stream_and_the_join(gt, T):
         _lib.check(lib.gt_join_beside(ctx), "join")
         want = start.astype(np.float64) + 3 * dy.astype(np.float64).sum(0)
         assert rel(a.numpy(), want) < 1e-5 and rel(b.numpy(), want) < 1e-5
+    # three matrices of one buffer into three bias gradients that sit `stride` floats apart, one launch
+    for rows, cols, stride in [(1024, 768, 768), (100, 36, 64), (64, 30, 30)]:           # the last: not 16-byte rows, one matrix at a time
+        dy3 = rng.standard_normal((3, rows, cols)).astype(np.float32)
+        out = T.from_numpy(np.zeros(3 * stride, np.float32))
+        d3 = T.from_numpy(dy3)
+        _lib.check(lib.gt_colsum_acc_batched_beside(ctx, c_void_p(out.ptr), stride, c_void_p(d3.ptr), rows * cols, rows, cols, cols, 3), "batched")
+        _lib.check(lib.gt_join_beside(ctx), "join")
+        got = out.numpy().reshape(3, stride)
+        assert rel(got[:, :cols], dy3.astype(np.float64).sum(1)) < 1e-5 and not got[:, cols:].any()
     # freed while the side stream may still read it: the free joins, and the block's next user cannot overtake the sums
     big = rng.standard_normal((8192, 3072)).astype(np.float32)
     d, acc = T.from_numpy(big), T.from_numpy(np.zeros(3072, np.float32))
