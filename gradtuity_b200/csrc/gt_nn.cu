@@ -389,19 +389,23 @@ template <int KV>
 __global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(float* __restrict__ dx, float* __restrict__ dgamma, float* __restrict__ dbeta,
                                                                  const float* __restrict__ dy, const float* __restrict__ x,
                                                                  const float* __restrict__ mean, const float* __restrict__ rstd,
-                                                                 const float* __restrict__ gamma, long long N, int dx_accumulate) {
+                                                                 const float* __restrict__ gamma, long long N, int dx_accumulate,
+                                                                 float* __restrict__ dx_colsum) {
   constexpr int H = 128 * KV;
-  __shared__ float sg[H], sb[H];
+  __shared__ float sg[H], sb[H], sd[H];
   gt_let_next_kernel_start();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int j = threadIdx.x; j < H; j += 256) { sg[j] = 0.0f; sb[j] = 0.0f; }
+  for (int j = threadIdx.x; j < H; j += 256) { sg[j] = 0.0f; sb[j] = 0.0f; sd[j] = 0.0f; }
   __syncthreads();
   gt_wait_for_previous_kernel();
-  float4 gam[KV], pg[KV], pb[KV];
+  // pd: column sums of the dx values as stored (after the accumulation): when dx is the finished gradient of the
+  // residual stream, they are the bias gradient of the Linear layer that produced the stream, and the separate
+  // pass over dx that would compute them is saved.
+  float4 gam[KV], pg[KV], pb[KV], pd[KV];
 #pragma unroll
   for (int c = 0; c < KV; ++c) {
     gam[c] = reinterpret_cast<const float4*>(gamma)[c * 32 + lane];
-    pg[c] = make_float4(0.f, 0.f, 0.f, 0.f); pb[c] = pg[c];
+    pg[c] = make_float4(0.f, 0.f, 0.f, 0.f); pb[c] = pg[c]; pd[c] = pg[c];
   }
   const long long warps_total = (long long)gridDim.x * 8;
   for (long long row = (long long)blockIdx.x * 8 + warp; row < N; row += warps_total) {
@@ -430,6 +434,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(float* __restri
                                k * ((float)H * dxh[c].z - s1 - xh[c].z * s2), k * ((float)H * dxh[c].w - s1 - xh[c].w * s2));
         if (dx_accumulate) { const float4 o = dxr[c * 32 + lane]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
         dxr[c * 32 + lane] = v;
+        pd[c].x += v.x; pd[c].y += v.y; pd[c].z += v.z; pd[c].w += v.w;
       }
     }
   }
@@ -438,11 +443,13 @@ __global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(float* __restri
     const int j = (c * 32 + lane) * 4;
     atomicAdd(&sg[j], pg[c].x); atomicAdd(&sg[j + 1], pg[c].y); atomicAdd(&sg[j + 2], pg[c].z); atomicAdd(&sg[j + 3], pg[c].w);
     atomicAdd(&sb[j], pb[c].x); atomicAdd(&sb[j + 1], pb[c].y); atomicAdd(&sb[j + 2], pb[c].z); atomicAdd(&sb[j + 3], pb[c].w);
+    if (dx_colsum) { atomicAdd(&sd[j], pd[c].x); atomicAdd(&sd[j + 1], pd[c].y); atomicAdd(&sd[j + 2], pd[c].z); atomicAdd(&sd[j + 3], pd[c].w); }
   }
   __syncthreads();
   for (int j = threadIdx.x; j < H; j += 256) {
     if (dgamma) atomicAdd(dgamma + j, sg[j]);
     if (dbeta) atomicAdd(dbeta + j, sb[j]);
+    if (dx_colsum) atomicAdd(dx_colsum + j, sd[j]);
   }
 }
 
@@ -969,7 +976,14 @@ extern "C" int gt_layernorm(gt_ctx* ctx, float* y, float* mean, float* rstd, con
 extern "C" int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
                                      const float* mean, const float* rstd, const float* gamma, int64_t N, int64_t H,
                                      int dx_accumulate) {
-  if (!ctx || !dy || !x || !mean || !rstd || !gamma || N <= 0 || H <= 0 || N > 0x7fffffff) return GT_ERR_INVALID_ARG;
+  return gt_layernorm_backward_colsum(ctx, dx, dgamma, dbeta, nullptr, dy, x, mean, rstd, gamma, N, H, dx_accumulate);
+}
+
+// The same, and dx_colsum[j] += sum over rows of dx[row, j] as stored (after the accumulation) when dx_colsum is given.
+extern "C" int gt_layernorm_backward_colsum(gt_ctx* ctx, float* dx, float* dgamma, float* dbeta, float* dx_colsum, const float* dy,
+                                            const float* x, const float* mean, const float* rstd, const float* gamma, int64_t N, int64_t H,
+                                            int dx_accumulate) {
+  if (!ctx || !dy || !x || !mean || !rstd || !gamma || N <= 0 || H <= 0 || N > 0x7fffffff || (dx_colsum && !dx)) return GT_ERR_INVALID_ARG;
   if (H > 256 * LN_MAX_COLS_PER_THREAD) GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "layernorm backward supports H <= %d, got %lld", 256 * LN_MAX_COLS_PER_THREAD, (long long)H);
   const bool al = ((((uintptr_t)dx | (uintptr_t)dy | (uintptr_t)x | (uintptr_t)gamma) & 15) == 0);
   if (al && H % 128 == 0 && H / 128 <= 8) {
@@ -986,7 +1000,7 @@ extern "C" int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, floa
       } \
       const long long cap = (long long)ctx->sm_count * per_sm; \
       nb = (unsigned)(wb < cap ? wb : cap); \
-      GT_CUDA_OK(ctx, gt_launch_overlapped(layernorm_bwd_warp_kernel<KV_>, dim3(nb), dim3(256), 0, ctx->stream, dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, dx_accumulate)); } break
+      GT_CUDA_OK(ctx, gt_launch_overlapped(layernorm_bwd_warp_kernel<KV_>, dim3(nb), dim3(256), 0, ctx->stream, dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, dx_accumulate, dx_colsum)); } break
     switch ((int)(H / 128)) { GT_LN_CASE(1); GT_LN_CASE(2); GT_LN_CASE(3); GT_LN_CASE(4); GT_LN_CASE(5); GT_LN_CASE(6); GT_LN_CASE(7); GT_LN_CASE(8); }
 #undef GT_LN_CASE
     GT_LAUNCH_CHECK(ctx, 1);
@@ -996,7 +1010,10 @@ extern "C" int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, floa
   const int rpb = (int)((N + blocks - 1) / blocks);
   blocks = (N + rpb - 1) / rpb;
   layernorm_bwd_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(dx, dgamma, dbeta, dy, x, mean, rstd, gamma, N, (int)H, rpb, dx_accumulate);
-  GT_LAUNCH_CHECK(ctx, 1);
+  GT_CUDA_OK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  if (dx_colsum) return gt_colsum_acc(ctx, dx_colsum, dx, N, H, H);      // this form of the kernel does not carry the sums
+  return GT_OK;
 }
 
 extern "C" int gt_embedding(gt_ctx* ctx, float* out, const float* W, const float* idx, int64_t n, int64_t D, int64_t V) {

@@ -203,6 +203,13 @@ class Tensor:
     _pitch = None
     # (group, index) when this tensor's gradient must live in a slice of a shared buffer (see _GradGroup).
     _grad_slot = None
+    # The bias of the Linear layer that produced this tensor, when the column sums of this tensor's finished gradient
+    # are that bias's gradient (linear_add, mlp_gelu): the op that writes the last contribution may compute them.
+    _grad_colsum_bias = None
+    # Children of this node whose backward has not run yet (valid during backward()).
+    _n_pending = 0
+    # On a gradient tensor: its column sums have already been added to the producer's bias gradient.
+    _colsum_done = False
 
     def __init__(self, data, shape: tuple[int, ...] | None = None, requires_grad: bool = False, name: str = "") -> None:
         if shape is None:
@@ -376,6 +383,11 @@ class Tensor:
             else:
                 topo.append(node)
 
+        for node in topo:
+            node._n_pending = 0
+        for node in topo:
+            for p in node._parents:
+                p._n_pending += 1
         obs = _backward_observer
         if obs is not None:
             obs.begin(topo)
@@ -384,6 +396,8 @@ class Tensor:
             parents = node._parents
             if node._backward is not None and node.grad is not None:
                 node._backward(node.grad)
+            for p in parents:
+                p._n_pending -= 1
             if parents:
                 node._parents = ()
                 node._backward = None
@@ -529,9 +543,11 @@ class Tensor:
         if weight._shape[1] != bias._shape[0]:
             raise ValueError(f"bias size {bias._shape[0]} doesn't match weight out_features {weight._shape[1]}")
 
-    def _linear_backward(self, x: "Tensor", weight: "Tensor", bias: "Tensor", dz_ptr: int, M: int, K: int, N: int) -> None:
-        """dX += dZ·Wᵀ (NT), dW += Xᵀ·dZ (TN), db += column sums of dZ (gradtuity/tensor.py:1628-1679)."""
-        if bias.requires_grad:
+    def _linear_backward(self, x: "Tensor", weight: "Tensor", bias: "Tensor", dz_ptr: int, M: int, K: int, N: int,
+                         bias_done: bool = False) -> None:
+        """dX += dZ·Wᵀ (NT), dW += Xᵀ·dZ (TN), db += column sums of dZ (gradtuity/tensor.py:1628-1679).
+        `bias_done`: the kernel that wrote dZ has already added its column sums to the bias gradient."""
+        if bias.requires_grad and not bias_done:
             # the column sums are memory-bound and read what the two GEMMs read: they run beside them, on the side stream
             ensure_grad(bias)
             _call("gt_colsum_acc_beside", _vp(bias.grad.ptr), _vp(dz_ptr), M, N, N)
@@ -541,7 +557,7 @@ class Tensor:
         if weight.requires_grad:
             ptr, acc = grad_target(weight)
             _gemm.gemm(LAYOUT_TN, K, N, M, x.ptr, K, dz_ptr, N, ptr, N, accumulate=acc)
-        if bias.requires_grad:
+        if bias.requires_grad and not bias_done:
             _call("gt_join_beside")          # before dZ can be freed and the bias gradient read
 
     def linear(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
@@ -683,11 +699,13 @@ class Tensor:
         x = self
 
         def _backward(g: "Tensor") -> None:
-            self._linear_backward(x, weight, bias, g.ptr, M, K, N)
+            self._linear_backward(x, weight, bias, g.ptr, M, K, N, bias_done=g._colsum_done)
             if residual.requires_grad:
                 pass_grad(residual, g)
 
         out._set_graph(parents=(self, weight, bias, residual), backward_fn=_backward)
+        if bias.requires_grad:
+            out._grad_colsum_bias = bias
         return out
 
     def mlp_gelu(self, w1: "Tensor", b1: "Tensor", w2: "Tensor", b2: "Tensor", residual: "Tensor | None" = None) -> "Tensor":
@@ -722,7 +740,7 @@ class Tensor:
             h.free(); pre.free()
 
         def _backward(g: "Tensor") -> None:
-            if b2.requires_grad:             # beside the GEMMs that follow
+            if b2.requires_grad and not g._colsum_done:             # beside the GEMMs that follow
                 ensure_grad(b2)
                 _call("gt_colsum_acc_beside", _vp(b2.grad.ptr), _vp(g.ptr), M, N, N)
             if w2.requires_grad:
@@ -742,6 +760,8 @@ class Tensor:
                 pass_grad(residual, g)
 
         out._set_graph(parents=(self, w1, b1, w2, b2) + ((residual,) if residual is not None else ()), backward_fn=_backward)
+        if b2.requires_grad and out._shape[-1] == N:
+            out._grad_colsum_bias = b2
         return out
 
     def linear_relu(self, weight: "Tensor", bias: "Tensor") -> "Tensor":
@@ -1020,7 +1040,16 @@ class Tensor:
             if beta.requires_grad:
                 ensure_grad(beta)
                 db_ptr = beta.grad.ptr
-            _call("gt_layernorm_backward", _vp(dx_ptr), _vp(dg_ptr), _vp(db_ptr), _vp(g.ptr), _vp(x.ptr), _vp(mean.ptr),
+            cs_ptr = 0
+            cb = x._grad_colsum_bias
+            if (cb is not None and dx_ptr and x._n_pending == 1 and cb.numel == Hd and not x.grad._colsum_done
+                    and os.environ.get("GRADTUITY_NO_LN_COLSUM") is None):
+                # This is the last contribution to x.grad (every other consumer of x has run): the kernel adds the
+                # column sums of the finished gradient to the bias gradient of the layer that produced x.
+                ensure_grad(cb)
+                cs_ptr = cb.grad.ptr
+                x.grad._colsum_done = True
+            _call("gt_layernorm_backward_colsum", _vp(dx_ptr), _vp(dg_ptr), _vp(db_ptr), _vp(cs_ptr), _vp(g.ptr), _vp(x.ptr), _vp(mean.ptr),
                   _vp(rstd.ptr), _vp(gamma.ptr), Nr, Hd, 1 if dx_acc else 0)
 
         out._set_graph(parents=(self, gamma, beta), backward_fn=_backward)

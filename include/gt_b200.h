@@ -330,6 +330,12 @@ int gt_layernorm(gt_ctx* ctx, float* y, float* mean, float* rstd, const float* x
 int gt_layernorm_backward(gt_ctx* ctx, float* dx, float* dgamma, float* dbeta, const float* dy, const float* x,
                           const float* mean, const float* rstd, const float* gamma, int64_t N, int64_t H,
                           int dx_accumulate);
+/* The same; with dx_colsum given, dx_colsum[j] += sum over rows of dx[row, j] as stored (after the accumulation).  When
+ * dx is then the finished gradient of a residual stream, these are the bias gradient of the Linear layer that produced
+ * the stream (gradtuity/tensor.py:1673-1679 computes it with a separate pass over the gradient). */
+int gt_layernorm_backward_colsum(gt_ctx* ctx, float* dx, float* dgamma, float* dbeta, float* dx_colsum, const float* dy,
+                                 const float* x, const float* mean, const float* rstd, const float* gamma, int64_t N, int64_t H,
+                                 int dx_accumulate);
 int gt_embedding(gt_ctx* ctx, float* out, const float* W, const float* idx, int64_t n, int64_t D, int64_t V);
 int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V);
 /* Rows of C logits may be padded: ld_logits / ld_dlogits are the row pitches in elements (>= C).  The tied

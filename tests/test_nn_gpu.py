@@ -473,3 +473,33 @@ def test_cross_entropy_with_the_row_held_in_shared_memory(gt, B, C, pitch):
     x64 = logits[:, :C].astype(np.float64)
     lse = np.log(np.exp(x64 - x64.max(1, keepdims=True)).sum(1)) + x64.max(1)
     assert np.allclose(row_lse.read((B,)), lse, rtol=1e-6, atol=1e-5)
+
+
+@pytest.mark.parametrize("rows,H", [(8192, 768), (300, 128), (77, 96)])
+def test_layernorm_backward_also_sums_the_columns_of_dx(gt, rows, H):
+    """gt_layernorm_backward_colsum: dx, dgamma, dbeta as gt_layernorm_backward, and the column sums of dx AS STORED (with
+    the accumulation) added to a fourth buffer; H = 96 takes the kernel form that does the sums in a second launch."""
+    from ctypes import c_void_p
+
+    from gradtuity_b200 import _lib
+    lib, ctx = _lib.load_library(), _lib.context()
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((rows, H)).astype(np.float32)
+    dy = rng.standard_normal((rows, H)).astype(np.float32)
+    gamma = rng.standard_normal(H).astype(np.float32)
+    dx0 = rng.standard_normal((rows, H)).astype(np.float32)
+    cs0 = rng.standard_normal(H).astype(np.float32)
+    mu = x.astype(np.float64).mean(1); var = x.astype(np.float64).var(1)
+    rstd = 1.0 / np.sqrt(var + 1e-5)
+    xh = (x - mu[:, None]) * rstd[:, None]
+    dxh = dy.astype(np.float64) * gamma
+    want_dx = dx0 + rstd[:, None] * (dxh - dxh.mean(1, keepdims=True) - xh * (dxh * xh).mean(1, keepdims=True))
+    b = {k: U.DeviceBuffer(v) for k, v in dict(x=x, dy=dy, gamma=gamma, dx=dx0, cs=cs0, mean=mu.astype(np.float32), rstd=rstd.astype(np.float32),
+                                               dg=np.zeros(H, np.float32), db=np.zeros(H, np.float32)).items()}
+    P = lambda k: c_void_p(b[k].ptr)
+    _lib.check(lib.gt_layernorm_backward_colsum(ctx, P("dx"), P("dg"), P("db"), P("cs"), P("dy"), P("x"), P("mean"), P("rstd"), P("gamma"), rows, H, 1), "ln")
+    assert _lib.device_status() == 0
+    got_dx = b["dx"].read((rows, H))
+    assert rel(got_dx, want_dx) < 1e-5
+    assert rel(b["cs"].read((H,)), cs0 + got_dx.astype(np.float64).sum(0)) < 1e-5
+    assert rel(b["dg"].read((H,)), (dy * xh).sum(0)) < 1e-5 and rel(b["db"].read((H,)), dy.astype(np.float64).sum(0)) < 1e-5
