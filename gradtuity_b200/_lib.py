@@ -91,6 +91,9 @@ SIGNATURES = {
     "gt_attention_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_int,
                                       c_void_p]),
+    "gt_attention_backward_bias": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int,
+                                           c_int, c_void_p]),
     "gt_launch_count": (c_int, [c_void_p, POINTER(c_int64)]),
     "gt_fill": (c_int, [c_void_p, c_void_p, c_float, c_int64]),
     "gt_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int]),

@@ -62,6 +62,7 @@ struct AttnParams {
   float* delta;             // (B, H, S) rowsum(dO * O) (backward)
   const float* o; const float* d_o;   // (B, S, H * 64), read directly by the dQ kernel for delta
   int* status;
+  float* dbq; float* dbk; float* dbv;   // backward, optional: (H * 64) vectors that receive the column sums of dQ, dK, dV (the projections' bias gradients)
   const int* sched;         // [gridDim.x][sched_stride] item numbers of every CTA in the order it takes them, -1 after the last
   int sched_stride;
 };
@@ -136,6 +137,22 @@ struct RingPos {
     return *this;
   }
 };
+
+// v[0..31] are 32 columns of this lane's row; returns in lane l the sum of column l over the warp's 32 rows (a butterfly
+// of 31 shuffles: each stage keeps half of the columns and adds the partner's half).  v is used up.
+__device__ __forceinline__ float warp_column_sums(float* v, int lane) {
+#pragma unroll
+  for (int s = 16; s >= 1; s >>= 1) {
+    const bool upper = (lane & s) != 0;
+#pragma unroll
+    for (int i = 0; i < s; ++i) {
+      const float send = upper ? v[i] : v[i + s];
+      const float keep = upper ? v[i + s] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+    }
+  }
+  return v[0];
+}
 
 // One 128 x 64 operand tile (two boxes of 32 columns) into L2.
 __device__ __forceinline__ void prefetch_tile(const CUtensorMap* map, int row0, int h, int b) {
@@ -1132,10 +1149,9 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
               make_float4(p.scale * v[4 * g], p.scale * v[4 * g + 1], p.scale * v[4 * g + 2], p.scale * v[4 * g + 3]);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) {
-          tma_store_4d(&map_dq, my_sub, eset * 32, i * AT_TILE + q * 32, h, b, accumulate != 0);
-          tma_store_wait_read<0>();
-        }
+        if (lane == 0) tma_store_4d(&map_dq, my_sub, eset * 32, i * AT_TILE + q * 32, h, b, accumulate != 0);
+        if (p.dbq) atomicAdd(p.dbq + h * AT_D + eset * 32 + lane, p.scale * warp_column_sums(v, lane));    // bias gradient of the q projection
+        if (lane == 0) tma_store_wait_read<0>();
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.bar_group);
@@ -1388,8 +1404,10 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         if (lane == 0) {
           if (eset < 2) tma_store_4d(&map_dv, my_sub, eset * 32, j * AT_TILE + q * 32, h, b, acc_dv != 0);
           else tma_store_4d(&map_dk, my_sub, (eset - 2) * 32, j * AT_TILE + q * 32, h, b, acc_dk != 0);
-          tma_store_wait_read<0>();
         }
+        if (float* const dbias = eset < 2 ? p.dbv : p.dbk)        // bias gradients of the v and k projections
+          atomicAdd(dbias + h * AT_D + (eset & 1) * 32 + lane, out_scale * warp_column_sums(v, lane));
+        if (lane == 0) tma_store_wait_read<0>();
         // every warp's store has read its part: the two slots go back to the producer
         __syncwarp();
         if (lane == 0) mbar_arrive(sm.bar_group);
@@ -1501,6 +1519,7 @@ extern "C" int gt_attention_forward(gt_ctx* ctx, float* o, float* p_out, float* 
   static const bool two_pass = getenv("GRADTUITY_ATTENTION_TWO_PASS") != nullptr;   // tuning aid: the two-pass forward also without P
   p.online = (!p_out && !two_pass) ? 1 : 0;
   p.lse = lse; p.delta = nullptr; p.o = nullptr; p.d_o = nullptr;
+  p.dbq = p.dbk = p.dbv = nullptr;
   p.status = ctx->d_status;
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
   if ((rc = attn_schedule(ctx, B, H, p.nblk, grid, &p.sched, &p.sched_stride)) != GT_OK) return rc;
@@ -1520,6 +1539,16 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
                                      const float* k, const float* v, const float* o, const float* lse, float* delta,
                                      int64_t B, int64_t S, int64_t H, int64_t D, float scale, int acc_dq, int acc_dk,
                                      int acc_dv, void* stream_) {
+  return gt_attention_backward_bias(ctx, dq, dk, dv, nullptr, nullptr, nullptr, d_o, q, k, v, o, lse, delta, B, S, H, D, scale, acc_dq, acc_dk,
+                                    acc_dv, stream_);
+}
+
+// The same; a non-null dbq / dbk / dbv (H * 64 floats) also receives the column sums over all tokens of what this call
+// computed for dQ / dK / dV (added to its contents): the bias gradients of the projections that produced q, k, v.
+extern "C" int gt_attention_backward_bias(gt_ctx* ctx, float* dq, float* dk, float* dv, float* dbq, float* dbk, float* dbv, const float* d_o,
+                                          const float* q, const float* k, const float* v, const float* o, const float* lse, float* delta,
+                                          int64_t B, int64_t S, int64_t H, int64_t D, float scale, int acc_dq, int acc_dk, int acc_dv,
+                                          void* stream_) {
   int rc = check_attn_args(ctx, q, k, v, B, S, H, D);
   if (rc != GT_OK) return rc;
   if (!dq || !dk || !dv || !d_o || !o || !lse || !delta) return GT_ERR_INVALID_ARG;
@@ -1546,6 +1575,7 @@ extern "C" int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* d
   p.scale = scale; p.scale_log2 = scale * AT_LOG2E;
   p.write_p = 0; p.online = 0;
   p.lse = const_cast<float*>(lse); p.delta = delta; p.o = o; p.d_o = d_o;
+  p.dbq = dbq; p.dbk = dbk; p.dbv = dbv;
   p.status = ctx->d_status;
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dq_kernel, ATQ_SMEM_BYTES);
   GT_SMEM_OPT_IN(ctx, gt_attn_bwd_dkv_kernel, ATK_SMEM_BYTES);

@@ -126,6 +126,7 @@ class _GradGroup:
         self.numel_each = numel_each
         self.storage: Storage | None = None
         self.written = [False] * members
+        self.colsum_done = [False] * members        # the kernel that wrote slice i has added its column sums to the bias gradient
 
     def slice_tensor(self, index: int, shape: tuple[int, ...], zero: bool) -> "Tensor":
         if self.storage is None:
@@ -619,8 +620,11 @@ class Tensor:
                 if not group.written[i]:
                     group.slice_tensor(i, (M, N), zero=True)
             dy = group.storage.ptr
-            # the three bias gradients: one launch when they sit N floats apart (they do when zero_grad made them), beside the GEMMs
-            if all(b.requires_grad for b in bs):
+            # the three bias gradients: nothing to do when the attention backward has added them already; else one launch
+            # when they sit N floats apart (they do when zero_grad made them), beside the GEMMs
+            if all(group.colsum_done[i] or not b.requires_grad for i, b in enumerate(bs)):
+                pass
+            elif all(b.requires_grad for b in bs) and not any(group.colsum_done):
                 for b in bs:
                     ensure_grad(b)
                 gp = [b.grad.ptr for b in bs]
@@ -631,7 +635,7 @@ class Tensor:
                         _call("gt_colsum_acc_beside", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
             else:
                 for i, b in enumerate(bs):
-                    if b.requires_grad:
+                    if b.requires_grad and not group.colsum_done[i]:
                         ensure_grad(b)
                         _call("gt_colsum_acc_beside", _vp(b.grad.ptr), _vp(dy + i * M * N * F32), M, N, N)
             if x.requires_grad:
@@ -670,6 +674,8 @@ class Tensor:
         for i, o in enumerate(outs):
             o._grad_slot = (group, i)
             o._set_graph(parents=(hub,), backward_fn=_child_backward)
+            if bs[i].requires_grad:
+                o._grad_colsum_bias = bs[i]
         return tuple(outs)
 
     @staticmethod
@@ -916,10 +922,21 @@ class Tensor:
                         st = alloc_storage(B * S * E * F32)
                         scratch.append(st)
                         targets.append((st.ptr, False))
+                # A projection bias whose gradient is the column sums of dQ / dK / dV (linear_qkv marks its outputs): the
+                # kernels add them when this call writes the whole of that gradient (nothing accumulated, no other consumer left).
+                dbias = [0, 0, 0]
+                if os.environ.get("GRADTUITY_NO_ATTN_COLSUM") is None:
+                    for n, t in enumerate((q, k, v)):
+                        cb = t._grad_colsum_bias
+                        if (cb is not None and t.requires_grad and not targets[n][1] and t._n_pending == 1 and t._grad_slot is not None
+                                and cb.numel == E):
+                            ensure_grad(cb)
+                            dbias[n] = cb.grad.ptr
+                            t._grad_slot[0].colsum_done[t._grad_slot[1]] = True
                 delta = alloc_storage(B * H * S * F32)
-                _call("gt_attention_backward", _vp(targets[0][0]), _vp(targets[1][0]), _vp(targets[2][0]), _vp(g.ptr),
-                      _vp(q.ptr), _vp(k.ptr), _vp(v.ptr), _vp(o_st.ptr), _vp(lse.ptr), _vp(delta.ptr), B, S, H, D, scale,
-                      int(targets[0][1]), int(targets[1][1]), int(targets[2][1]), None)
+                _call("gt_attention_backward_bias", _vp(targets[0][0]), _vp(targets[1][0]), _vp(targets[2][0]), _vp(dbias[0]), _vp(dbias[1]),
+                      _vp(dbias[2]), _vp(g.ptr), _vp(q.ptr), _vp(k.ptr), _vp(v.ptr), _vp(o_st.ptr), _vp(lse.ptr), _vp(delta.ptr), B, S, H, D,
+                      scale, int(targets[0][1]), int(targets[1][1]), int(targets[2][1]), None)
                 delta.free()
                 for st in scratch:
                     st.free()

@@ -230,6 +230,13 @@ int gt_attention_backward(gt_ctx* ctx, float* dq, float* dk, float* dv, const fl
                           const float* lse, float* delta, int64_t B, int64_t T, int64_t H,
                           int64_t D, float scale, int acc_dq, int acc_dk, int acc_dv,
                           void* stream);
+/* The same; a non-null dbq / dbk / dbv (H * D floats each) also receives, added to its contents, the column sums over all
+ * tokens of what this call computed for dQ / dK / dV: the bias gradients of the projections that produced q, k and v
+ * (gradtuity/tensor.py:1673-1679 takes them with a separate pass over each gradient). */
+int gt_attention_backward_bias(gt_ctx* ctx, float* dq, float* dk, float* dv, float* dbq, float* dbk, float* dbv,
+                               const float* d_o, const float* q, const float* k, const float* v, const float* o,
+                               const float* lse, float* delta, int64_t B, int64_t T, int64_t H, int64_t D, float scale,
+                               int acc_dq, int acc_dk, int acc_dv, void* stream);
 
 /* The GEMM on HOST buffers: hA, hB, hC, h_bias point to host memory (pinned, for the copies to
  * overlap); leading dimensions in elements.  B is uploaded once, A in `chunks` row blocks of C; the

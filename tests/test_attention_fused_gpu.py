@@ -154,3 +154,42 @@ def test_single_pass_forward_matches_oracle(gt, B, H, S):
     assert np.all(np.isfinite(o)) and np.all(np.isfinite(lse))
     assert O.rel_frobenius(o, merge(ref_o, B, S, H)) <= 3e-3      # peaked rows amplify the tf32 rounding of the scores
     assert np.allclose(lse, ref_lse, rtol=1e-3, atol=5e-3)      # a score of 40 carries a tf32 rounding error of 0.02
+
+
+@pytest.mark.parametrize("B,H,S", [(1, 1, 128), (2, 3, 384), (2, 12, 1024)])
+def test_backward_adds_the_projection_bias_gradients(gt, B, H, S):
+    """gt_attention_backward_bias: dbq / dbk / dbv receive, added to their contents, the column sums over all tokens of the
+    dQ / dK / dV the call wrote; a null pointer leaves that one out; dQ, dK, dV themselves are those of the plain call."""
+    from gradtuity_b200 import _lib
+
+    lib, ctx = _lib.load_library(), _lib.context()
+    rng = np.random.default_rng(S + 5 * H)
+    q, k, v, do = (rng.standard_normal((B, S, H * D)).astype(np.float32) for _ in range(4))
+    want_dq, want_dk, want_dv, _, _ = run_backward(q, k, v, do, B, S, H)
+    scale = 1.0 / np.sqrt(D)
+    bq, bk, bv, bdo = (U.DeviceBuffer(a) for a in (q, k, v, do))
+    bo, bl = U.DeviceBuffer(np.zeros((B, S, H * D), np.float32)), U.DeviceBuffer(np.zeros((B, H, S), np.float32))
+    bd = U.DeviceBuffer(np.zeros((B, H, S), np.float32))
+    _lib.check(lib.gt_attention_forward(ctx, c_void_p(bo.ptr), None, c_void_p(bl.ptr), c_void_p(bq.ptr), c_void_p(bk.ptr),
+                                        c_void_p(bv.ptr), B, S, H, D, c_float(scale), None), "gt_attention_forward")
+    start = rng.standard_normal((3, H * D)).astype(np.float32)
+    for present in ((True, True, True), (False, True, False)):
+        gq, gk, gv = (U.DeviceBuffer(np.full((B, S, H * D), np.nan, np.float32)) for _ in range(3))
+        db = [U.DeviceBuffer(start[i]) for i in range(3)]
+        ptrs = [c_void_p(db[i].ptr) if present[i] else None for i in range(3)]
+        _lib.check(lib.gt_attention_backward_bias(ctx, c_void_p(gq.ptr), c_void_p(gk.ptr), c_void_p(gv.ptr), ptrs[0], ptrs[1], ptrs[2],
+                                                  c_void_p(bdo.ptr), c_void_p(bq.ptr), c_void_p(bk.ptr), c_void_p(bv.ptr), c_void_p(bo.ptr),
+                                                  c_void_p(bl.ptr), c_void_p(bd.ptr), B, S, H, D, c_float(scale), 0, 0, 0, None),
+                   "gt_attention_backward_bias")
+        assert _lib.device_status() == 0
+        shape = (B, S, H * D)
+        for got, want in ((gq.read(shape), want_dq), (gk.read(shape), want_dk), (gv.read(shape), want_dv)):
+            assert np.array_equal(got, want)
+        for i, grad in enumerate((want_dq, want_dk, want_dv)):
+            have = db[i].read((H * D,))
+            if present[i]:
+                # the sums nearly cancel (rows of dS sum to about zero): the bar is relative to the magnitudes that were added
+                tol = 1e-5 * np.abs(grad).sum((0, 1)).max() + 2e-6 * np.abs(start[i]).max()
+                assert np.abs(have - (start[i] + grad.astype(np.float64).sum((0, 1)))).max() <= tol
+            else:
+                assert np.array_equal(have, start[i])
