@@ -2,24 +2,25 @@
 //
 // The reference builds attention from separate launches (gradtuity/nn.py:511-554: three
 // transposes, bmm, scale_inplace, softmax_with_causal_mask, bmm) and keeps S, P, dP and dS, each
-// (B, H, T, T), in memory.  The kernels here compute the same quantities tile by tile in tensor
-// memory and shared memory:
+// (B, H, T, T), in memory.  The kernels here compute the same quantities tile by tile:
 //
-//   gt_attn_fwd_kernel      O = softmax(scale * Q K^T + causal mask) V, row statistics (log-sum-exp)
-//                           saved; P is written out only on request.
-//   gt_attn_bwd_dq_kernel   per 128-query block: recomputes P from Q, K and the saved statistics,
-//                           dP = dO V^T, dS = scale * P (dP - delta), dQ = dS K; also writes
-//                           delta = rowsum(dO * O).
-//   gt_attn_bwd_dkv_kernel  per 128-key block: the transposed products S^T = K Q^T, dP^T = V dO^T,
-//                           dV = P^T dO, dK = dS^T Q.
+//   gt_attn_fwd_online_kernel  O = softmax(scale * Q K^T + causal mask) V in one pass over the key tiles, row
+//                              statistics (log-sum-exp) saved: the form the training step uses.
+//   gt_attn_fwd_kernel         the same in two passes, with P written out on request.
+//   gt_attn_bwd_dq_kernel      per 128-query block: recomputes P from Q, K and the saved statistics,
+//                              dP = dO V^T, dS = scale * P (dP - delta), dQ = dS K; also writes
+//                              delta = rowsum(dO * O).
+//   gt_attn_bwd_dkv_kernel     per 128-key block: the transposed products S^T = K Q^T, dP^T = V dO^T,
+//                              dV = P^T dO, dK = dS^T Q.
 //
-// All three share one structure: a persistent CTA per SM walks (batch, head, block) items, heaviest
-// first; warp 0 issues TMA loads into a ring of 32 KB slots, lane 0 of warp 1 issues tcgen05.mma,
-// warps 2-17 (lane = row of the 128-row tile, four warps per tensor-memory lane quarter, one per
-// 32-column chunk of a tile) do the softmax arithmetic between tensor memory and the shared-memory
-// tile that the next MMA reads as its A operand.  Q, K, V, dO are read in place from the
-// (B, T, H * 64) projection outputs; TMA rounds them to tf32.  The probabilities are rounded to tf32
-// (nearest) before they are written to shared memory, so the tensor core does not truncate them.
+// Common structure: a persistent CTA per SM takes (batch, head, block) items from a table built on the host
+// (heaviest first, each to the CTA with the least work so far); warp 0 issues TMA loads into a ring of 32 KB
+// slots, lane 0 of warp 1 issues tcgen05.mma, warps 2-17 (lane = row of the 128-row tile, four warps per
+// tensor-memory lane quarter, one per 32-column chunk of a tile) do the softmax arithmetic.  In the three
+// training kernels that arithmetic stays in tensor memory: P (or dS, P^T, dS^T) is written over the accumulator
+// it was computed from, rounded to tf32, and the next product reads it from there as its A operand; the products
+// are issued in an order that lets the tensor core's in-order execution stand in for "buffer free" barriers (see
+// each kernel).  Q, K, V, dO are read in place from the (B, T, H * 64) projection outputs; TMA rounds them to tf32.
 //
 // Every wait is bounded (see mbar_wait): on a time-out the CTA raises the context's status word,
 // all roles leave their loops and tensor memory is released.
@@ -811,21 +812,19 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 
 // ---- backward ----------------------------------------------------------------------------------
 // Both backward kernels hold two operand tiles for the whole item (Q and dO of the query block, or
-// K and V of the key block), stream the other side's tiles through a ring of three 32 KB slots, keep
-// S and dP (or their transposes) in tensor memory, and pass P / dS through one 64 KB shared-memory
-// tile that the following product reads as its K-major A operand.  The B operand of those products
+// K and V of the key block) and stream the other side's tiles through a ring of five 32 KB slots; S, dP
+// (or their transposes), P and dS live in tensor memory only.  The B operand of the second products
 // (K, dO or Q, stored (rows, 64) with the head dimension contiguous) is MN-major: it is loaded a second
-// time with the five-dimensional map that lays it out in 32-wide chunks.
-constexpr int ATB_SLOTS = 3;                   // dK / dV kernel: ring slots beside K, V and the 64 KB P^T / dS^T tile
+// time with the five-dimensional map that lays it out in 32-wide chunks (a K-major descriptor cannot read
+// that layout).  The item's last ring slot(s) stage the outputs for TMA stores.
 constexpr int ATB_CTRL_BYTES = 1536;           // barriers, the tensor-memory address, the abort flag, 2 x 128 floats of statistics
-constexpr int ATB_SMEM_BYTES = 2 * AT_SLOT_BYTES + ATB_SLOTS * AT_SLOT_BYTES + AT_P_BYTES + 1024 + ATB_CTRL_BYTES;
 
 struct BwdSmem {
   int nslots;
   uint32_t fix0, fix1, ring, tile;
   uint8_t* tile_ptr;
   uint32_t bar_fix_full, bar_fix_empty, bar_ring_full, bar_ring_empty, bar_sdp_full, bar_sdp_empty;
-  uint32_t bar_t1_full, bar_t1_empty, bar_t2_full, bar_t2_empty, bar_out_full, bar_out_empty, bar_group, bar_drain;
+  uint32_t bar_out_full, bar_out_empty, bar_group, bar_drain;
   uint32_t bar_s_full, bar_dp_full, bar_pa_full, bar_pb_full;      // dK / dV kernel (s_full, pa_full, pb_full: two barriers each)
   uint32_t bar_ds_full, bar_delta_full, bar_delta_empty;           // dQ kernel (two barriers each)
   uint32_t* tmem_slot;
@@ -849,8 +848,6 @@ __device__ __forceinline__ BwdSmem carve_bwd(uint8_t* smem_raw, int nslots, int 
   s.bar_fix_full = bars;        s.bar_fix_empty = bars + 8;
   s.bar_ring_full = bars + 16;  s.bar_ring_empty = bars + 16 + 8 * nslots;       // up to six slots below offset 128
   s.bar_sdp_full = bars + 128;  s.bar_sdp_empty = bars + 136;
-  s.bar_t1_full = bars + 144;   s.bar_t1_empty = bars + 152;
-  s.bar_t2_full = bars + 160;   s.bar_t2_empty = bars + 168;
   s.bar_out_full = bars + 176;  s.bar_out_empty = bars + 184;
   s.bar_group = bars + 192;     s.bar_drain = bars + 200;
   s.bar_s_full = bars + 208;    /* two */  s.bar_dp_full = bars + 224;
@@ -867,8 +864,6 @@ __device__ __forceinline__ void bwd_setup(const BwdSmem& sm, int warp, int out_a
     mbar_init(sm.bar_fix_full, 1); mbar_init(sm.bar_fix_empty, 1);
     for (int i = 0; i < sm.nslots; ++i) { mbar_init(sm.bar_ring_full + 8 * i, 1); mbar_init(sm.bar_ring_empty + 8 * i, 1); }
     mbar_init(sm.bar_sdp_full, 1); mbar_init(sm.bar_sdp_empty, AT_SOFTMAX_WARPS);
-    mbar_init(sm.bar_t1_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_t1_empty, 1);
-    mbar_init(sm.bar_t2_full, AT_SOFTMAX_WARPS); mbar_init(sm.bar_t2_empty, 1);
     mbar_init(sm.bar_out_full, 1); mbar_init(sm.bar_out_empty, out_arrivals);
     mbar_init(sm.bar_group, AT_SOFTMAX_WARPS); mbar_init(sm.bar_drain, 1);
     for (int i = 0; i < 2; ++i) {
