@@ -634,8 +634,7 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         if (!mbar_wait(sm.bar_kv_full + 8 * slot, ring_it.phase, sm.abort_flag, p.status)) return false;
         tc_fence_after();
         mma_qk(tmem_base + FW_S + (uint32_t)((s_it & 1) * 128), sm.q, sm.ring + slot * AT_SLOT_BYTES);
-        tc_commit(sm.bar_kv_empty + 8 * slot);
-        tc_commit(sm.bar_s_full + 8 * (s_it & 1));
+        tc_commit(sm.bar_s_full + 8 * (s_it & 1));            // also tells the first softmax warp that the K slot is free (see there)
         ++ring_it; ++s_it;
         return true;
       };
@@ -654,8 +653,7 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           if (j == 0 && !mbar_wait(sm.bar_o_empty, (uint32_t)(o_it & 1) ^ 1u, sm.abort_flag, p.status)) { ok = false; break; }
           tc_fence_after();
           mma_pv_chunks(tmem_base + FW_O, tmem_base + FW_S + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, j != 0);
-          if (j < i) tc_commit(sm.bar_kv_empty + 8 * slot);         // the item's last slot stages its output: released there
-          tc_commit(sm.bar_pv_done);
+          tc_commit(sm.bar_pv_done);                                // the V slot is handed back by the first softmax warp
           if (j == i) { tc_commit(sm.bar_o_full); ++o_it; }
           ++ring_it; ++tt;
         }
@@ -675,7 +673,7 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     const uint32_t my_o = lane_base + FW_O + (uint32_t)(eset * 64);      // this warp's accumulator
     const int sw = r_local & 7;
     int tt = 0, o_it = 0, g_it = 0;
-    long long ring_base = 0;                   // ring loads of the items so far: 2 per tile
+    int base_mod = 0;                          // ring slot of the item's first load (2 loads per tile: K0; then K(j+1), V(j))
     bool ok = true;
     auto group_sync = [&]() -> bool {
       __syncwarp();
@@ -693,6 +691,13 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const int sb = tt & 1;
         if (!mbar_wait(sm.bar_s_full + 8 * sb, (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
+        if (warp == 2 && lane == 0) {
+          // Ring slots go back to the producer from here, not from the MMA thread (whose every instruction delays the
+          // next product): S(j) complete means K(j) has been read, and, the tensor core executing in issue order
+          // S(j), P(j-1) V(j-1), S(j+1), ..., that the product with V(j-2) has completed too.
+          mbar_arrive(sm.bar_kv_empty + 8 * ((base_mod + (j == 0 ? 0 : 2 * j - 1)) % ATF_SLOTS));
+          if (j >= 2) mbar_arrive(sm.bar_kv_empty + 8 * ((base_mod + 2 * j - 2) % ATF_SLOTS));
+        }
         const int col0 = j * AT_TILE + eset * 32;
         const bool dead = (j == i) && (eset > q);              // chunk wholly right of the diagonal for this warp's rows
         const int nvalid = (j < i) ? 32 : row - col0 + 1;      // keys <= query
@@ -764,6 +769,7 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       if (!mbar_wait(sm.bar_o_full, (uint32_t)(o_it & 1), sm.abort_flag, p.status)) { ok = false; break; }
       ++o_it;
       tc_fence_after();
+      if (warp == 2 && lane == 0 && i >= 1) mbar_arrive(sm.bar_kv_empty + 8 * ((base_mod + 2 * i) % ATF_SLOTS));     // V(i-1); V(i) stages the output
       // this thread's 16 output columns: the weighted sum over the four accumulators
       float out[16];
 #pragma unroll
@@ -781,8 +787,8 @@ gt_attn_fwd_online_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       __syncwarp();
       if (lane == 0) mbar_arrive(sm.bar_o_empty);
       // O leaves through the ring slot of the item's last load (V of the last tile), whose reader has completed
-      ring_base += 2LL * (i + 1);
-      const int slot_out = (int)((ring_base - 1) % ATF_SLOTS);
+      const int slot_out = (base_mod + 2 * i + 1) % ATF_SLOTS;
+      base_mod = (base_mod + 2 * (i + 1)) % ATF_SLOTS;
       {
         uint8_t* const my_row = sm.ring_ptr + slot_out * AT_SLOT_BYTES + (eset >> 1) * 16384 + r_local * 128;
 #pragma unroll
@@ -995,15 +1001,13 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         tc_fence_after();
         int slot = ring_it.slot;
         mma_qk(tmem_base + DQ_S, sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
-        tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
         if (!bwd_ring_wait(sm, p, ring_it)) return false;
         tc_fence_after();
         slot = ring_it.slot;
         mma_qk(tmem_base + DQ_DP + (uint32_t)((s_it & 1) * 128), sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
-        tc_commit(sm.bar_ring_empty + 8 * slot);
         ++ring_it;
-        tc_commit(sm.bar_sdp_full);
+        tc_commit(sm.bar_sdp_full);                           // the ring slots are handed back by the first softmax warp (see there)
         ++s_it;
         return true;
       };
@@ -1022,7 +1026,6 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           tc_fence_after();
           const int slot = ring_it.slot;
           mma_pv_ts(tmem_base + DQ_ACC, tmem_base + DQ_DP + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, j != 0);     // dQ (+)= dS K
-          if (j < i) tc_commit(sm.bar_ring_empty + 8 * slot);      // the item's last slot stages its output: released there
           if (j == i) { tc_commit(sm.bar_out_full); ++o_it; }
           ++ring_it; ++tt;
         }
@@ -1069,7 +1072,7 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     const int sw = r_local & 7;
     int tt = 0, o_it = 0, g_it = 0, n_it = 0;
-    long long ring_base = 0;                   // ring loads of the items so far: 3 per tile
+    int base_mod = 0;                          // ring slot of the item's first load (3 loads per tile: K0, V0; then K(j+1), V(j+1), K(j) MN-major)
     bool ok = true;
     for (int k_ = 0, item; ok && (item = sched_item(p, k_)) >= 0; ++k_, ++n_it) {
       int i, h, b;
@@ -1084,6 +1087,14 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int j = 0; j <= i; ++j) {
         if (!mbar_wait(sm.bar_sdp_full, (uint32_t)(tt & 1), sm.abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
+        if (warp == 2 && lane == 0) {
+          // Ring slots go back to the producer from here, not from the MMA thread: S(j) and dP(j) complete means K(j)
+          // and V(j) have been read and, the tensor core executing in issue order ... dQ(j-2), S(j), dP(j), dQ(j-1) ...,
+          // that the dQ product with the MN-major K(j-2) has completed too.
+          mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + (j == 0 ? 0 : 3 * j - 1)) % sm.nslots));
+          mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + (j == 0 ? 1 : 3 * j)) % sm.nslots));
+          if (j >= 2) mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + 3 * (j - 2) + 4) % sm.nslots));
+        }
         const int col0 = j * AT_TILE + eset * 32;
         const int nvalid = (j < i) ? 32 : row - col0 + 1;        // keys <= query
         const bool dead = (j == i) && (eset > q);                 // chunk wholly right of the diagonal for this warp's rows
@@ -1126,8 +1137,9 @@ gt_attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tc_fence_after();
       // dQ (64 columns: chunks 0 and 1) leaves through the ring slot of the item's last load (K of the last tile,
       // MN-major), whose reader, the last dQ product, has completed; the slot goes back to the producer below.
-      ring_base += 3LL * (i + 1);
-      const int slot_out = (int)((ring_base - 1) % sm.nslots);
+      if (warp == 2 && lane == 0 && i >= 1) mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + 3 * (i - 1) + 4) % sm.nslots));   // MN-major K(i-1); K(i) stages the output
+      const int slot_out = (base_mod + 3 * i + 2) % sm.nslots;
+      base_mod = (base_mod + 3 * (i + 1)) % sm.nslots;
       if (eset < 2) {
         float v[32];
         tc_ld32(lane_base + DQ_ACC + (uint32_t)(eset * 32), v);
@@ -1233,8 +1245,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tc_fence_after();
         const int slot = ring_it.slot;
         mma_qk(tmem_base + KV_ST + (uint32_t)((s_tt & 1) * 128), sm.fix0, sm.ring + slot * AT_SLOT_BYTES);
-        tc_commit(sm.bar_ring_empty + 8 * slot);
-        tc_commit(sm.bar_s_full + 8 * (s_tt & 1));
+        tc_commit(sm.bar_s_full + 8 * (s_tt & 1));          // the ring slots are handed back by the first softmax warp (see there)
         ++ring_it; ++s_tt;
         return true;
       };
@@ -1243,7 +1254,6 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tc_fence_after();
         const int slot = ring_it.slot;
         mma_qk(tmem_base + KV_DPT, sm.fix1, sm.ring + slot * AT_SLOT_BYTES);
-        tc_commit(sm.bar_ring_empty + 8 * slot);
         tc_commit(sm.bar_dp_full);
         ++ring_it;
         return true;
@@ -1264,7 +1274,6 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           tc_fence_after();
           int slot = ring_it.slot;
           mma_pv_ts(tmem_base + KV_DV, tmem_base + KV_ST + (uint32_t)((tt & 1) * 128), sm.ring + slot * AT_SLOT_BYTES, i != j);
-          if (i < nblk - 1) tc_commit(sm.bar_ring_empty + 8 * slot);     // the item's last two slots stage its outputs: released there
           ++ring_it;
           // dK (+)= dS^T Q
           if (!bwd_ring_wait(sm, p, ring_it)) { ok = false; break; }
@@ -1272,7 +1281,6 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           tc_fence_after();
           slot = ring_it.slot;
           mma_pv_ts(tmem_base + KV_DK, tmem_base + KV_DPT, sm.ring + slot * AT_SLOT_BYTES, i != j);
-          if (i < nblk - 1) tc_commit(sm.bar_ring_empty + 8 * slot);
           ++ring_it; ++tt;
           if (i == nblk - 1) { tc_commit(sm.bar_out_full); ++o_it; }
           if (i + 1 < nblk) {
@@ -1293,7 +1301,7 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
     const int sw = r_local & 7;
     int tt = 0, o_it = 0, g_it = 0;
-    long long ring_base = 0;                   // ring loads of the items so far: 4 per tile
+    int base_mod = 0;                          // ring slot of the item's first load (4 loads per tile: Q(j), dO(j); then Q(i+1), dO(i) and Q(i) MN-major, dO(i+1))
     bool ok = true;
     for (int k_ = 0, item; ok && (item = sched_item(p, k_)) >= 0; ++k_) {
       int j, h, b;
@@ -1311,6 +1319,9 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         // ---- S^T -> P^T, in place
         if (!mbar_wait(sm.bar_s_full + 8 * (tt & 1), (uint32_t)((tt >> 1) & 1), sm.abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
+        const int t_in = i - j;                  // tile number inside the item
+        // Ring slots go back to the producer from here, not from the MMA thread: S^T(i) complete means Q(i) has been read
+        if (warp == 2 && lane == 0) mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + (t_in == 0 ? 0 : 4 * t_in - 2)) % sm.nslots));
         if (dead) {
 #pragma unroll
           for (int t = 0; t < 32; ++t) pr[t] = 0.0f;
@@ -1347,6 +1358,15 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         // ---- dP^T -> dS^T, in place (without the factor `scale`: dK takes it once, at the output)
         if (!mbar_wait(sm.bar_dp_full, (uint32_t)(tt & 1), sm.abort_flag, p.status)) { ok = false; break; }
         tc_fence_after();
+        if (warp == 2 && lane == 0) {
+          // dP^T(i) complete: dO(i) has been read and, in issue order ... dV(i-1), dK(i-1), dP^T(i) ..., so have the
+          // MN-major dO(i-1) and Q(i-1)
+          mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + (t_in == 0 ? 1 : 4 * t_in + 1)) % sm.nslots));
+          if (t_in >= 1) {
+            mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + 4 * (t_in - 1) + 3) % sm.nslots));
+            mbar_arrive(sm.bar_ring_empty + 8 * ((base_mod + 4 * (t_in - 1) + 4) % sm.nslots));
+          }
+        }
         if (dead) {
 #pragma unroll
           for (int t = 0; t < 32; ++t) v[t] = 0.0f;
@@ -1384,8 +1404,9 @@ gt_attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(sm.bar_out_empty);
-        ring_base += 4LL * (nblk - j);
-        const int slot_dv = (int)((ring_base - 2) % sm.nslots), slot_dk = (int)((ring_base - 1) % sm.nslots);
+        const int n_tiles = nblk - j;
+        const int slot_dv = (base_mod + 4 * n_tiles - 2) % sm.nslots, slot_dk = (base_mod + 4 * n_tiles - 1) % sm.nslots;
+        base_mod = (base_mod + 4 * n_tiles) % sm.nslots;
         const uint32_t stage_off = (uint32_t)((eset < 2 ? slot_dv : slot_dk) * AT_SLOT_BYTES + (eset & 1) * 16384);
         uint8_t* const my_row = sm.tile_ptr - sm.nslots * AT_SLOT_BYTES + stage_off + r_local * 128;    // the ring ends where the tile would start
         const uint32_t my_sub = sm.ring + stage_off + (uint32_t)(q * 4096);
