@@ -595,6 +595,87 @@ def run_attn(args) -> dict:
     return out
 
 
+def run_nn(args) -> dict:
+    """Kernel-only timing of the memory-bound kernels of the GPT-2 step at its sizes (8192 tokens, 768 / 3072 / 50257
+    columns, 124 M parameters), reported as algorithmic bytes per launch over time against the measured HBM copy
+    bandwidth.  Inputs smaller than L2 are rotated through eight copies so that every launch reads from HBM."""
+    import numpy as np
+    from ctypes import byref, c_float, c_void_p
+
+    from gradtuity_b200 import _lib
+    from gradtuity_b200.optim import AdamW, clip_grad_norm_
+    from gradtuity_b200.tensor import Tensor
+
+    lib = _lib.load_library()
+    ctx = _lib.context()
+    rng = np.random.default_rng(4)
+    M, E, I, V, LD = 8192, 768, 3072, 50257, 50272
+    hbm = _hbm_peak()
+    R = 8                                             # copies of the small operands: 8 x 25 MB > 126 MB of L2
+    P = lambda t: c_void_p(t.ptr)
+    rnd = lambda *shape: Tensor.from_numpy(rng.standard_normal(shape, dtype=np.float32))
+    x = [rnd(M, E) for _ in range(R)]; dy = [rnd(M, E) for _ in range(R)]; y = [Tensor._zeros((M, E)) for _ in range(R)]
+    gamma, beta = rnd(E), rnd(E)
+    mean, rstd = Tensor._zeros((M,)), Tensor._zeros((M,))
+    dg, dbt, cs = Tensor._zeros((E,)), Tensor._zeros((E,)), Tensor._zeros((E,))
+    wide = [rnd(M, I) for _ in range(2)]; cs_wide = Tensor._zeros((I,))
+    _lib.check(lib.gt_layernorm(ctx, P(y[0]), P(mean), P(rstd), P(x[0]), P(gamma), P(beta), M, E, c_float(1e-5)), "gt_layernorm")
+    logits = Tensor._zeros((M, LD)); dlogits = Tensor._zeros((M, LD))
+    _lib.check(lib.gt_memcpy_h2d(ctx, P(logits), (rng.standard_normal((M, LD), dtype=np.float32) * 3).ctypes.data_as(c_void_p), M * LD * 4), "h2d")
+    tgt = Tensor.from_numpy(rng.integers(0, V, M).astype(np.float32))
+    loss, row_loss, row_lse = Tensor._zeros((1,)), Tensor._zeros((M,)), Tensor._zeros((M,))
+    n_par = 124_439_808
+    params = [Tensor.from_numpy(np.zeros(n_par // 8, np.float32), requires_grad=True) for _ in range(8)]
+    for q in params:
+        q.grad = Tensor.from_numpy(np.full(q.shape, 1e-3, np.float32))
+    opt = AdamW(params, lr=1e-4)
+    opt.step()                                        # creates m and v
+    it = [0]
+    def nxt():
+        it[0] += 1
+        return it[0] % R
+    def ln_fwd():
+        i = nxt(); _lib.check(lib.gt_layernorm(ctx, P(y[i]), P(mean), P(rstd), P(x[i]), P(gamma), P(beta), M, E, c_float(1e-5)), "ln")
+    def ln_bwd(colsum):
+        i = nxt()
+        _lib.check(lib.gt_layernorm_backward_colsum(ctx, P(y[i]), P(dg), P(dbt), P(cs) if colsum else None, P(dy[i]), P(x[i]), P(mean), P(rstd),
+                                                    P(gamma), M, E, 1), "ln bwd")
+    cases = {
+        "layernorm forward 8192 x 768": (ln_fwd, 2.0 * M * E * 4),
+        "layernorm backward 8192 x 768, dx accumulated": (lambda: ln_bwd(False), 4.0 * M * E * 4),
+        "the same with the column sums of dx": (lambda: ln_bwd(True), 4.0 * M * E * 4),
+        "column sums 8192 x 768": (lambda: _lib.check(lib.gt_colsum_acc(ctx, P(cs), P(dy[nxt()]), M, E, E), "colsum"), 1.0 * M * E * 4),
+        "column sums 8192 x 3072": (lambda: _lib.check(lib.gt_colsum_acc(ctx, P(cs_wide), P(wide[nxt() % 2]), M, I, I), "colsum"), 1.0 * M * I * 4),
+        "cross-entropy loss + dlogits, one launch, 8192 x 50257": (
+            lambda: _lib.check(lib.gt_cross_entropy_fused(ctx, P(loss), P(row_loss), P(row_lse), P(dlogits), LD, P(logits), LD, P(tgt), M, V, 1,
+                                                          c_float(1.0 / M)), "ce fused"), 2.0 * M * V * 4),
+        "cross-entropy loss alone": (lambda: _lib.check(lib.gt_cross_entropy(ctx, P(loss), P(row_loss), P(row_lse), P(logits), LD, P(tgt), M, V, 1), "ce"),
+                                     1.0 * M * V * 4),
+        "cross-entropy backward alone": (lambda: _lib.check(lib.gt_cross_entropy_backward(ctx, P(dlogits), LD, P(logits), LD, P(tgt), P(row_lse), None,
+                                                                                            c_float(1.0 / M), M, V, 0), "ce bwd"), 2.0 * M * V * 4),
+        "AdamW, 124 M parameters, one launch": (lambda: opt.step(), 7.0 * n_par * 4),
+        "gradient norm (sum of squares), 124 M": (lambda: clip_grad_norm_(params, 1.0, defer=True), 1.0 * n_par * 4),
+    }
+    out = {"nn": True, "config": "GPT-2-small step sizes: 8192 tokens, E = 768, 3072, V = 50257 at a pitch of 50272, 124 M parameters",
+           "hbm_peak_gbs": hbm, "cases": {}}
+    for name, (fn, nbytes) in cases.items():
+        for _ in range(args.warmup):
+            fn()
+        e0, e1 = c_void_p(), c_void_p()
+        lib.gt_event_create(ctx, byref(e0)); lib.gt_event_create(ctx, byref(e1))
+        lib.gt_event_record(ctx, e0)
+        for _ in range(args.steps):
+            fn()
+        lib.gt_event_record(ctx, e1)
+        ms = c_float()
+        _lib.check(lib.gt_event_elapsed_ms(ctx, e0, e1, byref(ms)), "gt_event_elapsed_ms")
+        t = ms.value / args.steps
+        out["cases"][name] = {"ms": round(t, 4), "algorithmic_mb": round(nbytes / 1e6, 1), "gbs": round(nbytes / t / 1e6, 1),
+                              "frac_hbm": round(nbytes / t / 1e6 / hbm, 3)}
+    _lib.device_status()
+    return out
+
+
 def _hbm_peak() -> float:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -746,6 +827,7 @@ def main():
     ap.add_argument("--accumulate", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="kernel-only timing of the whole config-1 GEMM sweep")
     ap.add_argument("--attn", action="store_true", help="kernel-only timing of the batched attention products (GB/s)")
+    ap.add_argument("--nn", action="store_true", help="kernel-only timing of the memory-bound kernels of the GPT-2 step (GB/s)")
     ap.add_argument("--no-train", dest="no_train", action="store_true", help="skip the GPT-2 training leg")
     ap.add_argument("--no-reference-gpu", dest="no_reference_gpu", action="store_true",
                     help="--impl reference: skip the reference's own Triton GEMM on the GPU")
@@ -757,6 +839,9 @@ def main():
         return
     if args.attn:
         print(json.dumps(run_attn(args)), flush=True)
+        return
+    if args.nn:
+        print(json.dumps(run_nn(args)), flush=True)
         return
     if args.shape:
         print(json.dumps(run_micro(args)), flush=True)
