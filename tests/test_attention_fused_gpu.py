@@ -111,7 +111,7 @@ def run_backward(q, k, v, do, B, S, H, accumulate=False):
     return gq.read(shape), gk.read(shape), gv.read(shape), bd.read((B, H, S)), bo.read(shape)
 
 
-@pytest.mark.parametrize("B,H,S", [(1, 1, 128), (2, 3, 256), (1, 2, 512), (2, 12, 1024)])
+@pytest.mark.parametrize("B,H,S", [(1, 1, 128), (2, 3, 256), (1, 2, 512), (2, 12, 1024), (1, 3, 2048), (40, 4, 128)])
 def test_backward_matches_oracle(gt, B, H, S):
     rng = np.random.default_rng(7 * S + H)
     q, k, v, do = (rng.standard_normal((B, S, H * D)).astype(np.float32) for _ in range(4))
@@ -134,7 +134,7 @@ def test_backward_accumulates_into_existing_gradients(gt):
         assert np.allclose(a1 - 1.0, a0, rtol=0, atol=1e-5 * max(1.0, np.abs(a0).max()))
 
 
-@pytest.mark.parametrize("B,H,S", [(1, 1, 128), (2, 3, 256), (1, 2, 640), (2, 12, 1024)])
+@pytest.mark.parametrize("B,H,S", [(1, 1, 128), (2, 3, 256), (1, 2, 640), (2, 12, 1024), (1, 3, 2048), (40, 4, 128)])
 def test_single_pass_forward_matches_oracle(gt, B, H, S):
     """Without a P output the forward is a single pass with a running reference maximum (O rescaled in tensor
     memory when a tile's maximum jumps): O and the log-sum-exp against float64, with row scales that differ by
