@@ -110,6 +110,9 @@ SIGNATURES = {
     "gt_colsum_acc_beside": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "gt_colsum_acc_batched_beside": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64]),
     "gt_join_beside": (c_int, [c_void_p]),
+    "gt_beside_begin": (c_int, [c_void_p]),
+    "gt_beside_end": (c_int, [c_void_p]),
+    "gt_beside_touches": (c_int, [c_void_p, c_void_p, c_size_t]),
     "gt_repack_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64]),
     "gt_maxpool2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int64] * 8),
     "gt_maxpool2d_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),

@@ -37,6 +37,9 @@ struct gt_ctx {
   cudaEvent_t side_fork;         // input (gt_colsum_acc_beside): forks from `stream` at side_fork, joins again at side_done
   cudaEvent_t side_done;
   int side_pending;              // work was put on side_stream since the last gt_join_beside
+  cudaStream_t side_saved;       // the compute stream while gt_beside_begin has `stream` point at side_stream (null otherwise)
+  struct { const char* ptr; size_t nbytes; } side_blocks[16];   // memory the pending side work touches and that may be freed before the join
+  int side_nblocks;              // entries in use; -1: too many to list, any gt_free joins
   void* attn_schedules;          // item tables of the attention kernels, by problem shape (gt_attn.cu)
   int64_t launches;
   int tma_round;              // 1: tensor maps use the TFLOAT32 data type (TMA rounds), 0: FLOAT32
@@ -69,6 +72,11 @@ int gt_smem_opt_in(gt_ctx* ctx, const void* kernel, int bytes);
 
 // Frees the attention kernels' item tables (gt_destroy).
 void gt_attn_release(gt_ctx* ctx);
+
+// Notes a block that pending side-stream work reads or writes and whose owner may free it before the join: gt_free of a
+// block that overlaps a noted one joins first; gt_free of anything else does not have to.
+void gt_side_note_block(gt_ctx* ctx, const void* ptr, size_t nbytes);
+bool gt_side_touches(gt_ctx* ctx, const void* ptr, size_t nbytes);
 
 // Makes ctx->stream wait for whatever was put on the side stream (gt_colsum_acc_beside); no-op when nothing was.
 extern "C" int gt_join_beside(gt_ctx* ctx);

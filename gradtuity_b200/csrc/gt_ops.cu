@@ -415,20 +415,78 @@ extern "C" int gt_colsum_acc_batched_beside(gt_ctx* ctx, float* db, int64_t db_s
     GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->side_fork, cudaEventDisableTiming));
     GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->side_done, cudaEventDisableTiming));
   }
+  if (ctx->side_saved) return colsum_acc_on(ctx, ctx->stream, db, dy, rows, cols, ld, batch, db_stride, dy_stride);   // already on the side stream
   GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_fork, ctx->stream));
   GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->side_fork, 0));
   const int rc = colsum_acc_on(ctx, ctx->side_stream, db, dy, rows, cols, ld, batch, db_stride, dy_stride);
   // recorded even when the launch failed: a join must never wait on an event that was not recorded after its fork
   GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_done, ctx->side_stream));
   ctx->side_pending = 1;
+  if (dy && rows > 0 && ld > 0) gt_side_note_block(ctx, dy, (size_t)(((batch - 1) * (dy_stride > 0 ? dy_stride : 0) + rows * ld) * 4));
   return rc;
+}
+
+// Everything this context launches between gt_beside_begin and gt_beside_end goes to the side stream, ordered behind what
+// the compute stream holds at the begin; gt_join_beside (or gt_sync, gt_device_status, a device-to-host copy) orders the
+// compute stream behind it again.  For memory-bound work whose results the next kernels do not need: the second half of
+// an optimizer step beside the first layers of the next forward pass.  The caller keeps alive what that work touches
+// until the join, or notes it with gt_beside_touches so that gt_free joins by itself.
+extern "C" int gt_beside_begin(gt_ctx* ctx) {
+  if (!ctx || ctx->side_saved) return GT_ERR_INVALID_ARG;
+  static const bool off = getenv("GRADTUITY_NO_SIDE_STREAM") != nullptr;
+  if (off) return GT_OK;
+  if (!ctx->side_stream) {
+    GT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+    GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->side_fork, cudaEventDisableTiming));
+    GT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->side_done, cudaEventDisableTiming));
+  }
+  GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_fork, ctx->stream));
+  GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->side_fork, 0));
+  ctx->side_saved = ctx->stream;
+  ctx->stream = ctx->side_stream;
+  return GT_OK;
+}
+
+extern "C" int gt_beside_end(gt_ctx* ctx) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  if (!ctx->side_saved) return GT_OK;              // side stream switched off, or no matching begin
+  ctx->stream = ctx->side_saved;
+  ctx->side_saved = nullptr;
+  GT_CUDA_OK(ctx, cudaEventRecord(ctx->side_done, ctx->side_stream));
+  ctx->side_pending = 1;
+  return GT_OK;
+}
+
+extern "C" int gt_beside_touches(gt_ctx* ctx, const void* ptr, size_t nbytes) {
+  if (!ctx || !ptr) return GT_ERR_INVALID_ARG;
+  gt_side_note_block(ctx, ptr, nbytes);
+  return GT_OK;
+}
+
+void gt_side_note_block(gt_ctx* ctx, const void* ptr, size_t nbytes) {
+  if (ctx->side_nblocks < 0) return;
+  if (ctx->side_nblocks >= 16) { ctx->side_nblocks = -1; return; }
+  ctx->side_blocks[ctx->side_nblocks].ptr = (const char*)ptr;
+  ctx->side_blocks[ctx->side_nblocks].nbytes = nbytes;
+  ++ctx->side_nblocks;
+}
+
+bool gt_side_touches(gt_ctx* ctx, const void* ptr, size_t nbytes) {
+  if (ctx->side_nblocks < 0) return true;
+  const char* a = (const char*)ptr;
+  for (int i = 0; i < ctx->side_nblocks; ++i) {
+    const char* b = ctx->side_blocks[i].ptr;
+    if (a < b + ctx->side_blocks[i].nbytes && b < a + (nbytes ? nbytes : 1)) return true;
+  }
+  return false;
 }
 
 extern "C" int gt_join_beside(gt_ctx* ctx) {
   if (!ctx) return GT_ERR_INVALID_ARG;
-  if (ctx->side_pending) {
+  if (ctx->side_pending && !ctx->side_saved) {
     GT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->side_done, 0));
     ctx->side_pending = 0;
+    ctx->side_nblocks = 0;
   }
   return GT_OK;
 }

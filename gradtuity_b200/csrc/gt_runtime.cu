@@ -262,8 +262,18 @@ extern "C" int gt_malloc(gt_ctx* ctx, size_t nbytes, void** ptr) {
 extern "C" int gt_free(gt_ctx* ctx, void* ptr) {
   if (!ctx) return GT_ERR_INVALID_ARG;
   if (!ptr) return GT_OK;
-  if (ctx->side_pending) gt_join_beside(ctx);     // the side stream may still read this block
   BlockCache* bc = (BlockCache*)ctx->block_cache;
+  if (ctx->side_pending) {
+    // The side stream may still use this block: join first if the block overlaps one that the pending side work noted
+    // (or if its size is unknown: the block did not come from the cache).
+    size_t size = 0;
+    if (bc && bc->enabled) {
+      std::lock_guard<std::mutex> guard(bc->lock);
+      auto it = bc->size_of.find(ptr);
+      if (it != bc->size_of.end()) size = it->second;
+    }
+    if (size == 0 || gt_side_touches(ctx, ptr, size)) gt_join_beside(ctx);
+  }
   if (bc && bc->enabled) {
     std::lock_guard<std::mutex> guard(bc->lock);
     auto it = bc->size_of.find(ptr);

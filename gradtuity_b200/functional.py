@@ -67,8 +67,9 @@ def zero_grad(params: list[Tensor]) -> None:
     sit side by side too and a batched backward can address them as one batch).  Existing gradients that are
     neighbours inside such a block (or inside the data-parallel gradient arena) are cleared by one memset per run of
     neighbours instead of one per parameter: one memset for a whole model after the first step."""
-    from .tensor import Storage, alloc_storage
+    from .tensor import Storage, alloc_storage, join_side_stream
 
+    join_side_stream()          # an optimizer step still running on the side stream reads the gradients
     fresh = [p for p in params if p.requires_grad and p.grad is None]
     if fresh:
         offsets, total = [], 0

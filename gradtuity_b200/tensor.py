@@ -49,6 +49,16 @@ def _call(name: str, *args) -> None:
     _lib.check(getattr(lib, name)(_lib.context(), *args), name)
 
 
+# The id of the side-stream work that has not been joined yet (0: none), in a list so that other modules can set it.
+_pending_join = [0]
+
+
+def join_side_stream() -> None:
+    """Order the compute stream behind whatever runs on the library's side stream (no-op when nothing does)."""
+    _pending_join[0] = 0
+    _call("gt_join_beside")
+
+
 def _vp(ptr: int):
     return c_void_p(ptr) if ptr else None
 
@@ -211,6 +221,9 @@ class Tensor:
     _n_pending = 0
     # On a gradient tensor: its column sums have already been added to the producer's bias gradient.
     _colsum_done = False
+    # Non-zero while work on the side stream (the second half of an optimizer step) may still be writing this tensor:
+    # the first access to its memory orders the compute stream behind that work (see `ptr`).
+    _join_id = 0
 
     def __init__(self, data, shape: tuple[int, ...] | None = None, requires_grad: bool = False, name: str = "") -> None:
         if shape is None:
@@ -310,6 +323,8 @@ class Tensor:
 
     @property
     def ptr(self) -> int:
+        if self._join_id and self._join_id == _pending_join[0]:
+            join_side_stream()
         if self._pitch is not None:
             self._pack_rows()
         return self._st.ptr
@@ -325,6 +340,8 @@ class Tensor:
 
     def _rows(self) -> tuple[int, int]:
         """(pointer, row pitch in floats) without packing."""
+        if self._join_id and self._join_id == _pending_join[0]:
+            join_side_stream()
         return self._st.ptr, (self._pitch if self._pitch is not None else self._shape[-1])
 
     @property
@@ -418,6 +435,8 @@ class Tensor:
             self._ctx = ctx
 
     def detach(self) -> "Tensor":
+        if self._join_id and self._join_id == _pending_join[0]:
+            join_side_stream()               # the alias carries no mark of its own
         shared = Storage(self._st.ptr, self._st.nbytes, owns=False, base=self._st)
         out = Tensor._wrap(shared, self._shape, requires_grad=False, name=f"{self.name}_detached" if self.name else "")
         out._pitch = self._pitch
@@ -425,6 +444,8 @@ class Tensor:
 
     def view(self, new_shape) -> "Tensor":
         """Same storage, different shape; one dimension may be -1/None (gradtuity/tensor.py:465-524)."""
+        if self._join_id and self._join_id == _pending_join[0]:
+            join_side_stream()               # the alias carries no mark of its own
         dims = list(new_shape)
         infer = None
         product = 1

@@ -294,6 +294,15 @@ int gt_colsum_acc_beside(gt_ctx* ctx, float* db, const float* dy, int64_t rows, 
 int gt_colsum_acc_batched_beside(gt_ctx* ctx, float* db, int64_t db_stride, const float* dy, int64_t dy_stride,
                                  int64_t rows, int64_t cols, int64_t ld, int64_t batch);
 int gt_join_beside(gt_ctx* ctx);
+/* Everything the context launches between the two calls goes to the side stream, ordered behind what the compute stream
+ * holds at the begin; gt_join_beside orders the compute stream behind it again.  Meant for memory-bound work whose
+ * results the next kernels do not need (AdamW of the later layers beside the first layers of the next forward pass).
+ * Allocate nothing in between.  What the side work touches must stay allocated until the join: the caller keeps it
+ * alive, or notes it with gt_beside_touches, after which a gt_free of an overlapping block joins by itself (a gt_free of
+ * any other block of this context's allocator does not). */
+int gt_beside_begin(gt_ctx* ctx);
+int gt_beside_end(gt_ctx* ctx);
+int gt_beside_touches(gt_ctx* ctx, const void* ptr, size_t nbytes);
 int gt_repack_rows(gt_ctx* ctx, float* dst, int64_t ld_dst, const float* src, int64_t ld_src, int64_t rows, int64_t cols); /* copy rows to another pitch */
 /* conv2d as im2col + GEMM (gradtuity/tensor.py:1906-2167; im2col_kernel_2d / col2im_kernel of
  * kernels_cuda/conv_kernels.py).  x is (N, C, H, W); col is (N * H_out * W_out, C * kH * kW) with rows

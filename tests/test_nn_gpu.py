@@ -503,3 +503,45 @@ def test_layernorm_backward_also_sums_the_columns_of_dx(gt, rows, H):
     assert rel(got_dx, want_dx) < 1e-5
     assert rel(b["cs"].read((H,)), cs0 + got_dx.astype(np.float64).sum(0)) < 1e-5
     assert rel(b["dg"].read((H,)), (dy * xh).sum(0)) < 1e-5 and rel(b["db"].read((H,)), dy.astype(np.float64).sum(0)) < 1e-5
+
+
+def test_adamw_split_over_two_streams_gives_the_same_parameters(gt, T, monkeypatch):
+    """A parameter list of more than 64 MB: the later parameters are updated on the side stream.  The first access to one
+    of them joins the streams, so what any later kernel or copy sees equals the one-stream result bit for bit; a kernel
+    that reads a late parameter straight after the step (a GEMM here) sees the updated values."""
+    from gradtuity_b200 import tensor as tmod
+    from gradtuity_b200.optim import AdamW, clip_grad_norm_
+
+    rng = np.random.default_rng(31)
+    shapes = [(2048, 2048)] * 5 + [(64,)]                      # 21 M elements: the last two and a half tensors are "late"
+    init = [rng.standard_normal(s).astype(np.float32) * 0.1 for s in shapes]
+    grads = [[rng.standard_normal(s).astype(np.float32) for s in shapes] for _ in range(3)]
+    probe = rng.standard_normal((8, 2048)).astype(np.float32)
+
+    def run(split: bool):
+        monkeypatch.setenv("GRADTUITY_ADAMW_BESIDE", "1" if split else "0")
+        params = [T.from_numpy(a, requires_grad=True) for a in init]
+        opt = AdamW(params, lr=1e-2, weight_decay=0.1)
+        seen, snapshots = [], []
+        for step in range(3):
+            for p, g in zip(params, grads[step]):
+                p.grad = T.from_numpy(g)
+            _, scale = clip_grad_norm_(params, 1.0, defer=True)
+            opt.step(grad_scale=scale)
+            if split:
+                assert tmod._pending_join[0] != 0 and params[4]._join_id == tmod._pending_join[0] and params[0]._join_id == 0
+            seen.append(T.from_numpy(probe).matmul(params[4]).numpy())          # reads a late parameter at once
+            if split:
+                assert tmod._pending_join[0] == 0                               # that access joined
+            snapshots.append(params[4].numpy())
+        return [p.numpy() for p in params], seen, snapshots
+
+    want, _, _ = run(False)
+    got, got_seen, snapshots = run(True)
+    for a, b in zip(got, want):
+        assert np.array_equal(a, b)
+    # the product saw the parameter as it is after the step (a step moves every element by about 10 %)
+    for step, (a, w) in enumerate(zip(got_seen, snapshots)):
+        assert rel(a, probe.astype(np.float64) @ w.astype(np.float64)) < 1e-3, step
+        if step:
+            assert rel(a, probe.astype(np.float64) @ snapshots[step - 1].astype(np.float64)) > 1e-2
