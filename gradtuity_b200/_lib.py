@@ -127,6 +127,7 @@ SIGNATURES = {
                                      c_int64, c_int64, c_int]),
     "gt_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
     "gt_embedding_backward": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64]),
+    "gt_embedding_backward_scaled": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_float]),
     "gt_cross_entropy": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int]),
     "gt_cross_entropy_fused": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                        c_int64, c_int64, c_int, c_float]),
@@ -142,6 +143,7 @@ SIGNATURES = {
     "gt_dist_destroy": (c_int, [c_void_p]),
     "gt_dist_allreduce": (c_int, [c_void_p, c_void_p, c_int64, c_int]),
     "gt_dist_broadcast": (c_int, [c_void_p, c_void_p, c_int64, c_int]),
+    "gt_dist_allgather": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
     "gt_dist_wait": (c_int, [c_void_p, c_int]),
     "gt_dist_info": (c_int, [c_void_p, POINTER(c_int), POINTER(c_int)]),
     "gt_dist_timeline": (c_int, [c_void_p, POINTER(c_float), c_int, POINTER(c_int)]),

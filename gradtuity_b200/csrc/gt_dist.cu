@@ -48,6 +48,7 @@ struct NcclApi {
   int (*CommDestroy)(ncclComm_t) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
   int (*Broadcast)(const void*, void*, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, ncclComm_t, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   int (*CommGetAsyncError)(ncclComm_t, int*) = nullptr;      // optional (NCCL >= 2.4)
   int (*CommAbort)(ncclComm_t) = nullptr;                    // optional
@@ -72,6 +73,7 @@ int load_nccl(char* err, size_t errlen) {
   GT_SYM(CommDestroy, "ncclCommDestroy");
   GT_SYM(AllReduce, "ncclAllReduce");
   GT_SYM(Broadcast, "ncclBroadcast");
+  GT_SYM(AllGather, "ncclAllGather");
   GT_SYM(GetErrorString, "ncclGetErrorString");
 #undef GT_SYM
   *(void**)(&g_nccl.CommGetAsyncError) = dlsym(h, "ncclCommGetAsyncError");
@@ -263,6 +265,31 @@ extern "C" int gt_dist_allreduce(gt_ctx* ctx, float* ptr, int64_t count, int ave
     }
   }
   GT_NCCL_OK(ctx, g_nccl.AllReduce(ptr, ptr, (size_t)count, ncclFloat32, average ? ncclAvg : ncclSum, st->comm, st->stream));
+  if (slot >= 0) GT_CUDA_OK(ctx, cudaEventRecord(st->tl_end[slot], st->stream));
+  st->pending += 1;
+  return GT_OK;
+}
+
+// dst (world x count floats) = the `count` floats at src of every rank, in rank order; enqueued like gt_dist_allreduce.
+// Every rank must pass the same count.
+extern "C" int gt_dist_allgather(gt_ctx* ctx, float* dst, const float* src, int64_t count) {
+  DistState* st = state_of(ctx);
+  if (!ctx || !dst || !src || count <= 0) return GT_ERR_INVALID_ARG;
+  if (!st) GT_FAIL(ctx, GT_ERR_NOT_INIT, "gt_dist_allgather: process group not initialised");
+  if (!st->comm) GT_FAIL(ctx, GT_ERR_NCCL, "gt_dist_allgather: the communicator was aborted after an error or a time-out");
+  GT_CUDA_OK(ctx, cudaEventRecord(st->ready, ctx->stream));
+  GT_CUDA_OK(ctx, cudaStreamWaitEvent(st->stream, st->ready, 0));
+  int slot = -1;
+  if (st->timeline) {
+    if (st->tl_closed) { st->tl_n = 0; st->tl_closed = false; }
+    if (st->tl_n < DistState::TL_MAX) {
+      slot = st->tl_n++;
+      st->tl_count[slot] = count * st->world;
+      GT_CUDA_OK(ctx, cudaEventRecord(st->tl_ready[slot], ctx->stream));
+      GT_CUDA_OK(ctx, cudaEventRecord(st->tl_start[slot], st->stream));
+    }
+  }
+  GT_NCCL_OK(ctx, g_nccl.AllGather(src, dst, (size_t)count, ncclFloat32, st->comm, st->stream));
   if (slot >= 0) GT_CUDA_OK(ctx, cudaEventRecord(st->tl_end[slot], st->stream));
   st->pending += 1;
   return GT_OK;

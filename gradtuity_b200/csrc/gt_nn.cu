@@ -467,13 +467,13 @@ __global__ void __launch_bounds__(256) embedding_gather_kernel(float* __restrict
   for (int j = threadIdx.x; j < D; j += blockDim.x) o[j] = w[j];
 }
 __global__ void __launch_bounds__(256) embedding_scatter_add_kernel(float* __restrict__ dW, const float* __restrict__ dout,
-                                                                    const float* __restrict__ idx, long long n, int D, int V) {
+                                                                    const float* __restrict__ idx, long long n, int D, int V, float alpha) {
   const long long row = blockIdx.x;
   int t = (int)idx[row];
   if (t < 0 || t >= V) return;
   float* w = dW + (long long)t * D;
   const float* g = dout + row * D;
-  for (int j = threadIdx.x; j < D; j += blockDim.x) atomicAdd(w + j, g[j]);
+  for (int j = threadIdx.x; j < D; j += blockDim.x) atomicAdd(w + j, alpha * g[j]);
 }
 
 // ---- cross-entropy ------------------------------------------------------------------------------
@@ -1023,8 +1023,14 @@ extern "C" int gt_embedding(gt_ctx* ctx, float* out, const float* W, const float
 }
 
 extern "C" int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V) {
+  return gt_embedding_backward_scaled(ctx, dW, dout, idx, n, D, V, 1.0f);
+}
+
+// dW[idx[r], :] += alpha * dout[r, :]: the rows of several ranks, gathered, are added with alpha = 1 / world size.
+extern "C" int gt_embedding_backward_scaled(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V,
+                                            float alpha) {
   if (!ctx || !dW || !dout || !idx || n <= 0 || D <= 0 || V <= 0 || n > 0x7fffffff || D > 0x7fffffff || V > 0x7fffffff) return GT_ERR_INVALID_ARG;
-  embedding_scatter_add_kernel<<<(unsigned)n, 256, 0, ctx->stream>>>(dW, dout, idx, n, (int)D, (int)V);
+  embedding_scatter_add_kernel<<<(unsigned)n, 256, 0, ctx->stream>>>(dW, dout, idx, n, (int)D, (int)V, alpha);
   GT_LAUNCH_CHECK(ctx, 1);
 }
 

@@ -32,6 +32,10 @@ class Backend:
     def broadcast(self, ptr: int, numel: int, src: int) -> None:
         raise NotImplementedError
 
+    def allgather_async(self, dst_ptr: int, src_ptr: int, numel: int) -> None:
+        """dst (world_size x numel floats) = every rank's numel floats at src, in rank order."""
+        raise NotImplementedError
+
     def wait(self, host_sync: bool = False) -> None:
         raise NotImplementedError
 
@@ -52,6 +56,10 @@ class NcclBackend(Backend):
     def broadcast(self, ptr: int, numel: int, src: int) -> None:
         lib = self._lib.load_library()
         self._lib.check(lib.gt_dist_broadcast(self._lib.context(), c_void_p(ptr), numel, src), "gt_dist_broadcast")
+
+    def allgather_async(self, dst_ptr: int, src_ptr: int, numel: int) -> None:
+        lib = self._lib.load_library()
+        self._lib.check(lib.gt_dist_allgather(self._lib.context(), c_void_p(dst_ptr), c_void_p(src_ptr), numel), "gt_dist_allgather")
 
     def wait(self, host_sync: bool = False) -> None:
         lib = self._lib.load_library()

@@ -32,6 +32,7 @@ from . import env as dist_env
 
 F32 = 4
 ARENA_ALIGN_ELEMS = 64          # 256-byte alignment of every gradient inside the arena
+SPARSE_MIN_BYTES = 32 << 20     # embedding tables smaller than this are not worth a separate exchange of rows
 
 
 def bucketize(nbytes_list: list[int], bucket_max_bytes: int) -> list[list[int]]:
@@ -83,6 +84,19 @@ class DeviceMemoryOps:
 
         return Tensor._from_ptr(arena.ptr + offset_elems * F32, tuple(shape), owns_memory=False, base=arena._st)
 
+    def alloc(self, numel: int):
+        from ..tensor import empty_tensor
+
+        return empty_tensor((numel,))
+
+    def scatter_rows(self, dw_ptr: int, rows_ptr: int, idx_ptr: int, n: int, d: int, v: int, alpha: float) -> None:
+        from ctypes import c_void_p
+
+        from .. import _lib
+
+        _lib.check(_lib.load_library().gt_embedding_backward_scaled(_lib.context(), c_void_p(dw_ptr), c_void_p(rows_ptr), c_void_p(idx_ptr),
+                                                                  n, d, v, float(alpha)), "gt_embedding_backward_scaled")
+
 
 class GradPlan:
     """Arena, views and buckets for one parameter list, plus the per-step readiness counters."""
@@ -117,6 +131,12 @@ class GradPlan:
         self.launch_order: list[int] = []
         self._consumers: dict[int, int] = {}
         self._bucket_left: list[int] = []
+        # Embedding tables whose gradient also has a dense part (the tied LM head): in an early-sending backward the
+        # rows that the embedding backward would scatter into the table's gradient, the last node of the graph, are
+        # kept aside instead, so that the table's bucket is final, and goes out, right after the dense part; finish()
+        # gathers every rank's rows and adds them (divided by the world size) to the reduced gradient.
+        self._defer: set[int] = set()                  # parameter indices whose embedding rows are kept aside in this backward
+        self.deferred: list[tuple] = []                # (parameter index, indices tensor, rows tensor, n, D, V)
 
     def intact(self) -> bool:
         """True while every parameter's grad is still the arena view this plan installed."""
@@ -144,6 +164,18 @@ class GradPlan:
         self.armed = False
         if not self.active:
             return
+        self._defer = set()
+        self.deferred = []
+        if os.environ.get("GRADTUITY_SPARSE_EMBED_SYNC", "1") != "0":
+            for node in topo:
+                w = getattr(node, "_embedding_of", None)
+                i = self.index.get(id(w)) if w is not None else None
+                # worth it for a table of at least 32 MB that has another (dense) consumer in the graph, when the rows of
+                # all ranks together are less data than the table (8192 tokens x 768 of a 50257 x 768 table: up to 6 ranks)
+                if (i is not None and cons.get(i, 0) >= 2 and i not in self._defer and self.params[i].numel * F32 >= SPARSE_MIN_BYTES
+                        and dist_env.get_world_size() * node.numel <= self.params[i].numel):
+                    self._defer.add(i)
+                    cons[i] -= 1
         self._consumers = cons
         self._bucket_left = [sum(1 for i in idxs if i in cons) for idxs in self.buckets]
         self._in_graph = [any(i in cons for i in idxs) for idxs in self.buckets]
@@ -157,7 +189,7 @@ class GradPlan:
             if i is None:
                 continue
             left = self._consumers.get(i)
-            if left is None:
+            if left is None or left <= 0:         # <= 0: the node whose rows were kept aside reports after the bucket went out
                 continue
             left -= 1
             self._consumers[i] = left
@@ -170,6 +202,16 @@ class GradPlan:
 
     def end(self) -> None:
         pass
+
+    def take_embedding_rows(self, w, idx, rows, n: int, d: int, v: int) -> bool:
+        """Called by the embedding backward: True if the plan keeps the rows (the caller then leaves w.grad alone)."""
+        if not self.active:
+            return False
+        i = self.index.get(id(w))
+        if i is None or i not in self._defer:
+            return False
+        self.deferred.append((i, idx, rows, n, d, v))
+        return True
 
     # ---- collectives ---------------------------------------------------------------------------
     def _launch(self, b: int) -> None:
@@ -184,7 +226,19 @@ class GradPlan:
         """Enqueue every bucket not sent during backward, then order the compute stream behind all."""
         for b in range(len(self.buckets)):
             self._launch(b)
-        comm._require().wait()
+        backend = comm._require()
+        gathered = []
+        for (i, idx, rows, n, d, v) in self.deferred:
+            world = backend.world_size
+            all_idx, all_rows = self.mem.alloc(world * n), self.mem.alloc(world * n * d)
+            backend.allgather_async(all_idx.ptr, idx.ptr, n)
+            backend.allgather_async(all_rows.ptr, rows.ptr, n * d)
+            gathered.append((i, all_idx, all_rows, world * n, d, v, 1.0 / world))
+        backend.wait()
+        for (i, all_idx, all_rows, n_all, d, v, alpha) in gathered:
+            self.mem.scatter_rows(self.views[i].ptr, all_rows.ptr, all_idx.ptr, n_all, d, v, alpha)
+        self.deferred = []
+        self._defer = set()
         self.active = False
         self.armed = True
         self.launched = set()

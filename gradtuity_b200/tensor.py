@@ -214,6 +214,8 @@ class Tensor:
     _pitch = None
     # (group, index) when this tensor's gradient must live in a slice of a shared buffer (see _GradGroup).
     _grad_slot = None
+    # The embedding table this tensor was gathered from (set by `embedding`).
+    _embedding_of = None
     # The bias of the Linear layer that produced this tensor, when the column sums of this tensor's finished gradient
     # are that bias's gradient (linear_add, mlp_gelu): the op that writes the last contribution may compute them.
     _grad_colsum_bias = None
@@ -1110,10 +1112,15 @@ class Tensor:
 
         def _backward(g: "Tensor") -> None:
             if w.requires_grad:
+                obs = _backward_observer
+                # a data-parallel plan may keep the rows aside and exchange them instead of reducing the whole table again
+                if obs is not None and obs.take_embedding_rows(w, idx, g, n, D, V):
+                    return
                 ensure_grad(w)
                 _call("gt_embedding_backward", _vp(w.grad.ptr), _vp(g.ptr), _vp(idx.ptr), n, D, V)
 
         out._set_graph(parents=(self,), backward_fn=_backward)
+        out._embedding_of = w
         return out
 
     def cross_entropy(self, targets: "Tensor", reduction: str = "mean") -> "Tensor":

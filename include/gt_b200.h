@@ -354,6 +354,9 @@ int gt_layernorm_backward_colsum(gt_ctx* ctx, float* dx, float* dgamma, float* d
                                  int dx_accumulate);
 int gt_embedding(gt_ctx* ctx, float* out, const float* W, const float* idx, int64_t n, int64_t D, int64_t V);
 int gt_embedding_backward(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V);
+/* The same with a factor: dW[idx[r], :] += alpha * dout[r, :] (the gathered rows of all ranks, alpha = 1 / world size). */
+int gt_embedding_backward_scaled(gt_ctx* ctx, float* dW, const float* dout, const float* idx, int64_t n, int64_t D, int64_t V,
+                                 float alpha);
 /* Rows of C logits may be padded: ld_logits / ld_dlogits are the row pitches in elements (>= C).  The tied
  * LM head writes its 50257-wide logits at a 16-byte aligned pitch so that both kernels use vector loads
  * and the GEMMs that read dlogits take the TMA path. */
@@ -409,6 +412,10 @@ int gt_dist_init(gt_ctx* ctx, int rank, int world, const char* uid128);
 int gt_dist_destroy(gt_ctx* ctx);
 int gt_dist_allreduce(gt_ctx* ctx, float* ptr, int64_t count, int average);
 int gt_dist_broadcast(gt_ctx* ctx, float* ptr, int64_t count, int root);
+/* dst (world x count floats) = the count floats at src of every rank, in rank order (ncclAllGather on the communication
+ * stream, ordered like gt_dist_allreduce; every rank passes the same count).  Used for the rows of the embedding table that
+ * a rank's batch touched, which are exchanged instead of a second all-reduce of the whole table's gradient. */
+int gt_dist_allgather(gt_ctx* ctx, float* dst, const float* src, int64_t count);
 int gt_dist_wait(gt_ctx* ctx, int host_sync);
 int gt_dist_info(gt_ctx* ctx, int* rank, int* world);
 int gt_dist_timeline(gt_ctx* ctx, float* out, int max_rows, int* n);

@@ -42,6 +42,15 @@ class HostMemoryOps:
     def copy(self, dst_ptr, src_ptr, nbytes):
         ctypes.memmove(dst_ptr, src_ptr, nbytes)
 
+    def alloc(self, numel):
+        return FakeTensor(np.zeros(numel, np.float32))
+
+    def scatter_rows(self, dw_ptr, rows_ptr, idx_ptr, n, d, v, alpha):
+        dw = as_array(dw_ptr, v * d).reshape(v, d)
+        rows = as_array(rows_ptr, n * d).reshape(n, d)
+        idx = as_array(idx_ptr, n).astype(np.int64)
+        np.add.at(dw, idx, alpha * rows)
+
     def view(self, arena, offset_elems, shape):
         n = int(np.prod(shape))
         v = FakeTensor.__new__(FakeTensor)
@@ -69,6 +78,11 @@ class RecordingBackend:
     def broadcast(self, ptr, numel, src):
         self.calls.append(("bcast", ptr, numel, src))
 
+    def allgather_async(self, dst_ptr, src_ptr, numel):
+        self.calls.append(("gather", dst_ptr, src_ptr, numel))
+        for r in range(self.world_size):                       # every "rank" holds this process's values
+            as_array(dst_ptr, self.world_size * numel)[r * numel:(r + 1) * numel] = as_array(src_ptr, numel)
+
     def wait(self, host_sync=False):
         self.waits += 1
 
@@ -94,6 +108,12 @@ class GlooBackend:
         import torch
 
         self.dist.broadcast(torch.from_numpy(as_array(ptr, numel)), src)
+
+    def allgather_async(self, dst_ptr, src_ptr, numel):
+        import torch
+
+        out = torch.from_numpy(as_array(dst_ptr, self.world_size * numel))
+        self.dist.all_gather(list(out.chunk(self.world_size)), torch.from_numpy(as_array(src_ptr, numel).copy()))
 
     def wait(self, host_sync=False):
         pass

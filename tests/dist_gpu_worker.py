@@ -46,6 +46,7 @@ def main():
         dist.barrier()
     elif mode == "sync_grads":
         os.environ["GRADTUITY_BUCKET_MB"] = "0.05"                 # several buckets even for the tiny model
+        ddp.SPARSE_MIN_BYTES = 1024                                 # the tied 257 x 64 table takes the row-exchange path
         model = tiny(seed=3)
         ref = tiny(seed=3)                                          # local copy used to compute the peer's gradient
         params = model.parameters()
@@ -61,12 +62,14 @@ def main():
             loss.backward()
             plan = next(iter(ddp._plans.values())) if ddp._plans else None
             sent_early = len(plan.launch_order) if plan is not None else 0
+            kept_aside = len(plan.deferred) if plan is not None else 0
             dist.sync_grads(params)
             _lib.device_status()
             for p, a, b in zip(params, g_mine, g_peer):
                 np.testing.assert_allclose(p.grad.numpy(), (a + b) / 2, rtol=1e-5, atol=1e-7)
             if step > 0:
                 assert sent_early >= 2, f"step {step}: only {sent_early} buckets went out during backward"
+                assert kept_aside == 1, f"step {step}: the embedding rows of the tied table were not kept aside ({kept_aside})"
         dist.barrier()
     elif mode == "init_sync":
         model = tiny(seed=3 + 10 * rank)                           # rank 1 starts from different weights

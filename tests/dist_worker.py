@@ -97,6 +97,55 @@ def main():
             np.testing.assert_allclose(p.grad.array, want, rtol=1e-5, atol=1e-6)
         dist.destroy_process_group()
         return
+    if mode == "embedding":
+        # A tied table: dense gradient reduced early, embedding rows gathered from both ranks at sync time.
+        import torch.distributed as dist
+        from gradtuity_b200.dist import comm, ddp
+        from tests._dist_host import FakeTensor, GlooBackend, HostMemoryOps
+
+        dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{os.environ['MASTER_PORT']}", rank=rank, world_size=world)
+        comm.set_backend(GlooBackend())
+        ddp._mem_ops = HostMemoryOps()
+        ddp.SPARSE_MIN_BYTES = 64
+        V, D, n = 9, 4, 6
+        params = [FakeTensor(np.zeros((V, D)), requires_grad=True), FakeTensor(np.zeros(8), requires_grad=True)]
+        os.environ["GRADTUITY_BUCKET_MB"] = str(64 / (1024 * 1024))
+        ddp.sync_grads(params)
+        plan = next(iter(ddp._plans.values()))
+        for p in params:
+            p.grad.array[...] = 0
+
+        def data(r):
+            g = np.random.default_rng(50 + r)
+            return (g.standard_normal((V, D)).astype(np.float32), g.integers(0, V, n).astype(np.float32),
+                    g.standard_normal((n, D)).astype(np.float32), g.standard_normal(8).astype(np.float32))
+
+        dense, idx, rows, vec = data(rank)
+        table = params[0]
+        def node(*parents):
+            t = FakeTensor(np.zeros(1)); t._parents = parents; return t
+        emb, head, other = node(table), node(table), node(params[1])
+        emb._embedding_of = table
+        plan.begin([table, emb, params[1], other, head])
+        table.grad.array[...] += dense
+        plan.node_done(head._parents)
+        params[1].grad.array[...] += vec
+        plan.node_done(other._parents)
+        kept_idx, kept_rows = FakeTensor(idx), FakeTensor(rows)
+        assert plan.take_embedding_rows(table, kept_idx, kept_rows, n, D, V)
+        plan.node_done(emb._parents)
+        plan.end()
+        ddp.sync_grads(params)
+        want = np.zeros((V, D), np.float64)
+        for r in range(world):
+            d_r, i_r, r_r, _ = data(r)
+            full = d_r.astype(np.float64).copy()
+            np.add.at(full, i_r.astype(int), r_r)
+            want += full / world
+        np.testing.assert_allclose(table.grad.array, want, rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(params[1].grad.array, sum(data(r)[3] for r in range(world)) / world, rtol=1e-6, atol=1e-7)
+        dist.destroy_process_group()
+        return
     raise SystemExit(f"unknown mode {mode}")
 
 

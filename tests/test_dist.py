@@ -125,6 +125,48 @@ def test_backward_observer_sends_buckets_as_soon_as_their_last_consumer_ran(monk
     assert next(iter(ddp._plans.values())) is not plan
 
 
+def test_embedding_rows_of_a_tied_table_are_exchanged_instead_of_a_late_reduce(monkeypatch):
+    """A large table with a dense consumer (the tied LM head) and an embedding consumer: in an early-sending backward the
+    table's bucket goes out as soon as the dense consumer has run, the embedding backward hands its rows to the plan, and
+    sync_grads gathers the rows of all ranks and adds them divided by the world size."""
+    monkeypatch.setattr(ddp, "SPARSE_MIN_BYTES", 64)
+    V, D, n = 6, 4, 5
+    params, be = _plan(monkeypatch, [(V, D), (8,)], 40)
+    table = params[0]
+    ddp.sync_grads(params)
+    plan = next(iter(ddp._plans.values()))
+    be.calls.clear()
+    for p in params:
+        p.grad.array[...] = 0
+
+    def node(*parents):
+        t = FakeTensor(np.zeros(1)); t._parents = parents; return t
+    emb, head, other = node(table), node(table), node(params[1])
+    emb._embedding_of = table
+    topo = [table, emb, params[1], other, head]
+    plan.begin(topo)
+    assert plan._defer == {0}
+    table.grad.array[...] += 1.0                    # the dense consumer (runs first in the reverse walk)
+    plan.node_done(head._parents)
+    assert [c[0] for c in be.calls] == [plan.ranges[0][0]]          # the table's bucket is out although the embedding has not run
+    plan.node_done(other._parents)
+    idx = FakeTensor(np.array([0, 2, 2, 5, 1], np.float32))
+    rows = FakeTensor(np.arange(n * D, dtype=np.float32).reshape(n, D))
+    assert plan.take_embedding_rows(table, idx, rows, n, D, V) is True
+    plan.node_done(emb._parents)                    # must not count the table a second time
+    plan.end()
+    ddp.sync_grads(params)
+    gathers = [c for c in be.calls if c[0] == "gather"]
+    assert [c[3] for c in gathers] == [n, n * D]
+    want = np.full((V, D), 10.0, np.float32)        # the recording all-reduce multiplied the dense part by 10
+    np.add.at(want, idx.array.astype(int), rows.array)             # world 2, both "ranks" hold the same rows: 2 * rows / 2
+    np.testing.assert_allclose(table.grad.array, want)
+    # a backward that does not send early keeps the rows local: the plan refuses them
+    plan.armed = False
+    plan.begin(topo)
+    assert plan.take_embedding_rows(table, idx, rows, n, D, V) is False
+
+
 def test_only_the_first_backward_after_a_sync_sends_buckets(monkeypatch):
     """backward(); backward(); sync_grads(): the second backward waits for the first one's collectives,
     sends nothing, and sync_grads reduces every bucket again; inside no_sync() nothing is sent at all."""
@@ -166,6 +208,11 @@ def test_only_the_first_backward_after_a_sync_sends_buckets(monkeypatch):
 
 def test_two_ranks_accumulate_two_backwards_then_sync_over_gloo():
     r = _launch("accumulate")
+    assert r.returncode == 0, r.stderr[-3000:]
+
+
+def test_two_ranks_exchange_embedding_rows_over_gloo():
+    r = _launch("embedding")
     assert r.returncode == 0, r.stderr[-3000:]
 
 
