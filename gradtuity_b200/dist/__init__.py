@@ -29,7 +29,7 @@ def barrier() -> None:
     comm.barrier()
 
 
-def sync_grads(params: list, bucket_mb: float = 25) -> None:
+def sync_grads(params: list, bucket_mb: float = ddp.DEFAULT_BUCKET_MB) -> None:
     ddp.sync_grads(params, bucket_mb=bucket_mb)
 
 

@@ -47,6 +47,7 @@ def main():
     elif mode == "sync_grads":
         os.environ["GRADTUITY_BUCKET_MB"] = "0.05"                 # several buckets even for the tiny model
         ddp.SPARSE_MIN_BYTES = 1024                                 # the tied 257 x 64 table takes the row-exchange path
+        os.environ["GRADTUITY_SPARSE_EMBED_SYNC"] = "1"
         model = tiny(seed=3)
         ref = tiny(seed=3)                                          # local copy used to compute the peer's gradient
         params = model.parameters()

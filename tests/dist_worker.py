@@ -107,6 +107,7 @@ def main():
         comm.set_backend(GlooBackend())
         ddp._mem_ops = HostMemoryOps()
         ddp.SPARSE_MIN_BYTES = 64
+        os.environ["GRADTUITY_SPARSE_EMBED_SYNC"] = "1"
         V, D, n = 9, 4, 6
         params = [FakeTensor(np.zeros((V, D)), requires_grad=True), FakeTensor(np.zeros(8), requires_grad=True)]
         os.environ["GRADTUITY_BUCKET_MB"] = str(64 / (1024 * 1024))

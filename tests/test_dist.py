@@ -130,6 +130,7 @@ def test_embedding_rows_of_a_tied_table_are_exchanged_instead_of_a_late_reduce(m
     table's bucket goes out as soon as the dense consumer has run, the embedding backward hands its rows to the plan, and
     sync_grads gathers the rows of all ranks and adds them divided by the world size."""
     monkeypatch.setattr(ddp, "SPARSE_MIN_BYTES", 64)
+    monkeypatch.setenv("GRADTUITY_SPARSE_EMBED_SYNC", "1")
     V, D, n = 6, 4, 5
     params, be = _plan(monkeypatch, [(V, D), (8,)], 40)
     table = params[0]
