@@ -443,7 +443,8 @@ def run_train(args, world: int, rank: int, barrier_max) -> dict:
             "gpu_launches_per_step": int(launches // steps), "loss_first": round(losses[0], 4), "loss_last": round(losses[-1], 4),
             "config": {"workload": "GPT-2-small train step, batch 8x1024 per GPU, fp32 storage, tf32 GEMMs, AdamW, clip 1.0",
                        "parallelism": f"dp{world}" if world > 1 else "single GPU",
-                       "sync": "sync_grads: NCCL all-reduce (avg) of 25 MiB buckets on a side stream, overlapped with backward" if world > 1 else "none"}}
+                       "sync": (f"sync_grads: NCCL all-reduce (avg) of {os.environ.get('GRADTUITY_BUCKET_MB', gdist.ddp.DEFAULT_BUCKET_MB)} MB "
+                                "buckets on a side stream, overlapped with backward") if world > 1 else "none"}}
 
 
 def reference_train_fixture() -> dict | None:

@@ -65,6 +65,9 @@ SIGNATURES = {
     "gt_gemm": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
                         c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                         c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p]),
+    "gt_gemm_gelu_grad_colsum": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
+                                         c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                         c_void_p, c_void_p, c_float, c_int]),
     "gt_gemm_batched": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64,
                                 c_void_p, c_int64, c_int64, c_int64,
                                 c_void_p, c_int64, c_int64, c_int64,

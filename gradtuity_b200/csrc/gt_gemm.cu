@@ -103,6 +103,34 @@ extern "C" int gt_gemm_batched_ex(gt_ctx* ctx, int layout, int64_t M, int64_t N,
   return run(ctx, g, stream);
 }
 
+// dX of the second Linear layer of a GELU MLP together with the bias gradient of the first:
+//   C = alpha * op(A) op(B) * gelu'(pre),   colsum[n] += sum_m C[m, n]
+// The sums are taken from the output tiles while they are staged in shared memory for their TMA store, so C is
+// not read again from HBM by a column-sum kernel (gradtuity/tensor.py:954-984 runs GELU backward, and
+// gradtuity/tensor.py:1781-1904 the bias sum, as separate passes over the (M, N) tensor).  The additions into
+// colsum are atomic, in no fixed order; with GRADTUITY_GEMM_DETERMINISTIC=1 the sums come from the ordered
+// column-sum kernel after the product instead.  Runs on the context's compute stream.
+extern "C" int gt_gemm_gelu_grad_colsum(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                                        const float* A, int64_t lda, const float* B, int64_t ldb,
+                                        float* C, int64_t ldc, const float* pre, float* colsum,
+                                        float alpha, int precision) {
+  if (!ctx) return GT_ERR_INVALID_ARG;
+  if (!colsum) GT_FAIL(ctx, GT_ERR_INVALID_ARG, "gemm_gelu_grad_colsum: null column-sum pointer");
+  static const bool ordered = getenv("GRADTUITY_GEMM_DETERMINISTIC") != nullptr;
+  gt_gemm_args g;
+  g.layout = layout; g.epilogue = GT_EPI_GELU_GRAD; g.precision = precision; g.accumulate = 0; g.flags = 0;
+  g.M = M; g.N = N; g.K = K;
+  g.A = A; g.lda = lda; g.sA0 = 0; g.sA1 = 0;
+  g.B = B; g.ldb = ldb; g.sB0 = 0; g.sB1 = 0;
+  g.C = C; g.ldc = ldc; g.sC0 = 0; g.sC1 = 0;
+  g.batch0 = 1; g.batch1 = 1;
+  g.bias = nullptr; g.aux = const_cast<float*>(pre); g.alpha = alpha;
+  g.colsum = ordered ? nullptr : colsum;
+  const int rc = run(ctx, g, nullptr);
+  if (rc != GT_OK || !ordered) return rc;
+  return gt_colsum_acc(ctx, colsum, C, M, N, ldc);
+}
+
 extern "C" int gt_gemm_path(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
                             const float* A, int64_t lda, const float* B, int64_t ldb,
                             const float* C, int64_t ldc, int precision, int* path) {

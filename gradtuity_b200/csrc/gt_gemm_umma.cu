@@ -59,6 +59,7 @@ constexpr int SMEM_BUDGET = 232448 - 1024 - 512 - EPI_SCRATCH_BYTES;   // 227 KB
 struct UmmaParams {
   const float* A; long long lda, sA0, sA1;     // used only when A is copied with cp.async
   float* C; const float* bias; float* aux;
+  float* colsum;                         // GT_EPI_GELU_GRAD: column sums of the result are added here (null: not wanted)
   long long bias_stride;                 // elements between the bias rows of consecutive batch entries (0: one shared bias)
   long long ldc, sC0, sC1;
   int M, N, K;
@@ -246,6 +247,18 @@ __device__ __forceinline__ bool prefetch_c(const UmmaParams& p, bool enabled, in
   return true;
 }
 
+// Column sums of the 32 x 32 block a warp has just written into its staging tile (128-byte-swizzle order), added into
+// colsum[nb ... nb + 31]: lane c reads column c of every row (one 128-byte row per instruction: no bank conflict) and
+// the warp issues one 128-byte reduction.  Rows at or beyond M hold zeros (their operand rows are the TMA fill value).
+// This is the bias gradient of the layer whose dX the product is, taken while the tile is still on the SM.
+__device__ __forceinline__ void staged_tile_colsum(float* colsum, const uint8_t* tile, int lane, int nb, int n_end) {
+  float s = 0.0f;
+  const int g = lane >> 2, w = (lane & 3) << 2;
+#pragma unroll
+  for (int r = 0; r < 32; ++r) s += *reinterpret_cast<const float*>(tile + r * 128 + ((g ^ (r & 7)) << 4) + w);
+  if (nb + lane < n_end) atomicAdd(colsum + nb + lane, s);
+}
+
 // Epilogue of one 32 x 32 block through shared memory and a TMA store.  Each lane owns one row:
 // it applies the fused epilogue in registers, writes its 128-byte row into the staging tile in the
 // 128-byte-swizzle order, and lane 0 hands the tile to the TMA unit, which writes whole rows,
@@ -307,6 +320,7 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
   if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, add);
+  if (epi == GT_EPI_GELU_GRAD && p.colsum) staged_tile_colsum(p.colsum, tile, lane, nb, p.N);
 }
 
 // The same for a chunk that lies wholly inside N, with the epilogue kind fixed at compile time: no
@@ -356,6 +370,7 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
   if (lane == 0) tma_store_4d(map_c, tile_u32, nb, row0, i0, i1, add);
+  if (EPI == GT_EPI_GELU_GRAD && p.colsum) staged_tile_colsum(p.colsum, tile, lane, nb, p.N);
 }
 
 __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
@@ -1637,7 +1652,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
 
   UmmaParams p;
   p.A = g.A; p.lda = g.lda; p.sA0 = g.sA0; p.sA1 = g.sA1;
-  p.C = g.C; p.bias = g.bias; p.aux = g.aux;
+  p.C = g.C; p.bias = g.bias; p.aux = g.aux; p.colsum = g.colsum;
   p.bias_stride = (g.flags & GT_GEMM_BIAS_PER_BATCH) ? g.N : 0;
   p.ldc = g.ldc; p.sC0 = g.sC0; p.sC1 = g.sC1;
   p.M = (int)g.M; p.N = (int)g.N; p.K = (int)g.K;
@@ -1732,6 +1747,9 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
              (!g.aux || ((uintptr_t)g.aux & 15) == 0) && (!g.bias || ((uintptr_t)g.bias & 15) == 0)) ? 1 : 0;   // the TMA epilogue uses float4 on aux and bias
   if (!p.c_tma && (g.epilogue == GT_EPI_BIAS_ADD || g.epilogue == GT_EPI_GELU_GRAD))
     GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm: the aux-reading epilogues need a C that TMA can describe (16-byte aligned, ldc a multiple of 4)");
+  // the column sums are taken from the staged output tiles: every element of the result must pass through one exactly once
+  if (g.colsum && (g.epilogue != GT_EPI_GELU_GRAD || nbatch != 1 || ksplit != 1 || g.accumulate))
+    GT_FAIL(ctx, GT_ERR_UNSUPPORTED, "gemm: column sums come with the gelu' epilogue of a single, non-accumulating product only");
   if (p.c_tma) {
     OperandView vc = {g.C, g.M, g.N, g.ldc, g.sC0, g.sC1};
     if ((rc = encode_map(ctx, &maps[4], vc, 32, 32, b0, b1, false, /*plain_f32=*/true)) != GT_OK) return rc;

@@ -127,6 +127,7 @@ struct gt_gemm_args {
   const float* bias;
   float* aux;
   float alpha;
+  float* colsum = nullptr;   // GT_EPI_GELU_GRAD only: length N, receives += the column sums of the result
 };
 
 // The context's shared scratch (the workspace and the last-wave flags behind d_status) serves one launch at a

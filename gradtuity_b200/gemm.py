@@ -40,6 +40,19 @@ def gemm(layout: int, M: int, N: int, K: int, a_ptr: int, lda: int, b_ptr: int, 
                "gt_gemm")
 
 
+def gemm_gelu_grad_colsum(layout: int, M: int, N: int, K: int, a_ptr: int, lda: int, b_ptr: int, ldb: int,
+                          c_ptr: int, ldc: int, pre_ptr: int, colsum_ptr: int, *, alpha: float = 1.0,
+                          precision: int | None = None) -> None:
+    """C = alpha * op(A) op(B) * gelu'(pre) and colsum[n] += sum_m C[m, n] in one launch: dX of the second layer
+    of a GELU MLP with the bias gradient of the first taken from the output tiles on their way out."""
+    lib = _lib.load_library()
+    if precision is None:
+        precision = default_precision()
+    _lib.check(lib.gt_gemm_gelu_grad_colsum(_lib.context(), layout, M, N, K, _p(a_ptr), lda, _p(b_ptr), ldb, _p(c_ptr), ldc,
+                                            _p(pre_ptr), _p(colsum_ptr), alpha, precision),
+               "gt_gemm_gelu_grad_colsum")
+
+
 def gemm_batched(layout: int, M: int, N: int, K: int,
                  a_ptr: int, lda: int, sa0: int, sa1: int,
                  b_ptr: int, ldb: int, sb0: int, sb1: int,

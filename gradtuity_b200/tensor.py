@@ -779,9 +779,15 @@ class Tensor:
             if x.requires_grad or w1.requires_grad or b1.requires_grad:
                 with temp_storage(M * I * F32) as dpre:
                     # d(pre-activation) = (dY @ W2^T) * gelu'(pre), the product in the GEMM's epilogue
-                    _gemm.gemm(LAYOUT_NT, M, I, N, g.ptr, N, w2.ptr, N, dpre.ptr, I, aux_ptr=pre.ptr, epilogue=EPI_GELU_GRAD)
+                    # with the first layer's bias gradient (the column sums of dpre) taken from the output tiles
+                    fused_db1 = b1.requires_grad and os.environ.get("GRADTUITY_NO_GEMM_COLSUM") is None
+                    if fused_db1:
+                        ensure_grad(b1)
+                        _gemm.gemm_gelu_grad_colsum(LAYOUT_NT, M, I, N, g.ptr, N, w2.ptr, N, dpre.ptr, I, pre.ptr, b1.grad.ptr)
+                    else:
+                        _gemm.gemm(LAYOUT_NT, M, I, N, g.ptr, N, w2.ptr, N, dpre.ptr, I, aux_ptr=pre.ptr, epilogue=EPI_GELU_GRAD)
                     pre.free()
-                    self._linear_backward(x, w1, b1, dpre.ptr, M, K, I)
+                    self._linear_backward(x, w1, b1, dpre.ptr, M, K, I, bias_done=fused_db1)
             else:
                 pre.free()
             _call("gt_join_beside")

@@ -185,6 +185,20 @@ int gt_gemm_batched_ex(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
                        const float* bias, float* aux, float alpha, int accumulate,
                        int epilogue, int precision, int flags, void* stream);
 
+/* gt_gemm with GT_EPI_GELU_GRAD that also produces the bias gradient of the layer whose pre-activation `pre` is:
+ *   C = alpha * op(A) op(B) * gelu'(pre[m, n]),   colsum[n] += sum over m of C[m, n]
+ * One launch stands where the reference runs the dX product, the GELU backward (gradtuity/tensor.py:954-984) and the
+ * bias-gradient reduction of the first Linear layer (gradtuity/tensor.py:1781-1904) as separate passes: the sums are
+ * taken from the output tiles while they are still in shared memory.  pre has C's shape and leading dimension; C and
+ * pre must be 16-byte aligned with ldc a multiple of 4 and the problem must take the tensor-core path (else
+ * GT_ERR_UNSUPPORTED).  The additions into colsum are atomic (run-to-run differences in its last bits);
+ * GRADTUITY_GEMM_DETERMINISTIC=1 takes the sums with the ordered column-sum kernel after the product instead.
+ * Runs on the context's compute stream.                                                                        */
+int gt_gemm_gelu_grad_colsum(gt_ctx* ctx, int layout, int64_t M, int64_t N, int64_t K,
+                             const float* A, int64_t lda, const float* B, int64_t ldb,
+                             float* C, int64_t ldc, const float* pre, float* colsum,
+                             float alpha, int precision);
+
 /* 3xTF32 GEMM for callers that must not cause a device allocation (no counterpart in the
  * reference, which allocates per tensor).  Same result as gt_gemm(..., GT_PREC_TF32X3) for a
  * single, non-batched problem without an aux output, but the hi/lo operand copies live in a

@@ -233,6 +233,35 @@ def test_aux_reading_epilogues(gt, layout, M, N, K, kind):
     assert np.array_equal(dx.read((M, N)), aux)                     # aux is read, never written
 
 
+@pytest.mark.parametrize("layout,M,N,K", [("NN", 300, 200, 96), ("NT", 8192, 3072, 768), ("TN", 260, 132, 64), ("NT", 2560, 2048, 4128),
+                                          ("NN", 8192, 768, 768), ("NT", 1000, 3072, 768)])
+def test_gelu_grad_product_with_column_sums(gt, layout, M, N, K):
+    """gt_gemm_gelu_grad_colsum: the same C as the GELU_GRAD epilogue, bit for bit where no K share is involved,
+    and colsum += the column sums of C (the first layer's bias gradient), taken from the staged output tiles.
+    Shapes with partial chunks and row blocks, the GPT-2 MLP shape, and shapes whose last wave is cut along K
+    (every share's partial sum passes through a tile: the sums must still add up)."""
+    from gradtuity_b200 import _lib, gemm as G
+
+    a, b, rng = U.make_operands(layout, M, N, K, seed=M + N + 1)
+    pre = rng.standard_normal((M, N)).astype(np.float32)
+    start = rng.standard_normal(N).astype(np.float32)
+    da, db, dp = U.DeviceBuffer(a), U.DeviceBuffer(b), U.DeviceBuffer(pre)
+    dc = U.DeviceBuffer(np.full((M, N), np.nan, np.float32))
+    guard = np.concatenate([start, np.full(40, 7.0, np.float32)])           # nothing may land beyond column N
+    ds = U.DeviceBuffer(guard)
+    G.gemm_gelu_grad_colsum(U.LAYOUTS[layout], M, N, K, da.ptr, a.shape[1], db.ptr, b.shape[1], dc.ptr, N, dp.ptr, ds.ptr)
+    _lib.device_status()
+    out = dc.read((M, N))
+    ref = O.gemm(a, b, layout) * O.gelu_tanh_grad(pre.astype(np.float64))
+    assert O.rel_frobenius(out, ref) <= U.TOL["tf32"]
+    sums = ds.read((N + 40,))
+    assert np.array_equal(sums[N:], guard[N:])
+    want = start.astype(np.float64) + out.astype(np.float64).sum(axis=0)   # sums of what the kernel itself wrote
+    scale = np.abs(out.astype(np.float64)).sum(axis=0) + np.abs(start)
+    assert np.all(np.abs(sums[:N] - want) <= 2e-5 * scale + 1e-6)
+    assert np.array_equal(dp.read((M, N)), pre)
+
+
 def test_aux_reading_epilogue_needs_aux_and_tensor_core_path(gt):
     from gradtuity_b200 import _lib, gemm as G
 
