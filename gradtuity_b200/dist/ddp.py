@@ -37,17 +37,29 @@ ARENA_ALIGN_ELEMS = 64          # 256-byte alignment of every gradient inside th
 # GPT-2-small step has 16 all-reduces of 0.1-0.2 ms at 25 MB and 6 at 100 MB, and loses 0.35 ms less to them (2 GPUs).
 DEFAULT_BUCKET_MB = 100
 SPARSE_MIN_BYTES = 32 << 20     # embedding tables smaller than this are not worth a separate exchange of rows
+# GRADTUITY_BUCKET_RAMP=3: the buckets at the front of the parameter list (the last ones backward completes) hold 1/8, 1/4,
+# 1/2 of the bucket size, so that less is left to reduce when backward ends.  Measured on 2 GPUs: the wait behind the last
+# node drops from 0.65 to 0.49 ms, the step time by no more than the run-to-run spread (17.6-17.7 ms either way): off.
+BUCKET_RAMP = 0
 
 
-def bucketize(nbytes_list: list[int], bucket_max_bytes: int) -> list[list[int]]:
+def bucketize(nbytes_list: list[int], bucket_max_bytes: int, ramp: int = 0) -> list[list[int]]:
     """Indices of consecutive entries per bucket: a bucket is closed when the next entry would
-    push it past bucket_max_bytes and it is not empty (gradtuity/dist/ddp.py:59-71)."""
+    push it past bucket_max_bytes and it is not empty (gradtuity/dist/ddp.py:59-71).
+    ramp > 0 (not in the reference): the first buckets of the list are smaller, bucket_max_bytes / 2^ramp, then twice
+    that, and so on up to bucket_max_bytes (a bucket that is one oversized entry does not count).  The front of the
+    parameter list is what backward finishes last, so these are the buckets whose all-reduce has little or nothing
+    left to hide behind: the less they hold, the shorter the wait at the end of backward."""
     buckets: list[list[int]] = []
     cur: list[int] = []
     cur_bytes = 0
+    level = max(int(ramp), 0)
     for i, n in enumerate(nbytes_list):
-        if cur_bytes + n > bucket_max_bytes and cur:
+        limit = max(bucket_max_bytes >> level, 1)
+        if cur_bytes + n > limit and cur:
             buckets.append(cur)
+            if cur_bytes <= limit and level > 0:
+                level -= 1
             cur, cur_bytes = [], 0
         cur.append(i)
         cur_bytes += n
@@ -119,7 +131,7 @@ class GradPlan:
             self.mem.copy(self.arena.ptr + off * F32, p.grad.ptr, p.numel * F32)
             p.grad = self.mem.view(self.arena, off, p.shape)
         self.views = [p.grad for p in self.params]
-        self.buckets = bucketize([n * F32 for n in numels], bucket_max_bytes)
+        self.buckets = bucketize([n * F32 for n in numels], bucket_max_bytes, int(os.environ.get("GRADTUITY_BUCKET_RAMP", BUCKET_RAMP)))
         self.bucket_of = {}
         self.ranges = []                                   # (ptr, numel) per bucket, padding included
         for b, idxs in enumerate(self.buckets):

@@ -39,6 +39,13 @@ def test_env_parsing(monkeypatch):
     assert dist_env.get_env_ranks() == (5, 6, 2, "127.0.0.1", "1234")
 
 
+@pytest.fixture(autouse=True)
+def _reference_bucket_rule(monkeypatch):
+    """The tests below pin bucket layouts that follow the reference's rule; the front-of-list ramp has its own test."""
+    monkeypatch.setattr(ddp, "BUCKET_RAMP", 0)
+    monkeypatch.setenv("GRADTUITY_BUCKET_RAMP", "0")          # inherited by the spawned workers
+
+
 def test_world_size_one_is_a_no_op(monkeypatch):
     monkeypatch.setenv("RANK", "0"); monkeypatch.setenv("WORLD_SIZE", "1"); monkeypatch.setenv("LOCAL_RANK", "0")
     p = FakeTensor(np.ones(4), requires_grad=True)
@@ -63,6 +70,26 @@ def test_bucket_rule_matches_the_reference():
     assert sum(sizes) == 124439808
     b = ddp.bucketize([4 * s for s in sizes], 25 * 1024 * 1024)
     assert b[0] == [0] and 15 <= len(b) <= 25
+
+
+def test_bucket_ramp_makes_the_front_of_the_list_small():
+    """ramp = 3: the first regular buckets hold at most 1/8, 1/4, 1/2 of the limit (they are what backward completes
+    last, so their all-reduce hides behind nothing); an oversized single entry does not use up a step of the ramp;
+    every index appears once, in order, whatever the ramp."""
+    sizes = [50257 * 768, 1024 * 768]
+    for _ in range(12):
+        sizes += [768, 768] + [768 * 768] * 4 + [768] * 4 + [768, 768, 768 * 3072, 3072, 3072 * 768, 768]
+    sizes += [768, 768]
+    nbytes = [4 * s for s in sizes]
+    limit = 100 << 20
+    b = ddp.bucketize(nbytes, limit, 3)
+    assert [i for idx in b for i in idx] == list(range(len(sizes)))
+    held = [sum(nbytes[i] for i in idx) for idx in b]
+    assert b[0] == [0] and held[0] > limit
+    assert held[1] <= limit // 8 and held[2] <= limit // 4 and held[3] <= limit // 2
+    assert all(h <= limit for h in held[1:]) and max(held[4:]) > limit // 2
+    assert ddp.bucketize([10, 10, 30, 5, 5], 20, 0) == ddp.bucketize([10, 10, 30, 5, 5], 20)
+    assert ddp.bucketize([4, 4, 4, 4, 4, 4, 4, 4], 16, 2) == [[0], [1, 2], [3, 4, 5, 6], [7]]
 
 
 def test_arena_offsets_are_aligned():
