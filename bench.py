@@ -477,7 +477,7 @@ def run_micro(args) -> dict:
     m, n, k = args.shape
     lay = {"NN": 0, "NT": 1, "TN": 2}[args.layout]
     prec = {"tf32": 0, "3xtf32": 1, "fp32": 2}[args.precision]
-    epi = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu": 3, "causal": 4}[args.epilogue]
+    epi = {"none": 0, "bias": 1, "bias_relu": 2, "bias_gelu": 3, "causal": 4, "bias_add": 5, "gelu_grad": 6, "gelu_grad_colsum": 6}[args.epilogue]
     rng = np.random.default_rng(1)
     ashape = (k, m) if lay == 2 else (m, k)
     bshape = (n, k) if lay == 1 else (k, n)
@@ -485,10 +485,15 @@ def run_micro(args) -> dict:
     tb = Tensor.from_numpy(rng.standard_normal(bshape, dtype=np.float32) / np.float32(np.sqrt(k)))
     tbias = Tensor.from_numpy(rng.standard_normal((n,), dtype=np.float32))
     tc = Tensor._zeros((m, n))
+    taux = Tensor.from_numpy(rng.standard_normal((m, n), dtype=np.float32)) if epi >= 5 else None    # residual / pre-activation
+    tsum = Tensor._zeros((n,))
 
     def step():
-        G.gemm(lay, m, n, k, ta.ptr, ashape[1], tb.ptr, bshape[1], tc.ptr, n, bias_ptr=tbias.ptr if 1 <= epi <= 3 else 0,
-               accumulate=args.accumulate, epilogue=epi, precision=prec)
+        if args.epilogue == "gelu_grad_colsum":
+            G.gemm_gelu_grad_colsum(lay, m, n, k, ta.ptr, ashape[1], tb.ptr, bshape[1], tc.ptr, n, taux.ptr, tsum.ptr, precision=prec)
+            return
+        G.gemm(lay, m, n, k, ta.ptr, ashape[1], tb.ptr, bshape[1], tc.ptr, n, bias_ptr=tbias.ptr if epi in (1, 2, 3, 5) else 0,
+               aux_ptr=taux.ptr if taux is not None else 0, accumulate=args.accumulate, epilogue=epi, precision=prec)
 
     for _ in range(args.warmup):
         step()
@@ -503,7 +508,7 @@ def run_micro(args) -> dict:
     _lib.device_status()
     t = ms.value / args.steps
     flops = 2.0 * m * n * k
-    nbytes = 4.0 * (m * k + k * n + m * n * (2 if args.accumulate else 1))
+    nbytes = 4.0 * (m * k + k * n + m * n * ((2 if args.accumulate else 1) + (1 if epi >= 5 else 0)))
     return {"micro": True, "shape": [m, n, k], "layout": args.layout, "precision": args.precision, "epilogue": args.epilogue,
             "accumulate": bool(args.accumulate), "ms": round(t, 5), "tflops": round(flops / t / 1e9, 2),
             "gbs": round(nbytes / t / 1e6, 1), "steps": args.steps, "warmup": args.warmup}
@@ -824,7 +829,7 @@ def main():
     ap.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"), help="kernel-only timing of one GEMM shape")
     ap.add_argument("--layout", default="NN", choices=["NN", "NT", "TN"])
     ap.add_argument("--precision", default="tf32", choices=["tf32", "3xtf32", "fp32"])
-    ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_relu", "bias_gelu", "causal"])
+    ap.add_argument("--epilogue", default="none", choices=["none", "bias", "bias_relu", "bias_gelu", "causal", "bias_add", "gelu_grad", "gelu_grad_colsum"])
     ap.add_argument("--accumulate", action="store_true")
     ap.add_argument("--sweep", action="store_true", help="kernel-only timing of the whole config-1 GEMM sweep")
     ap.add_argument("--attn", action="store_true", help="kernel-only timing of the batched attention products (GB/s)")
