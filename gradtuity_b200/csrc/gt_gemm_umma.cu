@@ -269,7 +269,7 @@ __device__ __forceinline__ void staged_tile_colsum(float* colsum, const uint8_t*
 // This is the general form: bias, aux and the output may end inside the chunk.
 __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                        int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                       uint8_t* tile, uint32_t tile_u32, int epi, bool add, bool aux_out) {
+                                                       uint8_t* tile, uint32_t tile_u32, int epi, bool add, bool aux_out, bool aux_staged) {
   const int row = row0 + lane;
   const bool has_bias = (epi >= GT_EPI_BIAS && epi <= GT_EPI_BIAS_GELU) || epi == GT_EPI_BIAS_ADD;
   const bool aux_in = epi == GT_EPI_BIAS_ADD || epi == GT_EPI_GELU_GRAD;       // aux is read, not written
@@ -291,7 +291,10 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
     }
     if (aux_in) {
       float a4[4] = {0.f, 0.f, 0.f, 0.f};
-      if (row_ok) {
+      if (aux_staged) {                             // a TMA load has put the block of aux into the tile (zeros outside the tensor)
+        const float4 a = *reinterpret_cast<const float4*>(tile + lane * 128 + ((((j >> 2) ^ (lane & 7))) << 4));
+        a4[0] = a.x; a4[1] = a.y; a4[2] = a.z; a4[3] = a.w;
+      } else if (row_ok) {
 #pragma unroll
         for (int t = 0; t < 4; ++t) if (nb + j + t < p.N) a4[t] = p.aux[row_off + nb + j + t];
       }
@@ -330,7 +333,7 @@ __device__ __forceinline__ void epilogue_chunk_tma_any(const UmmaParams& p, cons
 template <int EPI, bool AUX, bool UNIT_ALPHA>
 __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                         int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                        uint8_t* tile, uint32_t tile_u32, bool add) {
+                                                        uint8_t* tile, uint32_t tile_u32, bool add, bool aux_staged) {
   constexpr bool HAS_BIAS = (EPI >= GT_EPI_BIAS && EPI <= GT_EPI_BIAS_GELU) || EPI == GT_EPI_BIAS_ADD;
   constexpr bool AUX_IN = EPI == GT_EPI_BIAS_ADD || EPI == GT_EPI_GELU_GRAD;     // aux is read, not written
   const int row = row0 + lane;
@@ -350,7 +353,9 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
       x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
     }
     if (AUX_IN) {
-      const float4 a = row_ok ? aux4[j] : make_float4(0.f, 0.f, 0.f, 0.f);
+      // aux_staged: a TMA load has put this block of aux into the tile, in the layout the result is written back in
+      const float4 a = aux_staged ? *reinterpret_cast<const float4*>(my_row + ((j ^ sw) << 4))
+                                  : (row_ok ? aux4[j] : make_float4(0.f, 0.f, 0.f, 0.f));
       if (EPI == GT_EPI_BIAS_ADD) { x.x += a.x; x.y += a.y; x.z += a.z; x.w += a.w; }
       else { x.x *= gt_gelu_tanh_grad(a.x); x.y *= gt_gelu_tanh_grad(a.y); x.z *= gt_gelu_tanh_grad(a.z); x.w *= gt_gelu_tanh_grad(a.w); }
     } else if (AUX) { if (row_ok) aux4[j] = x; }
@@ -375,14 +380,14 @@ __device__ __forceinline__ void epilogue_chunk_tma_fast(const UmmaParams& p, con
 
 __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const float* bias, const CUtensorMap* map_c, const float* v, int lane,
                                                    int row0, int nb, int i0, int i1, long long row_off, bool row_ok,
-                                                   uint8_t* tile, uint32_t tile_u32, int epi, bool add) {
+                                                   uint8_t* tile, uint32_t tile_u32, int epi, bool add, bool aux_staged = false) {
   // aux is an OUTPUT (pre-activation) only for the kinds that produce one, and never for a K share that merely adds
   const bool aux_out = p.aux != nullptr && epi == p.epilogue && epi != GT_EPI_BIAS_ADD && epi != GT_EPI_GELU_GRAD;
   // alpha == 1 (every Linear layer): the multiply is left out of the per-element work (warp-uniform choice)
 #define GT_EPI_FAST(E, X)                                                                                                       \
   do {                                                                                                                          \
-    if (p.alpha == 1.0f) epilogue_chunk_tma_fast<E, X, true>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add);  \
-    else epilogue_chunk_tma_fast<E, X, false>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add); \
+    if (p.alpha == 1.0f) epilogue_chunk_tma_fast<E, X, true>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add, aux_staged);  \
+    else epilogue_chunk_tma_fast<E, X, false>(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, add, aux_staged); \
   } while (0)
   if (nb + 32 <= p.N) {                              // warp-uniform
     switch (epi) {
@@ -411,7 +416,7 @@ __device__ __forceinline__ void epilogue_chunk_tma(const UmmaParams& p, const fl
     }
   }
 #undef GT_EPI_FAST
-  epilogue_chunk_tma_any(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, epi, add, aux_out);
+  epilogue_chunk_tma_any(p, bias, map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, tile, tile_u32, epi, add, aux_out, aux_staged);
 }
 
 // Same epilogue for outputs whose rows are not 16-byte aligned (odd leading dimension, e.g. the
@@ -1104,7 +1109,7 @@ static_assert(PAIR_SMEM_BYTES <= 232448, "CTA-pair kernel exceeds the 227 KB of 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const __grid_constant__ CUtensorMap map_c, const UmmaParams p) {
+                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_aux, const UmmaParams p) {
   constexpr int STAGES = PAIR_STAGES;
   constexpr int TM = 256, TN = 256, HALF = 128;
   extern __shared__ uint8_t smem_raw[];
@@ -1120,6 +1125,7 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t bar_tfull = bar_empty + 8 * MAX_STAGES;
   const uint32_t bar_tempty = bar_tfull + 16;
   const uint32_t bar_drain = bar_tempty + 16;
+  const uint32_t bar_aux = smem_u32(ctrl + 384);           // one per epilogue warp: its block of aux has landed in its staging tile
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();                 // 0: leader
@@ -1133,6 +1139,7 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     for (int s = 0; s < STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(bar_tfull + 8 * a, 1); mbar_init(bar_tempty + 8 * a, 16); }   // 8 epilogue warps x 2 CTAs
     mbar_init(bar_drain, 1);
+    for (int w = 0; w < 8; ++w) mbar_init(bar_aux + 8 * w, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1257,6 +1264,8 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint8_t* epi_bytes = epi_scratch + (warp - 2) * EPI_WARP_BYTES;
     const uint32_t epi_u32 = smem_u32(epi_bytes);
     int acc = 0; uint32_t aph = 0;
+    const uint32_t my_aux_bar = bar_aux + 8 * (uint32_t)(warp - 2);
+    uint32_t aux_ph = 0;
     // Last-wave split (see gt_gemm_umma_kernel): the K shares of a last-wave tile ADD into C, so unless the call is
     // C += ..., pair i zeroes the i-th such tile first, each CTA its own 128 rows, and publishes flag 2 i + rank.
     if (p.tail_split > 1 && p.tail_zero && warp == 2) {
@@ -1318,17 +1327,36 @@ gt_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       if (!wait_x(bar_tfull + 8 * acc, aph)) break;
       tc_fence_after();
+      // The epilogues that READ aux (residual, stored pre-activation): a TMA load brings the warp's 32 x 32 block of aux
+      // into its staging tile while the accumulator columns come out of tensor memory; the lanes then read aux from the
+      // tile and write the result over it.  (Read with one global load per lane and row piece, 32 lines per
+      // instruction, these warps stalled on the loads four times as long as they issued.)
+      const bool aux_staged = unit_epi == GT_EPI_BIAS_ADD || unit_epi == GT_EPI_GELU_GRAD;
+      bool lost = false;
       if (row0 < p.M) {                       // warp-uniform: a 32-row block wholly below M has nothing to write
 #pragma unroll 1
         for (int c = eset; c < TN / 32; c += 2) {
           const int nb = n0 + c * 32;
           if (nb >= p.N) break;
+          if (aux_staged) {
+            __syncwarp();                     // every lane is done with the tile's previous contents
+            if (lane == 0) {
+              tma_store_wait_read<0>();       // and so is the store that was reading them
+              mbar_expect_tx(my_aux_bar, EPI_WARP_BYTES);
+              tma_load_4d(epi_u32, &map_aux, my_aux_bar, nb, row0, i0, i1);
+            }
+          }
           float v[32];
           tc_ld32(lane_base + (uint32_t)(acc * TN + c * 32), v);
           tc_wait_ld();
-          epilogue_chunk_tma(p, unit_bias, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, unit_epi, unit_add);
+          if (aux_staged) {
+            if (!mbar_wait(my_aux_bar, aux_ph, abort_flag, p.status)) { lost = true; break; }
+            aux_ph ^= 1u;
+          }
+          epilogue_chunk_tma(p, unit_bias, &map_c, v, lane, row0, nb, i0, i1, row_off, row_ok, epi_bytes, epi_u32, unit_epi, unit_add, aux_staged);
         }
       }
+      if (__any_sync(0xffffffffu, lost)) break;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_tempty + 8 * acc);      // this warp is done with the accumulator
@@ -1458,11 +1486,11 @@ void pair_launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* attr, int 
 }
 
 template <class Kern>
-int pair_launch(gt_ctx* ctx, Kern kern, int clusters, cudaStream_t stream, const CUtensorMap maps[5], const UmmaParams& p) {
+int pair_launch(gt_ctx* ctx, Kern kern, int clusters, cudaStream_t stream, const CUtensorMap* maps, const UmmaParams& p) {
   GT_SMEM_OPT_IN(ctx, kern, PAIR_SMEM_BYTES);
   cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
   pair_launch_config<Kern>(&cfg, attr, clusters, stream);
-  GT_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[4], p));
+  GT_CUDA_OK(ctx, cudaLaunchKernelEx(&cfg, kern, maps[0], maps[1], maps[4], maps[5], p));
   ctx->launches += 1;
   return GT_OK;
 }
@@ -1591,7 +1619,7 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
   if (a_mn) va = {g.A, g.K, g.M, g.lda, g.sA0, g.sA1}; else va = {g.A, g.M, g.K, g.lda, g.sA0, g.sA1};
   if (b_mn) vb = {g.B, g.K, g.N, g.ldb, g.sB0, g.sB1}; else vb = {g.B, g.N, g.K, g.ldb, g.sB0, g.sB1};
 
-  CUtensorMap maps[5];
+  CUtensorMap maps[6];           // A (hi, lo), B (hi, lo), C, aux
   long long b0 = g.batch0, b1 = g.batch1;
   OperandView va_lo = va, vb_lo = vb;
   if (x3) {
@@ -1755,6 +1783,13 @@ static int umma_launch_impl(gt_ctx* ctx, const gt_gemm_args& g, cudaStream_t str
     if ((rc = encode_map(ctx, &maps[4], vc, 32, 32, b0, b1, false, /*plain_f32=*/true)) != GT_OK) return rc;
   } else {
     maps[4] = maps[1];
+  }
+  // the CTA-pair kernel loads the aux its epilogue READS (residual, pre-activation) by TMA, block by block like C
+  if (pair && p.c_tma && (g.epilogue == GT_EPI_BIAS_ADD || g.epilogue == GT_EPI_GELU_GRAD)) {
+    OperandView vx = {g.aux, g.M, g.N, g.ldc, g.sC0, g.sC1};
+    if ((rc = encode_map(ctx, &maps[5], vx, 32, 32, b0, b1, false, /*plain_f32=*/true)) != GT_OK) return rc;
+  } else {
+    maps[5] = maps[4];
   }
   // Last partial wave.  A persistent CTA per SM walks the tiles round-robin, so T tiles on P SMs take
   // ceil(T / P) rounds even when the last round has few tiles (the 768-wide projections of GPT-2: 192
