@@ -631,11 +631,9 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
                                  const float* __restrict__ targets, float* __restrict__ row_loss, float* __restrict__ row_lse,
                                  float scale, int C, long long rows, int* status) {
   extern __shared__ __align__(128) uint8_t ce_smem[];
-  __shared__ float red[33];
+  __shared__ float red_m[32], red_s[32];                     // one (maximum, sum) pair per warp
   __shared__ __align__(8) unsigned long long bars[CE_ROW_CHUNKS];
   __shared__ int abort_word;
-  __shared__ float s_lse;
-  __shared__ int s_t;
   volatile int* abort_flag = &abort_word;
   float4* const row4 = reinterpret_cast<float4*>(ce_smem);
   const uint32_t row_addr = (uint32_t)__cvta_generic_to_shared(ce_smem);
@@ -663,6 +661,7 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
   uint32_t failed_parity = 0;
   for (int it = 0; ok && row < rows; row += gridDim.x, ++it) {
     const uint32_t parity = (uint32_t)(it & 1);
+    const float t_early = targets[row];                        // asked for now by every thread, needed after the reduction
     // ---- pass 1: running maximum and sum, chunk by chunk as they arrive
     float m = -INFINITY, sum = 0.0f;
     for (int c = 0; c < CE_ROW_CHUNKS; ++c) {
@@ -680,22 +679,24 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
         sum += (__expf(v.x - m) + __expf(v.y - m)) + (__expf(v.z - m) + __expf(v.w - m));
       }
     }
-    if (!__syncthreads_and(ok)) { ok = false; failed_parity = parity; break; }     // all threads leave together, or none
-    const float gm = block_max_all(m, red);
-    sum = (m == -INFINITY) ? 0.0f : sum * __expf(m - gm);
-    sum = block_sum_all(sum, red);
-    if (tid == 0) {
-      int t = (int)targets[row];
-      if (t < 0 || t >= C) { atomicExch(status, GT_ERR_INVALID_ARG); t = t < 0 ? 0 : C - 1; }
-      const float lse = gm + logf(sum);
-      row_lse[row] = lse;
-      row_loss[row] = lse - reinterpret_cast<const float*>(ce_smem)[t];
-      s_lse = lse;
-      s_t = t;
+    // One block-wide step between the passes: each warp reduces its (maximum, sum) pairs, the 32 warp results go through
+    // shared memory, and every warp reduces those again for itself, so that all threads hold the log-sum-exp after a
+    // single barrier (which is also the vote on `ok`: all threads leave together, or none).
+    {
+      const float wm = warp_max(m);
+      sum = warp_sum(m == -INFINITY ? 0.0f : sum * __expf(m - wm));
+      if ((tid & 31) == 0) { red_m[tid >> 5] = wm; red_s[tid >> 5] = sum; }
     }
-    __syncthreads();
-    const float lse = s_lse;
-    const int t = s_t;
+    if (!__syncthreads_and(ok)) { ok = false; failed_parity = parity; break; }
+    m = red_m[tid & 31];
+    const float gm = warp_max(m);
+    sum = warp_sum(m == -INFINITY ? 0.0f : red_s[tid & 31] * __expf(m - gm));
+    const float lse = gm + logf(sum);
+    int t = (int)t_early;
+    if (t < 0 || t >= C) {
+      if (tid == 0) atomicExch(status, GT_ERR_INVALID_ARG);
+      t = t < 0 ? 0 : C - 1;
+    }
     // ---- pass 2: the gradient over the row, in place; each chunk leaves as soon as the whole block has written it
     const long long next = row + gridDim.x;
     for (int c = 0; c < CE_ROW_CHUNKS; ++c) {
@@ -704,8 +705,10 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
         const float4 x = row4[u];
         float4 g;
         g.x = scale * __expf(x.x - lse); g.y = scale * __expf(x.y - lse); g.z = scale * __expf(x.z - lse); g.w = scale * __expf(x.w - lse);
-        if ((t >> 2) == u) {
+        if ((t >> 2) == u) {                                 // the one thread that holds the target's logit also writes the loss
           const int k = t & 3;
+          row_lse[row] = lse;
+          row_loss[row] = lse - (k == 0 ? x.x : k == 1 ? x.y : k == 2 ? x.z : x.w);
           if (k == 0) g.x -= scale; else if (k == 1) g.y -= scale; else if (k == 2) g.z -= scale; else g.w -= scale;
         }
         if (4 * u + 3 >= C) {
@@ -721,18 +724,18 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
         asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
                      ::"l"(dlogits + row * ld_d + (long long)u0 * 4), "r"(row_addr + (uint32_t)u0 * 16u), "r"((uint32_t)(u1 - u0) * 16u) : "memory");
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        // chunk c - 1 of the next row may come in once the store of chunk c - 1 has been read out of shared memory: it was
+        // issued a chunk ago, so the wait is short, and the next row's first chunks are on their way while this row's
+        // last ones are still being computed
+        if (c >= 1 && next < rows) {
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          request(next, c - 1);
+        }
       }
     }
-    // ---- chunk c of the next row may come in once the store of chunk c has been read out of shared memory
     if (tid == 0 && next < rows) {
-      asm volatile("cp.async.bulk.wait_group.read 7;" ::: "memory"); request(next, 0);
-      asm volatile("cp.async.bulk.wait_group.read 6;" ::: "memory"); request(next, 1);
-      asm volatile("cp.async.bulk.wait_group.read 5;" ::: "memory"); request(next, 2);
-      asm volatile("cp.async.bulk.wait_group.read 4;" ::: "memory"); request(next, 3);
-      asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); request(next, 4);
-      asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory"); request(next, 5);
-      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); request(next, 6);
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); request(next, 7);
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      request(next, CE_ROW_CHUNKS - 1);
     }
   }
   if (tid == 0) {
