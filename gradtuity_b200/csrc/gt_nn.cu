@@ -626,6 +626,9 @@ __device__ __forceinline__ bool ce_bar_wait(uint32_t bar, uint32_t parity, volat
   }
 }
 
+constexpr float CE_LOG2E = 1.4426950408889634f;
+__device__ __forceinline__ float ce_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
 __global__ void __launch_bounds__(CE_ROW_THREADS, 1)
 cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, const float* __restrict__ logits, long long ld_x,
                                  const float* __restrict__ targets, float* __restrict__ row_loss, float* __restrict__ row_lse,
@@ -663,7 +666,7 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
     const uint32_t parity = (uint32_t)(it & 1);
     const float t_early = targets[row];                        // asked for now by every thread, needed after the reduction
     // ---- pass 1: running maximum and sum, chunk by chunk as they arrive
-    float m = -INFINITY, sum = 0.0f;
+    float m = -INFINITY, sum = 0.0f, m2 = 0.0f;                // m2 = -m log2(e), set with the first maximum
     for (int c = 0; c < CE_ROW_CHUNKS; ++c) {
       if (!ce_bar_wait(bar0 + 8 * c, parity, abort_flag, status)) { ok = false; break; }     // leaves the chunk loop only
       const int u1 = min((c + 1) * q4, n4);
@@ -675,8 +678,9 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
           v.w = -INFINITY;
         }
         const float vm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-        if (vm > m) { sum *= __expf(m - vm); m = vm; }
-        sum += (__expf(v.x - m) + __expf(v.y - m)) + (__expf(v.z - m) + __expf(v.w - m));
+        if (vm > m) { sum *= __expf(m - vm); m = vm; m2 = -vm * CE_LOG2E; }
+        // e^(x - m) as 2^(x log2(e) - m log2(e)): one multiply-add and one ex2 per logit
+        sum += (ce_ex2(fmaf(v.x, CE_LOG2E, m2)) + ce_ex2(fmaf(v.y, CE_LOG2E, m2))) + (ce_ex2(fmaf(v.z, CE_LOG2E, m2)) + ce_ex2(fmaf(v.w, CE_LOG2E, m2)));
       }
     }
     // One block-wide step between the passes: each warp reduces its (maximum, sum) pairs, the 32 warp results go through
@@ -692,6 +696,7 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
     const float gm = warp_max(m);
     sum = warp_sum(m == -INFINITY ? 0.0f : red_s[tid & 31] * __expf(m - gm));
     const float lse = gm + logf(sum);
+    const float k2 = log2f(scale) - lse * CE_LOG2E;
     int t = (int)t_early;
     if (t < 0 || t >= C) {
       if (tid == 0) atomicExch(status, GT_ERR_INVALID_ARG);
@@ -704,7 +709,8 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
       for (int u = u0 + tid; u < u1; u += CE_ROW_THREADS) {
         const float4 x = row4[u];
         float4 g;
-        g.x = scale * __expf(x.x - lse); g.y = scale * __expf(x.y - lse); g.z = scale * __expf(x.z - lse); g.w = scale * __expf(x.w - lse);
+        // scale e^(x - lse) as 2^(x log2(e) + k), k = log2(scale) - lse log2(e): one multiply-add and one ex2 per logit
+        g.x = ce_ex2(fmaf(x.x, CE_LOG2E, k2)); g.y = ce_ex2(fmaf(x.y, CE_LOG2E, k2)); g.z = ce_ex2(fmaf(x.z, CE_LOG2E, k2)); g.w = ce_ex2(fmaf(x.w, CE_LOG2E, k2));
         if ((t >> 2) == u) {                                 // the one thread that holds the target's logit also writes the loss
           const int k = t & 3;
           row_lse[row] = lse;
@@ -1062,7 +1068,7 @@ extern "C" int gt_cross_entropy_fused(gt_ctx* ctx, float* loss, float* row_loss,
       C > 0x7fffffff || ld_logits < C || ld_dlogits < C) return GT_ERR_INVALID_ARG;
   const bool vec = (((uintptr_t)logits & 15) == 0) && ld_logits % 4 == 0 && (((uintptr_t)dlogits & 15) == 0) && ld_dlogits % 4 == 0;
   static const bool row_in_smem = getenv("GRADTUITY_CE_NO_ROW_IN_SMEM") == nullptr;
-  if (vec && row_in_smem && C >= 4096 && C <= CE_ROW_MAX_CLASSES) {
+  if (vec && row_in_smem && C >= 4096 && C <= CE_ROW_MAX_CLASSES && grad_scale > 0.0f) {     // the kernel folds log2(grad_scale) into an exponent
     const int bytes = (int)((C + 3) / 4 * 16);
     GT_SMEM_OPT_IN(ctx, cross_entropy_row_in_smem_kernel, CE_ROW_MAX_CLASSES * 4);      // once, for the widest row admitted
     const unsigned grid = (unsigned)(B < ctx->sm_count ? B : ctx->sm_count);
