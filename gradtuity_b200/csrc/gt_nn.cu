@@ -598,11 +598,13 @@ __global__ void __launch_bounds__(512) cross_entropy_fused_kernel(float* __restr
 }
 // The same with the row held in shared memory, for rows of up to 56 000 classes that start on 16-byte boundaries
 // (GPT-2's 50257 at a pitch of 50272): one persistent block per SM takes rows in turn; the bulk-copy engine brings a
-// row in as eight chunks (an mbarrier each, so the first pass starts on chunk 0 while chunk 7 is still in flight), the
-// second pass overwrites it in place with the gradient, and the engine writes it out chunk by chunk; a chunk of the
-// next row is requested as soon as the store of the same chunk has been read out of shared memory.  Every byte of
-// the logits crosses HBM once in each direction, whatever the L2 holds.
-constexpr int CE_ROW_CHUNKS = 8;
+// row in as a few chunks (an mbarrier each, so the first pass starts on chunk 0 while the last is still in flight),
+// the second pass overwrites it in place with the gradient, and the engine writes it out chunk by chunk; a chunk of
+// the next row is requested as soon as the store of the same chunk has been read out of shared memory, which is
+// while the following chunk's gradient is being computed.  Every byte of the logits crosses HBM once in each
+// direction, whatever the L2 holds.
+constexpr int CE_ROW_CHUNKS = 8;          // chunks a short row is cut into (the launcher picks the number)
+constexpr int CE_ROW_MAX_CHUNKS = 14;     // barriers provided
 constexpr int CE_ROW_THREADS = 1024;
 constexpr int CE_ROW_MAX_CLASSES = 56000;
 
@@ -632,20 +634,20 @@ __device__ __forceinline__ float ce_ex2(float x) { float y; asm("ex2.approx.ftz.
 __global__ void __launch_bounds__(CE_ROW_THREADS, 1)
 cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, const float* __restrict__ logits, long long ld_x,
                                  const float* __restrict__ targets, float* __restrict__ row_loss, float* __restrict__ row_lse,
-                                 float scale, int C, long long rows, int* status) {
+                                 float scale, int C, long long rows, int nchunks, int* status) {
   extern __shared__ __align__(128) uint8_t ce_smem[];
   __shared__ float red_m[32], red_s[32];                     // one (maximum, sum) pair per warp
-  __shared__ __align__(8) unsigned long long bars[CE_ROW_CHUNKS];
+  __shared__ __align__(8) unsigned long long bars[CE_ROW_MAX_CHUNKS];
   __shared__ int abort_word;
   volatile int* abort_flag = &abort_word;
   float4* const row4 = reinterpret_cast<float4*>(ce_smem);
   const uint32_t row_addr = (uint32_t)__cvta_generic_to_shared(ce_smem);
   const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
   const int n4 = (C + 3) >> 2;                               // 16-byte units of a row (the pitch covers the last one)
-  const int q4 = (n4 + CE_ROW_CHUNKS - 1) / CE_ROW_CHUNKS;   // units per chunk (none is empty: the caller admits C >= 4096 only)
+  const int q4 = (n4 + nchunks - 1) / nchunks;               // units per chunk (none is empty: the caller admits C >= 4096 only)
   const int tid = threadIdx.x;
   if (tid == 0) {
-    for (int c = 0; c < CE_ROW_CHUNKS; ++c) ce_bar_init(bar0 + 8 * c, 1);
+    for (int c = 0; c < CE_ROW_MAX_CHUNKS; ++c) ce_bar_init(bar0 + 8 * c, 1);
     abort_word = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -659,7 +661,7 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
   };
   long long row = blockIdx.x;
   if (tid == 0 && row < rows)
-    for (int c = 0; c < CE_ROW_CHUNKS; ++c) request(row, c);
+    for (int c = 0; c < nchunks; ++c) request(row, c);
   bool ok = true;
   uint32_t failed_parity = 0;
   for (int it = 0; ok && row < rows; row += gridDim.x, ++it) {
@@ -667,7 +669,7 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
     const float t_early = targets[row];                        // asked for now by every thread, needed after the reduction
     // ---- pass 1: running maximum and sum, chunk by chunk as they arrive
     float m = -INFINITY, sum = 0.0f, m2 = 0.0f;                // m2 = -m log2(e), set with the first maximum
-    for (int c = 0; c < CE_ROW_CHUNKS; ++c) {
+    for (int c = 0; c < nchunks; ++c) {
       if (!ce_bar_wait(bar0 + 8 * c, parity, abort_flag, status)) { ok = false; break; }     // leaves the chunk loop only
       const int u1 = min((c + 1) * q4, n4);
       for (int u = c * q4 + tid; u < u1; u += CE_ROW_THREADS) {
@@ -704,7 +706,7 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
     }
     // ---- pass 2: the gradient over the row, in place; each chunk leaves as soon as the whole block has written it
     const long long next = row + gridDim.x;
-    for (int c = 0; c < CE_ROW_CHUNKS; ++c) {
+    for (int c = 0; c < nchunks; ++c) {
       const int u0 = c * q4, u1 = min(u0 + q4, n4);
       for (int u = u0 + tid; u < u1; u += CE_ROW_THREADS) {
         const float4 x = row4[u];
@@ -741,13 +743,13 @@ cross_entropy_row_in_smem_kernel(float* __restrict__ dlogits, long long ld_d, co
     }
     if (tid == 0 && next < rows) {
       asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-      request(next, CE_ROW_CHUNKS - 1);
+      request(next, nchunks - 1);
     }
   }
   if (tid == 0) {
     if (!ok) {     // giving up: let the copies of the row that was being waited for land (bounded) before shared memory is released
       const long long t0 = clock64();
-      for (int c = 0; c < CE_ROW_CHUNKS; ++c)
+      for (int c = 0; c < nchunks; ++c)
         while (!ce_bar_test(bar0 + 8 * c, failed_parity) && clock64() - t0 < 2000000000LL) {}
     }
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -1071,9 +1073,17 @@ extern "C" int gt_cross_entropy_fused(gt_ctx* ctx, float* loss, float* row_loss,
   if (vec && row_in_smem && C >= 4096 && C <= CE_ROW_MAX_CLASSES && grad_scale > 0.0f) {     // the kernel folds log2(grad_scale) into an exponent
     const int bytes = (int)((C + 3) / 4 * 16);
     GT_SMEM_OPT_IN(ctx, cross_entropy_row_in_smem_kernel, CE_ROW_MAX_CLASSES * 4);      // once, for the widest row admitted
+    // Chunks per row: eight for rows of up to 20 480 classes, chunks of about 40 KB beyond.  Measured at 50257 classes
+    // (201 KB), 4 / 5 / 6 / 7 / 8 / 10 / 13 chunks: 0.576 / 0.531 / 0.560 / 0.558 / 0.602 / 0.724 / 0.658 ms: large
+    // copies move faster, and the block's passes over a chunk should fill their last step (GRADTUITY_CE_CHUNKS overrides).
+    static const int ce_chunks_env = getenv("GRADTUITY_CE_CHUNKS") ? atoi(getenv("GRADTUITY_CE_CHUNKS")) : 0;
+    const long long units = (C + 3) / 4;
+    const int ce_chunks_rule = units >= 5120 ? (int)((units + 1280) / 2560) : CE_ROW_CHUNKS;
+    const int ce_chunks_want = ce_chunks_env > 0 ? ce_chunks_env : ce_chunks_rule;
+    const int ce_chunks = ce_chunks_want < 2 ? 2 : ce_chunks_want > CE_ROW_MAX_CHUNKS ? CE_ROW_MAX_CHUNKS : ce_chunks_want;
     const unsigned grid = (unsigned)(B < ctx->sm_count ? B : ctx->sm_count);
     cross_entropy_row_in_smem_kernel<<<grid, CE_ROW_THREADS, bytes, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss, row_lse,
-                                                                                  grad_scale, (int)C, (long long)B, ctx->d_status);
+                                                                                  grad_scale, (int)C, (long long)B, ce_chunks, ctx->d_status);
   } else if (vec) {
     GT_SMEM_OPT_IN(ctx, cross_entropy_fused_kernel<true>, CE_FUSED_SMEM);
     cross_entropy_fused_kernel<true><<<(unsigned)B, 512, CE_FUSED_SMEM, ctx->stream>>>(dlogits, ld_dlogits, logits, ld_logits, targets, row_loss,
