@@ -412,8 +412,14 @@ __global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(float* __restri
     const float mu = mean[row], rs = rstd[row];
     const float4* xr = reinterpret_cast<const float4*>(x + row * H);
     const float4* gr = reinterpret_cast<const float4*>(dy + row * H);
-    float4 xh[KV], dxh[KV];
+    float4 xh[KV], dxh[KV], old[KV];
     float s1 = 0.0f, s2 = 0.0f;
+    // what dx holds (when the result is added to it) is asked for together with x and dy, not after the row's sums are
+    // known: one memory latency per row instead of two
+    const bool add_old = dx != nullptr && dx_accumulate != 0;
+#pragma unroll
+    for (int c = 0; c < KV; ++c)
+      old[c] = add_old ? reinterpret_cast<const float4*>(dx + row * H)[c * 32 + lane] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < KV; ++c) {
       const float4 xv = xr[c * 32 + lane], g = gr[c * 32 + lane];
@@ -432,7 +438,7 @@ __global__ void __launch_bounds__(256) layernorm_bwd_warp_kernel(float* __restri
       for (int c = 0; c < KV; ++c) {
         float4 v = make_float4(k * ((float)H * dxh[c].x - s1 - xh[c].x * s2), k * ((float)H * dxh[c].y - s1 - xh[c].y * s2),
                                k * ((float)H * dxh[c].z - s1 - xh[c].z * s2), k * ((float)H * dxh[c].w - s1 - xh[c].w * s2));
-        if (dx_accumulate) { const float4 o = dxr[c * 32 + lane]; v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w; }
+        if (add_old) { v.x += old[c].x; v.y += old[c].y; v.z += old[c].z; v.w += old[c].w; }
         dxr[c * 32 + lane] = v;
         pd[c].x += v.x; pd[c].y += v.y; pd[c].z += v.z; pd[c].w += v.w;
       }
