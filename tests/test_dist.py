@@ -312,6 +312,15 @@ def test_two_ranks_sync_grads_over_gloo():
     assert r.returncode == 0, r.stderr[-3000:]
 
 
+def test_two_ranks_sync_grads_over_gloo_with_the_bucket_ramp(monkeypatch):
+    """Smaller buckets at the front of the parameter list move boundaries, not values: the same means come back."""
+    monkeypatch.setenv("GRADTUITY_BUCKET_RAMP", "3")
+    r = _launch("allreduce")
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = _launch("accumulate")
+    assert r.returncode == 0, r.stderr[-3000:]
+
+
 def test_launcher_stops_siblings_and_propagates_the_exit_code():
     t0 = time.monotonic()
     r = _launch("fail")
